@@ -1,0 +1,130 @@
+"""Oracle restatement of the reference GPTQ layer solver (test infrastructure).
+
+Follows llmc/compression/quantization/gptq.py: add_batch :254-295, hessian_sorting
+:58-64, process_hessian_and_weights :128-176, weight_transform :199-244,
+search_column_qparams :359-366, merge/update qparams :344-356, :398-409 and the
+deploy-time w_qdq :425-452.  Only the configuration the hot path covers is restated:
+nn.Linear, per_group with group_size == blocksize, static_groups off, no OWQ.
+"""
+import math
+import torch
+from . import quant_ref as Q
+
+
+def hessian_init(columns):
+    """layer_init (gptq.py:298-308)."""
+    return {'H': torch.zeros(columns, columns), 'nsamples': 0}
+
+
+def add_batch(state, inp):
+    """gptq.py:254-295 at world size 1: inp is (b, T, C) or (T, C) in the model dtype."""
+    if inp.dim() == 2:
+        inp = inp.unsqueeze(0)
+    b = inp.shape[0]
+    x = inp.reshape(-1, inp.shape[-1]).t()
+    state['H'] *= state['nsamples'] / (state['nsamples'] + b)
+    state['nsamples'] += b
+    x = math.sqrt(2 / state['nsamples']) * x.float()
+    state['H'] += x.matmul(x.t())
+    return state
+
+
+def prepare(W, H, percdamp=0.01, actorder=True):
+    """hessian_sorting + process_hessian_and_weights (gptq.py:58-64, :128-176).
+    Returns permuted fp32 W, upper Cholesky factor U of the damped inverse Hessian, perm, invperm."""
+    W = W.clone().float()
+    H = H.clone()
+    C = W.shape[1]
+    perm = torch.argsort(torch.diag(H), descending=True) if actorder else torch.arange(C)
+    dead = torch.diag(H) == 0
+    H[dead, dead] = 1
+    W[:, dead] = 0
+    W = W[:, perm]
+    H = H[perm][:, perm]
+    invperm = torch.argsort(perm)
+    damp = percdamp * torch.mean(torch.diag(H))
+    idx = torch.arange(C)
+    H[idx, idx] += damp
+    L = torch.linalg.cholesky(H)
+    Hinv = torch.cholesky_inverse(L)
+    U = torch.linalg.cholesky(Hinv, upper=True)
+    return W, U, perm, invperm
+
+
+def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128):
+    """gptq.py:199-244.  W is modified in place like the reference; returns
+    (kept weights `tmp`, Losses, per-group scales list, per-group zeros list)."""
+    assert group_size == blocksize
+    R, C = W.shape
+    tmp = torch.zeros_like(W)
+    Losses = torch.zeros_like(W)
+    g_scales, g_zeros = [], []
+    for i1 in range(0, C, blocksize):
+        i2 = min(i1 + blocksize, C)
+        W1 = W[:, i1:i2].clone()
+        U1 = U[i1:i2, i1:i2]
+        Err1 = torch.zeros_like(W1)
+        for i in range(i2 - i1):
+            w = W1[:, i].clone()
+            d = U1[i, i]
+            if (i1 + i) % group_size == 0:
+                cols = W[:, i1 + i: min(i1 + i + group_size, C)]
+                s, z, qmax, qmin = Q.int_qparams(cols, bit, sym)
+                g_scales.append(s)
+                g_zeros.append(z)
+            q = Q.int_dequant(Q.int_quant(w.unsqueeze(1), s, z, qmax, qmin), s, z).squeeze(1)
+            tmp[:, i1 + i] = w
+            Losses[:, i1 + i] = (w - q) ** 2 / (2 * d ** 2)
+            err = (w - q) / d
+            W1[:, i:] -= err.unsqueeze(1).matmul(U1[i, i:].unsqueeze(0))
+            Err1[:, i] = err
+        W[:, i2:] -= Err1.matmul(U[i1:i2, i2:])
+    return tmp, Losses, g_scales, g_zeros
+
+
+def merge_group_qparams(per_group):
+    """merge_qparams for per_group (gptq.py:353-355): list of (R,1) -> (R*n_g, 1)."""
+    return torch.stack(per_group, dim=1).reshape(-1, 1)
+
+
+def quantize_layer(W, H, bit=4, sym=False, group_size=128, blocksize=128,
+                   percdamp=0.01, actorder=True):
+    """layer_transform (gptq.py:114-117, :178-196): returns a dict with the reference's
+    per-layer results: weight (compensated, fp32, original column order), buf_scales,
+    buf_zeros (permuted-group order), buf_perm, buf_invperm, loss."""
+    Wp, U, perm, invperm = prepare(W, H, percdamp, actorder)
+    tmp, Losses, gs, gz = weight_transform(Wp, U, bit, sym, group_size, blocksize)
+    out = {
+        'weight': tmp[:, invperm].contiguous(),
+        'buf_scales': merge_group_qparams(gs),
+        'buf_perm': perm, 'buf_invperm': invperm,
+        'loss': float(Losses.sum()),
+        'U': U,
+    }
+    out['buf_zeros'] = None if sym else merge_group_qparams(gz)
+    return out
+
+
+def codes_permuted(res, bit=4, sym=False, group_size=128):
+    """Int codes as the reference defines them on the fake-quant path (gptq.py:425-452 with
+    quant.py:698-700): quant(weight[:, perm] grouped, buf_scales, buf_zeros).  (R, C), permuted order."""
+    qmin, qmax = Q.int_range(bit, sym)
+    w = res['weight'][:, res['buf_perm']]
+    z = torch.tensor(0.0) if sym else res['buf_zeros']
+    g = w.reshape(-1, group_size)
+    return Q.int_quant(g, res['buf_scales'], z, qmax, qmin).reshape(w.shape)
+
+
+def w_qdq(res, model_dtype, bit=4, sym=False, group_size=128):
+    """Deploy-time fake quant (gptq.py:425-452): permute, static qdq, un-permute, model dtype."""
+    w = res['weight'][:, res['buf_perm']]
+    z = torch.tensor(0.0) if sym else res['buf_zeros']
+    out = Q.int_fake_quant_static(w, res['buf_scales'], z, bit, sym, 'per_group', group_size)
+    return out.to(model_dtype)[:, res['buf_invperm']]
+
+
+def recon_error(W, Wq, X):
+    """||W X - Wq X|| / ||W X|| over calibration rows X (T, C), fp64 accumulate."""
+    Xd = X.double()
+    ref = Xd @ W.double().t()
+    return float((Xd @ (W.double() - Wq.double()).t()).norm() / ref.norm())

@@ -1,0 +1,134 @@
+"""Oracle restatement of the reference quantizer arithmetic (test infrastructure).
+
+Follows llmc/compression/quantization/quant.py:
+  reshape_tensor :611-641, get_minmax_range :134-145, get_qparams :544-558,
+  IntegerQuantizer.quant/dequant/quant_dequant :698-716,
+  fake_quant_weight_dynamic :832-868, real_quant_weight_dynamic :915-952,
+  fake_quant_act_dynamic :753-782, FloatQuantizer :963-1002, :1042-1080.
+
+Everything is evaluated with torch CPU ops *in the dtype of the input tensor*,
+because that is what the reference does: for a bf16 weight every intermediate
+(min, max, scale, zero, w/s ...) is rounded to bf16 after each op.
+"""
+import torch
+
+
+def int_range(bit, sym):
+    """qmin/qmax as 0-dim tensors with the reference's dtypes (quant.py:664-676)."""
+    if sym:
+        return torch.tensor(-(2 ** (bit - 1))), torch.tensor(2 ** (bit - 1) - 1)
+    return torch.tensor(0.0), torch.tensor(2 ** bit - 1)
+
+
+def group_view(t, granularity, group_size=None):
+    """quant.py:611-641 without padding: per_group -> (-1, g); otherwise identity."""
+    if granularity == 'per_group':
+        if t.shape[-1] >= group_size:
+            if t.shape[-1] % group_size:
+                raise ValueError(
+                    f'Dimension {t.shape[-1]} not divisible by group size {group_size}')
+            return t.reshape(-1, group_size)
+        return t
+    if granularity in ('per_channel', 'per_token'):
+        return t
+    raise NotImplementedError(granularity)
+
+
+def int_qparams(g, bit, sym):
+    """min/max -> (scales, zeros, qmax, qmin); quant.py:134-145 and :544-558."""
+    qmin, qmax = int_range(bit, sym)
+    mx = g.amax(dim=-1, keepdim=True)
+    mn = g.amin(dim=-1, keepdim=True)
+    if sym:
+        a = torch.max(mx.abs(), mn.abs()).clamp(min=1e-5)
+        return a / qmax, torch.tensor(0.0), qmax, qmin
+    s = (mx - mn).clamp(min=1e-5) / (qmax - qmin)
+    z = (qmin - torch.round(mn / s)).clamp(qmin, qmax)
+    return s, z, qmax, qmin
+
+
+def int_quant(g, s, z, qmax, qmin):
+    """quant.py:698-700 (round_zp=True, torch.round = half to even)."""
+    return torch.clamp(torch.round(g / s) + z, qmin, qmax)
+
+
+def int_dequant(q, s, z):
+    """quant.py:709-711."""
+    return (q - z) * s
+
+
+def int_fake_quant_dynamic(w, bit, sym, granularity, group_size=None):
+    """fake_quant_weight_dynamic / fake_quant_act_dynamic (quant.py:832-868, :753-782)."""
+    g = group_view(w, granularity, group_size)
+    s, z, qmax, qmin = int_qparams(g, bit, sym)
+    out = int_dequant(int_quant(g, s, z, qmax, qmin), s, z)
+    return out.reshape(w.shape).to(w.dtype)
+
+
+def int_fake_quant_static(w, s, z, bit, sym, granularity, group_size=None):
+    """fake_quant_weight_static (quant.py:784-830) without the optional args."""
+    qmin, qmax = int_range(bit, sym)
+    g = group_view(w, granularity, group_size)
+    out = int_dequant(int_quant(g, s, z, qmax, qmin), s, z)
+    return out.reshape(w.shape).to(w.dtype)
+
+
+def int_real_quant_dynamic(w, bit, sym, granularity, group_size=None):
+    """real_quant_weight_dynamic (quant.py:915-952): codes, scales (R,-1), zeros (R,-1)|None."""
+    g = group_view(w, granularity, group_size)
+    s, z, qmax, qmin = int_qparams(g, bit, sym)
+    q = int_quant(g, s, z, qmax, qmin).reshape(w.shape)
+    if bit == 8:
+        dt = torch.int8 if sym else torch.uint8
+    else:
+        dt = torch.int32
+    q = q.to(dt)
+    zeros = None if sym else z.to(dt).view(w.shape[0], -1)
+    return q, s.view(w.shape[0], -1), zeros
+
+
+def e4m3_round(x_f32):
+    """Stand-in for qtorch.quant.float_quantize(x, 4, 3, 'nearest') (quant.py:1065).
+
+    PARITY UNPINNED: qtorch is not vendored with the reference.  Restated as a
+    round-to-nearest-even cast onto the float8_e4m3fn grid, subnormals included,
+    which is the conversion the reference itself applies next in
+    real_quant_weight_* (quant.py:1182, :1210).
+    """
+    return x_f32.to(torch.float8_e4m3fn).float()
+
+
+def fp8_qparams(g):
+    """FloatQuantizer.get_tensor_qparams with use_qtorch (quant.py:1042-1058, :544-551)."""
+    mx = g.amax(dim=-1, keepdim=True)
+    mn = g.amin(dim=-1, keepdim=True)
+    a = torch.max(mx.abs(), mn.abs()).clamp(min=1e-5)
+    s = a / torch.tensor(448.0)
+    s[s == 0] = 1           # quant.py:1061
+    return s
+
+
+def fp8_fake_quant_dynamic(w):
+    """FloatQuantizer.fake_quant_{weight,act}_dynamic, e4m3, per_channel/per_token
+    (quant.py:1099-1108, :1141-1158, :1060-1080).  q stays fp32 (the cast at :1068 is
+    discarded), so the dequant product is fp32 and rounded once to the input dtype."""
+    s = fp8_qparams(w)
+    u = w / s + torch.tensor(0.0)
+    q = e4m3_round(u.float())
+    return ((q - torch.tensor(0.0)) * s).reshape(w.shape).to(w.dtype)
+
+
+def fp8_real_quant_dynamic(w):
+    """FloatQuantizer.real_quant_weight_dynamic (quant.py:1194-1220): e4m3 codes, scales (R,-1)."""
+    s = fp8_qparams(w)
+    u = w / s + torch.tensor(0.0)
+    q = e4m3_round(u.float())
+    return q.to(torch.float8_e4m3fn), s.view(w.shape[0], -1)
+
+
+def pack_int4_rows(codes_u8):
+    """Two 4-bit codes per byte along the input dim, low nibble first (the nibble order of
+    the compressed-tensors packer used by the reference's export path,
+    module_utils.py:931-955, which packs 8 nibbles per int32 little-nibble first)."""
+    c = codes_u8.to(torch.uint8)
+    return (c[..., 0::2] | (c[..., 1::2] << 4)).contiguous()

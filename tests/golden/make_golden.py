@@ -1,0 +1,177 @@
+"""Generates the golden fixtures in this directory by running the reference itself on CPU.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/LightCompress
+
+The reference is imported unmodified; three process-local shims make its CUDA-only lines
+run on CPU (`Tensor.cuda` -> identity, `torch.cuda.synchronize` -> no-op, a stub `accelerate`
+/ `easydict` when those packages are absent) and a single-rank gloo group satisfies the
+`dist.all_reduce` calls in `GPTQ.add_batch`.  The FP8 fixtures additionally substitute the
+un-vendored `qtorch.quant.float_quantize` by a float8_e4m3fn round trip; they are marked
+`pinned: False` for that reason.
+
+Inputs are small and stored next to the outputs, so the tests never need the reference.
+"""
+import contextlib
+import os
+import sys
+import types
+
+import torch
+
+
+def _import_reference(ref_root):
+    os.environ.update(WORLD_SIZE='1', RANK='0', LOCAL_RANK='0',
+                      MASTER_ADDR='127.0.0.1', MASTER_PORT='29613')
+    import torch.distributed as dist
+    import transformers  # noqa: F401  (must precede the accelerate stub)
+    if 'accelerate' not in sys.modules:
+        try:
+            import accelerate  # noqa: F401
+        except Exception:
+            acc = types.ModuleType('accelerate')
+            acc.init_empty_weights = contextlib.nullcontext
+            sys.modules['accelerate'] = acc
+    try:
+        import easydict  # noqa: F401
+    except ImportError:
+        ed = types.ModuleType('easydict')
+
+        class EasyDict(dict):
+            __getattr__ = dict.__getitem__
+            __setattr__ = dict.__setitem__
+        ed.EasyDict = EasyDict
+        sys.modules['easydict'] = ed
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    torch.cuda.synchronize = lambda *a, **k: None
+    torch.cuda.empty_cache = lambda *a, **k: None
+    sys.path.insert(0, ref_root)
+    if not dist.is_initialized():
+        dist.init_process_group('gloo', rank=0, world_size=1)
+    import llmc.compression.quantization.quant as rq
+    import llmc.compression.quantization.gptq as rg
+    return rq, rg
+
+
+def _rtn_inputs(gen, dtype, rows, cols):
+    w = (torch.randn(rows, cols, generator=gen) * 0.02)
+    # edge rows: constant group (1e-5 floor), exact zeros, tiny magnitudes, wide range,
+    # values on exact .5 multiples of a power-of-two step (round-half-even ties)
+    w[0, :128] = 0.0137
+    w[1, :] = 0.0
+    w[2, :128] = torch.randn(128, generator=gen) * 1e-7
+    w[3, :128] = torch.randn(128, generator=gen) * 50.0
+    step = 2.0 ** -6
+    w[4, :128] = (torch.arange(128) - 64).float() * step * 0.5
+    w[4, 0], w[4, 127] = -7.5 * step * 1.0, 7.5 * step
+    w[5, :128] = torch.linspace(0, 15, 128) * 0.25
+    return w.to(dtype)
+
+
+def make_rtn(rq, out_dir):
+    gen = torch.Generator().manual_seed(1001)
+    cases = {}
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for sym in (False, True):
+            for bit in (4, 8):
+                for gran, gs in (('per_group', 128), ('per_group', 64), ('per_channel', None)):
+                    w = _rtn_inputs(gen, dtype, 12, 384)
+                    kw = {'group_size': gs} if gs else {}
+                    qz = rq.IntegerQuantizer(bit, sym, gran, **kw)
+                    fq = qz.fake_quant_weight_dynamic(w.clone())
+                    codes, scales, zeros = qz.real_quant_weight_dynamic(w.clone())
+                    key = f'{str(dtype)[6:]}_{"sym" if sym else "asym"}_b{bit}_{gran}_{gs}'
+                    cases[key] = dict(w=w, bit=bit, sym=sym, granularity=gran, group_size=gs,
+                                      fake=fq, codes=codes, scales=scales, zeros=zeros)
+    # per-token activations (B, T, C)
+    for dtype in (torch.float32, torch.bfloat16):
+        for sym in (False, True):
+            x = torch.randn(2, 5, 320, generator=gen).to(dtype)
+            x[0, 0, 7] = 37.0
+            qz = rq.IntegerQuantizer(8, sym, 'per_token')
+            fq = qz.fake_quant_act_dynamic(x.clone())
+            key = f'act_{str(dtype)[6:]}_{"sym" if sym else "asym"}_b8_per_token'
+            cases[key] = dict(w=x, bit=8, sym=sym, granularity='per_token', group_size=None, fake=fq)
+    torch.save(cases, os.path.join(out_dir, 'rtn_int.pt'))
+    print('rtn_int.pt', len(cases), 'cases')
+
+
+def make_fp8(rq, out_dir):
+    rq.float_quantize = lambda x, e, m, rounding: x.to(torch.float8_e4m3fn).float()
+    gen = torch.Generator().manual_seed(5001)
+    cases = {}
+    for dtype in (torch.bfloat16, torch.float32, torch.float16):
+        w = (torch.randn(10, 352, generator=gen) * 0.02).to(dtype)
+        w[1, :] = 0
+        w[2, :] = (torch.randn(352, generator=gen) * 1e-6).to(dtype)
+        qz = rq.FloatQuantizer('e4m3', True, 'per_channel', use_qtorch=True)
+        fq = qz.fake_quant_weight_dynamic(w.clone())
+        codes, scales, _ = qz.real_quant_weight_dynamic(w.clone())
+        x = torch.randn(3, 4, 352, generator=gen).to(dtype)
+        qa = rq.FloatQuantizer('e4m3', True, 'per_token', use_qtorch=True)
+        fa = qa.fake_quant_act_dynamic(x.clone())
+        cases[str(dtype)[6:]] = dict(w=w, fake=fq, codes=codes.view(torch.uint8), scales=scales,
+                                     x=x, fake_act=fa, pinned=False)
+    torch.save(cases, os.path.join(out_dir, 'fp8_e4m3.pt'))
+    print('fp8_e4m3.pt', len(cases), 'cases')
+
+
+def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01):
+    """Drives the reference GPTQ class on one nn.Linear, bypassing its model plumbing."""
+    g = object.__new__(rg.GPTQ)
+    g.dev = torch.device('cpu')
+    g.wquantizer = rq.IntegerQuantizer(bit, sym, 'per_group', group_size=128)
+    g.true_sequential, g.static_groups, g.actorder = True, False, actorder
+    g.percdamp, g.blocksize, g.owq, g.chunk_num = percdamp, 128, False, 1
+    g.need_perm = actorder
+    g.layers_cache = {'l': {}}
+    g.model_dtype = W.dtype
+    layer = torch.nn.Linear(W.shape[1], W.shape[0], bias=False, dtype=W.dtype)
+    layer.weight.data = W.clone()
+    # collect_block_qparams leaves RTN buffers on the layer (base_blockwise_quantization.py:362-376)
+    _, s, z, qmax, qmin = g.wquantizer.get_tensor_qparams(layer.weight.data)
+    layer.register_buffer('buf_scales', s)
+    layer.register_buffer('buf_zeros', z)
+    layer.register_buffer('buf_qmax', qmax)
+    layer.register_buffer('buf_qmin', qmin)
+    g.layer_init(layer, 'l')
+    for i in range(X.shape[0]):
+        g.add_batch(layer, 'l', X[i:i + 1], None)
+    H = g.layers_cache['l']['H'].clone()
+    g.layer_transform(layer, 'l')
+    fq = g.w_qdq(layer, g.wquantizer)
+    perm = layer.buf_perm if actorder else torch.arange(W.shape[1])
+    codes = g.wquantizer.quant(layer.weight.data[:, perm].reshape(-1, 128), layer.buf_scales,
+                               layer.buf_zeros if not sym else torch.tensor(0.0),
+                               layer.buf_qmax, layer.buf_qmin).reshape(W.shape)
+    return dict(W=W, X=X, H=H, bit=bit, sym=sym, actorder=actorder, percdamp=percdamp,
+                weight=layer.weight.data.clone(), buf_scales=layer.buf_scales.clone(),
+                buf_zeros=None if sym else layer.buf_zeros.clone(),
+                buf_perm=perm.clone(), codes_perm=codes.to(torch.int16), w_qdq=fq.clone())
+
+
+def make_gptq(rq, rg, out_dir):
+    gen = torch.Generator().manual_seed(2001)
+    cases = {}
+    for name, R, C, ns, T, sym, act in (('asym_act', 48, 384, 6, 160, False, True),
+                                        ('sym_act', 32, 256, 4, 128, True, True),
+                                        ('asym_noact', 32, 256, 4, 128, False, False)):
+        W = (torch.randn(R, C, generator=gen) * 0.02).to(torch.bfloat16)
+        X = torch.randn(ns, T, C, generator=gen)
+        out_ch = torch.randperm(C, generator=gen)[:max(1, C // 100)]
+        X[:, :, out_ch] *= 20
+        X = X.to(torch.bfloat16)
+        cases[name] = _ref_gptq_layer(rq, rg, W, X, 4, sym, act)
+    torch.save(cases, os.path.join(out_dir, 'gptq_layer.pt'))
+    print('gptq_layer.pt', len(cases), 'cases')
+
+
+if __name__ == '__main__':
+    ref_root = sys.argv[1]
+    out_dir = os.path.dirname(os.path.abspath(__file__))
+    rq, rg = _import_reference(ref_root)
+    torch.set_num_threads(1)
+    make_rtn(rq, out_dir)
+    make_gptq(rq, rg, out_dir)
+    make_fp8(rq, out_dir)

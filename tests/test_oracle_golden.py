@@ -1,0 +1,62 @@
+"""The CPU oracle must reproduce, bit for bit, what the reference produced when the golden
+fixtures were generated (tests/golden/make_golden.py ran the reference itself on CPU)."""
+import torch
+
+from oracle import gptq_ref, quant_ref
+
+
+def _eq(a, b):
+    assert a.dtype == b.dtype and a.shape == b.shape
+    assert torch.equal(a.view(torch.uint8) if a.dtype == torch.float8_e4m3fn else a,
+                       b.view(torch.uint8) if b.dtype == torch.float8_e4m3fn else b)
+
+
+def test_rtn_int_oracle_matches_reference(golden):
+    cases = golden('rtn_int.pt')
+    assert len(cases) == 40
+    for key, c in cases.items():
+        fq = quant_ref.int_fake_quant_dynamic(c['w'], c['bit'], c['sym'], c['granularity'], c['group_size'])
+        _eq(fq, c['fake'])
+        if 'codes' in c:
+            q, s, z = quant_ref.int_real_quant_dynamic(c['w'], c['bit'], c['sym'], c['granularity'], c['group_size'])
+            _eq(q, c['codes'])
+            _eq(s, c['scales'])
+            if c['sym']:
+                assert z is None and c['zeros'] is None
+            else:
+                _eq(z, c['zeros'])
+
+
+def test_fp8_oracle_matches_reference_with_substituted_rounding(golden):
+    for key, c in golden('fp8_e4m3.pt').items():
+        assert c['pinned'] is False       # qtorch is not vendored: parity unpinned for the rounding call
+        _eq(quant_ref.fp8_fake_quant_dynamic(c['w']), c['fake'])
+        q, s = quant_ref.fp8_real_quant_dynamic(c['w'])
+        _eq(q.view(torch.uint8), c['codes'])
+        _eq(s, c['scales'])
+        _eq(quant_ref.fp8_fake_quant_dynamic(c['x']), c['fake_act'])
+
+
+def test_gptq_oracle_matches_reference(golden):
+    torch.set_num_threads(1)
+    for key, c in golden('gptq_layer.pt').items():
+        st = gptq_ref.hessian_init(c['W'].shape[1])
+        for i in range(c['X'].shape[0]):
+            gptq_ref.add_batch(st, c['X'][i:i + 1])
+        _eq(st['H'], c['H'])
+        res = gptq_ref.quantize_layer(c['W'], c['H'], bit=c['bit'], sym=c['sym'],
+                                      percdamp=c['percdamp'], actorder=c['actorder'])
+        _eq(res['buf_perm'], c['buf_perm'])
+        _eq(res['weight'], c['weight'])
+        _eq(res['buf_scales'], c['buf_scales'])
+        if not c['sym']:
+            _eq(res['buf_zeros'], c['buf_zeros'])
+        codes = gptq_ref.codes_permuted(res, c['bit'], c['sym'])
+        assert torch.equal(codes.to(torch.int16), c['codes_perm'])
+        _eq(gptq_ref.w_qdq(res, c['W'].dtype, c['bit'], c['sym']), c['w_qdq'])
+
+
+def test_group_not_divisible_raises():
+    import pytest
+    with pytest.raises(ValueError):
+        quant_ref.int_fake_quant_dynamic(torch.zeros(2, 200), 4, False, 'per_group', 128)
