@@ -1,0 +1,172 @@
+/*
+ * lc_b200.h -- C ABI of the B200 (sm_100a) kernels behind LightCompress's
+ * calibration-time quantization plugins (RTN / GPTQ / AWQ, IntegerQuantizer /
+ * FloatQuantizer).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name ends in `_host`.
+ *   - Nothing here allocates or frees memory: the caller passes every output and
+ *     every scratch buffer.
+ *   - Every function enqueues its work on `stream` and returns without
+ *     synchronising.  The int result is a host-side status (argument, shape and
+ *     alignment validation, launch errors).  Failures that only the device can
+ *     see (a bounded wait that expired) are written to the optional `int32_t*
+ *     status` word and must be read after the stream is synchronised.
+ *   - Matrices are row-major and contiguous.  "rows x cols" weights follow
+ *     torch.nn.Linear: rows = out_features, cols = in_features; quantization
+ *     groups run along cols.
+ *   - Reference citations are paths inside the LightCompress source tree.
+ */
+#ifndef LC_B200_H_
+#define LC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* lc_stream_t; /* a cudaStream_t / CUstream handle; NULL = legacy default stream */
+
+enum lc_status_code {
+  LC_OK = 0,
+  LC_ERR_ARG = -1,       /* null pointer / unknown enum / unsupported combination */
+  LC_ERR_SHAPE = -2,     /* sizes that the reference itself rejects (e.g. cols % group != 0) */
+  LC_ERR_ALIGN = -3,     /* pointer or row pitch not aligned as the kernel requires */
+  LC_ERR_ARCH = -4,      /* device is not sm_100 */
+  LC_ERR_WORKSPACE = -5, /* scratch buffer too small */
+  LC_ERR_NOT_PD = -6,    /* matrix not positive definite */
+  LC_ERR_TIMEOUT = -7,   /* device-side bounded wait expired (reported through *status) */
+  LC_ERR_CUDA = -8       /* CUDA runtime / driver error */
+};
+
+enum lc_dtype { LC_F32 = 0, LC_BF16 = 1, LC_F16 = 2 };
+
+/* How integer codes are written by lc_rtn_int_quant. */
+enum lc_code_fmt {
+  LC_CODES_NONE = 0,
+  LC_CODES_I32 = 1,  /* one int32 per element: dtype of IntegerQuantizer.real_quant_weight_* for bit != 8 */
+  LC_CODES_I8 = 2,   /* one byte per element (int8 if symmetric, uint8 otherwise): the bit == 8 dtype */
+  LC_CODES_PACK4 = 3 /* bits == 4 only: two codes per byte along cols, low nibble first, stored as q - qmin */
+};
+
+int lc_version(void);
+const char* lc_status_string(int status);
+
+/* Makes `device` current for the calling thread inside this library's CUDA runtime. */
+int lc_set_device(int device);
+
+/* ------------------------------------------------------------------------------------------
+ * Family 1: integer quant / dequant in one pass over HBM.
+ *
+ * Replaces IntegerQuantizer.get_tensor_qparams, quant, dequant, quant_dequant,
+ * fake_quant_weight_dynamic / _static, fake_quant_act_dynamic and real_quant_weight_dynamic
+ * (llmc/compression/quantization/quant.py:689-716, :753-868, :915-952) for calib_algo
+ * 'minmax', round_zp = True, granularity per_group / per_channel / per_token.
+ *
+ *   in         rows x cols, element type `dtype`
+ *   group      quantization group length along cols; 0 = the whole row (per_channel/per_token)
+ *   bits, sym  integer width (2..8) and symmetric flag; the code range is the reference's
+ *              (quant.py:664-676): sym -> [-2^(b-1), 2^(b-1)-1], asym -> [0, 2^b-1]
+ *   scales_in, zeros_in
+ *              NULL = dynamic (min/max computed here).  Non-NULL = static: one value per
+ *              group in `dtype`, laid out (rows * cols/group); zeros_in may be NULL when sym.
+ *   fake_out   rows x cols dequantised values in `dtype`, or NULL
+ *   codes_out  integer codes in the layout `code_fmt` names, or NULL with LC_CODES_NONE
+ *   scales_out, zeros_out
+ *              per-group scale / zero point in `dtype` (zero point is an integer held in a
+ *              float, as get_qparams returns it), or NULL
+ *
+ * Arithmetic is the reference's, op for op, in `dtype` (IEEE divide, round-half-even, a
+ * rounding to `dtype` after every torch-level op), so codes, scales, zeros and dequantised
+ * values are bit-identical to the reference's.
+ * ------------------------------------------------------------------------------------------ */
+int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t group,
+                     int bits, int sym, const void* scales_in, const void* zeros_in,
+                     void* fake_out, void* codes_out, int code_fmt, void* scales_out,
+                     void* zeros_out, lc_stream_t stream);
+
+/* FP8 e4m3 per-row (per_channel weights / per_token activations) quant / dequant.
+ * Replaces FloatQuantizer.get_tensor_qparams, quant, dequant, fake_quant_weight_dynamic,
+ * fake_quant_act_dynamic and real_quant_weight_dynamic with use_qtorch (quant.py:1042-1080,
+ * :1099-1108, :1141-1158, :1194-1220).  The third-party qtorch.float_quantize call
+ * (quant.py:1065) is evaluated as round-to-nearest-even onto float8_e4m3fn.
+ *   fake_out  rows x cols in `dtype`, or NULL;  codes_out  rows x cols e4m3 bytes, or NULL
+ *   scales_out rows values in `dtype`, or NULL */
+int lc_fp8_e4m3_quant(const void* in, int dtype, int64_t rows, int64_t cols, void* fake_out,
+                      void* codes_out, void* scales_out, lc_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Family 2: Hessian accumulation on the tcgen05 tensor cores.
+ *
+ * Replaces the matmul of GPTQ.add_batch (llmc/compression/quantization/gptq.py:283-290):
+ *     H <- beta * H + alpha * X^T X
+ *   X  tokens x cols, bf16, row-major (tokens of all sequences of the batch, flattened)
+ *   H  cols x cols fp32, full symmetric matrix is maintained
+ * cols must be a multiple of 8 (16-byte row pitch for TMA); X and H 16-byte aligned.
+ * Products of bf16 values are exact in fp32; accumulation is fp32 in tensor memory.
+ * Only tiles on or above the diagonal are computed; each is added to H and to its mirror.
+ * `ksplit` > 1 splits the token range over that many CTAs per tile (0 = choose); partial
+ * sums are combined with fp32 atomic adds, so the summation order may vary between runs.
+ * `status` (may be NULL) receives LC_ERR_TIMEOUT if a bounded pipeline wait expires.
+ * ------------------------------------------------------------------------------------------ */
+int lc_hessian_accum(const void* x_bf16, int64_t tokens, int64_t cols, float* H, float alpha,
+                     float beta, int ksplit, int32_t* status, lc_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Family 3: GPTQ layer solver pieces.
+ * ------------------------------------------------------------------------------------------ */
+
+/* diag_out[i] = H[i][i].  Feeds GPTQ.hessian_sorting's argsort (gptq.py:58-64). */
+int lc_gptq_diag(const float* H, int64_t cols, float* diag_out, lc_stream_t stream);
+
+/* The gather + dampening part of GPTQ.process_hessian_and_weights (gptq.py:135-170):
+ *   Wp[r][j] = dead(perm[j]) ? 0 : float(W[r][perm[j]])
+ *   Hp[i][j] = hscale * H[perm[i]][perm[j]]   (dead diagonal -> 1), then Hp[i][i] += damp
+ * where dead(c) means H[c][c] == 0 and damp = percdamp * mean(diag(Hp)).  `hscale` lets the
+ * caller keep H as the raw sum of X^T X and apply 2/nsamples here.
+ *   W rows x cols in `w_dtype`; perm int64 (cols) or NULL for identity
+ *   scratch: at least 1 float (receives damp) */
+int lc_gptq_permute_damp(const void* W, int w_dtype, const float* H, const int64_t* perm,
+                         int64_t rows, int64_t cols, float hscale, float percdamp, float* Wp,
+                         float* Hp, float* scratch, lc_stream_t stream);
+
+/* One 128-column block of GPTQ.weight_transform (gptq.py:199-241), group_size == blocksize:
+ * per row, asymmetric/symmetric int qparams from the block's current columns
+ * (search_column_qparams, gptq.py:359-366), then for each column quantise, keep the
+ * pre-quantisation value, propagate err * U[i][j] to the columns j > i of the block.
+ *   W       rows x cols fp32 (permuted order), updated in place: on return columns
+ *           [col0, col0+count) hold the kept ("tmp") values
+ *   U       cols x cols fp32 upper Cholesky factor of the damped inverse Hessian
+ *   err_out rows x 128 fp32: (w - q) / U[i][i] per column (zero for columns >= count)
+ *   scales, zeros  (rows * n_groups) fp32 in the reference's merged layout
+ *           (update_model_qparams, gptq.py:398-409): index r * n_groups + block
+ *   codes_u8 rows x cols bytes (q - qmin), permuted order, or NULL
+ *   loss_rows rows fp32, += sum over the block of (w-q)^2 / (2 U_ii^2), or NULL */
+int lc_gptq_block_quant(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0,
+                        int count, int bits, int sym, float* err_out, float* scales,
+                        float* zeros, int64_t n_groups, uint8_t* codes_u8, float* loss_rows,
+                        lc_stream_t stream);
+
+/* Trailing update of GPTQ.weight_transform (gptq.py:244):
+ *   W[:, col1:] -= Err[:, :k] * U[col0:col0+k, col1:]      (fp32, K = k <= 128) */
+int lc_gptq_trailing_update(float* W, const float* err, const float* U, int64_t rows,
+                            int64_t cols, int64_t col0, int k, int64_t col1,
+                            lc_stream_t stream);
+
+/* Whole GPTQ.weight_transform loop (gptq.py:199-244): alternates the two kernels above on
+ * `stream` without host synchronisation.  scratch_err: rows x 128 fp32. */
+int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t cols, int bits,
+                             int sym, float* scratch_err, float* scales, float* zeros,
+                             uint8_t* codes_u8, float* loss_rows, lc_stream_t stream);
+
+/* Un-permute the kept weights (gptq.py:186-193): out[r][perm[j]] = Wp[r][j], written in
+ * `out_dtype`.  perm NULL = identity. */
+int lc_gptq_unpermute(const float* Wp, const int64_t* perm, int64_t rows, int64_t cols,
+                      void* out, int out_dtype, lc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LC_B200_H_ */

@@ -1,0 +1,11 @@
+"""B200-native kernels for LightCompress's calibration-time quantization hot path.
+
+Host-side mirrors of the reference plugin interface (`IntegerQuantizer`, `FloatQuantizer`,
+`GPTQ`, `RTN`) over a C-ABI library of hand-written sm_100a CUDA kernels.
+"""
+from . import _lib  # noqa: F401  (raises if the CUDA library is not built)
+from .quant import FloatQuantizer, IntegerQuantizer  # noqa: F401
+from .gptq import GPTQ  # noqa: F401
+from .rtn import RTN  # noqa: F401
+
+__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'GPTQ', 'RTN']

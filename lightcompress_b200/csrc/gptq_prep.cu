@@ -1,0 +1,121 @@
+// Family 3: the data-movement steps around the GPTQ solver -- diagonal extraction for the
+// act-order sort, the permute + dampen gather that feeds the Cholesky factorisation, and the
+// final un-permute of the kept weights.
+#include "lc_common.cuh"
+
+namespace lc {
+namespace {
+
+__global__ void diag_kernel(const float* H, int64_t cols, float* out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < cols) out[i] = H[i * cols + i];
+}
+
+// damp = percdamp * mean_i( dead_i ? 1 : hscale * H_ii ); one CTA, fixed summation order
+__global__ void __launch_bounds__(1024) damp_kernel(const float* H, int64_t cols, float hscale, float percdamp,
+                                                    float* damp_out) {
+  __shared__ double red[32];
+  double acc = 0.0;
+  for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
+    const float h = H[i * cols + i];
+    acc += (h == 0.f) ? 1.0 : (double)(hscale * h);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+    damp_out[0] = percdamp * (float)(t / (double)cols);
+  }
+}
+
+__global__ void __launch_bounds__(256) permute_h_kernel(const float* H, const int64_t* perm, int64_t cols,
+                                                        float hscale, const float* damp, float* Hp) {
+  const int64_t i = blockIdx.y;
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= cols) return;
+  const int64_t pi = perm ? perm[i] : i;
+  const int64_t pj = perm ? perm[j] : j;
+  float v = hscale * H[pi * cols + pj];
+  if (i == j) {
+    if (v == 0.f) v = 1.f;
+    v += damp[0];
+  }
+  Hp[i * cols + j] = v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) permute_w_kernel(const T* W, const float* H, const int64_t* perm,
+                                                        int64_t rows, int64_t cols, float* Wp) {
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= cols) return;
+  const int64_t pj = perm ? perm[j] : j;
+  const bool dead = H[pj * cols + pj] == 0.f;
+  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+    Wp[r * cols + j] = dead ? 0.f : Elem<T>::to_f(W[r * cols + pj]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) unpermute_kernel(const float* Wp, const int64_t* perm, int64_t rows,
+                                                        int64_t cols, T* out) {
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= cols) return;
+  const int64_t pj = perm ? perm[j] : j;
+  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+    out[r * cols + pj] = Elem<T>::from_f(Wp[r * cols + j]);
+  }
+}
+
+}  // namespace
+}  // namespace lc
+
+extern "C" LC_API int lc_gptq_diag(const float* H, int64_t cols, float* diag_out, lc_stream_t stream) {
+  if (!H || !diag_out || cols <= 0) return LC_ERR_ARG;
+  lc::diag_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(H, cols,
+                                                                                                     diag_out);
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
+
+extern "C" LC_API int lc_gptq_permute_damp(const void* W, int w_dtype, const float* H, const int64_t* perm, int64_t rows,
+                                    int64_t cols, float hscale, float percdamp, float* Wp, float* Hp,
+                                    float* scratch, lc_stream_t stream) {
+  using namespace lc;
+  if (!W || !H || !Wp || !Hp || !scratch || rows <= 0 || cols <= 0) return LC_ERR_ARG;
+  if (w_dtype != LC_F32 && w_dtype != LC_BF16 && w_dtype != LC_F16) return LC_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  damp_kernel<<<1, 1024, 0, st>>>(H, cols, hscale, percdamp, scratch);
+  LC_LAUNCH_CHECK();
+  dim3 gh((unsigned)((cols + 255) / 256), (unsigned)cols);
+  permute_h_kernel<<<gh, 256, 0, st>>>(H, perm, cols, hscale, scratch, Hp);
+  LC_LAUNCH_CHECK();
+  dim3 gw((unsigned)((cols + 255) / 256), (unsigned)(rows < 1024 ? rows : 1024));
+  switch (w_dtype) {
+    case LC_F32: permute_w_kernel<float><<<gw, 256, 0, st>>>((const float*)W, H, perm, rows, cols, Wp); break;
+    case LC_BF16:
+      permute_w_kernel<__nv_bfloat16><<<gw, 256, 0, st>>>((const __nv_bfloat16*)W, H, perm, rows, cols, Wp);
+      break;
+    default: permute_w_kernel<__half><<<gw, 256, 0, st>>>((const __half*)W, H, perm, rows, cols, Wp); break;
+  }
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
+
+extern "C" LC_API int lc_gptq_unpermute(const float* Wp, const int64_t* perm, int64_t rows, int64_t cols, void* out,
+                                 int out_dtype, lc_stream_t stream) {
+  using namespace lc;
+  if (!Wp || !out || rows <= 0 || cols <= 0) return LC_ERR_ARG;
+  if (out_dtype != LC_F32 && out_dtype != LC_BF16 && out_dtype != LC_F16) return LC_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 g((unsigned)((cols + 255) / 256), (unsigned)(rows < 1024 ? rows : 1024));
+  switch (out_dtype) {
+    case LC_F32: unpermute_kernel<float><<<g, 256, 0, st>>>(Wp, perm, rows, cols, (float*)out); break;
+    case LC_BF16: unpermute_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(Wp, perm, rows, cols, (__nv_bfloat16*)out); break;
+    default: unpermute_kernel<__half><<<g, 256, 0, st>>>(Wp, perm, rows, cols, (__half*)out); break;
+  }
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}

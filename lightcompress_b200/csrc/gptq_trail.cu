@@ -1,0 +1,179 @@
+// Family 3: trailing update of the GPTQ solver,  W[:, col1:] -= Err * U[col0:col0+k, col1:].
+//
+// fp32 in, fp32 out, K <= 128, so the update is bound by the read-modify-write of W
+// (32 flop per byte); an fp32 FFMA tile kernel keeps the reference's fp32 products.
+// Err is stored k-major ([128][rows]) by the block kernel so that both operand tiles are
+// contiguous along the dimension the threads walk.
+//
+// CTA tile 128 (rows) x 128 (cols), 256 threads, 8x8 accumulators per thread, K in chunks of
+// 16 staged through shared memory with register prefetch of the next chunk.
+#include "lc_common.cuh"
+
+namespace lc {
+namespace {
+
+constexpr int TM = 128, TN = 128, TK = 16;
+
+struct TrailArgs {
+  float* W;
+  const float* err_t;  // [128][rows]
+  const float* U;
+  int64_t rows, cols, col0, col1;
+  int k;
+};
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) gptq_trail_kernel(TrailArgs a) {
+  __shared__ __align__(16) float As[2][TK][TM];
+  __shared__ __align__(16) float Bs[2][TK][TN];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int64_t m0 = (int64_t)blockIdx.y * TM;
+  const int64_t n0 = a.col1 + (int64_t)blockIdx.x * TN;
+
+  // global -> smem assignment: each thread moves 2 float4 of A and 2 of B per chunk
+  // A chunk: TK rows (k) x TM floats (m): 16 x 32 float4 = 512 float4
+  float4 pa[2], pb[2];
+  auto load_chunk = [&](int kc) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int v = tid + t * 256;
+      const int kk = v >> 5, c4 = (v & 31) * 4;
+      const int kg = kc * TK + kk;
+      float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vb = va;
+      if (kg < a.k) {
+        const float* pa_g = a.err_t + (int64_t)kg * a.rows + m0 + c4;
+        const float* pb_g = a.U + (a.col0 + kg) * a.cols + n0 + c4;
+        if (VEC) {
+          if (m0 + c4 < a.rows) va = *reinterpret_cast<const float4*>(pa_g);
+          if (n0 + c4 < a.cols) vb = *reinterpret_cast<const float4*>(pb_g);
+        } else {
+          if (m0 + c4 + 0 < a.rows) va.x = pa_g[0];
+          if (m0 + c4 + 1 < a.rows) va.y = pa_g[1];
+          if (m0 + c4 + 2 < a.rows) va.z = pa_g[2];
+          if (m0 + c4 + 3 < a.rows) va.w = pa_g[3];
+          if (n0 + c4 + 0 < a.cols) vb.x = pb_g[0];
+          if (n0 + c4 + 1 < a.cols) vb.y = pb_g[1];
+          if (n0 + c4 + 2 < a.cols) vb.z = pb_g[2];
+          if (n0 + c4 + 3 < a.cols) vb.w = pb_g[3];
+        }
+      }
+      pa[t] = va;
+      pb[t] = vb;
+    }
+  };
+  auto store_chunk = [&](int buf) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int v = tid + t * 256;
+      const int kk = v >> 5, c4 = (v & 31) * 4;
+      *reinterpret_cast<float4*>(&As[buf][kk][c4]) = pa[t];
+      *reinterpret_cast<float4*>(&Bs[buf][kk][c4]) = pb[t];
+    }
+  };
+
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  const int nchunks = (a.k + TK - 1) / TK;
+  load_chunk(0);
+  store_chunk(0);
+  __syncthreads();
+  for (int kc = 0; kc < nchunks; ++kc) {
+    const int buf = kc & 1;
+    if (kc + 1 < nchunks) load_chunk(kc + 1);
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    if (kc + 1 < nchunks) {
+      store_chunk(buf ^ 1);
+      __syncthreads();
+    }
+  }
+
+  // W -= acc
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (m >= a.rows) continue;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t n = n0 + (h == 0 ? tx * 4 : 64 + tx * 4);
+      float* p = a.W + m * a.cols + n;
+      if (VEC) {
+        if (n < a.cols) {
+          float4 c = *reinterpret_cast<float4*>(p);
+          c.x -= acc[i][h * 4 + 0];
+          c.y -= acc[i][h * 4 + 1];
+          c.z -= acc[i][h * 4 + 2];
+          c.w -= acc[i][h * 4 + 3];
+          *reinterpret_cast<float4*>(p) = c;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n + j < a.cols) p[j] -= acc[i][h * 4 + j];
+      }
+    }
+  }
+}
+
+}  // namespace
+
+int gptq_trail_launch(float* W, const float* err_t, const float* U, int64_t rows, int64_t cols, int64_t col0,
+                      int k, int64_t col1, cudaStream_t st) {
+  if (col1 >= cols) return LC_OK;
+  TrailArgs a{W, err_t, U, rows, cols, col0, col1, k};
+  dim3 grid((unsigned)((cols - col1 + TN - 1) / TN), (unsigned)((rows + TM - 1) / TM));
+  const bool vec = (cols % 4 == 0) && (rows % 4 == 0) && (col1 % 4 == 0) && aligned16(W) && aligned16(err_t) &&
+                   aligned16(U);
+  if (vec) gptq_trail_kernel<true><<<grid, 256, 0, st>>>(a);
+  else gptq_trail_kernel<false><<<grid, 256, 0, st>>>(a);
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
+
+int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0, int count,
+                      int bits, int sym, float* err_t, float* scales, float* zeros, int64_t n_groups,
+                      uint8_t* codes, float* loss_rows, cudaStream_t st);
+
+}  // namespace lc
+
+extern "C" LC_API int lc_gptq_trailing_update(float* W, const float* err, const float* U, int64_t rows, int64_t cols,
+                                       int64_t col0, int k, int64_t col1, lc_stream_t stream) {
+  if (!W || !err || !U) return LC_ERR_ARG;
+  if (rows <= 0 || cols <= 0 || k < 1 || k > 128 || col0 < 0 || col0 + k > cols || col1 < col0 + k) return LC_ERR_ARG;
+  return lc::gptq_trail_launch(W, err, U, rows, cols, col0, k, col1, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" LC_API int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t cols, int bits, int sym,
+                                        float* scratch_err, float* scales, float* zeros, uint8_t* codes_u8,
+                                        float* loss_rows, lc_stream_t stream) {
+  if (!W || !U || !scratch_err || !scales || !zeros) return LC_ERR_ARG;
+  if (rows <= 0 || cols <= 0 || bits < 2 || bits > 8) return LC_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t n_groups = (cols + 127) / 128;
+  if (loss_rows) LC_CHECK_CUDA(cudaMemsetAsync(loss_rows, 0, rows * sizeof(float), st));
+  for (int64_t i1 = 0; i1 < cols; i1 += 128) {
+    const int count = (int)((cols - i1 < 128) ? (cols - i1) : 128);
+    int rc = lc::gptq_block_launch(W, U, rows, cols, i1, count, bits, sym, scratch_err, scales, zeros, n_groups,
+                                   codes_u8, loss_rows, st);
+    if (rc != LC_OK) return rc;
+    rc = lc::gptq_trail_launch(W, scratch_err, U, rows, cols, i1, count, i1 + count, st);
+    if (rc != LC_OK) return rc;
+  }
+  return LC_OK;
+}

@@ -1,0 +1,400 @@
+// Family 1: single-pass integer quant / dequant (RTN) for per-group, per-channel and
+// per-token granularity.  HBM-bound: every input element is read once with a 128-bit load
+// and every requested output is written once.
+//
+// Three kernels:
+//   group_vec_kernel  group fits in <= 32 lanes x 16 bytes: a sub-warp of L lanes owns a group,
+//                     min/max by xor-shuffles, all lanes derive (scale, zero) redundantly.
+//   row_vec_kernel    long rows (per_channel / per_token, or groups > 512 bytes): one CTA per
+//                     row segment, the segment stays in registers between reduce and quantise.
+//   generic_kernel    any shape / alignment: scalar loads, two passes (second pass hits L2).
+#include "lc_common.cuh"
+
+namespace lc {
+namespace {
+
+template <typename T> struct Vec16 { uint4 raw; };
+
+template <typename T, int N>
+__device__ __forceinline__ void unpack(const uint4& v, float (&f)[N]) {
+  const T* p = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int i = 0; i < N; ++i) f[i] = Elem<T>::to_f(p[i]);
+}
+template <typename T, int N>
+__device__ __forceinline__ uint4 pack(const float (&f)[N]) {
+  uint4 v;
+  T* p = reinterpret_cast<T*>(&v);
+#pragma unroll
+  for (int i = 0; i < N; ++i) p[i] = Elem<T>::from_f(f[i]);
+  return v;
+}
+
+struct QuantArgs {
+  const void* in;
+  const void* scales_in;
+  const void* zeros_in;
+  void* fake_out;
+  void* codes_out;
+  void* scales_out;
+  void* zeros_out;
+  int64_t rows, cols, group, n_groups_total;
+  int bits, sym, code_fmt;
+  QRange qr;
+};
+
+// Writes the codes of one 16-byte input vector (N elements starting at element index e0).
+template <int N>
+__device__ __forceinline__ void store_codes(const QuantArgs& a, int64_t e0, const float (&q)[N]) {
+  if (a.code_fmt == LC_CODES_I32) {
+    int32_t* dst = reinterpret_cast<int32_t*>(a.codes_out) + e0;
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+      int4 v = make_int4(code_to_int(q[i]), code_to_int(q[i + 1]), code_to_int(q[i + 2]), code_to_int(q[i + 3]));
+      *reinterpret_cast<int4*>(dst + i) = v;
+    }
+  } else if (a.code_fmt == LC_CODES_I8) {
+    uint32_t w[N / 4];
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+      w[i / 4] = (uint32_t)(code_to_int(q[i]) & 0xff) | ((uint32_t)(code_to_int(q[i + 1]) & 0xff) << 8) |
+                 ((uint32_t)(code_to_int(q[i + 2]) & 0xff) << 16) | ((uint32_t)(code_to_int(q[i + 3]) & 0xff) << 24);
+    }
+    uint8_t* dst = reinterpret_cast<uint8_t*>(a.codes_out) + e0;
+    if (N == 4) {
+      *reinterpret_cast<uint32_t*>(dst) = w[0];
+    } else {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[N / 4 - 1]);
+    }
+  } else if (a.code_fmt == LC_CODES_PACK4) {
+    const int qmin = (int)a.qr.qmin;
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) w |= (uint32_t)((code_to_int(q[i]) - qmin) & 0xf) << (4 * i);
+    uint8_t* dst = reinterpret_cast<uint8_t*>(a.codes_out) + (e0 >> 1);
+    if (N == 4) {
+      *reinterpret_cast<uint16_t*>(dst) = (uint16_t)w;
+    } else {
+      *reinterpret_cast<uint32_t*>(dst) = w;
+    }
+  }
+}
+
+// ---- kernel A: L lanes per group, U groups in flight per thread --------------------------------
+template <typename T, int L, int U>
+__global__ void __launch_bounds__(256) group_vec_kernel(QuantArgs a) {
+  using E = Elem<T>;
+  constexpr int N = E::kPerVec;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int sub = threadIdx.x % L;  // lane inside the group
+  const int64_t groups_per_sweep = nthreads / L;
+  const uint4* in = reinterpret_cast<const uint4*>(a.in);
+  const T* s_in = reinterpret_cast<const T*>(a.scales_in);
+  const T* z_in = reinterpret_cast<const T*>(a.zeros_in);
+  const bool is_static = a.scales_in != nullptr;
+
+  // The loop bound is warp-uniform (first group of the warp) because every lane must reach the
+  // full-mask shuffles below; lanes whose own group is past the end are masked by ok[u].
+  const int64_t lane_group = (threadIdx.x & 31) / L;
+  for (int64_t gw = (tid - (threadIdx.x & 31)) / L; gw < a.n_groups_total; gw += groups_per_sweep * U) {
+    const int64_t g0 = gw + lane_group;
+    uint4 v[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t g = g0 + (int64_t)u * groups_per_sweep;
+      ok[u] = g < a.n_groups_total;
+      if (ok[u]) v[u] = __ldcs(in + g * L + sub);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t g = g0 + (int64_t)u * groups_per_sweep;
+      // inactive sub-warps still take part in the shuffles of their (fully inactive) group
+      float f[N];
+      float s, z;
+      if (ok[u]) unpack<T, N>(v[u], f);
+      if (!is_static) {
+        float mx = ok[u] ? f[0] : 0.f, mn = mx;
+        if (ok[u]) {
+#pragma unroll
+          for (int i = 1; i < N; ++i) {
+            mx = nan_max(mx, f[i]);
+            mn = nan_min(mn, f[i]);
+          }
+        }
+#pragma unroll
+        for (int o = L / 2; o > 0; o >>= 1) {
+          mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        }
+        int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
+      } else if (ok[u]) {
+        s = E::to_f(s_in[g]);
+        z = (a.sym || z_in == nullptr) ? 0.f : E::to_f(z_in[g]);
+      }
+      if (!ok[u]) continue;
+      float q[N], d[N];
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        q[i] = int_quant<T>(f[i], s, z, a.qr);
+        d[i] = int_dequant<T>(q[i], s, z);
+      }
+      const int64_t vidx = g * L + sub;
+      if (a.fake_out) __stcs(reinterpret_cast<uint4*>(a.fake_out) + vidx, pack<T, N>(d));
+      if (a.codes_out) store_codes<N>(a, vidx * N, q);
+      if (sub == 0) {
+        if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(s);
+        if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(z);
+      }
+    }
+  }
+}
+
+// ---- kernel B: one CTA per group (a long row segment), V vectors per thread in registers ------
+template <typename T, int V>
+__global__ void __launch_bounds__(256) row_vec_kernel(QuantArgs a) {
+  using E = Elem<T>;
+  constexpr int N = E::kPerVec;
+  __shared__ float s_mx[8], s_mn[8];
+  const int64_t nvec = a.group / N;  // vectors per group
+  const T* s_in = reinterpret_cast<const T*>(a.scales_in);
+  const T* z_in = reinterpret_cast<const T*>(a.zeros_in);
+  const bool is_static = a.scales_in != nullptr;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  for (int64_t g = blockIdx.x; g < a.n_groups_total; g += gridDim.x) {
+    const uint4* in = reinterpret_cast<const uint4*>(a.in) + g * nvec;
+    uint4 v[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const int64_t i = threadIdx.x + (int64_t)k * 256;
+      if (i < nvec) v[k] = __ldcs(in + i);
+    }
+    float s, z;
+    if (!is_static) {
+      float mx = -INFINITY, mn = INFINITY;
+      bool any = false;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const int64_t i = threadIdx.x + (int64_t)k * 256;
+        if (i < nvec) {
+          float f[N];
+          unpack<T, N>(v[k], f);
+#pragma unroll
+          for (int e = 0; e < N; ++e) {
+            mx = nan_max(mx, f[e]);
+            mn = nan_min(mn, f[e]);
+          }
+          any = true;
+        }
+      }
+      (void)any;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      }
+      if (lane == 0) {
+        s_mx[warp] = mx;
+        s_mn[warp] = mn;
+      }
+      __syncthreads();
+      mx = s_mx[0];
+      mn = s_mn[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) {
+        mx = nan_max(mx, s_mx[w]);
+        mn = nan_min(mn, s_mn[w]);
+      }
+      __syncthreads();
+      int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
+    } else {
+      s = E::to_f(s_in[g]);
+      z = (a.sym || z_in == nullptr) ? 0.f : E::to_f(z_in[g]);
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const int64_t i = threadIdx.x + (int64_t)k * 256;
+      if (i < nvec) {
+        float f[N], q[N], d[N];
+        unpack<T, N>(v[k], f);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+          q[e] = int_quant<T>(f[e], s, z, a.qr);
+          d[e] = int_dequant<T>(q[e], s, z);
+        }
+        const int64_t vidx = g * nvec + i;
+        if (a.fake_out) __stcs(reinterpret_cast<uint4*>(a.fake_out) + vidx, pack<T, N>(d));
+        if (a.codes_out) store_codes<N>(a, vidx * N, q);
+      }
+    }
+    if (threadIdx.x == 0) {
+      if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(s);
+      if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(z);
+    }
+  }
+}
+
+// ---- kernel C: any group length / alignment; scalar, two passes --------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) generic_kernel(QuantArgs a) {
+  using E = Elem<T>;
+  __shared__ float s_mx[8], s_mn[8];
+  const T* s_in = reinterpret_cast<const T*>(a.scales_in);
+  const T* z_in = reinterpret_cast<const T*>(a.zeros_in);
+  const bool is_static = a.scales_in != nullptr;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t g = blockIdx.x; g < a.n_groups_total; g += gridDim.x) {
+    const T* in = reinterpret_cast<const T*>(a.in) + g * a.group;
+    float s, z;
+    if (!is_static) {
+      float mx = -INFINITY, mn = INFINITY;
+      for (int64_t i = threadIdx.x; i < a.group; i += 256) {
+        const float f = E::to_f(in[i]);
+        mx = nan_max(mx, f);
+        mn = nan_min(mn, f);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      }
+      if (lane == 0) {
+        s_mx[warp] = mx;
+        s_mn[warp] = mn;
+      }
+      __syncthreads();
+      mx = s_mx[0];
+      mn = s_mn[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) {
+        mx = nan_max(mx, s_mx[w]);
+        mn = nan_min(mn, s_mn[w]);
+      }
+      __syncthreads();
+      int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
+    } else {
+      s = E::to_f(s_in[g]);
+      z = (a.sym || z_in == nullptr) ? 0.f : E::to_f(z_in[g]);
+    }
+    const int qmin = (int)a.qr.qmin;
+    // PACK4 pairs never straddle threads: each thread handles element pairs
+    for (int64_t i = 2 * (int64_t)threadIdx.x; i < a.group; i += 512) {
+      float q2[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (i + e >= a.group) { q2[e] = a.qr.qmin; continue; }
+        const float f = E::to_f(in[i + e]);
+        const float q = int_quant<T>(f, s, z, a.qr);
+        q2[e] = q;
+        const int64_t idx = g * a.group + i + e;
+        if (a.fake_out) reinterpret_cast<T*>(a.fake_out)[idx] = E::from_f(int_dequant<T>(q, s, z));
+        if (a.code_fmt == LC_CODES_I32) reinterpret_cast<int32_t*>(a.codes_out)[idx] = code_to_int(q);
+        if (a.code_fmt == LC_CODES_I8) reinterpret_cast<uint8_t*>(a.codes_out)[idx] = (uint8_t)(code_to_int(q) & 0xff);
+      }
+      if (a.code_fmt == LC_CODES_PACK4) {
+        // group and cols are even here (checked on the host)
+        reinterpret_cast<uint8_t*>(a.codes_out)[(g * a.group + i) >> 1] =
+            (uint8_t)(((code_to_int(q2[0]) - qmin) & 0xf) | (((code_to_int(q2[1]) - qmin) & 0xf) << 4));
+      }
+    }
+    if (threadIdx.x == 0) {
+      if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(s);
+      if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(z);
+    }
+  }
+}
+
+template <typename T, int L>
+void launch_group_vec(const QuantArgs& a, cudaStream_t st) {
+  constexpr int U = 4;
+  const int64_t threads_needed = (a.n_groups_total * L + U - 1) / U;
+  int64_t blocks = (threads_needed + 255) / 256;
+  const int64_t cap = (int64_t)kNumSMsB200 * 8 * 4;  // a few waves of 8 resident CTAs per SM
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  group_vec_kernel<T, L, U><<<(unsigned)blocks, 256, 0, st>>>(a);
+}
+
+template <typename T>
+int dispatch(const QuantArgs& a, cudaStream_t st) {
+  constexpr int N = Elem<T>::kPerVec;
+  const bool ptr_ok = aligned16(a.in) && (!a.fake_out || aligned16(a.fake_out)) &&
+                      (!a.codes_out || aligned16(a.codes_out));
+  const bool vec_ok = ptr_ok && (a.group % N == 0);
+  const int64_t lanes = a.group / N;
+  if (vec_ok && lanes <= 32 && (lanes & (lanes - 1)) == 0) {
+    switch ((int)lanes) {
+      case 32: launch_group_vec<T, 32>(a, st); break;
+      case 16: launch_group_vec<T, 16>(a, st); break;
+      case 8: launch_group_vec<T, 8>(a, st); break;
+      case 4: launch_group_vec<T, 4>(a, st); break;
+      case 2: launch_group_vec<T, 2>(a, st); break;
+      default: launch_group_vec<T, 1>(a, st); break;
+    }
+  } else if (vec_ok && lanes <= 256 * 16) {
+    int64_t blocks = a.n_groups_total;
+    const int64_t cap = (int64_t)kNumSMsB200 * 8 * 8;
+    if (blocks > cap) blocks = cap;
+    if (lanes <= 256) row_vec_kernel<T, 1><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else if (lanes <= 512) row_vec_kernel<T, 2><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else if (lanes <= 1024) row_vec_kernel<T, 4><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else if (lanes <= 2048) row_vec_kernel<T, 8><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else row_vec_kernel<T, 16><<<(unsigned)blocks, 256, 0, st>>>(a);
+  } else {
+    int64_t blocks = a.n_groups_total;
+    const int64_t cap = (int64_t)kNumSMsB200 * 8 * 8;
+    if (blocks > cap) blocks = cap;
+    generic_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(a);
+  }
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
+
+}  // namespace
+}  // namespace lc
+
+extern "C" LC_API int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t group,
+                                int bits, int sym, const void* scales_in, const void* zeros_in,
+                                void* fake_out, void* codes_out, int code_fmt, void* scales_out,
+                                void* zeros_out, lc_stream_t stream) {
+  using namespace lc;
+  if (rows < 0 || cols < 0 || group < 0) return LC_ERR_ARG;
+  if (bits < 2 || bits > 8) return LC_ERR_ARG;
+  if (dtype != LC_F32 && dtype != LC_BF16 && dtype != LC_F16) return LC_ERR_ARG;
+  if (code_fmt < LC_CODES_NONE || code_fmt > LC_CODES_PACK4) return LC_ERR_ARG;
+  if ((code_fmt != LC_CODES_NONE) != (codes_out != nullptr)) return LC_ERR_ARG;
+  if (code_fmt == LC_CODES_PACK4 && bits != 4) return LC_ERR_ARG;
+  if (rows == 0 || cols == 0) return LC_OK;
+  if (in == nullptr) return LC_ERR_ARG;
+  // IntegerQuantizer.reshape_tensor (quant.py:611-631): a last dim shorter than the group is
+  // left un-grouped; a non-divisible one is an error.
+  if (group == 0 || group > cols) group = cols;
+  if (cols % group != 0) return LC_ERR_SHAPE;
+  if (code_fmt == LC_CODES_PACK4 && (group % 2 != 0)) return LC_ERR_SHAPE;
+  if (scales_in == nullptr && zeros_in != nullptr) return LC_ERR_ARG;
+
+  QuantArgs a;
+  a.in = in;
+  a.scales_in = scales_in;
+  a.zeros_in = zeros_in;
+  a.fake_out = fake_out;
+  a.codes_out = codes_out;
+  a.scales_out = scales_out;
+  a.zeros_out = zeros_out;
+  a.rows = rows;
+  a.cols = cols;
+  a.group = group;
+  a.n_groups_total = rows * (cols / group);
+  a.bits = bits;
+  a.sym = sym ? 1 : 0;
+  a.code_fmt = code_fmt;
+  a.qr = int_qrange(bits, a.sym);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case LC_F32: return dispatch<float>(a, st);
+    case LC_BF16: return dispatch<__nv_bfloat16>(a, st);
+    default: return dispatch<__half>(a, st);
+  }
+}

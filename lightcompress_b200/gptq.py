@@ -1,0 +1,181 @@
+"""Host-side mirror of the reference GPTQ algorithm's per-layer hot methods.
+
+Method names, arguments and the buffers left on each layer follow
+llmc/compression/quantization/gptq.py: layer_init :298-308, add_batch :254-295,
+layer_transform :114-117 (hessian_sorting :58-64, process_hessian_and_weights :128-176,
+update_layer_with_transformed_weights :178-196, weight_transform :199-244,
+update_model_qparams :398-409), w_qdq :425-452, free :466-471.  `plugin.install` binds them
+onto the reference's registered `GPTQ` class; used stand-alone the class drives one or more
+`nn.Linear` layers directly.
+
+Differences in schedule, not in result: the Hessian is kept as the raw sum of X^T X and scaled
+by 2/nsamples once, and with several ranks it is all-reduced once per layer (in
+`layer_transform`) instead of after every `add_batch` call.
+"""
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from .quant import IntegerQuantizer
+
+
+class GPTQ:
+    def __init__(self, wquantizer=None, special=None, model_dtype=torch.bfloat16, **wq_kwargs):
+        special = dict(special or {})
+        self.wquantizer = wquantizer or IntegerQuantizer(4, False, 'per_group', group_size=128, **wq_kwargs)
+        self.true_sequential = special.get('true_sequential', True)
+        self.static_groups = special.get('static_groups', False)
+        self.actorder = special.get('actorder', True)
+        self.percdamp = special.get('percdamp', 0.01)
+        self.blocksize = special.get('blocksize', 128)
+        self.owq = special.get('owq', False)
+        self.chunk_num = special.get('chunk_num', 1)
+        self.emit_codes = special.get('emit_codes', True)
+        self.model_dtype = model_dtype
+        self.layers_cache = {}
+        self._check_config()
+        self.need_perm = (self.wquantizer.granularity == 'per_group' and not self.static_groups
+                          and self.actorder)
+
+    def _check_config(self):
+        wq = self.wquantizer
+        if self.owq or self.static_groups:
+            raise NotImplementedError('owq / static_groups are outside the B200 hot path')
+        if wq.granularity != 'per_group' or wq.group_size != 128 or self.blocksize != 128:
+            # gptq.py:216-223 reads group statistics that are only well defined when a group
+            # starts at a block boundary; the kernels implement group_size == blocksize == 128.
+            raise NotImplementedError('GPTQ kernels need per_group with group_size == blocksize == 128')
+        wq._check_supported()
+
+    # ---- Hessian ---------------------------------------------------------------------------
+    @torch.no_grad()
+    def layer_init(self, layer, name):
+        cols = layer.weight.shape[1]
+        self.layers_cache[name] = {
+            'H': torch.zeros((cols, cols), device=layer.weight.device, dtype=torch.float32),
+            'nsamples': 0, 'columns': cols,
+            'status': torch.zeros(1, dtype=torch.int32, device=layer.weight.device),
+        }
+
+    @torch.no_grad()
+    def add_batch(self, layer, name, inp, out=None):
+        """H_raw += X^T X over the tokens of `inp` ((b, T, C) or (T, C)); nsamples += b."""
+        st = self.layers_cache[name]
+        if inp.dim() == 2:
+            inp = inp.unsqueeze(0)
+        b = inp.shape[0]
+        x = inp.reshape(-1, inp.shape[-1])
+        if x.dtype != torch.bfloat16:
+            raise NotImplementedError('the Hessian kernel takes bf16 activations')
+        x = x if x.is_contiguous() else x.contiguous()
+        L.require_cuda(x)
+        L.call('lc_hessian_accum', L.ptr(x), x.shape[0], x.shape[1], L.ptr(st['H']), 1.0, 1.0, 0,
+               L.ptr(st['status']), L.stream_of(x))
+        st['nsamples'] += b
+
+    def _finish_hessian(self, name):
+        """All-reduce once per layer (gptq.py:292-295 does it per call); returns (H_raw, 2/n)."""
+        st = self.layers_cache[name]
+        n = st['nsamples']
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(st['H'], op=dist.ReduceOp.SUM)
+            nt = torch.tensor([n], dtype=torch.int64, device=st['H'].device)
+            dist.all_reduce(nt, op=dist.ReduceOp.SUM)
+            n = int(nt.item())
+        code = int(st['status'].item())
+        if code != 0:
+            raise L.LcError('lc_hessian_accum', code, L.status_string(code))
+        if n == 0:
+            raise RuntimeError(f'no calibration samples were accumulated for layer {name}')
+        return st['H'], 2.0 / n
+
+    # ---- solver ----------------------------------------------------------------------------
+    @torch.no_grad()
+    def layer_transform(self, layer, name, rows=None):
+        """Quantises `layer` in place like the reference: weight.data becomes the fp32
+        error-compensated weight and buf_scales / buf_zeros / buf_perm / buf_invperm are
+        registered.  `rows=(r0, r1)` restricts the solve to a row range (rows are independent);
+        the caller then gathers the pieces."""
+        H, hscale = self._finish_hessian(name)
+        res = self.solve(layer.weight.data, H, hscale, rows=rows)
+        if rows is None:
+            self._install(layer, res)
+        return res
+
+    @torch.no_grad()
+    def solve(self, W, H, hscale=1.0, rows=None):
+        wq = self.wquantizer
+        L.require_cuda(W, H)
+        W = W if W.is_contiguous() else W.contiguous()
+        if rows is not None:
+            W = W[rows[0]:rows[1]]
+        R, C = W.shape
+        dev = W.device
+        stream = L.stream_of(W)
+        n_groups = (C + 127) // 128
+        if self.actorder:
+            diag = torch.empty(C, dtype=torch.float32, device=dev)
+            L.call('lc_gptq_diag', L.ptr(H), C, L.ptr(diag), stream)
+            perm = torch.argsort(diag, descending=True)
+            invperm = torch.argsort(perm)
+        else:
+            perm = invperm = None
+        Wp = torch.empty((R, C), dtype=torch.float32, device=dev)
+        Hp = torch.empty((C, C), dtype=torch.float32, device=dev)
+        scratch = torch.empty(4, dtype=torch.float32, device=dev)
+        L.call('lc_gptq_permute_damp', L.ptr(W), L.lc_dtype(W), L.ptr(H), L.ptr(perm), R, C, float(hscale),
+               float(self.percdamp), L.ptr(Wp), L.ptr(Hp), L.ptr(scratch), stream)
+        U = self.inverse_cholesky_upper(Hp)
+        del Hp
+        err = torch.empty((128, R), dtype=torch.float32, device=dev)
+        scales = torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev)
+        zeros = torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev)
+        codes = torch.empty((R, C), dtype=torch.uint8, device=dev) if self.emit_codes else None
+        loss_rows = torch.empty(R, dtype=torch.float32, device=dev)
+        L.call('lc_gptq_weight_transform', L.ptr(Wp), L.ptr(U), R, C, int(wq.bit), int(wq.sym), L.ptr(err),
+               L.ptr(scales), L.ptr(zeros), L.ptr(codes), L.ptr(loss_rows), stream)
+        out = torch.empty((R, C), dtype=torch.float32, device=dev)
+        L.call('lc_gptq_unpermute', L.ptr(Wp), L.ptr(perm), R, C, L.ptr(out), L.LC_F32, stream)
+        return {'weight': out, 'buf_scales': scales, 'buf_zeros': None if wq.sym else zeros,
+                'buf_perm': perm, 'buf_invperm': invperm, 'codes_perm': codes, 'loss_rows': loss_rows}
+
+    @staticmethod
+    def inverse_cholesky_upper(Hp):
+        """U with U^T U = Hp^-1 (gptq.py:172-174): cuSOLVER through torch, on the current stream.
+        Raises torch.linalg.LinAlgError when Hp is not positive definite, like the reference."""
+        Lc = torch.linalg.cholesky(Hp)
+        Hinv = torch.cholesky_inverse(Lc)
+        del Lc
+        return torch.linalg.cholesky(Hinv, upper=True)
+
+    def _install(self, layer, res):
+        layer.weight.data = res['weight'].reshape(layer.weight.shape)
+        wq = self.wquantizer
+        for k in ('buf_scales', 'buf_zeros', 'buf_perm', 'buf_invperm'):
+            v = res[k]
+            if v is None:
+                continue
+            if k in layer._buffers:
+                layer._buffers[k] = v
+            else:
+                layer.register_buffer(k, v)
+        if 'buf_qmax' not in layer._buffers:
+            layer.register_buffer('buf_qmax', wq.qmax.to(layer.weight.device))
+            layer.register_buffer('buf_qmin', wq.qmin.to(layer.weight.device))
+
+    @torch.no_grad()
+    def w_qdq(self, module, wquantizer):
+        """Deploy-time fake quant (gptq.py:425-452)."""
+        weight = module.weight
+        if self.need_perm:
+            weight = weight[:, module.buf_perm]
+        args = {'scales': module.buf_scales, 'zeros': getattr(module, 'buf_zeros', None),
+                'qmax': module.buf_qmax, 'qmin': module.buf_qmin}
+        weight = wquantizer.fake_quant_weight_static(weight, args).to(self.model_dtype)
+        if self.need_perm:
+            weight = weight[:, module.buf_invperm]
+        return weight
+
+    @torch.no_grad()
+    def free(self, name):
+        del self.layers_cache[name]

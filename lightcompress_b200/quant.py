@@ -1,0 +1,269 @@
+"""Host-side mirrors of the reference quantizer objects.
+
+`IntegerQuantizer` and `FloatQuantizer` keep the constructor signature, attributes and method
+names of llmc/compression/quantization/quant.py (BaseQuantizer :48-103, IntegerQuantizer
+:660-959, FloatQuantizer :962-1228) so that the algorithm classes and replacement modules that
+call them work unchanged, but every method body is one launch of a fused sm_100a kernel through
+the C ABI.  Configurations outside the accelerated path (calib_algo other than 'minmax',
+per_tensor / per_head / per_block granularity, round_zp=False, mixed-precision index args)
+raise NotImplementedError: there is no fallback.
+"""
+import torch
+
+from . import _lib as L
+
+_INT_GRANS = ('per_group', 'per_channel', 'per_token')
+
+
+class BaseQuantizer(object):
+    """Constructor contract of quant.py:48-103."""
+
+    def __init__(self, bit, symmetric, granularity, **kwargs):
+        self.bit = bit
+        self.sym = symmetric
+        self.granularity = granularity
+        self.kwargs = kwargs
+        self.calib_algo = kwargs.get('calib_algo', 'minmax')
+        if granularity == 'per_group':
+            self.group_size = kwargs['group_size']
+        elif granularity == 'per_head':
+            self.head_num = kwargs['head_num']
+        elif granularity == 'per_block':
+            self.block_size = kwargs['block_size']
+        self.round_zp = kwargs.get('round_zp', True)
+        self.ste = kwargs.get('ste', False)
+        self.ste_all = bool(kwargs.get('ste_all', False))
+
+    def _check_supported(self):
+        if self.calib_algo != 'minmax':
+            raise NotImplementedError(f"calib_algo '{self.calib_algo}' is outside the B200 hot path")
+        if self.granularity not in _INT_GRANS:
+            raise NotImplementedError(f"granularity '{self.granularity}' is outside the B200 hot path")
+        if not self.round_zp:
+            raise NotImplementedError('round_zp=False is outside the B200 hot path')
+
+    def _group_len(self, last_dim):
+        """Group length along the last dim, 0 = whole row; mirrors reshape_tensor (quant.py:611-641)."""
+        if self.granularity == 'per_group':
+            if last_dim >= self.group_size:
+                if last_dim % self.group_size:
+                    raise ValueError(
+                        f'Dimension {last_dim} not divisible by group size {self.group_size}')
+                return self.group_size
+        return 0
+
+    def reshape_tensor(self, tensor, allow_padding=False):
+        g = self._group_len(tensor.shape[-1])
+        if self.granularity == 'per_group' and g:
+            return tensor.reshape(-1, g)
+        if self.granularity in _INT_GRANS:
+            return tensor
+        raise NotImplementedError(self.granularity)
+
+    def restore_tensor(self, tensor, shape):
+        return tensor if tensor.shape == shape else tensor.reshape(shape)
+
+
+def _as_2d(t):
+    t = t if t.is_contiguous() else t.contiguous()
+    return t, t.reshape(-1, t.shape[-1])
+
+
+class IntegerQuantizer(BaseQuantizer):
+    """quant.py:660-959 over lc_rtn_int_quant."""
+
+    def __init__(self, bit, symmetric, granularity, **kwargs):
+        super().__init__(bit, symmetric, granularity, **kwargs)
+        self.quant_type = 'int-quant'
+        if 'int_range' in kwargs:
+            raise NotImplementedError('int_range is outside the B200 hot path')
+        if self.sym:
+            self.qmin = torch.tensor(-(2 ** (bit - 1)))
+            self.qmax = torch.tensor(2 ** (bit - 1) - 1)
+        else:
+            self.qmin = torch.tensor(0.0)
+            self.qmax = torch.tensor(2 ** bit - 1)
+        self.dst_nbins = 2 ** bit
+
+    # ---- one fused launch ------------------------------------------------------------------
+    def _launch(self, t2d, group, scales_in=None, zeros_in=None, fake=False, codes=L.LC_CODES_NONE,
+                params=False):
+        self._check_supported()
+        L.require_cuda(t2d, scales_in, zeros_in)
+        rows, cols = t2d.shape
+        g = group if group else cols
+        n_groups = rows * (cols // g) if cols else 0
+        dev, dt = t2d.device, t2d.dtype
+        fake_out = torch.empty_like(t2d) if fake else None
+        codes_out = None
+        if codes == L.LC_CODES_I32:
+            codes_out = torch.empty((rows, cols), dtype=torch.int32, device=dev)
+        elif codes == L.LC_CODES_I8:
+            codes_out = torch.empty((rows, cols), dtype=torch.int8 if self.sym else torch.uint8, device=dev)
+        elif codes == L.LC_CODES_PACK4:
+            codes_out = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+        s_out = torch.empty((n_groups, 1), dtype=dt, device=dev) if params else None
+        z_out = torch.empty((n_groups, 1), dtype=dt, device=dev) if params and not self.sym else None
+        if scales_in is not None:
+            scales_in = scales_in.to(dt).contiguous()
+            if scales_in.numel() != n_groups:
+                raise NotImplementedError('static scales must hold one value per group')
+            if zeros_in is not None and not self.sym:
+                zeros_in = zeros_in.to(dt).contiguous()
+                if zeros_in.numel() != n_groups:
+                    raise NotImplementedError('static zeros must hold one value per group')
+            else:
+                zeros_in = None
+        L.call('lc_rtn_int_quant', L.ptr(t2d), L.lc_dtype(t2d), rows, cols, group, int(self.bit), int(self.sym),
+               L.ptr(scales_in), L.ptr(zeros_in), L.ptr(fake_out), L.ptr(codes_out), codes, L.ptr(s_out),
+               L.ptr(z_out), L.stream_of(t2d))
+        return fake_out, codes_out, s_out, z_out
+
+    def _code_fmt(self):
+        return L.LC_CODES_I8 if self.bit == 8 else L.LC_CODES_I32
+
+    # ---- reference API ---------------------------------------------------------------------
+    def get_tensor_qparams(self, tensor, args={}):
+        t, t2d = _as_2d(tensor)
+        group = self._group_len(t.shape[-1])
+        _, _, s, z = self._launch(t2d, group, params=True)
+        shape = s.shape if group else (*t.shape[:-1], 1)
+        s = s.reshape(shape)
+        z = torch.tensor(0.0) if self.sym else z.reshape(shape)
+        return self.reshape_tensor(t), s, z, self.qmax, self.qmin
+
+    def _static_2d(self, tensor):
+        t, t2d = _as_2d(tensor)
+        return t, t2d, (t2d.shape[-1] if t2d.shape[-1] else 0)
+
+    def quant(self, tensor, scales, zeros, qmax, qmin):
+        """tensor is already grouped (rows, group); scales/zeros hold one value per row."""
+        t, t2d, g = self._static_2d(tensor)
+        _, codes, _, _ = self._launch(t2d, g, scales, None if self.sym else zeros, codes=L.LC_CODES_I32)
+        return codes.to(t.dtype).reshape(t.shape)
+
+    def dequant(self, tensor, scales, zeros):
+        # Not on the hot path: the fused kernels never materialise codes as floats.
+        return (tensor - zeros) * scales
+
+    def quant_dequant(self, tensor, scales, zeros, qmax, qmin, output_scale_factor=1):
+        if output_scale_factor != 1:
+            raise NotImplementedError('output_scale_factor is outside the B200 hot path')
+        t, t2d, g = self._static_2d(tensor)
+        fake, _, _, _ = self._launch(t2d, g, scales, None if self.sym else zeros, fake=True)
+        return fake.reshape(t.shape)
+
+    def _reject_args(self, args, allowed=()):
+        bad = [k for k in args if k not in allowed]
+        if bad:
+            raise NotImplementedError(f'args {bad} are outside the B200 hot path')
+
+    def fake_quant_weight_dynamic(self, weight, args={}):
+        self._reject_args(args)
+        t, t2d = _as_2d(weight)
+        fake, _, _, _ = self._launch(t2d, self._group_len(t.shape[-1]), fake=True)
+        return fake.reshape(t.shape)
+
+    def fake_quant_act_dynamic(self, act, args={}):
+        self._reject_args(args)
+        t, t2d = _as_2d(act)
+        fake, _, _, _ = self._launch(t2d, self._group_len(t.shape[-1]), fake=True)
+        return fake.reshape(t.shape)
+
+    def fake_quant_weight_static(self, weight, args):
+        self._reject_args(args, ('scales', 'zeros', 'qmax', 'qmin'))
+        t, t2d = _as_2d(weight)
+        fake, _, _, _ = self._launch(t2d, self._group_len(t.shape[-1]), args['scales'],
+                                     None if self.sym else args.get('zeros'), fake=True)
+        return fake.reshape(t.shape)
+
+    fake_quant_act_static = fake_quant_weight_static
+
+    def _real(self, weight, scales=None, zeros=None):
+        t, t2d = _as_2d(weight)
+        if t.dim() != 2:
+            raise NotImplementedError('real quant expects a 2-D weight')
+        dyn = scales is None
+        _, codes, s, z = self._launch(t2d, self._group_len(t.shape[-1]), scales, zeros,
+                                      codes=self._code_fmt(), params=dyn)
+        if not dyn:
+            s, z = scales, (None if self.sym else zeros)
+        s = s.reshape(t.shape[0], -1)
+        z = None if self.sym else z.to(codes.dtype).reshape(t.shape[0], -1)
+        return codes, s, z
+
+    def real_quant_weight_dynamic(self, weight, args={}):
+        self._reject_args(args)
+        return self._real(weight)
+
+    def real_quant_weight_static(self, weight, args):
+        self._reject_args(args, ('scales', 'zeros', 'qmax', 'qmin'))
+        return self._real(weight, args['scales'], args.get('zeros'))
+
+    # ---- additions (no counterpart on the reference quantizer) -------------------------------
+    def quant_all_dynamic(self, weight, packed=False):
+        """One pass producing everything: (fake, codes, scales, zeros).  With packed=True (4-bit)
+        the codes are two nibbles per byte, low nibble first, stored as q - qmin."""
+        t, t2d = _as_2d(weight)
+        fmt = L.LC_CODES_PACK4 if packed else self._code_fmt()
+        fake, codes, s, z = self._launch(t2d, self._group_len(t.shape[-1]), fake=True, codes=fmt, params=True)
+        return fake.reshape(t.shape), codes, s.reshape(t2d.shape[0], -1), (
+            None if self.sym else z.reshape(t2d.shape[0], -1))
+
+    def __repr__(self):
+        return (f'IntegerQuantizer(bit={self.bit}, sym={self.sym}, granularity={self.granularity}, '
+                f'kwargs={self.kwargs}, qmin={self.qmin}, qmax={self.qmax})')
+
+
+class FloatQuantizer(BaseQuantizer):
+    """quant.py:962-1228 (use_qtorch path, e4m3, per_channel / per_token) over lc_fp8_e4m3_quant."""
+
+    def __init__(self, bit, symmetric, granularity, **kwargs):
+        super().__init__(bit, symmetric, granularity, **kwargs)
+        self.sym = True
+        self.quant_type = 'float-quant'
+        self.e_bits = int(self.bit[1])
+        self.m_bits = int(self.bit[-1])
+        self.sign_bits = 1
+        self.num_bits = self.e_bits + self.m_bits + self.sign_bits
+        self.use_qtorch = kwargs.get('use_qtorch')
+        if self.bit != 'e4m3' or not self.use_qtorch or 'float_range' in kwargs:
+            raise NotImplementedError('only e4m3 with use_qtorch=True is on the B200 hot path')
+        finfo = torch.finfo(torch.float8_e4m3fn)
+        self.qmin, self.qmax = torch.tensor(finfo.min), torch.tensor(finfo.max)
+
+    def _launch(self, t2d, fake=False, codes=False, scales=False):
+        if self.calib_algo != 'minmax' or self.granularity not in ('per_channel', 'per_token'):
+            raise NotImplementedError(f'{self.calib_algo}/{self.granularity} is outside the B200 hot path')
+        L.require_cuda(t2d)
+        rows, cols = t2d.shape
+        fake_out = torch.empty_like(t2d) if fake else None
+        codes_out = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=t2d.device) if codes else None
+        s_out = torch.empty((rows, 1), dtype=t2d.dtype, device=t2d.device) if scales else None
+        L.call('lc_fp8_e4m3_quant', L.ptr(t2d), L.lc_dtype(t2d), rows, cols, L.ptr(fake_out), L.ptr(codes_out),
+               L.ptr(s_out), L.stream_of(t2d))
+        return fake_out, codes_out, s_out
+
+    def get_tensor_qparams(self, tensor, args={}):
+        t, t2d = _as_2d(tensor)
+        _, _, s = self._launch(t2d, scales=True)
+        return t, s.reshape(*t.shape[:-1], 1), torch.tensor(0.0), self.qmax, self.qmin
+
+    def fake_quant_weight_dynamic(self, weight, args={}):
+        if args:
+            raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
+        t, t2d = _as_2d(weight)
+        return self._launch(t2d, fake=True)[0].reshape(t.shape)
+
+    fake_quant_act_dynamic = fake_quant_weight_dynamic
+
+    def real_quant_weight_dynamic(self, weight, args={}):
+        if args:
+            raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
+        t, t2d = _as_2d(weight)
+        _, codes, s = self._launch(t2d, codes=True, scales=True)
+        return codes.reshape(t.shape), s.reshape(t.shape[0], -1), None
+
+    def __repr__(self):
+        return (f'FloatQuantizer(bit={self.bit}, e_bits={self.e_bits}, m_bits={self.m_bits}, '
+                f'granularity={self.granularity}, kwargs={self.kwargs}, qmin={self.qmin}, qmax={self.qmax})')

@@ -1,0 +1,114 @@
+"""GPU parity of the fused quant / dequant kernels, called through the C ABI, against the
+committed reference outputs (tests/golden) and against the CPU oracle on seeded inputs.
+Integer and byte results are compared bit for bit."""
+import pytest
+import torch
+
+from oracle import quant_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.contiguous().view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+
+
+def _same(a, b, what=''):
+    a = a.cpu()
+    assert a.dtype == b.dtype and a.shape == b.shape, (what, a.dtype, b.dtype, a.shape, b.shape)
+    if a.is_floating_point() and a.dtype != torch.float8_e4m3fn:
+        # compare bit patterns, but let +0 == -0 and NaN == NaN like torch.equal would not
+        ia = a.contiguous().view(torch.int32 if a.dtype == torch.float32 else torch.int16)
+        ib = b.contiguous().view(ia.dtype)
+        bad = (ia != ib) & ~((a == 0) & (b == 0)) & ~(a.isnan() & b.isnan())
+        assert not bad.any(), f'{what}: {int(bad.sum())} of {a.numel()} elements differ'
+    else:
+        assert torch.equal(_bits(a), _bits(b)), what
+
+
+def test_rtn_matches_reference_golden(golden):
+    from lightcompress_b200 import IntegerQuantizer
+    for key, c in golden('rtn_int.pt').items():
+        kw = {'group_size': c['group_size']} if c['group_size'] else {}
+        qz = IntegerQuantizer(c['bit'], c['sym'], c['granularity'], **kw)
+        w = c['w'].cuda()
+        if 'codes' in c:
+            _same(qz.fake_quant_weight_dynamic(w), c['fake'], key + ' fake')
+            codes, s, z = qz.real_quant_weight_dynamic(w)
+            _same(codes, c['codes'], key + ' codes')
+            _same(s, c['scales'], key + ' scales')
+            if c['sym']:
+                assert z is None
+            else:
+                _same(z, c['zeros'], key + ' zeros')
+            # static path reproduces the dynamic one when fed the same parameters
+            t, s2, z2, qmax, qmin = qz.get_tensor_qparams(w)
+            _same(s2.reshape(s.shape), c['scales'], key + ' qparams')
+            fq = qz.fake_quant_weight_static(w, {'scales': s2, 'zeros': z2, 'qmax': qmax, 'qmin': qmin})
+            _same(fq, c['fake'], key + ' static')
+        else:
+            _same(qz.fake_quant_act_dynamic(w), c['fake'], key + ' act')
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize('shape,gran,gs', [((4096, 4096), 'per_group', 128), ((512, 11008), 'per_group', 128),
+                                           ((300, 4096), 'per_channel', None), ((64, 11008), 'per_channel', None),
+                                           ((7, 33, 1408), 'per_token', None), ((5, 1000), 'per_token', None),
+                                           ((16, 96), 'per_group', 32), ((3, 130), 'per_channel', None)])
+def test_rtn_matches_oracle(dtype, shape, gran, gs):
+    from lightcompress_b200 import IntegerQuantizer
+    g = torch.Generator().manual_seed(1000 + len(shape) + shape[-1])
+    w = (torch.randn(*shape, generator=g) * 0.02).to(dtype)
+    for sym, bit in ((False, 4), (True, 4), (False, 8), (True, 8)):
+        kw = {'group_size': gs} if gs else {}
+        qz = IntegerQuantizer(bit, sym, gran, **kw)
+        wc = w.cuda()
+        _same(qz.fake_quant_weight_dynamic(wc), quant_ref.int_fake_quant_dynamic(w, bit, sym, gran, gs), 'fake')
+        if w.dim() == 2:
+            q, s, z = quant_ref.int_real_quant_dynamic(w, bit, sym, gran, gs)
+            codes, s2, z2 = qz.real_quant_weight_dynamic(wc)
+            _same(codes, q, 'codes')
+            _same(s2, s, 'scales')
+            if not sym:
+                _same(z2, z, 'zeros')
+            if bit == 4 and shape[-1] % 2 == 0:
+                fake, packed, s3, z3 = qz.quant_all_dynamic(wc, packed=True)
+                off = 8 if sym else 0
+                _same(packed, quant_ref.pack_int4_rows((q + off).to(torch.uint8)), 'packed')
+                _same(s3, s, 'scales(all)')
+
+
+def test_rtn_full_size_roundtrip_property():
+    """Config-1 size: quantising the dequantised output again is a fixed point for the codes."""
+    from lightcompress_b200 import IntegerQuantizer
+    g = torch.Generator().manual_seed(1001)
+    w = (torch.randn(4096, 4096, generator=g) * 0.02).cuda()
+    qz = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    fake, codes, s, z = qz.quant_all_dynamic(w)
+    assert int(codes.min()) >= 0 and int(codes.max()) <= 15
+    deq = ((codes.float().reshape(-1, 128) - z.reshape(-1, 1).float()) * s.reshape(-1, 1)).reshape(w.shape)
+    assert torch.equal(deq, fake)
+    assert float((fake - w).abs().max()) <= float(s.max()) * 0.5 + 1e-7
+
+
+def test_fp8_matches_reference_golden_and_oracle(golden):
+    from lightcompress_b200 import FloatQuantizer
+    for key, c in golden('fp8_e4m3.pt').items():
+        qw = FloatQuantizer('e4m3', True, 'per_channel', use_qtorch=True)
+        qa = FloatQuantizer('e4m3', True, 'per_token', use_qtorch=True)
+        _same(qw.fake_quant_weight_dynamic(c['w'].cuda()), c['fake'], key + ' fake')
+        codes, s, z = qw.real_quant_weight_dynamic(c['w'].cuda())
+        assert z is None
+        _same(codes.view(torch.uint8), c['codes'], key + ' codes')
+        _same(s, c['scales'], key + ' scales')
+        _same(qa.fake_quant_act_dynamic(c['x'].cuda()), c['fake_act'], key + ' act')
+    g = torch.Generator().manual_seed(5002)
+    for dtype in (torch.bfloat16, torch.float32, torch.float16):
+        for shape in ((1408, 2048), (2048, 1408), (37, 1001), (16, 11008)):
+            w = (torch.randn(*shape, generator=g)).to(dtype)
+            qw = FloatQuantizer('e4m3', True, 'per_channel', use_qtorch=True)
+            _same(qw.fake_quant_weight_dynamic(w.cuda()), quant_ref.fp8_fake_quant_dynamic(w), 'fp8 fake')
+            q, s = quant_ref.fp8_real_quant_dynamic(w)
+            codes, s2, _ = qw.real_quant_weight_dynamic(w.cuda())
+            _same(codes.view(torch.uint8), q.view(torch.uint8), 'fp8 codes')
+            _same(s2, s, 'fp8 scales')
