@@ -146,7 +146,9 @@ class GPTQ:
         Lc = torch.linalg.cholesky(Hp)
         Hinv = torch.cholesky_inverse(Lc)
         del Lc
-        return torch.linalg.cholesky(Hinv, upper=True)
+        # torch returns the upper factor as a transposed view of the lower one; the kernels read
+        # row-major memory, so materialise it.
+        return torch.linalg.cholesky(Hinv, upper=True).contiguous()
 
     def _install(self, layer, res):
         layer.weight.data = res['weight'].reshape(layer.weight.shape)
