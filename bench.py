@@ -3,8 +3,9 @@ tokens, W4 asymmetric g128, act-order, percdamp 0.01 (the single-layer GPTQ conf
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-A step = Hessian accumulation over every calibration sample (one lc_hessian_accum call per
-sample, the way the algorithm's forward hook delivers them) + the GPTQ layer solve.  Inputs are
+A step = Hessian accumulation over every calibration sample (add_batch is called once per
+sequence, the way the algorithm's forward hook delivers them; the plugin hands 8 sequences to
+one lc_hessian_accum_multi launch) + the GPTQ layer solve.  Inputs are
 seeded synthetic tensors with the configuration's shapes and value distributions.
 
 N > 1 (launched by torch.distributed.run): calibration sequences are sharded over the ranks,
@@ -102,10 +103,13 @@ class ClockSampler:
                 'samples': len(sm), 'reasons': sorted(reasons)}
 
 
+HESSIAN_BATCH = 8   # sequences handed to one Hessian launch (GPTQ special key `hessian_batch`)
+
+
 def launches_per_step(n_seq):
     n_blocks = C // 128
-    # hessian per sample + diag + (damp, permute H, permute W) + block + trailing + un-permute
-    return n_seq + 1 + 3 + n_blocks + (n_blocks - 1) + 1
+    # hessian per batch of sequences + diag + (damp, permute H, permute W) + flip + block + trailing + un-permute
+    return -(-n_seq // HESSIAN_BATCH) + 1 + 3 + 1 + n_blocks + (n_blocks - 1) + 1
 
 
 def cpu_port(n_hess_samples=8, threads=None):
@@ -183,7 +187,8 @@ def main():
     W = W_host.to(dev)
     X = X_host.to(dev)
     wq = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
-    solver = lc.GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'emit_codes': True})
+    solver = lc.GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'emit_codes': True,
+                          'hessian_batch': HESSIAN_BATCH})
     layer = torch.nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device=dev)
     r0, r1 = rank * (R // world), (rank + 1) * (R // world)
     hess_ev = []
@@ -236,7 +241,9 @@ def main():
     ms_step = ms_total / args.steps
     value = 1e3 / ms_step
     hess_ms = sum(a.elapsed_time(b) for a, b in hess_ev) / len(hess_ev)
-    hess_launch_ms = hess_ms / n_seq
+    n_hess_launches = -(-n_seq // HESSIAN_BATCH)
+    hess_launch_ms = hess_ms / n_hess_launches
+    tok_per_launch = T * n_seq / n_hess_launches
 
     # ---- end to end: host buffers in, host result out ------------------------------------------
     e2e = None
@@ -284,15 +291,16 @@ def main():
         return
 
     # ---- roofline of the dominant kernel (Hessian GEMM) ------------------------------------------
-    alg_flops = 2.0 * T * C * C                       # per launch: the full square the reference computes
-    n_tiles = sum((C // 256) - (mi >> 1) for mi in range(C // 128))
-    exe_flops = 2.0 * T * 128 * 256 * n_tiles         # tiles actually issued (upper triangle)
+    alg_flops = 2.0 * tok_per_launch * C * C          # per launch: the full square the reference computes
+    n_super = (C // 256) * (C // 256 + 1) // 2
+    exe_flops = 2.0 * tok_per_launch * 256 * 256 * n_super   # 256x256 tiles actually issued (upper triangle)
     achieved = alg_flops / (hess_launch_ms * 1e-3) / 1e12
     peak = tf_sust
     roofline = {'bound': 'tensor', 'kernel': 'hessian_umma_kernel', 'achieved': achieved, 'peak': peak,
                 'unit': 'TFLOP/s', 'frac': achieved / peak, 'peak_kind': f'{peak_kind} sustained cuBLAS bf16',
                 'achieved_executed': exe_flops / (hess_launch_ms * 1e-3) / 1e12,
-                'launch_ms': hess_launch_ms, 'launches_per_step': n_seq, 'share_of_step': hess_ms / ms_step,
+                'launch_ms': hess_launch_ms, 'launches_per_step': n_hess_launches,
+                'tokens_per_launch': tok_per_launch, 'share_of_step': hess_ms / ms_step,
                 'traffic': None}
 
     line = {'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,

@@ -106,13 +106,23 @@ int lc_fp8_e4m3_quant(const void* in, int dtype, int64_t rows, int64_t cols, voi
  *   H  cols x cols fp32, full symmetric matrix is maintained
  * cols must be a multiple of 8 (16-byte row pitch for TMA); X and H 16-byte aligned.
  * Products of bf16 values are exact in fp32; accumulation is fp32 in tensor memory.
- * Only tiles on or above the diagonal are computed; each is added to H and to its mirror.
- * `ksplit` > 1 splits the token range over that many CTAs per tile (0 = choose); partial
- * sums are combined with fp32 atomic adds, so the summation order may vary between runs.
+ * Only 256x256 tiles on or above the diagonal are computed; each is added to H and to its
+ * mirror with fp32 atomic adds.  `ksplit` > 1 splits the token range over that many work items
+ * per tile (0 = choose); the order in which partial sums reach H may then vary between runs.
  * `status` (may be NULL) receives LC_ERR_TIMEOUT if a bounded pipeline wait expires.
  * ------------------------------------------------------------------------------------------ */
 int lc_hessian_accum(const void* x_bf16, int64_t tokens, int64_t cols, float* H, float alpha,
                      float beta, int ksplit, int32_t* status, lc_stream_t stream);
+
+/* Same update over up to 8 separate activation tensors in one launch,
+ *     H <- beta * H + alpha * sum_s X_s^T X_s,
+ * so that a caller whose forward hook delivers one sequence at a time (GPTQ.cache_input_hook,
+ * gptq.py:247-251) can hand over several of them at once: the accumulators then stay in tensor
+ * memory across all of them and H is updated once.  xs_host / tokens_host are HOST arrays of
+ * `nseg` device pointers / token counts (each X_s is tokens_s x cols bf16, 16-byte aligned). */
+int lc_hessian_accum_multi(const void* const* xs_host, const int64_t* tokens_host, int nseg,
+                           int64_t cols, float* H, float alpha, float beta, int ksplit,
+                           int32_t* status, lc_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Family 3: GPTQ layer solver pieces.
@@ -127,10 +137,18 @@ int lc_gptq_diag(const float* H, int64_t cols, float* diag_out, lc_stream_t stre
  * where dead(c) means H[c][c] == 0 and damp = percdamp * mean(diag(Hp)).  `hscale` lets the
  * caller keep H as the raw sum of X^T X and apply 2/nsamples here.
  *   W rows x cols in `w_dtype`; perm int64 (cols) or NULL for identity
+ *   reverse_h != 0: Hp is written with both index orders reversed, Hp[i][j] <- entry
+ *           (cols-1-i, cols-1-j), which is the input of the single-factorisation route to the
+ *           upper factor of the inverse (see lc_gptq_flip); Wp is not affected
  *   scratch: at least 1 float (receives damp) */
 int lc_gptq_permute_damp(const void* W, int w_dtype, const float* H, const int64_t* perm,
-                         int64_t rows, int64_t cols, float hscale, float percdamp, float* Wp,
-                         float* Hp, float* scratch, lc_stream_t stream);
+                         int64_t rows, int64_t cols, float hscale, float percdamp, int reverse_h,
+                         float* Wp, float* Hp, float* scratch, lc_stream_t stream);
+
+/* out[i][j] = in[n-1-i][n-1-j] (out-of-place).  With J the index reversal: if J H J = M M^T
+ * (M lower Cholesky factor) then U = J M^-1 J is upper triangular with U^T U = H^-1, i.e. the
+ * matrix that gptq.py:172-174 obtains with cholesky -> cholesky_inverse -> cholesky(upper). */
+int lc_gptq_flip(const float* in, int64_t n, float* out, lc_stream_t stream);
 
 /* One 128-column block of GPTQ.weight_transform (gptq.py:199-241), group_size == blocksize:
  * per row, asymmetric/symmetric int qparams from the block's current columns

@@ -30,8 +30,10 @@ SIGNATURES = {
     'lc_rtn_int_quant': [_p, _i, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p, _i, _p, _p, _p],
     'lc_fp8_e4m3_quant': [_p, _i, _i64, _i64, _p, _p, _p, _p],
     'lc_hessian_accum': [_p, _i64, _i64, _p, _f, _f, _i, _p, _p],
+    'lc_hessian_accum_multi': [_p, _p, _i, _i64, _p, _f, _f, _i, _p, _p],
     'lc_gptq_diag': [_p, _i64, _p, _p],
-    'lc_gptq_permute_damp': [_p, _i, _p, _p, _i64, _i64, _f, _f, _p, _p, _p, _p],
+    'lc_gptq_permute_damp': [_p, _i, _p, _p, _i64, _i64, _f, _f, _i, _p, _p, _p, _p],
+    'lc_gptq_flip': [_p, _i64, _p, _p],
     'lc_gptq_block_quant': [_p, _p, _i64, _i64, _i64, _i, _i, _i, _p, _p, _p, _i64, _p, _p, _p],
     'lc_gptq_trailing_update': [_p, _p, _p, _i64, _i64, _i64, _i, _i64, _p],
     'lc_gptq_weight_transform': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p],
@@ -48,11 +50,15 @@ class LcError(RuntimeError):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f'{LIB_PATH} is missing: build it with `python -m lightcompress_b200.build` '
+            f'{LIB_PATH} is missing: build it with `python __graft_entry__.py` '
             '(nvcc, sm_100a).  There is no fallback implementation.')
     lib = ctypes.CDLL(LIB_PATH)
     for name, argtypes in SIGNATURES.items():
-        fn = getattr(lib, name)           # AttributeError if the library lacks a declared symbol
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            raise ImportError(f'{LIB_PATH} is stale (no symbol {name}): rebuild it with '
+                              '`python __graft_entry__.py`') from None
         fn.argtypes = argtypes
         fn.restype = ctypes.c_char_p if name == 'lc_status_string' else ctypes.c_int
     return lib

@@ -1,6 +1,7 @@
 """Builds the C-ABI shared library (liblc_b200.so) in-tree with nvcc for sm_100a.
 
-    python -m lightcompress_b200.build [--force]
+    python __graft_entry__.py            (from the repository root; loads this file by path)
+    python lightcompress_b200/build.py [--force]
 
 One translation unit per kernel family; objects go to build/, the library next to this file.
 """

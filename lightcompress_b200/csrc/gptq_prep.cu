@@ -32,12 +32,15 @@ __global__ void __launch_bounds__(1024) damp_kernel(const float* H, int64_t cols
 }
 
 __global__ void __launch_bounds__(256) permute_h_kernel(const float* H, const int64_t* perm, int64_t cols,
-                                                        float hscale, const float* damp, float* Hp) {
+                                                        float hscale, const float* damp, float* Hp, int reverse) {
   const int64_t i = blockIdx.y;
   const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= cols) return;
-  const int64_t pi = perm ? perm[i] : i;
-  const int64_t pj = perm ? perm[j] : j;
+  // reverse: write Hp with both index orders reversed (row i, col j hold entry cols-1-i, cols-1-j)
+  const int64_t si = reverse ? cols - 1 - i : i;
+  const int64_t sj = reverse ? cols - 1 - j : j;
+  const int64_t pi = perm ? perm[si] : si;
+  const int64_t pj = perm ? perm[sj] : sj;
   float v = hscale * H[pi * cols + pj];
   if (i == j) {
     if (v == 0.f) v = 1.f;
@@ -69,8 +72,23 @@ __global__ void __launch_bounds__(256) unpermute_kernel(const float* Wp, const i
   }
 }
 
+// out[i][j] = in[n-1-i][n-1-j]
+__global__ void __launch_bounds__(256) flip2_kernel(const float* in, int64_t n, float* out) {
+  const int64_t i = blockIdx.y;
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j < n) out[i * n + j] = in[(n - 1 - i) * n + (n - 1 - j)];
+}
+
 }  // namespace
 }  // namespace lc
+
+extern "C" LC_API int lc_gptq_flip(const float* in, int64_t n, float* out, lc_stream_t stream) {
+  if (!in || !out || n <= 0 || in == out) return LC_ERR_ARG;
+  dim3 g((unsigned)((n + 255) / 256), (unsigned)n);
+  lc::flip2_kernel<<<g, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(in, n, out);
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
 
 extern "C" LC_API int lc_gptq_diag(const float* H, int64_t cols, float* diag_out, lc_stream_t stream) {
   if (!H || !diag_out || cols <= 0) return LC_ERR_ARG;
@@ -81,8 +99,8 @@ extern "C" LC_API int lc_gptq_diag(const float* H, int64_t cols, float* diag_out
 }
 
 extern "C" LC_API int lc_gptq_permute_damp(const void* W, int w_dtype, const float* H, const int64_t* perm, int64_t rows,
-                                    int64_t cols, float hscale, float percdamp, float* Wp, float* Hp,
-                                    float* scratch, lc_stream_t stream) {
+                                    int64_t cols, float hscale, float percdamp, int reverse_h, float* Wp,
+                                    float* Hp, float* scratch, lc_stream_t stream) {
   using namespace lc;
   if (!W || !H || !Wp || !Hp || !scratch || rows <= 0 || cols <= 0) return LC_ERR_ARG;
   if (w_dtype != LC_F32 && w_dtype != LC_BF16 && w_dtype != LC_F16) return LC_ERR_ARG;
@@ -90,7 +108,7 @@ extern "C" LC_API int lc_gptq_permute_damp(const void* W, int w_dtype, const flo
   damp_kernel<<<1, 1024, 0, st>>>(H, cols, hscale, percdamp, scratch);
   LC_LAUNCH_CHECK();
   dim3 gh((unsigned)((cols + 255) / 256), (unsigned)cols);
-  permute_h_kernel<<<gh, 256, 0, st>>>(H, perm, cols, hscale, scratch, Hp);
+  permute_h_kernel<<<gh, 256, 0, st>>>(H, perm, cols, hscale, scratch, Hp, reverse_h);
   LC_LAUNCH_CHECK();
   dim3 gw((unsigned)((cols + 255) / 256), (unsigned)(rows < 1024 ? rows : 1024));
   switch (w_dtype) {

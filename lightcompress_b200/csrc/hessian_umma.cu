@@ -1,16 +1,22 @@
-// Family 2: Hessian accumulation  H <- beta*H + alpha * X^T X  on the sm_100a tensor cores.
+// Family 2: Hessian accumulation  H <- beta*H + alpha * sum_s X_s^T X_s  on the sm_100a tensor cores.
 //
-// X is (tokens x cols) bf16 row-major, so for D[m][n] = sum_t X[t][m] X[t][n] both MMA operands
-// are "MN-major": the contraction index (tokens) is the strided one.  TMA copies 64-channel x
-// 64-token boxes (128-byte rows, 128B swizzle) into shared memory; tcgen05.mma (128x256x16,
-// bf16 in, fp32 accumulate in tensor memory) consumes them through MN-major shared-memory
-// descriptors.  Only tiles that touch the upper triangle are computed; the epilogue adds each
-// tile to H and to its transposed position.
+// Each X_s is (tokens x cols) bf16 row-major, so for D[m][n] = sum_t X[t][m] X[t][n] both MMA
+// operands are "MN-major": the contraction index (tokens) is the strided one.  TMA copies
+// 64-channel x 32-token boxes (128-byte rows, 128B swizzle) into shared memory and tcgen05.mma
+// (128x256x16, bf16 in, fp32 accumulate) consumes them through MN-major shared-memory descriptors.
 //
-// CTA = one (128x256 tile, token range) work item, 6 warps:
+// Work unit: a 256x256 "super-tile" of H on or above the diagonal.  Its two 128x256 halves share
+// the B operand and live in the two halves of the SM's tensor memory (512 columns), so one
+// pipeline stage (A0, A1, B = 512 channels x 32 tokens) feeds four MMAs.  Diagonal super-tiles
+// load B only: A0 and A1 are its two halves.  CTAs are persistent (one per SM) and walk the
+// (token-split, super-tile) items split-major, so that CTAs running at the same time stream the
+// same token range and X is read from HBM about once.
+//
+// 6 warps per CTA:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      MMA issuer (one elected lane); owns the TMEM allocation
-//   warps 2..5  epilogue: tcgen05.ld -> scale -> red.global.add.f32
+//   warps 2..5  epilogue: tcgen05.ld -> scale -> 128-bit red.global.add.f32 to H and, through a
+//               per-warp shared-memory transpose, to the mirrored position
 // Every wait is bounded: when a limit expires the kernel raises a flag, drains its own copies,
 // frees its tensor memory and returns; the host sees LC_ERR_TIMEOUT in *status.
 #include <cuda.h>
@@ -20,19 +26,20 @@
 namespace lc {
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 64;        // tokens per pipeline stage
-constexpr int UMMA_K = 16;    // bf16
-constexpr int STAGES = 4;
-constexpr int ATOM = 64;      // channels per 128-byte swizzle row
-constexpr int ATOM_BYTES = ATOM * 2 * BK;          // 8192: one 64ch x 64tok box
-constexpr int A_BYTES = (BM / ATOM) * ATOM_BYTES;  // 16384
-constexpr int B_BYTES = (BN / ATOM) * ATOM_BYTES;  // 32768
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;     // 49152
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int TMEM_COLS = 256;
+constexpr int ST = 256;        // super-tile edge
+constexpr int BK = 32;         // tokens per pipeline stage
+constexpr int UMMA_K = 16;     // bf16
+constexpr int STAGES = 6;
+constexpr int ATOM = 64;       // channels per 128-byte swizzle row
+constexpr int ATOM_BYTES = ATOM * 2 * BK;   // 4096: one 64ch x 32tok box
+constexpr int A_ATOMS = 2, B_ATOMS = 4;
+constexpr int STAGE_BYTES = (2 * A_ATOMS + B_ATOMS) * ATOM_BYTES;  // 32768
+constexpr int STG_STRIDE = 36;                                     // floats per staged row
+constexpr int STG_BYTES_PER_WARP = 32 * STG_STRIDE * 4;            // 4608
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * STG_BYTES_PER_WARP + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = 512;
 constexpr int kThreads = 192;
+constexpr int MAX_SEG = 8;
 constexpr uint32_t kSpinLimit = 20u * 1000u * 1000u;  // x >= 50 ns sleeps: about a second
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -43,6 +50,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -117,61 +127,74 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t saddr, uint32_t 
   return d;
 }
 
-// Instruction descriptor, kind::f16: fp32 accumulate, bf16 x bf16, both operands MN-major.
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 x bf16, both operands MN-major, M=128, N=256.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
-                            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                            ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+struct TmapArray {
+  CUtensorMap m[MAX_SEG];
+};
 
 struct HessArgs {
   float* H;
   int32_t* status;
   int64_t cols;
-  int tokens;
-  int m_tiles, n_tiles, ksplit;
+  int n_st;        // super-tiles per dimension
+  int n_super;     // super-tiles on or above the diagonal
+  int n_items;     // n_super * ksplit
+  int ksplit;
+  int k_total;     // pipeline iterations over all segments
+  int nseg;
+  int seg_k[MAX_SEG];
   float alpha;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_constant__ CUtensorMap tmap, HessArgs a) {
+struct Item {
+  int si, sj, k_begin, k_end;
+};
+
+__device__ __forceinline__ Item decode_item(const HessArgs& a, int item) {
+  Item it;
+  const int split = item / a.n_super;
+  int t = item % a.n_super;
+  int si = 0;
+  for (; si < a.n_st; ++si) {
+    const int cnt = a.n_st - si;
+    if (t < cnt) break;
+    t -= cnt;
+  }
+  it.si = si;
+  it.sj = si + t;
+  const int chunk = (a.k_total + a.ksplit - 1) / a.ksplit;
+  it.k_begin = split * chunk;
+  it.k_end = min(a.k_total, it.k_begin + chunk);
+  return it;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_constant__ TmapArray maps, HessArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + STAGES * STAGE_BYTES);
-  // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulator ready, then tmem slot + abort flag
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  float* staging = reinterpret_cast<float*>(gen_base + STAGES * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + STAGES * STAGE_BYTES + 4 * STG_BYTES_PER_WARP);
+  // bars: [0,S) full, [S,2S) empty, 2S accumulator full, 2S+1 accumulator empty; then tmem slot, abort flag
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const uint32_t bar0 = base + STAGES * STAGE_BYTES;
+  const uint32_t bar0 = base + STAGES * STAGE_BYTES + 4 * STG_BYTES_PER_WARP;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  const uint32_t accum_bar = bar0 + 8u * (2 * STAGES);
+  const uint32_t accum_full = bar0 + 8u * (2 * STAGES);
+  const uint32_t accum_empty = bar0 + 8u * (2 * STAGES + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // ---- which work item ------------------------------------------------------------------------
-  int t = blockIdx.x / a.ksplit;
-  const int split = blockIdx.x % a.ksplit;
-  int mi = 0, ni = 0;
-  for (mi = 0; mi < a.m_tiles; ++mi) {
-    const int first = mi >> 1;
-    const int cnt = a.n_tiles - first;
-    if (t < cnt) {
-      ni = first + t;
-      break;
-    }
-    t -= cnt;
-  }
-  const int k_iters_total = (a.tokens + BK - 1) / BK;
-  const int chunk = (k_iters_total + a.ksplit - 1) / a.ksplit;
-  const int k_begin = split * chunk;
-  const int k_end = min(k_iters_total, k_begin + chunk);
-  if (mi >= a.m_tiles || k_begin >= k_end) return;  // uniform for the CTA
-  const int n_iters = k_end - k_begin;
-
-  // ---- setup ----------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(accum_bar, 1);
+    mbar_init(accum_full, 1);
+    mbar_init(accum_empty, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -185,31 +208,56 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
+  const int64_t C = a.cols;
 
   if (warp == 0) {
     // ---- TMA producer -------------------------------------------------------------------------
     if (lane == 0) {
-      int issued = 0;
-      for (int n = 0; n < n_iters; ++n) {
-        const int s = n % STAGES;
-        const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(full_bar(s), STAGE_BYTES);
-        const uint32_t sa = base + s * STAGE_BYTES;
-        const int tok = (k_begin + n) * BK;
+      uint32_t n = 0;  // running stage counter across items
+      uint32_t issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < a.n_items; item += gridDim.x) {
+        const Item w = decode_item(a, item);
+        if (w.k_begin >= w.k_end) continue;
+        const bool diag = (w.si == w.sj);
+        const bool has_a1 = (int64_t)w.si * ST + 128 < C;
+        // locate the first iteration inside the segment list
+        int seg = 0, kloc = w.k_begin;
+        while (seg < a.nseg && kloc >= a.seg_k[seg]) kloc -= a.seg_k[seg++];
+        for (int k = w.k_begin; k < w.k_end; ++k, ++n) {
+          const int s = n % STAGES;
+          const uint32_t ph = (n / STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const int n_atoms = B_ATOMS + (diag ? 0 : (has_a1 ? 2 * A_ATOMS : A_ATOMS));
+          mbar_expect_tx(full_bar(s), n_atoms * ATOM_BYTES);
+          const uint32_t sa = base + s * STAGE_BYTES;
+          const CUtensorMap* map = &maps.m[seg];
+          const int tok = kloc * BK;
+          if (!diag) {
 #pragma unroll
-        for (int q = 0; q < BM / ATOM; ++q) tma_load_2d(sa + q * ATOM_BYTES, &tmap, mi * BM + q * ATOM, tok, full_bar(s));
+            for (int q = 0; q < A_ATOMS; ++q) tma_load_2d(sa + q * ATOM_BYTES, map, w.si * ST + q * ATOM, tok, full_bar(s));
+            if (has_a1) {
 #pragma unroll
-        for (int q = 0; q < BN / ATOM; ++q)
-          tma_load_2d(sa + A_BYTES + q * ATOM_BYTES, &tmap, ni * BN + q * ATOM, tok, full_bar(s));
-        issued = n + 1;
+              for (int q = 0; q < A_ATOMS; ++q)
+                tma_load_2d(sa + (A_ATOMS + q) * ATOM_BYTES, map, w.si * ST + 128 + q * ATOM, tok, full_bar(s));
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < B_ATOMS; ++q)
+            tma_load_2d(sa + (2 * A_ATOMS + q) * ATOM_BYTES, map, w.sj * ST + q * ATOM, tok, full_bar(s));
+          issued = n + 1;
+          if (++kloc >= a.seg_k[seg]) {
+            kloc = 0;
+            ++seg;
+          }
+        }
       }
       if (*abort_flag) {
         // drain: the copies this thread started must land before the CTA's shared memory goes away
-        const int first = issued > STAGES ? issued - STAGES : 0;
-        for (int n = first; n < issued; ++n) {
-          const int s = n % STAGES;
-          const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
+        const uint32_t first = issued > STAGES ? issued - STAGES : 0;
+        for (uint32_t i = first; i < issued; ++i) {
+          const int s = i % STAGES;
+          const uint32_t ph = (i / STAGES) & 1u;
           for (uint32_t it = 0; it < kSpinLimit && !mbar_test(full_bar(s), ph); ++it) __nanosleep(50);
         }
       }
@@ -217,67 +265,108 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
   } else if (warp == 1) {
     // ---- MMA issuer ---------------------------------------------------------------------------
     if (lane == 0) {
-      bool any = false;
-      for (int n = 0; n < n_iters; ++n) {
-        const int s = n % STAGES;
-        const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
-        if (!mbar_wait(full_bar(s), ph, abort_flag)) break;
+      uint32_t n = 0, items_done = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < a.n_items; item += gridDim.x) {
+        const Item w = decode_item(a, item);
+        if (w.k_begin >= w.k_end) continue;
+        const bool diag = (w.si == w.sj);
+        const bool has_a1 = (int64_t)w.si * ST + 128 < C;
+        // the epilogue must have drained the accumulators of the previous item
+        if (!mbar_wait(accum_empty, (items_done & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
-        const uint32_t sa = base + s * STAGE_BYTES;
+        for (int k = w.k_begin; k < w.k_end; ++k, ++n) {
+          const int s = n % STAGES;
+          const uint32_t ph = (n / STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = base + s * STAGE_BYTES;
+          const uint32_t b_base = sa + 2 * A_ATOMS * ATOM_BYTES;
+          const uint32_t a0_base = diag ? b_base : sa;
+          const uint32_t a1_base = diag ? b_base + A_ATOMS * ATOM_BYTES : sa + A_ATOMS * ATOM_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // one MMA consumes 16 tokens = two 8-row groups of 1024 bytes
-          const uint64_t ad = make_desc_mn_sw128(sa + k * 2048, ATOM_BYTES, 1024);
-          const uint64_t bd = make_desc_mn_sw128(sa + A_BYTES + k * 2048, ATOM_BYTES, 1024);
-          umma_bf16(tmem_acc, ad, bd, kIdesc, (n > 0 || k > 0) ? 1u : 0u);
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // one MMA consumes 16 tokens = two 8-row groups of 1024 bytes
+            const uint32_t acc = (k > w.k_begin || kk > 0) ? 1u : 0u;
+            const uint64_t bd = make_desc_mn_sw128(b_base + kk * 2048, ATOM_BYTES, 1024);
+            umma_bf16(tmem_acc, make_desc_mn_sw128(a0_base + kk * 2048, ATOM_BYTES, 1024), bd, kIdesc, acc);
+            if (has_a1)
+              umma_bf16(tmem_acc + 256, make_desc_mn_sw128(a1_base + kk * 2048, ATOM_BYTES, 1024), bd, kIdesc, acc);
+          }
+          umma_commit(empty_bar(s));
         }
-        umma_commit(empty_bar(s));
-        any = true;
+        if (!ok) break;
+        umma_commit(accum_full);  // arrives when every MMA of this item has completed
+        ++items_done;
       }
-      umma_commit(accum_bar);  // arrives when every MMA issued above has completed
-      if (*abort_flag && any) {
-        for (uint32_t it = 0; it < kSpinLimit && !mbar_test(accum_bar, 0); ++it) __nanosleep(50);
+      if (*abort_flag) {
+        // make sure nothing is still writing tensor memory before it is freed
+        umma_commit(accum_full);
+        for (uint32_t it = 0; it < kSpinLimit && !mbar_test(accum_full, items_done & 1u); ++it) __nanosleep(50);
       }
     }
   } else {
     // ---- epilogue -----------------------------------------------------------------------------
-    const bool ready = mbar_wait(accum_bar, 0, abort_flag);
-    tcgen05_fence_after();
-    if (ready && !*abort_flag) {
-      const int q = warp & 3;  // TMEM lane quarter this warp may read
-      const int64_t m = (int64_t)mi * BM + q * 32 + lane;
-      const int64_t n_base = (int64_t)ni * BN;
-      const int64_t C = a.cols;
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    float* stg = staging + q * (STG_BYTES_PER_WARP / 4);
+    uint32_t items_done = 0;
+    for (int item = blockIdx.x; item < a.n_items; item += gridDim.x) {
+      const Item w = decode_item(a, item);
+      if (w.k_begin >= w.k_end) continue;
+      if (!mbar_wait(accum_full, items_done & 1u, abort_flag) || *abort_flag) break;
+      tcgen05_fence_after();
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        float v[32];
-        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(cc * 32), v);
-        const int64_t n0 = n_base + cc * 32;
-        if (n0 >= C) continue;
+      for (int h = 0; h < 2; ++h) {
+        const int64_t m_blk0 = (int64_t)w.si * ST + h * 128 + q * 32;
+        if ((int64_t)w.si * ST + h * 128 >= C) break;
+        const int64_t m = m_blk0 + lane;
+#pragma unroll 1
+        for (int cc = 0; cc < ST / 32; ++cc) {
+          const int64_t n0 = (int64_t)w.sj * ST + cc * 32;
+          if (n0 >= C) break;
+          if (n0 < m_blk0) continue;  // block strictly below the diagonal: covered by a mirror write
+          float v[32];
+          tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256 + cc * 32), v);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] *= a.alpha;
-        // direct: H[m][n] for n >= m
-        if (m < C) {
-          float* row = a.H + m * C;
+          for (int j = 0; j < 32; ++j) v[j] *= a.alpha;
+          if (n0 > m_blk0) {
+            // block strictly above the diagonal: every element goes to H[m][n] and H[n][m]
+            if (m < C) {
+              float* row = a.H + m * C + n0;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int64_t n = n0 + j;
-            if (n + 3 < C && n >= m) {
-              red_add_v4(row + n, v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
+              for (int j = 0; j < 32; j += 4)
+                if (n0 + j < C) red_add_v4(row + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+            __syncwarp();
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (n + e < C && n + e >= m) red_add(row + n + e, v[j + e]);
+            for (int j = 0; j < 32; ++j) stg[j * STG_STRIDE + lane] = v[j];
+            __syncwarp();
+            const int mq = lane & 7;
+            if (m_blk0 + 4 * mq < C) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int nl = (lane >> 3) + 4 * i;
+                const float4 t = *reinterpret_cast<const float4*>(&stg[nl * STG_STRIDE + 4 * mq]);
+                if (n0 + nl < C) red_add_v4(a.H + (n0 + nl) * C + m_blk0 + 4 * mq, t.x, t.y, t.z, t.w);
+              }
+            }
+          } else {
+            // diagonal block (n0 == m_blk0): element-wise, n >= m direct and n > m mirrored
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int64_t nn = n0 + j;
+              if (m < C && nn < C) {
+                if (j >= lane) red_add(a.H + m * C + nn, v[j]);
+                if (j > lane) red_add(a.H + nn * C + m, v[j]);
+              }
             }
           }
         }
-        // mirror: H[n][m] for n > m (lanes hold consecutive m: coalesced)
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int64_t n = n0 + j;
-          if (m < C && n < C && n > m) red_add(a.H + n * C + m, v[j]);
-        }
       }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(accum_empty);
+      ++items_done;
     }
   }
 
@@ -320,75 +409,95 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-}  // namespace
-}  // namespace lc
-
-extern "C" LC_API int lc_hessian_accum(const void* x_bf16, int64_t tokens, int64_t cols, float* H, float alpha, float beta,
-                                int ksplit, int32_t* status, lc_stream_t stream) {
-  using namespace lc;
-  if (!H || cols <= 0 || tokens < 0 || ksplit < 0) return LC_ERR_ARG;
-  if (tokens > 0 && !x_bf16) return LC_ERR_ARG;
+int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64_t cols, float* H, float alpha,
+                   float beta, int ksplit, int32_t* status, cudaStream_t st) {
+  if (!H || cols <= 0 || ksplit < 0 || nseg < 0 || nseg > MAX_SEG) return LC_ERR_ARG;
   if (cols % 8 != 0) return LC_ERR_ALIGN;
-  if (!aligned16(H) || (tokens > 0 && !aligned16(x_bf16))) return LC_ERR_ALIGN;
-  if (tokens >= (int64_t)1 << 31) return LC_ERR_SHAPE;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-
+  if (!aligned16(H)) return LC_ERR_ALIGN;
+  for (int s = 0; s < nseg; ++s) {
+    if (tokens[s] < 0 || tokens[s] >= ((int64_t)1 << 31)) return LC_ERR_SHAPE;
+    if (tokens[s] > 0 && (!xs[s] || !aligned16(xs[s]))) return xs[s] ? LC_ERR_ALIGN : LC_ERR_ARG;
+  }
   int dev = 0;
   LC_CHECK_CUDA(cudaGetDevice(&dev));
-  int major = 0;
+  int major = 0, sms = 0;
   LC_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
   if (major != 10) return LC_ERR_ARCH;
+  LC_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
   if (beta != 1.f) {
     const int64_t n = cols * cols;
     scale_kernel<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, st>>>(H, n, beta);
     LC_LAUNCH_CHECK();
   }
-  if (tokens == 0) return LC_OK;
 
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return LC_ERR_CUDA;
-  CUtensorMap tmap;
-  const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)tokens};
-  const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
-  const cuuint32_t box[2] = {ATOM, BK};
-  const cuuint32_t estr[2] = {1, 1};
-  if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x_bf16), gdim, gstride, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return LC_ERR_CUDA;
-
+  TmapArray maps;
   HessArgs a;
+  a.nseg = 0;
+  a.k_total = 0;
+  for (int s = 0; s < nseg; ++s) {
+    if (tokens[s] == 0) continue;
+    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)tokens[s]};
+    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {ATOM, BK};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&maps.m[a.nseg], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xs[s]), gdim, gstride, box,
+               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return LC_ERR_CUDA;
+    a.seg_k[a.nseg] = (int)((tokens[s] + BK - 1) / BK);
+    a.k_total += a.seg_k[a.nseg];
+    ++a.nseg;
+  }
+  if (a.nseg == 0) return LC_OK;
+  for (int s = a.nseg; s < MAX_SEG; ++s) {
+    maps.m[s] = maps.m[0];
+    a.seg_k[s] = 0;
+  }
   a.H = H;
   a.status = status;
   a.cols = cols;
-  a.tokens = (int)tokens;
-  a.m_tiles = (int)((cols + BM - 1) / BM);
-  a.n_tiles = (int)((cols + BN - 1) / BN);
+  a.n_st = (int)((cols + ST - 1) / ST);
+  a.n_super = a.n_st * (a.n_st + 1) / 2;
   a.alpha = alpha;
-  int64_t tiles = 0;
-  for (int mi = 0; mi < a.m_tiles; ++mi) tiles += a.n_tiles - (mi >> 1);
-  const int k_iters = (int)((tokens + BK - 1) / BK);
   if (ksplit == 0) {
-    // Fill whole waves of 148 CTAs while keeping at least 32 pipeline iterations per CTA.
-    int best = 1;
-    double best_eff = 0.0;
-    const int max_split = k_iters / 32 > 0 ? k_iters / 32 : 1;
-    for (int s = 1; s <= max_split && s <= 64; ++s) {
-      const int64_t items = tiles * s;
-      const int64_t waves = (items + kNumSMsB200 - 1) / kNumSMsB200;
-      const double eff = (double)items / (double)(waves * kNumSMsB200);
-      if (eff > best_eff + 0.02) {
-        best_eff = eff;
-        best = s;
-      }
+    // Enough super-tiles to occupy the SMs: no token split (one epilogue per super-tile).
+    // Otherwise split the token range so that about one item lands on every SM.
+    ksplit = 1;
+    if (a.n_super * 2 <= sms) {
+      ksplit = sms / a.n_super;
+      const int max_split = a.k_total / 8 > 0 ? a.k_total / 8 : 1;
+      if (ksplit > max_split) ksplit = max_split;
     }
-    ksplit = best;
   }
-  if (ksplit > k_iters) ksplit = k_iters;
+  if (ksplit > a.k_total) ksplit = a.k_total;
   a.ksplit = ksplit;
+  a.n_items = a.n_super * ksplit;
+  const int grid = a.n_items < sms ? a.n_items : sms;
   LC_CHECK_CUDA(cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-  hessian_umma_kernel<<<(unsigned)(tiles * ksplit), kThreads, SMEM_BYTES, st>>>(tmap, a);
+  hessian_umma_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(maps, a);
   LC_LAUNCH_CHECK();
   return LC_OK;
+}
+
+}  // namespace
+}  // namespace lc
+
+extern "C" LC_API int lc_hessian_accum(const void* x_bf16, int64_t tokens, int64_t cols, float* H, float alpha,
+                                       float beta, int ksplit, int32_t* status, lc_stream_t stream) {
+  if (tokens < 0) return LC_ERR_ARG;
+  const void* xs[1] = {x_bf16};
+  const int64_t tk[1] = {tokens};
+  if (tokens > 0 && !x_bf16) return LC_ERR_ARG;
+  return lc::hessian_launch(xs, tk, 1, cols, H, alpha, beta, ksplit, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" LC_API int lc_hessian_accum_multi(const void* const* xs_host, const int64_t* tokens_host, int nseg,
+                                             int64_t cols, float* H, float alpha, float beta, int ksplit,
+                                             int32_t* status, lc_stream_t stream) {
+  if (nseg < 0 || nseg > lc::MAX_SEG || (nseg > 0 && (!xs_host || !tokens_host))) return LC_ERR_ARG;
+  return lc::hessian_launch(xs_host, tokens_host, nseg, cols, H, alpha, beta, ksplit, status,
+                            reinterpret_cast<cudaStream_t>(stream));
 }

@@ -12,6 +12,8 @@ Differences in schedule, not in result: the Hessian is kept as the raw sum of X^
 by 2/nsamples once, and with several ranks it is all-reduced once per layer (in
 `layer_transform`) instead of after every `add_batch` call.
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -31,6 +33,12 @@ class GPTQ:
         self.owq = special.get('owq', False)
         self.chunk_num = special.get('chunk_num', 1)
         self.emit_codes = special.get('emit_codes', True)
+        # 'direct': one Cholesky of the index-reversed matrix + one triangular inverse;
+        # 'reference': the reference's three factorisations (gptq.py:172-174).  Same U up to fp32 rounding.
+        self.factorization = special.get('factorization', 'direct')
+        # forward hooks deliver one sequence per call; up to `hessian_batch` of them (<= 8) are
+        # held by reference and accumulated in one launch, so H is updated once per batch
+        self.hessian_batch = max(1, min(8, int(special.get('hessian_batch', 8))))
         self.model_dtype = model_dtype
         self.layers_cache = {}
         self._check_config()
@@ -55,6 +63,7 @@ class GPTQ:
             'H': torch.zeros((cols, cols), device=layer.weight.device, dtype=torch.float32),
             'nsamples': 0, 'columns': cols,
             'status': torch.zeros(1, dtype=torch.int32, device=layer.weight.device),
+            'pending': [],
         }
 
     @torch.no_grad()
@@ -69,13 +78,26 @@ class GPTQ:
             raise NotImplementedError('the Hessian kernel takes bf16 activations')
         x = x if x.is_contiguous() else x.contiguous()
         L.require_cuda(x)
-        L.call('lc_hessian_accum', L.ptr(x), x.shape[0], x.shape[1], L.ptr(st['H']), 1.0, 1.0, 0,
-               L.ptr(st['status']), L.stream_of(x))
+        st['pending'].append(x)
         st['nsamples'] += b
+        if len(st['pending']) >= self.hessian_batch:
+            self._flush(st)
+
+    def _flush(self, st):
+        xs = st['pending']
+        if not xs:
+            return
+        n = len(xs)
+        ptrs = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
+        toks = (ctypes.c_int64 * n)(*[x.shape[0] for x in xs])
+        L.call('lc_hessian_accum_multi', ptrs, toks, n, xs[0].shape[1], L.ptr(st['H']), 1.0, 1.0, 0,
+               L.ptr(st['status']), L.stream_of(xs[0]))
+        st['pending'] = []
 
     def _finish_hessian(self, name):
         """All-reduce once per layer (gptq.py:292-295 does it per call); returns (H_raw, 2/n)."""
         st = self.layers_cache[name]
+        self._flush(st)
         n = st['nsamples']
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(st['H'], op=dist.ReduceOp.SUM)
@@ -123,9 +145,10 @@ class GPTQ:
         Wp = torch.empty((R, C), dtype=torch.float32, device=dev)
         Hp = torch.empty((C, C), dtype=torch.float32, device=dev)
         scratch = torch.empty(4, dtype=torch.float32, device=dev)
+        direct = self.factorization == 'direct'
         L.call('lc_gptq_permute_damp', L.ptr(W), L.lc_dtype(W), L.ptr(H), L.ptr(perm), R, C, float(hscale),
-               float(self.percdamp), L.ptr(Wp), L.ptr(Hp), L.ptr(scratch), stream)
-        U = self.inverse_cholesky_upper(Hp)
+               float(self.percdamp), int(direct), L.ptr(Wp), L.ptr(Hp), L.ptr(scratch), stream)
+        U = self.inverse_cholesky_upper_reversed(Hp) if direct else self.inverse_cholesky_upper(Hp)
         del Hp
         err = torch.empty((128, R), dtype=torch.float32, device=dev)
         scales = torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev)
@@ -149,6 +172,20 @@ class GPTQ:
         # torch returns the upper factor as a transposed view of the lower one; the kernels read
         # row-major memory, so materialise it.
         return torch.linalg.cholesky(Hinv, upper=True).contiguous()
+
+    @staticmethod
+    def inverse_cholesky_upper_reversed(Hr):
+        """Same U from the index-reversed matrix Hr = J Hp J: Hr = M M^T (one cuSOLVER potrf), then
+        U = J M^-1 J (one cuBLAS triangular solve against the identity and a flip)."""
+        C = Hr.shape[0]
+        M = torch.linalg.cholesky(Hr)
+        eye = torch.eye(C, dtype=Hr.dtype, device=Hr.device)
+        Minv = torch.linalg.solve_triangular(M, eye, upper=False)
+        del M, eye
+        Minv = Minv if Minv.is_contiguous() else Minv.contiguous()   # the kernels read row-major memory
+        U = torch.empty_like(Minv)
+        L.call('lc_gptq_flip', L.ptr(Minv), C, L.ptr(U), L.stream_of(Minv))
+        return U
 
     def _install(self, layer, res):
         layer.weight.data = res['weight'].reshape(layer.weight.shape)

@@ -52,6 +52,27 @@ def test_hessian_matches_fp64(ns, T, C):
         assert torch.allclose(H, H.t(), rtol=1e-5, atol=1e-5 * float(ref.abs().max()))
 
 
+def test_hessian_multi_segment_equals_separate_calls():
+    import ctypes
+    from lightcompress_b200 import _lib as L
+    g = torch.Generator().manual_seed(2200)
+    C = 512
+    xs = [_x(g, 1, T, C)[0].cuda() for T in (96, 300, 32, 1000, 77)]
+    H = torch.zeros(C, C, device='cuda')
+    status = torch.zeros(1, dtype=torch.int32, device='cuda')
+    ptrs = (ctypes.c_void_p * len(xs))(*[x.data_ptr() for x in xs])
+    toks = (ctypes.c_int64 * len(xs))(*[x.shape[0] for x in xs])
+    L.call('lc_hessian_accum_multi', ptrs, toks, len(xs), C, L.ptr(H), 1.0, 0.0, 0, L.ptr(status), L.stream_of(H))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = sum(x.double().t() @ x.double() for x in xs)
+    assert float((H.double() - ref).abs().max() / ref.abs().max()) < 2e-5
+    # more than 8 segments is rejected on the host
+    many = (ctypes.c_void_p * 9)(*[xs[0].data_ptr()] * 9)
+    tk9 = (ctypes.c_int64 * 9)(*[96] * 9)
+    assert L.lib.lc_hessian_accum_multi(many, tk9, 9, C, L.ptr(H), 1.0, 1.0, 0, None, None) == L.LC_ERR_ARG
+
+
 def test_hessian_alpha_beta_and_empty():
     from lightcompress_b200 import _lib as L
     g = torch.Generator().manual_seed(2100)
@@ -83,10 +104,11 @@ def _mismatch(codes_perm_gpu, perm_gpu, codes_perm_ref, perm_ref):
     return float((a != b).float().mean())
 
 
-def _run_gpu_layer(W, H, sym, actorder, hscale=1.0):
+def _run_gpu_layer(W, H, sym, actorder, hscale=1.0, factorization='direct'):
     from lightcompress_b200 import GPTQ, IntegerQuantizer
     wq = IntegerQuantizer(4, sym, 'per_group', group_size=128)
-    solver = GPTQ(wq, {'actorder': actorder, 'percdamp': 0.01, 'blocksize': 128}, model_dtype=W.dtype)
+    solver = GPTQ(wq, {'actorder': actorder, 'percdamp': 0.01, 'blocksize': 128,
+                       'factorization': factorization}, model_dtype=W.dtype)
     res = solver.solve(W.cuda(), H.cuda().float(), hscale)
     torch.cuda.synchronize()
     return solver, {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in res.items()}
@@ -118,9 +140,10 @@ def test_solver_with_reference_factor_is_near_exact(golden):
         assert mism < CODE_MISMATCH_MAX, (key, mism)
 
 
-def test_layer_matches_reference_golden(golden):
+@pytest.mark.parametrize('factorization', ['direct', 'reference'])
+def test_layer_matches_reference_golden(golden, factorization):
     for key, c in golden('gptq_layer.pt').items():
-        solver, res = _run_gpu_layer(c['W'], c['H'], c['sym'], c['actorder'])
+        solver, res = _run_gpu_layer(c['W'], c['H'], c['sym'], c['actorder'], factorization=factorization)
         perm = res['buf_perm'] if c['actorder'] else torch.arange(c['W'].shape[1])
         assert torch.equal(perm, c['buf_perm']), key
         off = 8 if c['sym'] else 0
@@ -137,7 +160,24 @@ def test_layer_matches_reference_golden(golden):
         assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref, (key, e_gpu, e_ref)
 
 
-@pytest.mark.parametrize('R,C,ns,T', [(256, 512, 8, 256), (1024, 1024, 16, 512)])
+def test_inverse_factor_routes_agree():
+    """U from one reversed Cholesky + triangular inverse equals U from the reference's three
+    factorisations, and both satisfy U^T U = H^-1."""
+    from lightcompress_b200 import GPTQ
+    g = torch.Generator().manual_seed(2300)
+    C = 768
+    X = _x(g, 1, 4096, C)[0].double()
+    Hp = (X.t() @ X / 4096 + 0.01 * torch.eye(C, dtype=torch.float64)).float().cuda()
+    Hr = torch.flip(Hp, (0, 1)).contiguous()
+    U1 = GPTQ.inverse_cholesky_upper(Hp.clone())
+    U2 = GPTQ.inverse_cholesky_upper_reversed(Hr)
+    assert torch.equal(U2, torch.triu(U2))
+    assert float((U1 - U2).abs().max() / U1.abs().max()) < 1e-4
+    resid = (U2.double().t() @ U2.double()) @ Hp.double() - torch.eye(C, dtype=torch.float64, device='cuda')
+    assert float(resid.abs().max()) < 1e-3
+
+
+@pytest.mark.parametrize('R,C,ns,T', [(256, 512, 8, 256), (1024, 1024, 16, 512), (384, 640, 11, 200)])
 def test_end_to_end_layer_vs_oracle(R, C, ns, T):
     """Hessian kernel -> solver -> deploy fake quant, against the CPU oracle on the same seeds."""
     from lightcompress_b200 import GPTQ, IntegerQuantizer
