@@ -190,7 +190,8 @@ def main():
     solver = lc.GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'emit_codes': True,
                           'hessian_batch': HESSIAN_BATCH})
     layer = torch.nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device=dev)
-    r0, r1 = rank * (R // world), (rank + 1) * (R // world)
+    from lightcompress_b200 import parallel
+    r0, r1 = parallel.row_shard(R)
     hess_ev = []
 
     def step(x_dev, record=False):
@@ -209,8 +210,7 @@ def main():
             out = res['weight']
         else:
             res = solver.layer_transform(layer, 'l', rows=(r0, r1))
-            out = torch.empty((R, C), dtype=torch.float32, device=dev)
-            dist.all_gather_into_tensor(out, res['weight'])
+            out = parallel.gather_rows(res['weight'], R)
         solver.free('l')
         return out, res
 

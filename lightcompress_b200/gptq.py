@@ -15,9 +15,9 @@ by 2/nsamples once, and with several ranks it is all-reduced once per layer (in
 import ctypes
 
 import torch
-import torch.distributed as dist
 
 from . import _lib as L
+from . import parallel
 from .quant import IntegerQuantizer
 
 
@@ -98,12 +98,7 @@ class GPTQ:
         """All-reduce once per layer (gptq.py:292-295 does it per call); returns (H_raw, 2/n)."""
         st = self.layers_cache[name]
         self._flush(st)
-        n = st['nsamples']
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            dist.all_reduce(st['H'], op=dist.ReduceOp.SUM)
-            nt = torch.tensor([n], dtype=torch.int64, device=st['H'].device)
-            dist.all_reduce(nt, op=dist.ReduceOp.SUM)
-            n = int(nt.item())
+        _, n = parallel.reduce_hessian(st['H'], st['nsamples'])
         code = int(st['status'].item())
         if code != 0:
             raise L.LcError('lc_hessian_accum', code, L.status_string(code))
