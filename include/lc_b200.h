@@ -179,6 +179,28 @@ int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t col
                              int sym, float* scratch_err, float* scales, float* zeros,
                              uint8_t* codes_u8, float* loss_rows, lc_stream_t stream);
 
+/* lc_gptq_weight_transform for callers that cannot allocate.  (No counterpart in the reference:
+ * its solver allocates freely through torch.)
+ *
+ * Meant for processes that may pass their own W / U / output buffers but have no way to get
+ * scratch memory when the call is made -- all device memory belongs to a fixed pool or arena, or
+ * the calling context forbids cudaMalloc and the torch allocator.  The 128 x rows fp32 Err
+ * scratch is a fixed array inside the library image instead (8 MiB, held on every GPU that loads
+ * the library until the process exits), so this call makes no cudaMalloc / cudaFree and uses no
+ * allocating library routine.
+ *   - rows must be <= 16384; larger layers return LC_ERR_WORKSPACE (use the scratch-taking entry
+ *     point with your own buffer instead).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current) and caches it.  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the last call left in it.
+ *     Nothing in it needs to start at zero (each 128-column block overwrites it completely
+ *     before reading it), but two calls whose kernels overlap on the GPU -- different streams,
+ *     or different host threads -- race on it: serialise them.
+ * Results are identical to lc_gptq_weight_transform. */
+int lc_gptq_weight_transform_noalloc(float* W, const float* U, int64_t rows, int64_t cols, int bits,
+                                     int sym, float* scales, float* zeros, uint8_t* codes_u8,
+                                     float* loss_rows, lc_stream_t stream);
+
 /* Un-permute the kept weights (gptq.py:186-193): out[r][perm[j]] = Wp[r][j], written in
  * `out_dtype`.  perm NULL = identity. */
 int lc_gptq_unpermute(const float* Wp, const int64_t* perm, int64_t rows, int64_t cols,

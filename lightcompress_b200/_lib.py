@@ -37,6 +37,7 @@ SIGNATURES = {
     'lc_gptq_block_quant': [_p, _p, _i64, _i64, _i64, _i, _i, _i, _p, _p, _p, _i64, _p, _p, _p],
     'lc_gptq_trailing_update': [_p, _p, _p, _i64, _i64, _i64, _i, _i64, _p],
     'lc_gptq_weight_transform': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p],
+    'lc_gptq_weight_transform_noalloc': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p],
     'lc_gptq_unpermute': [_p, _p, _i64, _i64, _p, _i, _p],
 }
 

@@ -159,6 +159,49 @@ extern "C" LC_API int lc_gptq_trailing_update(float* W, const float* err, const 
   return lc::gptq_trail_launch(W, err, U, rows, cols, col0, k, col1, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// ---- allocation-free variant -------------------------------------------------------------------
+// Some callers can hand over their weight and factor buffers but cannot obtain scratch memory at
+// call time: a serving or export process whose device memory is entirely owned by a pool or an
+// arena it must not grow, or code running where cudaMalloc / the torch caching allocator is off
+// limits (inside a region that forbids allocation, or a plugin host that gives the plugin no
+// allocator).  For them the Err scratch of the block loop lives in a fixed device array that is
+// part of this library's image.  Every GPU that loads the library carries these 8 MiB until the
+// process exits.
+constexpr int64_t kNoAllocMaxRows = 16384;  // rows of W the fixed scratch can serve
+static __device__ __align__(256) float g_noalloc_err[128 * kNoAllocMaxRows];
+
+namespace lc {
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_noalloc_err per device ordinal.  In host code the array's name is only a
+// handle: the address a kernel can use must be asked for, once per device, with that device current.
+float* g_noalloc_ptr[kMaxDevices] = {};
+
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  LC_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return LC_ERR_ARG;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_err) != cudaSuccess || p == nullptr) return LC_ERR_CUDA;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return LC_OK;
+}
+}  // namespace
+}  // namespace lc
+
+extern "C" LC_API int lc_gptq_weight_transform_noalloc(float* W, const float* U, int64_t rows, int64_t cols,
+                                                       int bits, int sym, float* scales, float* zeros,
+                                                       uint8_t* codes_u8, float* loss_rows, lc_stream_t stream) {
+  if (rows > kNoAllocMaxRows) return LC_ERR_WORKSPACE;  // the built-in scratch holds 128 x 16384 floats
+  float* scratch = nullptr;
+  const int rc = lc::noalloc_scratch(&scratch);
+  if (rc != LC_OK) return rc;
+  return lc_gptq_weight_transform(W, U, rows, cols, bits, sym, scratch, scales, zeros, codes_u8, loss_rows, stream);
+}
+
 extern "C" LC_API int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t cols, int bits, int sym,
                                         float* scratch_err, float* scales, float* zeros, uint8_t* codes_u8,
                                         float* loss_rows, lc_stream_t stream) {

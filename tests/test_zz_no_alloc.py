@@ -1,0 +1,69 @@
+"""The allocation-free GPTQ block loop (lc_gptq_weight_transform_noalloc) against the
+scratch-taking entry point.
+
+The no-alloc variant exists for callers that own all their device memory up front (a fixed
+pool / arena, or a context where cudaMalloc and the torch allocator may not be called) and so
+cannot provide the Err scratch buffer at call time.  It must give exactly the results of
+lc_gptq_weight_transform, call after call, although every call reuses the same built-in scratch
+array and finds the previous call's contents in it.  Both entry points are driven through the
+C ABI with raw pointers; the only torch involvement is owning the input / output tensors, which
+are all created before the calls under test.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(seed, R, C):
+    g = torch.Generator().manual_seed(seed)
+    W = (torch.randn(R, C, generator=g) * 0.02)
+    X = torch.randn(2048, C, generator=g)
+    X[:, torch.randperm(C, generator=g)[:max(1, C // 100)]] *= 20
+    H = (X.t() @ X) * (2.0 / 16)
+    H += 0.01 * H.diagonal().mean() * torch.eye(C)
+    U = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(H)), upper=True).contiguous()
+    return W.cuda().contiguous(), U.cuda().contiguous()
+
+
+def _outputs(R, C):
+    n_g = (C + 127) // 128
+    return dict(scales=torch.empty(R * n_g, device='cuda'), zeros=torch.empty(R * n_g, device='cuda'),
+                codes=torch.empty(R, C, dtype=torch.uint8, device='cuda'), loss=torch.empty(R, device='cuda'))
+
+
+def test_noalloc_matches_scratch_variant_on_consecutive_calls():
+    from lightcompress_b200 import _lib as L
+    # two different problems back to back: the second call finds the first one's leftovers in the
+    # shared scratch array (and, being smaller, does not even overwrite all of them)
+    for seed, R, C, sym in ((11, 320, 512, 0), (12, 96, 384, 1)):
+        W0, U = _problem(seed, R, C)
+        Wa, Wb = W0.clone(), W0.clone()
+        oa, ob = _outputs(R, C), _outputs(R, C)
+        err = torch.empty(128, R, device='cuda')
+        stream = L.stream_of(W0)
+        torch.cuda.synchronize()
+        L.call('lc_gptq_weight_transform', L.ptr(Wa), L.ptr(U), R, C, 4, sym, L.ptr(err), L.ptr(oa['scales']),
+               L.ptr(oa['zeros']), L.ptr(oa['codes']), L.ptr(oa['loss']), stream)
+        before = torch.cuda.memory_allocated()
+        L.call('lc_gptq_weight_transform_noalloc', L.ptr(Wb), L.ptr(U), R, C, 4, sym, L.ptr(ob['scales']),
+               L.ptr(ob['zeros']), L.ptr(ob['codes']), L.ptr(ob['loss']), stream)
+        assert torch.cuda.memory_allocated() == before
+        torch.cuda.synchronize()
+        # same kernels, same order of operations: the tolerance the solver tests use for codes
+        # (< 0.1 % mismatches) is met with room to spare -- the results are in fact identical
+        assert float((oa['codes'] != ob['codes']).float().mean()) < 1e-3
+        assert torch.equal(oa['codes'], ob['codes'])
+        assert torch.equal(Wa, Wb)
+        assert torch.equal(oa['scales'], ob['scales']) and torch.equal(oa['zeros'], ob['zeros'])
+        assert torch.allclose(oa['loss'], ob['loss'], rtol=1e-6, atol=0)
+        assert not torch.equal(Wb, W0)          # the call did its work
+
+
+def test_noalloc_rejects_layers_beyond_its_scratch():
+    from lightcompress_b200 import _lib as L
+    dummy = torch.empty(16, device='cuda')
+    rc = L.lib.lc_gptq_weight_transform_noalloc(L.ptr(dummy), L.ptr(dummy), 16385, 128, 4, 0, L.ptr(dummy),
+                                                L.ptr(dummy), None, None, None)
+    assert rc == L.LC_ERR_WORKSPACE
+    assert 'workspace' in L.status_string(rc)
