@@ -1,21 +1,26 @@
-"""Benchmark of the GPTQ hot path: one linear layer 4096 -> 4096 (bf16), 128 x 2048 calibration
-tokens, W4 asymmetric g128, act-order, percdamp 0.01 (the single-layer GPTQ configuration).
+"""Benchmark of the GPTQ calibration hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload block|layer]
 
-A step = Hessian accumulation over every calibration sample (add_batch is called once per
-sequence, the way the algorithm's forward hook delivers them; the plugin hands 8 sequences to
-one lc_hessian_accum_multi launch) + the GPTQ layer solve.  Inputs are
-seeded synthetic tensors with the configuration's shapes and value distributions.
+Default workload `block` (the end-to-end GPTQ configuration's unit of work): ONE Llama-2-7B-shape
+decoder layer (hidden 4096, 32 heads, MLP 11008, bf16, weights N(0, 0.02^2)) quantised with GPTQ
+W4A16 asymmetric g128, act-order, percdamp 0.01, true_sequential, quant_out, on 128 x 2048 tokens
+of synthetic hidden states (N(0,1), 1 % outlier channels x20).  A step = the reference's
+per-block schedule (5 forwards of the block over all sequences, 4 distinct Hessians, 7 layer
+solves); value = decoder layers per second.
 
-N > 1 (launched by torch.distributed.run): calibration sequences are sharded over the ranks,
-the raw Hessian is all-reduced once (NCCL), the rows of the layer are split over the ranks for
-the solve and all-gathered.  Total work is fixed: strong scaling.
+Workload `layer` (the single-linear GPTQ configuration): one 4096 -> 4096 linear, 128 x 2048 x 4096
+calibration activations; a step = Hessian accumulation over all sequences + the layer solve.
+
+N > 1 (launched by torch.distributed.run): calibration sequences are sharded over the ranks, each
+Hessian is all-reduced once (NCCL), the (linear, row-range) solve units are dealt to the ranks.
+Total work is fixed: strong scaling.
 
 `--impl reference` times the CPU restatement of the reference (oracle/) on the host cores, on a
 bounded sample of the same workload.
 """
 import argparse
+import copy
 import json
 import os
 import subprocess
@@ -27,11 +32,19 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-R, C, NS, T = 4096, 4096, 128, 2048
-METRIC = 'GPTQ W4 g128 layers/sec'
+NS, T, HID, INTER, HEADS = 128, 2048, 4096, 11008, 32
+METRIC = 'GPTQ W4 g128 decoder layers/sec'
 UNIT = 'layers/s'
-WORKLOAD = ('GPTQ single linear 4096x4096 bf16, calibration 128x2048x4096 N(0,1) with 1% outlier channels x20, '
-            'W4 asym g128, blocksize 128, percdamp 0.01, act_order')
+HESSIAN_BATCH = 8   # sequences handed to one Hessian launch (GPTQ special key `hessian_batch`)
+SPECIAL = {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'true_sequential': True,
+           'static_groups': False, 'hessian_batch': HESSIAN_BATCH, 'emit_codes': True}
+WORKLOADS = {
+    'block': ('one Llama-2-7B-shape decoder layer (hidden 4096, 32 heads, MLP 11008, bf16 N(0,0.02^2)), GPTQ W4A16 '
+              'asym g128, act_order, percdamp 0.01, true_sequential, quant_out; calibration 128x2048 tokens of '
+              'hidden states N(0,1) with 1% outlier channels x20'),
+    'layer': ('GPTQ single linear 4096x4096 bf16 N(0,0.02^2), calibration 128x2048x4096 N(0,1) with 1% outlier '
+              'channels x20, W4 asym g128, blocksize 128, percdamp 0.01, act_order'),
+}
 
 
 def peaks():
@@ -42,20 +55,61 @@ def peaks():
     return 6650.0, 1590.0, 1400.0, 'fallback'
 
 
-def make_inputs(n_seq, seed_offset=0, pin=False):
+# ---- synthetic inputs --------------------------------------------------------------------------
+def make_activations(n_seq, seed, pin=False):
+    """(n_seq, T, HID) bf16, N(0,1) with 1 % of the channels scaled x20 (same channels on every rank)."""
     import torch
     g = torch.Generator().manual_seed(2000)
-    W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16)
-    ch = torch.randperm(C, generator=g)[:C // 100]
-    gx = torch.Generator().manual_seed(2001 + seed_offset)
-    X = torch.empty((n_seq, T, C), dtype=torch.bfloat16, pin_memory=pin)
+    ch = torch.randperm(HID, generator=g)[:HID // 100]
+    gx = torch.Generator().manual_seed(seed)
+    X = torch.empty((n_seq, T, HID), dtype=torch.bfloat16, pin_memory=pin)
     for i in range(n_seq):
-        x = torch.randn(T, C, generator=gx)
+        x = torch.randn(T, HID, generator=gx)
         x[:, ch] *= 20
         X[i] = x.to(torch.bfloat16)
-    if pin:
-        W = W.pin_memory()
-    return W, X
+    return X
+
+
+def make_linear_weight():
+    import torch
+    g = torch.Generator().manual_seed(2000)
+    return (torch.randn(HID, HID, generator=g) * 0.02).to(torch.bfloat16)
+
+
+def make_block(seq_len=T):
+    """Random-init Llama decoder layer of the 7B shape from the installed transformers + forward kwargs."""
+    import torch
+    from transformers import LlamaConfig
+    from transformers.models.llama.modeling_llama import LlamaDecoderLayer, LlamaRotaryEmbedding
+    cfg = LlamaConfig(hidden_size=HID, intermediate_size=INTER, num_attention_heads=HEADS,
+                      num_key_value_heads=HEADS, num_hidden_layers=1, vocab_size=32000,
+                      max_position_embeddings=4096, rms_norm_eps=1e-5)
+    cfg._attn_implementation = 'sdpa'
+    g = torch.Generator().manual_seed(4000)
+    block = LlamaDecoderLayer(cfg, 0).to(torch.bfloat16)
+    for p in block.parameters():
+        if p.dim() == 2:
+            p.data = (torch.randn(p.shape, generator=g) * 0.02).to(torch.bfloat16)
+    rot = LlamaRotaryEmbedding(cfg)
+    pos = torch.arange(seq_len)[None]
+    cos, sin = rot(torch.zeros(1, seq_len, HID, dtype=torch.bfloat16), pos)
+    return block, {'position_embeddings': (cos, sin), 'attention_mask': None, 'position_ids': pos}
+
+
+def kwargs_to(kwargs, dev):
+    import torch
+    out = {}
+    for k, v in kwargs.items():
+        if torch.is_tensor(v):
+            out[k] = v.to(dev)
+        elif isinstance(v, tuple):
+            out[k] = tuple(t.to(dev) for t in v)
+        else:
+            out[k] = v
+    return out
+
+
+LINEAR_SHAPES = [(HID, HID)] * 4 + [(INTER, HID)] * 2 + [(HID, INTER)]   # (rows, cols) of q,k,v,o,gate,up,down
 
 
 class ClockSampler:
@@ -97,68 +151,140 @@ class ClockSampler:
                     reasons.add(n)
         if not sm:
             return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['no samples']}
-        # median over the busier half of the samples (the sampler also sees idle gaps)
+        # median over the samples taken under load (the sampler also sees idle gaps between phases)
         busy = sorted(s for s, p in zip(sm, power) if p >= 0.5 * max(power)) or sorted(sm)
         return {'sm_mhz': busy[len(busy) // 2], 'sm_max_mhz': max(mx), 'power_w_max': max(power),
                 'samples': len(sm), 'reasons': sorted(reasons)}
 
 
-HESSIAN_BATCH = 8   # sequences handed to one Hessian launch (GPTQ special key `hessian_batch`)
-
-
-def launches_per_step(n_seq):
-    n_blocks = C // 128
-    # hessian per batch of sequences + diag + (damp, permute H, permute W) + flip + block + trailing + un-permute
-    return -(-n_seq // HESSIAN_BATCH) + 1 + 3 + 1 + n_blocks + (n_blocks - 1) + 1
-
-
-def cpu_port(n_hess_samples=8, threads=None):
-    """Times the oracle port on a bounded sample; returns (layers/s extrapolated, description, cores)."""
+# ---- CPU port (oracle) on a bounded sample --------------------------------------------------------
+def cpu_port_layer(n_hess_samples=8):
     import torch
     from oracle import gptq_ref
-    cores = threads or os.cpu_count()
+    cores = os.cpu_count()
     torch.set_num_threads(cores)
-    W, X = make_inputs(n_hess_samples)
-    st = gptq_ref.hessian_init(C)
+    W = make_linear_weight()
+    X = make_activations(n_hess_samples, 2001)
+    st = gptq_ref.hessian_init(HID)
     t0 = time.perf_counter()
     for i in range(n_hess_samples):
         gptq_ref.add_batch(st, X[i:i + 1])
     t_h = (time.perf_counter() - t0) / n_hess_samples * NS
-    # a well-conditioned stand-in for the full-data Hessian: the solver's cost does not depend on values
     t0 = time.perf_counter()
-    gptq_ref.quantize_layer(W, st['H'] + 1e-3 * torch.eye(C) * float(st['H'].diagonal().mean()))
+    gptq_ref.quantize_layer(W, st['H'] + 1e-3 * torch.eye(HID) * float(st['H'].diagonal().mean()))
     t_s = time.perf_counter() - t0
-    desc = (f'Hessian: {n_hess_samples} of {NS} samples timed and scaled x{NS // n_hess_samples}; '
-            f'prepare + weight_transform: full 4096x4096 layer')
-    return 1.0 / (t_h + t_s), desc, cores, t_h, t_s
+    desc = (f'Hessian: {n_hess_samples} of {NS} sequences timed and scaled x{NS // n_hess_samples}; '
+            f'prepare + weight_transform: the full 4096x4096 layer')
+    return 1.0 / (t_h + t_s), desc, cores, {'hessian_s': t_h, 'solver_s': t_s}
+
+
+def cpu_port_block():
+    """One sequence through the reference schedule's five forwards with its Hessian hooks (scaled
+    x128), plus the solver: prepare and weight_transform timed on a 4096x4096 linear and scaled to
+    the seven linears by C^3 and rows*cols respectively."""
+    import torch
+    from oracle import gptq_block_ref, gptq_ref
+    cores = os.cpu_count()
+    torch.set_num_threads(cores)
+    block, kwargs = make_block()
+    x = make_activations(1, 2001)
+    subsets = gptq_block_ref.llama_subsets(block)
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        for p in range(5):
+            # pass 0 hooks all seven linears, passes 1-3 the next subset, pass 4 (quant_out) none
+            items = [it for s in subsets for it in s] if p == 0 else (subsets[p] if p < 4 else [])
+            states, hs = {}, []
+            for name, parent, attr in items:
+                layer = getattr(parent, attr)
+                states[name] = gptq_ref.hessian_init(layer.weight.shape[1])
+
+                def hook(m, inp, out, name=name, states=states):
+                    gptq_ref.add_batch(states[name], inp[0].data)
+                hs.append(layer.register_forward_hook(hook))
+            block(x[0:1], **kwargs)
+            for h in hs:
+                h.remove()
+    t_fwd = (time.perf_counter() - t0) * NS
+    W = make_linear_weight()
+    g = torch.Generator().manual_seed(1)
+    Xs = torch.randn(8192, HID, generator=g)
+    H = (Xs.t() @ Xs) * (2.0 / 4)
+    t0 = time.perf_counter()
+    Wp, U, perm, invperm = gptq_ref.prepare(W, H)
+    t_prep = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    gptq_ref.weight_transform(Wp, U)
+    t_wt = time.perf_counter() - t0
+    t_solver = sum(t_prep * (c / HID) ** 3 + t_wt * (r * c) / (HID * HID) for r, c in LINEAR_SHAPES)
+    desc = (f'forwards + Hessian hooks: 1 of {NS} sequences through the 5 passes, scaled x{NS}; solver: prepare and '
+            f'weight_transform timed on one 4096x4096 linear, scaled to the 7 linears by C^3 and rows*cols')
+    return 1.0 / (t_fwd + t_solver), desc, cores, {'forward_hessian_s': t_fwd, 'solver_s': t_solver}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    vals = []
-    desc = cores = None
+    fn = cpu_port_block if args.workload == 'block' else (lambda: cpu_port_layer(4))
+    vals, desc, cores = [], None, None
     for i in range(args.warmup + args.steps):
-        v, desc, cores, t_h, t_s = cpu_port(4 if args.steps + args.warmup > 2 else 8)
+        v, desc, cores, _ = fn()
         if i >= args.warmup:
             vals.append(v)
     v = sum(vals) / len(vals)
-    line = {'impl': 'reference', 'metric': METRIC, 'value': v, 'unit': UNIT, 'n_gpus': args.gpus,
-            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 / v, 'higher_is_better': True,
-            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'bf16 in / fp32 accumulate', 'data': 'synthetic',
-            'config': {'workload': WORKLOAD},
-            'cpu_baseline': {'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc},
-            'e2e': {'value': v, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
-            'gpu_launches': 0}
-    print(json.dumps(line))
+    print(json.dumps({
+        'impl': 'reference', 'metric': METRIC, 'value': v, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': args.steps,
+        'warmup': args.warmup, 'ms_per_step': 1e3 / v, 'higher_is_better': True, 'scaling': 'strong',
+        'vs_baseline': None, 'dtype': 'bf16 in / fp32 accumulate', 'data': 'synthetic',
+        'config': {'workload': WORKLOADS[args.workload], 'name': args.workload},
+        'cpu_baseline': {'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc},
+        'e2e': {'value': v, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}, 'gpu_launches': 0}))
+
+
+# ---- GPU workloads ---------------------------------------------------------------------------------
+class HessianTimer:
+    """Brackets every Hessian launch with CUDA events on the launching stream."""
+
+    def __init__(self, solver):
+        self.pairs = []
+        self.on = False
+        orig = solver._flush
+
+        def flush(st):
+            if not self.on or not st['pending']:
+                return orig(st)
+            import torch
+            cols = st['pending'][0].shape[1]
+            toks = sum(x.shape[0] for x in st['pending'])
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            orig(st)
+            e1.record()
+            self.pairs.append((cols, toks, e0, e1))
+        solver._flush = flush
+
+    def summary(self):
+        by_c = {}
+        for cols, toks, e0, e1 in self.pairs:
+            d = by_c.setdefault(cols, [0, 0.0, 0])
+            d[0] += 1
+            d[1] += e0.elapsed_time(e1)
+            d[2] += toks
+        return by_c
+
+
+def n_super(c):
+    s = -(-c // 256)
+    return s * (s + 1) // 2
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=5)
+    ap.add_argument('--steps', type=int, default=3)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    ap.add_argument('--workload', default='block', choices=['block', 'layer'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
     args = ap.parse_args()
@@ -172,47 +298,114 @@ def main():
     import torch
     import torch.distributed as dist
     import lightcompress_b200 as lc
-    from lightcompress_b200 import _lib as L
+    from lightcompress_b200 import parallel
 
     torch.cuda.set_device(local_rank)
     dev = torch.device('cuda', local_rank)
     if world > 1:
         dist.init_process_group('nccl', device_id=dev)
     assert world == args.gpus, f'--gpus {args.gpus} but WORLD_SIZE={world}'
-    assert NS % world == 0 and R % world == 0
-    n_seq = NS // world
+    s0, s1 = parallel.sequence_shard(NS)
+    n_seq = s1 - s0
     hbm_peak, tf_burst, tf_sust, peak_kind = peaks()
-
-    W_host, X_host = make_inputs(n_seq, seed_offset=rank, pin=not args.no_e2e)
-    W = W_host.to(dev)
-    X = X_host.to(dev)
     wq = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
-    solver = lc.GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'emit_codes': True,
-                          'hessian_batch': HESSIAN_BATCH})
-    layer = torch.nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device=dev)
-    from lightcompress_b200 import parallel
-    r0, r1 = parallel.row_shard(R)
-    hess_ev = []
 
-    def step(x_dev, record=False):
-        layer.weight.data = W
-        solver.layer_init(layer, 'l')
-        if record:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-        for i in range(n_seq):
-            solver.add_batch(layer, 'l', x_dev[i:i + 1])
-        if record:
-            e1.record()
-            hess_ev.append((e0, e1))
-        if world == 1:
-            res = solver.layer_transform(layer, 'l')
-            out = res['weight']
-        else:
-            res = solver.layer_transform(layer, 'l', rows=(r0, r1))
-            out = parallel.gather_rows(res['weight'], R)
-        solver.free('l')
-        return out, res
+    X_host = make_activations(n_seq, 2001 + rank, pin=not args.no_e2e)
+    X = X_host.to(dev)
+
+    if args.workload == 'block':
+        block_host, kwargs_host = make_block()
+        kwargs = kwargs_to(kwargs_host, dev)
+        master = copy.deepcopy(block_host).to(dev)
+        runner = lc.GPTQBlockwise(wq, SPECIAL, quant_out=True)
+        solver = runner.solver
+        timer = HessianTimer(solver)
+        inputs = [X[i:i + 1] for i in range(n_seq)]
+
+        def step():
+            block = copy.deepcopy(master)          # device copy of the bf16 block (the reference does block.cuda())
+            outs = runner.block_opt(block, inputs, kwargs)
+            return block, outs
+
+        if not args.no_e2e:
+            for p in block_host.parameters():
+                p.data = p.data.pin_memory()
+            x_stage = torch.empty_like(X)
+            w_host = {n: torch.empty(rc, dtype=torch.float32).pin_memory()
+                      for n, rc in zip(['q', 'k', 'v', 'o', 'gate', 'up', 'down'], LINEAR_SHAPES)}
+
+            host_params = [p.data for p in block_host.parameters()]
+
+            def e2e_step():
+                x_stage.copy_(X_host, non_blocking=True)
+                block = copy.deepcopy(master)          # module skeleton on the device ...
+                for p, hp in zip(block.parameters(), host_params):
+                    p.data.copy_(hp, non_blocking=True)    # ... filled from pinned host memory (block.cuda())
+                outs = runner.block_opt(block, [x_stage[i:i + 1] for i in range(n_seq)], kwargs)
+                a, m = block.self_attn, block.mlp
+                for key, mod in zip(w_host, [a.q_proj, a.k_proj, a.v_proj, a.o_proj, m.gate_proj, m.up_proj,
+                                             m.down_proj]):
+                    w_host[key].copy_(mod.weight, non_blocking=True)     # the reference's block.cpu()
+                return outs
+            h2d = int(X_host.numel() * 2 + sum(p.numel() * 2 for p in block_host.parameters()))
+            d2h = int(sum(w.numel() * 4 for w in w_host.values()))
+        n_blocks_solver = sum(-(-c // 128) for r, c in LINEAR_SHAPES)
+        # 4 Hessians, 4 diag, per linear (damp, permute H, permute W, flip, un-permute), block + trailing
+        # kernels, per linear the deploy-time fake quant (gather is torch)
+        launches = 4 * -(-n_seq // HESSIAN_BATCH) + 4 + 7 * 5 + (2 * n_blocks_solver - 7) + 7
+    else:
+        W_host = make_linear_weight().pin_memory() if not args.no_e2e else make_linear_weight()
+        W = W_host.to(dev)
+        solver = lc.GPTQ(wq, SPECIAL)
+        timer = HessianTimer(solver)
+        layer = torch.nn.Linear(HID, HID, bias=False, dtype=torch.bfloat16, device=dev)
+        r0, r1 = parallel.row_shard(HID)
+
+        def run_layer(x_dev, w):
+            layer.weight.data = w
+            solver.layer_init(layer, 'l')
+            for i in range(n_seq):
+                solver.add_batch(layer, 'l', x_dev[i:i + 1])
+            res = solver.layer_transform(layer, 'l', rows=None if world == 1 else (r0, r1))
+            out = res['weight'] if world == 1 else parallel.gather_rows(res['weight'], HID)
+            solver.free('l')
+            return out, res
+
+        def step():
+            return run_layer(X, W)
+
+        if not args.no_e2e:
+            copy_stream = torch.cuda.Stream(device=dev)
+            x_stage = torch.empty_like(X)
+            rows_here = HID if world == 1 else r1 - r0
+            out_host = torch.empty((rows_here, HID), dtype=torch.float32).pin_memory()
+            sc_host = torch.empty((rows_here * (HID // 128), 1), dtype=torch.float32).pin_memory()
+            zr_host = torch.empty_like(sc_host).pin_memory()
+
+            def e2e_step():
+                main_s = torch.cuda.current_stream()
+                copy_stream.wait_stream(main_s)       # the previous step's readers of x_stage are done
+                layer.weight.data = W_host.to(dev, non_blocking=True)
+                solver.layer_init(layer, 'l')
+                evs = []
+                with torch.cuda.stream(copy_stream):
+                    for i in range(0, n_seq, HESSIAN_BATCH):
+                        x_stage[i:i + HESSIAN_BATCH].copy_(X_host[i:i + HESSIAN_BATCH], non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record(copy_stream)
+                        evs.append(ev)
+                for k, i in enumerate(range(0, n_seq, HESSIAN_BATCH)):
+                    main_s.wait_event(evs[k])
+                    for j in range(i, min(i + HESSIAN_BATCH, n_seq)):
+                        solver.add_batch(layer, 'l', x_stage[j:j + 1])
+                res = solver.layer_transform(layer, 'l', rows=None if world == 1 else (r0, r1))
+                out_host.copy_(res['weight'], non_blocking=True)
+                sc_host.copy_(res['buf_scales'], non_blocking=True)
+                zr_host.copy_(res['buf_zeros'], non_blocking=True)
+                solver.free('l')
+            h2d = int(X_host.numel() * 2 + W_host.numel() * 2)
+            d2h = int(out_host.numel() * 4 + sc_host.numel() * 8)
+        launches = -(-n_seq // HESSIAN_BATCH) + 1 + 3 + 1 + 2 * (HID // 128) - 1 + 1
 
     def sync_all():
         torch.cuda.synchronize()
@@ -235,54 +428,22 @@ def main():
 
     # ---- device-resident throughput ------------------------------------------------------------
     for _ in range(args.warmup):
-        step(X)
+        step()
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    ms_total = timed(lambda: step(X, record=True), args.steps)
-    ms_step = ms_total / args.steps
+    timer.on = True
+    ms_step = timed(step, args.steps) / args.steps
+    timer.on = False
     value = 1e3 / ms_step
-    hess_ms = sum(a.elapsed_time(b) for a, b in hess_ev) / len(hess_ev)
-    n_hess_launches = -(-n_seq // HESSIAN_BATCH)
-    hess_launch_ms = hess_ms / n_hess_launches
-    tok_per_launch = T * n_seq / n_hess_launches
+    hess = timer.summary()
 
     # ---- end to end: host buffers in, host result out ------------------------------------------
     e2e = None
     if not args.no_e2e:
-        copy_stream = torch.cuda.Stream(device=dev)
-        x_stage = torch.empty_like(X)
-        out_host = torch.empty((R // world, C), dtype=torch.float32).pin_memory()
-        sc_host = torch.empty((R // world * (C // 128), 1), dtype=torch.float32).pin_memory()
-        zr_host = torch.empty_like(sc_host).pin_memory()
-        chunk = 8
-
-        def e2e_step():
-            main = torch.cuda.current_stream()
-            copy_stream.wait_stream(main)       # previous step's readers of x_stage are done
-            layer.weight.data = W_host.to(dev, non_blocking=True)
-            solver.layer_init(layer, 'l')
-            evs = []
-            with torch.cuda.stream(copy_stream):
-                for i in range(0, n_seq, chunk):
-                    x_stage[i:i + chunk].copy_(X_host[i:i + chunk], non_blocking=True)
-                    ev = torch.cuda.Event()
-                    ev.record(copy_stream)
-                    evs.append(ev)
-            for k, i in enumerate(range(0, n_seq, chunk)):
-                main.wait_event(evs[k])
-                for j in range(i, min(i + chunk, n_seq)):
-                    solver.add_batch(layer, 'l', x_stage[j:j + 1])
-            res = solver.layer_transform(layer, 'l', rows=None if world == 1 else (r0, r1))
-            out_host.copy_(res['weight'], non_blocking=True)
-            sc_host.copy_(res['buf_scales'], non_blocking=True)
-            zr_host.copy_(res['buf_zeros'], non_blocking=True)
-            solver.free('l')
-
         for _ in range(2):
             e2e_step()
         e2e_ms = timed(e2e_step, args.steps) / args.steps
-        e2e = {'value': 1e3 / e2e_ms, 'unit': UNIT, 'ms_per_step': e2e_ms,
-               'h2d_bytes_per_step': int(X_host.numel() * 2 + W_host.numel() * 2),
-               'd2h_bytes_per_step': int(out_host.numel() * 4 + sc_host.numel() * 8)}
+        e2e = {'value': 1e3 / e2e_ms, 'unit': UNIT, 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': h2d,
+               'd2h_bytes_per_step': d2h}
     clocks = sampler.stop() if sampler else None
 
     if rank != 0:
@@ -290,31 +451,37 @@ def main():
             dist.destroy_process_group()
         return
 
-    # ---- roofline of the dominant kernel (Hessian GEMM) ------------------------------------------
-    alg_flops = 2.0 * tok_per_launch * C * C          # per launch: the full square the reference computes
-    n_super = (C // 256) * (C // 256 + 1) // 2
-    exe_flops = 2.0 * tok_per_launch * 256 * 256 * n_super   # 256x256 tiles actually issued (upper triangle)
-    achieved = alg_flops / (hess_launch_ms * 1e-3) / 1e12
-    peak = tf_sust
-    roofline = {'bound': 'tensor', 'kernel': 'hessian_umma_kernel', 'achieved': achieved, 'peak': peak,
-                'unit': 'TFLOP/s', 'frac': achieved / peak, 'peak_kind': f'{peak_kind} sustained cuBLAS bf16',
-                'achieved_executed': exe_flops / (hess_launch_ms * 1e-3) / 1e12,
-                'launch_ms': hess_launch_ms, 'launches_per_step': n_hess_launches,
-                'tokens_per_launch': tok_per_launch, 'share_of_step': hess_ms / ms_step,
+    # ---- roofline of the dominant kernel of ours: the Hessian GEMM -------------------------------
+    # algorithmic FLOPs = 2 * tokens * C^2 per launch (the full square the reference computes);
+    # executed = the 256x256 tiles on/above the diagonal that are actually issued
+    n_l = sum(d[0] for d in hess.values())
+    ms_l = sum(d[1] for d in hess.values())
+    alg = sum(2.0 * d[2] * c * c for c, d in hess.items())
+    exe = sum(2.0 * d[2] * 256 * 256 * n_super(c) for c, d in hess.items())
+    achieved = alg / (ms_l * 1e-3) / 1e12
+    roofline = {'bound': 'tensor', 'kernel': 'hessian_umma_kernel', 'achieved': achieved, 'peak': tf_sust,
+                'unit': 'TFLOP/s', 'frac': achieved / tf_sust,
+                'peak_kind': f'{peak_kind} sustained cuBLAS bf16 (of measured)',
+                'achieved_executed': exe / (ms_l * 1e-3) / 1e12, 'frac_executed': exe / (ms_l * 1e-3) / 1e12 / tf_sust,
+                'launch_ms': ms_l / n_l, 'launches_per_step': n_l / args.steps,
+                'share_of_step': ms_l / args.steps / ms_step,
+                'per_cols': {str(c): {'launches_per_step': d[0] / args.steps, 'launch_ms': d[1] / d[0],
+                                      'tokens_per_launch': d[2] / d[0]} for c, d in hess.items()},
                 'traffic': None}
 
     line = {'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'bf16 in / fp32 accumulate', 'data': 'synthetic',
-            'config': {'workload': WORKLOAD, 'l2': 'inputs (2.1 GB of activations per step) exceed the 126 MB L2',
-                       'sharding': f'{n_seq} sequences and {R // world} rows per rank'},
-            'roofline': roofline, 'gpu_launches': launches_per_step(n_seq) * args.steps, 'clocks': clocks}
+            'config': {'workload': WORKLOADS[args.workload], 'name': args.workload,
+                       'l2': 'inputs (2.1 GB of activations per step) exceed the 126 MB L2',
+                       'sharding': f'{n_seq} sequences per rank; solve units (linear, row range) dealt to the ranks',
+                       'hessian_batch': HESSIAN_BATCH},
+            'roofline': roofline, 'gpu_launches': launches * args.steps, 'clocks': clocks}
     if e2e:
         line['e2e'] = e2e
     if not args.no_cpu_baseline and world == 1:
-        v, desc, cores, t_h, t_s = cpu_port(8)
-        line['cpu_baseline'] = {'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc,
-                                'hessian_s': t_h, 'solver_s': t_s}
+        v, desc, cores, parts = (cpu_port_block() if args.workload == 'block' else cpu_port_layer(8))
+        line['cpu_baseline'] = dict({'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc}, **parts)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -1,0 +1,215 @@
+"""Block-level driver of the GPTQ hot path: one decoder block through the reference's schedule.
+
+Mirrors, for the GPTQ algorithm, what BaseBlockwiseQuantization does per block
+(llmc/compression/quantization/base_blockwise_quantization.py: block_opt :403-432, run :447-485,
+block_transform :487-527, rehook_next_subset :529-549, block_forward :378-401) with the subsets of
+the Llama adapter (llmc/models/llama.py:52-91):
+
+    hook the linears -> forward all calibration sequences (Hessians accumulate in the hooks)
+    for each subset [q,k,v] -> [o] -> [gate,up] -> [down]:
+        quantise its linears (GPTQ.layer_transform)
+        true_sequential: swap them for fake-quant linears, hook the next subset, forward again
+    quant_out: forward once more through the fully fake-quantised block -> inputs of the next block
+
+Two schedule differences that do not change any result:
+  * the linears of a subset read the same tensor, so one Hessian is accumulated per subset and
+    shared (the reference accumulates identical copies, gptq.py:247-251, :298-308);
+  * with true_sequential the first pass only hooks the first subset: the Hessians of later subsets
+    collected in that pass are re-zeroed by subset_init before use (gptq.py:311-315).
+
+Several ranks: each rank forwards its own sequences; every Hessian is all-reduced once; the
+(linear, row-range) solve units of a subset are dealt round-robin to the ranks and the results
+broadcast, so every rank continues with identical weights.
+"""
+from collections import OrderedDict
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import parallel
+from .gptq import GPTQ
+
+
+class FakeQuantLinear(nn.Module):
+    """Replacement linear used for the re-forwards (module_utils.py:679-771): keeps the fp32
+    compensated weight and the buf_* buffers, computes the fake-quantised weight once."""
+
+    def __init__(self, module, w_qdq):
+        super().__init__()
+        self.register_buffer('weight', module.weight.data)
+        self.bias = None if getattr(module, 'bias', None) is None else module.bias.data
+        for name, buf in module.named_buffers():
+            if name.startswith('buf_'):
+                self.register_buffer(name, buf.data)
+        self.w_qdq = w_qdq
+        self.in_features, self.out_features = module.in_features, module.out_features
+
+    def forward(self, x):
+        if not hasattr(self, 'tmp_weight'):
+            self.register_buffer('tmp_weight', self.w_qdq(self), persistent=False)
+        return F.linear(x, self.tmp_weight, self.bias)
+
+
+def llama_subsets(block):
+    """The four GPTQ subsets of a Llama decoder block (llmc/models/llama.py:52-91), as
+    (parent module, attribute name) pairs so that modules can be swapped."""
+    a, m = block.self_attn, block.mlp
+    return [
+        OrderedDict([('self_attn.q_proj', (a, 'q_proj')), ('self_attn.k_proj', (a, 'k_proj')),
+                     ('self_attn.v_proj', (a, 'v_proj'))]),
+        OrderedDict([('self_attn.o_proj', (a, 'o_proj'))]),
+        OrderedDict([('mlp.gate_proj', (m, 'gate_proj')), ('mlp.up_proj', (m, 'up_proj'))]),
+        OrderedDict([('mlp.down_proj', (m, 'down_proj'))]),
+    ]
+
+
+class _StopForward(Exception):
+    """Raised by a Hessian hook once the tensor it needs has been seen (see early_exit)."""
+
+
+class GPTQBlockwise:
+    def __init__(self, wquantizer, special=None, model_dtype=torch.bfloat16, quant_out=True):
+        special = dict(special or {})
+        self.solver = GPTQ(wquantizer, special, model_dtype)
+        self.wquantizer = wquantizer
+        self.quant_out = quant_out
+        self.true_sequential = self.solver.true_sequential
+        # A re-forward whose only purpose is to feed the hooks of one subset stops as soon as that
+        # subset's input has been seen: the rest of the block computes values nobody reads.
+        self.early_exit = special.get('early_exit', True)
+        self.forward_passes = 0
+
+    # ---- forwards ----------------------------------------------------------------------------
+    @torch.no_grad()
+    def block_forward(self, block, inputs, kwargs, need_output=True):
+        self.forward_passes += 1
+        outs = []
+        for i, x in enumerate(inputs):
+            try:
+                out = block(x, **(kwargs[i] if isinstance(kwargs, (list, tuple)) else kwargs))
+            except _StopForward:
+                continue
+            if need_output:
+                outs.append(out[0] if isinstance(out, tuple) else out)
+        return outs
+
+    def _hook_subset(self, subset, stop=False):
+        """One Hessian per subset: hook the linear of the subset that the block calls first, alias
+        the state for the others.  With stop=True the forward of each sequence ends there."""
+        names = list(subset)
+        first = names[0]
+        parent, attr = subset[first]
+        layer = getattr(parent, attr)
+        self.solver.layer_init(layer, first)
+        for n in names[1:]:
+            self.solver.layers_cache[n] = self.solver.layers_cache[first]
+
+        if stop:
+            # pre-hook: the layer itself (and everything after it) is skipped for this sequence
+            def pre_hook(mod, args):
+                self.solver.add_batch(mod, first, args[0].data, None)
+                raise _StopForward()
+            return layer.register_forward_pre_hook(pre_hook)
+
+        def hook(mod, inp, out):
+            self.solver.add_batch(mod, first, inp[0].data, None)
+        return layer.register_forward_hook(hook)
+
+    # ---- one subset --------------------------------------------------------------------------
+    @torch.no_grad()
+    def subset_transform(self, subset):
+        rank, world = parallel.world()
+        names = list(subset)
+        layers = [getattr(*subset[n]) for n in names]
+        H, hscale = self.solver._finish_hessian(names[0])
+        if world == 1:
+            for n, layer in zip(names, layers):
+                self.solver._install(layer, self.solver.solve(layer.weight.data, H, hscale))
+        else:
+            self._sharded_solve(names, layers, H, hscale, rank, world)
+        for n in names:
+            self.solver.layers_cache.pop(n, None)
+
+    def _sharded_solve(self, names, layers, H, hscale, rank, world):
+        # units = (linear, row range); a linear is cut in max(1, world // n_linears) row chunks
+        chunks = max(1, world // len(layers))
+        units = []
+        for li, layer in enumerate(layers):
+            R = layer.weight.shape[0]
+            for c in range(chunks):
+                r0, r1 = parallel.row_shard(R, c, chunks)
+                if r1 > r0:
+                    units.append((li, r0, r1))
+        mine = {}
+        for u, (li, r0, r1) in enumerate(units):
+            if u % world == rank:
+                mine[u] = self.solver.solve(layers[li].weight.data, H, hscale, rows=(r0, r1))
+        # every rank computes the same permutation from the same (reduced) Hessian
+        perm, invperm = self.solver.act_order(H)
+        dev = H.device
+        n_groups = (H.shape[0] + 127) // 128
+        full = []
+        for layer in layers:
+            R, C = layer.weight.shape
+            full.append({'weight': torch.empty((R, C), dtype=torch.float32, device=dev),
+                         'buf_scales': torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
+                         'buf_zeros': None if self.wquantizer.sym else
+                         torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
+                         'buf_perm': perm, 'buf_invperm': invperm})
+        for u, (li, r0, r1) in enumerate(units):
+            owner = u % world
+            for key in ('weight', 'buf_scales', 'buf_zeros'):
+                dst = full[li][key]
+                if dst is None:
+                    continue
+                view = dst[r0:r1] if key == 'weight' else dst[r0 * n_groups:r1 * n_groups]
+                if owner == rank:
+                    view.copy_(mine[u][key])
+                dist.broadcast(view, src=owner)
+        for layer, res in zip(layers, full):
+            self.solver._install(layer, res)
+
+    # ---- the block -----------------------------------------------------------------------------
+    @torch.no_grad()
+    def block_opt(self, block, inputs, kwargs, subsets=None):
+        """inputs: list of (b, T, C) tensors on the block's device (this rank's share);
+        kwargs: dict or list of dicts of extra forward arguments.  Returns the inputs of the next
+        block (outputs of the quantised block when quant_out, of the original block otherwise)."""
+        subsets = subsets or llama_subsets(block)
+        outs = None
+        if self.true_sequential:
+            stop_first = self.early_exit and self.quant_out      # the fp output is only needed without quant_out
+            handle = self._hook_subset(subsets[0], stop=stop_first)
+            first_out = self.block_forward(block, inputs, kwargs, need_output=not self.quant_out)
+            handle.remove()
+            if not self.quant_out:
+                outs = first_out
+            del first_out
+            for i, subset in enumerate(subsets):
+                self.subset_transform(subset)
+                self._replace(subset)
+                if i + 1 < len(subsets):
+                    handle = self._hook_subset(subsets[i + 1], stop=self.early_exit)
+                    self.block_forward(block, inputs, kwargs, need_output=False)
+                    handle.remove()
+        else:
+            handles = [self._hook_subset(s) for s in subsets]
+            first_out = self.block_forward(block, inputs, kwargs)
+            for h in handles:
+                h.remove()
+            if not self.quant_out:
+                outs = first_out
+            for subset in subsets:
+                self.subset_transform(subset)
+                self._replace(subset)
+        if self.quant_out:
+            outs = self.block_forward(block, inputs, kwargs)
+        return outs
+
+    def _replace(self, subset):
+        for n, (parent, attr) in subset.items():
+            mod = getattr(parent, attr)
+            if not isinstance(mod, FakeQuantLinear):
+                setattr(parent, attr, FakeQuantLinear(mod, lambda m: self.solver.w_qdq(m, self.wquantizer)))

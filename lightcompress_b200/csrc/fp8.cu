@@ -27,11 +27,25 @@ __device__ __forceinline__ float fp8_scale(float absmax) {
   return (s == 0.f) ? 1.f : s;
 }
 
+// rnd_T(w / s).  For bf16 the reciprocal-based quotient rounds to the same bf16 value as the IEEE
+// one (see div_rint<__nv_bfloat16>); the other types keep the IEEE division.
+template <typename T>
+__device__ __forceinline__ float fp8_div(float w, float s, float r, bool exact) {
+  return Elem<T>::rnd(__fdiv_rn(w, s));
+}
+template <>
+__device__ __forceinline__ float fp8_div<__nv_bfloat16>(float w, float s, float r, bool exact) {
+  if (exact) return Elem<__nv_bfloat16>::rnd(ieee_div(w, s));
+  const float q0 = __fmul_rn(w, r);
+  const float q1 = __fmaf_rn(__fmaf_rn(-q0, s, w), r, q0);
+  return Elem<__nv_bfloat16>::rnd(q1);
+}
+
 // u = w / s + 0 in T, q = e4m3(u) as fp32, fake = T(q * s)
 template <typename T>
-__device__ __forceinline__ void fp8_one(float w, float s, float& fake, uint8_t& code) {
+__device__ __forceinline__ void fp8_one(float w, float s, float r, bool exact, float& fake, uint8_t& code) {
   using E = Elem<T>;
-  float u = E::rnd(__fdiv_rn(w, s));
+  float u = fp8_div<T>(w, s, r, exact);
   u = E::rnd(__fadd_rn(u, 0.f));
   const __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3);
   code = (uint8_t)c;
@@ -79,6 +93,8 @@ __global__ void __launch_bounds__(256) fp8_row_vec_kernel(Fp8Args a) {
     }
     am = block_absmax(am, smem);
     const float s = fp8_scale<T>(am);
+    const float rs = __frcp_rn(s);
+    const bool exact = !(s > 1e-30f && s < 1e30f) || !(__fmul_rn(am, rs) < 1e37f);
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;
@@ -90,7 +106,7 @@ __global__ void __launch_bounds__(256) fp8_row_vec_kernel(Fp8Args a) {
 #pragma unroll
         for (int e = 0; e < N; ++e) {
           float fake;
-          fp8_one<T>(E::to_f(p[e]), s, fake, codes[e]);
+          fp8_one<T>(E::to_f(p[e]), s, rs, exact, fake, codes[e]);
           o[e] = E::from_f(fake);
         }
         const int64_t vidx = r * nvec + i;
@@ -121,10 +137,12 @@ __global__ void __launch_bounds__(256) fp8_generic_kernel(Fp8Args a) {
     for (int64_t i = threadIdx.x; i < a.cols; i += 256) am = nan_max(am, fabsf(E::to_f(in[i])));
     am = block_absmax(am, smem);
     const float s = fp8_scale<T>(am);
+    const float rs = __frcp_rn(s);
+    const bool exact = !(s > 1e-30f && s < 1e30f) || !(__fmul_rn(am, rs) < 1e37f);
     for (int64_t i = threadIdx.x; i < a.cols; i += 256) {
       float fake;
       uint8_t code;
-      fp8_one<T>(E::to_f(in[i]), s, fake, code);
+      fp8_one<T>(E::to_f(in[i]), s, rs, exact, fake, code);
       if (a.fake_out) reinterpret_cast<T*>(a.fake_out)[r * a.cols + i] = E::from_f(fake);
       if (a.codes_out) reinterpret_cast<uint8_t*>(a.codes_out)[r * a.cols + i] = code;
     }

@@ -28,7 +28,8 @@ struct BlockArgs {
 };
 
 __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
-  extern __shared__ float u1[];  // [128][128], zero outside count x count
+  extern __shared__ float u1[];  // [128][128], zero outside count x count; then 128 reciprocals of its diagonal
+  float* dinv = u1 + kBlk * kBlk;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
   for (int idx = threadIdx.x; idx < kBlk * kBlk; idx += kThreads) {
@@ -36,6 +37,7 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
     float v = 0.f;
     if (i < a.count && j < a.count && j >= i) v = a.U[(a.col0 + i) * a.cols + a.col0 + j];
     u1[idx] = v;
+    if (i == j) dinv[i] = __frcp_rn(v);
   }
   __syncthreads();
 
@@ -71,6 +73,8 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
   }
   float s, z;
   int_qparams<float>(mn, mx, a.qr, a.sym, s, z);
+  // error feedback can move a weight a little outside the block's initial range: leave headroom
+  const QuantCtx qc = make_quant_ctx(s, z, 16.f * nan_max(fabsf(mx), fabsf(mn)));
 
   float loss = 0.f;
 #pragma unroll
@@ -79,11 +83,14 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
     for (int il = 0; il < lim; ++il) {
       const int i = 32 * c + il;
       const float wi = __shfl_sync(0xffffffffu, w[c], il);
-      const float d = u1[i * kBlk + i];
-      const float q = int_quant<float>(wi, s, z, a.qr);
-      const float dq = int_dequant<float>(q, s, z);
+      const float d = u1[i * kBlk + i], rd = dinv[i];
+      const float q = int_quant_fast<float>(wi, qc, a.qr);   // the same code the IEEE division gives
+      const float dq = int_dequant_fast<float>(q, qc);
       const float diff = __fsub_rn(wi, dq);
-      const float err = __fdiv_rn(diff, d);
+      // (w - q) / d through the precomputed reciprocal and one residual correction: within an ulp
+      // of the IEEE quotient (the value only feeds the error propagation)
+      const float e0 = __fmul_rn(diff, rd);
+      const float err = __fmaf_rn(__fmaf_rn(-e0, d, diff), rd, e0);
       loss = fmaf(0.5f * err, err, loss);
       if (lane == il) {
         er[c] = err;
@@ -123,7 +130,7 @@ int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int6
                       uint8_t* codes, float* loss_rows, cudaStream_t st) {
   // per-device attribute; setting it on every call keeps multi-device processes correct
   if (cudaFuncSetAttribute(gptq_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kBlk * kBlk * (int)sizeof(float)) != cudaSuccess)
+                           (kBlk * kBlk + kBlk) * (int)sizeof(float)) != cudaSuccess)
     return LC_ERR_CUDA;
   BlockArgs a;
   a.W = W;
@@ -141,7 +148,7 @@ int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int6
   a.sym = sym ? 1 : 0;
   a.qr = int_qrange(bits, a.sym);
   const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
-  gptq_block_kernel<<<grid, kThreads, kBlk * kBlk * sizeof(float), st>>>(a);
+  gptq_block_kernel<<<grid, kThreads, (kBlk * kBlk + kBlk) * sizeof(float), st>>>(a);
   LC_LAUNCH_CHECK();
   return LC_OK;
 }

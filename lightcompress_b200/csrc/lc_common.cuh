@@ -54,13 +54,19 @@ template <> struct Elem<__half> {
   __device__ __forceinline__ static float rnd(float v) { return __half2float(__float2half_rn(v)); }
 };
 
-// max / min that propagate NaN like torch.amax / torch.amin
-__device__ __forceinline__ float nan_max(float a, float b) { return (a > b || a != a) ? a : b; }
-__device__ __forceinline__ float nan_min(float a, float b) { return (a < b || a != a) ? a : b; }
-// torch.clamp(x, lo, hi) = min(max(x, lo), hi) with NaN passed through
-__device__ __forceinline__ float clampf(float x, float lo, float hi) {
-  return (x != x) ? x : fminf(fmaxf(x, lo), hi);
+// max / min that propagate NaN like torch.amax / torch.amin (one FMNMX.NAN each)
+__device__ __forceinline__ float nan_max(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
 }
+__device__ __forceinline__ float nan_min(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+// torch.clamp(x, lo, hi) = min(max(x, lo), hi) with NaN passed through
+__device__ __forceinline__ float clampf(float x, float lo, float hi) { return nan_min(nan_max(x, lo), hi); }
 
 // ---- integer quantisation parameters (IntegerQuantizer.get_qparams) ---------------------------
 struct QRange {
@@ -113,6 +119,84 @@ template <typename T>
 __device__ __forceinline__ float int_dequant(float q, float s, float z) {
   using E = Elem<T>;
   return E::rnd(__fmul_rn(E::rnd(__fsub_rn(q, z)), s));
+}
+
+// ---- fast exact quantisation ---------------------------------------------------------------------
+// The element-wise cost of the fused kernels is dominated by the IEEE division w / s.  The scale is
+// shared by a whole group, so its reciprocal is computed once (QuantCtx) and each element uses
+//   q0 = w * r;  e = fma(-q0, s, w);  q1 = fma(e, r, q0)
+// which is within one ulp of RN(w / s) and almost always equal to it.  The result only feeds a
+// rounding (to T, then to an integer), so it can differ from the exact path only when q1 sits
+// within an ulp of a rounding boundary; those elements (and non-finite ones) take the IEEE
+// division.  Codes and dequantised values therefore stay bit-identical to the reference's.
+struct QuantCtx {
+  float s, z, r;   // scale, zero point, 1/s
+  bool exact;      // use the IEEE division for every element of the group
+};
+
+// absmax: largest |w| the context will be used on (NaN / inf allowed: they select the exact path)
+__device__ __forceinline__ QuantCtx make_quant_ctx(float s, float z, float absmax) {
+  QuantCtx c;
+  c.s = s;
+  c.z = z;
+  c.r = __frcp_rn(s);
+  // Keep the IEEE division when the reciprocal would lose accuracy (tiny / huge / non-finite
+  // scale) or when w * r could overflow or is not finite; every comparison is false for NaN.
+  c.exact = !(s > 1e-30f && s < 1e30f) || !(__fmul_rn(absmax, c.r) < 1e37f);
+  return c;
+}
+
+// IEEE division kept out of line: the rare slow path must be a real branch, not a predicated
+// copy of the whole division sequence in every element's instruction stream.
+static __device__ __noinline__ float ieee_div(float a, float b) { return __fdiv_rn(a, b); }
+
+// rint(rnd_T(w / s)) -- exactly what torch.round(w / s) gives on a tensor of dtype T.
+// In the saturated region (|result| > 1024) the integer may be off by one; it is clamped anyway.
+template <typename T>
+__device__ __forceinline__ float div_rint(float w, const QuantCtx& c);
+
+template <>
+__device__ __forceinline__ float div_rint<float>(float w, const QuantCtx& c) {
+  if (c.exact) return rintf(ieee_div(w, c.s));
+  const float q0 = __fmul_rn(w, c.r);
+  const float e = __fmaf_rn(-q0, c.s, w);
+  const float q1 = __fmaf_rn(e, c.r, q0);
+  float k = rintf(q1);
+  // within 1e-4 of a half-integer (more than an ulp for |q1| <= 1024), or NaN / inf
+  if (!(fabsf(fabsf(__fsub_rn(q1, k)) - 0.5f) >= 1e-4f)) k = rintf(ieee_div(w, c.s));
+  return k;
+}
+
+template <>
+__device__ __forceinline__ float div_rint<__nv_bfloat16>(float w, const QuantCtx& c) {
+  if (c.exact) return rintf(Elem<__nv_bfloat16>::rnd(ieee_div(w, c.s)));
+  // w and s are bf16 values (8-bit significands a, b).  The quotient a/b is either exactly a
+  // bf16 rounding midpoint (9 significant bits) or at least 1/(512*255) ~ 7.7e-6 away from every
+  // midpoint in relative terms -- 64 fp32 ulps.  q1 is within one ulp of RN(w/s) and equals the
+  // quotient whenever that is representable, so rounding q1 to bf16 gives the reference's value
+  // with no boundary check.
+  const float q0 = __fmul_rn(w, c.r);
+  const float e = __fmaf_rn(-q0, c.s, w);
+  const float q1 = __fmaf_rn(e, c.r, q0);
+  return rintf(Elem<__nv_bfloat16>::rnd(q1));
+}
+
+template <>
+__device__ __forceinline__ float div_rint<__half>(float w, const QuantCtx& c) {
+  return rintf(Elem<__half>::rnd(__fdiv_rn(w, c.s)));   // fp16 keeps the inline IEEE division
+}
+
+// clamp(round(w / s) + z, qmin, qmax) through the fast division.  For codes of at most 8 bits the
+// sum of two integers needs no rounding to T: it is exact up to 256 and saturates beyond.
+template <typename T>
+__device__ __forceinline__ float int_quant_fast(float w, const QuantCtx& c, QRange qr) {
+  return clampf(__fadd_rn(div_rint<T>(w, c), c.z), qr.qmin, qr.qmax);
+}
+
+// (q - z) * s rounded to T; q - z is an integer of magnitude <= 255, exact in every T.
+template <typename T>
+__device__ __forceinline__ float int_dequant_fast(float q, const QuantCtx& c) {
+  return __fmul_rn(__fsub_rn(q, c.z), c.s);   // the caller's conversion to T is the rounding
 }
 
 __device__ __forceinline__ int code_to_int(float q) { return (q != q) ? 0 : __float2int_rn(q); }

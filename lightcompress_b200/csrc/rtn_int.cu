@@ -3,7 +3,7 @@
 // and every requested output is written once.
 //
 // Three kernels:
-//   group_vec_kernel  group fits in <= 32 lanes x 16 bytes: a sub-warp of L lanes owns a group,
+//   group_vec_kernel  group of up to 2 KB: a sub-warp of L lanes owns a group, V vectors per lane,
 //                     min/max by xor-shuffles, all lanes derive (scale, zero) redundantly.
 //   row_vec_kernel    long rows (per_channel / per_token, or groups > 512 bytes): one CTA per
 //                     row segment, the segment stays in registers between reduce and quantise.
@@ -80,14 +80,18 @@ __device__ __forceinline__ void store_codes(const QuantArgs& a, int64_t e0, cons
   }
 }
 
-// ---- kernel A: L lanes per group, U groups in flight per thread --------------------------------
-template <typename T, int L, int U>
+// ---- kernel A: L lanes per group, V 16-byte vectors per lane -------------------------------------
+// Lane j of a group reads vectors j, j+L, j+2L, ... so that every load instruction of a warp
+// covers whole 128-byte lines; the V loads of a thread are independent and issued back to back.
+template <typename T, int L, int V>
 __global__ void __launch_bounds__(256) group_vec_kernel(QuantArgs a) {
   using E = Elem<T>;
   constexpr int N = E::kPerVec;
+  constexpr int GV = L * V;  // vectors per group
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
-  const int sub = threadIdx.x % L;  // lane inside the group
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % L;  // lane inside the group
   const int64_t groups_per_sweep = nthreads / L;
   const uint4* in = reinterpret_cast<const uint4*>(a.in);
   const T* s_in = reinterpret_cast<const T*>(a.scales_in);
@@ -95,58 +99,60 @@ __global__ void __launch_bounds__(256) group_vec_kernel(QuantArgs a) {
   const bool is_static = a.scales_in != nullptr;
 
   // The loop bound is warp-uniform (first group of the warp) because every lane must reach the
-  // full-mask shuffles below; lanes whose own group is past the end are masked by ok[u].
-  const int64_t lane_group = (threadIdx.x & 31) / L;
-  for (int64_t gw = (tid - (threadIdx.x & 31)) / L; gw < a.n_groups_total; gw += groups_per_sweep * U) {
-    const int64_t g0 = gw + lane_group;
-    uint4 v[U];
-    bool ok[U];
+  // full-mask shuffles below; lanes whose own group is past the end are masked by `ok`.
+  for (int64_t gw = (tid - lane) / L; gw < a.n_groups_total; gw += groups_per_sweep) {
+    const int64_t g = gw + lane / L;
+    const bool ok = g < a.n_groups_total;
+    float f[V][N];
+    float mx = -INFINITY, mn = INFINITY;
+    if (ok) {
+      uint4 v[V];
+      const uint4* src = in + g * GV + sub;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t g = g0 + (int64_t)u * groups_per_sweep;
-      ok[u] = g < a.n_groups_total;
-      if (ok[u]) v[u] = __ldcs(in + g * L + sub);
-    }
+      for (int k = 0; k < V; ++k) v[k] = __ldcs(src + L * k);
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t g = g0 + (int64_t)u * groups_per_sweep;
-      // inactive sub-warps still take part in the shuffles of their (fully inactive) group
-      float f[N];
-      float s, z;
-      if (ok[u]) unpack<T, N>(v[u], f);
-      if (!is_static) {
-        float mx = ok[u] ? f[0] : 0.f, mn = mx;
-        if (ok[u]) {
+      for (int k = 0; k < V; ++k) {
+        unpack<T, N>(v[k], f[k]);
 #pragma unroll
-          for (int i = 1; i < N; ++i) {
-            mx = nan_max(mx, f[i]);
-            mn = nan_min(mn, f[i]);
-          }
+        for (int i = 0; i < N; ++i) {
+          mx = nan_max(mx, f[k][i]);
+          mn = nan_min(mn, f[k][i]);
         }
-#pragma unroll
-        for (int o = L / 2; o > 0; o >>= 1) {
-          mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-          mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-        }
-        int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
-      } else if (ok[u]) {
-        s = E::to_f(s_in[g]);
-        z = (a.sym || z_in == nullptr) ? 0.f : E::to_f(z_in[g]);
       }
-      if (!ok[u]) continue;
+    }
+    QuantCtx c;
+    if (!is_static) {
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) {
+        mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      }
+      float s, z;
+      int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
+      c = make_quant_ctx(s, z, nan_max(fabsf(mx), fabsf(mn)));
+    } else if (ok) {
+      const float s = E::to_f(s_in[g]);
+      const float z = (a.sym || z_in == nullptr) ? 0.f : E::to_f(z_in[g]);
+      // this thread's own elements decide whether its fast path is safe
+      c = make_quant_ctx(s, z, nan_max(fabsf(mx), fabsf(mn)));
+    }
+    if (!ok) continue;
+    const int64_t vbase = g * GV + sub;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
       float q[N], d[N];
 #pragma unroll
       for (int i = 0; i < N; ++i) {
-        q[i] = int_quant<T>(f[i], s, z, a.qr);
-        d[i] = int_dequant<T>(q[i], s, z);
+        q[i] = int_quant_fast<T>(f[k][i], c, a.qr);
+        d[i] = int_dequant_fast<T>(q[i], c);
       }
-      const int64_t vidx = g * L + sub;
+      const int64_t vidx = vbase + L * k;
       if (a.fake_out) __stcs(reinterpret_cast<uint4*>(a.fake_out) + vidx, pack<T, N>(d));
       if (a.codes_out) store_codes<N>(a, vidx * N, q);
-      if (sub == 0) {
-        if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(s);
-        if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(z);
-      }
+    }
+    if (sub == 0) {
+      if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(c.s);
+      if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(c.z);
     }
   }
 }
@@ -172,9 +178,9 @@ __global__ void __launch_bounds__(256) row_vec_kernel(QuantArgs a) {
       if (i < nvec) v[k] = __ldcs(in + i);
     }
     float s, z;
+    float mx_all = 0.f, mn_all = 0.f;
     if (!is_static) {
       float mx = -INFINITY, mn = INFINITY;
-      bool any = false;
 #pragma unroll
       for (int k = 0; k < V; ++k) {
         const int64_t i = threadIdx.x + (int64_t)k * 256;
@@ -186,10 +192,8 @@ __global__ void __launch_bounds__(256) row_vec_kernel(QuantArgs a) {
             mx = nan_max(mx, f[e]);
             mn = nan_min(mn, f[e]);
           }
-          any = true;
         }
       }
-      (void)any;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -209,10 +213,14 @@ __global__ void __launch_bounds__(256) row_vec_kernel(QuantArgs a) {
       }
       __syncthreads();
       int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
+      mx_all = mx;
+      mn_all = mn;
     } else {
       s = E::to_f(s_in[g]);
       z = (a.sym || z_in == nullptr) ? 0.f : E::to_f(z_in[g]);
     }
+    // static mode has no min/max: keep the exact division there
+    const QuantCtx c = make_quant_ctx(s, z, is_static ? INFINITY : nan_max(fabsf(mx_all), fabsf(mn_all)));
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;
@@ -221,8 +229,8 @@ __global__ void __launch_bounds__(256) row_vec_kernel(QuantArgs a) {
         unpack<T, N>(v[k], f);
 #pragma unroll
         for (int e = 0; e < N; ++e) {
-          q[e] = int_quant<T>(f[e], s, z, a.qr);
-          d[e] = int_dequant<T>(q[e], s, z);
+          q[e] = int_quant_fast<T>(f[e], c, a.qr);
+          d[e] = int_dequant_fast<T>(q[e], c);
         }
         const int64_t vidx = g * nvec + i;
         if (a.fake_out) __stcs(reinterpret_cast<uint4*>(a.fake_out) + vidx, pack<T, N>(d));
@@ -306,15 +314,14 @@ __global__ void __launch_bounds__(256) generic_kernel(QuantArgs a) {
   }
 }
 
-template <typename T, int L>
+template <typename T, int L, int V>
 void launch_group_vec(const QuantArgs& a, cudaStream_t st) {
-  constexpr int U = 4;
-  const int64_t threads_needed = (a.n_groups_total * L + U - 1) / U;
+  const int64_t threads_needed = a.n_groups_total * L;
   int64_t blocks = (threads_needed + 255) / 256;
-  const int64_t cap = (int64_t)kNumSMsB200 * 8 * 4;  // a few waves of 8 resident CTAs per SM
+  const int64_t cap = (int64_t)kNumSMsB200 * 4 * 8;  // a few waves of resident CTAs per SM
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  group_vec_kernel<T, L, U><<<(unsigned)blocks, 256, 0, st>>>(a);
+  group_vec_kernel<T, L, V><<<(unsigned)blocks, 256, 0, st>>>(a);
 }
 
 template <typename T>
@@ -323,24 +330,26 @@ int dispatch(const QuantArgs& a, cudaStream_t st) {
   const bool ptr_ok = aligned16(a.in) && (!a.fake_out || aligned16(a.fake_out)) &&
                       (!a.codes_out || aligned16(a.codes_out));
   const bool vec_ok = ptr_ok && (a.group % N == 0);
-  const int64_t lanes = a.group / N;
-  if (vec_ok && lanes <= 32 && (lanes & (lanes - 1)) == 0) {
-    switch ((int)lanes) {
-      case 32: launch_group_vec<T, 32>(a, st); break;
-      case 16: launch_group_vec<T, 16>(a, st); break;
-      case 8: launch_group_vec<T, 8>(a, st); break;
-      case 4: launch_group_vec<T, 4>(a, st); break;
-      case 2: launch_group_vec<T, 2>(a, st); break;
-      default: launch_group_vec<T, 1>(a, st); break;
+  const int64_t nvec = a.group / N;  // 16-byte vectors per group
+  if (vec_ok && nvec <= 128 && (nvec & (nvec - 1)) == 0) {
+    switch ((int)nvec) {
+      case 128: launch_group_vec<T, 32, 4>(a, st); break;
+      case 64: launch_group_vec<T, 16, 4>(a, st); break;
+      case 32: launch_group_vec<T, 8, 4>(a, st); break;
+      case 16: launch_group_vec<T, 4, 4>(a, st); break;
+      case 8: launch_group_vec<T, 2, 4>(a, st); break;
+      case 4: launch_group_vec<T, 1, 4>(a, st); break;
+      case 2: launch_group_vec<T, 2, 1>(a, st); break;
+      default: launch_group_vec<T, 1, 1>(a, st); break;
     }
-  } else if (vec_ok && lanes <= 256 * 16) {
+  } else if (vec_ok && nvec <= 256 * 16) {
     int64_t blocks = a.n_groups_total;
     const int64_t cap = (int64_t)kNumSMsB200 * 8 * 8;
     if (blocks > cap) blocks = cap;
-    if (lanes <= 256) row_vec_kernel<T, 1><<<(unsigned)blocks, 256, 0, st>>>(a);
-    else if (lanes <= 512) row_vec_kernel<T, 2><<<(unsigned)blocks, 256, 0, st>>>(a);
-    else if (lanes <= 1024) row_vec_kernel<T, 4><<<(unsigned)blocks, 256, 0, st>>>(a);
-    else if (lanes <= 2048) row_vec_kernel<T, 8><<<(unsigned)blocks, 256, 0, st>>>(a);
+    if (nvec <= 256) row_vec_kernel<T, 1><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else if (nvec <= 512) row_vec_kernel<T, 2><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else if (nvec <= 1024) row_vec_kernel<T, 4><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else if (nvec <= 2048) row_vec_kernel<T, 8><<<(unsigned)blocks, 256, 0, st>>>(a);
     else row_vec_kernel<T, 16><<<(unsigned)blocks, 256, 0, st>>>(a);
   } else {
     int64_t blocks = a.n_groups_total;

@@ -130,13 +130,7 @@ class GPTQ:
         dev = W.device
         stream = L.stream_of(W)
         n_groups = (C + 127) // 128
-        if self.actorder:
-            diag = torch.empty(C, dtype=torch.float32, device=dev)
-            L.call('lc_gptq_diag', L.ptr(H), C, L.ptr(diag), stream)
-            perm = torch.argsort(diag, descending=True)
-            invperm = torch.argsort(perm)
-        else:
-            perm = invperm = None
+        perm, invperm = self.act_order(H)
         Wp = torch.empty((R, C), dtype=torch.float32, device=dev)
         Hp = torch.empty((C, C), dtype=torch.float32, device=dev)
         scratch = torch.empty(4, dtype=torch.float32, device=dev)
@@ -156,6 +150,16 @@ class GPTQ:
         L.call('lc_gptq_unpermute', L.ptr(Wp), L.ptr(perm), R, C, L.ptr(out), L.LC_F32, stream)
         return {'weight': out, 'buf_scales': scales, 'buf_zeros': None if wq.sym else zeros,
                 'buf_perm': perm, 'buf_invperm': invperm, 'codes_perm': codes, 'loss_rows': loss_rows}
+
+    def act_order(self, H):
+        """perm = argsort(diag(H), descending) and its inverse (gptq.py:58-64, :158), or (None, None)."""
+        if not self.actorder:
+            return None, None
+        C = H.shape[0]
+        diag = torch.empty(C, dtype=torch.float32, device=H.device)
+        L.call('lc_gptq_diag', L.ptr(H), C, L.ptr(diag), L.stream_of(H))
+        perm = torch.argsort(diag, descending=True)
+        return perm, torch.argsort(perm)
 
     @staticmethod
     def inverse_cholesky_upper(Hp):

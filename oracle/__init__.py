@@ -16,4 +16,4 @@ the un-vendored third-party `qtorch.quant.float_quantize` (no pinned version):
 for that single call parity is UNPINNED; it is restated as round-to-nearest-even
 onto the float8_e4m3fn grid.
 """
-from . import quant_ref, gptq_ref  # noqa: F401
+from . import quant_ref, gptq_ref, gptq_block_ref  # noqa: F401

@@ -11,9 +11,9 @@ import torch
 from . import quant_ref as Q
 
 
-def hessian_init(columns):
+def hessian_init(columns, device='cpu'):
     """layer_init (gptq.py:298-308)."""
-    return {'H': torch.zeros(columns, columns), 'nsamples': 0}
+    return {'H': torch.zeros(columns, columns, device=device), 'nsamples': 0}
 
 
 def add_batch(state, inp):
@@ -35,7 +35,7 @@ def prepare(W, H, percdamp=0.01, actorder=True):
     W = W.clone().float()
     H = H.clone()
     C = W.shape[1]
-    perm = torch.argsort(torch.diag(H), descending=True) if actorder else torch.arange(C)
+    perm = torch.argsort(torch.diag(H), descending=True) if actorder else torch.arange(C, device=H.device)
     dead = torch.diag(H) == 0
     H[dead, dead] = 1
     W[:, dead] = 0
@@ -43,7 +43,7 @@ def prepare(W, H, percdamp=0.01, actorder=True):
     H = H[perm][:, perm]
     invperm = torch.argsort(perm)
     damp = percdamp * torch.mean(torch.diag(H))
-    idx = torch.arange(C)
+    idx = torch.arange(C, device=H.device)
     H[idx, idx] += damp
     L = torch.linalg.cholesky(H)
     Hinv = torch.cholesky_inverse(L)

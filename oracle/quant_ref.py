@@ -37,6 +37,7 @@ def group_view(t, granularity, group_size=None):
 def int_qparams(g, bit, sym):
     """min/max -> (scales, zeros, qmax, qmin); quant.py:134-145 and :544-558."""
     qmin, qmax = int_range(bit, sym)
+    qmin, qmax = qmin.to(g.device), qmax.to(g.device)      # quant.py:546-547
     mx = g.amax(dim=-1, keepdim=True)
     mn = g.amin(dim=-1, keepdim=True)
     if sym:
@@ -49,7 +50,7 @@ def int_qparams(g, bit, sym):
 
 def int_quant(g, s, z, qmax, qmin):
     """quant.py:698-700 (round_zp=True, torch.round = half to even)."""
-    return torch.clamp(torch.round(g / s) + z, qmin, qmax)
+    return torch.clamp(torch.round(g / s) + z, qmin.to(g.device), qmax.to(g.device))
 
 
 def int_dequant(q, s, z):

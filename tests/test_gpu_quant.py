@@ -78,6 +78,49 @@ def test_rtn_matches_oracle(dtype, shape, gran, gs):
                 _same(s3, s, 'scales(all)')
 
 
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_rtn_rounding_boundaries_are_exact(dtype):
+    """Elements placed within a few ulps of every rounding boundary of w / s (half-integers, and
+    for bf16 the bf16 rounding midpoints): the reciprocal-based division must agree with the IEEE
+    division of the reference on each of them."""
+    from lightcompress_b200 import IntegerQuantizer
+    g = torch.Generator().manual_seed(1234)
+    rows = 4096
+    s0 = (torch.rand(rows, 1, generator=g) * 0.05 + 1e-3)
+    k = torch.randint(0, 15, (rows, 128), generator=g).float()
+    w = (k + 0.5) * s0
+    # walk a few ulps around each boundary
+    steps = torch.randint(-3, 4, (rows, 128), generator=g, dtype=torch.int32)
+    wi = w.view(torch.int32) + steps
+    w = wi.view(torch.float32).clone()
+    w[:, 0] = 0.0
+    w[:, 1] = 15.0 * s0[:, 0]          # pins min = 0, max = 15 s0 so that the scale is ~s0
+    w = w.to(dtype)
+    if dtype == torch.bfloat16:
+        # also sit on bf16 midpoints of the quotient: w = s * (m + half-ulp), a few fp32 ulps around
+        s_b = w[:, 1:2].float() / 15
+        m = torch.randint(64, 128, (rows, 64), generator=g).float() / 8   # bf16-representable quotients
+        mid = (m + 1.0 / 32) * s_b                                          # half a bf16 ulp above (ulp = 1/16)
+        w[:, 64:] = mid.to(dtype)
+    for sym, bit in ((False, 4), (False, 8), (True, 4)):
+        qz = IntegerQuantizer(bit, sym, 'per_group', group_size=128)
+        q, sc, z = quant_ref.int_real_quant_dynamic(w, bit, sym, 'per_group', 128)
+        codes, s2, z2 = qz.real_quant_weight_dynamic(w.cuda())
+        _same(codes, q, 'codes')
+        _same(s2, sc, 'scales')
+        _same(qz.fake_quant_weight_dynamic(w.cuda()), quant_ref.int_fake_quant_dynamic(w, bit, sym, 'per_group', 128),
+              'fake')
+    # non-finite and huge inputs take the exact path
+    w2 = (torch.randn(64, 256, generator=g)).to(dtype)
+    w2[0, 3] = float('inf')
+    w2[1, 7] = float('nan')
+    w2[2, :128] = 3e37 if dtype == torch.float32 else 3e37
+    w2[3, :] = 0
+    qz = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    _same(qz.fake_quant_weight_dynamic(w2.cuda()), quant_ref.int_fake_quant_dynamic(w2, 4, False, 'per_group', 128),
+          'non-finite')
+
+
 def test_rtn_full_size_roundtrip_property():
     """Config-1 size: quantising the dequantised output again is a fixed point for the codes."""
     from lightcompress_b200 import IntegerQuantizer
