@@ -140,7 +140,9 @@ int lc_gptq_diag(const float* H, int64_t cols, float* diag_out, lc_stream_t stre
  *   reverse_h != 0: Hp is written with both index orders reversed, Hp[i][j] <- entry
  *           (cols-1-i, cols-1-j), which is the input of the single-factorisation route to the
  *           upper factor of the inverse (see lc_gptq_flip); Wp is not affected
- *   scratch: at least 1 float (receives damp) */
+ *   scratch: at least 1 float (receives damp)
+ * W/Wp may both be NULL (only the Hessian part runs: one factorisation serves every linear that
+ * shares the input) and Hp may be NULL (only the weight gather runs). */
 int lc_gptq_permute_damp(const void* W, int w_dtype, const float* H, const int64_t* perm,
                          int64_t rows, int64_t cols, float hscale, float percdamp, int reverse_h,
                          float* Wp, float* Hp, float* scratch, lc_stream_t stream);

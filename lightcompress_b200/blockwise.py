@@ -17,6 +17,12 @@ Two schedule differences that do not change any result:
   * with true_sequential the first pass only hooks the first subset: the Hessians of later subsets
     collected in that pass are re-zeroed by subset_init before use (gptq.py:311-315).
 
+For blocks with the Llama layout (pre-norm attention + gated MLP) the same schedule runs as a
+staged plan: the tensor each re-forward would recompute up to the next subset's input is kept from
+the previous stage (attention context, post-attention residual, MLP product), so the block's GEMMs
+and its attention are evaluated once instead of up to five times.  The modules and their order are
+those of the block's own forward, so every tensor is bit-identical to the re-forwarded one.
+
 Several ranks: each rank forwards its own sequences; every Hessian is all-reduced once; the
 (linear, row-range) solve units of a subset are dealt round-robin to the ranks and the results
 broadcast, so every rank continues with identical weights.
@@ -65,6 +71,14 @@ def llama_subsets(block):
     ]
 
 
+def is_llama_layout(block):
+    a, m = getattr(block, 'self_attn', None), getattr(block, 'mlp', None)
+    return (a is not None and m is not None and hasattr(block, 'input_layernorm')
+            and hasattr(block, 'post_attention_layernorm')
+            and all(hasattr(a, k) for k in ('q_proj', 'k_proj', 'v_proj', 'o_proj'))
+            and all(hasattr(m, k) for k in ('gate_proj', 'up_proj', 'down_proj', 'act_fn')))
+
+
 class _StopForward(Exception):
     """Raised by a Hessian hook once the tensor it needs has been seen (see early_exit)."""
 
@@ -79,6 +93,7 @@ class GPTQBlockwise:
         # A re-forward whose only purpose is to feed the hooks of one subset stops as soon as that
         # subset's input has been seen: the rest of the block computes values nobody reads.
         self.early_exit = special.get('early_exit', True)
+        self.stage_plan = special.get('stage_plan', True)
         self.forward_passes = 0
 
     # ---- forwards ----------------------------------------------------------------------------
@@ -94,6 +109,13 @@ class GPTQBlockwise:
             if need_output:
                 outs.append(out[0] if isinstance(out, tuple) else out)
         return outs
+
+    def _init_subset(self, subset):
+        names = list(subset)
+        self.solver.layer_init(getattr(*subset[names[0]]), names[0])
+        for n in names[1:]:
+            self.solver.layers_cache[n] = self.solver.layers_cache[names[0]]
+        return names[0], getattr(*subset[names[0]])
 
     def _hook_subset(self, subset, stop=False):
         """One Hessian per subset: hook the linear of the subset that the block calls first, alias
@@ -124,15 +146,17 @@ class GPTQBlockwise:
         names = list(subset)
         layers = [getattr(*subset[n]) for n in names]
         H, hscale = self.solver._finish_hessian(names[0])
+        fac = self.solver.factorize(H, hscale)       # shared by the linears of the subset
         if world == 1:
             for n, layer in zip(names, layers):
-                self.solver._install(layer, self.solver.solve(layer.weight.data, H, hscale))
+                self.solver._install(layer, self.solver.solve(layer.weight.data, H, hscale, factor=fac))
         else:
-            self._sharded_solve(names, layers, H, hscale, rank, world)
+            self._sharded_solve(names, layers, fac, rank, world)
         for n in names:
             self.solver.layers_cache.pop(n, None)
 
-    def _sharded_solve(self, names, layers, H, hscale, rank, world):
+    def _sharded_solve(self, names, layers, fac, rank, world):
+        H = fac['H']
         # units = (linear, row range); a linear is cut in max(1, world // n_linears) row chunks
         chunks = max(1, world // len(layers))
         units = []
@@ -145,9 +169,9 @@ class GPTQBlockwise:
         mine = {}
         for u, (li, r0, r1) in enumerate(units):
             if u % world == rank:
-                mine[u] = self.solver.solve(layers[li].weight.data, H, hscale, rows=(r0, r1))
+                mine[u] = self.solver.solve(layers[li].weight.data, H, rows=(r0, r1), factor=fac)
         # every rank computes the same permutation from the same (reduced) Hessian
-        perm, invperm = self.solver.act_order(H)
+        perm, invperm = fac['perm'], fac['invperm']
         dev = H.device
         n_groups = (H.shape[0] + 127) // 128
         full = []
@@ -177,6 +201,9 @@ class GPTQBlockwise:
         """inputs: list of (b, T, C) tensors on the block's device (this rank's share);
         kwargs: dict or list of dicts of extra forward arguments.  Returns the inputs of the next
         block (outputs of the quantised block when quant_out, of the original block otherwise)."""
+        if (subsets is None and self.stage_plan and self.true_sequential and self.quant_out
+                and is_llama_layout(block)):
+            return self._block_opt_llama_staged(block, inputs, kwargs)
         subsets = subsets or llama_subsets(block)
         outs = None
         if self.true_sequential:
@@ -206,6 +233,68 @@ class GPTQBlockwise:
                 self._replace(subset)
         if self.quant_out:
             outs = self.block_forward(block, inputs, kwargs)
+        return outs
+
+    @torch.no_grad()
+    def _block_opt_llama_staged(self, block, inputs, kwargs):
+        """true_sequential + quant_out on a Llama-layout block, one evaluation of every module:
+        norm -> [H qkv, solve] -> attention (quantised q,k,v) -> [H o, solve] -> o_proj + residual
+        -> norm -> [H gate/up, solve] -> act(gate) * up -> [H down, solve] -> down_proj + residual."""
+        a, m = block.self_attn, block.mlp
+        subsets = llama_subsets(block)
+        kw = (lambda i: kwargs[i]) if isinstance(kwargs, (list, tuple)) else (lambda i: kwargs)
+        n = len(inputs)
+        self.forward_passes += 1
+
+        name, layer = self._init_subset(subsets[0])
+        for x in inputs:
+            self.solver.add_batch(layer, name, block.input_layernorm(x), None)
+        self.subset_transform(subsets[0])
+        self._replace(subsets[0])
+
+        name, layer = self._init_subset(subsets[1])
+        seen = {}
+
+        def grab(mod, args):
+            seen['x'] = args[0]
+            raise _StopForward()
+        handle = a.o_proj.register_forward_pre_hook(grab)
+        ctx = []
+        for i, x in enumerate(inputs):
+            try:
+                a(hidden_states=block.input_layernorm(x), **kw(i))
+            except _StopForward:
+                pass
+            ctx.append(seen.pop('x'))
+            self.solver.add_batch(layer, name, ctx[-1], None)
+        handle.remove()
+        self.subset_transform(subsets[1])
+        self._replace(subsets[1])
+
+        name, layer = self._init_subset(subsets[2])
+        resid = []
+        for i, x in enumerate(inputs):
+            h = x + a.o_proj(ctx[i])
+            ctx[i] = None
+            resid.append(h)
+            self.solver.add_batch(layer, name, block.post_attention_layernorm(h), None)
+        self.subset_transform(subsets[2])
+        self._replace(subsets[2])
+
+        name, layer = self._init_subset(subsets[3])
+        prod = []
+        for i in range(n):
+            y = block.post_attention_layernorm(resid[i])
+            prod.append(m.act_fn(m.gate_proj(y)) * m.up_proj(y))
+            self.solver.add_batch(layer, name, prod[-1], None)
+        self.subset_transform(subsets[3])
+        self._replace(subsets[3])
+
+        outs = []
+        for i in range(n):
+            outs.append(resid[i] + m.down_proj(prod[i]))
+            prod[i] = None
+            resid[i] = None
         return outs
 
     def _replace(self, subset):

@@ -102,14 +102,18 @@ extern "C" LC_API int lc_gptq_permute_damp(const void* W, int w_dtype, const flo
                                     int64_t cols, float hscale, float percdamp, int reverse_h, float* Wp,
                                     float* Hp, float* scratch, lc_stream_t stream) {
   using namespace lc;
-  if (!W || !H || !Wp || !Hp || !scratch || rows <= 0 || cols <= 0) return LC_ERR_ARG;
+  if (!H || cols <= 0 || (W != nullptr) != (Wp != nullptr) || (Hp && !scratch) || (!W && !Hp)) return LC_ERR_ARG;
+  if (W && rows <= 0) return LC_ERR_ARG;
   if (w_dtype != LC_F32 && w_dtype != LC_BF16 && w_dtype != LC_F16) return LC_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  damp_kernel<<<1, 1024, 0, st>>>(H, cols, hscale, percdamp, scratch);
-  LC_LAUNCH_CHECK();
-  dim3 gh((unsigned)((cols + 255) / 256), (unsigned)cols);
-  permute_h_kernel<<<gh, 256, 0, st>>>(H, perm, cols, hscale, scratch, Hp, reverse_h);
-  LC_LAUNCH_CHECK();
+  if (Hp) {
+    damp_kernel<<<1, 1024, 0, st>>>(H, cols, hscale, percdamp, scratch);
+    LC_LAUNCH_CHECK();
+    dim3 gh((unsigned)((cols + 255) / 256), (unsigned)cols);
+    permute_h_kernel<<<gh, 256, 0, st>>>(H, perm, cols, hscale, scratch, Hp, reverse_h);
+    LC_LAUNCH_CHECK();
+  }
+  if (!W) return LC_OK;
   dim3 gw((unsigned)((cols + 255) / 256), (unsigned)(rows < 1024 ? rows : 1024));
   switch (w_dtype) {
     case LC_F32: permute_w_kernel<float><<<gw, 256, 0, st>>>((const float*)W, H, perm, rows, cols, Wp); break;

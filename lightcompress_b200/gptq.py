@@ -39,6 +39,9 @@ class GPTQ:
         # forward hooks deliver one sequence per call; up to `hessian_batch` of them (<= 8) are
         # held by reference and accumulated in one launch, so H is updated once per batch
         self.hessian_batch = max(1, min(8, int(special.get('hessian_batch', 8))))
+        # token split of the Hessian kernel: 0 = chosen per launch (may combine partial sums with
+        # atomics in varying order when the matrix is small), 1 = one work item per tile (deterministic)
+        self.hessian_ksplit = int(special.get('hessian_ksplit', 0))
         self.model_dtype = model_dtype
         self.layers_cache = {}
         self._check_config()
@@ -90,7 +93,7 @@ class GPTQ:
         n = len(xs)
         ptrs = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
         toks = (ctypes.c_int64 * n)(*[x.shape[0] for x in xs])
-        L.call('lc_hessian_accum_multi', ptrs, toks, n, xs[0].shape[1], L.ptr(st['H']), 1.0, 1.0, 0,
+        L.call('lc_hessian_accum_multi', ptrs, toks, n, xs[0].shape[1], L.ptr(st['H']), 1.0, 1.0, self.hessian_ksplit,
                L.ptr(st['status']), L.stream_of(xs[0]))
         st['pending'] = []
 
@@ -120,8 +123,26 @@ class GPTQ:
         return res
 
     @torch.no_grad()
-    def solve(self, W, H, hscale=1.0, rows=None):
+    def factorize(self, H, hscale=1.0):
+        """Everything of process_hessian_and_weights (gptq.py:128-176) that depends on H only:
+        act-order permutation, dampening, and U with U^T U = (permuted, damped H)^-1.  Linears that
+        read the same input (q/k/v, gate/up) share one result."""
+        L.require_cuda(H)
+        C = H.shape[0]
+        perm, invperm = self.act_order(H)
+        Hp = torch.empty((C, C), dtype=torch.float32, device=H.device)
+        scratch = torch.empty(4, dtype=torch.float32, device=H.device)
+        direct = self.factorization == 'direct'
+        L.call('lc_gptq_permute_damp', None, L.LC_F32, L.ptr(H), L.ptr(perm), 0, C, float(hscale),
+               float(self.percdamp), int(direct), None, L.ptr(Hp), L.ptr(scratch), L.stream_of(H))
+        U = self.inverse_cholesky_upper_reversed(Hp) if direct else self.inverse_cholesky_upper(Hp)
+        return {'H': H, 'perm': perm, 'invperm': invperm, 'U': U}
+
+    @torch.no_grad()
+    def solve(self, W, H, hscale=1.0, rows=None, factor=None):
         wq = self.wquantizer
+        fac = factor or self.factorize(H, hscale)
+        H, perm, invperm, U = fac['H'], fac['perm'], fac['invperm'], fac['U']
         L.require_cuda(W, H)
         W = W if W.is_contiguous() else W.contiguous()
         if rows is not None:
@@ -130,15 +151,9 @@ class GPTQ:
         dev = W.device
         stream = L.stream_of(W)
         n_groups = (C + 127) // 128
-        perm, invperm = self.act_order(H)
         Wp = torch.empty((R, C), dtype=torch.float32, device=dev)
-        Hp = torch.empty((C, C), dtype=torch.float32, device=dev)
-        scratch = torch.empty(4, dtype=torch.float32, device=dev)
-        direct = self.factorization == 'direct'
-        L.call('lc_gptq_permute_damp', L.ptr(W), L.lc_dtype(W), L.ptr(H), L.ptr(perm), R, C, float(hscale),
-               float(self.percdamp), int(direct), L.ptr(Wp), L.ptr(Hp), L.ptr(scratch), stream)
-        U = self.inverse_cholesky_upper_reversed(Hp) if direct else self.inverse_cholesky_upper(Hp)
-        del Hp
+        L.call('lc_gptq_permute_damp', L.ptr(W), L.lc_dtype(W), L.ptr(H), L.ptr(perm), R, C, 1.0, 0.0, 0,
+               L.ptr(Wp), None, None, stream)
         err = torch.empty((128, R), dtype=torch.float32, device=dev)
         scales = torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev)
         zeros = torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev)
@@ -178,13 +193,30 @@ class GPTQ:
         U = J M^-1 J (one cuBLAS triangular solve against the identity and a flip)."""
         C = Hr.shape[0]
         M = torch.linalg.cholesky(Hr)
-        eye = torch.eye(C, dtype=Hr.dtype, device=Hr.device)
-        Minv = torch.linalg.solve_triangular(M, eye, upper=False)
-        del M, eye
-        Minv = Minv if Minv.is_contiguous() else Minv.contiguous()   # the kernels read row-major memory
+        # explicitly row-major: zeros_like would inherit the column-major strides cuSOLVER results carry
+        Minv = torch.zeros(M.shape, dtype=M.dtype, device=M.device)
+        GPTQ._lower_inverse(M, Minv)
+        del M
         U = torch.empty_like(Minv)
         L.call('lc_gptq_flip', L.ptr(Minv), C, L.ptr(U), L.stream_of(Minv))
         return U
+
+    @staticmethod
+    def _lower_inverse(M, out, leaf=1024):
+        """out <- M^-1 for lower-triangular M, written into the (pre-zeroed) row-major `out`:
+        inv([[A, 0], [B, D]]) = [[A^-1, 0], [-D^-1 B A^-1, D^-1]], recursively; leaves by a cuBLAS
+        triangular solve against the identity.  One third of the FLOPs of a full-size solve against
+        the identity, almost all of them in large fp32 GEMMs."""
+        n = M.shape[0]
+        if n <= leaf:
+            eye = torch.eye(n, dtype=M.dtype, device=M.device)
+            out.copy_(torch.linalg.solve_triangular(M, eye, upper=False))
+            return
+        h = (n // 2 + 127) // 128 * 128
+        GPTQ._lower_inverse(M[:h, :h], out[:h, :h], leaf)
+        GPTQ._lower_inverse(M[h:, h:], out[h:, h:], leaf)
+        torch.matmul(out[h:, h:], torch.matmul(M[h:, :h], out[:h, :h]), out=out[h:, :h])
+        out[h:, :h].neg_()
 
     def _install(self, layer, res):
         layer.weight.data = res['weight'].reshape(layer.weight.shape)

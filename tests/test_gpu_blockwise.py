@@ -69,7 +69,7 @@ def test_block_schedule_matches_oracle(true_sequential, oracle_device):
     gblock = copy.deepcopy(block).cuda()
     wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
     runner = GPTQBlockwise(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128,
-                                'true_sequential': true_sequential, 'hessian_batch': 4})
+                                'true_sequential': true_sequential, 'hessian_batch': 4, 'stage_plan': False})
     outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
     torch.cuda.synchronize()
     assert runner.forward_passes == (5 if true_sequential else 2)
@@ -102,3 +102,34 @@ def test_block_schedule_matches_oracle(true_sequential, oracle_device):
     rel = float((o_gpu - o_ref).norm() / o_ref.norm())
     print(f'block output rel diff {rel:.4e}')
     assert rel < 0.05
+
+
+def test_staged_plan_is_bit_identical_to_reforwarding():
+    """The Llama stage plan (every module evaluated once) against the generic re-forwarding
+    schedule, with and without early exit: same weights, parameters, permutation and outputs,
+    bit for bit."""
+    from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer, llama_subsets
+    block, xs, kwargs = _make_block(seed=3)
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    results = []
+    for special in ({'stage_plan': True}, {'stage_plan': False, 'early_exit': True},
+                    {'stage_plan': False, 'early_exit': False}):
+        gblock = copy.deepcopy(block).cuda()
+        # hessian_ksplit=1: a deterministic Hessian (no atomically combined token splits), so that
+        # the three runs can be compared bit for bit
+        runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'hessian_batch': 8,
+                                         'hessian_ksplit': 1}, **special))
+        outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
+        torch.cuda.synchronize()
+        state = {}
+        for subset in llama_subsets(gblock):
+            for name, (parent, attr) in subset.items():
+                mod = getattr(parent, attr)
+                state[name] = (mod.weight.clone(), mod.buf_scales.clone(), mod.buf_zeros.clone(), mod.buf_perm.clone())
+        results.append((state, torch.cat(outs), runner.forward_passes))
+    assert [r[2] for r in results] == [1, 5, 5]
+    for state, out, _ in results[1:]:
+        assert torch.equal(out, results[0][1])
+        for name in state:
+            for a, b in zip(state[name], results[0][0][name]):
+                assert torch.equal(a, b), name
