@@ -167,6 +167,114 @@ def make_gptq(rq, rg, out_dir):
     print('gptq_layer.pt', len(cases), 'cases')
 
 
+class _TorchProxy:
+    """Stands in for the `torch` name inside the reference's awq module: drops device='cuda'."""
+
+    def __getattr__(self, name):
+        return getattr(torch, name)
+
+    @staticmethod
+    def tensor(*a, device=None, **k):
+        return torch.tensor(*a, **k)
+
+    @staticmethod
+    def zeros_like(*a, device=None, **k):
+        return torch.zeros_like(*a, **k)
+
+
+def tiny_llama_block(hidden=256, inter=512, heads=4, T=64, seed=0):
+    from transformers import LlamaConfig
+    from transformers.models.llama.modeling_llama import LlamaDecoderLayer, LlamaRotaryEmbedding
+    cfg = LlamaConfig(hidden_size=hidden, intermediate_size=inter, num_attention_heads=heads,
+                      num_key_value_heads=heads, num_hidden_layers=1, vocab_size=128, max_position_embeddings=4 * T)
+    cfg._attn_implementation = 'sdpa'
+    block = LlamaDecoderLayer(cfg, 0).to(torch.bfloat16)
+    g = torch.Generator().manual_seed(seed)
+    for p in block.parameters():
+        p.data = ((torch.randn(p.shape, generator=g) * 0.02) if p.dim() == 2
+                  else (1 + 0.1 * torch.randn(p.shape, generator=g))).to(torch.bfloat16)
+    rot = LlamaRotaryEmbedding(cfg)
+    pos = torch.arange(T)[None]
+    cos, sin = rot(torch.zeros(1, T, hidden, dtype=torch.bfloat16), pos)
+    return block, {'position_embeddings': (cos, sin), 'attention_mask': None, 'position_ids': pos}
+
+
+def make_awq(rq, out_dir):
+    """Drives the reference Awq class (search_scale_subset / apply_scale / AutoClipper) on one tiny
+    Llama block, bypassing its model plumbing."""
+    import llmc.compression.quantization.awq as rawq
+    import llmc.compression.quantization.auto_clip as rclip
+    rawq.torch = _TorchProxy()
+    torch.nn.Module.cuda = lambda self, *a, **k: self
+    # The reference recognises norm layers through transformers' ALL_LAYERNORM_LAYERS
+    # (module_utils.py:9, :1180).  The transformers releases it is written for (>= 4.45,
+    # requirements/runtime.txt) register LlamaRMSNorm there; the 5.x release installed here no
+    # longer does, which would make the reference skip the two norm-fed subsets.  Restore the entry.
+    from transformers.models.llama.modeling_llama import LlamaRMSNorm
+    from transformers.pytorch_utils import ALL_LAYERNORM_LAYERS
+    if LlamaRMSNorm not in ALL_LAYERNORM_LAYERS:
+        ALL_LAYERNORM_LAYERS.append(LlamaRMSNorm)
+    cases = {}
+    for name, sym, clip_sym in (('asym', False, False), ('sym_clipsym', True, True)):
+        block, kwargs = tiny_llama_block(seed=11)
+        g = torch.Generator().manual_seed(3001)
+        x = torch.randn(4, 64, 256, generator=g)
+        x[:, :, torch.randperm(256, generator=g)[:3]] *= 20
+        x = x.to(torch.bfloat16)
+        state0 = {k: v.clone() for k, v in block.state_dict().items()}
+
+        a = object.__new__(rawq.Awq)
+        a.wquantizer = rq.IntegerQuantizer(4, sym, 'per_group', group_size=128)
+        a.aquantizer, a.w_only, a.padding_mask = None, True, None
+        a.trans, a.trans_version, a.save_scale, a.awq_bs, a.save_mem = True, 'v2', False, None, True
+        a.weight_clip, a.clip_version, a.act_static, a.true_sequential = True, 'v1', False, False
+        a.has_gqa, a.do_gqa_trans, a.block_idx, a.n_samples = False, False, 0, 4
+
+        class Cfg(dict):
+            __getattr__ = dict.__getitem__
+        a.config = Cfg(model=Cfg(type='Llama'), calib=Cfg(seq_len=64))
+
+        class Model:
+            # llmc/models/__init__.py imports every adapter (and packages that are not installed),
+            # so the four Llama subsets (llmc/models/llama.py:52-91) are written out here
+            block_name_prefix = 'model.layers'
+
+            @staticmethod
+            def get_subsets_in_block(b):
+                sa, mlp = b.self_attn, b.mlp
+                return [
+                    {'layers': {'self_attn.q_proj': sa.q_proj, 'self_attn.k_proj': sa.k_proj,
+                                'self_attn.v_proj': sa.v_proj},
+                     'prev_op': [b.input_layernorm], 'input': ['self_attn.q_proj'], 'inspect': sa, 'has_kwargs': True},
+                    {'layers': {'self_attn.o_proj': sa.o_proj}, 'prev_op': [sa.v_proj],
+                     'input': ['self_attn.o_proj'], 'inspect': sa.o_proj, 'has_kwargs': False},
+                    {'layers': {'mlp.gate_proj': mlp.gate_proj, 'mlp.up_proj': mlp.up_proj},
+                     'prev_op': [b.post_attention_layernorm], 'input': ['mlp.gate_proj'], 'inspect': mlp,
+                     'has_kwargs': False, 'is_mlp': True},
+                    {'layers': {'mlp.down_proj': mlp.down_proj}, 'prev_op': [mlp.up_proj],
+                     'input': ['mlp.down_proj'], 'inspect': mlp.down_proj, 'has_kwargs': False, 'is_mlp': True},
+                ]
+        a.model = Model()
+        a.auto_clipper = rclip.AutoClipper(w_only=True, wquantizer=a.wquantizer, aquantizer=None, clip_version='v1',
+                                           clip_sym=clip_sym, save_clip=False, padding_mask=None)
+        # cache the linears' inputs the way BlockwiseOpt.cache_input_hook does
+        feats, hooks = {}, []
+        for n, m in block.named_modules():
+            if isinstance(m, torch.nn.Linear):
+                def hook(mod, inp, out, n=n):
+                    feats.setdefault(n, []).append(inp[0].data.clone())
+                hooks.append(m.register_forward_hook(hook))
+        with torch.no_grad():
+            block(x, **kwargs)
+        for h in hooks:
+            h.remove()
+        a.block_transform(block, feats, [dict(kwargs, past_key_values=None, use_cache=False)])
+        cases[name] = dict(x=x, sym=sym, clip_sym=clip_sym, state0=state0,
+                           state1={k: v.clone() for k, v in block.state_dict().items()})
+    torch.save(cases, os.path.join(out_dir, 'awq_block.pt'))
+    print('awq_block.pt', len(cases), 'cases')
+
+
 if __name__ == '__main__':
     ref_root = sys.argv[1]
     out_dir = os.path.dirname(os.path.abspath(__file__))
@@ -175,3 +283,4 @@ if __name__ == '__main__':
     make_rtn(rq, out_dir)
     make_gptq(rq, rg, out_dir)
     make_fp8(rq, out_dir)
+    make_awq(rq, out_dir)

@@ -60,3 +60,31 @@ def test_group_not_divisible_raises():
     import pytest
     with pytest.raises(ValueError):
         quant_ref.int_fake_quant_dynamic(torch.zeros(2, 200), 4, False, 'per_group', 128)
+
+
+def _tiny_block(state, hidden=256, inter=512, heads=4, T=64):
+    from transformers import LlamaConfig
+    from transformers.models.llama.modeling_llama import LlamaDecoderLayer, LlamaRotaryEmbedding
+    cfg = LlamaConfig(hidden_size=hidden, intermediate_size=inter, num_attention_heads=heads,
+                      num_key_value_heads=heads, num_hidden_layers=1, vocab_size=128, max_position_embeddings=4 * T)
+    cfg._attn_implementation = 'sdpa'
+    block = LlamaDecoderLayer(cfg, 0).to(torch.bfloat16)
+    block.load_state_dict(state)
+    rot = LlamaRotaryEmbedding(cfg)
+    pos = torch.arange(T)[None]
+    cos, sin = rot(torch.zeros(1, T, hidden, dtype=torch.bfloat16), pos)
+    return block, {'position_embeddings': (cos, sin), 'attention_mask': None, 'position_ids': pos}
+
+
+def test_awq_oracle_matches_reference_block(golden):
+    """The reference's own Awq.block_transform (scale search, scale application, clip search and
+    clamp) on a tiny Llama block: the oracle must leave bit-identical weights and norms."""
+    from oracle import awq_ref
+    torch.set_num_threads(1)
+    for key, c in golden('awq_block.pt').items():
+        block, kwargs = _tiny_block(c['state0'])
+        awq_ref.awq_block(block, c['x'], kwargs, bit=4, sym=c['sym'], clip_sym=c['clip_sym'], n_sample_token=64)
+        got = block.state_dict()
+        for k, v in c['state1'].items():
+            assert torch.equal(got[k], v), (key, k, int((got[k] != v).sum()))
+        assert any(not torch.equal(c['state0'][k], c['state1'][k]) for k in c['state1'])
