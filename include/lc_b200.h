@@ -208,6 +208,44 @@ int lc_gptq_weight_transform_noalloc(float* W, const float* U, int64_t rows, int
 int lc_gptq_unpermute(const float* Wp, const int64_t* perm, int64_t rows, int64_t cols,
                       void* out, int out_dtype, lc_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Family 4: AWQ scale + clip search.
+ * ------------------------------------------------------------------------------------------ */
+
+/* out[c] = mean over tokens of |x[t][c]| in `dtype` (fp32 accumulation, one rounding):
+ * Awq.get_act_scale (llmc/compression/quantization/awq.py:74-76).
+ * scratch: at least min(64, ceil(tokens/256)) * cols floats. */
+int lc_awq_act_mean(const void* x, int dtype, int64_t tokens, int64_t cols, void* out, float* scratch,
+                    int64_t scratch_floats, lc_stream_t stream);
+
+/* fake_out = quant_dequant(round_to_dtype(w * col_scale[col])), per group of `group` columns:
+ * Awq.scaling_weight + fake_quant_weight_dynamic (awq.py:40-46, :147-164) in one pass, without
+ * touching w.  col_scale: `cols` values in `dtype`.  Same arithmetic as lc_rtn_int_quant. */
+int lc_awq_scale_quant(const void* w, const void* col_scale, int dtype, int64_t rows, int64_t cols,
+                       int64_t group, int bits, int sym, void* fake_out, lc_stream_t stream);
+
+/* out[r][c] = x[r][c] / col_scale[c] rounded to `dtype`: scaling_input / update_input_feat
+ * (llmc/compression/quantization/base_blockwise_quantization.py:900-920).  out may alias x. */
+int lc_awq_div_cols(const void* x, const void* col_scale, int dtype, int64_t rows, int64_t cols, void* out,
+                    lc_stream_t stream);
+
+/* loss_out[0] = mean((a - b)^2), the subtraction rounded to `dtype`, squares and sum in fp32 or
+ * wider: Awq.calculate_loss (awq.py:134-136).  scratch: at least 592 doubles. */
+int lc_awq_loss(const void* a, const void* b, int dtype, int64_t n, float* loss_out, double* scratch,
+                int64_t scratch_doubles, lc_stream_t stream);
+
+/* AutoClipper.auto_clip_layer + apply_clip, clip_version v1
+ * (llmc/compression/quantization/auto_clip.py:84-191, :194-212), fused: for every (row, group)
+ * the grid of int(max_shrink * n_grid) shrink ratios 1 - i/n_grid is evaluated on the sampled
+ * tokens x[0::x_token_step] with the reference's rounding after every op, the best range is
+ * written to best_max / best_min ((rows, cols/group) in `dtype`) and, if W_out is not NULL, the
+ * clamped weights to W_out (may alias W).
+ *   W rows x cols, X x_tokens x cols, both `dtype` (bf16 or fp16); group must be 128; at most 512
+ *   sampled tokens. */
+int lc_awq_clip_search(const void* W, const void* X, int dtype, int64_t rows, int64_t cols, int64_t x_tokens,
+                       int64_t x_token_step, int64_t group, int bits, int sym, int clip_sym, int n_grid,
+                       double max_shrink, void* best_max, void* best_min, void* W_out, lc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,6 +7,7 @@ from . import _lib  # noqa: F401  (raises if the CUDA library is not built)
 from .quant import FloatQuantizer, IntegerQuantizer  # noqa: F401
 from .gptq import GPTQ  # noqa: F401
 from .rtn import RTN  # noqa: F401
+from .awq import Awq  # noqa: F401
 from .blockwise import GPTQBlockwise, FakeQuantLinear, llama_subsets  # noqa: F401
 
-__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'GPTQ', 'RTN', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets']
+__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'GPTQ', 'RTN', 'Awq', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets']

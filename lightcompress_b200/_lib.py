@@ -20,7 +20,7 @@ LC_CODES_NONE, LC_CODES_I32, LC_CODES_I8, LC_CODES_PACK4 = 0, 1, 2, 3
 
 _DTYPES = {torch.float32: LC_F32, torch.bfloat16: LC_BF16, torch.float16: LC_F16}
 
-_p, _i, _i64, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+_p, _i, _i64, _f, _d = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_double
 
 # name -> argtypes; every function returns int except the two noted below
 SIGNATURES = {
@@ -39,6 +39,11 @@ SIGNATURES = {
     'lc_gptq_weight_transform': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p],
     'lc_gptq_weight_transform_noalloc': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p],
     'lc_gptq_unpermute': [_p, _p, _i64, _i64, _p, _i, _p],
+    'lc_awq_act_mean': [_p, _i, _i64, _i64, _p, _p, _i64, _p],
+    'lc_awq_scale_quant': [_p, _p, _i, _i64, _i64, _i64, _i, _i, _p, _p],
+    'lc_awq_div_cols': [_p, _p, _i, _i64, _i64, _p, _p],
+    'lc_awq_loss': [_p, _p, _i, _i64, _p, _p, _i64, _p],
+    'lc_awq_clip_search': [_p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _d, _p, _p, _p, _p],
 }
 
 

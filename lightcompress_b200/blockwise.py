@@ -247,8 +247,10 @@ class GPTQBlockwise:
         self.forward_passes += 1
 
         name, layer = self._init_subset(subsets[0])
+        normed = []
         for x in inputs:
-            self.solver.add_batch(layer, name, block.input_layernorm(x), None)
+            normed.append(block.input_layernorm(x))
+            self.solver.add_batch(layer, name, normed[-1], None)
         self.subset_transform(subsets[0])
         self._replace(subsets[0])
 
@@ -260,11 +262,12 @@ class GPTQBlockwise:
             raise _StopForward()
         handle = a.o_proj.register_forward_pre_hook(grab)
         ctx = []
-        for i, x in enumerate(inputs):
+        for i in range(n):
             try:
-                a(hidden_states=block.input_layernorm(x), **kw(i))
+                a(hidden_states=normed[i], **kw(i))
             except _StopForward:
                 pass
+            normed[i] = None
             ctx.append(seen.pop('x'))
             self.solver.add_batch(layer, name, ctx[-1], None)
         handle.remove()
@@ -272,19 +275,21 @@ class GPTQBlockwise:
         self._replace(subsets[1])
 
         name, layer = self._init_subset(subsets[2])
-        resid = []
+        resid, normed = [], []
         for i, x in enumerate(inputs):
             h = x + a.o_proj(ctx[i])
             ctx[i] = None
             resid.append(h)
-            self.solver.add_batch(layer, name, block.post_attention_layernorm(h), None)
+            normed.append(block.post_attention_layernorm(h))
+            self.solver.add_batch(layer, name, normed[-1], None)
         self.subset_transform(subsets[2])
         self._replace(subsets[2])
 
         name, layer = self._init_subset(subsets[3])
         prod = []
         for i in range(n):
-            y = block.post_attention_layernorm(resid[i])
+            y = normed[i]
+            normed[i] = None
             prod.append(m.act_fn(m.gate_proj(y)) * m.up_proj(y))
             self.solver.add_batch(layer, name, prod[-1], None)
         self.subset_transform(subsets[3])

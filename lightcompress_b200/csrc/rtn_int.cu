@@ -31,6 +31,7 @@ __device__ __forceinline__ uint4 pack(const float (&f)[N]) {
 }
 
 struct QuantArgs {
+  const void* col_scale;  // optional per-column multiplier applied (and rounded to T) before everything else
   const void* in;
   const void* scales_in;
   const void* zeros_in;
@@ -93,6 +94,7 @@ __global__ void __launch_bounds__(256) group_vec_kernel(QuantArgs a) {
   const int lane = threadIdx.x & 31;
   const int sub = lane % L;  // lane inside the group
   const int64_t groups_per_sweep = nthreads / L;
+  const int64_t groups_per_row = a.cols / a.group;
   const uint4* in = reinterpret_cast<const uint4*>(a.in);
   const T* s_in = reinterpret_cast<const T*>(a.scales_in);
   const T* z_in = reinterpret_cast<const T*>(a.zeros_in);
@@ -110,6 +112,20 @@ __global__ void __launch_bounds__(256) group_vec_kernel(QuantArgs a) {
       const uint4* src = in + g * GV + sub;
 #pragma unroll
       for (int k = 0; k < V; ++k) v[k] = __ldcs(src + L * k);
+      if (a.col_scale) {
+        // w <- rnd_T(w * s[col]) (the in-place mul_ of AWQ's scaling_weight); groups tile the row
+        const int64_t vec_in_row = (g % groups_per_row) * GV + sub;
+        const uint4* sc = reinterpret_cast<const uint4*>(a.col_scale) + vec_in_row;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          float w[N], m[N];
+          unpack<T, N>(v[k], w);
+          unpack<T, N>(__ldg(sc + L * k), m);
+#pragma unroll
+          for (int i = 0; i < N; ++i) w[i] = E::rnd(__fmul_rn(w[i], m[i]));
+          v[k] = pack<T, N>(w);
+        }
+      }
 #pragma unroll
       for (int k = 0; k < V; ++k) {
         unpack<T, N>(v[k], f[k]);
@@ -331,6 +347,8 @@ int dispatch(const QuantArgs& a, cudaStream_t st) {
                       (!a.codes_out || aligned16(a.codes_out));
   const bool vec_ok = ptr_ok && (a.group % N == 0);
   const int64_t nvec = a.group / N;  // 16-byte vectors per group
+  if (a.col_scale && !(vec_ok && aligned16(a.col_scale) && nvec >= 1 && nvec <= 128 && (nvec & (nvec - 1)) == 0))
+    return LC_ERR_SHAPE;  // the column-scaled variant exists for vectorisable groups of up to 2 KB only
   if (vec_ok && nvec <= 128 && (nvec & (nvec - 1)) == 0) {
     switch ((int)nvec) {
       case 128: launch_group_vec<T, 32, 4>(a, st); break;
@@ -364,10 +382,9 @@ int dispatch(const QuantArgs& a, cudaStream_t st) {
 }  // namespace
 }  // namespace lc
 
-extern "C" LC_API int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t group,
-                                int bits, int sym, const void* scales_in, const void* zeros_in,
-                                void* fake_out, void* codes_out, int code_fmt, void* scales_out,
-                                void* zeros_out, lc_stream_t stream) {
+static int rtn_quant_impl(const void* in, const void* col_scale, int dtype, int64_t rows, int64_t cols, int64_t group,
+                          int bits, int sym, const void* scales_in, const void* zeros_in, void* fake_out,
+                          void* codes_out, int code_fmt, void* scales_out, void* zeros_out, lc_stream_t stream) {
   using namespace lc;
   if (rows < 0 || cols < 0 || group < 0) return LC_ERR_ARG;
   if (bits < 2 || bits > 8) return LC_ERR_ARG;
@@ -385,6 +402,7 @@ extern "C" LC_API int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, 
   if (scales_in == nullptr && zeros_in != nullptr) return LC_ERR_ARG;
 
   QuantArgs a;
+  a.col_scale = col_scale;
   a.in = in;
   a.scales_in = scales_in;
   a.zeros_in = zeros_in;
@@ -406,4 +424,19 @@ extern "C" LC_API int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, 
     case LC_BF16: return dispatch<__nv_bfloat16>(a, st);
     default: return dispatch<__half>(a, st);
   }
+}
+
+extern "C" LC_API int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t group, int bits,
+                                       int sym, const void* scales_in, const void* zeros_in, void* fake_out,
+                                       void* codes_out, int code_fmt, void* scales_out, void* zeros_out,
+                                       lc_stream_t stream) {
+  return rtn_quant_impl(in, nullptr, dtype, rows, cols, group, bits, sym, scales_in, zeros_in, fake_out, codes_out,
+                        code_fmt, scales_out, zeros_out, stream);
+}
+
+extern "C" LC_API int lc_awq_scale_quant(const void* w, const void* col_scale, int dtype, int64_t rows, int64_t cols,
+                                         int64_t group, int bits, int sym, void* fake_out, lc_stream_t stream) {
+  if (!col_scale || !fake_out) return LC_ERR_ARG;
+  return rtn_quant_impl(w, col_scale, dtype, rows, cols, group, bits, sym, nullptr, nullptr, fake_out, nullptr,
+                        LC_CODES_NONE, nullptr, nullptr, stream);
 }

@@ -1,0 +1,175 @@
+"""GPU parity of the AWQ kernels and of the block-level scale + clip search (through the C ABI)
+against the oracle and against the reference's own result on a small Llama block (tests/golden).
+
+Element-wise kernels (scaled fake quant, activation scaling) are bit-exact.  Reductions (mean |x|,
+the output error, the 128-term dot products of the clip search) accumulate in fp32 like torch but
+in a different order, so they can differ from torch in the last bit of a bf16 rounding; the tests
+state how often.  Bars for the block: the same scale grid point per subset, fewer than 0.1 % of the
+final int codes different from the reference's when each stage is fed the reference's inputs
+(teacher forcing), and a block-output error within 1 % of the reference's."""
+import pytest
+import torch
+
+from oracle import awq_ref, quant_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _wq(sym=False):
+    from lightcompress_b200 import IntegerQuantizer
+    return IntegerQuantizer(4, sym, 'per_group', group_size=128)
+
+
+def test_scale_quant_and_div_cols_are_bit_exact():
+    from lightcompress_b200 import Awq
+    g = torch.Generator().manual_seed(3100)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        w = (torch.randn(192, 512, generator=g) * 0.02).to(dtype)
+        s = (torch.rand(512, generator=g) * 3 + 0.05).to(dtype)
+        x = torch.randn(3, 70, 512, generator=g).to(dtype)
+        for sym in (False, True):
+            awq = Awq(_wq(sym))
+            got = awq.fake_quantize_weight(w.cuda(), s.cuda()).cpu()
+            assert torch.equal(got, awq_ref.fake_quant_scaled_weight(w, s, 4, sym, 128))
+        got = Awq(_wq()).scaling_input(x.cuda(), s.cuda()).cpu()
+        assert torch.equal(got, x / s.view(1, -1))
+
+
+def test_act_mean_and_loss():
+    from lightcompress_b200 import Awq
+    g = torch.Generator().manual_seed(3200)
+    awq = Awq(_wq())
+    x = torch.randn(16, 300, 1024, generator=g)
+    x[:, :, 5] *= 20
+    x = x.to(torch.bfloat16).cuda()
+    got = awq.get_act_scale(x)
+    ref = awq_ref.act_scale(x)                          # torch on the same GPU
+    exact = x.abs().float().view(-1, 1024).double().mean(0)
+    frac = float((got != ref).float().mean())
+    print(f'act_mean: {frac:.4%} of channels differ from torch in the last bf16 bit')
+    assert float(((got.double() - exact).abs() / exact).max()) < 2 ** -8     # within half a bf16 ulp of the exact mean
+    assert frac < 0.02
+    a = torch.randn(8, 128, 512, generator=g).to(torch.bfloat16).cuda()
+    b = (a.float() + 0.01 * torch.randn(8, 128, 512, generator=g).cuda()).to(torch.bfloat16)
+    slot = torch.zeros(1, device='cuda')
+    awq.calculate_loss(a, b, slot, torch.empty(1024, dtype=torch.float64, device='cuda'))
+    ref = (a - b).float().pow(2).mean().item()
+    assert abs(slot.item() - ref) <= 1e-5 * ref
+
+
+@pytest.mark.parametrize('sym,clip_sym', [(False, False), (True, True)])
+def test_clip_search_matches_oracle(sym, clip_sym):
+    from lightcompress_b200 import Awq
+    g = torch.Generator().manual_seed(3300)
+    R, C, T = 512, 512, 2048
+    w = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    x = torch.randn(4, T // 4, C, generator=g)
+    x[:, :, torch.randperm(C, generator=g)[:5]] *= 20
+    x = x.to(torch.bfloat16).cuda()
+    mx_ref, mn_ref = awq_ref.auto_clip_layer(w, x, 4, sym, 128, clip_sym, n_sample_token=512)   # torch on the GPU
+    ref_w = awq_ref.apply_clip(w, mn_ref, mx_ref, clip_sym)
+    awq = Awq(_wq(sym), {'clip_sym': clip_sym}, calib_seq_len=512)
+    w2 = w.clone()
+    mx, mn = awq.auto_clip_layer(w2, x)
+    diff = float(((mx != mx_ref) | (mn != mn_ref)).float().mean())
+    wdiff = float((w2 != ref_w).float().mean())
+    print(f'clip search sym={sym}: {diff:.3%} of (row, group) ranges differ, {wdiff:.4%} of clamped weights')
+    # fp32 summation order inside the 128-term dot products decides near-ties of a flat objective
+    assert diff < 0.05
+    # whatever range is chosen, it is one of the grid points and the weights are clamped to it
+    org_max = (w.abs() if clip_sym else w).reshape(R, -1, 128).amax(-1, keepdim=True)
+    cand = torch.cat([org_max * (1 - i / 20) for i in range(10)], dim=-1)      # bf16, like the reference
+    assert bool((mx == cand).any(-1).all())
+    assert torch.equal(w2, awq_ref.apply_clip(w, mn, mx, clip_sym))
+
+
+def _tiny_block(state, hidden=256, inter=512, heads=4, T=64):
+    from tests.test_oracle_golden import _tiny_block as tb
+    return tb(state, hidden, inter, heads, T)
+
+
+def _cuda_kwargs(kwargs):
+    return {k: (v.cuda() if torch.is_tensor(v) else tuple(t.cuda() for t in v) if isinstance(v, tuple) else v)
+            for k, v in kwargs.items()}
+
+
+def _codes(w, sym):
+    q, s, z = quant_ref.int_real_quant_dynamic(w.cpu(), 4, sym, 'per_group', 128)
+    return q
+
+
+def test_block_against_reference_golden(golden):
+    from lightcompress_b200 import Awq
+    for key, c in golden('awq_block.pt').items():
+        block, kwargs = _tiny_block(c['state0'])
+        block = block.cuda()
+        awq = Awq(_wq(c['sym']), {'clip_sym': c['clip_sym']}, calib_seq_len=64)
+        rep = awq.block_transform(block, c['x'].cuda(), _cuda_kwargs(kwargs))
+        torch.cuda.synchronize()
+        # the reference's chosen scales are visible in its norm weights: ln1 = ln0 / s
+        got = {k: v.cpu() for k, v in block.state_dict().items()}
+        for ln in ('input_layernorm.weight', 'post_attention_layernorm.weight'):
+            same = float((got[ln] == c['state1'][ln]).float().mean())
+            print(f'{key} {ln}: {same:.2%} identical to the reference')
+            assert same > 0.99, (key, ln)
+        tot = dif = 0
+        for name in ('self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj', 'self_attn.o_proj', 'mlp.gate_proj',
+                     'mlp.up_proj', 'mlp.down_proj'):
+            a, b = _codes(got[name + '.weight'], c['sym']), _codes(c['state1'][name + '.weight'], c['sym'])
+            d = float((a != b).float().mean())
+            tot += a.numel()
+            dif += int((a != b).sum())
+            print(f'{key} {name}: final int-code mismatch vs reference (CPU run) {d:.4%}')
+        print(f'{key}: overall code mismatch {dif / tot:.4%}')
+        # The reference fixture was produced on the CPU: its bf16 forwards round differently from the
+        # GPU's, which moves near-ties of the flat search objectives (on the same device the mismatch
+        # is zero, see the teacher-forced test).  The robust bar is the block-output error of the
+        # quantised block, within 1 % of the reference's.
+        errs = []
+        for state in (got, c['state1']):
+            qb, _ = _tiny_block(c['state0'])
+            sd = {k: (quant_ref.int_fake_quant_dynamic(v, 4, c['sym'], 'per_group', 128) if v.dim() == 2 else v)
+                  for k, v in state.items()}
+            qb.load_state_dict(sd)
+            fb, _ = _tiny_block(c['state0'])
+            with torch.no_grad():
+                o_q = qb.cuda()(c['x'].cuda(), **_cuda_kwargs(kwargs))
+                o_f = fb.cuda()(c['x'].cuda(), **_cuda_kwargs(kwargs))
+            o_q, o_f = (o[0] if isinstance(o, tuple) else o for o in (o_q, o_f))
+            errs.append(float((o_q.float() - o_f.float()).norm() / o_f.float().norm()))
+        print(f'{key}: block-output error ours {errs[0]:.5f} reference {errs[1]:.5f}')
+        assert abs(errs[0] - errs[1]) <= 0.01 * errs[1] + 1e-4
+
+
+def test_block_teacher_forced_against_oracle_on_gpu(golden):
+    """Every stage fed the oracle's own inputs (oracle = torch on the same GPU): scale grid point
+    per subset identical, clip decisions and final codes within the 0.1 % bar."""
+    import copy
+    from lightcompress_b200 import Awq
+    c = golden('awq_block.pt')['asym']
+    block, kwargs = _tiny_block(c['state0'])
+    kw = _cuda_kwargs(kwargs)
+    ref_block = copy.deepcopy(block).cuda()
+    x = c['x'].cuda()
+    ref = awq_ref.awq_block(ref_block, x, kw, bit=4, sym=False, clip_sym=False, n_sample_token=64)
+    gblock = copy.deepcopy(block).cuda()
+    awq = Awq(_wq(False), {'clip_sym': False}, calib_seq_len=64)
+    rep = awq.block_transform(gblock, x, kw)
+    torch.cuda.synchronize()
+    for k in ref['scales']:
+        n_ref = int(torch.tensor(ref['losses'][k]).argmin())
+        n_got = int(rep['losses'][k].argmin())
+        rel = float(((rep['losses'][k].cpu().double() - torch.tensor(ref['losses'][k]).double()).abs()
+                     / torch.tensor(ref['losses'][k]).double()).max())
+        print(f'subset {k}: grid point ref {n_ref} got {n_got}; losses agree to {rel:.2e}')
+        assert n_ref == n_got
+        assert rel < 1e-3
+    tot = dif = 0
+    for name, mod in gblock.named_modules():
+        if isinstance(mod, torch.nn.Linear):
+            a = _codes(mod.weight.data, False)
+            b = _codes(dict(ref_block.named_modules())[name].weight.data, False)
+            tot += a.numel()
+            dif += int((a != b).sum())
+    print(f'final int-code mismatch vs oracle on the same GPU: {dif / tot:.4%}')
+    assert dif / tot < 1e-3
