@@ -246,6 +246,19 @@ int lc_awq_clip_search(const void* W, const void* X, int dtype, int64_t rows, in
                        int64_t x_token_step, int64_t group, int bits, int sym, int clip_sym, int n_grid,
                        double max_shrink, void* best_max, void* best_min, void* W_out, lc_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Export layouts for 4-bit codes (what follows the hot path when a real-quant model is saved).
+ * ------------------------------------------------------------------------------------------ */
+
+/* AutoAWQ GEMM layout, the packing loops of AutoawqRealQuantLinear.gemm_pack
+ * (llmc/compression/quantization/module_utils.py:1130-1158): codes (rows = out_features x cols =
+ * in_features, one byte per code, 0..15) -> out (cols x rows/8) int32, word (k, c) holding output
+ * rows 8c + {0,2,4,6,1,3,5,7} of input column k in nibbles 0..7.  Zero points pack the same way
+ * (codes = zeros (out x n_groups) -> (n_groups x out/8)).  rows must be a multiple of 8.
+ * The compressed-tensors int4 layout of VllmRealQuantLinear.pack (module_utils.py:931-955) needs no
+ * routine of its own: it is LC_CODES_PACK4 from lc_rtn_int_quant (symmetric, stored as q + 8). */
+int lc_pack_int4_awq(const uint8_t* codes, int64_t rows, int64_t cols, int32_t* out, lc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

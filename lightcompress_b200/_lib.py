@@ -43,6 +43,7 @@ SIGNATURES = {
     'lc_awq_scale_quant': [_p, _p, _i, _i64, _i64, _i64, _i, _i, _p, _p],
     'lc_awq_div_cols': [_p, _p, _i, _i64, _i64, _p, _p],
     'lc_awq_loss': [_p, _p, _i, _i64, _p, _p, _i64, _p],
+    'lc_pack_int4_awq': [_p, _i64, _i64, _p, _p],
     'lc_awq_clip_search': [_p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _d, _p, _p, _p, _p],
 }
 

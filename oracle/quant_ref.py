@@ -133,3 +133,29 @@ def pack_int4_rows(codes_u8):
     module_utils.py:931-955, which packs 8 nibbles per int32 little-nibble first)."""
     c = codes_u8.to(torch.uint8)
     return (c[..., 0::2] | (c[..., 1::2] << 4)).contiguous()
+
+
+def pack_compressed_tensors(codes_signed, num_bits=4):
+    """VllmRealQuantLinear.pack (module_utils.py:931-955): (q + 2^(b-1)) packed 32/b per int32 along
+    the input dim, first element in the lowest bits."""
+    import numpy as np
+    offset = 2 ** num_bits // 2
+    w = (codes_signed + offset).to(torch.uint8).cpu().numpy().astype(np.uint32)
+    pf = 32 // num_bits
+    packed = np.zeros((w.shape[0], -(-w.shape[1] // pf)), dtype=np.uint32)
+    w = np.pad(w, [(0, 0), (0, packed.shape[1] * pf - w.shape[1])])
+    for i in range(pf):
+        packed |= w[:, i::pf] << (num_bits * i)
+    return torch.from_numpy(packed.view(np.int32))
+
+
+def pack_autoawq(int_t, bit=4):
+    """The packing loops of AutoawqRealQuantLinear.gemm_pack (module_utils.py:1130-1158):
+    int_t is (in, out) int32 (already transposed); returns (in, out/8) int32."""
+    order = [0, 2, 4, 6, 1, 3, 5, 7]
+    pack_num = 32 // bit
+    q = torch.zeros((int_t.shape[0], int_t.shape[1] // 32 * bit), dtype=torch.int32)
+    for col in range(int_t.shape[1] // pack_num):
+        for i in range(pack_num):
+            q[:, col] |= int_t[:, col * pack_num + order[i]] << (i * bit)
+    return q

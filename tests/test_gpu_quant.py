@@ -155,3 +155,22 @@ def test_fp8_matches_reference_golden_and_oracle(golden):
             codes, s2, _ = qw.real_quant_weight_dynamic(w.cuda())
             _same(codes.view(torch.uint8), q.view(torch.uint8), 'fp8 codes')
             _same(s2, s, 'fp8 scales')
+
+
+def test_export_packing_layouts():
+    """compressed-tensors int4 (LC_CODES_PACK4 viewed as int32) and the AutoAWQ GEMM layout against
+    restatements of the reference's packers."""
+    from lightcompress_b200 import IntegerQuantizer
+    from lightcompress_b200.export import pack_autoawq_gemm, pack_compressed_tensors_int4
+    g = torch.Generator().manual_seed(6001)
+    w = (torch.randn(256, 512, generator=g) * 0.02).to(torch.bfloat16)
+    qs = IntegerQuantizer(4, True, 'per_group', group_size=128)
+    packed, s = pack_compressed_tensors_int4(w.cuda(), qs)
+    q, s_ref, _ = quant_ref.int_real_quant_dynamic(w, 4, True, 'per_group', 128)
+    assert torch.equal(packed.cpu(), quant_ref.pack_compressed_tensors(q))
+    _same(s, s_ref, 'scales')
+    qa = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    codes, s2, z2 = qa.real_quant_weight_dynamic(w.cuda())
+    qweight, qzeros = pack_autoawq_gemm(codes.to(torch.uint8), z2.to(torch.uint8))
+    assert torch.equal(qweight.cpu(), quant_ref.pack_autoawq(codes.cpu().t().contiguous()))
+    assert torch.equal(qzeros.cpu(), quant_ref.pack_autoawq(z2.cpu().t().contiguous()))
