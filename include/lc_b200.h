@@ -124,6 +124,11 @@ int lc_hessian_accum_multi(const void* const* xs_host, const int64_t* tokens_hos
                            int64_t cols, float* H, float alpha, float beta, int ksplit,
                            int32_t* status, lc_stream_t stream);
 
+/* Exercises the bounded-wait path of the tensor-core kernels without touching them: a one-thread
+ * kernel waits (about a millisecond) on a barrier nothing arrives on and must write LC_ERR_TIMEOUT
+ * to *status and return normally.  (No counterpart in the reference.) */
+int lc_selftest_wait_expiry(int32_t* status, lc_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Family 3: GPTQ layer solver pieces.
  * ------------------------------------------------------------------------------------------ */
@@ -180,6 +185,30 @@ int lc_gptq_trailing_update(float* W, const float* err, const float* U, int64_t 
 int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t cols, int bits,
                              int sym, float* scratch_err, float* scales, float* zeros,
                              uint8_t* codes_u8, float* loss_rows, lc_stream_t stream);
+
+/* lo[i] = x[i] - tf32_truncate(x[i]) (the part of an fp32 value a kind::tf32 tensor-core operand
+ * drops).  Used once per factor U by the tensor-core variant below. */
+int lc_gptq_split_tf32(const float* x, int64_t n, float* lo, lc_stream_t stream);
+
+/* One per-panel trailing update on the tensor cores:
+ *     W[:, p2:] -= E^T * U[p1:p2, p2:]        (E stored k-major: (p2 - p1) x rows)
+ * with e_hi = E, e_lo = E - tf32_truncate(E), U_lo likewise (three-term tf32 split, fp32-level
+ * accuracy).  The building block of lc_gptq_weight_transform_tc; p2 - p1 must be a multiple of 16. */
+int lc_gptq_panel_update(float* W, const float* e_hi, const float* e_lo, const float* U, const float* U_lo,
+                         int64_t rows, int64_t cols, int64_t p1, int64_t p2, int32_t* status, lc_stream_t stream);
+
+/* GPTQ.weight_transform (gptq.py:199-244) with the trailing update on the tensor cores: the update
+ * after each 128-column block covers only the rest of its 1024-column panel (fp32 FFMA); columns to
+ * the right of a panel are updated once per panel by a K = 1024 tcgen05 kind::tf32 GEMM with a
+ * three-term hi/lo split (fp32-level accuracy).  Same sums as the reference, associated differently.
+ *   U_lo        cols x cols from lc_gptq_split_tf32(U)
+ *   scratch_err 128 x rows;  panel_hi, panel_lo  1024 x rows each (fp32 scratch)
+ *   status      optional, receives LC_ERR_TIMEOUT if a bounded pipeline wait expires
+ * Needs cols % 128 == 0 and rows % 4 == 0 (LC_ERR_SHAPE otherwise: use lc_gptq_weight_transform). */
+int lc_gptq_weight_transform_tc(float* W, const float* U, const float* U_lo, int64_t rows, int64_t cols,
+                                int bits, int sym, float* scratch_err, float* panel_hi, float* panel_lo,
+                                float* scales, float* zeros, uint8_t* codes_u8, float* loss_rows,
+                                int32_t* status, lc_stream_t stream);
 
 /* lc_gptq_weight_transform for callers that cannot allocate.  (No counterpart in the reference:
  * its solver allocates freely through torch.)

@@ -31,6 +31,7 @@ SIGNATURES = {
     'lc_fp8_e4m3_quant': [_p, _i, _i64, _i64, _p, _p, _p, _p],
     'lc_hessian_accum': [_p, _i64, _i64, _p, _f, _f, _i, _p, _p],
     'lc_hessian_accum_multi': [_p, _p, _i, _i64, _p, _f, _f, _i, _p, _p],
+    'lc_selftest_wait_expiry': [_p, _p],
     'lc_gptq_diag': [_p, _i64, _p, _p],
     'lc_gptq_permute_damp': [_p, _i, _p, _p, _i64, _i64, _f, _f, _i, _p, _p, _p, _p],
     'lc_gptq_flip': [_p, _i64, _p, _p],
@@ -38,6 +39,9 @@ SIGNATURES = {
     'lc_gptq_trailing_update': [_p, _p, _p, _i64, _i64, _i64, _i, _i64, _p],
     'lc_gptq_weight_transform': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p],
     'lc_gptq_weight_transform_noalloc': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p],
+    'lc_gptq_split_tf32': [_p, _i64, _p, _p],
+    'lc_gptq_panel_update': [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _p],
+    'lc_gptq_weight_transform_tc': [_p, _p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     'lc_gptq_unpermute': [_p, _p, _i64, _i64, _p, _i, _p],
     'lc_awq_act_mean': [_p, _i, _i64, _i64, _p, _p, _i64, _p],
     'lc_awq_scale_quant': [_p, _p, _i, _i64, _i64, _i64, _i, _i, _p, _p],

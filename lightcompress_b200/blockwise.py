@@ -233,6 +233,7 @@ class GPTQBlockwise:
                 self._replace(subset)
         if self.quant_out:
             outs = self.block_forward(block, inputs, kwargs)
+        self.solver.check_status()
         return outs
 
     @torch.no_grad()
@@ -300,6 +301,7 @@ class GPTQBlockwise:
             outs.append(resid[i] + m.down_proj(prod[i]))
             prod[i] = None
             resid[i] = None
+        self.solver.check_status()
         return outs
 
     def _replace(self, subset):

@@ -18,6 +18,9 @@ struct BlockArgs {
   float* W;
   const float* U;
   float* err_t;       // [128][rows]
+  float* panel_hi;    // optional [panel depth][rows]: err again, row panel_k0 + i (tensor-core operand)
+  float* panel_lo;    // optional: err - tf32_truncate(err), same layout
+  int panel_k0;
   float* scales;
   float* zeros;
   uint8_t* codes;
@@ -114,6 +117,11 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
       if (a.codes) a.codes[r * a.cols + a.col0 + j] = (uint8_t)cd[c];
     }
     a.err_t[(int64_t)j * a.rows + r] = er[c];
+    if (a.panel_hi) {
+      const float hi = __uint_as_float(__float_as_uint(er[c]) & 0xffffe000u);
+      a.panel_hi[(int64_t)(a.panel_k0 + j) * a.rows + r] = er[c];
+      a.panel_lo[(int64_t)(a.panel_k0 + j) * a.rows + r] = er[c] - hi;
+    }
   }
   if (lane == 0) {
     const int64_t g = r * a.n_groups + a.col0 / kBlk;
@@ -127,7 +135,8 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
 
 int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0, int count,
                       int bits, int sym, float* err_t, float* scales, float* zeros, int64_t n_groups,
-                      uint8_t* codes, float* loss_rows, cudaStream_t st) {
+                      uint8_t* codes, float* loss_rows, cudaStream_t st, float* panel_hi, float* panel_lo,
+                      int panel_k0) {
   // per-device attribute; setting it on every call keeps multi-device processes correct
   if (cudaFuncSetAttribute(gptq_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (kBlk * kBlk + kBlk) * (int)sizeof(float)) != cudaSuccess)
@@ -136,6 +145,9 @@ int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int6
   a.W = W;
   a.U = U;
   a.err_t = err_t;
+  a.panel_hi = panel_hi;
+  a.panel_lo = panel_lo;
+  a.panel_k0 = panel_k0;
   a.scales = scales;
   a.zeros = zeros;
   a.codes = codes;
@@ -165,5 +177,5 @@ extern "C" LC_API int lc_gptq_block_quant(float* W, const float* U, int64_t rows
   if (bits < 2 || bits > 8) return LC_ERR_ARG;
   if (n_groups < (cols + 127) / 128) return LC_ERR_SHAPE;
   return lc::gptq_block_launch(W, U, rows, cols, col0, count, bits, sym, err_out, scales, zeros, n_groups,
-                               codes_u8, loss_rows, reinterpret_cast<cudaStream_t>(stream));
+                               codes_u8, loss_rows, reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, 0);
 }

@@ -18,7 +18,7 @@ struct TrailArgs {
   float* W;
   const float* err_t;  // [128][rows]
   const float* U;
-  int64_t rows, cols, col0, col1;
+  int64_t rows, cols, col0, col1, col_end;  // updates columns [col1, col_end)
   int k;
 };
 
@@ -46,16 +46,16 @@ __global__ void __launch_bounds__(256) gptq_trail_kernel(TrailArgs a) {
         const float* pb_g = a.U + (a.col0 + kg) * a.cols + n0 + c4;
         if (VEC) {
           if (m0 + c4 < a.rows) va = *reinterpret_cast<const float4*>(pa_g);
-          if (n0 + c4 < a.cols) vb = *reinterpret_cast<const float4*>(pb_g);
+          if (n0 + c4 < a.col_end) vb = *reinterpret_cast<const float4*>(pb_g);
         } else {
           if (m0 + c4 + 0 < a.rows) va.x = pa_g[0];
           if (m0 + c4 + 1 < a.rows) va.y = pa_g[1];
           if (m0 + c4 + 2 < a.rows) va.z = pa_g[2];
           if (m0 + c4 + 3 < a.rows) va.w = pa_g[3];
-          if (n0 + c4 + 0 < a.cols) vb.x = pb_g[0];
-          if (n0 + c4 + 1 < a.cols) vb.y = pb_g[1];
-          if (n0 + c4 + 2 < a.cols) vb.z = pb_g[2];
-          if (n0 + c4 + 3 < a.cols) vb.w = pb_g[3];
+          if (n0 + c4 + 0 < a.col_end) vb.x = pb_g[0];
+          if (n0 + c4 + 1 < a.col_end) vb.y = pb_g[1];
+          if (n0 + c4 + 2 < a.col_end) vb.z = pb_g[2];
+          if (n0 + c4 + 3 < a.col_end) vb.w = pb_g[3];
         }
       }
       pa[t] = va;
@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(256) gptq_trail_kernel(TrailArgs a) {
       const int64_t n = n0 + (h == 0 ? tx * 4 : 64 + tx * 4);
       float* p = a.W + m * a.cols + n;
       if (VEC) {
-        if (n < a.cols) {
+        if (n < a.col_end) {
           float4 c = *reinterpret_cast<float4*>(p);
           c.x -= acc[i][h * 4 + 0];
           c.y -= acc[i][h * 4 + 1];
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(256) gptq_trail_kernel(TrailArgs a) {
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (n + j < a.cols) p[j] -= acc[i][h * 4 + j];
+          if (n + j < a.col_end) p[j] -= acc[i][h * 4 + j];
       }
     }
   }
@@ -134,12 +134,13 @@ __global__ void __launch_bounds__(256) gptq_trail_kernel(TrailArgs a) {
 }  // namespace
 
 int gptq_trail_launch(float* W, const float* err_t, const float* U, int64_t rows, int64_t cols, int64_t col0,
-                      int k, int64_t col1, cudaStream_t st) {
-  if (col1 >= cols) return LC_OK;
-  TrailArgs a{W, err_t, U, rows, cols, col0, col1, k};
-  dim3 grid((unsigned)((cols - col1 + TN - 1) / TN), (unsigned)((rows + TM - 1) / TM));
-  const bool vec = (cols % 4 == 0) && (rows % 4 == 0) && (col1 % 4 == 0) && aligned16(W) && aligned16(err_t) &&
-                   aligned16(U);
+                      int k, int64_t col1, cudaStream_t st, int64_t col_end) {
+  if (col_end < 0 || col_end > cols) col_end = cols;
+  if (col1 >= col_end) return LC_OK;
+  TrailArgs a{W, err_t, U, rows, cols, col0, col1, col_end, k};
+  dim3 grid((unsigned)((col_end - col1 + TN - 1) / TN), (unsigned)((rows + TM - 1) / TM));
+  const bool vec = (cols % 4 == 0) && (rows % 4 == 0) && (col1 % 4 == 0) && (col_end % 4 == 0) && aligned16(W) &&
+                   aligned16(err_t) && aligned16(U);
   if (vec) gptq_trail_kernel<true><<<grid, 256, 0, st>>>(a);
   else gptq_trail_kernel<false><<<grid, 256, 0, st>>>(a);
   LC_LAUNCH_CHECK();
@@ -148,7 +149,8 @@ int gptq_trail_launch(float* W, const float* err_t, const float* U, int64_t rows
 
 int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0, int count,
                       int bits, int sym, float* err_t, float* scales, float* zeros, int64_t n_groups,
-                      uint8_t* codes, float* loss_rows, cudaStream_t st);
+                      uint8_t* codes, float* loss_rows, cudaStream_t st, float* panel_hi, float* panel_lo,
+                      int panel_k0);
 
 }  // namespace lc
 
@@ -156,7 +158,7 @@ extern "C" LC_API int lc_gptq_trailing_update(float* W, const float* err, const 
                                        int64_t col0, int k, int64_t col1, lc_stream_t stream) {
   if (!W || !err || !U) return LC_ERR_ARG;
   if (rows <= 0 || cols <= 0 || k < 1 || k > 128 || col0 < 0 || col0 + k > cols || col1 < col0 + k) return LC_ERR_ARG;
-  return lc::gptq_trail_launch(W, err, U, rows, cols, col0, k, col1, reinterpret_cast<cudaStream_t>(stream));
+  return lc::gptq_trail_launch(W, err, U, rows, cols, col0, k, col1, reinterpret_cast<cudaStream_t>(stream), -1);
 }
 
 // ---- allocation-free variant -------------------------------------------------------------------
@@ -213,9 +215,9 @@ extern "C" LC_API int lc_gptq_weight_transform(float* W, const float* U, int64_t
   for (int64_t i1 = 0; i1 < cols; i1 += 128) {
     const int count = (int)((cols - i1 < 128) ? (cols - i1) : 128);
     int rc = lc::gptq_block_launch(W, U, rows, cols, i1, count, bits, sym, scratch_err, scales, zeros, n_groups,
-                                   codes_u8, loss_rows, st);
+                                   codes_u8, loss_rows, st, nullptr, nullptr, 0);
     if (rc != LC_OK) return rc;
-    rc = lc::gptq_trail_launch(W, scratch_err, U, rows, cols, i1, count, i1 + count, st);
+    rc = lc::gptq_trail_launch(W, scratch_err, U, rows, cols, i1, count, i1 + count, st, -1);
     if (rc != LC_OK) return rc;
   }
   return LC_OK;

@@ -36,6 +36,9 @@ class GPTQ:
         # 'direct': one Cholesky of the index-reversed matrix + one triangular inverse;
         # 'reference': the reference's three factorisations (gptq.py:172-174).  Same U up to fp32 rounding.
         self.factorization = special.get('factorization', 'direct')
+        # 'tensor': trailing update batched per 1024-column panel on tcgen05 (3-term tf32 split);
+        # 'ffma': the reference's per-block update with the fp32 FFMA kernel
+        self.trailing = special.get('trailing', 'tensor')
         # forward hooks deliver one sequence per call; up to `hessian_batch` of them (<= 8) are
         # held by reference and accumulated in one launch, so H is updated once per batch
         self.hessian_batch = max(1, min(8, int(special.get('hessian_batch', 8))))
@@ -44,6 +47,7 @@ class GPTQ:
         self.hessian_ksplit = int(special.get('hessian_ksplit', 0))
         self.model_dtype = model_dtype
         self.layers_cache = {}
+        self._pending_status = []       # device status words of tensor-core launches, read lazily
         self._check_config()
         self.need_perm = (self.wquantizer.granularity == 'per_group' and not self.static_groups
                           and self.actorder)
@@ -102,6 +106,7 @@ class GPTQ:
         st = self.layers_cache[name]
         self._flush(st)
         _, n = parallel.reduce_hessian(st['H'], st['nsamples'])
+        self.check_status()
         code = int(st['status'].item())
         if code != 0:
             raise L.LcError('lc_hessian_accum', code, L.status_string(code))
@@ -123,20 +128,29 @@ class GPTQ:
         return res
 
     @torch.no_grad()
-    def factorize(self, H, hscale=1.0):
+    def factorize(self, H, hscale=1.0, perm=None):
         """Everything of process_hessian_and_weights (gptq.py:128-176) that depends on H only:
         act-order permutation, dampening, and U with U^T U = (permuted, damped H)^-1.  Linears that
         read the same input (q/k/v, gate/up) share one result."""
         L.require_cuda(H)
         C = H.shape[0]
-        perm, invperm = self.act_order(H)
+        if perm is None:
+            perm, invperm = self.act_order(H)
+        else:
+            # caller-supplied column order (argsort leaves the order of equal diagonal entries open)
+            perm = perm.to(H.device).contiguous()
+            invperm = torch.argsort(perm)
         Hp = torch.empty((C, C), dtype=torch.float32, device=H.device)
         scratch = torch.empty(4, dtype=torch.float32, device=H.device)
         direct = self.factorization == 'direct'
         L.call('lc_gptq_permute_damp', None, L.LC_F32, L.ptr(H), L.ptr(perm), 0, C, float(hscale),
                float(self.percdamp), int(direct), None, L.ptr(Hp), L.ptr(scratch), L.stream_of(H))
         U = self.inverse_cholesky_upper_reversed(Hp) if direct else self.inverse_cholesky_upper(Hp)
-        return {'H': H, 'perm': perm, 'invperm': invperm, 'U': U}
+        fac = {'H': H, 'perm': perm, 'invperm': invperm, 'U': U, 'U_lo': None}
+        if self.trailing == 'tensor' and C % 128 == 0 and C > 1024:
+            fac['U_lo'] = torch.empty_like(U)
+            L.call('lc_gptq_split_tf32', L.ptr(U), U.numel(), L.ptr(fac['U_lo']), L.stream_of(U))
+        return fac
 
     @torch.no_grad()
     def solve(self, W, H, hscale=1.0, rows=None, factor=None):
@@ -159,8 +173,16 @@ class GPTQ:
         zeros = torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev)
         codes = torch.empty((R, C), dtype=torch.uint8, device=dev) if self.emit_codes else None
         loss_rows = torch.empty(R, dtype=torch.float32, device=dev)
-        L.call('lc_gptq_weight_transform', L.ptr(Wp), L.ptr(U), R, C, int(wq.bit), int(wq.sym), L.ptr(err),
-               L.ptr(scales), L.ptr(zeros), L.ptr(codes), L.ptr(loss_rows), stream)
+        if fac.get('U_lo') is not None and R % 4 == 0:
+            panel = torch.empty((2, 1024, R), dtype=torch.float32, device=dev)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            L.call('lc_gptq_weight_transform_tc', L.ptr(Wp), L.ptr(U), L.ptr(fac['U_lo']), R, C, int(wq.bit),
+                   int(wq.sym), L.ptr(err), L.ptr(panel[0]), L.ptr(panel[1]), L.ptr(scales), L.ptr(zeros),
+                   L.ptr(codes), L.ptr(loss_rows), L.ptr(status), stream)
+            self._pending_status.append(status)
+        else:
+            L.call('lc_gptq_weight_transform', L.ptr(Wp), L.ptr(U), R, C, int(wq.bit), int(wq.sym), L.ptr(err),
+                   L.ptr(scales), L.ptr(zeros), L.ptr(codes), L.ptr(loss_rows), stream)
         out = torch.empty((R, C), dtype=torch.float32, device=dev)
         L.call('lc_gptq_unpermute', L.ptr(Wp), L.ptr(perm), R, C, L.ptr(out), L.LC_F32, stream)
         return {'weight': out, 'buf_scales': scales, 'buf_zeros': None if wq.sym else zeros,
@@ -245,6 +267,15 @@ class GPTQ:
         if self.need_perm:
             weight = weight[:, module.buf_invperm]
         return weight
+
+    def check_status(self):
+        """Reads (one sync) the device status words of the tensor-core launches issued so far."""
+        if self._pending_status:
+            codes = torch.cat(self._pending_status).tolist()
+            self._pending_status = []
+            for c in codes:
+                if c != 0:
+                    raise L.LcError('lc_gptq_weight_transform_tc', c, L.status_string(c))
 
     @torch.no_grad()
     def free(self, name):
