@@ -285,6 +285,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--workload', default='block', choices=['block', 'layer'])
+    ap.add_argument('--calib-bs', type=int, default=1,
+                    help='sequences per block-forward call (calib.bs of the reference config; block workload)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
     args = ap.parse_args()
@@ -320,7 +322,8 @@ def main():
         runner = lc.GPTQBlockwise(wq, SPECIAL, quant_out=True)
         solver = runner.solver
         timer = HessianTimer(solver)
-        inputs = [X[i:i + 1] for i in range(n_seq)]
+        bs = max(1, min(args.calib_bs, n_seq))
+        inputs = [X[i:i + bs] for i in range(0, n_seq, bs)]
 
         def step():
             block = copy.deepcopy(master)          # device copy of the bf16 block (the reference does block.cuda())
@@ -335,24 +338,56 @@ def main():
                       for n, rc in zip(['q', 'k', 'v', 'o', 'gate', 'up', 'down'], LINEAR_SHAPES)}
 
             host_params = [p.data for p in block_host.parameters()]
+            copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+            chunk = 8
+            name_to_key = {'self_attn.q_proj': 'q', 'self_attn.k_proj': 'k', 'self_attn.v_proj': 'v',
+                           'self_attn.o_proj': 'o', 'mlp.gate_proj': 'gate', 'mlp.up_proj': 'up',
+                           'mlp.down_proj': 'down'}
 
             def e2e_step():
-                x_stage.copy_(X_host, non_blocking=True)
-                block = copy.deepcopy(master)          # module skeleton on the device ...
+                # host -> device copies of the activations run on their own stream, chunk by chunk; the
+                # first stage of the block waits for the chunk it is about to read.  Each subset's
+                # quantised weights go back to the host on a third stream while the next stage computes
+                # (the reference's block.cuda() / block.cpu()).
+                main_s = torch.cuda.current_stream()
+                copy_in.wait_stream(main_s)
+                block = copy.deepcopy(master)
                 for p, hp in zip(block.parameters(), host_params):
-                    p.data.copy_(hp, non_blocking=True)    # ... filled from pinned host memory (block.cuda())
-                outs = runner.block_opt(block, [x_stage[i:i + 1] for i in range(n_seq)], kwargs)
-                a, m = block.self_attn, block.mlp
-                for key, mod in zip(w_host, [a.q_proj, a.k_proj, a.v_proj, a.o_proj, m.gate_proj, m.up_proj,
-                                             m.down_proj]):
-                    w_host[key].copy_(mod.weight, non_blocking=True)     # the reference's block.cpu()
+                    p.data.copy_(hp, non_blocking=True)
+                evs = []
+                with torch.cuda.stream(copy_in):
+                    for i in range(0, n_seq, chunk):
+                        x_stage[i:i + chunk].copy_(X_host[i:i + chunk], non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record(copy_in)
+                        evs.append(ev)
+                mods = dict(block.named_modules())
+
+                def on_input(i):
+                    if (i * bs) % chunk == 0:
+                        main_s.wait_event(evs[min(len(evs) - 1, (i * bs) // chunk)])
+                    if bs > chunk:
+                        main_s.wait_event(evs[min(len(evs) - 1, ((i + 1) * bs - 1) // chunk)])
+
+                def on_subset_done(names):
+                    done = torch.cuda.Event()
+                    done.record(main_s)
+                    copy_out.wait_event(done)
+                    with torch.cuda.stream(copy_out):
+                        for nme in names:
+                            w_host[name_to_key[nme]].copy_(mods[nme].weight, non_blocking=True)
+                runner.on_input, runner.on_subset_done = on_input, on_subset_done
+                outs = runner.block_opt(block, [x_stage[i:i + bs] for i in range(0, n_seq, bs)], kwargs)
+                runner.on_input = runner.on_subset_done = None
+                main_s.wait_stream(copy_out)
                 return outs
             h2d = int(X_host.numel() * 2 + sum(p.numel() * 2 for p in block_host.parameters()))
             d2h = int(sum(w.numel() * 4 for w in w_host.values()))
         n_blocks_solver = sum(-(-c // 128) for r, c in LINEAR_SHAPES)
         # 4 Hessians, 4 diag, per linear (damp, permute H, permute W, flip, un-permute), block + trailing
         # kernels, per linear the deploy-time fake quant (gather is torch)
-        launches = 4 * -(-n_seq // HESSIAN_BATCH) + 4 + 7 * 5 + (2 * n_blocks_solver - 7) + 7
+        n_calls = -(-n_seq // bs)
+        launches = 4 * -(-n_calls // HESSIAN_BATCH) + 4 + 7 * 5 + (2 * n_blocks_solver - 7) + 7 + 3 * 7
     else:
         W_host = make_linear_weight().pin_memory() if not args.no_e2e else make_linear_weight()
         W = W_host.to(dev)
@@ -475,7 +510,7 @@ def main():
             'config': {'workload': WORKLOADS[args.workload], 'name': args.workload,
                        'l2': 'inputs (2.1 GB of activations per step) exceed the 126 MB L2',
                        'sharding': f'{n_seq} sequences per rank; solve units (linear, row range) dealt to the ranks',
-                       'hessian_batch': HESSIAN_BATCH},
+                       'hessian_batch': HESSIAN_BATCH, 'calib_bs': args.calib_bs if args.workload == 'block' else 1},
             'roofline': roofline, 'gpu_launches': launches * args.steps, 'clocks': clocks}
     if e2e:
         line['e2e'] = e2e

@@ -95,6 +95,11 @@ class GPTQBlockwise:
         self.early_exit = special.get('early_exit', True)
         self.stage_plan = special.get('stage_plan', True)
         self.forward_passes = 0
+        # optional callbacks for callers that stream a block through the GPU: on_input(i) runs before
+        # the i-th input is first read (e.g. wait for its host-to-device copy), on_subset_done(names)
+        # right after a subset's linears were quantised (e.g. start copying them back)
+        self.on_input = None
+        self.on_subset_done = None
 
     # ---- forwards ----------------------------------------------------------------------------
     @torch.no_grad()
@@ -102,6 +107,8 @@ class GPTQBlockwise:
         self.forward_passes += 1
         outs = []
         for i, x in enumerate(inputs):
+            if self.on_input is not None and self.forward_passes == 1:
+                self.on_input(i)
             try:
                 out = block(x, **(kwargs[i] if isinstance(kwargs, (list, tuple)) else kwargs))
             except _StopForward:
@@ -154,6 +161,8 @@ class GPTQBlockwise:
             self._sharded_solve(names, layers, fac, rank, world)
         for n in names:
             self.solver.layers_cache.pop(n, None)
+        if self.on_subset_done is not None:
+            self.on_subset_done(names)
 
     def _sharded_solve(self, names, layers, fac, rank, world):
         H = fac['H']
@@ -249,7 +258,9 @@ class GPTQBlockwise:
 
         name, layer = self._init_subset(subsets[0])
         normed = []
-        for x in inputs:
+        for i, x in enumerate(inputs):
+            if self.on_input is not None:
+                self.on_input(i)
             normed.append(block.input_layernorm(x))
             self.solver.add_batch(layer, name, normed[-1], None)
         self.subset_transform(subsets[0])

@@ -8,6 +8,8 @@
 //   row_vec_kernel    long rows (per_channel / per_token, or groups > 512 bytes): one CTA per
 //                     row segment, the segment stays in registers between reduce and quantise.
 //   generic_kernel    any shape / alignment: scalar loads, two passes (second pass hits L2).
+#include <type_traits>
+
 #include "lc_common.cuh"
 
 namespace lc {
@@ -169,6 +171,106 @@ __global__ void __launch_bounds__(256) group_vec_kernel(QuantArgs a) {
     if (sub == 0) {
       if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(c.s);
       if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(c.z);
+    }
+  }
+}
+
+// ---- kernel A2: bf16, dynamic, dequantised output only -- packed bf16x2 arithmetic ------------------
+// For bf16 tensors most of the reference's ops are bf16 ops already, so they map one-to-one onto
+// packed bf16x2 instructions with the same round-to-nearest-even: the optional pre-scale w*s[col]
+// (HMUL2), round(u) (h2rint), + zero (HADD2), clamp (HMNMX2 with NaN propagation), (q - z) (HSUB2,
+// exact) and * scale (HMUL2).  Only the quotient w / s needs fp32 (reciprocal + one correction,
+// see div_rint<__nv_bfloat16>); it is rounded to bf16 two at a time by one conversion.
+__device__ __forceinline__ __nv_bfloat162 as_bf2(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+template <int L, int V>
+__global__ void __launch_bounds__(256) group_vec_bf16_fake_kernel(QuantArgs a) {
+  using T = __nv_bfloat16;
+  using E = Elem<T>;
+  constexpr int GV = L * V;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % L;
+  const int64_t groups_per_sweep = nthreads / L;
+  const int64_t groups_per_row = a.cols / a.group;
+  const uint4* in = reinterpret_cast<const uint4*>(a.in);
+  const __nv_bfloat162 qmin2 = __float2bfloat162_rn(a.qr.qmin), qmax2 = __float2bfloat162_rn(a.qr.qmax);
+
+  for (int64_t gw = (tid - lane) / L; gw < a.n_groups_total; gw += groups_per_sweep) {
+    const int64_t g = gw + lane / L;
+    const bool ok = g < a.n_groups_total;
+    uint32_t v[V][4];
+    __nv_bfloat162 mx2 = __float2bfloat162_rn(-INFINITY), mn2 = __float2bfloat162_rn(INFINITY);
+    if (ok) {
+      const uint4* src = in + g * GV + sub;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const uint4 t = __ldcs(src + L * k);
+        v[k][0] = t.x; v[k][1] = t.y; v[k][2] = t.z; v[k][3] = t.w;
+      }
+      if (a.col_scale) {
+        const uint4* sc = reinterpret_cast<const uint4*>(a.col_scale) + (g % groups_per_row) * GV + sub;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const uint4 m = __ldg(sc + L * k);
+          v[k][0] = as_u32(__hmul2(as_bf2(v[k][0]), as_bf2(m.x)));
+          v[k][1] = as_u32(__hmul2(as_bf2(v[k][1]), as_bf2(m.y)));
+          v[k][2] = as_u32(__hmul2(as_bf2(v[k][2]), as_bf2(m.z)));
+          v[k][3] = as_u32(__hmul2(as_bf2(v[k][3]), as_bf2(m.w)));
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < V; ++k)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mx2 = __hmax2_nan(mx2, as_bf2(v[k][j]));
+          mn2 = __hmin2_nan(mn2, as_bf2(v[k][j]));
+        }
+    }
+    float mx = nan_max(__low2float(mx2), __high2float(mx2));
+    float mn = nan_min(__low2float(mn2), __high2float(mn2));
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) {
+      mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    }
+    float s, z;
+    int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
+    const QuantCtx c = make_quant_ctx(s, z, nan_max(fabsf(mx), fabsf(mn)));
+    if (!ok) continue;
+    const int64_t vbase = g * GV + sub;
+    const __nv_bfloat162 s2 = __float2bfloat162_rn(s), z2 = __float2bfloat162_rn(z);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      uint32_t o[4];
+      if (!c.exact) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float w0 = __uint_as_float(v[k][j] << 16), w1 = __uint_as_float(v[k][j] & 0xffff0000u);
+          const float a0 = __fmul_rn(w0, c.r), a1 = __fmul_rn(w1, c.r);
+          const float u0 = __fmaf_rn(__fmaf_rn(-a0, s, w0), c.r, a0);
+          const float u1 = __fmaf_rn(__fmaf_rn(-a1, s, w1), c.r, a1);
+          __nv_bfloat162 t = h2rint(__floats2bfloat162_rn(u0, u1));
+          t = __hmin2_nan(__hmax2_nan(__hadd2(t, z2), qmin2), qmax2);
+          o[j] = as_u32(__hmul2(__hsub2(t, z2), s2));
+        }
+      } else {
+        // tiny / huge / non-finite group: the scalar path with the IEEE division
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float w0 = __uint_as_float(v[k][j] << 16), w1 = __uint_as_float(v[k][j] & 0xffff0000u);
+          const float d0 = int_dequant_fast<T>(int_quant_fast<T>(w0, c, a.qr), c);
+          const float d1 = int_dequant_fast<T>(int_quant_fast<T>(w1, c, a.qr), c);
+          o[j] = as_u32(__floats2bfloat162_rn(d0, d1));
+        }
+      }
+      __stcs(reinterpret_cast<uint4*>(a.fake_out) + vbase + L * k, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+    if (sub == 0) {
+      if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(s);
+      if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(z);
     }
   }
 }
@@ -337,6 +439,13 @@ void launch_group_vec(const QuantArgs& a, cudaStream_t st) {
   const int64_t cap = (int64_t)kNumSMsB200 * 4 * 8;  // a few waves of resident CTAs per SM
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    // dynamic fake quant of a bf16 tensor (the RTN / AWQ case): packed-arithmetic kernel
+    if (a.fake_out && !a.codes_out && !a.scales_in) {
+      group_vec_bf16_fake_kernel<L, V><<<(unsigned)blocks, 256, 0, st>>>(a);
+      return;
+    }
+  }
   group_vec_kernel<T, L, V><<<(unsigned)blocks, 256, 0, st>>>(a);
 }
 
