@@ -4,6 +4,8 @@
 // scalar two-pass kernel.
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "lc_common.cuh"
 
 namespace lc {
@@ -67,6 +69,34 @@ __device__ __forceinline__ float block_absmax(float a, float* smem) {
   return a;
 }
 
+// bf16 rows: quotient in fp32 (reciprocal + one correction), everything else packed bf16x2 -- the
+// reference's ops on a bf16 tensor are bf16 ops: u = w/s, u + 0, e4m3 round, q * s.
+__device__ __forceinline__ void fp8_bf16_vec(const uint4& raw, float s, float rs, __nv_bfloat162 s2, uint4& fake,
+                                             uint2& codes) {
+  const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[4];
+  uint16_t cpair[4];
+  const __nv_bfloat162 zero2 = __float2bfloat162_rn(0.f);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float w0 = __uint_as_float(in[j] << 16), w1 = __uint_as_float(in[j] & 0xffff0000u);
+    const float a0 = __fmul_rn(w0, rs), a1 = __fmul_rn(w1, rs);
+    const float u0 = __fmaf_rn(__fmaf_rn(-a0, s, w0), rs, a0);
+    const float u1 = __fmaf_rn(__fmaf_rn(-a1, s, w1), rs, a1);
+    const __nv_bfloat162 u2 = __hadd2(__floats2bfloat162_rn(u0, u1), zero2);
+    const __nv_fp8x2_storage_t c2 =
+        __nv_cvt_bfloat16raw2_to_fp8x2(*reinterpret_cast<const __nv_bfloat162_raw*>(&u2), __NV_SATFINITE, __NV_E4M3);
+    cpair[j] = (uint16_t)c2;
+    const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(c2, __NV_E4M3);
+    const float2 qf = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+    const __nv_bfloat162 q2 = __floats2bfloat162_rn(qf.x, qf.y);   // e4m3 values are exact in bf16
+    const __nv_bfloat162 f2 = __hmul2(__hsub2(q2, zero2), s2);
+    o[j] = *reinterpret_cast<const uint32_t*>(&f2);
+  }
+  fake = make_uint4(o[0], o[1], o[2], o[3]);
+  codes = make_uint2((uint32_t)cpair[0] | ((uint32_t)cpair[1] << 16), (uint32_t)cpair[2] | ((uint32_t)cpair[3] << 16));
+}
+
 template <typename T, int V>
 __global__ void __launch_bounds__(256) fp8_row_vec_kernel(Fp8Args a) {
   using E = Elem<T>;
@@ -95,6 +125,25 @@ __global__ void __launch_bounds__(256) fp8_row_vec_kernel(Fp8Args a) {
     const float s = fp8_scale<T>(am);
     const float rs = __frcp_rn(s);
     const bool exact = !(s > 1e-30f && s < 1e30f) || !(__fmul_rn(am, rs) < 1e37f);
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      if (!exact) {
+        const __nv_bfloat162 s2 = __float2bfloat162_rn(s);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const int64_t i = threadIdx.x + (int64_t)k * 256;
+          if (i < nvec) {
+            uint4 fake;
+            uint2 cds;
+            fp8_bf16_vec(v[k], s, rs, s2, fake, cds);
+            const int64_t vidx = r * nvec + i;
+            if (a.fake_out) __stcs(reinterpret_cast<uint4*>(a.fake_out) + vidx, fake);
+            if (a.codes_out) *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.codes_out) + vidx * 8) = cds;
+          }
+        }
+        if (threadIdx.x == 0 && a.scales_out) reinterpret_cast<T*>(a.scales_out)[r] = E::from_f(s);
+        continue;
+      }
+    }
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;

@@ -184,6 +184,24 @@ __global__ void __launch_bounds__(256) group_vec_kernel(QuantArgs a) {
 __device__ __forceinline__ __nv_bfloat162 as_bf2(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
 __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
+// quantise + dequantise one 16-byte vector of bf16 values with packed arithmetic (group not `exact`)
+__device__ __forceinline__ uint4 bf16_qdq_vec(const uint4& raw, const QuantCtx& c, __nv_bfloat162 s2, __nv_bfloat162 z2,
+                                              __nv_bfloat162 qmin2, __nv_bfloat162 qmax2) {
+  const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float w0 = __uint_as_float(in[j] << 16), w1 = __uint_as_float(in[j] & 0xffff0000u);
+    const float a0 = __fmul_rn(w0, c.r), a1 = __fmul_rn(w1, c.r);
+    const float u0 = __fmaf_rn(__fmaf_rn(-a0, c.s, w0), c.r, a0);
+    const float u1 = __fmaf_rn(__fmaf_rn(-a1, c.s, w1), c.r, a1);
+    __nv_bfloat162 t = h2rint(__floats2bfloat162_rn(u0, u1));
+    t = __hmin2_nan(__hmax2_nan(__hadd2(t, z2), qmin2), qmax2);
+    o[j] = as_u32(__hmul2(__hsub2(t, z2), s2));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 template <int L, int V>
 __global__ void __launch_bounds__(256) group_vec_bf16_fake_kernel(QuantArgs a) {
   using T = __nv_bfloat16;
@@ -339,6 +357,24 @@ __global__ void __launch_bounds__(256) row_vec_kernel(QuantArgs a) {
     }
     // static mode has no min/max: keep the exact division there
     const QuantCtx c = make_quant_ctx(s, z, is_static ? INFINITY : nan_max(fabsf(mx_all), fabsf(mn_all)));
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      if (!c.exact && a.fake_out && !a.codes_out) {
+        // bf16 dequantised output only: packed bf16x2 arithmetic (see group_vec_bf16_fake_kernel)
+        const __nv_bfloat162 s2 = __float2bfloat162_rn(s), z2 = __float2bfloat162_rn(z);
+        const __nv_bfloat162 qmin2 = __float2bfloat162_rn(a.qr.qmin), qmax2 = __float2bfloat162_rn(a.qr.qmax);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const int64_t i = threadIdx.x + (int64_t)k * 256;
+          if (i < nvec)
+            __stcs(reinterpret_cast<uint4*>(a.fake_out) + g * nvec + i, bf16_qdq_vec(v[k], c, s2, z2, qmin2, qmax2));
+        }
+        if (threadIdx.x == 0) {
+          if (a.scales_out) reinterpret_cast<T*>(a.scales_out)[g] = E::from_f(s);
+          if (a.zeros_out) reinterpret_cast<T*>(a.zeros_out)[g] = E::from_f(z);
+        }
+        continue;
+      }
+    }
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;
