@@ -1,10 +1,23 @@
 // Family 3: the 128-column in-block step of the GPTQ solver.
 //
-// Rows of W are independent (they only share the inverse-Hessian factor U), so one warp owns
-// one row: lane l keeps columns l, l+32, l+64, l+96 of the block in registers.  The 128x128
-// diagonal block of U sits in shared memory and is shared by the 16 rows of the CTA.  The 128
-// dependent column steps run entirely in registers / shuffles; nothing is written to global
-// memory until the block is finished.
+// Rows of W are independent (they only share the inverse-Hessian factor U) and every row is a
+// chain of 128 dependent column steps (quantise column i, spread its error over columns > i), so
+// the kernel is bound by the latency of that chain and by how many instructions a row-step costs,
+// not by memory.  Two mappings:
+//
+//  * quad kernel (full 128-column blocks, 16-byte aligned rows): four lanes own one row, eight rows
+//    per warp.  Lane `sub` keeps, for each 16-column slot g, columns 16g + 4*sub .. +3 (one float4
+//    of W and of the U row).  The quantisation arithmetic of a step, identical for all lanes of a
+//    row, is thereby shared by 8 rows per instruction instead of 1, and the error spread costs
+//    32 columns per lane.  Slots are retired front to back: after 16 steps the finished slot is
+//    stored and the register file shifts down by one slot, so that all register indices stay
+//    static without unrolling the 128 steps.
+//  * warp kernel (any block width up to 128): one warp per row, lane l keeps columns l, l+32, l+64,
+//    l+96.  Used for ragged tails and unaligned tensors.
+//
+// Both run the same per-element arithmetic in the same order and give bit-identical results.  The
+// 128x128 diagonal block of U sits in shared memory; nothing is written to global memory until a
+// slot (quad) or the block (warp) is finished.
 #include "lc_common.cuh"
 
 namespace lc {
@@ -131,13 +144,180 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
   }
 }
 
+
+// ---- quad kernel -----------------------------------------------------------------------------------
+constexpr int kQuadWarps = 4;
+constexpr int kQuadRowsPerCta = kQuadWarps * 8;
+constexpr int kQuadThreads = kQuadWarps * 32;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gsrc));
+}
+
+// clamp(rint(w / s) + z, qmin, qmax) like int_quant_fast<float>, with the rounding done by adding
+// and subtracting 1.5 * 2^23 (two FADDs on the dependent chain instead of a conversion-unit op).
+// For |q| < 2^22 that is exactly rintf (round-half-even); beyond it the value is saturated by the
+// clamp whichever integer comes out, and NaN / inf fall to the IEEE path through the guard.
+__device__ __forceinline__ float quad_quant(float w, const QuantCtx& c, QRange qr) {
+  const float q0 = __fmul_rn(w, c.r);
+  const float e = __fmaf_rn(-q0, c.s, w);
+  const float q1 = __fmaf_rn(e, c.r, q0);
+  float k = __fsub_rn(__fadd_rn(q1, 12582912.f), 12582912.f);
+  if (c.exact || !(fabsf(fabsf(__fsub_rn(q1, k)) - 0.5f) >= 1e-4f)) k = rintf(ieee_div(w, c.s));
+  return clampf(__fadd_rn(k, c.z), qr.qmin, qr.qmax);
+}
+
+struct QuadRow {
+  float w[32];       // slot g (16 columns) of the not yet retired part of the row: w[4g .. 4g+3]
+  float loss;
+};
+
+// The 16 column steps of slot `t` with NG live slots (the current one and NG-1 to its right), then
+// the slot is stored and the register file shifts down by one slot.  All U values of a step are
+// fetched before the step's dependent chain starts, so the chain never waits on shared memory.
+template <int NG>
+__device__ __forceinline__ void quad_slot(QuadRow& row, const BlockArgs& a, const float* u1, const float* dinv,
+                                          const QuantCtx& qc, int t, int sub, int quad_base, bool live, int64_t r,
+                                          float* wrow) {
+  float er[4] = {0.f, 0.f, 0.f, 0.f};
+  int cd[4] = {0, 0, 0, 0};
+  float (&w)[32] = row.w;
+#pragma unroll
+  for (int st = 0; st < 16; ++st) {
+    const int owner = st >> 2, k = st & 3;
+    const int i = 16 * t + st;
+    const float* urow = u1 + i * kBlk;
+    const float d = urow[i], rd = dinv[i];
+    float4 u[NG];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) u[g] = *reinterpret_cast<const float4*>(urow + 16 * (t + g) + 4 * sub);
+
+    const float wi = __shfl_sync(0xffffffffu, w[k], quad_base | owner);
+    const float q = quad_quant(wi, qc, a.qr);
+    const float dq = int_dequant_fast<float>(q, qc);
+    const float diff = __fsub_rn(wi, dq);
+    const float e0 = __fmul_rn(diff, rd);
+    const float err = __fmaf_rn(__fmaf_rn(-e0, d, diff), rd, e0);
+    row.loss = fmaf(0.5f * err, err, row.loss);
+    if (sub == owner) {
+      er[k] = err;
+      cd[k] = code_to_int(q) - (int)a.qr.qmin;
+    }
+    // current slot: only the columns behind column i move
+    {
+      const float uu[4] = {u[0].x, u[0].y, u[0].z, u[0].w};
+#pragma unroll
+      for (int k2 = 0; k2 < 4; ++k2) {
+        const float upd = __fsub_rn(w[k2], __fmul_rn(err, uu[k2]));
+        if (sub > owner || (sub == owner && k2 > k)) w[k2] = upd;
+      }
+    }
+#pragma unroll
+    for (int g = 1; g < NG; ++g) {
+      w[4 * g + 0] = __fsub_rn(w[4 * g + 0], __fmul_rn(err, u[g].x));
+      w[4 * g + 1] = __fsub_rn(w[4 * g + 1], __fmul_rn(err, u[g].y));
+      w[4 * g + 2] = __fsub_rn(w[4 * g + 2], __fmul_rn(err, u[g].z));
+      w[4 * g + 3] = __fsub_rn(w[4 * g + 3], __fmul_rn(err, u[g].w));
+    }
+  }
+  if (live) {
+    const int j0 = 16 * t + 4 * sub;
+    *reinterpret_cast<float4*>(wrow + j0) = make_float4(w[0], w[1], w[2], w[3]);
+    if (a.codes)
+      *reinterpret_cast<uchar4*>(a.codes + r * a.cols + a.col0 + j0) =
+          make_uchar4((unsigned char)cd[0], (unsigned char)cd[1], (unsigned char)cd[2], (unsigned char)cd[3]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      a.err_t[(int64_t)(j0 + k) * a.rows + r] = er[k];
+      if (a.panel_hi) {
+        const float hi = __uint_as_float(__float_as_uint(er[k]) & 0xffffe000u);
+        a.panel_hi[(int64_t)(a.panel_k0 + j0 + k) * a.rows + r] = er[k];
+        a.panel_lo[(int64_t)(a.panel_k0 + j0 + k) * a.rows + r] = er[k] - hi;
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 28; ++k) w[k] = w[k + 4];
+}
+
+__global__ void __launch_bounds__(kQuadThreads) gptq_block_quad_kernel(BlockArgs a) {
+  extern __shared__ float u1[];  // [128][128]; row i is only filled from column (i & ~3) on
+  float* dinv = u1 + kBlk * kBlk;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 3;
+
+  // U block -> shared memory, 16 bytes per copy, upper triangle only (all copies in flight at once)
+  {
+    const float* ublk = a.U + a.col0 * a.cols + a.col0;
+    for (int idx = threadIdx.x; idx < kBlk * (kBlk / 4); idx += kQuadThreads) {
+      const int i = idx >> 5, j4 = (idx & 31) << 2;
+      if (j4 + 3 >= i) cp_async16(&u1[i * kBlk + j4], ublk + (int64_t)i * a.cols + j4);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x < kBlk) dinv[threadIdx.x] = __frcp_rn(u1[threadIdx.x * kBlk + threadIdx.x]);
+  __syncthreads();
+
+  const int64_t r_raw = (int64_t)blockIdx.x * kQuadRowsPerCta + warp * 8 + (lane >> 2);
+  const bool live = r_raw < a.rows;
+  const int64_t r = live ? r_raw : a.rows - 1;   // idle lanes shadow the last row and store nothing
+
+  float* wrow = a.W + r * a.cols + a.col0;
+  QuadRow row;
+  float (&w)[32] = row.w;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const float4 v = *reinterpret_cast<const float4*>(wrow + 16 * g + 4 * sub);
+    w[4 * g + 0] = v.x, w[4 * g + 1] = v.y, w[4 * g + 2] = v.z, w[4 * g + 3] = v.w;
+  }
+  float mx = w[0], mn = w[0];
+#pragma unroll
+  for (int k = 1; k < 32; ++k) {
+    mx = nan_max(mx, w[k]);
+    mn = nan_min(mn, w[k]);
+  }
+#pragma unroll
+  for (int o = 1; o <= 2; o <<= 1) {
+    mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+  }
+  float s, z;
+  int_qparams<float>(mn, mx, a.qr, a.sym, s, z);
+  const QuantCtx qc = make_quant_ctx(s, z, 16.f * nan_max(fabsf(mx), fabsf(mn)));
+  row.loss = 0.f;
+  const int quad_base = lane & ~3;
+
+  // live slots shrink as slots retire; four code copies (8, 6, 4, 2 live slots), two slots each
+#pragma unroll 1
+  for (int t = 0; t < 2; ++t) quad_slot<8>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+#pragma unroll 1
+  for (int t = 2; t < 4; ++t) quad_slot<6>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+#pragma unroll 1
+  for (int t = 4; t < 6; ++t) quad_slot<4>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+#pragma unroll 1
+  for (int t = 6; t < 8; ++t) quad_slot<2>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+
+  if (live && sub == 0) {
+    const int64_t g = r * a.n_groups + a.col0 / kBlk;
+    a.scales[g] = s;
+    a.zeros[g] = z;
+    if (a.loss_rows) a.loss_rows[r] += row.loss;
+  }
+}
+
 }  // namespace
 
 int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0, int count,
                       int bits, int sym, float* err_t, float* scales, float* zeros, int64_t n_groups,
                       uint8_t* codes, float* loss_rows, cudaStream_t st, float* panel_hi, float* panel_lo,
                       int panel_k0) {
+  constexpr int kSmem = (kBlk * kBlk + kBlk) * (int)sizeof(float);
   // per-device attribute; setting it on every call keeps multi-device processes correct
+  if (cudaFuncSetAttribute(gptq_block_quad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+      cudaSuccess)
+    return LC_ERR_CUDA;
   if (cudaFuncSetAttribute(gptq_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (kBlk * kBlk + kBlk) * (int)sizeof(float)) != cudaSuccess)
     return LC_ERR_CUDA;
@@ -159,8 +339,15 @@ int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int6
   a.count = count;
   a.sym = sym ? 1 : 0;
   a.qr = int_qrange(bits, a.sym);
-  const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
-  gptq_block_kernel<<<grid, kThreads, (kBlk * kBlk + kBlk) * sizeof(float), st>>>(a);
+  const bool quad = count == kBlk && cols % 4 == 0 && aligned16(W) && aligned16(U) &&
+                    (!codes || (reinterpret_cast<uintptr_t>(codes) & 3u) == 0);
+  if (quad) {
+    const unsigned grid = (unsigned)((rows + kQuadRowsPerCta - 1) / kQuadRowsPerCta);
+    gptq_block_quad_kernel<<<grid, kQuadThreads, kSmem, st>>>(a);
+  } else {
+    const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
+    gptq_block_kernel<<<grid, kThreads, kSmem, st>>>(a);
+  }
   LC_LAUNCH_CHECK();
   return LC_OK;
 }
