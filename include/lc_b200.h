@@ -288,6 +288,34 @@ int lc_awq_clip_search(const void* W, const void* X, int dtype, int64_t rows, in
  * routine of its own: it is LC_CODES_PACK4 from lc_rtn_int_quant (symmetric, stored as q + 8). */
 int lc_pack_int4_awq(const uint8_t* codes, int64_t rows, int64_t cols, int32_t* out, lc_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Element-wise pieces of the calibration block forward.  The reference has no functions of its
+ * own here: block_forward (llmc/compression/quantization/base_blockwise_quantization.py:378-401)
+ * runs the decoder block's stock module code, whose rotary embedding and gated activation are
+ * chains of 7 and 2 separate tensor ops, and whose RMS norm is a chain of 8.  These routines replace
+ * those chains, rounding to `dtype` after every op of the chain, so that the block's outputs do not
+ * change by a bit.
+ * ------------------------------------------------------------------------------------------ */
+
+/* out = (x * cos) + (rotate_half(x) * sin), rotate_half(x) = cat(-x[d/2:], x[:d/2]) per head.
+ * x, out: [tokens][heads][head_dim] contiguous; cos_tab, sin_tab: [tokens][head_dim]; all `dtype`.
+ * head_dim must be a multiple of 8 (fp32) / 16 (bf16, fp16) elements.  out must not alias x. */
+int lc_rope_apply(const void* x, const void* cos_tab, const void* sin_tab, int dtype, int64_t tokens, int heads,
+                  int head_dim, void* out, lc_stream_t stream);
+
+/* out = silu(gate) * up over n elements, silu(x) = x / (1 + exp(-x)) evaluated in fp32 and rounded
+ * to `dtype` before the product.  n must be a multiple of the 16-byte vector.  out may alias either input. */
+int lc_silu_mul(const void* gate, const void* up, int dtype, int64_t n, void* out, lc_stream_t stream);
+
+/* out = weight * (xf * rsqrt(mean(xf^2, last dim) + eps)).to(dtype), xf = x.float(): the RMS norm of
+ * Llama-style decoder blocks.  x, out: [rows][cols], weight: [cols], all `dtype`.  The sum of squares
+ * is associated like torch's row reduction of a contiguous fp32 tensor (see block_ops.cu), which fixes
+ * 128 <= cols < 8192 and cols % 128 == 0 (LC_ERR_SHAPE otherwise); mean_factor is 1/cols as the
+ * replaced mean computes it, (float)rows / (float)(rows * cols).  The host mirror verifies bit
+ * equality with the module it replaces on random data before first use. */
+int lc_rmsnorm(const void* x, const void* weight, int dtype, int64_t rows, int64_t cols, float mean_factor,
+               float eps, void* out, lc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,9 @@ SIGNATURES = {
     'lc_awq_div_cols': [_p, _p, _i, _i64, _i64, _p, _p],
     'lc_awq_loss': [_p, _p, _i, _i64, _p, _p, _i64, _p],
     'lc_pack_int4_awq': [_p, _i64, _i64, _p, _p],
+    'lc_rope_apply': [_p, _p, _p, _i, _i64, _i, _i, _p, _p],
+    'lc_silu_mul': [_p, _p, _i, _i64, _p, _p],
+    'lc_rmsnorm': [_p, _p, _i, _i64, _i64, _f, _f, _p, _p],
     'lc_awq_clip_search': [_p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _d, _p, _p, _p, _p],
 }
 

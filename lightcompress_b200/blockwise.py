@@ -27,6 +27,7 @@ Several ranks: each rank forwards its own sequences; every Hessian is all-reduce
 (linear, row-range) solve units of a subset are dealt round-robin to the ranks and the results
 broadcast, so every rank continues with identical weights.
 """
+import contextlib
 from collections import OrderedDict
 
 import torch
@@ -34,7 +35,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import parallel
+from . import block_ops, parallel
 from .gptq import GPTQ
 
 
@@ -94,6 +95,9 @@ class GPTQBlockwise:
         # subset's input has been seen: the rest of the block computes values nobody reads.
         self.early_exit = special.get('early_exit', True)
         self.stage_plan = special.get('stage_plan', True)
+        # staged schedule only: RMS norm, rotary embedding and gated activation as one kernel each
+        # (bit-identical to the block's stock tensor ops, checked on random data before first use)
+        self.fused_block_ops = special.get('fused_block_ops', True)
         self.forward_passes = 0
         # optional callbacks for callers that stream a block through the GPU: on_input(i) runs before
         # the i-th input is first read (e.g. wait for its host-to-device copy), on_subset_done(names)
@@ -255,13 +259,14 @@ class GPTQBlockwise:
         kw = (lambda i: kwargs[i]) if isinstance(kwargs, (list, tuple)) else (lambda i: kwargs)
         n = len(inputs)
         self.forward_passes += 1
+        norm = block_ops.rms_norm if self.fused_block_ops else (lambda mod, t: mod(t))
 
         name, layer = self._init_subset(subsets[0])
         normed = []
         for i, x in enumerate(inputs):
             if self.on_input is not None:
                 self.on_input(i)
-            normed.append(block.input_layernorm(x))
+            normed.append(norm(block.input_layernorm, x))
             self.solver.add_batch(layer, name, normed[-1], None)
         self.subset_transform(subsets[0])
         self._replace(subsets[0])
@@ -274,14 +279,17 @@ class GPTQBlockwise:
             raise _StopForward()
         handle = a.o_proj.register_forward_pre_hook(grab)
         ctx = []
-        for i in range(n):
-            try:
-                a(hidden_states=normed[i], **kw(i))
-            except _StopForward:
-                pass
-            normed[i] = None
-            ctx.append(seen.pop('x'))
-            self.solver.add_batch(layer, name, ctx[-1], None)
+        rotary = (block_ops.fused_rotary(a, normed[0].device, normed[0].dtype) if self.fused_block_ops
+                  else contextlib.nullcontext())
+        with rotary:
+            for i in range(n):
+                try:
+                    a(hidden_states=normed[i], **kw(i))
+                except _StopForward:
+                    pass
+                normed[i] = None
+                ctx.append(seen.pop('x'))
+                self.solver.add_batch(layer, name, ctx[-1], None)
         handle.remove()
         self.subset_transform(subsets[1])
         self._replace(subsets[1])
@@ -292,7 +300,7 @@ class GPTQBlockwise:
             h = x + a.o_proj(ctx[i])
             ctx[i] = None
             resid.append(h)
-            normed.append(block.post_attention_layernorm(h))
+            normed.append(norm(block.post_attention_layernorm, h))
             self.solver.add_batch(layer, name, normed[-1], None)
         self.subset_transform(subsets[2])
         self._replace(subsets[2])
@@ -302,7 +310,10 @@ class GPTQBlockwise:
         for i in range(n):
             y = normed[i]
             normed[i] = None
-            prod.append(m.act_fn(m.gate_proj(y)) * m.up_proj(y))
+            if self.fused_block_ops:
+                prod.append(block_ops.gated_act(m.act_fn, m.gate_proj(y), m.up_proj(y)))
+            else:
+                prod.append(m.act_fn(m.gate_proj(y)) * m.up_proj(y))
             self.solver.add_batch(layer, name, prod[-1], None)
         self.subset_transform(subsets[3])
         self._replace(subsets[3])
