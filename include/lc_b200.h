@@ -197,6 +197,38 @@ int lc_gptq_split_tf32(const float* x, int64_t n, float* lo, lc_stream_t stream)
 int lc_gptq_panel_update(float* W, const float* e_hi, const float* e_lo, const float* U, const float* U_lo,
                          int64_t rows, int64_t cols, int64_t p1, int64_t p2, int32_t* status, lc_stream_t stream);
 
+/* fp32-accurate GEMM on the tensor cores (tcgen05 kind::tf32, three-term hi/lo split), the building
+ * block of lc_gptq_panel_update and lc_gptq_factorize:
+ *     C[M][N] (pitch ldc) = beta * C + sign * A^T B,   A: [K][M] (pitch lda), B: [K][N] (pitch ldb)
+ * x_hi is the fp32 operand itself, x_lo = x - tf32_truncate(x) (lc_gptq_split_tf32).  K % 16 == 0; M, N
+ * and the pitches multiples of 4; beta 0 or 1; sign +1 or -1; flags: LC_GEMM_*.  Replaces the fp32
+ * cuBLAS products of the reference (gptq.py:244 and the GEMMs inside its factorisations). */
+#define LC_GEMM_UPPER_ONLY 1 /* C is a diagonal-aligned square block: tiles below the diagonal are skipped */
+#define LC_GEMM_B_LOWER 2    /* B[k][n] == 0 for k < n */
+#define LC_GEMM_A_UPPER 4    /* A[k][m] == 0 for k > m */
+int lc_tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, int64_t lda, const float* B_hi,
+                      const float* B_lo, int64_t ldb, int64_t M, int64_t N, int64_t K, int beta, float sign,
+                      int flags, int32_t* status, lc_stream_t stream);
+
+/* U (n x n, upper triangular, zeros below) with U^T U = H^-1, from A = J H J, the permuted and
+ * dampened Hessian with rows and columns reversed (lc_gptq_permute_damp with reverse_h = 1): the
+ * factorisation chain of GPTQ.process_hessian_and_weights (gptq.py:172-174: cholesky, cholesky_inverse,
+ * cholesky upper) as one blocked Cholesky and one blocked triangular inverse with the large products on
+ * the tensor cores.  A is destroyed.  U_lo, if not NULL, receives U - tf32_truncate(U).  n % 128 == 0.
+ * workspace: lc_gptq_factor_workspace_floats(n) floats.  A non-positive pivot sets *status to
+ * LC_ERR_NOT_PD (the reference raises LinAlgError); a timed-out device wait to LC_ERR_TIMEOUT. */
+int64_t lc_gptq_factor_workspace_floats(int64_t n);
+int lc_gptq_factorize(float* A, int64_t n, float* U, float* U_lo, float* workspace, int64_t workspace_floats,
+                      int32_t* status, lc_stream_t stream);
+
+/* The second half of lc_gptq_factorize alone: G (n x n, row-major, upper triangle read) is the upper
+ * Cholesky factor of A = J H J (A = G^T G), e.g. from cuSOLVER's potrf -- whose column-major lower
+ * factor is this row-major upper factor, byte for byte.  Computes U = J (G^-1)^T J (and U_lo) with
+ * the blocked triangular inverse on the tensor cores.  Same workspace and status as above; G is
+ * not modified. */
+int lc_gptq_invert_factor(const float* G, int64_t n, float* U, float* U_lo, float* workspace,
+                          int64_t workspace_floats, int32_t* status, lc_stream_t stream);
+
 /* GPTQ.weight_transform (gptq.py:199-244) with the trailing update on the tensor cores: the update
  * after each 128-column block covers only the rest of its 1024-column panel (fp32 FFMA); columns to
  * the right of a panel are updated once per panel by a K = 1024 tcgen05 kind::tf32 GEMM with a

@@ -22,7 +22,7 @@ _DTYPES = {torch.float32: LC_F32, torch.bfloat16: LC_BF16, torch.float16: LC_F16
 
 _p, _i, _i64, _f, _d = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_double
 
-# name -> argtypes; every function returns int except the two noted below
+# name -> argtypes; every function returns int except those given another restype in _load
 SIGNATURES = {
     'lc_version': [],
     'lc_status_string': [_i],
@@ -48,6 +48,10 @@ SIGNATURES = {
     'lc_awq_div_cols': [_p, _p, _i, _i64, _i64, _p, _p],
     'lc_awq_loss': [_p, _p, _i, _i64, _p, _p, _i64, _p],
     'lc_pack_int4_awq': [_p, _i64, _i64, _p, _p],
+    'lc_tf32x3_gemm_tn': [_p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i, _f, _i, _p, _p],
+    'lc_gptq_factor_workspace_floats': [_i64],
+    'lc_gptq_factorize': [_p, _i64, _p, _p, _p, _i64, _p, _p],
+    'lc_gptq_invert_factor': [_p, _i64, _p, _p, _p, _i64, _p, _p],
     'lc_rope_apply': [_p, _p, _p, _i, _i64, _i, _i, _p, _p],
     'lc_silu_mul': [_p, _p, _i, _i64, _p, _p],
     'lc_rmsnorm': [_p, _p, _i, _i64, _i64, _f, _f, _p, _p],
@@ -74,7 +78,8 @@ def _load():
             raise ImportError(f'{LIB_PATH} is stale (no symbol {name}): rebuild it with '
                               '`python __graft_entry__.py`') from None
         fn.argtypes = argtypes
-        fn.restype = ctypes.c_char_p if name == 'lc_status_string' else ctypes.c_int
+        fn.restype = {'lc_status_string': ctypes.c_char_p,
+                      'lc_gptq_factor_workspace_floats': ctypes.c_int64}.get(name, ctypes.c_int)
     return lib
 
 

@@ -33,9 +33,12 @@ class GPTQ:
         self.owq = special.get('owq', False)
         self.chunk_num = special.get('chunk_num', 1)
         self.emit_codes = special.get('emit_codes', True)
-        # 'direct': one Cholesky of the index-reversed matrix + one triangular inverse;
+        # 'direct': one Cholesky of the index-reversed matrix + one triangular inverse (cuSOLVER / cuBLAS);
+        # 'native': the Cholesky by cuSOLVER, the triangular inverse blocked on 128x128 diagonal blocks with
+        #           its products on the tensor cores (lc_gptq_invert_factor; C % 128 == 0, else 'direct');
+        # 'native_full': the Cholesky blocked the same way too (lc_gptq_factorize);
         # 'reference': the reference's three factorisations (gptq.py:172-174).  Same U up to fp32 rounding.
-        self.factorization = special.get('factorization', 'direct')
+        self.factorization = special.get('factorization', 'native')
         # 'tensor': trailing update batched per 1024-column panel on tcgen05 (3-term tf32 split);
         # 'ffma': the reference's per-block update with the fp32 FFMA kernel
         self.trailing = special.get('trailing', 'tensor')
@@ -142,15 +145,46 @@ class GPTQ:
             invperm = torch.argsort(perm)
         Hp = torch.empty((C, C), dtype=torch.float32, device=H.device)
         scratch = torch.empty(4, dtype=torch.float32, device=H.device)
-        direct = self.factorization == 'direct'
+        native = self.factorization in ('native', 'native_full') and C % 128 == 0
+        direct = native or self.factorization in ('direct', 'native', 'native_full')
         L.call('lc_gptq_permute_damp', None, L.LC_F32, L.ptr(H), L.ptr(perm), 0, C, float(hscale),
                float(self.percdamp), int(direct), None, L.ptr(Hp), L.ptr(scratch), L.stream_of(H))
+        want_lo = self.trailing == 'tensor' and C % 128 == 0 and C > 1024
+        fac = {'H': H, 'perm': perm, 'invperm': invperm, 'U': None, 'U_lo': None}
+        if native:
+            # blocked Cholesky + triangular inverse with the products on the tensor cores; a matrix that
+            # is not positive definite is reported through the status word at the next check_status()
+            U = torch.empty((C, C), dtype=torch.float32, device=H.device)
+            U_lo = torch.empty_like(U) if want_lo else None
+            ws_floats = int(L.lib.lc_gptq_factor_workspace_floats(C))
+            ws = self._workspace(ws_floats, H.device)
+            status = torch.zeros(1, dtype=torch.int32, device=H.device)
+            if self.factorization == 'native_full':
+                L.call('lc_gptq_factorize', L.ptr(Hp), C, L.ptr(U), L.ptr(U_lo), L.ptr(ws), ws_floats,
+                       L.ptr(status), L.stream_of(H))
+            else:
+                # cuSOLVER returns the lower factor M column-major: the same bytes are the row-major upper
+                # factor G = M^T that the inverse reads
+                M = torch.linalg.cholesky(Hp)
+                G = M.t() if M.stride() == (1, C) else M.t().contiguous()
+                L.call('lc_gptq_invert_factor', L.ptr(G), C, L.ptr(U), L.ptr(U_lo), L.ptr(ws), ws_floats,
+                       L.ptr(status), L.stream_of(H))
+            self._pending_status.append(status)
+            fac['U'], fac['U_lo'] = U, U_lo
+            return fac
         U = self.inverse_cholesky_upper_reversed(Hp) if direct else self.inverse_cholesky_upper(Hp)
-        fac = {'H': H, 'perm': perm, 'invperm': invperm, 'U': U, 'U_lo': None}
-        if self.trailing == 'tensor' and C % 128 == 0 and C > 1024:
+        fac['U'] = U
+        if want_lo:
             fac['U_lo'] = torch.empty_like(U)
             L.call('lc_gptq_split_tf32', L.ptr(U), U.numel(), L.ptr(fac['U_lo']), L.stream_of(U))
         return fac
+
+    def _workspace(self, floats, device):
+        """Scratch of the native factorisation, kept between calls (2.4 GB at C = 11008)."""
+        ws = getattr(self, '_ws', None)
+        if ws is None or ws.numel() < floats or ws.device != device:
+            self._ws = ws = torch.empty(floats, dtype=torch.float32, device=device)
+        return ws
 
     @torch.no_grad()
     def solve(self, W, H, hscale=1.0, rows=None, factor=None):
@@ -275,7 +309,10 @@ class GPTQ:
             self._pending_status = []
             for c in codes:
                 if c != 0:
-                    raise L.LcError('lc_gptq_weight_transform_tc', c, L.status_string(c))
+                    if c == L.LC_ERR_NOT_PD:
+                        raise torch.linalg.LinAlgError('lc_gptq_factorize: the dampened Hessian is not '
+                                                       'positive definite')
+                    raise L.LcError('lc_gptq_weight_transform_tc / lc_gptq_factorize', c, L.status_string(c))
 
     @torch.no_grad()
     def free(self, name):
