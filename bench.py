@@ -273,6 +273,42 @@ class HessianTimer:
         return by_c
 
 
+def rtn_aux(hbm_peak, dev):
+    """quant_dequant GB/s of the RTN kernel on the configuration of the reference's CPU-runnable case
+    (fp32 4096x4096, W4 asymmetric, groups of 128) and on a tensor far larger than L2; raw C-ABI calls,
+    8 rotating buffers so that no launch finds its input in L2, CUDA events around 40 launches."""
+    import torch
+    from lightcompress_b200 import _lib as L
+    out = {}
+    for name, rows, cols, dt in (('rtn_w4_g128_fp32_4096x4096', 4096, 4096, torch.float32),
+                                 ('rtn_w4_g128_fp32_16384x8192', 16384, 8192, torch.float32),
+                                 ('rtn_w4_g128_bf16_16384x8192', 16384, 8192, torch.bfloat16)):
+        n_buf = 8 if rows == 4096 else 2
+        g = torch.Generator().manual_seed(1001)
+        ws = [(torch.randn(rows, cols, generator=g) * 0.02).to(dt).to(dev) for _ in range(n_buf)]
+        outs = [torch.empty_like(w) for w in ws]
+        st = L.stream_of(ws[0])
+
+        def run(i):
+            L.call('lc_rtn_int_quant', L.ptr(ws[i % n_buf]), L.lc_dtype(ws[0]), rows, cols, 128, 4, 0, None, None,
+                   L.ptr(outs[i % n_buf]), None, L.LC_CODES_NONE, None, None, st)
+        for i in range(8):
+            run(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(40):
+            run(i)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / 40 * 1e3
+        nbytes = 2 * rows * cols * ws[0].element_size()
+        gbs = nbytes / us / 1e3
+        out[name] = {'us': us, 'algorithmic_bytes': nbytes, 'gb_s': gbs, 'frac_of_measured_hbm': gbs / hbm_peak}
+        del ws, outs
+    return out
+
+
 def n_super(c):
     s = -(-c // 256)
     return s * (s + 1) // 2
@@ -333,7 +369,7 @@ def main():
         if not args.no_e2e:
             for p in block_host.parameters():
                 p.data = p.data.pin_memory()
-            x_stage = torch.empty_like(X)
+            x_stages = [torch.empty_like(X), torch.empty_like(X)]
             w_host = {n: torch.empty(rc, dtype=torch.float32).pin_memory()
                       for n, rc in zip(['q', 'k', 'v', 'o', 'gate', 'up', 'down'], LINEAR_SHAPES)}
 
@@ -343,24 +379,44 @@ def main():
             name_to_key = {'self_attn.q_proj': 'q', 'self_attn.k_proj': 'k', 'self_attn.v_proj': 'v',
                            'self_attn.o_proj': 'o', 'mlp.gate_proj': 'gate', 'mlp.up_proj': 'up',
                            'mlp.down_proj': 'down'}
+            # steps_left: steps still to run in the current (warm-up or timed) sequence; pending: the
+            # copy events of activations already on their way for the next step, and their buffer
+            e2e_state = {'steps_left': 0, 'pending': None, 'buf': 0}
+
+            def start_input_copy(buf):
+                evs = []
+                with torch.cuda.stream(copy_in):
+                    for i in range(0, n_seq, chunk):
+                        x_stages[buf][i:i + chunk].copy_(X_host[i:i + chunk], non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record(copy_in)
+                        evs.append(ev)
+                return evs
 
             def e2e_step():
-                # host -> device copies of the activations run on their own stream, chunk by chunk; the
-                # first stage of the block waits for the chunk it is about to read.  Each subset's
-                # quantised weights go back to the host on a third stream while the next stage computes
-                # (the reference's block.cuda() / block.cpu()).
+                # Host -> device copies of the activations run on their own stream, chunk by chunk, into
+                # one of two staging buffers; the first stage of the block waits for the chunk it is about
+                # to read.  While a step computes, the activations of the NEXT step of the same sequence
+                # of steps are already copied into the other buffer (a caller that streams a model's
+                # blocks through the GPU prefetches the same way); the first step of a sequence copies its
+                # own inputs, the last one prefetches nothing, so every copy lies inside the timed region.
+                # Each subset's quantised weights go back to the host on a third stream while the next
+                # stage computes (the reference's block.cuda() / block.cpu()).
                 main_s = torch.cuda.current_stream()
                 copy_in.wait_stream(main_s)
                 block = copy.deepcopy(master)
                 for p, hp in zip(block.parameters(), host_params):
                     p.data.copy_(hp, non_blocking=True)
-                evs = []
-                with torch.cuda.stream(copy_in):
-                    for i in range(0, n_seq, chunk):
-                        x_stage[i:i + chunk].copy_(X_host[i:i + chunk], non_blocking=True)
-                        ev = torch.cuda.Event()
-                        ev.record(copy_in)
-                        evs.append(ev)
+                if e2e_state['pending'] is None:
+                    e2e_state['pending'] = start_input_copy(e2e_state['buf'])
+                evs, buf = e2e_state['pending'], e2e_state['buf']
+                x_stage = x_stages[buf]
+                e2e_state['steps_left'] -= 1
+                if e2e_state['steps_left'] > 0:
+                    e2e_state['buf'] = 1 - buf
+                    e2e_state['pending'] = start_input_copy(1 - buf)
+                else:
+                    e2e_state['pending'] = None
                 mods = dict(block.named_modules())
 
                 def on_input(i):
@@ -383,11 +439,24 @@ def main():
                 return outs
             h2d = int(X_host.numel() * 2 + sum(p.numel() * 2 for p in block_host.parameters()))
             d2h = int(sum(w.numel() * 4 for w in w_host.values()))
-        n_blocks_solver = sum(-(-c // 128) for r, c in LINEAR_SHAPES)
-        # 4 Hessians, 4 diag, per linear (damp, permute H, permute W, flip, un-permute), block + trailing
-        # kernels, per linear the deploy-time fake quant (gather is torch)
+        # kernels of this library per step (torch's own kernels -- cuBLAS GEMMs of the forward, cuSOLVER
+        # potrf, SDPA, argsort, gathers -- are not counted):
+        #   Hessian launches, 4 diag; per distinct Hessian (3 x C=4096, 1 x C=11008): damp + permute,
+        #   low-part split, leaf inverse, flip, and 5 launches (2 GEMMs, 2 splits, 1 transpose) per internal
+        #   node of the recursive triangular inverse (C/128 - 1 nodes);
+        #   per linear: permute W, un-permute, deploy-time fake quant, and per 128-column block the block
+        #   kernel plus one eager GEMM (not for the last block of a 1024-column panel), per panel but the
+        #   last one lazy GEMM;
+        #   per sequence: 2 RMS norms, 2 rotary embeddings, 1 SiLU-gate.
         n_calls = -(-n_seq // bs)
-        launches = 4 * -(-n_calls // HESSIAN_BATCH) + 4 + 7 * 5 + (2 * n_blocks_solver - 7) + 7 + 3 * 7
+
+        def solver_launches(c):
+            blocks, panels = -(-c // 128), -(-c // 1024)
+            return blocks + (blocks - panels) + (panels - 1)
+        launches = (4 * -(-n_calls // HESSIAN_BATCH) + 4
+                    + sum(2 + 1 + 1 + 1 + 5 * (c // 128 - 1) for c in (HID, HID, HID, INTER))
+                    + sum(3 + solver_launches(c) for r, c in LINEAR_SHAPES)
+                    + 5 * n_calls)
     else:
         W_host = make_linear_weight().pin_memory() if not args.no_e2e else make_linear_weight()
         W = W_host.to(dev)
@@ -474,12 +543,24 @@ def main():
     # ---- end to end: host buffers in, host result out ------------------------------------------
     e2e = None
     if not args.no_e2e:
+        if args.workload == 'block':
+            e2e_state['steps_left'] = 2
         for _ in range(2):
             e2e_step()
+        if args.workload == 'block':
+            e2e_state['steps_left'] = args.steps
         e2e_ms = timed(e2e_step, args.steps) / args.steps
         e2e = {'value': 1e3 / e2e_ms, 'unit': UNIT, 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': h2d,
-               'd2h_bytes_per_step': d2h}
+               'd2h_bytes_per_step': d2h,
+               'overlap': ('copies on side streams; the activations of step s+1 are prefetched into a second '
+                           'staging buffer while step s computes (not for the first step, none after the last: '
+                           'all copies lie inside the timed region)') if args.workload == 'block' else 'none'}
     clocks = sampler.stop() if sampler else None
+
+    # ---- the other two headline kernels, timed alone (HBM-bound family 1) ----------------------
+    aux = None
+    if rank == 0 and args.workload == 'block':
+        aux = rtn_aux(hbm_peak, dev)
 
     if rank != 0:
         if world > 1:
@@ -503,6 +584,13 @@ def main():
                 'per_cols': {str(c): {'launches_per_step': d[0] / args.steps, 'launch_ms': d[1] / d[0],
                                       'tokens_per_launch': d[2] / d[0]} for c, d in hess.items()},
                 'traffic': None}
+    # DRAM bytes per 16384-token launch from the ncu captures summarised in profiles/hessian_umma_C4096.md
+    # (dram__bytes_read.sum + dram__bytes_write.sum); the bench launches the same shapes
+    ncu_traffic = {4096: 213.3e6, 11008: 3321.0e6}
+    if all(c in ncu_traffic and abs(d[2] / d[0] - 16384) < 1 for c, d in hess.items()):
+        roofline['traffic'] = sum(d[0] * ncu_traffic[c] for c, d in hess.items()) / n_l
+        roofline['traffic_source'] = 'ncu, per launch, weighted over the launch mix of the step'
+        roofline['algorithmic_bytes'] = sum(d[0] * (2.0 * 16384 * c + 8.0 * c * c) for c, d in hess.items()) / n_l
 
     line = {'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
@@ -514,6 +602,8 @@ def main():
             'roofline': roofline, 'gpu_launches': launches * args.steps, 'clocks': clocks}
     if e2e:
         line['e2e'] = e2e
+    if aux:
+        line['aux_kernels'] = aux
     if not args.no_cpu_baseline and world == 1:
         v, desc, cores, parts = (cpu_port_block() if args.workload == 'block' else cpu_port_layer(8))
         line['cpu_baseline'] = dict({'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc}, **parts)

@@ -257,11 +257,27 @@ unsigned grid_1d(int64_t items) {
 }
 
 struct Factor {
-  int64_t n;
+  int64_t n, h;   // h: pitch (and largest extent) of the scratch squares T and R
   float *A, *G, *G_lo, *Vt, *Vt_lo, *T, *T_lo, *R, *R_lo, *Vd, *Vd_lo;
+  GemmMat mG, mVt, mT, mR, mVd, mA;   // operands with their tensor maps, prepared once (mA: A with G_lo as low part)
   int32_t* status;
   cudaStream_t st;
 };
+
+int prepare_operands(Factor& f, bool with_cholesky) {
+  int rc;
+  if ((rc = gemm_mat_init(&f.mG, f.G, f.G_lo, f.n, f.n, f.n)) != LC_OK) return rc;
+  if ((rc = gemm_mat_init(&f.mVt, f.Vt, f.Vt_lo, f.n, f.n, f.n)) != LC_OK) return rc;
+  if (f.n > kB) {
+    if ((rc = gemm_mat_init(&f.mT, f.T, f.T_lo, f.h, f.h, f.h)) != LC_OK) return rc;
+    if ((rc = gemm_mat_init(&f.mR, f.R, f.R_lo, f.h, f.h, f.h)) != LC_OK) return rc;
+  }
+  if (with_cholesky) {
+    if ((rc = gemm_mat_init(&f.mVd, f.Vd, f.Vd_lo, f.n, kB, kB)) != LC_OK) return rc;
+    if ((rc = gemm_mat_init(&f.mA, f.A, f.G_lo, f.n, f.n, f.n)) != LC_OK) return rc;
+  }
+  return LC_OK;
+}
 
 int split_region(const Factor& f, const float* x, float* lo, int64_t rows, int64_t cols, int64_t ld) {
   split_region_kernel<<<grid_1d(rows * (cols >> 2)), 256, 0, f.st>>>(x, lo, rows, cols, ld);
@@ -279,19 +295,19 @@ int invert_range(const Factor& f, int64_t lo, int64_t hi) {
   if ((rc = invert_range(f, h, hi)) != LC_OK) return rc;
   const int64_t n = f.n, m1 = h - lo, m2 = hi - h;
   // T (m2 x m1) = G[lo:h, h:hi]^T Vt[lo:h, lo:h]
-  if ((rc = tf32x3_gemm_tn(f.T, m1, f.G + lo * n + h, f.G_lo + lo * n + h, n, f.Vt + lo * n + lo,
-                           f.Vt_lo + lo * n + lo, n, m2, m1, m1, 0, 1.f, kGemmBLower, f.status, f.st)) != LC_OK)
+  if ((rc = tf32x3_gemm_launch(f.T, f.h, f.mG, lo, h, f.mVt, lo, lo, m2, m1, m1, 0, 1.f, kGemmBLower, f.status,
+                               f.st)) != LC_OK)
     return rc;
-  if ((rc = split_region(f, f.T, f.T_lo, m2, m1, m1)) != LC_OK) return rc;
+  if ((rc = split_region(f, f.T, f.T_lo, m2, m1, f.h)) != LC_OK) return rc;
   // R (m2 x m2) = Vt[h:hi, h:hi]^T (upper)
   {
     const dim3 grid((unsigned)((m2 + 31) / 32), (unsigned)((m2 + 31) / 32));
-    transpose_split_kernel<<<grid, 256, 0, f.st>>>(f.Vt + h * n + h, n, f.R, f.R_lo, m2, (int)m2);
+    transpose_split_kernel<<<grid, 256, 0, f.st>>>(f.Vt + h * n + h, n, f.R, f.R_lo, f.h, (int)m2);
     LC_LAUNCH_CHECK();
   }
   // Vt[h:hi, lo:h] = -R^T T
-  if ((rc = tf32x3_gemm_tn(f.Vt + h * n + lo, n, f.R, f.R_lo, m2, f.T, f.T_lo, m1, m2, m1, m2, 0, -1.f, kGemmAUpper,
-                           f.status, f.st)) != LC_OK)
+  if ((rc = tf32x3_gemm_launch(f.Vt + h * n + lo, n, f.mR, 0, 0, f.mT, 0, 0, m2, m1, m2, 0, -1.f, kGemmAUpper,
+                               f.status, f.st)) != LC_OK)
     return rc;
   return split_region(f, f.Vt + h * n + lo, f.Vt_lo + h * n + lo, m2, m1, n);
 }
@@ -314,21 +330,17 @@ int factorize(const Factor& f) {
       if (right == 0) break;
       // G[k:k2, k2:] = V_kk^T A[k:k2, k2:]; the low part of the A panel borrows the place of the result's
       if ((rc = split_region(f, f.A + k * n + k2, f.G_lo + k * n + k2, kB, right, n)) != LC_OK) return rc;
-      if ((rc = tf32x3_gemm_tn(f.G + k * n + k2, n, f.Vd + blk, f.Vd_lo + blk, kB, f.A + k * n + k2,
-                               f.G_lo + k * n + k2, n, kB, right, kB, 0, 1.f, kGemmAUpper, f.status, f.st)) != LC_OK)
+      if ((rc = tf32x3_gemm_launch(f.G + k * n + k2, n, f.mVd, k, 0, f.mA, k, k2, kB, right, kB, 0, 1.f, kGemmAUpper,
+                                   f.status, f.st)) != LC_OK)
         return rc;
       if ((rc = split_region(f, f.G + k * n + k2, f.G_lo + k * n + k2, kB, right, n)) != LC_OK) return rc;
       // eager update of the rest of the outer block's rows
-      if (k2 < o2 &&
-          (rc = tf32x3_gemm_tn(f.A + k2 * n + k2, n, f.G + k * n + k2, f.G_lo + k * n + k2, n, f.G + k * n + k2,
-                               f.G_lo + k * n + k2, n, o2 - k2, right, kB, 1, -1.f, kGemmUpperOnly, f.status,
-                               f.st)) != LC_OK)
+      if (k2 < o2 && (rc = tf32x3_gemm_launch(f.A + k2 * n + k2, n, f.mG, k, k2, f.mG, k, k2, o2 - k2, right, kB, 1,
+                                              -1.f, kGemmUpperOnly, f.status, f.st)) != LC_OK)
         return rc;
     }
-    if (o2 < n &&
-        (rc = tf32x3_gemm_tn(f.A + o2 * n + o2, n, f.G + o * n + o2, f.G_lo + o * n + o2, n, f.G + o * n + o2,
-                             f.G_lo + o * n + o2, n, n - o2, n - o2, o2 - o, 1, -1.f, kGemmUpperOnly, f.status,
-                             f.st)) != LC_OK)
+    if (o2 < n && (rc = tf32x3_gemm_launch(f.A + o2 * n + o2, n, f.mG, o, o2, f.mG, o, o2, n - o2, n - o2, o2 - o, 1,
+                                           -1.f, kGemmUpperOnly, f.status, f.st)) != LC_OK)
       return rc;
   }
   return invert_range(f, 0, n);
@@ -388,7 +400,10 @@ extern "C" LC_API int lc_gptq_factorize(float* A, int64_t n, float* U, float* U_
   f.Vd_lo = p;
   f.status = status;
   f.st = reinterpret_cast<cudaStream_t>(stream);
-  const int rc = factorize(f);
+  f.h = h;
+  int rc = prepare_operands(f, true);
+  if (rc != LC_OK) return rc;
+  rc = factorize(f);
   if (rc != LC_OK) return rc;
   flip_upper_kernel<<<grid_1d(n * (n >> 2)), 256, 0, f.st>>>(f.Vt, n, U, U_lo);
   LC_LAUNCH_CHECK();
@@ -422,7 +437,10 @@ extern "C" LC_API int lc_gptq_invert_factor(const float* G, int64_t n, float* U,
   f.Vd = f.Vd_lo = nullptr;
   f.status = status;
   f.st = reinterpret_cast<cudaStream_t>(stream);
-  const int rc = invert_factor(f);
+  f.h = h;
+  int rc = prepare_operands(f, false);
+  if (rc != LC_OK) return rc;
+  rc = invert_factor(f);
   if (rc != LC_OK) return rc;
   flip_upper_kernel<<<grid_1d(n * (n >> 2)), 256, 0, f.st>>>(f.Vt, n, U, U_lo);
   LC_LAUNCH_CHECK();

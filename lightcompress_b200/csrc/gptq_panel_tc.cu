@@ -86,19 +86,29 @@ extern "C" LC_API int lc_gptq_weight_transform_tc(float* W, const float* U, cons
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int64_t n_groups = cols / 128;
   if (loss_rows) LC_CHECK_CUDA(cudaMemsetAsync(loss_rows, 0, rows * sizeof(float), st));
+  // operands of every update: E (k-major panel buffer) and U, prepared once
+  GemmMat E, Um;
+  {
+    int rc;
+    if ((rc = gemm_mat_init(&E, panel_hi, panel_lo, kPanel, rows, rows)) != LC_OK) return rc;
+    if ((rc = gemm_mat_init(&Um, U, U_lo, cols, cols, cols)) != LC_OK) return rc;
+  }
   for (int64_t p1 = 0; p1 < cols; p1 += kPanel) {
     const int64_t p2 = (p1 + kPanel < cols) ? p1 + kPanel : cols;
-    const bool has_right = p2 < cols;
     for (int64_t i1 = p1; i1 < p2; i1 += 128) {
+      const int k0 = (int)(i1 - p1);
+      const bool has_right = p2 < cols;
       int rc = gptq_block_launch(W, U, rows, cols, i1, 128, bits, sym, scratch_err, scales, zeros, n_groups, codes_u8,
-                                 loss_rows, st, has_right ? panel_hi : nullptr, has_right ? panel_lo : nullptr,
-                                 (int)(i1 - p1));
+                                 loss_rows, st, has_right ? panel_hi : nullptr, has_right ? panel_lo : nullptr, k0);
       if (rc != LC_OK) return rc;
-      rc = gptq_trail_launch(W, scratch_err, U, rows, cols, i1, 128, i1 + 128, st, p2);   // rest of the panel only
+      // eager update of the rest of the panel, W[:, i2:p2] -= E_block^T U[i1:i2, i2:p2]: K = 128 and at most
+      // 896 columns, where the fp32 FFMA kernel beats the fixed cost of a tensor-core launch (measured)
+      rc = gptq_trail_launch(W, scratch_err, U, rows, cols, i1, 128, i1 + 128, st, p2);
       if (rc != LC_OK) return rc;
     }
-    if (has_right) {
-      const int rc = panel_update_launch(W, panel_hi, panel_lo, U, U_lo, rows, cols, (int)p1, (int)p2, status, st);
+    if (p2 < cols) {
+      const int rc = tf32x3_gemm_launch(W + p2, cols, E, 0, 0, Um, p1, p2, rows, cols - p2, p2 - p1, 1, -1.f, 0, status,
+                                        st);
       if (rc != LC_OK) return rc;
     }
   }

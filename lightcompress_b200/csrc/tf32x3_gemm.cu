@@ -45,6 +45,7 @@ struct GemmArgs {
   float* C;
   int32_t* status;
   int64_t ldc;
+  int a_k0, a_m0, b_k0, b_n0;   // origins of the operand sub-matrices inside their tensor maps
   int M, N, K;
   int m_tiles, n_tiles;
   int beta;
@@ -120,14 +121,16 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
           const uint32_t sa = base + s * P_STAGE_BYTES;
 #pragma unroll
           for (int q = 0; q < A_ATOMS; ++q) {
-            tma_load_2d(sa + q * P_ATOM_BYTES, &maps.a_hi, w.m0 + q * ATOM_F, krow, full_bar(s));
-            tma_load_2d(sa + (A_ATOMS + q) * P_ATOM_BYTES, &maps.a_lo, w.m0 + q * ATOM_F, krow, full_bar(s));
+            tma_load_2d(sa + q * P_ATOM_BYTES, &maps.a_hi, a.a_m0 + w.m0 + q * ATOM_F, a.a_k0 + krow, full_bar(s));
+            tma_load_2d(sa + (A_ATOMS + q) * P_ATOM_BYTES, &maps.a_lo, a.a_m0 + w.m0 + q * ATOM_F, a.a_k0 + krow,
+                        full_bar(s));
           }
 #pragma unroll
           for (int q = 0; q < B_ATOMS; ++q) {
-            tma_load_2d(sa + (2 * A_ATOMS + q) * P_ATOM_BYTES, &maps.b_hi, w.n0 + q * ATOM_F, krow, full_bar(s));
-            tma_load_2d(sa + (2 * A_ATOMS + B_ATOMS + q) * P_ATOM_BYTES, &maps.b_lo, w.n0 + q * ATOM_F, krow,
+            tma_load_2d(sa + (2 * A_ATOMS + q) * P_ATOM_BYTES, &maps.b_hi, a.b_n0 + w.n0 + q * ATOM_F, a.b_k0 + krow,
                         full_bar(s));
+            tma_load_2d(sa + (2 * A_ATOMS + B_ATOMS + q) * P_ATOM_BYTES, &maps.b_lo, a.b_n0 + w.n0 + q * ATOM_F,
+                        a.b_k0 + krow, full_bar(s));
           }
           issued = n + 1;
         }
@@ -252,25 +255,59 @@ int encode_f32_2d(CUtensorMap* m, const float* base, int64_t inner, int64_t oute
   return LC_OK;
 }
 
+// SM count and the kernel's shared-memory attribute, once per device
+int device_setup(int* sms_out) {
+  static int sms_of[64] = {0};
+  int dev = 0;
+  LC_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return LC_ERR_ARG;
+  if (sms_of[dev] == 0) {
+    int sms = 0;
+    LC_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    LC_CHECK_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+    sms_of[dev] = sms;
+  }
+  *sms_out = sms_of[dev];
+  return LC_OK;
+}
+
 }  // namespace
 
-int tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, int64_t lda, const float* B_hi,
-                   const float* B_lo, int64_t ldb, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
-                   int32_t* status, cudaStream_t st) {
-  if (M <= 0 || N <= 0 || K <= 0) return LC_OK;
-  if (K % PBK != 0 || M % 4 != 0 || N % 4 != 0 || lda % 4 != 0 || ldb % 4 != 0 || ldc % 4 != 0) return LC_ERR_SHAPE;
-  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return LC_ERR_SHAPE;
-  if (!aligned16(C) || !aligned16(A_hi) || !aligned16(A_lo) || !aligned16(B_hi) || !aligned16(B_lo)) return LC_ERR_ALIGN;
-  GemmMaps maps;
+int gemm_mat_init(GemmMat* m, const float* hi, const float* lo, int64_t k_extent, int64_t mn_extent, int64_t ld) {
+  if (k_extent <= 0 || mn_extent <= 0 || ld % 4 != 0 || ld < mn_extent) return LC_ERR_SHAPE;
+  if (!aligned16(hi) || !aligned16(lo)) return LC_ERR_ALIGN;
   int rc;
-  if ((rc = encode_f32_2d(&maps.a_hi, A_hi, M, K, lda)) != LC_OK) return rc;
-  if ((rc = encode_f32_2d(&maps.a_lo, A_lo, M, K, lda)) != LC_OK) return rc;
-  if ((rc = encode_f32_2d(&maps.b_hi, B_hi, N, K, ldb)) != LC_OK) return rc;
-  if ((rc = encode_f32_2d(&maps.b_lo, B_lo, N, K, ldb)) != LC_OK) return rc;
+  if ((rc = encode_f32_2d(&m->map_hi, hi, mn_extent, k_extent, ld)) != LC_OK) return rc;
+  if ((rc = encode_f32_2d(&m->map_lo, lo, mn_extent, k_extent, ld)) != LC_OK) return rc;
+  m->k_extent = k_extent;
+  m->mn_extent = mn_extent;
+  return LC_OK;
+}
+
+int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, int64_t a_m0, const GemmMat& B,
+                       int64_t b_k0, int64_t b_n0, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
+                       int32_t* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return LC_OK;
+  if (K % PBK != 0 || M % 4 != 0 || N % 4 != 0 || ldc % 4 != 0 || a_m0 % 4 != 0 || b_n0 % 4 != 0) return LC_ERR_SHAPE;
+  if (a_k0 < 0 || a_m0 < 0 || b_k0 < 0 || b_n0 < 0 || a_k0 + K > A.k_extent || a_m0 + M > A.mn_extent ||
+      b_k0 + K > B.k_extent || b_n0 + N > B.mn_extent)
+    return LC_ERR_SHAPE;
+  if (A.k_extent > (1 << 30) || A.mn_extent > (1 << 30) || B.k_extent > (1 << 30) || B.mn_extent > (1 << 30))
+    return LC_ERR_SHAPE;
+  if (!aligned16(C)) return LC_ERR_ALIGN;
+  GemmMaps maps;
+  maps.a_hi = A.map_hi;
+  maps.a_lo = A.map_lo;
+  maps.b_hi = B.map_hi;
+  maps.b_lo = B.map_lo;
   GemmArgs a;
   a.C = C;
   a.status = status;
   a.ldc = ldc;
+  a.a_k0 = (int)a_k0;
+  a.a_m0 = (int)a_m0;
+  a.b_k0 = (int)b_k0;
+  a.b_n0 = (int)b_n0;
   a.M = (int)M;
   a.N = (int)N;
   a.K = (int)K;
@@ -279,15 +316,23 @@ int tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, 
   a.beta = beta ? 1 : 0;
   a.sign = sign;
   a.flags = flags;
-  int dev = 0, sms = 0;
-  LC_CHECK_CUDA(cudaGetDevice(&dev));
-  LC_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int sms = 0, rc;
+  if ((rc = device_setup(&sms)) != LC_OK) return rc;
   const int tiles = a.m_tiles * a.n_tiles;
-  // per-device attribute; setting it on every call keeps multi-device processes correct
-  LC_CHECK_CUDA(cudaFuncSetAttribute(tf32x3_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
   tf32x3_gemm_kernel<<<tiles < sms ? tiles : sms, kThreads, P_SMEM_BYTES, st>>>(maps, a);
   LC_LAUNCH_CHECK();
   return LC_OK;
+}
+
+int tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, int64_t lda, const float* B_hi,
+                   const float* B_lo, int64_t ldb, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
+                   int32_t* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return LC_OK;
+  GemmMat A, B;
+  int rc;
+  if ((rc = gemm_mat_init(&A, A_hi, A_lo, K, M, lda)) != LC_OK) return rc;
+  if ((rc = gemm_mat_init(&B, B_hi, B_lo, K, N, ldb)) != LC_OK) return rc;
+  return tf32x3_gemm_launch(C, ldc, A, 0, 0, B, 0, 0, M, N, K, beta, sign, flags, status, st);
 }
 
 }  // namespace lc

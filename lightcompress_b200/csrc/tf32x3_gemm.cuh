@@ -1,6 +1,7 @@
 // Internal interface of the three-term tf32 tensor-core GEMM (tf32x3_gemm.cu).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -11,9 +12,26 @@ constexpr int kGemmUpperOnly = 1;   // C is a diagonal-aligned square: tiles ent
 constexpr int kGemmBLower = 2;      // B[k][n] == 0 for k < n: a tile's k range starts at its first column
 constexpr int kGemmAUpper = 4;      // A[k][m] == 0 for k > m: a tile's k range ends after its last row
 
-// C[M][N] (pitch ldc) = beta * C + sign * A^T B; A = A_hi + A_lo: [K][M] (pitch lda), B = B_hi + B_lo:
-// [K][N] (pitch ldb).  K % 16 == 0; M, N and the pitches multiples of 4; pointers 16-byte aligned.
-// x_hi is the fp32 value itself (the tensor core truncates it), x_lo = x - truncate_tf32(x).
+// A k-row operand matrix X = hi + lo, [k_extent][mn_extent] with pitch ld, and its two tensor maps.
+// Prepared once, then any sub-matrix of it can be an operand (origin given per launch), which keeps
+// tensor-map encoding out of loops that launch hundreds of small products.
+struct GemmMat {
+  CUtensorMap map_hi, map_lo;
+  int64_t k_extent = 0, mn_extent = 0;
+};
+// hi, lo: 16-byte aligned, ld % 4 == 0.  x_hi is the fp32 value itself (the tensor core truncates it),
+// x_lo = x - truncate_tf32(x).
+int gemm_mat_init(GemmMat* m, const float* hi, const float* lo, int64_t k_extent, int64_t mn_extent, int64_t ld);
+
+// C[M][N] (pitch ldc) = beta * C + sign * A'^T B', A' = A[a_k0 : a_k0 + K, a_m0 : a_m0 + M],
+// B' = B[b_k0 : b_k0 + K, b_n0 : b_n0 + N].  K % 16 == 0; M, N, ldc and the origins multiples of 4.
+// Rows / columns of a tile beyond M / N read whatever follows in the operand matrix (or zeros beyond
+// its extent) and are never stored.
+int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, int64_t a_m0, const GemmMat& B,
+                       int64_t b_k0, int64_t b_n0, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
+                       int32_t* status, cudaStream_t st);
+
+// One-off product: prepares both operands and launches.
 int tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, int64_t lda, const float* B_hi,
                    const float* B_lo, int64_t ldb, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
                    int32_t* status, cudaStream_t st);

@@ -1,7 +1,7 @@
 """Small, self-terminating workloads of each kernel family, sized for profiler captures
 (inputs larger than the 126 MB L2, a few hundred MB on the device, a handful of launches).
 
-    python -m lightcompress_b200.profile_cases hessian|rtn|fp8|gptq [--launches N]
+    python -m lightcompress_b200.profile_cases hessian|hessian_wide|rtn|fp8|gptq|factor|block_ops [--launches N]
 """
 import argparse
 
@@ -24,6 +24,48 @@ def hessian(n):
     for T1 in (2048,):
         for _ in range(n):
             L.call('lc_hessian_accum', L.ptr(X), T1, C, L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
+    torch.cuda.synchronize()
+
+
+def hessian_wide(n):
+    """The down_proj width: C = 11008, 16384 tokens per launch."""
+    C, T = 11008, 16384
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(T, C, generator=g).to(torch.bfloat16).cuda()
+    H = torch.zeros(C, C, device='cuda')
+    status = torch.zeros(1, dtype=torch.int32, device='cuda')
+    for _ in range(n):
+        L.call('lc_hessian_accum', L.ptr(X), T, C, L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+
+
+def factor(n):
+    """Blocked triangular inverse (and the tensor-core GEMM under it) on a 4096 x 4096 Hessian."""
+    C = 4096
+    g = torch.Generator().manual_seed(6)
+    X = torch.randn(2 * C, C, generator=g).cuda()
+    H = X.t() @ X
+    solver = GPTQ(IntegerQuantizer(4, False, 'per_group', group_size=128), {'actorder': True})
+    for _ in range(n):
+        solver.factorize(H, 0.5)
+    solver.check_status()
+    torch.cuda.synchronize()
+
+
+def block_ops(n):
+    """RMS norm, rotary embedding and SiLU-gate on one 2048-token sequence of Llama-2-7B width."""
+    from . import block_ops as B
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(8, 2048, 4096, generator=g).to(torch.bfloat16).cuda()
+    w = torch.ones(4096, dtype=torch.bfloat16, device='cuda')
+    q = x.view(8, 2048, 32, 128).transpose(1, 2)
+    cs = torch.randn(8, 2048, 128, generator=g).to(torch.bfloat16).cuda()
+    gate = torch.randn(8 * 2048, 11008, generator=g).to(torch.bfloat16).cuda()
+    for _ in range(n):
+        B._rms_raw(x, w, 1e-5)
+        B.rope_apply_one(q, cs, cs)
+        B.silu_mul(gate, gate)
     torch.cuda.synchronize()
 
 
@@ -69,8 +111,9 @@ def gptq(n):
 
 if __name__ == '__main__':
     ap = argparse.ArgumentParser()
-    ap.add_argument('case', choices=['hessian', 'rtn', 'fp8', 'gptq'])
+    ap.add_argument('case', choices=['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'factor', 'block_ops'])
     ap.add_argument('--launches', type=int, default=3)
     a = ap.parse_args()
-    {'hessian': hessian, 'rtn': rtn, 'fp8': fp8, 'gptq': gptq}[a.case](a.launches)
+    {'hessian': hessian, 'hessian_wide': hessian_wide, 'rtn': rtn, 'fp8': fp8, 'gptq': gptq, 'factor': factor,
+     'block_ops': block_ops}[a.case](a.launches)
     print('done', a.case)
