@@ -309,6 +309,64 @@ def rtn_aux(hbm_peak, dev):
     return out
 
 
+def run_secondary(args):
+    """`--workload awq`: AWQ scale + clip search of one Llama-2-7B-shape block on 128 x 512 calibration
+    tokens in one batch (W4 asym g128, trans_version v2, clip_version v1).  `--workload moe`: FP8 e4m3
+    fake quant of a 64-expert MoE layer (per-channel weights once, per-token activations per forward).
+    Device-resident inputs, CUDA events, one JSON line with the configuration's own metric."""
+    import torch
+    import lightcompress_b200 as lc
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    hbm_peak = peaks()[0]
+    if args.workload == 'awq':
+        from lightcompress_b200.awq import Awq
+        block_host, kwargs_host = make_block(seq_len=512)
+        kwargs = kwargs_to(kwargs_host, dev)
+        g = torch.Generator().manual_seed(3001)
+        X = torch.randn(NS, 512, HID, generator=g)
+        X[:, :, torch.randperm(HID, generator=g)[:41]] *= 20
+        X = X.to(torch.bfloat16).to(dev)
+        master = copy.deepcopy(block_host).to(dev)
+        wq = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
+        awq = Awq(wq, {'trans': True, 'trans_version': 'v2', 'weight_clip': True, 'clip_version': 'v1'},
+                  calib_seq_len=512)
+
+        def step():
+            return awq.block_transform(copy.deepcopy(master), X, kwargs)
+        metric, unit = 'AWQ W4 g128 scale+clip search blocks/sec', 'blocks/s'
+        workload = ('one Llama-2-7B-shape decoder block, AWQ W4 asym g128, 20-point scale grid on 4 subsets + clip '
+                    'search on 5 linears, 128x512 calibration tokens in one batch')
+    else:
+        from lightcompress_b200.moe_fp8 import Fp8FakeQuantMoE
+        g = torch.Generator().manual_seed(5001)
+        x = torch.randn(16384, 2048, generator=g).to(torch.bfloat16).to(dev)
+        moe = Fp8FakeQuantMoE(device=dev)
+        pristine = [t.clone() for t in (moe.w_gate, moe.w_up, moe.w_down, moe.s_gate, moe.s_up, moe.s_down)]
+
+        def step():
+            moe.w_gate, moe.w_up, moe.w_down, moe.s_gate, moe.s_up, moe.s_down = pristine
+            moe.quantize_weights()
+            return moe.forward(x)
+        metric, unit = 'FP8 e4m3 fake-quant MoE layer passes/sec (weights quantised + one forward)', 'passes/s'
+        workload = ('64 routed experts (1408 x 2048) + shared MLP, top-6, 16384 tokens, e4m3 per-channel weights, '
+                    'per-token dynamic activations')
+    for _ in range(max(1, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({'metric': metric, 'value': 1e3 / ms, 'unit': unit, 'n_gpus': 1, 'steps': args.steps,
+                      'warmup': args.warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
+                      'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+                      'config': {'workload': workload, 'name': args.workload}, 'hbm_peak_gbs': hbm_peak}))
+
+
 def n_super(c):
     s = -(-c // 256)
     return s * (s + 1) // 2
@@ -320,7 +378,7 @@ def main():
     ap.add_argument('--steps', type=int, default=3)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--workload', default='block', choices=['block', 'layer'])
+    ap.add_argument('--workload', default='block', choices=['block', 'layer', 'awq', 'moe'])
     ap.add_argument('--calib-bs', type=int, default=1,
                     help='sequences per block-forward call (calib.bs of the reference config; block workload)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -329,6 +387,11 @@ def main():
     rank = int(os.environ.get('RANK', 0))
     local_rank = int(os.environ.get('LOCAL_RANK', 0))
     world = int(os.environ.get('WORLD_SIZE', 1))
+    if args.workload in ('awq', 'moe'):
+        # secondary configurations (AWQ block search, FP8 MoE fake quant): one GPU, their own metric
+        if rank == 0:
+            run_secondary(args)
+        return
     if args.impl == 'reference':
         run_reference(args, rank)
         return

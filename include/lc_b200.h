@@ -87,6 +87,18 @@ int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int6
                      void* fake_out, void* codes_out, int code_fmt, void* scales_out,
                      void* zeros_out, lc_stream_t stream);
 
+/* MSE range search (calib_algo 'mse'): BaseQuantizer.get_mse_range with the integer quantizer's
+ * get_qparams and quant_dequant inside its loop (llmc/compression/quantization/quant.py:147-205,
+ * :544-558, :698-716).  For each group of `group` elements along cols (0 = the whole row) the range
+ * [min, max] of the group is shrunk by p = 1 - i / mse_grid for i < int(maxshrink * mse_grid), always
+ * from the best range found so far (the reference shrinks in place through views), and the range
+ * with the smallest sum |qdq(x) - x|^norm (strict <) is written to min_out / max_out (fp32, one value
+ * per group: the reference converts the tensor with .float() first).  Reference defaults:
+ * maxshrink 0.8, mse_grid 100, norm 2.4.  Group lengths: 128, 256, 512, 1024, 2048. */
+int lc_rtn_mse_range(const void* in, int dtype, int64_t rows, int64_t cols, int64_t group, int bits, int sym,
+                     double maxshrink, int mse_grid, float norm, float* min_out, float* max_out,
+                     lc_stream_t stream);
+
 /* FP8 e4m3 per-row (per_channel weights / per_token activations) quant / dequant.
  * Replaces FloatQuantizer.get_tensor_qparams, quant, dequant, fake_quant_weight_dynamic,
  * fake_quant_act_dynamic and real_quant_weight_dynamic with use_qtorch (quant.py:1042-1080,

@@ -52,6 +52,7 @@ SIGNATURES = {
     'lc_gptq_factor_workspace_floats': [_i64],
     'lc_gptq_factorize': [_p, _i64, _p, _p, _p, _i64, _p, _p],
     'lc_gptq_invert_factor': [_p, _i64, _p, _p, _p, _i64, _p, _p],
+    'lc_rtn_mse_range': [_p, _i, _i64, _i64, _i64, _i, _i, _d, _i, _f, _p, _p, _p],
     'lc_rope_apply': [_p, _p, _p, _i, _i64, _i, _i, _p, _p],
     'lc_silu_mul': [_p, _p, _i, _i64, _p, _p],
     'lc_rmsnorm': [_p, _p, _i, _i64, _i64, _f, _f, _p, _p],

@@ -4,9 +4,9 @@
 names of llmc/compression/quantization/quant.py (BaseQuantizer :48-103, IntegerQuantizer
 :660-959, FloatQuantizer :962-1228) so that the algorithm classes and replacement modules that
 call them work unchanged, but every method body is one launch of a fused sm_100a kernel through
-the C ABI.  Configurations outside the accelerated path (calib_algo other than 'minmax',
-per_tensor / per_head / per_block granularity, round_zp=False, mixed-precision index args)
-raise NotImplementedError: there is no fallback.
+the C ABI.  Configurations outside the accelerated path (calib_algo other than 'minmax' and,
+for integer weights, 'mse'; per_tensor / per_head / per_block granularity, round_zp=False,
+mixed-precision index args) raise NotImplementedError: there is no fallback.
 """
 import torch
 
@@ -31,11 +31,14 @@ class BaseQuantizer(object):
         elif granularity == 'per_block':
             self.block_size = kwargs['block_size']
         self.round_zp = kwargs.get('round_zp', True)
+        self.mse_b_num = kwargs.get('mse_b_num', 1)
+        self.maxshrink = kwargs.get('maxshrink', 0.8)
+        self.mse_grid = kwargs.get('mse_grid', 100)
         self.ste = kwargs.get('ste', False)
         self.ste_all = bool(kwargs.get('ste_all', False))
 
-    def _check_supported(self):
-        if self.calib_algo != 'minmax':
+    def _check_supported(self, allow_mse=False):
+        if self.calib_algo != 'minmax' and not (allow_mse and self.calib_algo == 'mse'):
             raise NotImplementedError(f"calib_algo '{self.calib_algo}' is outside the B200 hot path")
         if self.granularity not in _INT_GRANS:
             raise NotImplementedError(f"granularity '{self.granularity}' is outside the B200 hot path")
@@ -88,7 +91,7 @@ class IntegerQuantizer(BaseQuantizer):
     # ---- one fused launch ------------------------------------------------------------------
     def _launch(self, t2d, group, scales_in=None, zeros_in=None, fake=False, codes=L.LC_CODES_NONE,
                 params=False):
-        self._check_supported()
+        self._check_supported(allow_mse=scales_in is not None)
         L.require_cuda(t2d, scales_in, zeros_in)
         rows, cols = t2d.shape
         g = group if group else cols
@@ -122,8 +125,60 @@ class IntegerQuantizer(BaseQuantizer):
     def _code_fmt(self):
         return L.LC_CODES_I8 if self.bit == 8 else L.LC_CODES_I32
 
+    # ---- calib_algo 'mse' (quant.py:147-205) --------------------------------------------------
+    def get_mse_range(self, tensor, norm=2.4, bs=256):
+        """(min, max) of the grouped tensor after the shrink-grid search, fp32, one value per group:
+        one launch of lc_rtn_mse_range (the reference: about a dozen tensor ops per grid step)."""
+        if self.quant_type != 'int-quant':
+            raise NotImplementedError('the MSE range kernel covers the integer quantizer')
+        self._check_supported(allow_mse=True)
+        L.require_cuda(tensor)
+        if tensor.shape[0] % self.mse_b_num:
+            raise AssertionError('Batch number must be divisible by tensor.shape[0],')
+        t, t2d = _as_2d(tensor)
+        rows, cols = t2d.shape
+        mn = torch.empty((rows, 1), dtype=torch.float32, device=t.device)
+        mx = torch.empty((rows, 1), dtype=torch.float32, device=t.device)
+        L.call('lc_rtn_mse_range', L.ptr(t2d), L.lc_dtype(t2d), rows, cols, 0, int(self.bit), int(self.sym),
+               float(self.maxshrink), int(self.mse_grid), float(norm), L.ptr(mn), L.ptr(mx), L.stream_of(t2d))
+        return mn, mx
+
+    def get_tensor_range(self, tensor, args={}):
+        """Range of an already grouped tensor (quant.py:124-132)."""
+        if self.calib_algo == 'mse':
+            return self.get_mse_range(tensor)
+        raise NotImplementedError("get_tensor_range is only a separate step for calib_algo 'mse'; "
+                                  'the minmax range is fused into the quantisation kernels')
+
+    def get_qparams(self, tensor_range, device):
+        """scales / zeros from a (min, max) pair (quant.py:544-558): a handful of ops on one value per
+        group, in the range's dtype."""
+        mn, mx = tensor_range
+        qmin, qmax = self.qmin.to(device), self.qmax.to(device)
+        if self.sym:
+            scales = torch.maximum(mx.abs(), mn.abs()).clamp(min=1e-5) / qmax
+            return scales, torch.tensor(0.0), qmax, qmin
+        scales = (mx - mn).clamp(min=1e-5) / (qmax - qmin)
+        zeros = (qmin - torch.round(mn / scales)).clamp(qmin, qmax)
+        return scales, zeros, qmax, qmin
+
+    def _mse_params(self, tensor):
+        grouped = self.reshape_tensor(tensor if tensor.is_contiguous() else tensor.contiguous())
+        scales, zeros, qmax, qmin = self.get_qparams(self.get_mse_range(grouped), tensor.device)
+        return grouped, scales, zeros, qmax, qmin
+
+    def _fake_mse(self, weight):
+        # fp32 parameters make the reference's quant / dequant ops run in fp32 on the promoted tensor;
+        # the result returns to the weight's dtype (quant.py:832-868)
+        grouped, scales, zeros, _, _ = self._mse_params(weight)
+        g32 = grouped.float()
+        fake, _, _, _ = self._launch(g32, g32.shape[-1], scales, None if self.sym else zeros, fake=True)
+        return fake.reshape(weight.shape).to(weight.dtype)
+
     # ---- reference API ---------------------------------------------------------------------
     def get_tensor_qparams(self, tensor, args={}):
+        if self.calib_algo == 'mse':
+            return self._mse_params(tensor)
         t, t2d = _as_2d(tensor)
         group = self._group_len(t.shape[-1])
         _, _, s, z = self._launch(t2d, group, params=True)
@@ -160,6 +215,8 @@ class IntegerQuantizer(BaseQuantizer):
 
     def fake_quant_weight_dynamic(self, weight, args={}):
         self._reject_args(args)
+        if self.calib_algo == 'mse':
+            return self._fake_mse(weight)
         t, t2d = _as_2d(weight)
         fake, _, _, _ = self._launch(t2d, self._group_len(t.shape[-1]), fake=True)
         return fake.reshape(t.shape)

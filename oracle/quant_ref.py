@@ -1,7 +1,7 @@
 """Oracle restatement of the reference quantizer arithmetic (test infrastructure).
 
 Follows llmc/compression/quantization/quant.py:
-  reshape_tensor :611-641, get_minmax_range :134-145, get_qparams :544-558,
+  reshape_tensor :611-641, get_minmax_range :134-145, get_mse_range :147-205, get_qparams :544-558,
   IntegerQuantizer.quant/dequant/quant_dequant :698-716,
   fake_quant_weight_dynamic :832-868, real_quant_weight_dynamic :915-952,
   fake_quant_act_dynamic :753-782, FloatQuantizer :963-1002, :1042-1080.
@@ -70,6 +70,55 @@ def int_fake_quant_static(w, s, z, bit, sym, granularity, group_size=None):
     """fake_quant_weight_static (quant.py:784-830) without the optional args."""
     qmin, qmax = int_range(bit, sym)
     g = group_view(w, granularity, group_size)
+    out = int_dequant(int_quant(g, s, z, qmax, qmin), s, z)
+    return out.reshape(w.shape).to(w.dtype)
+
+
+def int_qparams_from_range(mn, mx, bit, sym):
+    """get_qparams on a given (min, max) (quant.py:544-558, round_zp=True)."""
+    qmin, qmax = int_range(bit, sym)
+    qmin, qmax = qmin.to(mn.device), qmax.to(mn.device)
+    if sym:
+        a = torch.max(mx.abs(), mn.abs()).clamp(min=1e-5)
+        return a / qmax, torch.tensor(0.0), qmax, qmin
+    s = (mx - mn).clamp(min=1e-5) / (qmax - qmin)
+    z = (qmin - torch.round(mn / s)).clamp(qmin, qmax)
+    return s, z, qmax, qmin
+
+
+def mse_range(g, bit, sym, maxshrink=0.8, mse_grid=100, norm=2.4):
+    """get_mse_range (quant.py:147-205) on a grouped tensor (G, group); returns fp32 (min, max), (G, 1).
+    The reference keeps its best range in the very tensors it shrinks from (views of min_val /
+    max_val written in place), so step i shrinks the best range found so far; stated here with
+    explicit copies."""
+    t = g.float()
+    cur_min = t.amin(dim=-1, keepdim=True)
+    cur_max = t.amax(dim=-1, keepdim=True)
+    best = torch.full([t.shape[0]], float('inf'), device=t.device)
+    for i in range(int(maxshrink * mse_grid)):
+        p = 1 - i / mse_grid
+        xmin, xmax = p * cur_min, p * cur_max
+        s, z, qmax, qmin = int_qparams_from_range(xmin, xmax, bit, sym)
+        q = int_dequant(int_quant(t, s, z, qmax, qmin), s, z)
+        q -= t
+        q.abs_()
+        q.pow_(norm)
+        err = torch.sum(q, 1)
+        better = err < best
+        if torch.any(better):
+            best[better] = err[better]
+            cur_min, cur_max = cur_min.clone(), cur_max.clone()
+            cur_min[better] = xmin[better]
+            cur_max[better] = xmax[better]
+    return cur_min, cur_max
+
+
+def int_fake_quant_mse(w, bit, sym, granularity, group_size=None, **kw):
+    """fake_quant_weight_dynamic with calib_algo 'mse' (quant.py:689-696, :832-868): fp32 range and
+    qparams, the quant / dequant ops promote the tensor to fp32, the result returns to w's dtype."""
+    g = group_view(w, granularity, group_size)
+    mn, mx = mse_range(g, bit, sym, **kw)
+    s, z, qmax, qmin = int_qparams_from_range(mn, mx, bit, sym)
     out = int_dequant(int_quant(g, s, z, qmax, qmin), s, z)
     return out.reshape(w.shape).to(w.dtype)
 

@@ -97,6 +97,26 @@ def make_rtn(rq, out_dir):
     print('rtn_int.pt', len(cases), 'cases')
 
 
+def make_rtn_mse(rq, out_dir):
+    """calib_algo 'mse': the searched ranges (get_tensor_range) and the fake-quantised weight."""
+    gen = torch.Generator().manual_seed(1002)
+    cases = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        for sym in (False, True):
+            for gran, gs in (('per_group', 128), ('per_channel', None)):
+                w = _rtn_inputs(gen, dtype, 12, 256 if gs is None else 384)
+                w[6, :128] += torch.randn(128, generator=gen) * 0.3 * (torch.rand(128, generator=gen) > 0.97)
+                kw = {'group_size': gs} if gs else {}
+                qz = rq.IntegerQuantizer(4, sym, gran, calib_algo='mse', **kw)
+                mn, mx = qz.get_tensor_range(qz.reshape_tensor(w.clone()))
+                fq = qz.fake_quant_weight_dynamic(w.clone())
+                key = f'{str(dtype)[6:]}_{"sym" if sym else "asym"}_{gran}_{gs}'
+                cases[key] = dict(w=w, bit=4, sym=sym, granularity=gran, group_size=gs, min=mn.clone(),
+                                  max=mx.clone(), fake=fq)
+    torch.save(cases, os.path.join(out_dir, 'rtn_mse.pt'))
+    print('rtn_mse.pt', len(cases), 'cases')
+
+
 def make_fp8(rq, out_dir):
     rq.float_quantize = lambda x, e, m, rounding: x.to(torch.float8_e4m3fn).float()
     gen = torch.Generator().manual_seed(5001)
@@ -281,6 +301,7 @@ if __name__ == '__main__':
     rq, rg = _import_reference(ref_root)
     torch.set_num_threads(1)
     make_rtn(rq, out_dir)
+    make_rtn_mse(rq, out_dir)
     make_gptq(rq, rg, out_dir)
     make_fp8(rq, out_dir)
     make_awq(rq, out_dir)

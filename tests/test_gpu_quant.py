@@ -134,6 +134,62 @@ def test_rtn_full_size_roundtrip_property():
     assert float((fake - w).abs().max()) <= float(s.max()) * 0.5 + 1e-7
 
 
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize('sym', [False, True])
+@pytest.mark.parametrize('gran,gs,shape', [('per_group', 128, (256, 1024)), ('per_channel', None, (192, 512)),
+                                           ('per_channel', None, (64, 2048))])
+def test_mse_range_matches_oracle_on_the_gpu(dtype, sym, gran, gs, shape):
+    """lc_rtn_mse_range against the oracle's chain of torch ops run on the same GPU: the same powf, the
+    same association of the group sums, so ranges and fake-quantised weights are equal bit for bit."""
+    from lightcompress_b200 import IntegerQuantizer
+    g = torch.Generator().manual_seed(shape[0] + shape[1])
+    w = torch.randn(*shape, generator=g) * 0.02
+    w += torch.randn(*shape, generator=g) * 0.2 * (torch.rand(*shape, generator=g) > 0.98)   # outliers worth clipping
+    w[0] = 0.0
+    w = w.to(dtype).cuda()
+    kw = {'group_size': gs} if gs else {}
+    qz = IntegerQuantizer(4, sym, gran, calib_algo='mse', **kw)
+    grouped = quant_ref.group_view(w, gran, gs)
+    mn, mx = qz.get_tensor_range(qz.reshape_tensor(w))
+    rmn, rmx = quant_ref.mse_range(grouped, 4, sym)
+    frac = float(((mn != rmn) | (mx != rmx)).float().mean())
+    shrunk = float((rmx != grouped.float().amax(-1, keepdim=True)).float().mean())
+    print(f'{dtype} sym={sym} {gran}: {frac:.4%} of the ranges differ; {shrunk:.1%} of the groups were shrunk')
+    assert shrunk > 0.2
+    assert frac == 0.0
+    fake = qz.fake_quant_weight_dynamic(w)
+    assert fake.dtype == w.dtype
+    assert torch.equal(fake, quant_ref.int_fake_quant_mse(w, 4, sym, gran, gs))
+    t, s, z, qmax, qmin = qz.get_tensor_qparams(w)
+    rs, rz, _, _ = quant_ref.int_qparams_from_range(rmn, rmx, 4, sym)
+    assert torch.equal(s, rs) and (sym or torch.equal(z, rz)) and s.dtype == torch.float32
+
+
+def test_mse_range_against_the_reference_golden(golden):
+    """Against the reference's own CPU result: CPU and GPU differ in powf and in the order of the
+    group sums, which can move a near-tie of the error curve to a neighbouring grid step."""
+    from lightcompress_b200 import IntegerQuantizer
+    n = bad = 0
+    for key, c in golden('rtn_mse.pt').items():
+        kw = {'group_size': c['group_size']} if c['group_size'] else {}
+        if c['granularity'] == 'per_channel' and c['w'].shape[-1] % 128:
+            continue
+        qz = IntegerQuantizer(c['bit'], c['sym'], c['granularity'], calib_algo='mse', **kw)
+        w = c['w'].cuda()
+        mn, mx = qz.get_tensor_range(qz.reshape_tensor(w))
+        diff = (mn.cpu() != c['min']) | (mx.cpu() != c['max'])
+        n += diff.numel()
+        bad += int(diff.sum())
+        fake = qz.fake_quant_weight_dynamic(w).cpu()
+        # where the range agrees the fake-quantised group agrees bit for bit
+        g_fake = quant_ref.group_view(fake, c['granularity'], c['group_size'])
+        g_ref = quant_ref.group_view(c['fake'], c['granularity'], c['group_size'])
+        same = ~diff.view(-1)
+        assert torch.equal(g_fake[same], g_ref[same]), key
+    print(f'mse ranges vs the CPU reference: {bad} of {n} groups on another grid step')
+    assert n > 0 and bad <= 0.02 * n
+
+
 def test_fp8_matches_reference_golden_and_oracle(golden):
     from lightcompress_b200 import FloatQuantizer
     for key, c in golden('fp8_e4m3.pt').items():

@@ -27,6 +27,19 @@ def test_rtn_int_oracle_matches_reference(golden):
                 _eq(z, c['zeros'])
 
 
+def test_rtn_mse_oracle_matches_reference(golden):
+    """calib_algo 'mse': searched ranges (including the reference's in-place compounding of accepted
+    shrinks) and the fake-quantised weight."""
+    cases = golden('rtn_mse.pt')
+    assert len(cases) == 8
+    for key, c in cases.items():
+        g = quant_ref.group_view(c['w'], c['granularity'], c['group_size'])
+        mn, mx = quant_ref.mse_range(g, c['bit'], c['sym'])
+        _eq(mn, c['min'])
+        _eq(mx, c['max'])
+        _eq(quant_ref.int_fake_quant_mse(c['w'], c['bit'], c['sym'], c['granularity'], c['group_size']), c['fake'])
+
+
 def test_fp8_oracle_matches_reference_with_substituted_rounding(golden):
     for key, c in golden('fp8_e4m3.pt').items():
         assert c['pinned'] is False       # qtorch is not vendored: parity unpinned for the rounding call
