@@ -109,6 +109,7 @@ def kwargs_to(kwargs, dev):
     return out
 
 
+LINEAR_KEYS = ['q', 'k', 'v', 'o', 'gate', 'up', 'down']
 LINEAR_SHAPES = [(HID, HID)] * 4 + [(INTER, HID)] * 2 + [(HID, INTER)]   # (rows, cols) of q,k,v,o,gate,up,down
 
 
@@ -434,7 +435,7 @@ def main():
                 p.data = p.data.pin_memory()
             x_stages = [torch.empty_like(X), torch.empty_like(X)]
             w_host = {n: torch.empty(rc, dtype=torch.float32).pin_memory()
-                      for n, rc in zip(['q', 'k', 'v', 'o', 'gate', 'up', 'down'], LINEAR_SHAPES)}
+                      for n, rc in zip(LINEAR_KEYS, LINEAR_SHAPES) if LINEAR_KEYS.index(n) % world == rank}
 
             host_params = [p.data for p in block_host.parameters()]
             copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
@@ -468,8 +469,12 @@ def main():
                 main_s = torch.cuda.current_stream()
                 copy_in.wait_stream(main_s)
                 block = copy.deepcopy(master)
+                # the block's parameters cross PCIe once (rank 0) and reach the other ranks over NVLink
                 for p, hp in zip(block.parameters(), host_params):
-                    p.data.copy_(hp, non_blocking=True)
+                    if rank == 0:
+                        p.data.copy_(hp, non_blocking=True)
+                    if world > 1:
+                        dist.broadcast(p.data, src=0)
                 if e2e_state['pending'] is None:
                     e2e_state['pending'] = start_input_copy(e2e_state['buf'])
                 evs, buf = e2e_state['pending'], e2e_state['buf']
@@ -493,15 +498,19 @@ def main():
                     done.record(main_s)
                     copy_out.wait_event(done)
                     with torch.cuda.stream(copy_out):
+                        # every rank holds the same quantised weights; each linear goes back to the host
+                        # from one rank only
                         for nme in names:
-                            w_host[name_to_key[nme]].copy_(mods[nme].weight, non_blocking=True)
+                            key = name_to_key[nme]
+                            if LINEAR_KEYS.index(key) % world == rank:
+                                w_host[key].copy_(mods[nme].weight, non_blocking=True)
                 runner.on_input, runner.on_subset_done = on_input, on_subset_done
                 outs = runner.block_opt(block, [x_stage[i:i + bs] for i in range(0, n_seq, bs)], kwargs)
                 runner.on_input = runner.on_subset_done = None
                 main_s.wait_stream(copy_out)
                 return outs
-            h2d = int(X_host.numel() * 2 + sum(p.numel() * 2 for p in block_host.parameters()))
-            d2h = int(sum(w.numel() * 4 for w in w_host.values()))
+            h2d = int(X_host.numel() * 2 * world + sum(p.numel() * 2 for p in block_host.parameters()))   # whole job
+            d2h = int(sum(r * c * 4 for r, c in LINEAR_SHAPES))
         # kernels of this library per step (torch's own kernels -- cuBLAS GEMMs of the forward, cuSOLVER
         # potrf, SDPA, argsort, gathers -- are not counted):
         #   Hessian launches, 4 diag; per distinct Hessian (3 x C=4096, 1 x C=11008): damp + permute,
