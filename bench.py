@@ -523,8 +523,10 @@ def main():
         n_calls = -(-n_seq // bs)
 
         def solver_launches(c):
-            blocks, panels = -(-c // 128), -(-c // 1024)
-            return blocks + (blocks - panels) + (panels - 1)
+            # block kernels, eager FFMA updates (one per block that is not the last of its 256-column
+            # sub-panel), K = 256 GEMMs (one per sub-panel that is not the last of its panel), K = 1024 GEMMs
+            blocks, subs, panels = -(-c // 128), -(-c // 256), -(-c // 1024)
+            return blocks + (blocks - subs) + (subs - panels) + (panels - 1)
         launches = (4 * -(-n_calls // HESSIAN_BATCH) + 4
                     + sum(2 + 1 + 1 + 1 + 5 * (c // 128 - 1) for c in (HID, HID, HID, INTER))
                     + sum(3 + solver_launches(c) for r, c in LINEAR_SHAPES)

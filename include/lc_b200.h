@@ -242,9 +242,10 @@ int lc_gptq_invert_factor(const float* G, int64_t n, float* U, float* U_lo, floa
                           int64_t workspace_floats, int32_t* status, lc_stream_t stream);
 
 /* GPTQ.weight_transform (gptq.py:199-244) with the trailing update on the tensor cores: the update
- * after each 128-column block covers only the rest of its 1024-column panel (fp32 FFMA); columns to
- * the right of a panel are updated once per panel by a K = 1024 tcgen05 kind::tf32 GEMM with a
- * three-term hi/lo split (lc_tf32x3_gemm_tn).  Same sums as the reference, associated differently.
+ * after each 128-column block covers only the rest of its 256-column sub-panel (fp32 FFMA); the rest of
+ * the 1024-column panel is updated once per sub-panel (K = 256) and the columns to the right of a panel
+ * once per panel (K = 1024), both by tcgen05 kind::tf32 GEMMs with a three-term hi/lo split
+ * (lc_tf32x3_gemm_tn).  Same sums as the reference, associated differently.
  *   U_lo        cols x cols from lc_gptq_split_tf32(U)
  *   scratch_err 128 x rows;  panel_hi, panel_lo  1024 x rows each (fp32 scratch)
  *   status      optional, receives LC_ERR_TIMEOUT if a bounded pipeline wait expires

@@ -1,11 +1,12 @@
-// Family 3: the GPTQ trailing update on the tensor cores, with two-level (lazy) batching.
+// Family 3: the GPTQ trailing update on the tensor cores, with three-level (lazy) batching.
 //
 // The reference updates all columns to the right after every 128-column block
 // (W[:, i2:] -= Err1 @ Hinv[i1:i2, i2:], gptq.py:244): K = 128, 32 flop per byte of W traffic.  Here
-// the eager update only covers the rest of a 1024-column panel (fp32 FFMA kernel); everything to the
-// right of the panel is updated once per panel,
+// the eager update after a block only covers the rest of its 256-column sub-panel (fp32 FFMA kernel,
+// at most 128 columns); the rest of the 1024-column panel is updated once per sub-panel (K = 256) and
+// everything to the right of the panel once per panel,
 //     W[:, p2:] -= E^T (rows x 1024) * U[p1:p2, p2:],
-// a K = 1024 GEMM on tcgen05 with kind::tf32 and the three-term split (tf32x3_gemm.cu).  The sums are
+// a K = 1024 GEMM; both on tcgen05 with kind::tf32 and the three-term split (tf32x3_gemm.cu).  The sums are
 // the reference's, associated differently.  The block kernel stores E k-major together with its low
 // part; lc_gptq_split_tf32 makes the low part of U.
 #include "lc_common.cuh"
@@ -74,7 +75,7 @@ extern "C" LC_API int lc_gptq_weight_transform_tc(float* W, const float* U, cons
                                                   uint8_t* codes_u8, float* loss_rows, int32_t* status,
                                                   lc_stream_t stream) {
   using namespace lc;
-  constexpr int kPanel = 1024;
+  constexpr int kPanel = 1024, kSub = 256;
   if (!W || !U || !U_lo || !scratch_err || !panel_hi || !panel_lo || !scales || !zeros) return LC_ERR_ARG;
   if (rows <= 0 || cols <= 0 || bits < 2 || bits > 8) return LC_ERR_ARG;
   if (cols % 128 != 0 || rows % 4 != 0) return LC_ERR_SHAPE;      // TMA pitch / whole blocks; use the FFMA entry point otherwise
@@ -95,17 +96,24 @@ extern "C" LC_API int lc_gptq_weight_transform_tc(float* W, const float* U, cons
   }
   for (int64_t p1 = 0; p1 < cols; p1 += kPanel) {
     const int64_t p2 = (p1 + kPanel < cols) ? p1 + kPanel : cols;
-    for (int64_t i1 = p1; i1 < p2; i1 += 128) {
-      const int k0 = (int)(i1 - p1);
-      const bool has_right = p2 < cols;
-      int rc = gptq_block_launch(W, U, rows, cols, i1, 128, bits, sym, scratch_err, scales, zeros, n_groups, codes_u8,
-                                 loss_rows, st, has_right ? panel_hi : nullptr, has_right ? panel_lo : nullptr, k0);
-      if (rc != LC_OK) return rc;
-      // eager update of the rest of the panel, W[:, i2:p2] -= E_block^T U[i1:i2, i2:p2]: K = 128 and at most
-      // 896 columns, where the fp32 FFMA kernel beats the fixed cost of a tensor-core launch (measured)
-      rc = gptq_trail_launch(W, scratch_err, U, rows, cols, i1, 128, i1 + 128, st, p2);
-      if (rc != LC_OK) return rc;
+    for (int64_t s1 = p1; s1 < p2; s1 += kSub) {
+      const int64_t s2 = (s1 + kSub < p2) ? s1 + kSub : p2;
+      for (int64_t i1 = s1; i1 < s2; i1 += 128) {
+        int rc = gptq_block_launch(W, U, rows, cols, i1, 128, bits, sym, scratch_err, scales, zeros, n_groups,
+                                   codes_u8, loss_rows, st, panel_hi, panel_lo, (int)(i1 - p1));
+        if (rc != LC_OK) return rc;
+        // level 1, eager: the rest of the 256-column sub-panel (K = 128, at most 128 columns: FFMA kernel)
+        rc = gptq_trail_launch(W, scratch_err, U, rows, cols, i1, 128, i1 + 128, st, s2);
+        if (rc != LC_OK) return rc;
+      }
+      // level 2: the rest of the panel, once per sub-panel (K = 256)
+      if (s2 < p2) {
+        const int rc = tf32x3_gemm_launch(W + s2, cols, E, s1 - p1, 0, Um, s1, s2, rows, p2 - s2, s2 - s1, 1, -1.f, 0,
+                                          status, st);
+        if (rc != LC_OK) return rc;
+      }
     }
+    // level 3: everything to the right of the panel, once per panel (K = 1024)
     if (p2 < cols) {
       const int rc = tf32x3_gemm_launch(W + p2, cols, E, 0, 0, Um, p1, p2, rows, cols - p2, p2 - p1, 1, -1.f, 0, status,
                                         st);

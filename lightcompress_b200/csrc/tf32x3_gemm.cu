@@ -51,6 +51,7 @@ struct GemmArgs {
   int beta;
   float sign;
   int flags;
+  int use3d;   // operand tiles fetched by one 3-D copy each instead of one 2-D copy per 32-float atom
 };
 
 struct TileWork {
@@ -119,6 +120,18 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
           const uint32_t sa = base + s * P_STAGE_BYTES;
+          if (a.use3d) {
+            // atoms land 2048 bytes apart, exactly like the per-atom copies below
+            tma_load_3d(sa, &maps.a_hi, 0, a.a_k0 + krow, (a.a_m0 + w.m0) / ATOM_F, full_bar(s));
+            tma_load_3d(sa + A_ATOMS * P_ATOM_BYTES, &maps.a_lo, 0, a.a_k0 + krow, (a.a_m0 + w.m0) / ATOM_F,
+                        full_bar(s));
+            tma_load_3d(sa + 2 * A_ATOMS * P_ATOM_BYTES, &maps.b_hi, 0, a.b_k0 + krow, (a.b_n0 + w.n0) / ATOM_F,
+                        full_bar(s));
+            tma_load_3d(sa + (2 * A_ATOMS + B_ATOMS) * P_ATOM_BYTES, &maps.b_lo, 0, a.b_k0 + krow,
+                        (a.b_n0 + w.n0) / ATOM_F, full_bar(s));
+            issued = n + 1;
+            continue;
+          }
 #pragma unroll
           for (int q = 0; q < A_ATOMS; ++q) {
             tma_load_2d(sa + q * P_ATOM_BYTES, &maps.a_hi, a.a_m0 + w.m0 + q * ATOM_F, a.a_k0 + krow, full_bar(s));
@@ -255,6 +268,23 @@ int encode_f32_2d(CUtensorMap* m, const float* base, int64_t inner, int64_t oute
   return LC_OK;
 }
 
+// 3-D view of a k-row matrix: (32 floats, k rows, atoms of 32 floats along M / N); a box of `atoms`
+// atoms x 16 rows is one operand tile of a pipeline stage
+int encode_f32_3d(CUtensorMap* m, const float* base, int64_t mn_extent, int64_t k_extent, int64_t pitch_elems,
+                  int atoms) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) return LC_ERR_CUDA;
+  const cuuint64_t gdim[3] = {(cuuint64_t)ATOM_F, (cuuint64_t)k_extent, (cuuint64_t)(mn_extent / ATOM_F)};
+  const cuuint64_t gstride[2] = {(cuuint64_t)pitch_elems * 4, (cuuint64_t)ATOM_F * 4};
+  const cuuint32_t box[3] = {ATOM_F, PBK, (cuuint32_t)atoms};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  if (encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), gdim, gstride, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return LC_ERR_CUDA;
+  return LC_OK;
+}
+
 // SM count and the kernel's shared-memory attribute, once per device
 int device_setup(int* sms_out) {
   static int sms_of[64] = {0};
@@ -281,6 +311,12 @@ int gemm_mat_init(GemmMat* m, const float* hi, const float* lo, int64_t k_extent
   if ((rc = encode_f32_2d(&m->map_lo, lo, mn_extent, k_extent, ld)) != LC_OK) return rc;
   m->k_extent = k_extent;
   m->mn_extent = mn_extent;
+  m->has3 = false;
+  if (mn_extent % ATOM_F == 0 && encode_f32_3d(&m->map3a_hi, hi, mn_extent, k_extent, ld, A_ATOMS) == LC_OK &&
+      encode_f32_3d(&m->map3a_lo, lo, mn_extent, k_extent, ld, A_ATOMS) == LC_OK &&
+      encode_f32_3d(&m->map3b_hi, hi, mn_extent, k_extent, ld, B_ATOMS) == LC_OK &&
+      encode_f32_3d(&m->map3b_lo, lo, mn_extent, k_extent, ld, B_ATOMS) == LC_OK)
+    m->has3 = true;
   return LC_OK;
 }
 
@@ -296,11 +332,12 @@ int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, in
     return LC_ERR_SHAPE;
   if (!aligned16(C)) return LC_ERR_ALIGN;
   GemmMaps maps;
-  maps.a_hi = A.map_hi;
-  maps.a_lo = A.map_lo;
-  maps.b_hi = B.map_hi;
-  maps.b_lo = B.map_lo;
   GemmArgs a;
+  a.use3d = (A.has3 && B.has3 && a_m0 % ATOM_F == 0 && b_n0 % ATOM_F == 0) ? 1 : 0;
+  maps.a_hi = a.use3d ? A.map3a_hi : A.map_hi;
+  maps.a_lo = a.use3d ? A.map3a_lo : A.map_lo;
+  maps.b_hi = a.use3d ? B.map3b_hi : B.map_hi;
+  maps.b_lo = a.use3d ? B.map3b_lo : B.map_lo;
   a.C = C;
   a.status = status;
   a.ldc = ldc;

@@ -16,7 +16,11 @@ constexpr int kGemmAUpper = 4;      // A[k][m] == 0 for k > m: a tile's k range 
 // Prepared once, then any sub-matrix of it can be an operand (origin given per launch), which keeps
 // tensor-map encoding out of loops that launch hundreds of small products.
 struct GemmMat {
-  CUtensorMap map_hi, map_lo;
+  CUtensorMap map_hi, map_lo;      // 2-D: one 32-float x 16-row box per copy
+  // 3-D views (32 floats, k rows, 32-float atoms): a whole operand tile per copy, 4 atoms when the matrix
+  // is the A operand, 8 when it is B
+  CUtensorMap map3a_hi, map3a_lo, map3b_hi, map3b_lo;
+  bool has3 = false;               // mn_extent % 32 == 0 and the driver accepted the views
   int64_t k_extent = 0, mn_extent = 0;
 };
 // hi, lo: 16-byte aligned, ld % 4 == 0.  x_hi is the fp32 value itself (the tensor core truncates it),
