@@ -61,6 +61,7 @@ struct HessArgs {
   int nseg;
   int seg_k[MAX_SEG];
   float alpha;
+  int use3d;       // tensor maps are 3-D views: two 64-channel atoms per copy
 };
 
 struct Item {
@@ -147,6 +148,15 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
           const uint32_t sa = base + s * STAGE_BYTES;
           const CUtensorMap* map = &maps.m[seg];
           const int tok = kloc * BK;
+          if (a.use3d) {
+            // one copy per pair of 64-channel atoms (8 KB); atoms land 4096 bytes apart as below
+            if (!diag) {
+              tma_load_3d(sa, map, 0, tok, (w.si * ST) / ATOM, full_bar(s));
+              if (has_a1) tma_load_3d(sa + A_ATOMS * ATOM_BYTES, map, 0, tok, (w.si * ST + 128) / ATOM, full_bar(s));
+            }
+            tma_load_3d(sa + 2 * A_ATOMS * ATOM_BYTES, map, 0, tok, (w.sj * ST) / ATOM, full_bar(s));
+            tma_load_3d(sa + (2 * A_ATOMS + 2) * ATOM_BYTES, map, 0, tok, (w.sj * ST) / ATOM + 2, full_bar(s));
+          } else {
           if (!diag) {
 #pragma unroll
             for (int q = 0; q < A_ATOMS; ++q) tma_load_2d(sa + q * ATOM_BYTES, map, w.si * ST + q * ATOM, tok, full_bar(s));
@@ -159,6 +169,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
 #pragma unroll
           for (int q = 0; q < B_ATOMS; ++q)
             tma_load_2d(sa + (2 * A_ATOMS + q) * ATOM_BYTES, map, w.sj * ST + q * ATOM, tok, full_bar(s));
+          }
           issued = n + 1;
           if (++kloc >= a.seg_k[seg]) {
             kloc = 0;
@@ -347,10 +358,24 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
   if (!encode) return LC_ERR_CUDA;
   TmapArray maps;
   HessArgs a;
+  // whole 64-channel atoms only: the 3-D view cannot describe a ragged last atom
+  const bool use3d = cols % ATOM == 0;
+  a.use3d = use3d ? 1 : 0;
   a.nseg = 0;
   a.k_total = 0;
   for (int s = 0; s < nseg; ++s) {
     if (tokens[s] == 0) continue;
+    if (use3d) {
+      // (64 channels, tokens, atoms of 64 channels): a box of two atoms x 32 tokens per copy
+      const cuuint64_t gdim[3] = {(cuuint64_t)ATOM, (cuuint64_t)tokens[s], (cuuint64_t)(cols / ATOM)};
+      const cuuint64_t gstride[2] = {(cuuint64_t)cols * 2, (cuuint64_t)ATOM * 2};
+      const cuuint32_t box[3] = {ATOM, BK, 2};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      if (encode(&maps.m[a.nseg], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(xs[s]), gdim, gstride, box,
+                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return LC_ERR_CUDA;
+    } else {
     const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)tokens[s]};
     const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
     const cuuint32_t box[2] = {ATOM, BK};
@@ -359,6 +384,7 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return LC_ERR_CUDA;
+    }
     a.seg_k[a.nseg] = (int)((tokens[s] + BK - 1) / BK);
     a.k_total += a.seg_k[a.nseg];
     ++a.nseg;
