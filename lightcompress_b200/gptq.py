@@ -51,6 +51,7 @@ class GPTQ:
         self.model_dtype = model_dtype
         self.layers_cache = {}
         self._pending_status = []       # device status words of tensor-core launches, read lazily
+        self._pending_info = []         # cuSOLVER potrf info words (non-zero: not positive definite)
         self._check_config()
         self.need_perm = (self.wquantizer.granularity == 'per_group' and not self.static_groups
                           and self.actorder)
@@ -165,7 +166,10 @@ class GPTQ:
             else:
                 # cuSOLVER returns the lower factor M column-major: the same bytes are the row-major upper
                 # factor G = M^T that the inverse reads
-                M = torch.linalg.cholesky(Hp)
+                # no host synchronisation here: potrf's info word joins the status words read at the next
+                # check_status(), which raises LinAlgError like torch.linalg.cholesky would have
+                M, info = torch.linalg.cholesky_ex(Hp, check_errors=False)
+                self._pending_info.append(info.reshape(1))
                 G = M.t() if M.stride() == (1, C) else M.t().contiguous()
                 L.call('lc_gptq_invert_factor', L.ptr(G), C, L.ptr(U), L.ptr(U_lo), L.ptr(ws), ws_floats,
                        L.ptr(status), L.stream_of(H))
@@ -304,6 +308,13 @@ class GPTQ:
 
     def check_status(self):
         """Reads (one sync) the device status words of the tensor-core launches issued so far."""
+        if self._pending_info:
+            infos = torch.cat(self._pending_info).tolist()
+            self._pending_info = []
+            if any(infos):
+                self._pending_status = []
+                raise torch.linalg.LinAlgError('cholesky: the dampened Hessian is not positive definite '
+                                               f'(potrf info {[i for i in infos if i]})')
         if self._pending_status:
             codes = torch.cat(self._pending_status).tolist()
             self._pending_status = []

@@ -295,6 +295,64 @@ def make_awq(rq, out_dir):
     print('awq_block.pt', len(cases), 'cases')
 
 
+def make_export_configs(ref_root, out_dir):
+    """config.json entries written by the reference's export helpers (llmc/utils/export_vllm.py,
+    export_autoawq.py), loaded by file path (they only need json)."""
+    import importlib.util
+    import json
+    import tempfile
+
+    def load(name):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(ref_root, 'llmc', 'utils', name + '.py'))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+    ev, ea = load('export_vllm'), load('export_autoawq')
+
+    class AD(dict):
+        __getattr__ = dict.__getitem__
+
+        def __init__(self, d):
+            super().__init__({k: (AD(v) if isinstance(v, dict) else v) for k, v in d.items()})
+
+    class Model:
+        def skip_layer_name(self):
+            return ['lm_head']
+    w8 = dict(bit=8, symmetric=True, granularity='per_channel')
+    fp8 = dict(quant_type='float-quant', bit='e4m3', symmetric=True)
+    cases = {
+        'w4a16_g128_pack': dict(weight=dict(bit=4, symmetric=True, granularity='per_group', group_size=128,
+                                            need_pack=True)),
+        'w8a8_int': dict(weight=w8, act=dict(bit=8, symmetric=True, granularity='per_token')),
+        'w4a16_channel': dict(weight=dict(bit=4, symmetric=False, granularity='per_channel')),
+        'fp8_block': dict(weight=dict(fp8, granularity='per_block', block_size=128),
+                          act=dict(fp8, granularity='per_group', group_size=128)),
+        'fp8_static': dict(weight=dict(fp8, granularity='per_tensor'),
+                           act=dict(fp8, granularity='per_tensor', static=True)),
+        'w8a8_static': dict(weight=w8, act=dict(bit=8, symmetric=True, granularity='per_tensor', static=True)),
+    }
+    out = {}
+
+    def fresh_dir():
+        d = tempfile.mkdtemp()
+        with open(os.path.join(d, 'config.json'), 'w') as f:
+            json.dump({'model_type': 'llama', 'quantization_config': {'old': 1}}, f)
+        return d
+    for k, c in cases.items():
+        d = fresh_dir()
+        ev.update_vllm_quant_config(Model(), AD({'quant': c}), d)
+        with open(os.path.join(d, 'config.json')) as f:
+            out['vllm_' + k] = {'in': c, 'config_json': json.load(f)}
+    c = dict(weight=dict(bit=4, symmetric=False, granularity='per_group', group_size=128, pack_version='gemm_pack'))
+    d = fresh_dir()
+    ea.update_autoawq_quant_config(AD({'quant': c}), d)
+    with open(os.path.join(d, 'config.json')) as f:
+        out['autoawq'] = {'in': c, 'config_json': json.load(f)}
+    with open(os.path.join(out_dir, 'export_configs.json'), 'w') as f:
+        json.dump(out, f, indent=1)
+    print('export_configs.json', len(out), 'cases')
+
+
 if __name__ == '__main__':
     ref_root = sys.argv[1]
     out_dir = os.path.dirname(os.path.abspath(__file__))
@@ -305,3 +363,4 @@ if __name__ == '__main__':
     make_gptq(rq, rg, out_dir)
     make_fp8(rq, out_dir)
     make_awq(rq, out_dir)
+    make_export_configs(ref_root, out_dir)
