@@ -241,6 +241,21 @@ int lc_gptq_factorize(float* A, int64_t n, float* U, float* U_lo, float* workspa
 int lc_gptq_invert_factor(const float* G, int64_t n, float* U, float* U_lo, float* workspace,
                           int64_t workspace_floats, int32_t* status, lc_stream_t stream);
 
+/* lc_gptq_invert_factor in two steps, for a process group whose ranks all factorise the same Hessian
+ * (the reference repeats the factorisation on every rank): the top node of the recursion holds three
+ * quarters of the inverse's FLOPs in its off-diagonal block Vt[h:n, 0:h], h = lc_gptq_factor_split(n).
+ * _part computes everything below the top node in full and that block only for columns
+ * [col_begin, col_end) (multiples of 128, within [0, h)); the caller then exchanges the column slices
+ * (the n x n row-major Vt starts lc_gptq_factor_vt_offset(n) floats into the workspace; collectives stay
+ * with the caller) and _finish writes U and U_lo from the completed Vt.  Same values as the one-call
+ * form, whatever the slicing. */
+int64_t lc_gptq_factor_split(int64_t n);
+int64_t lc_gptq_factor_vt_offset(int64_t n);
+int lc_gptq_invert_factor_part(const float* G, int64_t n, float* workspace, int64_t workspace_floats,
+                               int64_t col_begin, int64_t col_end, int32_t* status, lc_stream_t stream);
+int lc_gptq_invert_factor_finish(int64_t n, const float* workspace, int64_t workspace_floats, float* U, float* U_lo,
+                                 lc_stream_t stream);
+
 /* GPTQ.weight_transform (gptq.py:199-244) with the trailing update on the tensor cores: the update
  * after each 128-column block covers only the rest of its 256-column sub-panel (fp32 FFMA); the rest of
  * the 1024-column panel is updated once per sub-panel (K = 256) and the columns to the right of a panel

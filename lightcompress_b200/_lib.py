@@ -52,6 +52,10 @@ SIGNATURES = {
     'lc_gptq_factor_workspace_floats': [_i64],
     'lc_gptq_factorize': [_p, _i64, _p, _p, _p, _i64, _p, _p],
     'lc_gptq_invert_factor': [_p, _i64, _p, _p, _p, _i64, _p, _p],
+    'lc_gptq_factor_split': [_i64],
+    'lc_gptq_factor_vt_offset': [_i64],
+    'lc_gptq_invert_factor_part': [_p, _i64, _p, _i64, _i64, _i64, _p, _p],
+    'lc_gptq_invert_factor_finish': [_i64, _p, _i64, _p, _p, _p],
     'lc_rtn_mse_range': [_p, _i, _i64, _i64, _i64, _i, _i, _d, _i, _f, _p, _p, _p],
     'lc_rope_apply': [_p, _p, _p, _i, _i64, _i, _i, _p, _p],
     'lc_silu_mul': [_p, _p, _i, _i64, _p, _p],
@@ -80,7 +84,9 @@ def _load():
                               '`python __graft_entry__.py`') from None
         fn.argtypes = argtypes
         fn.restype = {'lc_status_string': ctypes.c_char_p,
-                      'lc_gptq_factor_workspace_floats': ctypes.c_int64}.get(name, ctypes.c_int)
+                      'lc_gptq_factor_workspace_floats': ctypes.c_int64,
+                      'lc_gptq_factor_split': ctypes.c_int64,
+                      'lc_gptq_factor_vt_offset': ctypes.c_int64}.get(name, ctypes.c_int)
     return lib
 
 

@@ -346,9 +346,32 @@ int factorize(const Factor& f) {
   return invert_range(f, 0, n);
 }
 
-// Vt = (G^-1)^T for a given upper factor G: all diagonal blocks inverted by one launch, then the
-// recursion.
-int invert_factor(const Factor& f) {
+// The top node of the recursion with the off-diagonal block Vt[h:n, 0:h] restricted to columns
+// [c0, c1): both children in full, then the two products on that column slice only.  Ranks of a
+// process group take different slices and exchange them afterwards.
+int invert_top_slice(const Factor& f, int64_t c0, int64_t c1) {
+  const int64_t n = f.n;
+  if (n <= kB) return LC_OK;
+  const int64_t h = ((n / kB + 1) / 2) * kB, m1 = h, m2 = n - h, w = c1 - c0;
+  int rc;
+  if ((rc = invert_range(f, 0, h)) != LC_OK) return rc;
+  if ((rc = invert_range(f, h, n)) != LC_OK) return rc;
+  if (w <= 0) return LC_OK;
+  if ((rc = tf32x3_gemm_launch(f.T + c0, f.h, f.mG, 0, h, f.mVt, 0, c0, m2, w, m1, 0, 1.f, kGemmBLower, f.status, f.st,
+                               c0)) != LC_OK)
+    return rc;
+  if ((rc = split_region(f, f.T + c0, f.T_lo + c0, m2, w, f.h)) != LC_OK) return rc;
+  {
+    const dim3 grid((unsigned)((m2 + 31) / 32), (unsigned)((m2 + 31) / 32));
+    transpose_split_kernel<<<grid, 256, 0, f.st>>>(f.Vt + h * n + h, n, f.R, f.R_lo, f.h, (int)m2);
+    LC_LAUNCH_CHECK();
+  }
+  return tf32x3_gemm_launch(f.Vt + h * n + c0, n, f.mR, 0, 0, f.mT, 0, c0, m2, w, m2, 0, -1.f, kGemmAUpper, f.status,
+                            f.st);
+}
+
+// Leaves and low parts common to the whole and the sliced inverse
+int invert_prologue(const Factor& f) {
   const int64_t n = f.n;
   int rc;
   LC_CHECK_CUDA(cudaFuncSetAttribute(chol_leaf_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -359,7 +382,35 @@ int invert_factor(const Factor& f) {
   chol_leaf_kernel<false><<<(unsigned)(n / kB), kLeafThreads, kB * kLd * sizeof(float), f.st>>>(
       f.G, n, nullptr, nullptr, 0, nullptr, nullptr, f.Vt, f.Vt_lo, n, nullptr);
   LC_LAUNCH_CHECK();
-  return invert_range(f, 0, n);
+  return LC_OK;
+}
+
+// Workspace carve-up of the inverse-only entry points
+void carve_inverse(Factor& f, const float* G, int64_t n, float* workspace, int32_t* status, cudaStream_t st) {
+  const int64_t h = ((n / 128 + 1) / 2) * 128;
+  f.n = n;
+  f.h = h;
+  f.A = nullptr;
+  f.G = const_cast<float*>(G);
+  float* p = workspace;
+  f.G_lo = p, p += n * n;
+  f.Vt = p, p += n * n;
+  f.Vt_lo = p, p += n * n;
+  f.T = p, p += h * h;
+  f.T_lo = p, p += h * h;
+  f.R = p, p += h * h;
+  f.R_lo = p;
+  f.Vd = f.Vd_lo = nullptr;
+  f.status = status;
+  f.st = st;
+}
+
+// Vt = (G^-1)^T for a given upper factor G: all diagonal blocks inverted by one launch, then the
+// recursion.
+int invert_factor(const Factor& f) {
+  const int rc = invert_prologue(f);
+  if (rc != LC_OK) return rc;
+  return invert_range(f, 0, f.n);
 }
 
 }  // namespace
@@ -421,28 +472,53 @@ extern "C" LC_API int lc_gptq_invert_factor(const float* G, int64_t n, float* U,
   LC_CHECK_CUDA(cudaGetDevice(&dev));
   LC_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
   if (major != 10) return LC_ERR_ARCH;
-  const int64_t h = ((n / 128 + 1) / 2) * 128;
   Factor f;
-  f.n = n;
-  f.A = nullptr;
-  f.G = const_cast<float*>(G);
-  float* p = workspace;
-  f.G_lo = p, p += n * n;
-  f.Vt = p, p += n * n;
-  f.Vt_lo = p, p += n * n;
-  f.T = p, p += h * h;
-  f.T_lo = p, p += h * h;
-  f.R = p, p += h * h;
-  f.R_lo = p;
-  f.Vd = f.Vd_lo = nullptr;
-  f.status = status;
-  f.st = reinterpret_cast<cudaStream_t>(stream);
-  f.h = h;
+  carve_inverse(f, G, n, workspace, status, reinterpret_cast<cudaStream_t>(stream));
   int rc = prepare_operands(f, false);
   if (rc != LC_OK) return rc;
   rc = invert_factor(f);
   if (rc != LC_OK) return rc;
   flip_upper_kernel<<<grid_1d(n * (n >> 2)), 256, 0, f.st>>>(f.Vt, n, U, U_lo);
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
+
+extern "C" LC_API int64_t lc_gptq_factor_split(int64_t n) { return n <= 128 ? n : ((n / 128 + 1) / 2) * 128; }
+
+extern "C" LC_API int64_t lc_gptq_factor_vt_offset(int64_t n) { return n * n; }
+
+extern "C" LC_API int lc_gptq_invert_factor_part(const float* G, int64_t n, float* workspace,
+                                                 int64_t workspace_floats, int64_t col_begin, int64_t col_end,
+                                                 int32_t* status, lc_stream_t stream) {
+  using namespace lc;
+  if (!G || !workspace || !status || n <= 0) return LC_ERR_ARG;
+  if (n % 128 != 0 || n <= 128) return LC_ERR_SHAPE;
+  const int64_t h = lc_gptq_factor_split(n);
+  if (col_begin < 0 || col_end < col_begin || col_end > h || col_begin % 128 != 0 || col_end % 128 != 0)
+    return LC_ERR_ARG;
+  if (workspace_floats < lc_gptq_factor_workspace_floats(n)) return LC_ERR_WORKSPACE;
+  if (!aligned16(G) || !aligned16(workspace)) return LC_ERR_ALIGN;
+  int dev = 0, major = 0;
+  LC_CHECK_CUDA(cudaGetDevice(&dev));
+  LC_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10) return LC_ERR_ARCH;
+  Factor f;
+  carve_inverse(f, G, n, workspace, status, reinterpret_cast<cudaStream_t>(stream));
+  int rc = prepare_operands(f, false);
+  if (rc != LC_OK) return rc;
+  if ((rc = invert_prologue(f)) != LC_OK) return rc;
+  return invert_top_slice(f, col_begin, col_end);
+}
+
+extern "C" LC_API int lc_gptq_invert_factor_finish(int64_t n, const float* workspace, int64_t workspace_floats,
+                                                   float* U, float* U_lo, lc_stream_t stream) {
+  using namespace lc;
+  if (!workspace || !U || n <= 0) return LC_ERR_ARG;
+  if (n % 128 != 0) return LC_ERR_SHAPE;
+  if (workspace_floats < lc_gptq_factor_workspace_floats(n)) return LC_ERR_WORKSPACE;
+  if (!aligned16(workspace) || !aligned16(U) || (U_lo && !aligned16(U_lo))) return LC_ERR_ALIGN;
+  flip_upper_kernel<<<grid_1d(n * (n >> 2)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      workspace + lc_gptq_factor_vt_offset(n), n, U, U_lo);
   LC_LAUNCH_CHECK();
   return LC_OK;
 }

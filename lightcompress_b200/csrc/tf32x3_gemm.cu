@@ -52,6 +52,7 @@ struct GemmArgs {
   float sign;
   int flags;
   int use3d;   // operand tiles fetched by one 3-D copy each instead of one 2-D copy per 32-float atom
+  int b_tri_shift;
 };
 
 struct TileWork {
@@ -63,7 +64,7 @@ __device__ __forceinline__ TileWork tile_work(const GemmArgs& a, int t) {
   TileWork w;
   w.m0 = (t % a.m_tiles) * PM;
   w.n0 = (t / a.m_tiles) * PN;
-  w.k0 = (a.flags & kGemmBLower) ? (w.n0 / PBK) * PBK : 0;
+  w.k0 = (a.flags & kGemmBLower) ? min(a.K, ((w.n0 + a.b_tri_shift) / PBK) * PBK) : 0;
   w.k1 = (a.flags & kGemmAUpper) ? min(a.K, w.m0 + PM) : a.K;
   w.skip = (a.flags & kGemmUpperOnly) && (w.n0 + PN <= w.m0);
   return w;
@@ -322,9 +323,10 @@ int gemm_mat_init(GemmMat* m, const float* hi, const float* lo, int64_t k_extent
 
 int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, int64_t a_m0, const GemmMat& B,
                        int64_t b_k0, int64_t b_n0, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
-                       int32_t* status, cudaStream_t st) {
+                       int32_t* status, cudaStream_t st, int64_t b_tri_shift) {
   if (M <= 0 || N <= 0 || K <= 0) return LC_OK;
   if (K % PBK != 0 || M % 4 != 0 || N % 4 != 0 || ldc % 4 != 0 || a_m0 % 4 != 0 || b_n0 % 4 != 0) return LC_ERR_SHAPE;
+  if (b_tri_shift < 0 || ((flags & kGemmBLower) && b_tri_shift + N > K)) return LC_ERR_SHAPE;
   if (a_k0 < 0 || a_m0 < 0 || b_k0 < 0 || b_n0 < 0 || a_k0 + K > A.k_extent || a_m0 + M > A.mn_extent ||
       b_k0 + K > B.k_extent || b_n0 + N > B.mn_extent)
     return LC_ERR_SHAPE;
@@ -353,6 +355,7 @@ int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, in
   a.beta = beta ? 1 : 0;
   a.sign = sign;
   a.flags = flags;
+  a.b_tri_shift = (int)b_tri_shift;
   int sms = 0, rc;
   if ((rc = device_setup(&sms)) != LC_OK) return rc;
   const int tiles = a.m_tiles * a.n_tiles;

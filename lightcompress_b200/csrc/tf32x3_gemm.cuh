@@ -31,9 +31,11 @@ int gemm_mat_init(GemmMat* m, const float* hi, const float* lo, int64_t k_extent
 // B' = B[b_k0 : b_k0 + K, b_n0 : b_n0 + N].  K % 16 == 0; M, N, ldc and the origins multiples of 4.
 // Rows / columns of a tile beyond M / N read whatever follows in the operand matrix (or zeros beyond
 // its extent) and are never stored.
+// b_tri_shift: with kGemmBLower, B' is columns [shift, shift + N) of a lower-triangular matrix whose rows
+// start at B''s first row, i.e. B'[k][n] == 0 for k < n + shift.
 int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, int64_t a_m0, const GemmMat& B,
                        int64_t b_k0, int64_t b_n0, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
-                       int32_t* status, cudaStream_t st);
+                       int32_t* status, cudaStream_t st, int64_t b_tri_shift = 0);
 
 // One-off product: prepares both operands and launches.
 int tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, int64_t lda, const float* B_hi,

@@ -21,6 +21,23 @@ from . import parallel
 from .quant import IntegerQuantizer
 
 
+def _balanced_slices(m1, m2, parts, step=128):
+    """Column boundaries (multiples of `step`) of `parts` slices of the m2 x m1 off-diagonal block with
+    about equal work: a column c costs (m1 - c) in the first product (the right factor is lower
+    triangular) and m2 / 2 in the second."""
+    cols = list(range(0, m1, step))
+    cost = [(m1 - c) + m2 / 2.0 for c in cols]
+    total, acc, bounds = sum(cost), 0.0, [0]
+    for i, c in enumerate(cols):
+        acc += cost[i]
+        while len(bounds) < parts and acc >= total * len(bounds) / parts:
+            bounds.append(min(m1, c + step))
+    while len(bounds) <= parts:
+        bounds.append(m1)
+    bounds[parts] = m1
+    return bounds
+
+
 class GPTQ:
     def __init__(self, wquantizer=None, special=None, model_dtype=torch.bfloat16, **wq_kwargs):
         special = dict(special or {})
@@ -42,6 +59,10 @@ class GPTQ:
         # 'tensor': trailing update batched per 1024-column panel on tcgen05 (3-term tf32 split);
         # 'ffma': the reference's per-block update with the fp32 FFMA kernel
         self.trailing = special.get('trailing', 'tensor')
+        # multi-rank runs: the top level of the triangular inverse is computed once per process group and
+        # exchanged (every rank factorises the same all-reduced Hessian), for C >= shared_inverse_min
+        self.shared_inverse = special.get('shared_inverse', True)
+        self.shared_inverse_min = int(special.get('shared_inverse_min', 1024))
         # forward hooks deliver one sequence per call; up to `hessian_batch` of them (<= 8) are
         # held by reference and accumulated in one launch, so H is updated once per batch
         self.hessian_batch = max(1, min(8, int(special.get('hessian_batch', 8))))
@@ -171,8 +192,12 @@ class GPTQ:
                 M, info = torch.linalg.cholesky_ex(Hp, check_errors=False)
                 self._pending_info.append(info.reshape(1))
                 G = M.t() if M.stride() == (1, C) else M.t().contiguous()
-                L.call('lc_gptq_invert_factor', L.ptr(G), C, L.ptr(U), L.ptr(U_lo), L.ptr(ws), ws_floats,
-                       L.ptr(status), L.stream_of(H))
+                world = parallel.world()[1] if self.shared_inverse else 1
+                if world > 1 and C >= self.shared_inverse_min:
+                    self._shared_inverse(G, C, U, U_lo, ws, ws_floats, status)
+                else:
+                    L.call('lc_gptq_invert_factor', L.ptr(G), C, L.ptr(U), L.ptr(U_lo), L.ptr(ws), ws_floats,
+                           L.ptr(status), L.stream_of(H))
             self._pending_status.append(status)
             fac['U'], fac['U_lo'] = U, U_lo
             return fac
@@ -182,6 +207,30 @@ class GPTQ:
             fac['U_lo'] = torch.empty_like(U)
             L.call('lc_gptq_split_tf32', L.ptr(U), U.numel(), L.ptr(fac['U_lo']), L.stream_of(U))
         return fac
+
+    def _shared_inverse(self, G, C, U, U_lo, ws, ws_floats, status):
+        """The triangular inverse with its top-level block (3/4 of the FLOPs) computed once per process
+        group instead of once per rank: every rank takes a column slice, the slices are broadcast.  All
+        ranks must call this with the same G (they do: the Hessian was all-reduced), and end with
+        bit-identical U."""
+        import torch.distributed as dist
+        rank, world = parallel.world()
+        h = int(L.lib.lc_gptq_factor_split(C))
+        bounds = _balanced_slices(h, C - h, world)
+        c0, c1 = bounds[rank], bounds[rank + 1]
+        st = L.stream_of(G)
+        L.call('lc_gptq_invert_factor_part', L.ptr(G), C, L.ptr(ws), ws_floats, c0, c1, L.ptr(status), st)
+        off = int(L.lib.lc_gptq_factor_vt_offset(C))
+        Vt = ws[off:off + C * C].view(C, C)
+        for r in range(world):
+            a, b = bounds[r], bounds[r + 1]
+            if b > a:
+                piece = Vt[h:, a:b].contiguous() if r == rank else torch.empty((C - h, b - a), dtype=torch.float32,
+                                                                              device=G.device)
+                dist.broadcast(piece, src=r)
+                if r != rank:
+                    Vt[h:, a:b].copy_(piece)
+        L.call('lc_gptq_invert_factor_finish', C, L.ptr(ws), ws_floats, L.ptr(U), L.ptr(U_lo), st)
 
     def _workspace(self, floats, device):
         """Scratch of the native factorisation, kept between calls (2.4 GB at C = 11008)."""

@@ -74,3 +74,43 @@ def test_two_rank_block_matches_single_gpu(tmp_path):
     full = torch.cat([o.cpu() for o in outs]).float()
     both = torch.cat(r0['outs'] + r1['outs']).float()
     assert float((full - both).norm() / full.norm()) < 1e-2
+
+
+def _inverse_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    res = {}
+    for n in (384, 1152):
+        g = torch.Generator().manual_seed(n)
+        X = torch.randn(3 * n, n, generator=g)
+        H = (X.t() @ X).cuda()
+        shared = GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'shared_inverse': True, 'shared_inverse_min': 256})
+        alone = GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'shared_inverse': False})
+        a, b = shared.factorize(H, 2.0 / 3), alone.factorize(H, 2.0 / 3)
+        shared.check_status()
+        alone.check_status()
+        res[n] = (a['U'].cpu(), b['U'].cpu())
+    torch.save(res, os.path.join(out_dir, f'inv{rank}.pt'))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_shared_triangular_inverse_equals_the_single_rank_one(tmp_path):
+    """The triangular inverse with its top-level block split over the ranks and exchanged: every rank
+    ends with the U it computes alone, bit for bit (skipping zero blocks of a triangular operand and
+    slicing the output columns do not change any sum)."""
+    import torch.multiprocessing as mp
+    port = 29300 + (os.getpid() % 200)
+    mp.spawn(_inverse_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = torch.load(os.path.join(str(tmp_path), 'inv0.pt'))
+    r1 = torch.load(os.path.join(str(tmp_path), 'inv1.pt'))
+    for n in r0:
+        assert torch.equal(r0[n][0], r0[n][1]), n
+        assert torch.equal(r1[n][0], r0[n][0]), n
+        assert torch.equal(r0[n][0], torch.triu(r0[n][0]))
