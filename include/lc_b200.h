@@ -358,10 +358,12 @@ int lc_pack_int4_awq(const uint8_t* codes, int64_t rows, int64_t cols, int32_t* 
  * ------------------------------------------------------------------------------------------ */
 
 /* out = (x * cos) + (rotate_half(x) * sin), rotate_half(x) = cat(-x[d/2:], x[:d/2]) per head.
- * x, out: [tokens][heads][head_dim] contiguous; cos_tab, sin_tab: [tokens][head_dim]; all `dtype`.
- * head_dim must be a multiple of 8 (fp32) / 16 (bf16, fp16) elements.  out must not alias x. */
+ * x, out: [tokens][heads][head_dim] contiguous; cos_tab, sin_tab: [table_tokens][head_dim], token t
+ * using row t % table_tokens (table_tokens = tokens, or the sequence length when all sequences of a
+ * batch share one table); all `dtype`.  head_dim must be a multiple of 8 (fp32) / 16 (bf16, fp16)
+ * elements.  out must not alias x. */
 int lc_rope_apply(const void* x, const void* cos_tab, const void* sin_tab, int dtype, int64_t tokens, int heads,
-                  int head_dim, void* out, lc_stream_t stream);
+                  int head_dim, int64_t table_tokens, void* out, lc_stream_t stream);
 
 /* out = silu(gate) * up over n elements, silu(x) = x / (1 + exp(-x)) evaluated in fp32 and rounded
  * to `dtype` before the product.  n must be a multiple of the 16-byte vector.  out may alias either input. */

@@ -57,7 +57,7 @@ SIGNATURES = {
     'lc_gptq_invert_factor_part': [_p, _i64, _p, _i64, _i64, _i64, _p, _p],
     'lc_gptq_invert_factor_finish': [_i64, _p, _i64, _p, _p, _p],
     'lc_rtn_mse_range': [_p, _i, _i64, _i64, _i64, _i, _i, _d, _i, _f, _p, _p, _p],
-    'lc_rope_apply': [_p, _p, _p, _i, _i64, _i, _i, _p, _p],
+    'lc_rope_apply': [_p, _p, _p, _i, _i64, _i, _i, _i64, _p, _p],
     'lc_silu_mul': [_p, _p, _i, _i64, _p, _p],
     'lc_rmsnorm': [_p, _p, _i, _i64, _i64, _f, _f, _p, _p],
     'lc_awq_clip_search': [_p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _d, _p, _p, _p, _p],

@@ -16,9 +16,12 @@ expressions so that their bf16 rounding is identical.  The 20 losses stay on the
 winning candidate is selected there (first minimum, like the reference's strict `<`), so a subset
 costs no host synchronisation.
 """
+import contextlib
+
 import torch
 
 from . import _lib as L
+from . import block_ops
 
 
 def _is_norm(m):
@@ -38,6 +41,7 @@ class Awq:
         self.n_grid = 20
         self.clip_n_grid, self.clip_max_shrink = 20, 0.5
         self.n_sample_token = calib_seq_len
+        self.fused_block_ops = special.get('fused_block_ops', True)
         if self.trans_version != 'v2' or self.clip_version != 'v1':
             raise NotImplementedError('only trans_version v2 / clip_version v1 are on the B200 hot path')
         if wquantizer.granularity != 'per_group':
@@ -176,6 +180,18 @@ class Awq:
         four scale searches with their scale application, then the clip search on v, o, gate, up,
         down (q / k are skipped, auto_clip.py:56-60).  x: (B, T, C) hidden states, one batch.
         Modifies the block in place; returns a report dict."""
+        a, m = block.self_attn, block.mlp
+        dtype, dev = a.q_proj.weight.dtype, a.q_proj.weight.device
+        with contextlib.ExitStack() as stack:
+            if self.fused_block_ops:
+                # the inspect-module forwards run 80 times per block: their rotary embedding and gated
+                # activation go through one kernel each, bit-identical to the modules' own tensor ops
+                stack.enter_context(block_ops.fused_rotary(a, dev, dtype))
+                stack.enter_context(block_ops.fused_gated_mlp(m))
+            return self._block_transform(block, x, kwargs)
+
+    @torch.no_grad()
+    def _block_transform(self, block, x, kwargs):
         a, m = block.self_attn, block.mlp
         feats, hooks = {}, []
         for name, mod in (('q', a.q_proj), ('o', a.o_proj), ('gate', m.gate_proj), ('down', m.down_proj)):

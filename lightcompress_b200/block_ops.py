@@ -22,13 +22,13 @@ _checked = {}
 
 
 def rope_apply_one(x, cos, sin):
-    """x: (B, H, T, D) view of a (B, T, H, D) contiguous tensor; cos, sin: (B, T, D) contiguous.
-    Returns the embedded tensor with x's shape and memory layout."""
+    """x: (B, H, T, D) view of a (B, T, H, D) contiguous tensor; cos, sin: (B, T, D) or (1, T, D)
+    contiguous.  Returns the embedded tensor with x's shape and memory layout."""
     B, H, T, D = x.shape
     mem = x.transpose(1, 2)
     out = torch.empty_like(mem)
-    L.call('lc_rope_apply', L.ptr(mem), L.ptr(cos), L.ptr(sin), L.lc_dtype(x), B * T, H, D, L.ptr(out),
-           L.stream_of(x))
+    L.call('lc_rope_apply', L.ptr(mem), L.ptr(cos), L.ptr(sin), L.lc_dtype(x), B * T, H, D, cos.shape[0] * T,
+           L.ptr(out), L.stream_of(x))
     return out.transpose(1, 2)
 
 
@@ -38,7 +38,8 @@ def _rope_fits(q, k, cos, sin, unsqueeze_dim):
     if not (k.dtype == cos.dtype == sin.dtype == q.dtype):
         return False
     B, _, T, D = q.shape
-    if cos.shape != (B, T, D) or sin.shape != (B, T, D) or k.shape[0] != B or k.shape[2:] != (T, D):
+    if cos.shape not in ((B, T, D), (1, T, D)) or sin.shape != cos.shape or k.shape[0] != B \
+            or k.shape[2:] != (T, D):
         return False
     if D % (8 if q.dtype == torch.float32 else 16):
         return False
@@ -156,3 +157,34 @@ def rms_norm(module, x):
     if _checked[key]:
         return _rms_raw(x, w.data, eps)
     return module(x)
+
+
+@contextlib.contextmanager
+def fused_gated_mlp(mlp):
+    """While active, `type(mlp).forward` is down_proj(act_fn(gate_proj(x)) * up_proj(x)) with the
+    activation and the product in one kernel (gated_act).  Only swapped in if the class's own forward
+    gives the same bits on random data for this module's layout; yields whether it was."""
+    cls = type(mlp)
+    need = all(hasattr(mlp, a) for a in ('gate_proj', 'up_proj', 'down_proj', 'act_fn'))
+    w = getattr(getattr(mlp, 'gate_proj', None), 'weight', None)
+    if not need or w is None or not w.is_cuda or w.dtype not in _DTYPES:
+        yield False
+        return
+    orig = cls.forward
+
+    def forward(self, x):
+        return self.down_proj(gated_act(self.act_fn, self.gate_proj(x), self.up_proj(x)))
+    key = ('mlp', cls, str(w.device), w.dtype)
+    if key not in _checked:
+        g = torch.Generator().manual_seed(17)
+        t = torch.randn(2, 24, w.shape[1], generator=g).to(w.dtype).to(w.device)
+        with torch.no_grad():
+            _checked[key] = torch.equal(orig(mlp, t), forward(mlp, t))
+    if not _checked[key]:
+        yield False
+        return
+    cls.forward = forward
+    try:
+        yield True
+    finally:
+        cls.forward = orig

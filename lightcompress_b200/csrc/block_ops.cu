@@ -30,11 +30,12 @@ __device__ __forceinline__ void st16(T* p, const Vec16<T>& r) {
 }
 
 // One thread per 16-byte vector of the first half of a head and its partner in the second half.
-// x, out: [tokens][heads][D]; cs, sn: [tokens][D].
+// x, out: [tokens][heads][D]; cs, sn: [table_tokens][D], token t reading row t % table_tokens (one
+// table shared by all sequences of a batch when table_tokens is the sequence length).
 template <typename T>
 __global__ void __launch_bounds__(256) rope_kernel(const T* __restrict__ x, const T* __restrict__ cs,
                                                    const T* __restrict__ sn, T* __restrict__ out, int64_t tokens,
-                                                   int heads, int D) {
+                                                   int heads, int D, int64_t table_tokens) {
   using E = Elem<T>;
   constexpr int V = E::kPerVec;
   const int half_vecs = D / 2 / V;
@@ -43,7 +44,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const T* __restrict__ x, cons
        idx += (int64_t)gridDim.x * blockDim.x) {
     const int hv = (int)(idx % half_vecs);
     const int64_t th = idx / half_vecs;          // token * heads + head
-    const int64_t tok = th / heads;
+    const int64_t tok = (th / heads) % table_tokens;
     const T* xp = x + th * D + hv * V;
     const T* cp = cs + tok * D + hv * V;
     const T* sp = sn + tok * D + hv * V;
@@ -170,11 +171,11 @@ unsigned grid_for(int64_t work_items, int threads) {
 
 template <typename T>
 int rope_launch(const void* x, const void* cs, const void* sn, void* out, int64_t tokens, int heads, int D,
-                cudaStream_t st) {
+                int64_t table_tokens, cudaStream_t st) {
   const int64_t total = tokens * heads * (D / 2 / Elem<T>::kPerVec);
   rope_kernel<T><<<grid_for(total, 256), 256, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(cs),
                                                        static_cast<const T*>(sn), static_cast<T*>(out), tokens, heads,
-                                                       D);
+                                                       D, table_tokens);
   LC_LAUNCH_CHECK();
   return LC_OK;
 }
@@ -183,18 +184,20 @@ int rope_launch(const void* x, const void* cs, const void* sn, void* out, int64_
 }  // namespace lc
 
 extern "C" LC_API int lc_rope_apply(const void* x, const void* cos_tab, const void* sin_tab, int dtype,
-                                    int64_t tokens, int heads, int head_dim, void* out, lc_stream_t stream) {
+                                    int64_t tokens, int heads, int head_dim, int64_t table_tokens, void* out,
+                                    lc_stream_t stream) {
   using namespace lc;
   if (!x || !cos_tab || !sin_tab || !out) return LC_ERR_ARG;
-  if (tokens <= 0 || heads <= 0 || head_dim <= 0) return LC_ERR_ARG;
+  if (tokens <= 0 || heads <= 0 || head_dim <= 0 || table_tokens <= 0 || tokens % table_tokens != 0) return LC_ERR_ARG;
   const int per_vec = dtype == LC_F32 ? 4 : 8;
   if (head_dim % (2 * per_vec) != 0) return LC_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(cos_tab) || !aligned16(sin_tab) || !aligned16(out)) return LC_ERR_ALIGN;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case LC_F32: return rope_launch<float>(x, cos_tab, sin_tab, out, tokens, heads, head_dim, st);
-    case LC_BF16: return rope_launch<__nv_bfloat16>(x, cos_tab, sin_tab, out, tokens, heads, head_dim, st);
-    case LC_F16: return rope_launch<__half>(x, cos_tab, sin_tab, out, tokens, heads, head_dim, st);
+    case LC_F32: return rope_launch<float>(x, cos_tab, sin_tab, out, tokens, heads, head_dim, table_tokens, st);
+    case LC_BF16:
+      return rope_launch<__nv_bfloat16>(x, cos_tab, sin_tab, out, tokens, heads, head_dim, table_tokens, st);
+    case LC_F16: return rope_launch<__half>(x, cos_tab, sin_tab, out, tokens, heads, head_dim, table_tokens, st);
     default: return LC_ERR_ARG;
   }
 }

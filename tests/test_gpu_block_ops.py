@@ -32,6 +32,26 @@ def test_rope_matches_the_op_chain(dtype, shape):
     oq, ok = block_ops.rope_apply_one(q, cos, sin), block_ops.rope_apply_one(k, cos, sin)
     assert oq.shape == rq.shape and (H == 1 or oq.stride() == rq.stride())
     assert torch.equal(oq, rq) and torch.equal(ok, rk)
+    # one table shared by all sequences of the batch: cos / sin of shape (1, T, D)
+    rq1, _ = _rope_chain(q, k, cos[:1], sin[:1])
+    assert torch.equal(block_ops.rope_apply_one(q, cos[:1].contiguous(), sin[:1].contiguous()), rq1)
+
+
+def test_fused_gated_mlp_swaps_and_restores_the_forward():
+    from lightcompress_b200 import block_ops
+    import transformers.models.llama.modeling_llama as ml
+    from transformers import LlamaConfig
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_attention_heads=4, num_key_value_heads=4,
+                      num_hidden_layers=1, vocab_size=64)
+    mlp = ml.LlamaMLP(cfg).to(torch.bfloat16).cuda()
+    x = torch.randn(3, 40, 256).to(torch.bfloat16).cuda()
+    orig = ml.LlamaMLP.forward
+    with torch.no_grad():
+        ref = mlp(x)
+        with block_ops.fused_gated_mlp(mlp) as active:
+            assert active and ml.LlamaMLP.forward is not orig
+            assert torch.equal(mlp(x), ref)
+    assert ml.LlamaMLP.forward is orig
 
 
 def test_rope_patch_swaps_and_restores_the_module_function():
