@@ -21,6 +21,8 @@
 //
 // Everything is enqueued on the caller's stream; nothing synchronises.  A non-positive pivot sets
 // the caller's status word to LC_ERR_NOT_PD (the reference raises torch.linalg.LinAlgError there).
+#include <vector>
+
 #include "lc_common.cuh"
 #include "tf32x3_gemm.cuh"
 
@@ -190,11 +192,20 @@ __global__ void __launch_bounds__(kLeafThreads, 1) chol_leaf_kernel(const float*
   if (tid == 0 && s_bad && status) atomicCAS(status, 0, (int)LC_ERR_NOT_PD);
 }
 
-// lo = x - tf32_truncate(x) on a rows x cols region (pitch ld for both)
-__global__ void __launch_bounds__(256) split_region_kernel(const float* __restrict__ x, float* __restrict__ lo,
-                                                           int64_t rows, int64_t cols, int64_t ld) {
-  const int64_t vec_per_row = cols >> 2;
-  const int64_t total = rows * vec_per_row;
+constexpr int kMaxRegions = 64;
+
+// lo = x - tf32_truncate(x) on up to kMaxRegions rows x cols regions (one pitch for all; region blockIdx.y)
+struct SplitRegions {
+  const float* x[kMaxRegions];
+  float* lo[kMaxRegions];
+  int rows[kMaxRegions], cols[kMaxRegions];
+};
+__global__ void __launch_bounds__(256) split_region_kernel(const __grid_constant__ SplitRegions rg, int64_t ld) {
+  const int g = blockIdx.y;
+  const float* x = rg.x[g];
+  float* lo = rg.lo[g];
+  const int64_t vec_per_row = rg.cols[g] >> 2;
+  const int64_t total = (int64_t)rg.rows[g] * vec_per_row;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = idx / vec_per_row, c = (idx % vec_per_row) << 2;
@@ -205,12 +216,23 @@ __global__ void __launch_bounds__(256) split_region_kernel(const float* __restri
   }
 }
 
-// out = in^T on an n x n block (pitches ldi / ldo), with the low part of the result
-__global__ void __launch_bounds__(256) transpose_split_kernel(const float* __restrict__ in, int64_t ldi,
-                                                              float* __restrict__ out, float* __restrict__ out_lo,
-                                                              int64_t ldo, int n) {
+// out = in^T on up to kMaxRegions square blocks (block blockIdx.z, edge n[z]; pitches ldi / ldo), with the
+// low part of the result
+struct TransposeBlocks {
+  const float* in[kMaxRegions];
+  float* out[kMaxRegions];
+  float* out_lo[kMaxRegions];
+  int n[kMaxRegions];
+};
+__global__ void __launch_bounds__(256) transpose_split_kernel(const __grid_constant__ TransposeBlocks tb, int64_t ldi,
+                                                              int64_t ldo) {
   __shared__ float tile[32][33];
+  const int z = blockIdx.z, n = tb.n[z];
   const int bx = blockIdx.x * 32, by = blockIdx.y * 32;
+  if (bx >= n || by >= n) return;
+  const float* in = tb.in[z];
+  float* out = tb.out[z];
+  float* out_lo = tb.out_lo[z];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
   for (int r = ty; r < 32; r += 8)
     if (by + r < n && bx + tx < n) tile[r][tx] = in[(int64_t)(by + r) * ldi + bx + tx];
@@ -269,8 +291,8 @@ int prepare_operands(Factor& f, bool with_cholesky) {
   if ((rc = gemm_mat_init(&f.mG, f.G, f.G_lo, f.n, f.n, f.n)) != LC_OK) return rc;
   if ((rc = gemm_mat_init(&f.mVt, f.Vt, f.Vt_lo, f.n, f.n, f.n)) != LC_OK) return rc;
   if (f.n > kB) {
-    if ((rc = gemm_mat_init(&f.mT, f.T, f.T_lo, f.h, f.h, f.h)) != LC_OK) return rc;
-    if ((rc = gemm_mat_init(&f.mR, f.R, f.R_lo, f.h, f.h, f.h)) != LC_OK) return rc;
+    if ((rc = gemm_mat_init(&f.mT, f.T, f.T_lo, f.n, f.h, f.h)) != LC_OK) return rc;
+    if ((rc = gemm_mat_init(&f.mR, f.R, f.R_lo, f.n, f.h, f.h)) != LC_OK) return rc;
   }
   if (with_cholesky) {
     if ((rc = gemm_mat_init(&f.mVd, f.Vd, f.Vd_lo, f.n, kB, kB)) != LC_OK) return rc;
@@ -279,37 +301,111 @@ int prepare_operands(Factor& f, bool with_cholesky) {
   return LC_OK;
 }
 
-int split_region(const Factor& f, const float* x, float* lo, int64_t rows, int64_t cols, int64_t ld) {
-  split_region_kernel<<<grid_1d(rows * (cols >> 2)), 256, 0, f.st>>>(x, lo, rows, cols, ld);
-  LC_LAUNCH_CHECK();
+struct Region {
+  const float* x;
+  float* lo;
+  int64_t rows, cols;
+};
+
+int split_regions(const Factor& f, const Region* r, int count, int64_t ld) {
+  for (int first = 0; first < count; first += kMaxRegions) {
+    const int nb = count - first < kMaxRegions ? count - first : kMaxRegions;
+    SplitRegions rg;
+    int64_t most = 1;
+    for (int i = 0; i < nb; ++i) {
+      rg.x[i] = r[first + i].x;
+      rg.lo[i] = r[first + i].lo;
+      rg.rows[i] = (int)r[first + i].rows;
+      rg.cols[i] = (int)r[first + i].cols;
+      const int64_t work = r[first + i].rows * (r[first + i].cols >> 2);
+      most = work > most ? work : most;
+    }
+    const dim3 grid(grid_1d(most), (unsigned)nb);
+    split_region_kernel<<<grid, 256, 0, f.st>>>(rg, ld);
+    LC_LAUNCH_CHECK();
+  }
   return LC_OK;
 }
 
-// Vt[lo:hi, lo:hi] from its two diagonal halves (leaves are already in place)
-int invert_range(const Factor& f, int64_t lo, int64_t hi) {
+int split_region(const Factor& f, const float* x, float* lo, int64_t rows, int64_t cols, int64_t ld) {
+  const Region r = {x, lo, rows, cols};
+  return split_regions(f, &r, 1, ld);
+}
+
+struct Node {
+  int64_t lo, h, hi;   // index range [lo, hi) split at h (multiples of 128)
+};
+
+// internal nodes of the recursion by depth; a range of one diagonal block is a leaf
+void collect_nodes(int64_t lo, int64_t hi, size_t depth, std::vector<std::vector<Node>>& levels) {
   const int64_t len = hi - lo;
-  if (len <= kB) return LC_OK;
+  if (len <= kB) return;
   const int64_t h = lo + ((len / kB + 1) / 2) * kB;
+  if (levels.size() <= depth) levels.resize(depth + 1);
+  levels[depth].push_back({lo, h, hi});
+  collect_nodes(lo, h, depth + 1, levels);
+  collect_nodes(h, hi, depth + 1, levels);
+}
+
+// Vt[hi, lo] = -Vt[hi, hi] (G[lo, hi])^T Vt[lo, lo] for every node of one level: two batched GEMMs, one
+// batched transpose, two batched splits.  Scratch: node j uses rows [h_j, hi_j) of T and R (n x f.h each),
+// which are disjoint across the nodes of a level.  [c0, c1): column slice of the off-diagonal block
+// (whole block: 0, h - lo), only meaningful for a level of one node.
+int invert_level(const Factor& f, const std::vector<Node>& nodes, int64_t c0 = 0, int64_t c1 = -1) {
+  const int64_t n = f.n, hp = f.h;
+  const int count = (int)nodes.size();
+  std::vector<GemmItem> g1(count), g2(count);
+  std::vector<Region> rt(count), rv(count);
   int rc;
-  if ((rc = invert_range(f, lo, h)) != LC_OK) return rc;
-  if ((rc = invert_range(f, h, hi)) != LC_OK) return rc;
-  const int64_t n = f.n, m1 = h - lo, m2 = hi - h;
-  // T (m2 x m1) = G[lo:h, h:hi]^T Vt[lo:h, lo:h]
-  if ((rc = tf32x3_gemm_launch(f.T, f.h, f.mG, lo, h, f.mVt, lo, lo, m2, m1, m1, 0, 1.f, kGemmBLower, f.status,
-                               f.st)) != LC_OK)
-    return rc;
-  if ((rc = split_region(f, f.T, f.T_lo, m2, m1, f.h)) != LC_OK) return rc;
-  // R (m2 x m2) = Vt[h:hi, h:hi]^T (upper)
-  {
-    const dim3 grid((unsigned)((m2 + 31) / 32), (unsigned)((m2 + 31) / 32));
-    transpose_split_kernel<<<grid, 256, 0, f.st>>>(f.Vt + h * n + h, n, f.R, f.R_lo, f.h, (int)m2);
+  for (int first = 0; first < count; first += kMaxRegions) {
+    const int nb = count - first < kMaxRegions ? count - first : kMaxRegions;
+    TransposeBlocks tb;
+    int64_t most = 1;
+    for (int i = 0; i < nb; ++i) {
+      const Node& nd = nodes[first + i];
+      const int64_t m2 = nd.hi - nd.h;
+      tb.in[i] = f.Vt + nd.h * n + nd.h;
+      tb.out[i] = f.R + nd.h * hp;
+      tb.out_lo[i] = f.R_lo + nd.h * hp;
+      tb.n[i] = (int)m2;
+      most = m2 > most ? m2 : most;
+    }
+    const dim3 grid((unsigned)((most + 31) / 32), (unsigned)((most + 31) / 32), (unsigned)nb);
+    transpose_split_kernel<<<grid, 256, 0, f.st>>>(tb, n, hp);
     LC_LAUNCH_CHECK();
   }
-  // Vt[h:hi, lo:h] = -R^T T
-  if ((rc = tf32x3_gemm_launch(f.Vt + h * n + lo, n, f.mR, 0, 0, f.mT, 0, 0, m2, m1, m2, 0, -1.f, kGemmAUpper,
-                               f.status, f.st)) != LC_OK)
+  for (int i = 0; i < count; ++i) {
+    const Node& nd = nodes[i];
+    const int64_t m1 = nd.h - nd.lo, m2 = nd.hi - nd.h;
+    const int64_t a = c1 < 0 ? 0 : c0, w = (c1 < 0 ? m1 : c1) - a;
+    // T (m2 x m1) = G[lo:h, h:hi]^T Vt[lo:h, lo:h]
+    g1[i].C = f.T + nd.h * hp + a;
+    g1[i].a_k0 = nd.lo, g1[i].a_m0 = nd.h, g1[i].b_k0 = nd.lo, g1[i].b_n0 = nd.lo + a;
+    g1[i].M = m2, g1[i].N = w, g1[i].K = m1, g1[i].b_tri_shift = a;
+    rt[i] = {f.T + nd.h * hp + a, f.T_lo + nd.h * hp + a, m2, w};
+    // Vt[h:hi, lo:h] = -R^T T, R = Vt[h:hi, h:hi]^T (upper)
+    g2[i].C = f.Vt + nd.h * n + nd.lo + a;
+    g2[i].a_k0 = nd.h, g2[i].a_m0 = 0, g2[i].b_k0 = nd.h, g2[i].b_n0 = a;
+    g2[i].M = m2, g2[i].N = w, g2[i].K = m2;
+    rv[i] = {f.Vt + nd.h * n + nd.lo + a, f.Vt_lo + nd.h * n + nd.lo + a, m2, w};
+  }
+  if ((rc = tf32x3_gemm_batched(f.mG, f.mVt, hp, g1.data(), count, 0, 1.f, kGemmBLower, f.status, f.st)) != LC_OK)
     return rc;
-  return split_region(f, f.Vt + h * n + lo, f.Vt_lo + h * n + lo, m2, m1, n);
+  if ((rc = split_regions(f, rt.data(), count, hp)) != LC_OK) return rc;
+  if ((rc = tf32x3_gemm_batched(f.mR, f.mT, n, g2.data(), count, 0, -1.f, kGemmAUpper, f.status, f.st)) != LC_OK)
+    return rc;
+  return split_regions(f, rv.data(), count, n);
+}
+
+// Vt[lo:hi, lo:hi] from its leaves, deepest level first.  skip_root: leave the top node to the caller.
+int invert_range(const Factor& f, int64_t lo, int64_t hi, bool skip_root = false) {
+  std::vector<std::vector<Node>> levels;
+  collect_nodes(lo, hi, 0, levels);
+  for (size_t d = levels.size(); d-- > (skip_root ? 1 : 0);) {
+    const int rc = invert_level(f, levels[d]);
+    if (rc != LC_OK) return rc;
+  }
+  return LC_OK;
 }
 
 int factorize(const Factor& f) {
@@ -352,22 +448,10 @@ int factorize(const Factor& f) {
 int invert_top_slice(const Factor& f, int64_t c0, int64_t c1) {
   const int64_t n = f.n;
   if (n <= kB) return LC_OK;
-  const int64_t h = ((n / kB + 1) / 2) * kB, m1 = h, m2 = n - h, w = c1 - c0;
-  int rc;
-  if ((rc = invert_range(f, 0, h)) != LC_OK) return rc;
-  if ((rc = invert_range(f, h, n)) != LC_OK) return rc;
-  if (w <= 0) return LC_OK;
-  if ((rc = tf32x3_gemm_launch(f.T + c0, f.h, f.mG, 0, h, f.mVt, 0, c0, m2, w, m1, 0, 1.f, kGemmBLower, f.status, f.st,
-                               c0)) != LC_OK)
-    return rc;
-  if ((rc = split_region(f, f.T + c0, f.T_lo + c0, m2, w, f.h)) != LC_OK) return rc;
-  {
-    const dim3 grid((unsigned)((m2 + 31) / 32), (unsigned)((m2 + 31) / 32));
-    transpose_split_kernel<<<grid, 256, 0, f.st>>>(f.Vt + h * n + h, n, f.R, f.R_lo, f.h, (int)m2);
-    LC_LAUNCH_CHECK();
-  }
-  return tf32x3_gemm_launch(f.Vt + h * n + c0, n, f.mR, 0, 0, f.mT, 0, c0, m2, w, m2, 0, -1.f, kGemmAUpper, f.status,
-                            f.st);
+  const int rc = invert_range(f, 0, n, true);
+  if (rc != LC_OK || c1 <= c0) return rc;
+  const std::vector<Node> root = {{0, ((n / kB + 1) / 2) * kB, n}};
+  return invert_level(f, root, c0, c1);
 }
 
 // Leaves and low parts common to the whole and the sliced inverse
@@ -396,9 +480,9 @@ void carve_inverse(Factor& f, const float* G, int64_t n, float* workspace, int32
   f.G_lo = p, p += n * n;
   f.Vt = p, p += n * n;
   f.Vt_lo = p, p += n * n;
-  f.T = p, p += h * h;
-  f.T_lo = p, p += h * h;
-  f.R = p, p += h * h;
+  f.T = p, p += n * h;
+  f.T_lo = p, p += n * h;
+  f.R = p, p += n * h;
   f.R_lo = p;
   f.Vd = f.Vd_lo = nullptr;
   f.status = status;
@@ -419,8 +503,8 @@ int invert_factor(const Factor& f) {
 extern "C" LC_API int64_t lc_gptq_factor_workspace_floats(int64_t n) {
   if (n <= 0) return 0;
   const int64_t h = ((n / 128 + 1) / 2) * 128;
-  // G, G_lo, Vt, Vt_lo (n^2 each), T, T_lo, R, R_lo (h^2 each), V_kk blocks and their low parts
-  return 4 * n * n + 4 * h * h + 2 * n * 128;
+  // G, G_lo, Vt, Vt_lo (n^2 each), T, T_lo, R, R_lo (n x h each), V_kk blocks and their low parts
+  return 4 * n * n + 4 * n * h + 2 * n * 128;
 }
 
 extern "C" LC_API int lc_gptq_factorize(float* A, int64_t n, float* U, float* U_lo, float* workspace,
@@ -443,10 +527,10 @@ extern "C" LC_API int lc_gptq_factorize(float* A, int64_t n, float* U, float* U_
   f.G_lo = p, p += n * n;
   f.Vt = p, p += n * n;
   f.Vt_lo = p, p += n * n;
-  f.T = p, p += h * h;
-  f.T_lo = p, p += h * h;
-  f.R = p, p += h * h;
-  f.R_lo = p, p += h * h;
+  f.T = p, p += n * h;
+  f.T_lo = p, p += n * h;
+  f.R = p, p += n * h;
+  f.R_lo = p, p += n * h;
   f.Vd = p, p += n * 128;
   f.Vd_lo = p;
   f.status = status;

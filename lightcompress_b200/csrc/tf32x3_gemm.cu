@@ -41,31 +41,46 @@ struct GemmMaps {
   CUtensorMap a_hi, a_lo, b_hi, b_lo;
 };
 
-struct GemmArgs {
+// One product of a batch: all problems of a launch share the operand matrices (tensor maps), the pitch
+// of C, beta, sign and flags, and differ in their sub-matrix origins and sizes.
+struct GemmProblem {
   float* C;
-  int32_t* status;
-  int64_t ldc;
   int a_k0, a_m0, b_k0, b_n0;   // origins of the operand sub-matrices inside their tensor maps
   int M, N, K;
-  int m_tiles, n_tiles;
+  int b_tri_shift;
+  int m_tiles;
+  int tile_end;                 // running tile count up to and including this problem
+};
+
+struct GemmArgs {
+  int32_t* status;
+  int64_t ldc;
+  int n_problems;
+  int total_tiles;
   int beta;
   float sign;
   int flags;
   int use3d;   // operand tiles fetched by one 3-D copy each instead of one 2-D copy per 32-float atom
-  int b_tri_shift;
+  GemmProblem p[kGemmMaxBatch];
 };
 
 struct TileWork {
+  int pi;          // problem index
   int m0, n0, k0, k1;
   bool skip;
 };
 
 __device__ __forceinline__ TileWork tile_work(const GemmArgs& a, int t) {
   TileWork w;
-  w.m0 = (t % a.m_tiles) * PM;
-  w.n0 = (t / a.m_tiles) * PN;
-  w.k0 = (a.flags & kGemmBLower) ? min(a.K, ((w.n0 + a.b_tri_shift) / PBK) * PBK) : 0;
-  w.k1 = (a.flags & kGemmAUpper) ? min(a.K, w.m0 + PM) : a.K;
+  int pi = 0;
+  while (pi + 1 < a.n_problems && t >= a.p[pi].tile_end) ++pi;
+  const GemmProblem& pr = a.p[pi];
+  const int local = t - (pi ? a.p[pi - 1].tile_end : 0);
+  w.pi = pi;
+  w.m0 = (local % pr.m_tiles) * PM;
+  w.n0 = (local / pr.m_tiles) * PN;
+  w.k0 = (a.flags & kGemmBLower) ? min(pr.K, ((w.n0 + pr.b_tri_shift) / PBK) * PBK) : 0;
+  w.k1 = (a.flags & kGemmAUpper) ? min(pr.K, w.m0 + PM) : pr.K;
   w.skip = (a.flags & kGemmUpperOnly) && (w.n0 + PN <= w.m0);
   return w;
 }
@@ -106,7 +121,7 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int n_tiles_total = a.m_tiles * a.n_tiles;
+  const int n_tiles_total = a.total_tiles;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -115,6 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
       for (int t = blockIdx.x; ok && t < n_tiles_total; t += gridDim.x) {
         const TileWork w = tile_work(a, t);
         if (w.skip) continue;
+        const int a_k0 = a.p[w.pi].a_k0, a_m0 = a.p[w.pi].a_m0, b_k0 = a.p[w.pi].b_k0, b_n0 = a.p[w.pi].b_n0;
         for (int krow = w.k0; krow < w.k1; krow += PBK, ++n) {
           const int s = n % PSTAGES;
           const uint32_t ph = (n / PSTAGES) & 1u;
@@ -123,28 +139,28 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
           const uint32_t sa = base + s * P_STAGE_BYTES;
           if (a.use3d) {
             // atoms land 2048 bytes apart, exactly like the per-atom copies below
-            tma_load_3d(sa, &maps.a_hi, 0, a.a_k0 + krow, (a.a_m0 + w.m0) / ATOM_F, full_bar(s));
-            tma_load_3d(sa + A_ATOMS * P_ATOM_BYTES, &maps.a_lo, 0, a.a_k0 + krow, (a.a_m0 + w.m0) / ATOM_F,
+            tma_load_3d(sa, &maps.a_hi, 0, a_k0 + krow, (a_m0 + w.m0) / ATOM_F, full_bar(s));
+            tma_load_3d(sa + A_ATOMS * P_ATOM_BYTES, &maps.a_lo, 0, a_k0 + krow, (a_m0 + w.m0) / ATOM_F,
                         full_bar(s));
-            tma_load_3d(sa + 2 * A_ATOMS * P_ATOM_BYTES, &maps.b_hi, 0, a.b_k0 + krow, (a.b_n0 + w.n0) / ATOM_F,
+            tma_load_3d(sa + 2 * A_ATOMS * P_ATOM_BYTES, &maps.b_hi, 0, b_k0 + krow, (b_n0 + w.n0) / ATOM_F,
                         full_bar(s));
-            tma_load_3d(sa + (2 * A_ATOMS + B_ATOMS) * P_ATOM_BYTES, &maps.b_lo, 0, a.b_k0 + krow,
-                        (a.b_n0 + w.n0) / ATOM_F, full_bar(s));
+            tma_load_3d(sa + (2 * A_ATOMS + B_ATOMS) * P_ATOM_BYTES, &maps.b_lo, 0, b_k0 + krow,
+                        (b_n0 + w.n0) / ATOM_F, full_bar(s));
             issued = n + 1;
             continue;
           }
 #pragma unroll
           for (int q = 0; q < A_ATOMS; ++q) {
-            tma_load_2d(sa + q * P_ATOM_BYTES, &maps.a_hi, a.a_m0 + w.m0 + q * ATOM_F, a.a_k0 + krow, full_bar(s));
-            tma_load_2d(sa + (A_ATOMS + q) * P_ATOM_BYTES, &maps.a_lo, a.a_m0 + w.m0 + q * ATOM_F, a.a_k0 + krow,
+            tma_load_2d(sa + q * P_ATOM_BYTES, &maps.a_hi, a_m0 + w.m0 + q * ATOM_F, a_k0 + krow, full_bar(s));
+            tma_load_2d(sa + (A_ATOMS + q) * P_ATOM_BYTES, &maps.a_lo, a_m0 + w.m0 + q * ATOM_F, a_k0 + krow,
                         full_bar(s));
           }
 #pragma unroll
           for (int q = 0; q < B_ATOMS; ++q) {
-            tma_load_2d(sa + (2 * A_ATOMS + q) * P_ATOM_BYTES, &maps.b_hi, a.b_n0 + w.n0 + q * ATOM_F, a.b_k0 + krow,
+            tma_load_2d(sa + (2 * A_ATOMS + q) * P_ATOM_BYTES, &maps.b_hi, b_n0 + w.n0 + q * ATOM_F, b_k0 + krow,
                         full_bar(s));
-            tma_load_2d(sa + (2 * A_ATOMS + B_ATOMS + q) * P_ATOM_BYTES, &maps.b_lo, a.b_n0 + w.n0 + q * ATOM_F,
-                        a.b_k0 + krow, full_bar(s));
+            tma_load_2d(sa + (2 * A_ATOMS + B_ATOMS + q) * P_ATOM_BYTES, &maps.b_lo, b_n0 + w.n0 + q * ATOM_F,
+                        b_k0 + krow, full_bar(s));
           }
           issued = n + 1;
         }
@@ -215,18 +231,20 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
       if (!mbar_wait(accum_full(buf), (tiles_done >> 1) & 1u, abort_flag) || *abort_flag) break;
       tcgen05_fence_after();
       const uint32_t tmem_acc = tmem_base + buf * PN;
+      const int pM = a.p[w.pi].M, pN = a.p[w.pi].N;
+      float* const pC = a.p[w.pi].C;
       const int m = w.m0 + q * 32 + lane;
 #pragma unroll 1
       for (int cc = 0; cc < PN / 32; ++cc) {
         const int n0 = w.n0 + cc * 32;
-        if (n0 >= a.N) break;
+        if (n0 >= pN) break;
         float v[32];
         tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(cc * 32), v);
-        if (m < a.M) {
-          float* row = a.C + (int64_t)m * a.ldc + n0;
+        if (m < pM) {
+          float* row = pC + (int64_t)m * a.ldc + n0;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
-            if (n0 + j < a.N) {
+            if (n0 + j < pN) {
               float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
               if (a.beta) c = *reinterpret_cast<float4*>(row + j);
               c.x = fmaf(a.sign, v[j], c.x);
@@ -321,47 +339,67 @@ int gemm_mat_init(GemmMat* m, const float* hi, const float* lo, int64_t k_extent
   return LC_OK;
 }
 
+int tf32x3_gemm_batched(const GemmMat& A, const GemmMat& B, int64_t ldc, const GemmItem* items, int count, int beta,
+                        float sign, int flags, int32_t* status, cudaStream_t st) {
+  if (count <= 0) return LC_OK;
+  if (ldc % 4 != 0) return LC_ERR_SHAPE;
+  if (A.k_extent > (1 << 30) || A.mn_extent > (1 << 30) || B.k_extent > (1 << 30) || B.mn_extent > (1 << 30))
+    return LC_ERR_SHAPE;
+  int sms = 0, rc;
+  if ((rc = device_setup(&sms)) != LC_OK) return rc;
+  for (int first = 0; first < count; first += kGemmMaxBatch) {
+    const int nb = count - first < kGemmMaxBatch ? count - first : kGemmMaxBatch;
+    GemmMaps maps;
+    GemmArgs a;
+    bool all3 = A.has3 && B.has3;
+    int tiles = 0, np = 0;
+    for (int i = 0; i < nb; ++i) {
+      const GemmItem& it = items[first + i];
+      if (it.M <= 0 || it.N <= 0 || it.K <= 0) continue;
+      if (it.K % PBK != 0 || it.M % 4 != 0 || it.N % 4 != 0 || it.a_m0 % 4 != 0 || it.b_n0 % 4 != 0) return LC_ERR_SHAPE;
+      if (it.a_k0 < 0 || it.a_m0 < 0 || it.b_k0 < 0 || it.b_n0 < 0 || it.a_k0 + it.K > A.k_extent ||
+          it.a_m0 + it.M > A.mn_extent || it.b_k0 + it.K > B.k_extent || it.b_n0 + it.N > B.mn_extent)
+        return LC_ERR_SHAPE;
+      if (it.b_tri_shift < 0 || ((flags & kGemmBLower) && it.b_tri_shift + it.N > it.K)) return LC_ERR_SHAPE;
+      if (!aligned16(it.C)) return LC_ERR_ALIGN;
+      all3 = all3 && it.a_m0 % ATOM_F == 0 && it.b_n0 % ATOM_F == 0;
+      GemmProblem& pr = a.p[np++];
+      pr.C = it.C;
+      pr.a_k0 = (int)it.a_k0, pr.a_m0 = (int)it.a_m0, pr.b_k0 = (int)it.b_k0, pr.b_n0 = (int)it.b_n0;
+      pr.M = (int)it.M, pr.N = (int)it.N, pr.K = (int)it.K;
+      pr.b_tri_shift = (int)it.b_tri_shift;
+      pr.m_tiles = (int)((it.M + PM - 1) / PM);
+      tiles += pr.m_tiles * (int)((it.N + PN - 1) / PN);
+      pr.tile_end = tiles;
+    }
+    if (np == 0) continue;
+    a.use3d = all3 ? 1 : 0;
+    maps.a_hi = all3 ? A.map3a_hi : A.map_hi;
+    maps.a_lo = all3 ? A.map3a_lo : A.map_lo;
+    maps.b_hi = all3 ? B.map3b_hi : B.map_hi;
+    maps.b_lo = all3 ? B.map3b_lo : B.map_lo;
+    a.status = status;
+    a.ldc = ldc;
+    a.n_problems = np;
+    a.total_tiles = tiles;
+    a.beta = beta ? 1 : 0;
+    a.sign = sign;
+    a.flags = flags;
+    tf32x3_gemm_kernel<<<tiles < sms ? tiles : sms, kThreads, P_SMEM_BYTES, st>>>(maps, a);
+    LC_LAUNCH_CHECK();
+  }
+  return LC_OK;
+}
+
 int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, int64_t a_m0, const GemmMat& B,
                        int64_t b_k0, int64_t b_n0, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
                        int32_t* status, cudaStream_t st, int64_t b_tri_shift) {
-  if (M <= 0 || N <= 0 || K <= 0) return LC_OK;
-  if (K % PBK != 0 || M % 4 != 0 || N % 4 != 0 || ldc % 4 != 0 || a_m0 % 4 != 0 || b_n0 % 4 != 0) return LC_ERR_SHAPE;
-  if (b_tri_shift < 0 || ((flags & kGemmBLower) && b_tri_shift + N > K)) return LC_ERR_SHAPE;
-  if (a_k0 < 0 || a_m0 < 0 || b_k0 < 0 || b_n0 < 0 || a_k0 + K > A.k_extent || a_m0 + M > A.mn_extent ||
-      b_k0 + K > B.k_extent || b_n0 + N > B.mn_extent)
-    return LC_ERR_SHAPE;
-  if (A.k_extent > (1 << 30) || A.mn_extent > (1 << 30) || B.k_extent > (1 << 30) || B.mn_extent > (1 << 30))
-    return LC_ERR_SHAPE;
-  if (!aligned16(C)) return LC_ERR_ALIGN;
-  GemmMaps maps;
-  GemmArgs a;
-  a.use3d = (A.has3 && B.has3 && a_m0 % ATOM_F == 0 && b_n0 % ATOM_F == 0) ? 1 : 0;
-  maps.a_hi = a.use3d ? A.map3a_hi : A.map_hi;
-  maps.a_lo = a.use3d ? A.map3a_lo : A.map_lo;
-  maps.b_hi = a.use3d ? B.map3b_hi : B.map_hi;
-  maps.b_lo = a.use3d ? B.map3b_lo : B.map_lo;
-  a.C = C;
-  a.status = status;
-  a.ldc = ldc;
-  a.a_k0 = (int)a_k0;
-  a.a_m0 = (int)a_m0;
-  a.b_k0 = (int)b_k0;
-  a.b_n0 = (int)b_n0;
-  a.M = (int)M;
-  a.N = (int)N;
-  a.K = (int)K;
-  a.m_tiles = (int)((M + PM - 1) / PM);
-  a.n_tiles = (int)((N + PN - 1) / PN);
-  a.beta = beta ? 1 : 0;
-  a.sign = sign;
-  a.flags = flags;
-  a.b_tri_shift = (int)b_tri_shift;
-  int sms = 0, rc;
-  if ((rc = device_setup(&sms)) != LC_OK) return rc;
-  const int tiles = a.m_tiles * a.n_tiles;
-  tf32x3_gemm_kernel<<<tiles < sms ? tiles : sms, kThreads, P_SMEM_BYTES, st>>>(maps, a);
-  LC_LAUNCH_CHECK();
-  return LC_OK;
+  GemmItem it;
+  it.C = C;
+  it.a_k0 = a_k0, it.a_m0 = a_m0, it.b_k0 = b_k0, it.b_n0 = b_n0;
+  it.M = M, it.N = N, it.K = K;
+  it.b_tri_shift = b_tri_shift;
+  return tf32x3_gemm_batched(A, B, ldc, &it, 1, beta, sign, flags, status, st);
 }
 
 int tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, int64_t lda, const float* B_hi,

@@ -37,6 +37,16 @@ int tf32x3_gemm_launch(float* C, int64_t ldc, const GemmMat& A, int64_t a_k0, in
                        int64_t b_k0, int64_t b_n0, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
                        int32_t* status, cudaStream_t st, int64_t b_tri_shift = 0);
 
+// Several products in one launch: same operand matrices, pitch of C, beta, sign and flags; each item
+// has its own sub-matrix origins, sizes and C.  Used for the many small products of one recursion level.
+constexpr int kGemmMaxBatch = 56;   // items per launch (more are issued in several launches)
+struct GemmItem {
+  float* C = nullptr;
+  int64_t a_k0 = 0, a_m0 = 0, b_k0 = 0, b_n0 = 0, M = 0, N = 0, K = 0, b_tri_shift = 0;
+};
+int tf32x3_gemm_batched(const GemmMat& A, const GemmMat& B, int64_t ldc, const GemmItem* items, int count, int beta,
+                        float sign, int flags, int32_t* status, cudaStream_t st);
+
 // One-off product: prepares both operands and launches.
 int tf32x3_gemm_tn(float* C, int64_t ldc, const float* A_hi, const float* A_lo, int64_t lda, const float* B_hi,
                    const float* B_lo, int64_t ldb, int64_t M, int64_t N, int64_t K, int beta, float sign, int flags,
