@@ -445,7 +445,7 @@ def main():
                            'mlp.down_proj': 'down'}
             # steps_left: steps still to run in the current (warm-up or timed) sequence; pending: the
             # copy events of activations already on their way for the next step, and their buffer
-            e2e_state = {'steps_left': 0, 'pending': None, 'buf': 0}
+            e2e_state = {'steps_left': 0, 'pending': None, 'buf': 0, 'prev_block': None}
 
             def start_input_copy(buf):
                 evs = []
@@ -457,32 +457,48 @@ def main():
                         evs.append(ev)
                 return evs
 
+            p_stages = [[torch.empty_like(p, device=dev) for p in host_params] for _ in range(2)] if rank == 0 else None
+
+            def start_copies(buf):
+                """Parameters (rank 0) and activations of one step, host -> staging buffers `buf`."""
+                p_ev = None
+                if rank == 0:
+                    with torch.cuda.stream(copy_in):
+                        for d, hp in zip(p_stages[buf], host_params):
+                            d.copy_(hp, non_blocking=True)
+                        p_ev = torch.cuda.Event()
+                        p_ev.record(copy_in)
+                return p_ev, start_input_copy(buf)
+
             def e2e_step():
-                # Host -> device copies of the activations run on their own stream, chunk by chunk, into
-                # one of two staging buffers; the first stage of the block waits for the chunk it is about
-                # to read.  While a step computes, the activations of the NEXT step of the same sequence
-                # of steps are already copied into the other buffer (a caller that streams a model's
-                # blocks through the GPU prefetches the same way); the first step of a sequence copies its
-                # own inputs, the last one prefetches nothing, so every copy lies inside the timed region.
+                # Host -> device copies run on their own stream into one of two sets of staging buffers:
+                # the block's parameters, then the activations chunk by chunk; the first stage of the block
+                # waits for the chunk it is about to read.  While a step computes, the parameters and
+                # activations of the NEXT step of the same sequence of steps are already copied into the
+                # other set (a caller that streams a model's blocks through the GPU prefetches the same
+                # way); the first step of a sequence copies its own inputs, the last one prefetches nothing
+                # and waits for its results to reach the host, so every copy lies inside the timed region.
                 # Each subset's quantised weights go back to the host on a third stream while the next
-                # stage computes (the reference's block.cuda() / block.cpu()).
+                # stage (or the next step) computes (the reference's block.cuda() / block.cpu()).
                 main_s = torch.cuda.current_stream()
                 copy_in.wait_stream(main_s)
                 block = copy.deepcopy(master)
+                if e2e_state['pending'] is None:
+                    e2e_state['pending'] = start_copies(e2e_state['buf'])
+                (p_ev, evs), buf = e2e_state['pending'], e2e_state['buf']
                 # the block's parameters cross PCIe once (rank 0) and reach the other ranks over NVLink
-                for p, hp in zip(block.parameters(), host_params):
+                if rank == 0:
+                    main_s.wait_event(p_ev)
+                for i, p in enumerate(block.parameters()):
                     if rank == 0:
-                        p.data.copy_(hp, non_blocking=True)
+                        p.data.copy_(p_stages[buf][i], non_blocking=True)
                     if world > 1:
                         dist.broadcast(p.data, src=0)
-                if e2e_state['pending'] is None:
-                    e2e_state['pending'] = start_input_copy(e2e_state['buf'])
-                evs, buf = e2e_state['pending'], e2e_state['buf']
                 x_stage = x_stages[buf]
                 e2e_state['steps_left'] -= 1
                 if e2e_state['steps_left'] > 0:
                     e2e_state['buf'] = 1 - buf
-                    e2e_state['pending'] = start_input_copy(1 - buf)
+                    e2e_state['pending'] = start_copies(1 - buf)
                 else:
                     e2e_state['pending'] = None
                 mods = dict(block.named_modules())
@@ -507,7 +523,12 @@ def main():
                 runner.on_input, runner.on_subset_done = on_input, on_subset_done
                 outs = runner.block_opt(block, [x_stage[i:i + bs] for i in range(0, n_seq, bs)], kwargs)
                 runner.on_input = runner.on_subset_done = None
-                main_s.wait_stream(copy_out)
+                # the device-to-host copies of the last subset may still run while the next step starts; the
+                # block they read from stays referenced until then.  The last step of a sequence waits.
+                e2e_state['prev_block'] = block
+                if e2e_state['steps_left'] <= 0:
+                    main_s.wait_stream(copy_out)
+                    e2e_state['prev_block'] = None
                 return outs
             h2d = int(X_host.numel() * 2 * world + sum(p.numel() * 2 for p in block_host.parameters()))   # whole job
             d2h = int(sum(r * c * 4 for r, c in LINEAR_SHAPES))
@@ -626,9 +647,10 @@ def main():
         e2e_ms = timed(e2e_step, args.steps) / args.steps
         e2e = {'value': 1e3 / e2e_ms, 'unit': UNIT, 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': h2d,
                'd2h_bytes_per_step': d2h,
-               'overlap': ('copies on side streams; the activations of step s+1 are prefetched into a second '
-                           'staging buffer while step s computes (not for the first step, none after the last: '
-                           'all copies lie inside the timed region)') if args.workload == 'block' else 'none'}
+               'overlap': ('copies on side streams; the parameters and activations of step s+1 are prefetched into '
+                           'a second set of staging buffers while step s computes (not for the first step, none '
+                           'after the last, which also waits for its results on the host: all copies lie inside '
+                           'the timed region)') if args.workload == 'block' else 'none'}
     clocks = sampler.stop() if sampler else None
 
     # ---- the other two headline kernels, timed alone (HBM-bound family 1) ----------------------
