@@ -682,7 +682,7 @@ def main():
                 'traffic': None}
     # DRAM bytes per 16384-token launch from the ncu captures summarised in profiles/hessian_umma_C4096.md
     # (dram__bytes_read.sum + dram__bytes_write.sum); the bench launches the same shapes
-    ncu_traffic = {4096: 213.3e6, 11008: 3321.0e6}
+    ncu_traffic = {4096: 213.7e6, 11008: 2833.0e6}
     if all(c in ncu_traffic and abs(d[2] / d[0] - 16384) < 1 for c, d in hess.items()):
         roofline['traffic'] = sum(d[0] * ncu_traffic[c] for c, d in hess.items()) / n_l
         roofline['traffic_source'] = 'ncu, per launch, weighted over the launch mix of the step'
