@@ -537,9 +537,9 @@ def main():
         #   Hessian launches, 4 diag; per distinct Hessian (3 x C=4096, 1 x C=11008): damp + permute,
         #   low-part split, leaf inverse, flip, and 5 launches (2 GEMMs, 2 splits, 1 transpose) per internal
         #   node of the recursive triangular inverse (C/128 - 1 nodes);
-        #   per linear: permute W, un-permute, deploy-time fake quant, and per 128-column block the block
-        #   kernel plus one eager GEMM (not for the last block of a 1024-column panel), per panel but the
-        #   last one lazy GEMM;
+        #   per subset (the rows of its linears are solved as one stacked matrix): permute W, un-permute, and
+        #   per 128-column block the block kernel plus the eager / sub-panel / panel updates counted below;
+        #   per linear the deploy-time fake quant;
         #   per sequence: 2 RMS norms, 2 rotary embeddings, 1 SiLU-gate.
         n_calls = -(-n_seq // bs)
 
@@ -550,7 +550,7 @@ def main():
             return blocks + (blocks - subs) + (subs - panels) + (panels - 1)
         launches = (4 * -(-n_calls // HESSIAN_BATCH) + 4
                     + sum(2 + 1 + 1 + 1 + 5 * (c // 128 - 1) for c in (HID, HID, HID, INTER))
-                    + sum(3 + solver_launches(c) for r, c in LINEAR_SHAPES)
+                    + sum(2 + solver_launches(c) for c in (HID, HID, HID, INTER)) + len(LINEAR_SHAPES)
                     + 5 * n_calls)
     else:
         W_host = make_linear_weight().pin_memory() if not args.no_e2e else make_linear_weight()

@@ -158,55 +158,59 @@ class GPTQBlockwise:
         layers = [getattr(*subset[n]) for n in names]
         H, hscale = self.solver._finish_hessian(names[0])
         fac = self.solver.factorize(H, hscale)       # shared by the linears of the subset
+        # The rows of all linears of a subset are independent given the shared factor: they are solved
+        # as one stacked matrix (q/k/v: 12288 rows, gate/up: 22016), which cuts the number of latency-bound
+        # 128-column steps by the number of linears; in a process group every rank takes a row range.
+        stacked = layers[0].weight.data if len(layers) == 1 else torch.cat([l.weight.data for l in layers], 0)
         if world == 1:
-            for n, layer in zip(names, layers):
-                self.solver._install(layer, self.solver.solve(layer.weight.data, H, hscale, factor=fac))
+            res = self.solver.solve(stacked, H, hscale, factor=fac)
         else:
-            self._sharded_solve(names, layers, fac, rank, world)
+            res = self._sharded_solve(stacked, fac, rank, world)
+        n_groups = (H.shape[0] + 127) // 128
+        r0 = 0
+        for layer in layers:
+            r1 = r0 + layer.weight.shape[0]
+            part = {'weight': res['weight'][r0:r1], 'buf_scales': res['buf_scales'][r0 * n_groups:r1 * n_groups],
+                    'buf_zeros': None if res['buf_zeros'] is None else res['buf_zeros'][r0 * n_groups:r1 * n_groups],
+                    'buf_perm': res['buf_perm'], 'buf_invperm': res['buf_invperm']}
+            self.solver._install(layer, part)
+            r0 = r1
         for n in names:
             self.solver.layers_cache.pop(n, None)
         if self.on_subset_done is not None:
             self.on_subset_done(names)
 
-    def _sharded_solve(self, names, layers, fac, rank, world):
+    def _sharded_solve(self, stacked, fac, rank, world):
+        """Row range `rank` of the stacked weight solved here, all ranges broadcast: every rank returns
+        the same full result."""
         H = fac['H']
-        # units = (linear, row range); a linear is cut in max(1, world // n_linears) row chunks
-        chunks = max(1, world // len(layers))
-        units = []
-        for li, layer in enumerate(layers):
-            R = layer.weight.shape[0]
-            for c in range(chunks):
-                r0, r1 = parallel.row_shard(R, c, chunks)
-                if r1 > r0:
-                    units.append((li, r0, r1))
-        mine = {}
-        for u, (li, r0, r1) in enumerate(units):
-            if u % world == rank:
-                mine[u] = self.solver.solve(layers[li].weight.data, H, rows=(r0, r1), factor=fac)
-        # every rank computes the same permutation from the same (reduced) Hessian
-        perm, invperm = fac['perm'], fac['invperm']
+        R, C = stacked.shape
+        n_groups = (C + 127) // 128
         dev = H.device
-        n_groups = (H.shape[0] + 127) // 128
-        full = []
-        for layer in layers:
-            R, C = layer.weight.shape
-            full.append({'weight': torch.empty((R, C), dtype=torch.float32, device=dev),
-                         'buf_scales': torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
-                         'buf_zeros': None if self.wquantizer.sym else
-                         torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
-                         'buf_perm': perm, 'buf_invperm': invperm})
-        for u, (li, r0, r1) in enumerate(units):
-            owner = u % world
+        full = {'weight': torch.empty((R, C), dtype=torch.float32, device=dev),
+                'buf_scales': torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
+                'buf_zeros': None if self.wquantizer.sym else
+                torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
+                # every rank computes the same permutation from the same (reduced) Hessian
+                'buf_perm': fac['perm'], 'buf_invperm': fac['invperm']}
+        # row ranges in multiples of 128 rows (whole CTAs of the in-block kernel), as even as possible
+        blocks = (R + 127) // 128
+        bounds = [min(R, 128 * ((blocks * r) // world)) for r in range(world)] + [R]
+        a, b = bounds[rank], bounds[rank + 1]
+        mine = self.solver.solve(stacked, H, rows=(a, b), factor=fac) if b > a else None
+        for owner in range(world):
+            a, b = bounds[owner], bounds[owner + 1]
+            if b <= a:
+                continue
             for key in ('weight', 'buf_scales', 'buf_zeros'):
-                dst = full[li][key]
+                dst = full[key]
                 if dst is None:
                     continue
-                view = dst[r0:r1] if key == 'weight' else dst[r0 * n_groups:r1 * n_groups]
+                view = dst[a:b] if key == 'weight' else dst[a * n_groups:b * n_groups]
                 if owner == rank:
-                    view.copy_(mine[u][key])
+                    view.copy_(mine[key])
                 dist.broadcast(view, src=owner)
-        for layer, res in zip(layers, full):
-            self.solver._install(layer, res)
+        return full
 
     # ---- the block -----------------------------------------------------------------------------
     @torch.no_grad()
