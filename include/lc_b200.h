@@ -109,6 +109,18 @@ int lc_rtn_mse_range(const void* in, int dtype, int64_t rows, int64_t cols, int6
 int lc_fp8_e4m3_quant(const void* in, int dtype, int64_t rows, int64_t cols, void* fake_out,
                       void* codes_out, void* scales_out, lc_stream_t stream);
 
+/* FP8 e4m3 block-wise weights: one fp32 scale per 128 x 128 block (FloatQuantizer with granularity
+ * 'per_block', llmc/compression/quantization/quant.py:637-641, :138-140, :544-551, :1060-1075, :1194-1220,
+ * and weight_cast_to_fp8 / weight_cast_to_bf16, quant.py:20-45; the reference's Triton kernels for the
+ * same two casts are kernel.py:56-131).  Ragged edge blocks are padded with zeros like the reference's
+ * reshape.  in: rows x cols in `dtype`; fake_out (same dtype), codes_out (one e4m3 byte per element) and
+ * scales_out (fp32, ceil(rows/128) x ceil(cols/128)) may each be NULL.  block must be 128. */
+int lc_fp8_e4m3_block_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t block, void* fake_out,
+                            void* codes_out, float* scales_out, lc_stream_t stream);
+/* out[r][c] = e4m3 value of codes[r][c] * scales[r/128][c/128], rounded once to out_dtype. */
+int lc_fp8_e4m3_block_dequant(const void* codes, const float* scales, int64_t rows, int64_t cols, int64_t block,
+                              void* out, int out_dtype, lc_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Family 2: Hessian accumulation on the tcgen05 tensor cores.
  *

@@ -273,7 +273,9 @@ class IntegerQuantizer(BaseQuantizer):
 
 
 class FloatQuantizer(BaseQuantizer):
-    """quant.py:962-1228 (use_qtorch path, e4m3, per_channel / per_token) over lc_fp8_e4m3_quant."""
+    """quant.py:962-1228 (use_qtorch path, e4m3): per_channel / per_token / per_group over lc_fp8_e4m3_quant
+    (scales in the tensor's dtype), per_block weights over lc_fp8_e4m3_block_quant (fp32 scales, one per
+    128 x 128 block)."""
 
     def __init__(self, bit, symmetric, granularity, **kwargs):
         super().__init__(bit, symmetric, granularity, **kwargs)
@@ -290,9 +292,20 @@ class FloatQuantizer(BaseQuantizer):
         self.qmin, self.qmax = torch.tensor(finfo.min), torch.tensor(finfo.max)
 
     def _launch(self, t2d, fake=False, codes=False, scales=False):
-        if self.calib_algo != 'minmax' or self.granularity not in ('per_channel', 'per_token'):
+        if self.calib_algo != 'minmax' or self.granularity not in ('per_channel', 'per_token', 'per_group'):
             raise NotImplementedError(f'{self.calib_algo}/{self.granularity} is outside the B200 hot path')
         L.require_cuda(t2d)
+        shape = t2d.shape
+        if self.granularity == 'per_group' and shape[-1] >= self.group_size:
+            if shape[-1] % self.group_size:
+                raise ValueError(f'Dimension {shape[-1]} not divisible by group size {self.group_size}')
+            t2d = t2d.reshape(-1, self.group_size)      # every group is a row of the kernel
+            fake_out, codes_out, s_out = self._launch_rows(t2d, fake, codes, scales)
+            return (None if fake_out is None else fake_out.reshape(shape),
+                    None if codes_out is None else codes_out.reshape(shape), s_out)
+        return self._launch_rows(t2d, fake, codes, scales)
+
+    def _launch_rows(self, t2d, fake, codes, scales):
         rows, cols = t2d.shape
         fake_out = torch.empty_like(t2d) if fake else None
         codes_out = torch.empty((rows, cols), dtype=torch.float8_e4m3fn, device=t2d.device) if codes else None
@@ -301,14 +314,41 @@ class FloatQuantizer(BaseQuantizer):
                L.ptr(s_out), L.stream_of(t2d))
         return fake_out, codes_out, s_out
 
+    def _launch_block(self, weight, fake=False, codes=False):
+        """per_block (quant.py:637-641, :138-140): one launch over the 2-D weight, fp32 block scales."""
+        if self.calib_algo != 'minmax':
+            raise NotImplementedError(f'{self.calib_algo}/per_block is outside the B200 hot path')
+        if self.block_size != 128:
+            raise NotImplementedError('the block-wise FP8 kernel has 128 x 128 blocks')
+        L.require_cuda(weight)
+        if weight.dim() != 2:
+            raise ValueError('per_block quantisation expects a 2-D weight')
+        m, n = weight.shape
+        if m % 128 and n % 128:
+            # the reference's restore_tensor cannot undo padding in both dimensions (quant.py:646-650)
+            raise RuntimeError(f'per_block: a {m} x {n} weight is ragged in both dimensions')
+        w = weight if weight.is_contiguous() else weight.contiguous()
+        fake_out = torch.empty_like(w) if fake else None
+        codes_out = torch.empty((m, n), dtype=torch.float8_e4m3fn, device=w.device) if codes else None
+        s_out = torch.empty((-(-m // 128), -(-n // 128)), dtype=torch.float32, device=w.device)
+        L.call('lc_fp8_e4m3_block_quant', L.ptr(w), L.lc_dtype(w), m, n, 128, L.ptr(fake_out), L.ptr(codes_out),
+               L.ptr(s_out), L.stream_of(w))
+        return fake_out, codes_out, s_out
+
     def get_tensor_qparams(self, tensor, args={}):
+        if self.granularity == 'per_block':
+            raise NotImplementedError('per_block: use fake_quant_weight_dynamic / real_quant_weight_dynamic')
         t, t2d = _as_2d(tensor)
         _, _, s = self._launch(t2d, scales=True)
+        if self.granularity == 'per_group' and t.shape[-1] >= self.group_size:
+            return t.reshape(-1, self.group_size), s, torch.tensor(0.0), self.qmax, self.qmin
         return t, s.reshape(*t.shape[:-1], 1), torch.tensor(0.0), self.qmax, self.qmin
 
     def fake_quant_weight_dynamic(self, weight, args={}):
         if args:
             raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
+        if self.granularity == 'per_block':
+            return self._launch_block(weight, fake=True)[0]
         t, t2d = _as_2d(weight)
         return self._launch(t2d, fake=True)[0].reshape(t.shape)
 
@@ -317,6 +357,9 @@ class FloatQuantizer(BaseQuantizer):
     def real_quant_weight_dynamic(self, weight, args={}):
         if args:
             raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
+        if self.granularity == 'per_block':
+            _, codes, s = self._launch_block(weight, codes=True)
+            return codes, s, None
         t, t2d = _as_2d(weight)
         _, codes, s = self._launch(t2d, codes=True, scales=True)
         return codes.reshape(t.shape), s.reshape(t.shape[0], -1), None
@@ -324,3 +367,25 @@ class FloatQuantizer(BaseQuantizer):
     def __repr__(self):
         return (f'FloatQuantizer(bit={self.bit}, e_bits={self.e_bits}, m_bits={self.m_bits}, '
                 f'granularity={self.granularity}, kwargs={self.kwargs}, qmin={self.qmin}, qmax={self.qmax})')
+
+
+def weight_cast_to_fp8(weight, block_size=128):
+    """quant.py:36-45 (kernel.py:73-83 when Triton is usable): (e4m3 weight, fp32 scales per block)."""
+    q = FloatQuantizer('e4m3', True, 'per_block', block_size=block_size, use_qtorch=True)
+    codes, scales, _ = q.real_quant_weight_dynamic(weight)
+    return codes, scales
+
+
+def weight_cast_to_bf16(weight, scale, block_size=128):
+    """quant.py:20-33 (kernel.py:115-131): e4m3 weight * its block scale, as bf16."""
+    if block_size != 128:
+        raise NotImplementedError('the block-wise FP8 kernel has 128 x 128 blocks')
+    L.require_cuda(weight, scale)
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    s = scale.to(torch.float32).contiguous()
+    m, n = w.shape
+    if s.shape != (-(-m // 128), -(-n // 128)):
+        raise ValueError('scale must hold one value per 128 x 128 block')
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=w.device)
+    L.call('lc_fp8_e4m3_block_dequant', L.ptr(w), L.ptr(s), m, n, 128, L.ptr(out), L.LC_BF16, L.stream_of(out))
+    return out

@@ -176,6 +176,49 @@ def fp8_real_quant_dynamic(w):
     return q.to(torch.float8_e4m3fn), s.view(w.shape[0], -1)
 
 
+def fp8_block_view(w, block=128):
+    """reshape_tensor, per_block (quant.py:637-641): zero-pad to whole blocks, view (mb, block, nb, block)."""
+    m, n = w.shape
+    mp, np_ = -(-m // block) * block, -(-n // block) * block
+    t = torch.zeros((mp, np_), dtype=w.dtype, device=w.device)
+    t[:m, :n] = w
+    return t.view(-1, block, np_ // block, block)
+
+
+def fp8_block_scales(t):
+    """per_block range (quant.py:138-140) and symmetric qparams (:544-551): fp32, shape (mb, 1, nb, 1)."""
+    mn = t.abs().float().amin(dim=(1, 3), keepdim=True)
+    mx = t.abs().float().amax(dim=(1, 3), keepdim=True)
+    s = torch.max(mx.abs(), mn.abs()).clamp(min=1e-5) / torch.tensor(448.0)
+    s[s == 0] = 1
+    return s
+
+
+def fp8_block_fake_quant(w, block=128):
+    """FloatQuantizer('e4m3', True, 'per_block').fake_quant_weight_dynamic (quant.py:1141-1158, :1060-1075)."""
+    t = fp8_block_view(w, block)
+    s = fp8_block_scales(t)
+    q = e4m3_round((t / s + torch.tensor(0.0)).float())
+    out = (q - torch.tensor(0.0)) * s
+    return out.reshape(-1, out.shape[2] * block)[:w.shape[0], :w.shape[1]].to(w.dtype)
+
+
+def fp8_block_real_quant(w, block=128):
+    """weight_cast_to_fp8 (quant.py:36-45 -> real_quant_weight_dynamic :1194-1220): codes, scales (mb, nb)."""
+    t = fp8_block_view(w, block)
+    s = fp8_block_scales(t)
+    q = e4m3_round((t / s + torch.tensor(0.0)).float())
+    q = q.reshape(-1, q.shape[2] * block)[:w.shape[0], :w.shape[1]]
+    return q.to(torch.float8_e4m3fn), s.view(s.shape[0], s.shape[2])
+
+
+def fp8_block_dequant(codes, scales, block=128):
+    """weight_cast_to_bf16 (quant.py:20-33): float(codes) * block scale, to bf16."""
+    t = fp8_block_view(codes.float(), block)
+    out = (t - 0) * scales.view(scales.shape[0], 1, scales.shape[1], 1)
+    return out.reshape(-1, out.shape[2] * block)[:codes.shape[0], :codes.shape[1]].to(torch.bfloat16)
+
+
 def pack_int4_rows(codes_u8):
     """Two 4-bit codes per byte along the input dim, low nibble first (the nibble order of
     the compressed-tensors packer used by the reference's export path,

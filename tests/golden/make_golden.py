@@ -135,6 +135,21 @@ def make_fp8(rq, out_dir):
                                      x=x, fake_act=fa, pinned=False)
     torch.save(cases, os.path.join(out_dir, 'fp8_e4m3.pt'))
     print('fp8_e4m3.pt', len(cases), 'cases')
+    # block-wise weights (one fp32 scale per 128 x 128 block): quant.py's own weight_cast_to_fp8 /
+    # weight_cast_to_bf16 (the torch versions the reference uses when its Triton kernels are unavailable)
+    blk = {}
+    for name, shape, dtype in (('bf16_128x256', (128, 256), torch.bfloat16), ('bf16_140x128', (140, 128), torch.bfloat16),
+                               ('bf16_128x132', (128, 132), torch.bfloat16), ('f32_130x128', (130, 128), torch.float32)):
+        w = (torch.randn(*shape, generator=gen) * 0.02).to(dtype)
+        w[:64, :64] = 0
+        w[100:, 100:] *= 30
+        codes, scales = rq.weight_cast_to_fp8(w.clone(), 128)
+        back = rq.weight_cast_to_bf16(codes, scales, 128)
+        qz = rq.FloatQuantizer('e4m3', True, 'per_block', block_size=128, use_qtorch=True)
+        fq = qz.fake_quant_weight_dynamic(w.clone())
+        blk[name] = dict(w=w, codes=codes.view(torch.uint8), scales=scales, back=back, fake=fq, pinned=False)
+    torch.save(blk, os.path.join(out_dir, 'fp8_block.pt'))
+    print('fp8_block.pt', len(blk), 'cases')
 
 
 def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01):

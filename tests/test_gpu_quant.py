@@ -213,6 +213,40 @@ def test_fp8_matches_reference_golden_and_oracle(golden):
             _same(s2, s, 'fp8 scales')
 
 
+def test_fp8_block_wise_matches_reference_golden_and_oracle(golden):
+    """128 x 128 block-wise e4m3 weights: codes, fp32 scales, dequantised bf16 and fake-quantised weights
+    against the reference's CPU result (fixtures) and against the oracle on larger seeded tensors."""
+    from lightcompress_b200 import FloatQuantizer
+    from lightcompress_b200.quant import weight_cast_to_bf16, weight_cast_to_fp8
+    for key, c in golden('fp8_block.pt').items():
+        w = c['w'].cuda()
+        codes, scales = weight_cast_to_fp8(w, 128)
+        assert torch.equal(codes.cpu().view(torch.uint8), c['codes']), key
+        _same(scales, c['scales'], key)
+        _same(weight_cast_to_bf16(codes, scales, 128), c['back'], key)
+        qz = FloatQuantizer('e4m3', True, 'per_block', block_size=128, use_qtorch=True)
+        _same(qz.fake_quant_weight_dynamic(w), c['fake'], key)
+    g = torch.Generator().manual_seed(88)
+    for dtype, shape in ((torch.bfloat16, (1408, 2048)), (torch.float16, (1000, 1024)), (torch.float32, (512, 700)),
+                         (torch.bfloat16, (384, 1001))):
+        w = (torch.randn(*shape, generator=g) * 0.05).to(dtype)
+        w[:, ::97] *= 40
+        codes, scales = weight_cast_to_fp8(w.cuda(), 128)
+        rc, rs = quant_ref.fp8_block_real_quant(w)
+        assert torch.equal(codes.cpu().view(torch.uint8), rc.view(torch.uint8)), (dtype, shape)
+        _same(scales, rs)
+        _same(weight_cast_to_bf16(codes, scales), quant_ref.fp8_block_dequant(rc, rs))
+        qz = FloatQuantizer('e4m3', True, 'per_block', block_size=128, use_qtorch=True)
+        _same(qz.fake_quant_weight_dynamic(w.cuda()), quant_ref.fp8_block_fake_quant(w))
+    with pytest.raises(RuntimeError):
+        weight_cast_to_fp8(torch.zeros(130, 130, device='cuda'), 128)
+    # per-token-group activations (1 x 128 groups): every group is a row of the per-row kernel
+    x = torch.randn(4, 33, 512, generator=g).to(torch.bfloat16)
+    qa = FloatQuantizer('e4m3', True, 'per_group', group_size=128, use_qtorch=True)
+    ref = quant_ref.fp8_fake_quant_dynamic(x.reshape(-1, 128)).reshape(x.shape)
+    _same(qa.fake_quant_act_dynamic(x.cuda()), ref)
+
+
 def test_export_packing_layouts():
     """compressed-tensors int4 (LC_CODES_PACK4 viewed as int32) and the AutoAWQ GEMM layout against
     restatements of the reference's packers."""

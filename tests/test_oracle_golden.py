@@ -50,6 +50,19 @@ def test_fp8_oracle_matches_reference_with_substituted_rounding(golden):
         _eq(quant_ref.fp8_fake_quant_dynamic(c['x']), c['fake_act'])
 
 
+def test_fp8_block_oracle_matches_reference_with_substituted_rounding(golden):
+    """Block-wise FP8 weights (one fp32 scale per 128 x 128 block): the reference's weight_cast_to_fp8 /
+    weight_cast_to_bf16 and per_block fake quant, with the same substituted float rounding as above."""
+    cases = golden('fp8_block.pt')
+    assert len(cases) == 4
+    for key, c in cases.items():
+        codes, s = quant_ref.fp8_block_real_quant(c['w'])
+        assert torch.equal(codes.view(torch.uint8), c['codes']), key
+        _eq(s, c['scales'])
+        _eq(quant_ref.fp8_block_dequant(codes, s), c['back'])
+        _eq(quant_ref.fp8_block_fake_quant(c['w']), c['fake'])
+
+
 def test_gptq_oracle_matches_reference(golden):
     torch.set_num_threads(1)
     for key, c in golden('gptq_layer.pt').items():
