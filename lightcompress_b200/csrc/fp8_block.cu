@@ -136,8 +136,64 @@ __global__ void __launch_bounds__(256) fp8_block_dequant_kernel(const uint8_t* _
   }
 }
 
+// act_quant of the block-wise FP8 linear (kernel.py:7-53): per group of 128 values, s = max|x| / 448 in
+// fp32 (no floor: an all-zero group gives s = 0 and NaN codes, like the reference), y = e4m3(x / s).
+// One warp per group, four elements per lane.
+template <typename T>
+__global__ void __launch_bounds__(256) fp8_act_quant_kernel(const T* __restrict__ x, int64_t n_groups,
+                                                            uint8_t* __restrict__ y, float* __restrict__ s_out) {
+  using E = Elem<T>;
+  const int lane = threadIdx.x & 31;
+  for (int64_t g = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); g < n_groups; g += (int64_t)gridDim.x * 8) {
+    const T* src = x + g * kBlk + lane * 4;
+    float v[4];
+    if constexpr (sizeof(T) == 4) {
+      const float4 t = *reinterpret_cast<const float4*>(src);
+      v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    } else {
+      const uint2 t = *reinterpret_cast<const uint2*>(src);
+      const T* e = reinterpret_cast<const T*>(&t);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = E::to_f(e[i]);
+    }
+    float am = nan_max(nan_max(fabsf(v[0]), fabsf(v[1])), nan_max(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) am = nan_max(am, __shfl_xor_sync(0xffffffffu, am, o));
+    const float s = __fdiv_rn(am, 448.f);
+    uint8_t c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(v[i], s), __NV_SATFINITE, __NV_E4M3);
+    *reinterpret_cast<uint32_t*>(y + g * kBlk + lane * 4) = *reinterpret_cast<const uint32_t*>(c);
+    if (lane == 0) s_out[g] = s;
+  }
+}
+
 }  // namespace
 }  // namespace lc
+
+extern "C" LC_API int lc_fp8_e4m3_act_quant(const void* x, int dtype, int64_t n, int64_t group, void* y, float* scales,
+                                            lc_stream_t stream) {
+  using namespace lc;
+  if (!x || !y || !scales || n <= 0 || group != kBlk) return LC_ERR_ARG;
+  if (n % kBlk != 0) return LC_ERR_SHAPE;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u)) return LC_ERR_ALIGN;
+  const int64_t n_groups = n / kBlk;
+  int64_t blocks = (n_groups + 7) / 8;
+  const int64_t cap = (int64_t)kNumSMsB200 * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* yo = static_cast<uint8_t*>(y);
+  switch (dtype) {
+    case LC_F32: fp8_act_quant_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((const float*)x, n_groups, yo, scales); break;
+    case LC_BF16:
+      fp8_act_quant_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, n_groups, yo, scales);
+      break;
+    case LC_F16: fp8_act_quant_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half*)x, n_groups, yo, scales); break;
+    default: return LC_ERR_ARG;
+  }
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
 
 extern "C" LC_API int lc_fp8_e4m3_block_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t block,
                                               void* fake_out, void* codes_out, float* scales_out, lc_stream_t stream) {

@@ -219,6 +219,29 @@ def fp8_block_dequant(codes, scales, block=128):
     return out.reshape(-1, out.shape[2] * block)[:codes.shape[0], :codes.shape[1]].to(torch.bfloat16)
 
 
+def fp8_act_quant(x, block=128):
+    """act_quant (kernel.py:7-53): per group of `block` values s = max|x| / 448 in fp32 (no floor),
+    y = e4m3(x / s).  Returns (y, s) with s of shape (*x.shape[:-1], x.shape[-1] // block)."""
+    g = x.float().reshape(-1, block)
+    s = g.abs().amax(dim=-1, keepdim=True) / 448.0
+    y = (g / s).to(torch.float8_e4m3fn)
+    return y.reshape(x.shape), s.reshape(*x.shape[:-1], x.shape[-1] // block)
+
+
+def fp8_block_gemm(a, a_s, b, b_s, block=128):
+    """fp8_gemm (kernel.py:153-242): per k block the exact product of the e4m3 values, times the row scale
+    of a and the block scale of b, accumulated in fp32."""
+    K = a.shape[-1]
+    a2, as2 = a.float().reshape(-1, K), a_s.reshape(-1, K // block)
+    bf = b.float()
+    acc = torch.zeros((a2.shape[0], b.shape[0]), dtype=torch.float32, device=a.device)
+    col_blk = torch.arange(b.shape[0], device=a.device) // block
+    for kb in range(K // block):
+        part = a2[:, kb * block:(kb + 1) * block] @ bf[:, kb * block:(kb + 1) * block].t()
+        acc += part * as2[:, kb:kb + 1] * b_s[col_blk, kb][None, :]
+    return acc.reshape(*a.shape[:-1], b.shape[0])
+
+
 def pack_int4_rows(codes_u8):
     """Two 4-bit codes per byte along the input dim, low nibble first (the nibble order of
     the compressed-tensors packer used by the reference's export path,
