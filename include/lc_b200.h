@@ -125,8 +125,8 @@ int lc_fp8_e4m3_block_dequant(const void* codes, const float* scales, int64_t ro
  * reference's Triton kernels act_quant (kernel.py:7-53) and fp8_gemm (kernel.py:153-242):
  *   act_quant: per group of 128 values along the last dimension, scales[g] = max|x| / 448 (fp32, no
  *              floor), y = e4m3(x / scales[g]); n = number of elements, a multiple of 128.
- *   gemm:      c[M][N] = sum over 128-wide k blocks kb of (a[:, kb] b[:, kb]^T) * a_s[m][kb] *
- *              b_s[n / 128][kb]; a: M x K e4m3 (row-major), a_s: M x K/128 fp32; b: N x K e4m3, b_s:
+ *   gemm:      c[M][N] = sum over 128-wide k blocks kb of (a[:, kb] b[:, kb]^T) * (a_s[m][kb] *
+ *              b_s[n / 128][kb]); a: M x K e4m3 (row-major), a_s: M x K/128 fp32; b: N x K e4m3, b_s:
  *              ceil(N/128) x K/128 fp32; c: bf16 or fp32.  K % 128 == 0.  tcgen05 kind::f8f6f4, each k
  *              block accumulated on its own in tensor memory and folded into fp32 registers with its
  *              scales.  *status receives LC_ERR_TIMEOUT if a bounded pipeline wait expires. */

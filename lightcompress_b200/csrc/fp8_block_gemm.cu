@@ -1,5 +1,5 @@
 // Block-scaled FP8 GEMM of the block-wise FP8 linear: C = sum over 128-wide k blocks of
-// (A_kb B_kb^T) * a_s[m][kb] * b_s[n / 128][kb], A (M x K) e4m3 activations with one fp32 scale per
+// (A_kb B_kb^T) * (a_s[m][kb] * b_s[n / 128][kb]), A (M x K) e4m3 activations with one fp32 scale per
 // row and k block (act_quant), B (N x K) e4m3 weights with one fp32 scale per 128 x 128 block
 // (the reference's Triton fp8_gemm, llmc/compression/quantization/kernel.py:153-242, called from
 // block_wise_fp8_forward_func, module_utils.py:41-46).
@@ -7,10 +7,11 @@
 // tcgen05 kind::f8f6f4, both operands K-major (a 128-byte swizzle row holds exactly one k block of a
 // row), 128 x 128 output tiles.  The scales differ per k block, so a k block's product cannot stay in
 // the tensor-core accumulator: each k block is accumulated on its own (4 MMAs of K = 32) into one of
-// four 128-column TMEM buffers, and the four epilogue warps fold it into fp32 registers with the
-// block's two scales while the tensor core already works on the next k blocks.  One TMA copy per operand
+// four 128-column TMEM buffers, and the eight epilogue warps fold it into fp32 registers with the
+// product of the block's two scales while the tensor core already works on the next k blocks.  One TMA copy per operand
 // and k block (16 KB each), six stages; persistent CTAs; warp 0 = TMA producer, warp 1 = MMA issuer,
-// warps 2-5 = promotion + epilogue (one output row per thread).
+// warps 2-9 = promotion + epilogue (a thread owns 64 columns of one output row; one 64-column
+// tensor-memory load and 64 FMAs per k block).
 // Every wait is bounded; on expiry the CTA raises its abort flag, drains its copies in flight, frees
 // its tensor memory and reports LC_ERR_TIMEOUT through the caller's status word.
 #include "umma_common.cuh"
@@ -27,7 +28,9 @@ constexpr int OPERAND_BYTES = TM * KB;         // 16384
 constexpr int STAGE_BYTES = 2 * OPERAND_BYTES;
 constexpr int NBUF = 4;                        // TMEM accumulators of 128 columns
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;                   // two warps per TMEM lane quarter, 64 columns each
+constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int EPI_COLS = TN / (kEpiWarps / 4);  // 64
 
 // kind::f8f6f4: D fp32, A = B = e4m3 (format 0), both K-major, N = 128, M = 128
 constexpr uint32_t kIdescF8 = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
@@ -54,6 +57,30 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
       : "memory");
 }
 
+// 64 consecutive columns of this warp's 32 TMEM lanes, one row per lane
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+        "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+        "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+        "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 __global__ void __launch_bounds__(kThreads, 1) fp8_block_gemm_kernel(const __grid_constant__ F8Maps maps, F8Args a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -75,7 +102,7 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_block_gemm_kernel(const __gri
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 4);
+      mbar_init(acc_empty(b), kEpiWarps);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -151,7 +178,8 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_block_gemm_kernel(const __gri
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;                     // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;           // which 64 columns of the tile
     uint32_t n = 0;
     bool ok = true;
     for (int t = blockIdx.x; ok && t < n_tiles_total; t += gridDim.x) {
@@ -160,33 +188,30 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_block_gemm_kernel(const __gri
       const bool row_ok = m < a.M;
       const float* as_row = a.a_s + (int64_t)(row_ok ? m : 0) * a.k_blocks;
       const float* bs_row = a.b_s + (int64_t)(n0 / TN) * a.k_blocks;
-      float acc[TN];
+      float acc[EPI_COLS];
 #pragma unroll
-      for (int j = 0; j < TN; ++j) acc[j] = 0.f;
+      for (int j = 0; j < EPI_COLS; ++j) acc[j] = 0.f;
       for (int kb = 0; kb < a.k_blocks; ++kb, ++n) {
         const uint32_t buf = n % NBUF;
+        const float sc = __fmul_rn(as_row[kb], bs_row[kb]);
         if (!mbar_wait(acc_full(buf), (n / NBUF) & 1u, abort_flag) || *abort_flag) { ok = false; break; }
         tcgen05_fence_after();
-        const float sa_ = as_row[kb], sb_ = bs_row[kb];
-        const uint32_t taddr = tmem_base + buf * TN + ((uint32_t)(q * 32) << 16);
-#pragma unroll
-        for (int c = 0; c < TN / 32; ++c) {
-          float v[32];
-          tmem_ld32(taddr + (uint32_t)(c * 32), v);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__fmul_rn(v[j], sa_), sb_, acc[c * 32 + j]);
-        }
+        float v[EPI_COLS];
+        tmem_ld64(tmem_base + buf * TN + half * EPI_COLS + ((uint32_t)(q * 32) << 16), v);
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty(buf));
+        if (lane == 0) mbar_arrive(acc_empty(buf));   // the values are in registers: the buffer is free again
+#pragma unroll
+        for (int j = 0; j < EPI_COLS; ++j) acc[j] = fmaf(v[j], sc, acc[j]);
       }
       if (!ok) break;
       if (row_ok) {
+        const int c0 = n0 + half * EPI_COLS;
         if (a.out_dtype == LC_BF16) {
-          __nv_bfloat16* row = static_cast<__nv_bfloat16*>(a.C) + (int64_t)m * a.N + n0;
-          if (n0 + TN <= a.N && (a.N & 7) == 0) {
+          __nv_bfloat16* row = static_cast<__nv_bfloat16*>(a.C) + (int64_t)m * a.N + c0;
+          if (c0 + EPI_COLS <= a.N && (a.N & 7) == 0) {
 #pragma unroll
-            for (int j = 0; j < TN; j += 8) {
+            for (int j = 0; j < EPI_COLS; j += 8) {
               __nv_bfloat16 o[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[j + e]);
@@ -194,14 +219,14 @@ __global__ void __launch_bounds__(kThreads, 1) fp8_block_gemm_kernel(const __gri
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < TN; ++j)
-              if (n0 + j < a.N) row[j] = __float2bfloat16_rn(acc[j]);
+            for (int j = 0; j < EPI_COLS; ++j)
+              if (c0 + j < a.N) row[j] = __float2bfloat16_rn(acc[j]);
           }
         } else {
-          float* row = static_cast<float*>(a.C) + (int64_t)m * a.N + n0;
+          float* row = static_cast<float*>(a.C) + (int64_t)m * a.N + c0;
 #pragma unroll
-          for (int j = 0; j < TN; ++j)
-            if (n0 + j < a.N) row[j] = acc[j];
+          for (int j = 0; j < EPI_COLS; ++j)
+            if (c0 + j < a.N) row[j] = acc[j];
         }
       }
     }

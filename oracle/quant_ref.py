@@ -238,7 +238,7 @@ def fp8_block_gemm(a, a_s, b, b_s, block=128):
     col_blk = torch.arange(b.shape[0], device=a.device) // block
     for kb in range(K // block):
         part = a2[:, kb * block:(kb + 1) * block] @ bf[:, kb * block:(kb + 1) * block].t()
-        acc += part * as2[:, kb:kb + 1] * b_s[col_blk, kb][None, :]
+        acc += part * (as2[:, kb:kb + 1] * b_s[col_blk, kb][None, :])
     return acc.reshape(*a.shape[:-1], b.shape[0])
 
 
