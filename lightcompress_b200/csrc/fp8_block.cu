@@ -143,28 +143,42 @@ template <typename T>
 __global__ void __launch_bounds__(256) fp8_act_quant_kernel(const T* __restrict__ x, int64_t n_groups,
                                                             uint8_t* __restrict__ y, float* __restrict__ s_out) {
   using E = Elem<T>;
+  constexpr int U = 4;   // groups per warp in flight
   const int lane = threadIdx.x & 31;
-  for (int64_t g = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); g < n_groups; g += (int64_t)gridDim.x * 8) {
-    const T* src = x + g * kBlk + lane * 4;
-    float v[4];
-    if constexpr (sizeof(T) == 4) {
-      const float4 t = *reinterpret_cast<const float4*>(src);
-      v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
-    } else {
-      const uint2 t = *reinterpret_cast<const uint2*>(src);
-      const T* e = reinterpret_cast<const T*>(&t);
+  const int64_t warps = (int64_t)gridDim.x * 8;
+  for (int64_t g0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * U; g0 < n_groups; g0 += warps * U) {
+    float v[U][4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = E::to_f(e[i]);
+    for (int u = 0; u < U; ++u) {
+      const int64_t g = g0 + u;
+      if (g < n_groups) {
+        const T* src = x + g * kBlk + lane * 4;
+        if constexpr (sizeof(T) == 4) {
+          const float4 t = __ldcs(reinterpret_cast<const float4*>(src));
+          v[u][0] = t.x, v[u][1] = t.y, v[u][2] = t.z, v[u][3] = t.w;
+        } else {
+          const uint2 t = __ldcs(reinterpret_cast<const uint2*>(src));
+          const T* e = reinterpret_cast<const T*>(&t);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[u][i] = E::to_f(e[i]);
+        }
+      }
     }
-    float am = nan_max(nan_max(fabsf(v[0]), fabsf(v[1])), nan_max(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) am = nan_max(am, __shfl_xor_sync(0xffffffffu, am, o));
-    const float s = __fdiv_rn(am, 448.f);
-    uint8_t c[4];
+    for (int u = 0; u < U; ++u) {
+      const int64_t g = g0 + u;
+      if (g >= n_groups) break;
+      float am = nan_max(nan_max(fabsf(v[u][0]), fabsf(v[u][1])), nan_max(fabsf(v[u][2]), fabsf(v[u][3])));
 #pragma unroll
-    for (int i = 0; i < 4; ++i) c[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(v[i], s), __NV_SATFINITE, __NV_E4M3);
-    *reinterpret_cast<uint32_t*>(y + g * kBlk + lane * 4) = *reinterpret_cast<const uint32_t*>(c);
-    if (lane == 0) s_out[g] = s;
+      for (int o = 16; o > 0; o >>= 1) am = nan_max(am, __shfl_xor_sync(0xffffffffu, am, o));
+      const float s = __fdiv_rn(am, 448.f);
+      uint8_t c[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        c[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(v[u][i], s), __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint32_t*>(y + g * kBlk + lane * 4) = *reinterpret_cast<const uint32_t*>(c);
+      if (lane == 0) s_out[g] = s;
+    }
   }
 }
 
@@ -178,7 +192,7 @@ extern "C" LC_API int lc_fp8_e4m3_act_quant(const void* x, int dtype, int64_t n,
   if (n % kBlk != 0) return LC_ERR_SHAPE;
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 3u)) return LC_ERR_ALIGN;
   const int64_t n_groups = n / kBlk;
-  int64_t blocks = (n_groups + 7) / 8;
+  int64_t blocks = (n_groups + 31) / 32;
   const int64_t cap = (int64_t)kNumSMsB200 * 16;
   if (blocks > cap) blocks = cap;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
