@@ -680,7 +680,7 @@ def main():
                 'per_cols': {str(c): {'launches_per_step': d[0] / args.steps, 'launch_ms': d[1] / d[0],
                                       'tokens_per_launch': d[2] / d[0]} for c, d in hess.items()},
                 'traffic': None}
-    # DRAM bytes per 16384-token launch from the ncu captures summarised in profiles/hessian_umma_C4096.md
+    # DRAM bytes per 16384-token launch from the ncu captures summarised under profiles/ (Hessian kernel)
     # (dram__bytes_read.sum + dram__bytes_write.sum); the bench launches the same shapes
     ncu_traffic = {4096: 213.7e6, 11008: 2833.0e6}
     if all(c in ncu_traffic and abs(d[2] / d[0] - 16384) < 1 for c, d in hess.items()):
