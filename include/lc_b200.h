@@ -87,6 +87,17 @@ int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int6
                      void* fake_out, void* codes_out, int code_fmt, void* scales_out,
                      void* zeros_out, lc_stream_t stream);
 
+/* GPTQ.w_qdq (gptq.py:425-452: weight[:, perm] -> static fake quant -> [:, invperm] -> model dtype) from
+ * the codes lc_gptq_weight_transform* already produced, in one pass: out[r][c] = ((codes[r][j] + qmin) -
+ * zeros[r][j / 128]) * scales[r][j / 128], j = invperm[c] (invperm NULL: identity), rounded once to
+ * out_dtype.  codes: rows x cols bytes in the permuted column order, stored as q - qmin; scales / zeros:
+ * (rows * ceil(cols / 128)) fp32 in the permuted-group order the solver writes (zeros NULL when
+ * symmetric).  The same bits as the reference's chain, because re-quantising a kept weight with the
+ * parameters it was quantised with reproduces its code. */
+int lc_gptq_dequant_unpermute(const uint8_t* codes, const float* scales, const float* zeros, const int64_t* invperm,
+                              int64_t rows, int64_t cols, int bits, int sym, void* out, int out_dtype,
+                              lc_stream_t stream);
+
 /* MSE range search (calib_algo 'mse'): BaseQuantizer.get_mse_range with the integer quantizer's
  * get_qparams and quant_dequant inside its loop (llmc/compression/quantization/quant.py:147-205,
  * :544-558, :698-716).  For each group of `group` elements along cols (0 = the whole row) the range

@@ -173,6 +173,8 @@ class GPTQBlockwise:
             part = {'weight': res['weight'][r0:r1], 'buf_scales': res['buf_scales'][r0 * n_groups:r1 * n_groups],
                     'buf_zeros': None if res['buf_zeros'] is None else res['buf_zeros'][r0 * n_groups:r1 * n_groups],
                     'buf_perm': res['buf_perm'], 'buf_invperm': res['buf_invperm']}
+            if res.get('codes_perm') is not None:
+                part['codes_perm'] = res['codes_perm'][r0:r1]
             self.solver._install(layer, part)
             r0 = r1
         for n in names:

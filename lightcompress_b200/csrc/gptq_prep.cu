@@ -72,6 +72,28 @@ __global__ void __launch_bounds__(256) unpermute_kernel(const float* Wp, const i
   }
 }
 
+// Deploy-time weight of a GPTQ-quantised linear straight from the solver's codes:
+// out[r][c] = T((q - z) * s) with q = codes[r][j] + qmin, j = invperm[c] the column's place in the
+// permuted order, and s, z the parameters of row r, group j / 128.  One thread per output column
+// (coalesced writes; the gathered reads are one byte and mostly hit L2).
+template <typename T>
+__global__ void __launch_bounds__(256) dequant_unpermute_kernel(const uint8_t* __restrict__ codes,
+                                                                const float* __restrict__ scales,
+                                                                const float* __restrict__ zeros,
+                                                                const int64_t* __restrict__ invperm, int64_t rows,
+                                                                int64_t cols, int64_t n_groups, float qmin,
+                                                                T* __restrict__ out) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const int64_t j = invperm ? invperm[c] : c;
+  const int64_t g = j >> 7;
+  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+    const float q = __fadd_rn((float)codes[r * cols + j], qmin);
+    const float z = zeros ? zeros[r * n_groups + g] : 0.f;
+    out[r * cols + c] = Elem<T>::from_f(__fmul_rn(__fsub_rn(q, z), scales[r * n_groups + g]));
+  }
+}
+
 // out[i][j] = in[n-1-i][n-1-j]
 __global__ void __launch_bounds__(256) flip2_kernel(const float* in, int64_t n, float* out) {
   const int64_t i = blockIdx.y;
@@ -137,6 +159,34 @@ extern "C" LC_API int lc_gptq_unpermute(const float* Wp, const int64_t* perm, in
     case LC_F32: unpermute_kernel<float><<<g, 256, 0, st>>>(Wp, perm, rows, cols, (float*)out); break;
     case LC_BF16: unpermute_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(Wp, perm, rows, cols, (__nv_bfloat16*)out); break;
     default: unpermute_kernel<__half><<<g, 256, 0, st>>>(Wp, perm, rows, cols, (__half*)out); break;
+  }
+  LC_LAUNCH_CHECK();
+  return LC_OK;
+}
+
+extern "C" LC_API int lc_gptq_dequant_unpermute(const uint8_t* codes, const float* scales, const float* zeros,
+                                                const int64_t* invperm, int64_t rows, int64_t cols, int bits, int sym,
+                                                void* out, int out_dtype, lc_stream_t stream) {
+  using namespace lc;
+  if (!codes || !scales || !out || rows <= 0 || cols <= 0 || bits < 2 || bits > 8) return LC_ERR_ARG;
+  if (out_dtype != LC_F32 && out_dtype != LC_BF16 && out_dtype != LC_F16) return LC_ERR_ARG;
+  const int64_t n_groups = (cols + 127) / 128;
+  const float qmin = int_qrange(bits, sym ? 1 : 0).qmin;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 g((unsigned)((cols + 255) / 256), (unsigned)(rows < 1024 ? rows : 1024));
+  switch (out_dtype) {
+    case LC_F32:
+      dequant_unpermute_kernel<float><<<g, 256, 0, st>>>(codes, scales, zeros, invperm, rows, cols, n_groups, qmin,
+                                                         (float*)out);
+      break;
+    case LC_BF16:
+      dequant_unpermute_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(codes, scales, zeros, invperm, rows, cols, n_groups,
+                                                                 qmin, (__nv_bfloat16*)out);
+      break;
+    default:
+      dequant_unpermute_kernel<__half><<<g, 256, 0, st>>>(codes, scales, zeros, invperm, rows, cols, n_groups, qmin,
+                                                          (__half*)out);
+      break;
   }
   LC_LAUNCH_CHECK();
   return LC_OK;

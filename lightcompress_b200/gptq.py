@@ -341,11 +341,28 @@ class GPTQ:
         if 'buf_qmax' not in layer._buffers:
             layer.register_buffer('buf_qmax', wq.qmax.to(layer.weight.device))
             layer.register_buffer('buf_qmin', wq.qmin.to(layer.weight.device))
+        # the solver's codes (permuted order), kept for the deploy-time weight; tied to this very weight
+        # tensor so that a weight replaced later falls back to re-quantising
+        codes = res.get('codes_perm')
+        layer._lc_codes = None if codes is None else (codes, layer.weight.data.data_ptr())
 
     @torch.no_grad()
     def w_qdq(self, module, wquantizer):
-        """Deploy-time fake quant (gptq.py:425-452)."""
+        """Deploy-time fake quant (gptq.py:425-452).  When the solver's codes of this weight are at hand the
+        chain gather -> static fake quant -> gather -> cast is one kernel that dequantises them."""
         weight = module.weight
+        kept = getattr(module, '_lc_codes', None)
+        if (kept is not None and kept[1] == weight.data.data_ptr() and wquantizer is self.wquantizer
+                and wquantizer.granularity == 'per_group' and wquantizer.group_size == 128
+                and self.model_dtype in (torch.bfloat16, torch.float16, torch.float32)):
+            codes = kept[0]
+            R, C = codes.shape
+            out = torch.empty((R, C), dtype=self.model_dtype, device=codes.device)
+            zeros = None if wquantizer.sym else module.buf_zeros
+            L.call('lc_gptq_dequant_unpermute', L.ptr(codes), L.ptr(module.buf_scales), L.ptr(zeros),
+                   L.ptr(module.buf_invperm) if self.need_perm else None, R, C, int(wquantizer.bit),
+                   int(wquantizer.sym), L.ptr(out), L.lc_dtype(out), L.stream_of(codes))
+            return out.reshape(weight.shape)
         if self.need_perm:
             weight = weight[:, module.buf_perm]
         args = {'scales': module.buf_scales, 'zeros': getattr(module, 'buf_zeros', None),

@@ -217,6 +217,11 @@ def test_end_to_end_layer_vs_oracle(R, C, ns, T):
     codes2 = wq.quant(layer.weight.data[:, res['buf_perm']].reshape(-1, 128), layer.buf_scales, layer.buf_zeros,
                       None, None).reshape(R, C)
     assert torch.equal(codes2.to(torch.uint8), res['codes_perm'])
+    # the deploy-time weight came from those codes in one kernel; the reference's chain (gather, static
+    # fake quant, gather, cast) gives the same bits
+    assert layer._lc_codes is not None
+    layer._lc_codes = None
+    assert torch.equal(solver.w_qdq(layer, wq), fq)
 
 
 @pytest.mark.parametrize('R,C', [(512, 2048), (300, 3200)])
