@@ -1,7 +1,7 @@
 """Small, self-terminating workloads of each kernel family, sized for profiler captures
 (inputs larger than the 126 MB L2, a few hundred MB on the device, a handful of launches).
 
-    python -m lightcompress_b200.profile_cases hessian|hessian_wide|rtn|fp8|gptq|factor|block_ops [--launches N]
+    python -m lightcompress_b200.profile_cases hessian|hessian_wide|rtn|fp8|gptq|factor|block_ops|fp8_linear|mse [--launches N]
 """
 import argparse
 
@@ -69,6 +69,31 @@ def block_ops(n):
     torch.cuda.synchronize()
 
 
+def fp8_linear(n):
+    """Block-wise FP8 linear forward: act_quant + block-scaled FP8 GEMM, M = 8192, N = 11008, K = 4096."""
+    from .fp8_linear import act_quant, fp8_gemm
+    from .quant import weight_cast_to_fp8
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(8192, 4096, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(11008, 4096, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    wq, ws = weight_cast_to_fp8(w)
+    for _ in range(n):
+        a, a_s = act_quant(x)
+        fp8_gemm(a, a_s, wq, ws)
+    torch.cuda.synchronize()
+
+
+def mse(n):
+    """MSE range search, W4 asymmetric g128 on an 8192 x 4096 fp32 weight."""
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(8192, 4096, generator=g) * 0.02).cuda()
+    qz = IntegerQuantizer(4, False, 'per_group', group_size=128, calib_algo='mse')
+    grouped = qz.reshape_tensor(w)
+    for _ in range(n):
+        qz.get_tensor_range(grouped)
+    torch.cuda.synchronize()
+
+
 def rtn(n):
     g = torch.Generator().manual_seed(2)
     w = (torch.randn(8192, 4096, generator=g) * 0.02).cuda()
@@ -111,9 +136,9 @@ def gptq(n):
 
 if __name__ == '__main__':
     ap = argparse.ArgumentParser()
-    ap.add_argument('case', choices=['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'factor', 'block_ops'])
+    ap.add_argument('case', choices=['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'factor', 'block_ops', 'fp8_linear', 'mse'])
     ap.add_argument('--launches', type=int, default=3)
     a = ap.parse_args()
     {'hessian': hessian, 'hessian_wide': hessian_wide, 'rtn': rtn, 'fp8': fp8, 'gptq': gptq, 'factor': factor,
-     'block_ops': block_ops}[a.case](a.launches)
+     'block_ops': block_ops, 'fp8_linear': fp8_linear, 'mse': mse}[a.case](a.launches)
     print('done', a.case)
