@@ -1,7 +1,7 @@
 """Small, self-terminating workloads of each kernel family, sized for profiler captures
 (inputs larger than the 126 MB L2, a few hundred MB on the device, a handful of launches).
 
-    python -m lightcompress_b200.profile_cases hessian|hessian_wide|rtn|fp8|gptq|factor|block_ops|fp8_linear|mse [--launches N]
+    python -m lightcompress_b200.profile_cases hessian|hessian_wide|rtn|fp8|gptq|factor|block_ops|fp8_linear|mse|awq_clip [--launches N]
 """
 import argparse
 
@@ -94,6 +94,18 @@ def mse(n):
     torch.cuda.synchronize()
 
 
+def awq_clip(n):
+    """AWQ clip search of one 4096 x 4096 bf16 linear on 512 sampled tokens (W4 asymmetric g128)."""
+    from .awq import Awq
+    g = torch.Generator().manual_seed(10)
+    w = (torch.randn(4096, 4096, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    x = torch.randn(16, 512, 4096, generator=g).to(torch.bfloat16).cuda()
+    awq = Awq(IntegerQuantizer(4, False, 'per_group', group_size=128), {}, calib_seq_len=512)
+    for _ in range(n):
+        awq.auto_clip_layer(w, x, apply=False)
+    torch.cuda.synchronize()
+
+
 def rtn(n):
     g = torch.Generator().manual_seed(2)
     w = (torch.randn(8192, 4096, generator=g) * 0.02).cuda()
@@ -136,9 +148,9 @@ def gptq(n):
 
 if __name__ == '__main__':
     ap = argparse.ArgumentParser()
-    ap.add_argument('case', choices=['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'factor', 'block_ops', 'fp8_linear', 'mse'])
+    ap.add_argument('case', choices=['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'factor', 'block_ops', 'fp8_linear', 'mse', 'awq_clip'])
     ap.add_argument('--launches', type=int, default=3)
     a = ap.parse_args()
     {'hessian': hessian, 'hessian_wide': hessian_wide, 'rtn': rtn, 'fp8': fp8, 'gptq': gptq, 'factor': factor,
-     'block_ops': block_ops, 'fp8_linear': fp8_linear, 'mse': mse}[a.case](a.launches)
+     'block_ops': block_ops, 'fp8_linear': fp8_linear, 'mse': mse, 'awq_clip': awq_clip}[a.case](a.launches)
     print('done', a.case)
