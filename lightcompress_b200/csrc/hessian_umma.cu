@@ -55,8 +55,10 @@ struct HessArgs {
   int64_t cols;
   int n_st;        // super-tiles per dimension
   int n_super;     // super-tiles on or above the diagonal
-  int n_items;     // n_super * ksplit
+  int n_items;     // n_super * ksplit, or tail_begin + (n_super - tail_begin) * tail_split
   int ksplit;
+  int tail_begin;  // super-tiles from this index on (the partial last wave) are split tail_split ways in k
+  int tail_split;  // 1 = no tail split
   int k_total;     // pipeline iterations over all segments
   int nseg;
   int seg_k[MAX_SEG];
@@ -70,8 +72,20 @@ struct Item {
 
 __device__ __forceinline__ Item decode_item(const HessArgs& a, int item) {
   Item it;
-  const int split = item / a.n_super;
+  int split = item / a.n_super;
   int t = item % a.n_super;
+  int parts = a.ksplit;
+  if (a.tail_split > 1) {
+    // whole super-tiles first, then the tail wave's super-tiles in tail_split token ranges each
+    if (item < a.tail_begin) {
+      t = item, split = 0, parts = 1;
+    } else {
+      const int idx = item - a.tail_begin;
+      t = a.tail_begin + idx / a.tail_split;
+      split = idx % a.tail_split;
+      parts = a.tail_split;
+    }
+  }
   int si = 0;
   for (; si < a.n_st; ++si) {
     const int cnt = a.n_st - si;
@@ -80,7 +94,7 @@ __device__ __forceinline__ Item decode_item(const HessArgs& a, int item) {
   }
   it.si = si;
   it.sj = si + t;
-  const int chunk = (a.k_total + a.ksplit - 1) / a.ksplit;
+  const int chunk = (a.k_total + parts - 1) / parts;
   it.k_begin = split * chunk;
   it.k_end = min(a.k_total, it.k_begin + chunk);
   return it;
@@ -400,6 +414,8 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
   a.n_st = (int)((cols + ST - 1) / ST);
   a.n_super = a.n_st * (a.n_st + 1) / 2;
   a.alpha = alpha;
+  a.tail_begin = a.n_super;
+  a.tail_split = 1;
   if (ksplit == 0) {
     // Enough super-tiles to occupy the SMs: no token split (one epilogue per super-tile).
     // Otherwise split the token range so that about one item lands on every SM.
@@ -408,11 +424,22 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
       ksplit = sms / a.n_super;
       const int max_split = a.k_total / 8 > 0 ? a.k_total / 8 : 1;
       if (ksplit > max_split) ksplit = max_split;
+    } else if (a.n_super > sms && a.n_super % sms != 0) {
+      // Several waves of whole super-tiles and a partial last one (C = 11008: 946 tiles = 6.4 waves of
+      // 148): the tail's tiles are cut in token ranges so that the last wave is a fraction of a tile long.
+      const int tail = a.n_super % sms;
+      int split = sms / tail;
+      if (split > 8) split = 8;
+      if (split > a.k_total / 8) split = a.k_total / 8;
+      if (split > 1) {
+        a.tail_begin = a.n_super - tail;
+        a.tail_split = split;
+      }
     }
   }
   if (ksplit > a.k_total) ksplit = a.k_total;
   a.ksplit = ksplit;
-  a.n_items = a.n_super * ksplit;
+  a.n_items = a.tail_split > 1 ? a.tail_begin + (a.n_super - a.tail_begin) * a.tail_split : a.n_super * ksplit;
   const int grid = a.n_items < sms ? a.n_items : sms;
   LC_CHECK_CUDA(cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   hessian_umma_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(maps, a);

@@ -39,8 +39,10 @@ def _hessian_gpu(X, ksplit=0, per_sample=True):
     return H
 
 
+# C = 4608 and 11008: more super-tiles than SMs (171 and 946), i.e. whole waves plus a tail wave that the
+# automatic setting cuts in token ranges
 @pytest.mark.parametrize('ns,T,C', [(1, 64, 256), (2, 300, 256), (3, 129, 384), (1, 2048, 1024), (2, 77, 200),
-                                    (1, 512, 4096)])
+                                    (1, 512, 4096), (1, 1024, 4608), (1, 512, 11008)])
 def test_hessian_matches_fp64(ns, T, C):
     g = torch.Generator().manual_seed(2000 + C + T)
     X = _x(g, ns, T, C)
