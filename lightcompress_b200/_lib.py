@@ -17,6 +17,7 @@ LC_ERR_ARG, LC_ERR_SHAPE, LC_ERR_ALIGN, LC_ERR_ARCH = -1, -2, -3, -4
 LC_ERR_WORKSPACE, LC_ERR_NOT_PD, LC_ERR_TIMEOUT, LC_ERR_CUDA = -5, -6, -7, -8
 LC_F32, LC_BF16, LC_F16 = 0, 1, 2
 LC_CODES_NONE, LC_CODES_I32, LC_CODES_I8, LC_CODES_PACK4 = 0, 1, 2, 3
+LC_GEMM_UPPER_ONLY, LC_GEMM_B_LOWER, LC_GEMM_A_UPPER = 1, 2, 4
 
 _DTYPES = {torch.float32: LC_F32, torch.bfloat16: LC_BF16, torch.float16: LC_F16}
 

@@ -61,6 +61,9 @@ class GPTQ:
         self.trailing = special.get('trailing', 'tensor')
         # multi-rank runs: the top level of the triangular inverse is computed once per process group and
         # exchanged (every rank factorises the same all-reduced Hessian), for C >= shared_inverse_min
+        # Cholesky of matrices at least this wide: blocked over 1024 rows with the panel solves and trailing
+        # updates on the tensor cores (cuSOLVER only factorises the diagonal blocks); below it cuSOLVER alone
+        self.blocked_cholesky_min = int(special.get('blocked_cholesky_min', 1 << 30))
         self.shared_inverse = special.get('shared_inverse', True)
         self.shared_inverse_min = int(special.get('shared_inverse_min', 1024))
         # forward hooks deliver one sequence per call; up to `hessian_batch` of them (<= 8) are
@@ -189,9 +192,12 @@ class GPTQ:
                 # factor G = M^T that the inverse reads
                 # no host synchronisation here: potrf's info word joins the status words read at the next
                 # check_status(), which raises LinAlgError like torch.linalg.cholesky would have
-                M, info = torch.linalg.cholesky_ex(Hp, check_errors=False)
-                self._pending_info.append(info.reshape(1))
-                G = M.t() if M.stride() == (1, C) else M.t().contiguous()
+                if C >= self.blocked_cholesky_min:
+                    G = self._blocked_cholesky_upper(Hp, status)
+                else:
+                    M, info = torch.linalg.cholesky_ex(Hp, check_errors=False)
+                    self._pending_info.append(info.reshape(1))
+                    G = M.t() if M.stride() == (1, C) else M.t().contiguous()
                 world = parallel.world()[1] if self.shared_inverse else 1
                 if world > 1 and C >= self.shared_inverse_min:
                     self._shared_inverse(G, C, U, U_lo, ws, ws_floats, status)
@@ -207,6 +213,47 @@ class GPTQ:
             fac['U_lo'] = torch.empty_like(U)
             L.call('lc_gptq_split_tf32', L.ptr(U), U.numel(), L.ptr(fac['U_lo']), L.stream_of(U))
         return fac
+
+    def _blocked_cholesky_upper(self, A, status, block=1024):
+        """Upper Cholesky factor G (A = G^T G, row-major) of a large matrix, right-looking over 1024-row
+        blocks: cuSOLVER factorises the diagonal block, everything that scales with C^2 per step -- the
+        panel solve X = G_kk^-T A[k, k+1:] (through the inverse of G_kk) and the trailing update
+        A[k+1:, k+1:] -= X^T X -- runs on the tensor cores (lc_tf32x3_gemm_tn).  cuSOLVER's own potrf
+        spends most of its time in its panel kernels at this size (13.3 ms at C = 11008).
+        A (upper triangle valid) is destroyed."""
+        n = A.shape[0]
+        dev, st = A.device, L.stream_of(A)
+        G = torch.zeros((n, n), dtype=torch.float32, device=dev)
+        lo = torch.empty((block, n), dtype=torch.float32, device=dev)      # low parts of the current row panel
+        ws_floats = int(L.lib.lc_gptq_factor_workspace_floats(block))
+        ws = torch.empty(ws_floats, dtype=torch.float32, device=dev)
+        Ukk = torch.empty((block, block), dtype=torch.float32, device=dev)
+        for k0 in range(0, n, block):
+            k1 = min(k0 + block, n)
+            b = k1 - k0
+            Gkk, info = torch.linalg.cholesky_ex(A[k0:k1, k0:k1], upper=True, check_errors=False)
+            self._pending_info.append(info.reshape(1))
+            Gkk = torch.triu(Gkk).contiguous()
+            G[k0:k1, k0:k1] = Gkk
+            if k1 == n:
+                break
+            # V = G_kk^-1 (upper): lc_gptq_invert_factor returns U = J (G_kk^-1)^T J, so V[i][j] = U[b-1-j][b-1-i]
+            u = Ukk[:b, :b] if b == block else torch.empty((b, b), dtype=torch.float32, device=dev)
+            L.call('lc_gptq_invert_factor', L.ptr(Gkk), b, L.ptr(u), None, L.ptr(ws), ws_floats, L.ptr(status), st)
+            V = u.flip(0, 1).t().contiguous()
+            V_lo = torch.empty_like(V)
+            L.call('lc_gptq_split_tf32', L.ptr(V), V.numel(), L.ptr(V_lo), st)
+            # X = V^T A[k0:k1, k1:] -> G[k0:k1, k1:]; the panel's rows are contiguous, so their low parts are too
+            rows_lo = lo[:b]
+            L.call('lc_gptq_split_tf32', L.ptr(A[k0:k1]), b * n, L.ptr(rows_lo), st)
+            L.call('lc_tf32x3_gemm_tn', L.ptr(G[k0:k1, k1:]), n, L.ptr(V), L.ptr(V_lo), b, L.ptr(A[k0:k1, k1:]),
+                   L.ptr(rows_lo[:, k1:]), n, b, n - k1, b, 0, 1.0, L.LC_GEMM_A_UPPER, L.ptr(status), st)
+            # A[k1:, k1:] -= X^T X (tiles that reach the diagonal or lie above it)
+            L.call('lc_gptq_split_tf32', L.ptr(G[k0:k1]), b * n, L.ptr(rows_lo), st)
+            L.call('lc_tf32x3_gemm_tn', L.ptr(A[k1:, k1:]), n, L.ptr(G[k0:k1, k1:]), L.ptr(rows_lo[:, k1:]), n,
+                   L.ptr(G[k0:k1, k1:]), L.ptr(rows_lo[:, k1:]), n, n - k1, n - k1, b, 1, -1.0,
+                   L.LC_GEMM_UPPER_ONLY, L.ptr(status), st)
+        return G
 
     def _shared_inverse(self, G, C, U, U_lo, ws, ws_floats, status):
         """The triangular inverse with its top-level block (3/4 of the FLOPs) computed once per process

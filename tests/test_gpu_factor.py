@@ -77,6 +77,34 @@ def test_native_factorisation_matches_cusolver(n, native):
         assert torch.equal(facs['native']['U_lo'], _lo(U1))
 
 
+def test_blocked_cholesky_matches_cusolver():
+    """The 1024-row blocked Cholesky used for wide matrices (forced here at n = 2304: two full blocks and a
+    ragged one) against cuSOLVER's potrf of the same matrix, through the whole factorisation."""
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    n = 2304
+    g = torch.Generator().manual_seed(n)
+    X = torch.randn(3 * n, n, generator=g)
+    X[:, torch.randperm(n, generator=g)[:23]] *= 20
+    H = (X.t() @ X).cuda()
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    facs = []
+    for min_n in (1024, 1 << 30):
+        solver = GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'blocked_cholesky_min': min_n})
+        facs.append(solver.factorize(H, 2.0 / 3))
+        solver.check_status()
+    U1, U2 = facs[0]['U'], facs[1]['U']
+    rel = float((U1 - U2).abs().max() / U2.abs().max())
+    perm = facs[0]['perm']
+    Hp = (H.double() * (2.0 / 3))[perm][:, perm]
+    Hp += torch.eye(n, device='cuda', dtype=torch.float64) * 0.01 * Hp.diagonal().mean()
+    eye = torch.eye(n, device='cuda', dtype=torch.float64)
+    r1 = float(((U1.double().t() @ U1.double()) @ Hp - eye).abs().max())
+    r2 = float(((U2.double().t() @ U2.double()) @ Hp - eye).abs().max())
+    print(f'blocked Cholesky vs potrf: max rel diff of U {rel:.2e}; residual {r1:.2e} vs {r2:.2e}')
+    assert torch.equal(U1, torch.triu(U1))
+    assert rel < 1e-4 and r1 < max(6 * r2, 1e-3)
+
+
 def test_native_factorisation_reports_not_positive_definite():
     from lightcompress_b200 import GPTQ, IntegerQuantizer
     n = 256
