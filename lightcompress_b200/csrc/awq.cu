@@ -88,14 +88,27 @@ __global__ void __launch_bounds__(256) div_cols_kernel(const T* x, const T* s, i
       rv[i] = __frcp_rn(sv[i]);
     }
   }
-  for (int64_t r = (int64_t)blockIdx.y * 8 + threadIdx.y; r < rows; r += (int64_t)gridDim.y * 8) {
-    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(x + r * cols + c0));
-    const T* p = reinterpret_cast<const T*>(&v);
-    uint4 o;
-    T* q = reinterpret_cast<T*>(&o);
+  // four rows per iteration: four 16-byte loads in flight per thread
+  constexpr int U = 4;
+  const int64_t stride = (int64_t)gridDim.y * 8;
+  for (int64_t r0 = (int64_t)blockIdx.y * 8 + threadIdx.y; r0 < rows; r0 += stride * U) {
+    uint4 v[U];
 #pragma unroll
-    for (int i = 0; i < N; ++i) q[i] = Elem<T>::from_f(div_rnd<T>(Elem<T>::to_f(p[i]), sv[i], rv[i]));
-    __stcs(reinterpret_cast<uint4*>(out + r * cols + c0), o);
+    for (int u = 0; u < U; ++u) {
+      const int64_t r = r0 + u * stride;
+      if (r < rows) v[u] = __ldcs(reinterpret_cast<const uint4*>(x + r * cols + c0));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t r = r0 + u * stride;
+      if (r >= rows) break;
+      const T* p = reinterpret_cast<const T*>(&v[u]);
+      uint4 o;
+      T* q = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int i = 0; i < N; ++i) q[i] = Elem<T>::from_f(div_rnd<T>(Elem<T>::to_f(p[i]), sv[i], rv[i]));
+      __stcs(reinterpret_cast<uint4*>(out + r * cols + c0), o);
+    }
   }
 }
 
