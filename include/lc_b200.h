@@ -307,6 +307,21 @@ int lc_gptq_weight_transform_tc(float* W, const float* U, const float* U_lo, int
                                 float* scales, float* zeros, uint8_t* codes_u8, float* loss_rows,
                                 int32_t* status, lc_stream_t stream);
 
+/* GPTQ.weight_transform in owq mode (gptq.py:44-50, :199-244 with n_nonout < columns): hessian_sorting
+ * (gptq.py:66-83) has moved the outlier columns to the end; only columns [0, n_quant) are quantised
+ * (the last group's qparams come from its columns below n_quant, gptq.py:216-223), the columns from
+ * n_quant on receive the error feedback and stay fp32 (gptq.py:186-188).  Otherwise as
+ * lc_gptq_weight_transform / lc_gptq_weight_transform_tc, which are these with n_quant == cols.
+ * scales / zeros keep (rows * ceil(cols / 128)) entries; groups that start at or beyond n_quant are not
+ * written; codes_u8 is written for columns below n_quant only. */
+int lc_gptq_weight_transform_owq(float* W, const float* U, int64_t rows, int64_t cols, int64_t n_quant, int bits,
+                                 int sym, float* scratch_err, float* scales, float* zeros, uint8_t* codes_u8,
+                                 float* loss_rows, lc_stream_t stream);
+int lc_gptq_weight_transform_tc_owq(float* W, const float* U, const float* U_lo, int64_t rows, int64_t cols,
+                                    int64_t n_quant, int bits, int sym, float* scratch_err, float* panel_hi,
+                                    float* panel_lo, float* scales, float* zeros, uint8_t* codes_u8,
+                                    float* loss_rows, int32_t* status, lc_stream_t stream);
+
 /* lc_gptq_weight_transform for callers that cannot allocate.  (No counterpart in the reference:
  * its solver allocates freely through torch.)
  *

@@ -157,7 +157,20 @@ class GPTQBlockwise:
         names = list(subset)
         layers = [getattr(*subset[n]) for n in names]
         H, hscale = self.solver._finish_hessian(names[0])
-        fac = self.solver.factorize(H, hscale)       # shared by the linears of the subset
+        # owq: linears with different outlier counts order the columns differently; each count gets its
+        # own factor (the reference's n_outs are equal within every Llama subset: one factor as usual)
+        by_n_out = OrderedDict()
+        for layer, n in zip(layers, names):
+            by_n_out.setdefault(self.solver.n_out_of(n), []).append(layer)
+        for n_out, group in by_n_out.items():
+            self._solve_group(group, H, hscale, n_out, rank, world)
+        for n in names:
+            self.solver.layers_cache.pop(n, None)
+        if self.on_subset_done is not None:
+            self.on_subset_done(names)
+
+    def _solve_group(self, layers, H, hscale, n_out, rank, world):
+        fac = self.solver.factorize(H, hscale, n_out=n_out)       # shared by the linears of the group
         # The rows of all linears of a subset are independent given the shared factor: they are solved
         # as one stacked matrix (q/k/v: 12288 rows, gate/up: 22016), which cuts the number of latency-bound
         # 128-column steps by the number of linears; in a process group every rank takes a row range.
@@ -172,15 +185,12 @@ class GPTQBlockwise:
             r1 = r0 + layer.weight.shape[0]
             part = {'weight': res['weight'][r0:r1], 'buf_scales': res['buf_scales'][r0 * n_groups:r1 * n_groups],
                     'buf_zeros': None if res['buf_zeros'] is None else res['buf_zeros'][r0 * n_groups:r1 * n_groups],
-                    'buf_perm': res['buf_perm'], 'buf_invperm': res['buf_invperm']}
+                    'buf_perm': res['buf_perm'], 'buf_invperm': res['buf_invperm'],
+                    'buf_n_nonout': res.get('buf_n_nonout')}
             if res.get('codes_perm') is not None:
                 part['codes_perm'] = res['codes_perm'][r0:r1]
             self.solver._install(layer, part)
             r0 = r1
-        for n in names:
-            self.solver.layers_cache.pop(n, None)
-        if self.on_subset_done is not None:
-            self.on_subset_done(names)
 
     def _sharded_solve(self, stacked, fac, rank, world):
         """Row range `rank` of the stacked weight solved here, all ranges broadcast: every rank returns
@@ -195,6 +205,8 @@ class GPTQBlockwise:
                 torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
                 # every rank computes the same permutation from the same (reduced) Hessian
                 'buf_perm': fac['perm'], 'buf_invperm': fac['invperm']}
+        if fac.get('n_out'):
+            full['buf_n_nonout'] = torch.tensor(C - fac['n_out'])
         # row ranges in multiples of 128 rows (whole CTAs of the in-block kernel), as even as possible
         blocks = (R + 127) // 128
         bounds = [min(R, 128 * ((blocks * r) // world)) for r in range(world)] + [R]
@@ -220,6 +232,9 @@ class GPTQBlockwise:
         """inputs: list of (b, T, C) tensors on the block's device (this rank's share);
         kwargs: dict or list of dicts of extra forward arguments.  Returns the inputs of the next
         block (outputs of the quantised block when quant_out, of the original block otherwise)."""
+        if self.solver.owq:
+            # n_outs are bound to the block's linears by position (gptq.py:89-93)
+            self.solver.set_block_linears([n for sub in (subsets or llama_subsets(block)) for n in sub])
         if (subsets is None and self.stage_plan and self.true_sequential and self.quant_out
                 and is_llama_layout(block)):
             return self._block_opt_llama_staged(block, inputs, kwargs)

@@ -69,15 +69,15 @@ extern "C" LC_API int lc_gptq_panel_update(float* W, const float* e_hi, const fl
                              reinterpret_cast<cudaStream_t>(stream));
 }
 
-extern "C" LC_API int lc_gptq_weight_transform_tc(float* W, const float* U, const float* U_lo, int64_t rows,
-                                                  int64_t cols, int bits, int sym, float* scratch_err,
-                                                  float* panel_hi, float* panel_lo, float* scales, float* zeros,
-                                                  uint8_t* codes_u8, float* loss_rows, int32_t* status,
-                                                  lc_stream_t stream) {
+extern "C" LC_API int lc_gptq_weight_transform_tc_owq(float* W, const float* U, const float* U_lo, int64_t rows,
+                                                      int64_t cols, int64_t n_quant, int bits, int sym,
+                                                      float* scratch_err, float* panel_hi, float* panel_lo,
+                                                      float* scales, float* zeros, uint8_t* codes_u8,
+                                                      float* loss_rows, int32_t* status, lc_stream_t stream) {
   using namespace lc;
   constexpr int kPanel = 1024, kSub = 256;
   if (!W || !U || !U_lo || !scratch_err || !panel_hi || !panel_lo || !scales || !zeros) return LC_ERR_ARG;
-  if (rows <= 0 || cols <= 0 || bits < 2 || bits > 8) return LC_ERR_ARG;
+  if (rows <= 0 || cols <= 0 || n_quant <= 0 || n_quant > cols || bits < 2 || bits > 8) return LC_ERR_ARG;
   if (cols % 128 != 0 || rows % 4 != 0) return LC_ERR_SHAPE;      // TMA pitch / whole blocks; use the FFMA entry point otherwise
   if (!aligned16(W) || !aligned16(U) || !aligned16(U_lo) || !aligned16(panel_hi) || !aligned16(panel_lo)) return LC_ERR_ALIGN;
   int dev = 0, major = 0;
@@ -94,31 +94,47 @@ extern "C" LC_API int lc_gptq_weight_transform_tc(float* W, const float* U, cons
     if ((rc = gemm_mat_init(&E, panel_hi, panel_lo, kPanel, rows, rows)) != LC_OK) return rc;
     if ((rc = gemm_mat_init(&Um, U, U_lo, cols, cols, cols)) != LC_OK) return rc;
   }
-  for (int64_t p1 = 0; p1 < cols; p1 += kPanel) {
+  // Only columns [0, n_quant) are quantised; q_end rounds that up to whole 128-column blocks.  The block
+  // kernel writes zero errors for the columns of a ragged last block it does not quantise, so the
+  // GEMM levels may contract over whole blocks.
+  const int64_t q_end = (n_quant + 127) / 128 * 128;
+  for (int64_t p1 = 0; p1 < q_end; p1 += kPanel) {
     const int64_t p2 = (p1 + kPanel < cols) ? p1 + kPanel : cols;
-    for (int64_t s1 = p1; s1 < p2; s1 += kSub) {
+    const int64_t pq = (p2 < q_end) ? p2 : q_end;
+    for (int64_t s1 = p1; s1 < pq; s1 += kSub) {
       const int64_t s2 = (s1 + kSub < p2) ? s1 + kSub : p2;
-      for (int64_t i1 = s1; i1 < s2; i1 += 128) {
-        int rc = gptq_block_launch(W, U, rows, cols, i1, 128, bits, sym, scratch_err, scales, zeros, n_groups,
+      const int64_t sq = (s2 < q_end) ? s2 : q_end;
+      for (int64_t i1 = s1; i1 < sq; i1 += 128) {
+        const int count = (int)((n_quant - i1 < 128) ? (n_quant - i1) : 128);
+        int rc = gptq_block_launch(W, U, rows, cols, i1, count, bits, sym, scratch_err, scales, zeros, n_groups,
                                    codes_u8, loss_rows, st, panel_hi, panel_lo, (int)(i1 - p1));
         if (rc != LC_OK) return rc;
-        // level 1, eager: the rest of the 256-column sub-panel (K = 128, at most 128 columns: FFMA kernel)
-        rc = gptq_trail_launch(W, scratch_err, U, rows, cols, i1, 128, i1 + 128, st, s2);
+        // level 1, eager: the rest of the 256-column sub-panel (K <= 128, at most 255 columns: FFMA kernel)
+        rc = gptq_trail_launch(W, scratch_err, U, rows, cols, i1, count, i1 + count, st, s2);
         if (rc != LC_OK) return rc;
       }
       // level 2: the rest of the panel, once per sub-panel (K = 256)
       if (s2 < p2) {
-        const int rc = tf32x3_gemm_launch(W + s2, cols, E, s1 - p1, 0, Um, s1, s2, rows, p2 - s2, s2 - s1, 1, -1.f, 0,
+        const int rc = tf32x3_gemm_launch(W + s2, cols, E, s1 - p1, 0, Um, s1, s2, rows, p2 - s2, sq - s1, 1, -1.f, 0,
                                           status, st);
         if (rc != LC_OK) return rc;
       }
     }
     // level 3: everything to the right of the panel, once per panel (K = 1024)
     if (p2 < cols) {
-      const int rc = tf32x3_gemm_launch(W + p2, cols, E, 0, 0, Um, p1, p2, rows, cols - p2, p2 - p1, 1, -1.f, 0, status,
+      const int rc = tf32x3_gemm_launch(W + p2, cols, E, 0, 0, Um, p1, p2, rows, cols - p2, pq - p1, 1, -1.f, 0, status,
                                         st);
       if (rc != LC_OK) return rc;
     }
   }
   return LC_OK;
+}
+
+extern "C" LC_API int lc_gptq_weight_transform_tc(float* W, const float* U, const float* U_lo, int64_t rows,
+                                                  int64_t cols, int bits, int sym, float* scratch_err,
+                                                  float* panel_hi, float* panel_lo, float* scales, float* zeros,
+                                                  uint8_t* codes_u8, float* loss_rows, int32_t* status,
+                                                  lc_stream_t stream) {
+  return lc_gptq_weight_transform_tc_owq(W, U, U_lo, rows, cols, cols, bits, sym, scratch_err, panel_hi, panel_lo, scales,
+                                         zeros, codes_u8, loss_rows, status, stream);
 }

@@ -204,16 +204,16 @@ extern "C" LC_API int lc_gptq_weight_transform_noalloc(float* W, const float* U,
   return lc_gptq_weight_transform(W, U, rows, cols, bits, sym, scratch, scales, zeros, codes_u8, loss_rows, stream);
 }
 
-extern "C" LC_API int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t cols, int bits, int sym,
-                                        float* scratch_err, float* scales, float* zeros, uint8_t* codes_u8,
-                                        float* loss_rows, lc_stream_t stream) {
+extern "C" LC_API int lc_gptq_weight_transform_owq(float* W, const float* U, int64_t rows, int64_t cols, int64_t n_quant,
+                                                   int bits, int sym, float* scratch_err, float* scales, float* zeros,
+                                                   uint8_t* codes_u8, float* loss_rows, lc_stream_t stream) {
   if (!W || !U || !scratch_err || !scales || !zeros) return LC_ERR_ARG;
-  if (rows <= 0 || cols <= 0 || bits < 2 || bits > 8) return LC_ERR_ARG;
+  if (rows <= 0 || cols <= 0 || n_quant <= 0 || n_quant > cols || bits < 2 || bits > 8) return LC_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int64_t n_groups = (cols + 127) / 128;
   if (loss_rows) LC_CHECK_CUDA(cudaMemsetAsync(loss_rows, 0, rows * sizeof(float), st));
-  for (int64_t i1 = 0; i1 < cols; i1 += 128) {
-    const int count = (int)((cols - i1 < 128) ? (cols - i1) : 128);
+  for (int64_t i1 = 0; i1 < n_quant; i1 += 128) {
+    const int count = (int)((n_quant - i1 < 128) ? (n_quant - i1) : 128);
     int rc = lc::gptq_block_launch(W, U, rows, cols, i1, count, bits, sym, scratch_err, scales, zeros, n_groups,
                                    codes_u8, loss_rows, st, nullptr, nullptr, 0);
     if (rc != LC_OK) return rc;
@@ -221,4 +221,11 @@ extern "C" LC_API int lc_gptq_weight_transform(float* W, const float* U, int64_t
     if (rc != LC_OK) return rc;
   }
   return LC_OK;
+}
+
+extern "C" LC_API int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t cols, int bits, int sym,
+                                        float* scratch_err, float* scales, float* zeros, uint8_t* codes_u8,
+                                        float* loss_rows, lc_stream_t stream) {
+  return lc_gptq_weight_transform_owq(W, U, rows, cols, cols, bits, sym, scratch_err, scales, zeros, codes_u8, loss_rows,
+                                      stream);
 }

@@ -49,6 +49,12 @@ class GPTQ:
         self.blocksize = special.get('blocksize', 128)
         self.owq = special.get('owq', False)
         self.chunk_num = special.get('chunk_num', 1)
+        if self.owq:
+            # gptq.py:47-50: one outlier-column count per linear of a block, in get_block_linears order
+            self.n_outs = list(special['n_outs'])
+            self.static_groups = False
+            self.actorder = False
+        self.n_out_dict = {}
         self.emit_codes = special.get('emit_codes', True)
         # 'direct': one Cholesky of the index-reversed matrix + one triangular inverse (cuSOLVER / cuBLAS);
         # 'native': the Cholesky by cuSOLVER, the triangular inverse blocked on 128x128 diagonal blocks with
@@ -78,12 +84,12 @@ class GPTQ:
         self._pending_info = []         # cuSOLVER potrf info words (non-zero: not positive definite)
         self._check_config()
         self.need_perm = (self.wquantizer.granularity == 'per_group' and not self.static_groups
-                          and self.actorder)
+                          and self.actorder) or self.owq
 
     def _check_config(self):
         wq = self.wquantizer
-        if self.owq or self.static_groups:
-            raise NotImplementedError('owq / static_groups are outside the B200 hot path')
+        if self.static_groups:
+            raise NotImplementedError('static_groups is outside the B200 hot path')
         if wq.granularity != 'per_group' or wq.group_size != 128 or self.blocksize != 128:
             # gptq.py:216-223 reads group statistics that are only well defined when a group
             # starts at a block boundary; the kernels implement group_size == blocksize == 128.
@@ -150,19 +156,55 @@ class GPTQ:
         registered.  `rows=(r0, r1)` restricts the solve to a row range (rows are independent);
         the caller then gathers the pieces."""
         H, hscale = self._finish_hessian(name)
-        res = self.solve(layer.weight.data, H, hscale, rows=rows)
+        n_out = self.n_out_of(name)
+        fac = self.factorize(H, hscale, n_out=n_out) if n_out else None
+        res = self.solve(layer.weight.data, H, hscale, rows=rows, factor=fac)
         if rows is None:
             self._install(layer, res)
         return res
 
     @torch.no_grad()
-    def factorize(self, H, hscale=1.0, perm=None):
+    def n_out_of(self, name):
+        """owq: the number of outlier columns of the linear `name` (gptq.py:122); 0 without owq."""
+        if not self.owq:
+            return 0
+        return int(self.n_out_dict[name])
+
+    def set_block_linears(self, names):
+        """owq: binds n_outs to the linears of a block by position (gptq.py:89-93)."""
+        if self.owq and not self.n_out_dict:
+            self.n_out_dict = {name: self.n_outs[i] for i, name in enumerate(names)}
+
+    def owq_order(self, H, n_out):
+        """hessian_sorting with owq (gptq.py:66-83): the n_out columns with the largest Hessian diagonal
+        go last, in descending order of it; the others keep their order."""
+        C = H.shape[0]
+        diag = torch.empty(C, dtype=torch.float32, device=H.device)
+        L.call('lc_gptq_diag', L.ptr(H), C, L.ptr(diag), L.stream_of(H))
+        top = torch.argsort(diag, descending=True)[:n_out]
+        keep = torch.ones(C, dtype=torch.bool, device=H.device)
+        keep[top] = False
+        perm = torch.cat([torch.arange(C, device=H.device)[keep], top])
+        return perm, torch.argsort(perm)
+
+    @torch.no_grad()
+    def factorize(self, H, hscale=1.0, perm=None, n_out=0):
         """Everything of process_hessian_and_weights (gptq.py:128-176) that depends on H only:
         act-order permutation, dampening, and U with U^T U = (permuted, damped H)^-1.  Linears that
-        read the same input (q/k/v, gate/up) share one result."""
+        read the same input (q/k/v, gate/up) share one result (with owq: if their n_out agree)."""
         L.require_cuda(H)
         C = H.shape[0]
-        if perm is None:
+        if n_out:
+            if not 0 < n_out < 128 or C % 128 != 0:
+                # the reference's own deploy step (gptq.py:425-452) only works while the group count stays
+                # C / group_size, i.e. with fewer outlier columns than a group
+                raise NotImplementedError('owq needs 0 < n_out < 128 and columns % 128 == 0')
+            if perm is None:
+                perm, invperm = self.owq_order(H, n_out)
+            else:
+                perm = perm.to(H.device).contiguous()
+                invperm = torch.argsort(perm)
+        elif perm is None:
             perm, invperm = self.act_order(H)
         else:
             # caller-supplied column order (argsort leaves the order of equal diagonal entries open)
@@ -175,7 +217,7 @@ class GPTQ:
         L.call('lc_gptq_permute_damp', None, L.LC_F32, L.ptr(H), L.ptr(perm), 0, C, float(hscale),
                float(self.percdamp), int(direct), None, L.ptr(Hp), L.ptr(scratch), L.stream_of(H))
         want_lo = self.trailing == 'tensor' and C % 128 == 0 and C > 1024
-        fac = {'H': H, 'perm': perm, 'invperm': invperm, 'U': None, 'U_lo': None}
+        fac = {'H': H, 'perm': perm, 'invperm': invperm, 'U': None, 'U_lo': None, 'n_out': int(n_out)}
         if native:
             # blocked Cholesky + triangular inverse with the products on the tensor cores; a matrix that
             # is not positive definite is reported through the status word at the next check_status()
@@ -307,20 +349,27 @@ class GPTQ:
         zeros = torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev)
         codes = torch.empty((R, C), dtype=torch.uint8, device=dev) if self.emit_codes else None
         loss_rows = torch.empty(R, dtype=torch.float32, device=dev)
+        # owq: the last n_out (permuted) columns are not quantised; they take the error feedback and stay fp32
+        n_quant = C - int(fac.get('n_out', 0))
         if fac.get('U_lo') is not None and R % 4 == 0:
             panel = torch.empty((2, 1024, R), dtype=torch.float32, device=dev)
             status = torch.zeros(1, dtype=torch.int32, device=dev)
-            L.call('lc_gptq_weight_transform_tc', L.ptr(Wp), L.ptr(U), L.ptr(fac['U_lo']), R, C, int(wq.bit),
-                   int(wq.sym), L.ptr(err), L.ptr(panel[0]), L.ptr(panel[1]), L.ptr(scales), L.ptr(zeros),
-                   L.ptr(codes), L.ptr(loss_rows), L.ptr(status), stream)
+            L.call('lc_gptq_weight_transform_tc_owq', L.ptr(Wp), L.ptr(U), L.ptr(fac['U_lo']), R, C, n_quant,
+                   int(wq.bit), int(wq.sym), L.ptr(err), L.ptr(panel[0]), L.ptr(panel[1]), L.ptr(scales),
+                   L.ptr(zeros), L.ptr(codes), L.ptr(loss_rows), L.ptr(status), stream)
             self._pending_status.append(status)
         else:
-            L.call('lc_gptq_weight_transform', L.ptr(Wp), L.ptr(U), R, C, int(wq.bit), int(wq.sym), L.ptr(err),
-                   L.ptr(scales), L.ptr(zeros), L.ptr(codes), L.ptr(loss_rows), stream)
+            L.call('lc_gptq_weight_transform_owq', L.ptr(Wp), L.ptr(U), R, C, n_quant, int(wq.bit), int(wq.sym),
+                   L.ptr(err), L.ptr(scales), L.ptr(zeros), L.ptr(codes), L.ptr(loss_rows), stream)
         out = torch.empty((R, C), dtype=torch.float32, device=dev)
         L.call('lc_gptq_unpermute', L.ptr(Wp), L.ptr(perm), R, C, L.ptr(out), L.LC_F32, stream)
-        return {'weight': out, 'buf_scales': scales, 'buf_zeros': None if wq.sym else zeros,
-                'buf_perm': perm, 'buf_invperm': invperm, 'codes_perm': codes, 'loss_rows': loss_rows}
+        res = {'weight': out, 'buf_scales': scales, 'buf_zeros': None if wq.sym else zeros,
+               'buf_perm': perm, 'buf_invperm': invperm, 'codes_perm': codes, 'loss_rows': loss_rows}
+        if n_quant < C:
+            res['buf_n_nonout'] = torch.tensor(n_quant)
+            if codes is not None:
+                codes[:, n_quant:] = 0          # the outlier columns have no codes
+        return res
 
     def act_order(self, H):
         """perm = argsort(diag(H), descending) and its inverse (gptq.py:58-64, :158), or (None, None)."""
@@ -377,8 +426,8 @@ class GPTQ:
     def _install(self, layer, res):
         layer.weight.data = res['weight'].reshape(layer.weight.shape)
         wq = self.wquantizer
-        for k in ('buf_scales', 'buf_zeros', 'buf_perm', 'buf_invperm'):
-            v = res[k]
+        for k in ('buf_scales', 'buf_zeros', 'buf_perm', 'buf_invperm', 'buf_n_nonout'):
+            v = res.get(k)
             if v is None:
                 continue
             if k in layer._buffers:
@@ -390,8 +439,10 @@ class GPTQ:
             layer.register_buffer('buf_qmin', wq.qmin.to(layer.weight.device))
         # the solver's codes (permuted order), kept for the deploy-time weight; tied to this very weight
         # tensor so that a weight replaced later falls back to re-quantising
+        # (not with owq: the outlier columns have no codes, deploy re-quantises like the reference)
         codes = res.get('codes_perm')
-        layer._lc_codes = None if codes is None else (codes, layer.weight.data.data_ptr())
+        layer._lc_codes = None if codes is None or res.get('buf_n_nonout') is not None else (
+            codes, layer.weight.data.data_ptr())
 
     @torch.no_grad()
     def w_qdq(self, module, wquantizer):
@@ -414,7 +465,10 @@ class GPTQ:
             weight = weight[:, module.buf_perm]
         args = {'scales': module.buf_scales, 'zeros': getattr(module, 'buf_zeros', None),
                 'qmax': module.buf_qmax, 'qmin': module.buf_qmin}
+        fp_weight = weight[:, int(module.buf_n_nonout):] if self.owq else None       # gptq.py:440-447
         weight = wquantizer.fake_quant_weight_static(weight, args).to(self.model_dtype)
+        if self.owq:
+            weight[:, int(module.buf_n_nonout):] = fp_weight.to(self.model_dtype)
         if self.need_perm:
             weight = weight[:, module.buf_invperm]
         return weight

@@ -4,7 +4,8 @@ Follows llmc/compression/quantization/gptq.py: add_batch :254-295, hessian_sorti
 :58-64, process_hessian_and_weights :128-176, weight_transform :199-244,
 search_column_qparams :359-366, merge/update qparams :344-356, :398-409 and the
 deploy-time w_qdq :425-452.  Only the configuration the hot path covers is restated:
-nn.Linear, per_group with group_size == blocksize, static_groups off, no OWQ.
+nn.Linear, per_group with group_size == blocksize, static_groups off; owq (:44-50, :66-83, :186-188,
+:440-447) with fewer outlier columns than a group.
 """
 import math
 import torch
@@ -29,13 +30,27 @@ def add_batch(state, inp):
     return state
 
 
-def prepare(W, H, percdamp=0.01, actorder=True):
-    """hessian_sorting + process_hessian_and_weights (gptq.py:58-64, :128-176).
+def owq_perm(H, n_out):
+    """hessian_sorting with owq (gptq.py:66-83; owq switches actorder off, gptq.py:47-50): the n_out
+    columns with the largest Hessian diagonal go last, in descending order of it; the others keep
+    their order."""
+    C = H.shape[0]
+    descending_ids = torch.argsort(torch.diag(H), descending=True)
+    keep = torch.full([C], True)
+    keep[descending_ids[:n_out]] = False
+    return torch.cat([torch.arange(C)[keep], descending_ids[:n_out]])
+
+
+def prepare(W, H, percdamp=0.01, actorder=True, n_out=0):
+    """hessian_sorting + process_hessian_and_weights (gptq.py:58-83, :128-176).
     Returns permuted fp32 W, upper Cholesky factor U of the damped inverse Hessian, perm, invperm."""
     W = W.clone().float()
     H = H.clone()
     C = W.shape[1]
-    perm = torch.argsort(torch.diag(H), descending=True) if actorder else torch.arange(C, device=H.device)
+    if n_out:
+        perm = owq_perm(H, n_out)
+    else:
+        perm = torch.argsort(torch.diag(H), descending=True) if actorder else torch.arange(C, device=H.device)
     dead = torch.diag(H) == 0
     H[dead, dead] = 1
     W[:, dead] = 0
@@ -51,16 +66,18 @@ def prepare(W, H, percdamp=0.01, actorder=True):
     return W, U, perm, invperm
 
 
-def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128):
+def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128, n_out=0):
     """gptq.py:199-244.  W is modified in place like the reference; returns
-    (kept weights `tmp`, Losses, per-group scales list, per-group zeros list)."""
+    (kept weights `tmp`, Losses, per-group scales list, per-group zeros list).  With owq the last
+    n_out columns are not quantised (they only receive the error feedback) and `tmp` is zero there."""
     assert group_size == blocksize
     R, C = W.shape
+    n_nonout = C - n_out
     tmp = torch.zeros_like(W)
     Losses = torch.zeros_like(W)
     g_scales, g_zeros = [], []
-    for i1 in range(0, C, blocksize):
-        i2 = min(i1 + blocksize, C)
+    for i1 in range(0, n_nonout, blocksize):
+        i2 = min(i1 + blocksize, n_nonout)
         W1 = W[:, i1:i2].clone()
         U1 = U[i1:i2, i1:i2]
         Err1 = torch.zeros_like(W1)
@@ -68,7 +85,7 @@ def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128):
             w = W1[:, i].clone()
             d = U1[i, i]
             if (i1 + i) % group_size == 0:
-                cols = W[:, i1 + i: min(i1 + i + group_size, C)]
+                cols = W[:, i1 + i: min(i1 + i + group_size, n_nonout)]
                 s, z, qmax, qmin = Q.int_qparams(cols, bit, sym)
                 g_scales.append(s)
                 g_zeros.append(z)
@@ -88,18 +105,23 @@ def merge_group_qparams(per_group):
 
 
 def quantize_layer(W, H, bit=4, sym=False, group_size=128, blocksize=128,
-                   percdamp=0.01, actorder=True):
+                   percdamp=0.01, actorder=True, n_out=0):
     """layer_transform (gptq.py:114-117, :178-196): returns a dict with the reference's
     per-layer results: weight (compensated, fp32, original column order), buf_scales,
-    buf_zeros (permuted-group order), buf_perm, buf_invperm, loss."""
-    Wp, U, perm, invperm = prepare(W, H, percdamp, actorder)
-    tmp, Losses, gs, gz = weight_transform(Wp, U, bit, sym, group_size, blocksize)
+    buf_zeros (permuted-group order), buf_perm, buf_invperm, loss.  n_out > 0 is the owq mode
+    (0 < n_out < group_size with C a multiple of group_size, so that the group count stays C / group_size:
+    the reference's w_qdq only works then): the outlier columns keep their error-compensated fp32 values
+    (gptq.py:186-188)."""
+    Wp, U, perm, invperm = prepare(W, H, percdamp, actorder and not n_out, n_out)
+    tmp, Losses, gs, gz = weight_transform(Wp, U, bit, sym, group_size, blocksize, n_out)
+    if n_out:
+        tmp[:, W.shape[1] - n_out:] = Wp[:, W.shape[1] - n_out:]
     out = {
         'weight': tmp[:, invperm].contiguous(),
         'buf_scales': merge_group_qparams(gs),
         'buf_perm': perm, 'buf_invperm': invperm,
         'loss': float(Losses.sum()),
-        'U': U,
+        'U': U, 'n_nonout': W.shape[1] - n_out,
     }
     out['buf_zeros'] = None if sym else merge_group_qparams(gz)
     return out
@@ -119,8 +141,11 @@ def w_qdq(res, model_dtype, bit=4, sym=False, group_size=128):
     """Deploy-time fake quant (gptq.py:425-452): permute, static qdq, un-permute, model dtype."""
     w = res['weight'][:, res['buf_perm']]
     z = torch.tensor(0.0) if sym else res['buf_zeros']
-    out = Q.int_fake_quant_static(w, res['buf_scales'], z, bit, sym, 'per_group', group_size)
-    return out.to(model_dtype)[:, res['buf_invperm']]
+    out = Q.int_fake_quant_static(w, res['buf_scales'], z, bit, sym, 'per_group', group_size).to(model_dtype)
+    n_nonout = res.get('n_nonout', w.shape[1])
+    if n_nonout < w.shape[1]:
+        out[:, n_nonout:] = w[:, n_nonout:].to(model_dtype)     # owq: the outlier columns stay unquantised
+    return out[:, res['buf_invperm']]
 
 
 def recon_error(W, Wq, X):

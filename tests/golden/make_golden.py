@@ -152,14 +152,16 @@ def make_fp8(rq, out_dir):
     print('fp8_block.pt', len(blk), 'cases')
 
 
-def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01):
-    """Drives the reference GPTQ class on one nn.Linear, bypassing its model plumbing."""
+def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01, n_out=0):
+    """Drives the reference GPTQ class on one nn.Linear, bypassing its model plumbing.  n_out > 0: owq."""
     g = object.__new__(rg.GPTQ)
     g.dev = torch.device('cpu')
     g.wquantizer = rq.IntegerQuantizer(bit, sym, 'per_group', group_size=128)
     g.true_sequential, g.static_groups, g.actorder = True, False, actorder
-    g.percdamp, g.blocksize, g.owq, g.chunk_num = percdamp, 128, False, 1
-    g.need_perm = actorder
+    g.percdamp, g.blocksize, g.owq, g.chunk_num = percdamp, 128, n_out > 0, 1
+    g.need_perm = actorder or n_out > 0
+    if n_out:
+        g.n_out_dict = {'l': n_out}
     g.layers_cache = {'l': {}}
     g.model_dtype = W.dtype
     layer = torch.nn.Linear(W.shape[1], W.shape[0], bias=False, dtype=W.dtype)
@@ -176,14 +178,14 @@ def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01):
     H = g.layers_cache['l']['H'].clone()
     g.layer_transform(layer, 'l')
     fq = g.w_qdq(layer, g.wquantizer)
-    perm = layer.buf_perm if actorder else torch.arange(W.shape[1])
+    perm = layer.buf_perm if (actorder or n_out) else torch.arange(W.shape[1])
     codes = g.wquantizer.quant(layer.weight.data[:, perm].reshape(-1, 128), layer.buf_scales,
                                layer.buf_zeros if not sym else torch.tensor(0.0),
                                layer.buf_qmax, layer.buf_qmin).reshape(W.shape)
     return dict(W=W, X=X, H=H, bit=bit, sym=sym, actorder=actorder, percdamp=percdamp,
                 weight=layer.weight.data.clone(), buf_scales=layer.buf_scales.clone(),
                 buf_zeros=None if sym else layer.buf_zeros.clone(),
-                buf_perm=perm.clone(), codes_perm=codes.to(torch.int16), w_qdq=fq.clone())
+                buf_perm=perm.clone(), codes_perm=codes.to(torch.int16), w_qdq=fq.clone(), n_out=n_out)
 
 
 def make_gptq(rq, rg, out_dir):
@@ -200,6 +202,22 @@ def make_gptq(rq, rg, out_dir):
         cases[name] = _ref_gptq_layer(rq, rg, W, X, 4, sym, act)
     torch.save(cases, os.path.join(out_dir, 'gptq_layer.pt'))
     print('gptq_layer.pt', len(cases), 'cases')
+
+
+def make_gptq_owq(rq, rg, out_dir):
+    """GPTQ with owq (gptq.py:44-50, :66-83): the n_out columns with the largest Hessian diagonal stay fp."""
+    gen = torch.Generator().manual_seed(2002)
+    cases = {}
+    for name, R, C, ns, T, sym, n_out in (('asym_out6', 48, 384, 6, 160, False, 6),
+                                          ('sym_out2', 32, 256, 4, 128, True, 2)):
+        W = (torch.randn(R, C, generator=gen) * 0.02).to(torch.bfloat16)
+        X = torch.randn(ns, T, C, generator=gen)
+        out_ch = torch.randperm(C, generator=gen)[:max(1, C // 50)]
+        X[:, :, out_ch] *= 20
+        X = X.to(torch.bfloat16)
+        cases[name] = _ref_gptq_layer(rq, rg, W, X, 4, sym, False, n_out=n_out)
+    torch.save(cases, os.path.join(out_dir, 'gptq_owq.pt'))
+    print('gptq_owq.pt', len(cases), 'cases')
 
 
 class _TorchProxy:
@@ -373,9 +391,11 @@ if __name__ == '__main__':
     out_dir = os.path.dirname(os.path.abspath(__file__))
     rq, rg = _import_reference(ref_root)
     torch.set_num_threads(1)
-    make_rtn(rq, out_dir)
-    make_rtn_mse(rq, out_dir)
-    make_gptq(rq, rg, out_dir)
-    make_fp8(rq, out_dir)
-    make_awq(rq, out_dir)
-    make_export_configs(ref_root, out_dir)
+    only = set(sys.argv[2:])            # optional: names of the fixtures to (re)make; default all
+    steps = {'rtn': lambda: make_rtn(rq, out_dir), 'rtn_mse': lambda: make_rtn_mse(rq, out_dir),
+             'gptq': lambda: make_gptq(rq, rg, out_dir), 'gptq_owq': lambda: make_gptq_owq(rq, rg, out_dir),
+             'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
+             'export': lambda: make_export_configs(ref_root, out_dir)}
+    for name, step in steps.items():
+        if not only or name in only:
+            step()

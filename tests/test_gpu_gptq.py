@@ -322,3 +322,78 @@ def test_wide_layer_tensor_core_path_vs_oracle():
     mism = float((res['codes_perm'].cpu().to(ref_codes.dtype) != ref_codes).float().mean())
     print(f'R={R} C={C} (tensor-core trailing, oracle Hessian): code mismatch {mism:.5%}')
     assert mism < CODE_MISMATCH_MAX
+
+
+# ---- owq (gptq.py:44-50, :66-83, :186-188, :440-447) -----------------------------------------------------
+
+def _owq_compare(res, fq, ref, ref_fq, W, X, n_out, key, sym=False):
+    C = W.shape[1]
+    nq = C - n_out
+    assert torch.equal(res['buf_perm'].cpu(), ref['buf_perm']), key
+    ref_codes = gptq_ref.codes_permuted(ref, 4, sym)[:, :nq]
+    off = 8 if sym else 0                       # the kernels emit q - qmin
+    mism = float((res['codes_perm'].cpu()[:, :nq].to(ref_codes.dtype) - off != ref_codes).float().mean())
+    # the outlier columns carry the accumulated error feedback, unquantised
+    out_gpu = res['weight'].cpu()[:, ref['buf_perm'][nq:]]
+    out_ref = ref['weight'][:, ref['buf_perm'][nq:]]
+    rel = float((out_gpu - out_ref).abs().max() / out_ref.abs().max())
+    Xf = X.reshape(-1, C).float()
+    e_ref = gptq_ref.recon_error(W.float(), ref_fq.float(), Xf)
+    e_gpu = gptq_ref.recon_error(W.float(), fq.cpu().float(), Xf)
+    print(f'{key}: code mismatch {mism:.5%}, outlier columns rel diff {rel:.2e}, recon ref {e_ref:.6f} gpu {e_gpu:.6f}')
+    assert mism < CODE_MISMATCH_MAX, key
+    assert rel < 2e-3, key
+    assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref, key
+
+
+def _owq_layer(W, H, sym, n_out, hscale=1.0):
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    wq = IntegerQuantizer(4, sym, 'per_group', group_size=128)
+    solver = GPTQ(wq, {'owq': True, 'n_outs': [n_out], 'percdamp': 0.01, 'blocksize': 128}, model_dtype=W.dtype)
+    assert solver.need_perm and not solver.actorder
+    R, C = W.shape
+    layer = torch.nn.Linear(C, R, bias=False, dtype=W.dtype).cuda()
+    layer.weight.data = W.cuda()
+    solver.set_block_linears(['l'])
+    fac = solver.factorize(H.cuda().float(), hscale, n_out=solver.n_out_of('l'))
+    res = solver.solve(layer.weight.data, H.cuda().float(), hscale, factor=fac)
+    solver._install(layer, res)
+    fq = solver.w_qdq(layer, wq)
+    solver.check_status()
+    assert int(layer.buf_n_nonout) == C - n_out and layer._lc_codes is None
+    return fac, res, fq
+
+
+def test_owq_layer_matches_reference_golden(golden):
+    """The reference's own owq runs: same column order, codes of the quantised columns, compensated
+    outlier columns and reconstruction error."""
+    for key, c in golden('gptq_owq.pt').items():
+        fac, res, fq = _owq_layer(c['W'], c['H'], c['sym'], c['n_out'])
+        ref = {'weight': c['weight'], 'buf_scales': c['buf_scales'], 'buf_zeros': c['buf_zeros'],
+               'buf_perm': c['buf_perm'], 'buf_invperm': torch.argsort(c['buf_perm'])}
+        _owq_compare(res, fq, ref, c['w_qdq'], c['W'], c['X'], c['n_out'], key, c['sym'])
+
+
+@pytest.mark.parametrize('R,C,n_out', [(256, 2304, 6), (128, 1024, 2), (64, 2048, 127)])
+def test_owq_vs_oracle(R, C, n_out):
+    """owq against the CPU oracle, on the tensor-core trailing path (C > 1024: the ragged last block
+    sits inside a panel whose GEMM levels contract over whole blocks) and the FFMA path."""
+    g = torch.Generator().manual_seed(2700 + C + n_out)
+    ns, T = 10, 512
+    W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16)
+    X = _x(g, ns, T, C)
+    st = gptq_ref.hessian_init(C)
+    for i in range(ns):
+        gptq_ref.add_batch(st, X[i:i + 1])
+    ref = gptq_ref.quantize_layer(W, st['H'], actorder=False, n_out=n_out)
+    fac, res, fq = _owq_layer(W, st['H'], False, n_out)
+    assert (fac['U_lo'] is not None) == (C > 1024)
+    _owq_compare(res, fq, ref, gptq_ref.w_qdq(ref, torch.bfloat16), W, X, n_out, f'R={R} C={C} n_out={n_out}')
+
+
+def test_owq_rejects_what_the_reference_cannot_deploy():
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    solver = GPTQ(IntegerQuantizer(4, False, 'per_group', group_size=128), {'owq': True, 'n_outs': [128]})
+    H = torch.eye(256, device='cuda')
+    with pytest.raises(NotImplementedError):
+        solver.factorize(H, 1.0, n_out=128)

@@ -82,6 +82,23 @@ def test_gptq_oracle_matches_reference(golden):
         _eq(gptq_ref.w_qdq(res, c['W'].dtype, c['bit'], c['sym']), c['w_qdq'])
 
 
+def test_gptq_owq_oracle_matches_reference(golden):
+    """owq: the n_out columns with the largest Hessian diagonal are permuted to the end and stay
+    unquantised (error feedback only); everything else as GPTQ without act-order."""
+    torch.set_num_threads(1)
+    cases = golden('gptq_owq.pt')
+    assert len(cases) == 2
+    for key, c in cases.items():
+        res = gptq_ref.quantize_layer(c['W'], c['H'], bit=c['bit'], sym=c['sym'], percdamp=c['percdamp'],
+                                      actorder=False, n_out=c['n_out'])
+        _eq(res['buf_perm'], c['buf_perm'])
+        _eq(res['weight'], c['weight'])
+        _eq(res['buf_scales'], c['buf_scales'])
+        if not c['sym']:
+            _eq(res['buf_zeros'], c['buf_zeros'])
+        _eq(gptq_ref.w_qdq(res, c['W'].dtype, c['bit'], c['sym']), c['w_qdq'])
+
+
 def test_group_not_divisible_raises():
     import pytest
     with pytest.raises(ValueError):
