@@ -98,6 +98,24 @@ int lc_gptq_dequant_unpermute(const uint8_t* codes, const float* scales, const f
                               int64_t rows, int64_t cols, int bits, int sym, void* out, int out_dtype,
                               lc_stream_t stream);
 
+/* Per-tensor ranges of a batch of calibration activations (static activation quantisation:
+ * BaseQuantizer.get_minmax_range with granularity 'per_tensor' inside get_minmax_stats and
+ * get_static_moving_minmax_range, llmc/compression/quantization/quant.py:134-137, :223-250, :523-542).
+ *   tensors, numels  HOST arrays of `count` device pointers (contiguous tensors of `dtype`) and their
+ *                    element counts (> 0: the reference's torch.max raises on an empty tensor)
+ *   min_out, max_out count fp32 values each (exact: every `dtype` value is an fp32 value); NaN
+ *                    propagates like torch.max / torch.min
+ * Every tensor is read once, all of them by one launch per 64 tensors. */
+int lc_act_range_per_tensor(const void* const* tensors, const int64_t* numels, int count, int dtype,
+                            float* min_out, float* max_out, lc_stream_t stream);
+
+/* The moving average of get_static_moving_minmax_range (quant.py:534-538) over the `count` per-tensor
+ * values above, in order: m = v[0]; m = m + alpha * (v[i] - m), every op rounded to `dtype` as the
+ * reference's 0-dim tensor arithmetic does.  out2[0] = moving min, out2[1] = moving max (fp32 holding
+ * `dtype` values). */
+int lc_act_range_moving(const float* mins, const float* maxs, int count, int dtype, double alpha,
+                        float* out2, lc_stream_t stream);
+
 /* MSE range search (calib_algo 'mse'): BaseQuantizer.get_mse_range with the integer quantizer's
  * get_qparams and quant_dequant inside its loop (llmc/compression/quantization/quant.py:147-205,
  * :544-558, :698-716).  For each group of `group` elements along cols (0 = the whole row) the range

@@ -4,15 +4,19 @@
 names of llmc/compression/quantization/quant.py (BaseQuantizer :48-103, IntegerQuantizer
 :660-959, FloatQuantizer :962-1228) so that the algorithm classes and replacement modules that
 call them work unchanged, but every method body is one launch of a fused sm_100a kernel through
-the C ABI.  Configurations outside the accelerated path (calib_algo other than 'minmax' and,
-for integer weights, 'mse'; per_tensor / per_head / per_block granularity, round_zp=False,
-mixed-precision index args) raise NotImplementedError: there is no fallback.
+the C ABI.  Configurations outside the accelerated path (calib_algo other than 'minmax', for
+integer weights 'mse', and for per_tensor activations 'static_minmax' / 'static_moving_minmax';
+per_head granularity, per_tensor weights, round_zp=False, mixed-precision index args) raise
+NotImplementedError: there is no fallback.
 """
+import ctypes
+
 import torch
 
 from . import _lib as L
 
 _INT_GRANS = ('per_group', 'per_channel', 'per_token')
+_STATIC_ALGOS = ('static_minmax', 'static_moving_minmax')
 
 
 class BaseQuantizer(object):
@@ -37,10 +41,13 @@ class BaseQuantizer(object):
         self.ste = kwargs.get('ste', False)
         self.ste_all = bool(kwargs.get('ste_all', False))
 
-    def _check_supported(self, allow_mse=False):
-        if self.calib_algo != 'minmax' and not (allow_mse and self.calib_algo == 'mse'):
+    def _check_supported(self, allow_mse=False, per_tensor=False):
+        """per_tensor: the caller is one of the static per-tensor activation methods."""
+        ok = (self.calib_algo == 'minmax' or (allow_mse and self.calib_algo == 'mse')
+              or (per_tensor and self.calib_algo in _STATIC_ALGOS))
+        if not ok:
             raise NotImplementedError(f"calib_algo '{self.calib_algo}' is outside the B200 hot path")
-        if self.granularity not in _INT_GRANS:
+        if self.granularity not in _INT_GRANS and not (per_tensor and self.granularity == 'per_tensor'):
             raise NotImplementedError(f"granularity '{self.granularity}' is outside the B200 hot path")
         if not self.round_zp:
             raise NotImplementedError('round_zp=False is outside the B200 hot path')
@@ -59,7 +66,7 @@ class BaseQuantizer(object):
         g = self._group_len(tensor.shape[-1])
         if self.granularity == 'per_group' and g:
             return tensor.reshape(-1, g)
-        if self.granularity in _INT_GRANS:
+        if self.granularity in _INT_GRANS or self.granularity == 'per_tensor':
             return tensor
         raise NotImplementedError(self.granularity)
 
@@ -91,7 +98,8 @@ class IntegerQuantizer(BaseQuantizer):
     # ---- one fused launch ------------------------------------------------------------------
     def _launch(self, t2d, group, scales_in=None, zeros_in=None, fake=False, codes=L.LC_CODES_NONE,
                 params=False):
-        self._check_supported(allow_mse=scales_in is not None)
+        self._check_supported(allow_mse=scales_in is not None,
+                              per_tensor=scales_in is not None and self.granularity == 'per_tensor')
         L.require_cuda(t2d, scales_in, zeros_in)
         rows, cols = t2d.shape
         g = group if group else cols
@@ -234,7 +242,108 @@ class IntegerQuantizer(BaseQuantizer):
                                      None if self.sym else args.get('zeros'), fake=True)
         return fake.reshape(t.shape)
 
-    fake_quant_act_static = fake_quant_weight_static
+    def fake_quant_act_static(self, act, args={}):
+        """quant.py:718-751.  per_tensor (the only granularity the reference allows for static
+        activations, base_blockwise_quantization.py:183-186): the scalar scale / zero point enter the
+        row kernel as one value per row.  They are first cast to the activation dtype, which is what the
+        reference's tensor ops do with the 0-dim CUDA buffers the calibration registered."""
+        if self.granularity != 'per_tensor':
+            return self.fake_quant_weight_static(act, args)
+        self._reject_args(args, ('scales', 'zeros', 'qmax', 'qmin'))
+        t, t2d = _as_2d(act)
+        rows = t2d.shape[0]
+        scales, zeros = args['scales'], args.get('zeros')
+        if scales.numel() != 1:
+            raise NotImplementedError('per_tensor static quantisation takes one scale')
+        s_rows = scales.to(device=t.device, dtype=t.dtype).reshape(1).expand(rows).contiguous()
+        z_rows = None
+        if not self.sym:
+            z_rows = zeros.to(device=t.device, dtype=t.dtype).reshape(1).expand(rows).contiguous()
+        fake, _, _, _ = self._launch(t2d, 0, s_rows, z_rows, fake=True)
+        return fake.reshape(t.shape)
+
+    # ---- static per-tensor activation ranges (quant.py:105-122, :134-137, :223-262, :523-585) ----
+    def _tensor_ranges(self, tensors):
+        """(mins, maxs) of a list of CUDA tensors of one dtype: fp32 device vectors, one launch."""
+        self._check_supported(per_tensor=True)
+        if self.granularity != 'per_tensor':
+            raise NotImplementedError('batched activation ranges are per_tensor (the reference allows no other '
+                                      'granularity for static activations)')
+        tensors = [t if t.is_contiguous() else t.contiguous() for t in tensors]
+        L.require_cuda(*tensors)
+        n = len(tensors)
+        if any(t.dtype != tensors[0].dtype or t.device != tensors[0].device for t in tensors):
+            raise NotImplementedError('calibration tensors of one input must share dtype and device')
+        dev = tensors[0].device
+        mins = torch.empty(n, dtype=torch.float32, device=dev)
+        maxs = torch.empty(n, dtype=torch.float32, device=dev)
+        ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in tensors])
+        numels = (ctypes.c_int64 * n)(*[t.numel() for t in tensors])
+        L.call('lc_act_range_per_tensor', ptrs, numels, n, L.lc_dtype(tensors[0]), L.ptr(mins), L.ptr(maxs),
+               L.stream_of(tensors[0]))
+        return mins, maxs, tensors
+
+    def get_minmax_range(self, tensor):
+        """per_tensor (quant.py:135-137): 0-dim (min, max) in the tensor's dtype.  For the other
+        granularities the range never leaves the fused quantisation kernels."""
+        mins, maxs, _ = self._tensor_ranges([tensor])
+        return mins[0].to(tensor.dtype), maxs[0].to(tensor.dtype)
+
+    def reshape_batch_tensors(self, act_tensors):
+        """quant.py:105-122."""
+        assert len(act_tensors) > 0, (
+            'Calibration data is insufficient. Please provide more data to ensure '
+            'all experts in the MOE receive an adequate number of tokens.')
+        if isinstance(act_tensors[0], tuple):
+            return [torch.stack(list(ts)) for ts in zip(*act_tensors)]
+        if len(act_tensors) == 1:
+            return [[act_tensors[0][i] for i in range(act_tensors[0].size(0))]]
+        return [act_tensors]
+
+    def get_minmax_stats(self, act_tensors):
+        """quant.py:223-250: per input, the (N,) fp32 host vectors of every tensor's min and max."""
+        stats = {}
+        for idx, tensors in enumerate(act_tensors):
+            mins, maxs, _ = self._tensor_ranges(list(tensors))
+            stats[idx] = {'min': mins.cpu(), 'max': maxs.cpu()}
+        return stats
+
+    def get_static_minmax_range(self, act_tensors):
+        """quant.py:252-262: the mean of the per-tensor ranges, on the host in fp32 like the reference."""
+        stats = self.get_minmax_stats(self.reshape_batch_tensors(act_tensors))
+        return ([r['min'].mean(dim=0) for r in stats.values()], [r['max'].mean(dim=0) for r in stats.values()])
+
+    def get_static_moving_minmax_range(self, act_tensors, alpha):
+        """quant.py:523-542: exponential moving average of the per-tensor ranges in the tensors' dtype;
+        one launch for the ranges, one single-warp launch for the average."""
+        mins_out, maxs_out = [], []
+        for tensors in self.reshape_batch_tensors(act_tensors):
+            mins, maxs, ts = self._tensor_ranges(list(tensors))
+            out2 = torch.empty(2, dtype=torch.float32, device=mins.device)
+            L.call('lc_act_range_moving', L.ptr(mins), L.ptr(maxs), len(ts), L.lc_dtype(ts[0]), float(alpha),
+                   L.ptr(out2), L.stream_of(ts[0]))
+            mins_out.append(out2[0].to(ts[0].dtype))
+            maxs_out.append(out2[1].to(ts[0].dtype))
+        return mins_out, maxs_out
+
+    def get_batch_tensors_qparams(self, act_tensors, alpha=0.01, args={}):
+        """quant.py:560-585 ('static_hist' is not built)."""
+        if self.calib_algo == 'static_minmax':
+            min_vals, max_vals = self.get_static_minmax_range(act_tensors)
+        elif self.calib_algo == 'static_moving_minmax':
+            min_vals, max_vals = self.get_static_moving_minmax_range(act_tensors, alpha)
+        elif self.calib_algo == 'static_hist':
+            raise NotImplementedError("calib_algo 'static_hist' is outside the B200 hot path")
+        else:
+            raise ValueError(f'Unsupported calibration algorithm: {self.calib_algo}')
+        scales_list, zeros_list, qmin_list, qmax_list = [], [], [], []
+        for mn, mx in zip(min_vals, max_vals):
+            scales, zeros, qmax, qmin = self.get_qparams((mn, mx), mn.device)
+            scales_list.append(scales)
+            zeros_list.append(zeros)
+            qmin_list.append(qmin)
+            qmax_list.append(qmax)
+        return scales_list, zeros_list, qmin_list, qmax_list
 
     def _real(self, weight, scales=None, zeros=None):
         t, t2d = _as_2d(weight)

@@ -29,7 +29,7 @@ def group_view(t, granularity, group_size=None):
                     f'Dimension {t.shape[-1]} not divisible by group size {group_size}')
             return t.reshape(-1, group_size)
         return t
-    if granularity in ('per_channel', 'per_token'):
+    if granularity in ('per_channel', 'per_token', 'per_tensor'):
         return t
     raise NotImplementedError(granularity)
 
@@ -84,6 +84,58 @@ def int_qparams_from_range(mn, mx, bit, sym):
     s = (mx - mn).clamp(min=1e-5) / (qmax - qmin)
     z = (qmin - torch.round(mn / s)).clamp(qmin, qmax)
     return s, z, qmax, qmin
+
+
+def reshape_batch_tensors(act_tensors):
+    """quant.py:105-122: a list of tensors is one input; a single tensor is split along its batch
+    dim; tuples (several inputs per call) are stacked per input."""
+    assert len(act_tensors) > 0
+    if isinstance(act_tensors[0], tuple):
+        return [torch.stack(list(ts)) for ts in zip(*act_tensors)]
+    if len(act_tensors) == 1:
+        return [[act_tensors[0][i] for i in range(act_tensors[0].size(0))]]
+    return [act_tensors]
+
+
+def static_minmax_range(act_tensors):
+    """get_static_minmax_range with per_tensor granularity (quant.py:134-137, :223-262): per input,
+    the mean over the calibration tensors of each tensor's min and max, taken in fp32 on the host."""
+    mins, maxs = [], []
+    for tensors in reshape_batch_tensors(act_tensors):
+        mn = torch.stack([torch.min(t).detach().cpu().to(torch.float32) for t in tensors])
+        mx = torch.stack([torch.max(t).detach().cpu().to(torch.float32) for t in tensors])
+        mins.append(mn.mean(dim=0))
+        maxs.append(mx.mean(dim=0))
+    return mins, maxs
+
+
+def static_moving_minmax_range(act_tensors, alpha=0.01):
+    """get_static_moving_minmax_range with per_tensor granularity (quant.py:523-542): an
+    exponential moving average over the calibration tensors, in the tensors' dtype."""
+    mins, maxs = [], []
+    for tensors in reshape_batch_tensors(act_tensors):
+        m_min = m_max = None
+        for t in tensors:
+            mn, mx = torch.min(t), torch.max(t)
+            if m_min is None:
+                m_min, m_max = mn, mx
+            else:
+                m_min = m_min + alpha * (mn - m_min)
+                m_max = m_max + alpha * (mx - m_max)
+        mins.append(m_min)
+        maxs.append(m_max)
+    return mins, maxs
+
+
+def batch_tensors_qparams(act_tensors, bit, sym, calib_algo, alpha=0.01):
+    """get_batch_tensors_qparams (quant.py:560-585) for 'static_minmax' / 'static_moving_minmax'."""
+    if calib_algo == 'static_minmax':
+        mins, maxs = static_minmax_range(act_tensors)
+    elif calib_algo == 'static_moving_minmax':
+        mins, maxs = static_moving_minmax_range(act_tensors, alpha)
+    else:
+        raise ValueError(f'Unsupported calibration algorithm: {calib_algo}')
+    return [int_qparams_from_range(mn, mx, bit, sym) for mn, mx in zip(mins, maxs)]
 
 
 def mse_range(g, bit, sym, maxshrink=0.8, mse_grid=100, norm=2.4):

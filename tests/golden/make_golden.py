@@ -117,6 +117,28 @@ def make_rtn_mse(rq, out_dir):
     print('rtn_mse.pt', len(cases), 'cases')
 
 
+def make_act_static(rq, out_dir):
+    """Static per-tensor activation quantisation: get_batch_tensors_qparams with calib_algo
+    'static_minmax' / 'static_moving_minmax' and fake_quant_act_static with the resulting buffers."""
+    gen = torch.Generator().manual_seed(2003)
+    cases = {}
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for algo in ('static_minmax', 'static_moving_minmax'):
+            for sym in (True, False):
+                acts = [(torch.randn(2, 12, 128, generator=gen) * (1 + 0.3 * i) + 0.1 * i).to(dtype) for i in range(6)]
+                qz = rq.IntegerQuantizer(8, sym, 'per_tensor', calib_algo=algo)
+                sl, zl, qminl, qmaxl = qz.get_batch_tensors_qparams([a.clone() for a in acts])
+                assert len(sl) == 1
+                x = (torch.randn(2, 9, 128, generator=gen) * 1.5).to(dtype)
+                args = {'scales': sl[0], 'zeros': zl[0], 'qmax': qmaxl[0], 'qmin': qminl[0]}
+                fq = qz.fake_quant_act_static(x.clone(), args)
+                name = f"{str(dtype).split('.')[-1]}_{algo}_{'sym' if sym else 'asym'}"
+                cases[name] = dict(acts=acts, dtype=dtype, algo=algo, sym=sym, bit=8, scales=sl[0], zeros=zl[0],
+                                   x=x, fake=fq)
+    torch.save(cases, os.path.join(out_dir, 'act_static.pt'))
+    print('act_static.pt', len(cases), 'cases')
+
+
 def make_fp8(rq, out_dir):
     rq.float_quantize = lambda x, e, m, rounding: x.to(torch.float8_e4m3fn).float()
     gen = torch.Generator().manual_seed(5001)
@@ -394,7 +416,7 @@ if __name__ == '__main__':
     only = set(sys.argv[2:])            # optional: names of the fixtures to (re)make; default all
     steps = {'rtn': lambda: make_rtn(rq, out_dir), 'rtn_mse': lambda: make_rtn_mse(rq, out_dir),
              'gptq': lambda: make_gptq(rq, rg, out_dir), 'gptq_owq': lambda: make_gptq_owq(rq, rg, out_dir),
-             'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
+             'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
              'export': lambda: make_export_configs(ref_root, out_dir)}
     for name, step in steps.items():
         if not only or name in only:

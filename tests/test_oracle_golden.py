@@ -99,6 +99,20 @@ def test_gptq_owq_oracle_matches_reference(golden):
         _eq(gptq_ref.w_qdq(res, c['W'].dtype, c['bit'], c['sym']), c['w_qdq'])
 
 
+def test_static_activation_ranges_oracle_matches_reference(golden):
+    """calib_algo 'static_minmax' / 'static_moving_minmax' (per_tensor): qparams from a batch of
+    calibration activations and the static fake quant that uses them."""
+    cases = golden('act_static.pt')
+    assert len(cases) == 12
+    for key, c in cases.items():
+        (s, z, qmax, qmin), = quant_ref.batch_tensors_qparams([a.clone() for a in c['acts']], c['bit'], c['sym'],
+                                                              c['algo'])
+        _eq(s, c['scales'])
+        _eq(z, c['zeros'])
+        fq = quant_ref.int_fake_quant_static(c['x'], s, z, c['bit'], c['sym'], 'per_tensor')
+        _eq(fq, c['fake'])
+
+
 def test_group_not_divisible_raises():
     import pytest
     with pytest.raises(ValueError):
