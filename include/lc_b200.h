@@ -87,6 +87,26 @@ int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int6
                      void* fake_out, void* codes_out, int code_fmt, void* scales_out,
                      void* zeros_out, lc_stream_t stream);
 
+/* One level of Weight48IntegerQuantizer (llmc/compression/quantization/quant.py:1232-1287): the code
+ * range (from `symmetric` or `int_range`), and the clamps get_qparams applies to the scale and the
+ * zero point (quant.py:1318-1323): [scales_qmin, scales_qmax] from scales_bit / scales_symmetric, else
+ * -inf .. inf; [zeros_qmin, zeros_qmax] from zeros_bit / zeros_symmetric, else [qmin, qmax]. */
+typedef struct {
+  float qmin, qmax;
+  int symmetric;
+  float scales_min, scales_max;
+  float zeros_min, zeros_max;
+} lc_w48_level;
+
+/* Weight48IntegerQuantizer.fake_quant_weight_dynamic (quant.py:1338-1367) in one pass: quantise each
+ * row with the bit8 level (per_channel), quantise those codes per `group` elements with the bit4 level
+ * (per_group), dequantise back through both.  in / out: rows x cols of `dtype`; bit-identical to the
+ * reference's op chain in that dtype.  cols % group == 0 (the reference raises otherwise); group a
+ * multiple of 8 (4 for fp32) with group / 8 (group / 4) a power of two <= 32, e.g. 128; cols <= 32768
+ * (16384 for fp32). */
+int lc_rtn_w48_fake_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t group,
+                          const lc_w48_level* bit8, const lc_w48_level* bit4, void* out, lc_stream_t stream);
+
 /* GPTQ.w_qdq (gptq.py:425-452: weight[:, perm] -> static fake quant -> [:, invperm] -> model dtype) from
  * the codes lc_gptq_weight_transform* already produced, in one pass: out[r][c] = ((codes[r][j] + qmin) -
  * zeros[r][j / 128]) * scales[r][j / 128], j = invperm[c] (invperm NULL: identity), rounded once to

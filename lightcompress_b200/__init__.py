@@ -4,10 +4,10 @@ Host-side mirrors of the reference plugin interface (`IntegerQuantizer`, `FloatQ
 `GPTQ`, `RTN`) over a C-ABI library of hand-written sm_100a CUDA kernels.
 """
 from . import _lib  # noqa: F401  (raises if the CUDA library is not built)
-from .quant import FloatQuantizer, IntegerQuantizer  # noqa: F401
+from .quant import FloatQuantizer, IntegerQuantizer, Weight48IntegerQuantizer  # noqa: F401
 from .gptq import GPTQ  # noqa: F401
 from .rtn import RTN  # noqa: F401
 from .awq import Awq  # noqa: F401
 from .blockwise import GPTQBlockwise, FakeQuantLinear, llama_subsets  # noqa: F401
 
-__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'GPTQ', 'RTN', 'Awq', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets']
+__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'Weight48IntegerQuantizer', 'GPTQ', 'RTN', 'Awq', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets']

@@ -478,6 +478,78 @@ class FloatQuantizer(BaseQuantizer):
                 f'granularity={self.granularity}, kwargs={self.kwargs}, qmin={self.qmin}, qmax={self.qmax})')
 
 
+class _W48Level(ctypes.Structure):
+    """lc_w48_level of the C ABI."""
+    _fields_ = [('qmin', ctypes.c_float), ('qmax', ctypes.c_float), ('symmetric', ctypes.c_int),
+                ('scales_min', ctypes.c_float), ('scales_max', ctypes.c_float),
+                ('zeros_min', ctypes.c_float), ('zeros_max', ctypes.c_float)]
+
+
+class Weight48IntegerQuantizer(BaseQuantizer):
+    """quant.py:1230-1367 over lc_rtn_w48_fake_quant: weights to 8 bits per row, those codes to 4 bits
+    per group, and back, in one pass.  The constructor keeps the reference's `bit_settings` (same keys,
+    including its use of scales_bit for the zero-point limits, quant.py:1272-1281)."""
+
+    def __init__(self, bit, bit4, bit8, **kwargs):
+        super().__init__(bit, None, None, **kwargs)
+        self.quant_type = 'int-quant-w48'
+        assert self.bit == 48, 'Only support 48-bit quantization'
+        self.bit_settings = {4: dict(bit4), 8: dict(bit8)}
+        for b in (4, 8):
+            st = self.bit_settings[b]
+            if 'int_range' in st:
+                st['qmin'], st['qmax'] = st['int_range'][0], st['int_range'][1]
+            elif st['symmetric']:
+                st['qmin'], st['qmax'] = -(2 ** (b - 1)), 2 ** (b - 1) - 1
+            else:
+                st['qmin'], st['qmax'] = 0, 2 ** b - 1
+            st['qmin'], st['qmax'] = torch.tensor(st['qmin']), torch.tensor(st['qmax'])
+            if 'scales_bit' in st:
+                if st['scales_symmetric']:
+                    st['scales_qmin'], st['scales_qmax'] = -(2 ** (st['scales_bit'] - 1)), 2 ** (st['scales_bit'] - 1) - 1
+                else:
+                    st['scales_qmin'], st['scales_qmax'] = 0, 2 ** st['scales_bit'] - 1
+            else:
+                st['scales_qmin'], st['scales_qmax'] = -torch.inf, torch.inf
+            if 'zeros_bit' in st:
+                if st['zeros_symmetric']:
+                    st['zeros_qmin'], st['zeros_qmax'] = -(2 ** (st['scales_bit'] - 1)), 2 ** (st['scales_bit'] - 1) - 1
+                else:
+                    st['zeros_qmin'], st['zeros_qmax'] = 0, 2 ** st['scales_bit'] - 1
+            else:
+                st['zeros_qmin'], st['zeros_qmax'] = st['qmin'], st['qmax']
+
+    def _level(self, b):
+        st = self.bit_settings[b]
+        return _W48Level(float(st['qmin']), float(st['qmax']), int(bool(st['symmetric'])),
+                         float(st['scales_qmin']), float(st['scales_qmax']),
+                         float(st['zeros_qmin']), float(st['zeros_qmax']))
+
+    def fake_quant_weight_dynamic(self, weight, args={}):
+        if args:
+            raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
+        if self.calib_algo != 'minmax':
+            raise NotImplementedError(f"calib_algo '{self.calib_algo}' is outside the B200 hot path")
+        g8, g4 = self.bit_settings[8].get('granularity'), self.bit_settings[4].get('granularity')
+        if g8 == 'per_group' or g4 != 'per_group':
+            # the kernel is built for the layout the reference ships (rows to 8 bits, groups to 4 bits)
+            raise NotImplementedError('the two-level kernel takes a row-wise 8-bit and a per_group 4-bit level')
+        L.require_cuda(weight)
+        t, t2d = _as_2d(weight)
+        rows, cols = t2d.shape
+        group = int(self.bit_settings[4]['group_size'])
+        if cols % group:
+            raise ValueError(f'Dimension {cols} not divisible by group size {group}')
+        out = torch.empty_like(t2d)
+        l8, l4 = self._level(8), self._level(4)
+        L.call('lc_rtn_w48_fake_quant', L.ptr(t2d), L.lc_dtype(t2d), rows, cols, group, ctypes.byref(l8),
+               ctypes.byref(l4), L.ptr(out), L.stream_of(t2d))
+        return out.reshape(t.shape)
+
+    def __repr__(self):
+        return f'Weight48IntegerQuantizer(bit_settings={self.bit_settings})'
+
+
 def weight_cast_to_fp8(weight, block_size=128):
     """quant.py:36-45 (kernel.py:73-83 when Triton is usable): (e4m3 weight, fp32 scales per block)."""
     q = FloatQuantizer('e4m3', True, 'per_block', block_size=block_size, use_qtorch=True)

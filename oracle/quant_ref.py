@@ -86,6 +86,74 @@ def int_qparams_from_range(mn, mx, bit, sym):
     return s, z, qmax, qmin
 
 
+def w48_level(cfg, bit):
+    """Weight48IntegerQuantizer.__init__ (quant.py:1232-1287) for one of its two levels: code range
+    and the clamps of scale and zero point.  (The reference derives the zero-point clamp from
+    scales_bit, quant.py:1272-1281; restated as is.)"""
+    c = dict(cfg)
+    if 'int_range' in c:
+        qmin, qmax = c['int_range']
+    elif c['symmetric']:
+        qmin, qmax = -(2 ** (bit - 1)), 2 ** (bit - 1) - 1
+    else:
+        qmin, qmax = 0, 2 ** bit - 1
+    out = {'symmetric': c['symmetric'], 'qmin': torch.tensor(qmin), 'qmax': torch.tensor(qmax),
+           'granularity': c.get('granularity'), 'group_size': c.get('group_size')}
+    if 'scales_bit' in c:
+        if c['scales_symmetric']:
+            out['scales_qmin'], out['scales_qmax'] = -(2 ** (c['scales_bit'] - 1)), 2 ** (c['scales_bit'] - 1) - 1
+        else:
+            out['scales_qmin'], out['scales_qmax'] = 0, 2 ** c['scales_bit'] - 1
+    else:
+        out['scales_qmin'], out['scales_qmax'] = -torch.inf, torch.inf
+    if 'zeros_bit' in c:
+        if c['zeros_symmetric']:
+            out['zeros_qmin'], out['zeros_qmax'] = -(2 ** (c['scales_bit'] - 1)), 2 ** (c['scales_bit'] - 1) - 1
+        else:
+            out['zeros_qmin'], out['zeros_qmax'] = 0, 2 ** c['scales_bit'] - 1
+    else:
+        out['zeros_qmin'], out['zeros_qmax'] = out['qmin'], out['qmax']
+    return out
+
+
+def _w48_qparams(t, lv):
+    """get_minmax_range over the last dim + Weight48IntegerQuantizer.get_qparams (quant.py:1304-1323)."""
+    mx = t.amax(dim=-1, keepdim=True)
+    mn = t.amin(dim=-1, keepdim=True)
+    qmin, qmax = lv['qmin'].to(t.device), lv['qmax'].to(t.device)
+    if lv['symmetric']:
+        scales = torch.max(mx.abs(), mn.abs()).clamp(min=1e-5) / qmax
+        zeros = torch.tensor(0.0)
+    else:
+        scales = (mx - mn).clamp(min=1e-5) / (qmax - qmin)
+        zeros = qmin - torch.round(mn / scales)
+    scales = scales.clamp(lv['scales_qmin'], lv['scales_qmax'])
+    zeros = zeros.clamp(lv['zeros_qmin'], lv['zeros_qmax'])
+    return scales, zeros, qmax, qmin
+
+
+def w48_fake_quant(w, bit4, bit8):
+    """Weight48IntegerQuantizer.fake_quant_weight_dynamic (quant.py:1338-1367): 16 -> 8 bits per the
+    bit8 level, 8 -> 4 bits per the bit4 level on the codes, and back."""
+    l8, l4 = w48_level(bit8, 8), w48_level(bit4, 4)
+
+    def view(t, lv):
+        if lv['granularity'] == 'per_group':
+            if t.shape[-1] % lv['group_size']:
+                raise ValueError(f"Dimension {t.shape[-1]} not divisible by group size {lv['group_size']}")
+            return t.reshape(-1, lv['group_size'])
+        return t
+    t8 = view(w, l8)
+    s8, z8, qmax8, qmin8 = _w48_qparams(t8, l8)
+    c8 = torch.clamp(torch.round(t8 / s8) + z8, qmin8, qmax8)
+    shape8, dtype8 = c8.shape, c8.dtype
+    t4 = view(c8, l4)
+    s4, z4, qmax4, qmin4 = _w48_qparams(t4, l4)
+    c4 = torch.clamp(torch.round(t4 / s4) + z4, qmin4, qmax4)
+    d8 = ((c4 - z4) * s4).reshape(shape8).to(dtype8)
+    return ((d8 - z8) * s8).reshape(w.shape).to(w.dtype)
+
+
 def reshape_batch_tensors(act_tensors):
     """quant.py:105-122: a list of tensors is one input; a single tensor is split along its batch
     dim; tuples (several inputs per call) are stacked per input."""

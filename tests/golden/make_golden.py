@@ -14,6 +14,7 @@ un-vendored `qtorch.quant.float_quantize` by a float8_e4m3fn round trip; they ar
 Inputs are small and stored next to the outputs, so the tests never need the reference.
 """
 import contextlib
+import copy
 import os
 import sys
 import types
@@ -137,6 +138,31 @@ def make_act_static(rq, out_dir):
                                    x=x, fake=fq)
     torch.save(cases, os.path.join(out_dir, 'act_static.pt'))
     print('act_static.pt', len(cases), 'cases')
+
+
+W48_BIT4 = {'symmetric': False, 'granularity': 'per_group', 'group_size': 128, 'scales_bit': 8,
+            'scales_symmetric': True, 'zeros_bit': 8, 'zeros_symmetric': True}
+W48_BIT8 = {'symmetric': True, 'granularity': 'per_channel', 'int_range': [-120, 120]}
+
+
+def make_w48(rq, out_dir):
+    """Weight48IntegerQuantizer.fake_quant_weight_dynamic with the levels of the reference's own
+    rtn_w_a_wint4aint8.yml, plus a symmetric 4-bit level without scale / zero-point limits."""
+    gen = torch.Generator().manual_seed(2004)
+    cases = {}
+    plain4 = {'symmetric': True, 'granularity': 'per_group', 'group_size': 128}
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for name, bit4 in (('yml', W48_BIT4), ('sym4', plain4)):
+            for R, C in ((24, 384), (5, 1024)):
+                w = (torch.randn(R, C, generator=gen) * 0.05)
+                w[0, :128] = 0.0                   # a constant group: the 1e-5 floor of the 4-bit scale
+                w[1, 7] = 3.0                      # an outlier that saturates the row's 8-bit range
+                w = w.to(dtype)
+                qz = rq.Weight48IntegerQuantizer(48, copy.deepcopy(bit4), copy.deepcopy(W48_BIT8))
+                fq = qz.fake_quant_weight_dynamic(w.clone())
+                cases[f"{str(dtype).split('.')[-1]}_{name}_{R}x{C}"] = dict(w=w, bit4=bit4, bit8=W48_BIT8, fake=fq)
+    torch.save(cases, os.path.join(out_dir, 'rtn_w48.pt'))
+    print('rtn_w48.pt', len(cases), 'cases')
 
 
 def make_fp8(rq, out_dir):
@@ -416,7 +442,7 @@ if __name__ == '__main__':
     only = set(sys.argv[2:])            # optional: names of the fixtures to (re)make; default all
     steps = {'rtn': lambda: make_rtn(rq, out_dir), 'rtn_mse': lambda: make_rtn_mse(rq, out_dir),
              'gptq': lambda: make_gptq(rq, rg, out_dir), 'gptq_owq': lambda: make_gptq_owq(rq, rg, out_dir),
-             'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
+             'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
              'export': lambda: make_export_configs(ref_root, out_dir)}
     for name, step in steps.items():
         if not only or name in only:

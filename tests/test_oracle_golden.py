@@ -113,6 +113,14 @@ def test_static_activation_ranges_oracle_matches_reference(golden):
         _eq(fq, c['fake'])
 
 
+def test_w48_oracle_matches_reference(golden):
+    """Weight48IntegerQuantizer: 8-bit rows, then 4-bit groups of the codes, and back."""
+    cases = golden('rtn_w48.pt')
+    assert len(cases) == 12
+    for key, c in cases.items():
+        _eq(quant_ref.w48_fake_quant(c['w'], c['bit4'], c['bit8']), c['fake'])
+
+
 def test_group_not_divisible_raises():
     import pytest
     with pytest.raises(ValueError):
