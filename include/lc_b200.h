@@ -87,6 +87,23 @@ int lc_rtn_int_quant(const void* in, int dtype, int64_t rows, int64_t cols, int6
                      void* fake_out, void* codes_out, int code_fmt, void* scales_out,
                      void* zeros_out, lc_stream_t stream);
 
+/* QUIK's activation statistic (get_tensor_scale, llmc/compression/quantization/quik.py:35-42):
+ * running[c] = max(running[c], max over tokens of |x[t][c]|), fp32 on the device (the reference keeps
+ * it on the host); start from zeros.  x: tokens x cols of `dtype`, cols a multiple of 8 (4 for fp32).
+ * NaN sticks, like torch.max. */
+int lc_quik_col_absmax(const void* x, int dtype, int64_t tokens, int64_t cols, float* running,
+                       lc_stream_t stream);
+
+/* IntegerQuantizer.fake_quant_weight_dynamic / fake_quant_act_dynamic with args['int_indices'] and
+ * args['fp_indices'] (quant.py:753-782, :832-868; used by QUIK.w_qdq / a_qdq, quik.py:128-151) for
+ * per_channel / per_token granularity: each row is quantised over its integer columns only, the
+ * floating-point columns pass through.  col_mask holds one byte per column (8-byte aligned):
+ * 0 = quantise, 1 = keep, 2 = write zero (a column in neither index list, as the reference's
+ * zeros_like + two scatters leave it).  cols a multiple of 8 (4 for fp32), at most 32768 (16384).
+ * Bit-identical to the reference's gather -> quant_dequant -> scatter chain. */
+int lc_rtn_int_fake_quant_masked(const void* in, int dtype, int64_t rows, int64_t cols, int bits, int sym,
+                                 const uint8_t* col_mask, void* out, lc_stream_t stream);
+
 /* One level of Weight48IntegerQuantizer (llmc/compression/quantization/quant.py:1232-1287): the code
  * range (from `symmetric` or `int_range`), and the clamps get_qparams applies to the scale and the
  * zero point (quant.py:1318-1323): [scales_qmin, scales_qmax] from scales_bit / scales_symmetric, else

@@ -67,6 +67,8 @@ SIGNATURES = {
     'lc_act_range_per_tensor': [_p, _p, _i, _i, _p, _p, _p],
     'lc_act_range_moving': [_p, _p, _i, _i, _d, _p, _p],
     'lc_rtn_w48_fake_quant': [_p, _i, _i64, _i64, _i64, _p, _p, _p, _p],
+    'lc_quik_col_absmax': [_p, _i, _i64, _i64, _p, _p],
+    'lc_rtn_int_fake_quant_masked': [_p, _i, _i64, _i64, _i, _i, _p, _p, _p],
     'lc_rtn_mse_range': [_p, _i, _i64, _i64, _i64, _i, _i, _d, _i, _f, _p, _p, _p],
     'lc_rope_apply': [_p, _p, _p, _i, _i64, _i, _i, _i64, _p, _p],
     'lc_silu_mul': [_p, _p, _i, _i64, _p, _p],

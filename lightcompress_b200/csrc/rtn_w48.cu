@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(256) w48_kernel(W48Args a) {
   const int lg = a.group / N;       // power of two, <= 32
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float abs8 = nan_max(fabsf(a.l8.qmin), fabsf(a.l8.qmax));
+  const bool z4_small = fabsf(a.l4.z_lo) <= 128.f && fabsf(a.l4.z_hi) <= 128.f;
 
   for (int64_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
     const uint4* in = reinterpret_cast<const uint4*>(a.in) + row * nvec;
@@ -148,8 +149,12 @@ __global__ void __launch_bounds__(256) w48_kernel(W48Args a) {
 #pragma unroll
         for (int e = 0; e < N; ++e) {
           const float q4 = int_quant_fast<T>(q8[e], c4, qr4);                       // step 2
-          const float d8 = E::rnd(__fmul_rn(E::rnd(__fsub_rn(q4, z4)), s4));        // step 3
-          d[e] = E::rnd(__fmul_rn(E::rnd(__fsub_rn(d8, z8)), s8));                  // step 4
+          // step 3: q4 - z4 is an integer; below 256 in magnitude it is exact in every T
+          const float t4 = z4_small ? __fsub_rn(q4, z4) : E::rnd(__fsub_rn(q4, z4));
+          const float d8 = E::rnd(__fmul_rn(t4, s4));
+          // step 4: subtracting a zero zero-point changes nothing; the store rounds the product to T
+          const float t8 = z8 == 0.f ? d8 : E::rnd(__fsub_rn(d8, z8));
+          d[e] = __fmul_rn(t8, s8);
         }
         __stcs(out + i, pack_vec<T, N>(d));
       }

@@ -221,7 +221,40 @@ class IntegerQuantizer(BaseQuantizer):
         if bad:
             raise NotImplementedError(f'args {bad} are outside the B200 hot path')
 
+    def _fake_masked(self, tensor, args):
+        """Mixed precision (quant.py:753-782, :832-868 with int_indices / fp_indices): rows quantised over
+        their integer columns, floating-point columns passed through, in one kernel.  `current_bit` is
+        accepted and, as in the reference, changes nothing: qmin / qmax were fixed by the constructor."""
+        self._reject_args(args, ('int_indices', 'fp_indices', 'current_bit'))
+        self._check_supported()
+        if self.granularity == 'per_group':
+            raise NotImplementedError('int_indices with per_group (groups over the gathered column order) is '
+                                      'outside the B200 hot path')
+        L.require_cuda(tensor)
+        t, t2d = _as_2d(tensor)
+        rows, cols = t2d.shape
+        int_ids, fp_ids = args['int_indices'], args['fp_indices']
+        key = (int_ids.data_ptr(), fp_ids.data_ptr(), int(int_ids.numel()), int(fp_ids.numel()), cols, str(t.device))
+        cache = self.__dict__.setdefault('_mask_cache', {})
+        mask = cache.get(key)
+        if mask is None:
+            mask = torch.full((cols,), 2, dtype=torch.uint8, device=t.device)
+            mask[int_ids.to(t.device)] = 0
+            mask[fp_ids.to(t.device)] = 1          # the reference scatters the fp part last
+            if len(cache) > 256:
+                cache.clear()
+            # the index tensors are held so that their addresses cannot be reused under the cached key
+            cache[key] = (mask, int_ids, fp_ids)
+        else:
+            mask = mask[0]
+        out = torch.empty_like(t2d)
+        L.call('lc_rtn_int_fake_quant_masked', L.ptr(t2d), L.lc_dtype(t2d), rows, cols, int(self.bit), int(self.sym),
+               L.ptr(mask), L.ptr(out), L.stream_of(t2d))
+        return out.reshape(t.shape)
+
     def fake_quant_weight_dynamic(self, weight, args={}):
+        if 'int_indices' in args:
+            return self._fake_masked(weight, args)
         self._reject_args(args)
         if self.calib_algo == 'mse':
             return self._fake_mse(weight)
@@ -230,6 +263,8 @@ class IntegerQuantizer(BaseQuantizer):
         return fake.reshape(t.shape)
 
     def fake_quant_act_dynamic(self, act, args={}):
+        if 'int_indices' in args:
+            return self._fake_masked(act, args)
         self._reject_args(args)
         t, t2d = _as_2d(act)
         fake, _, _, _ = self._launch(t2d, self._group_len(t.shape[-1]), fake=True)

@@ -86,6 +86,32 @@ def int_qparams_from_range(mn, mx, bit, sym):
     return s, z, qmax, qmin
 
 
+def int_fake_quant_mixed(t, bit, sym, granularity, int_indices, fp_indices):
+    """fake_quant_weight_dynamic / fake_quant_act_dynamic with int_indices / fp_indices (quant.py:753-782,
+    :832-868): the last dim's integer columns are gathered and quantised, then both parts are scattered
+    into a zeroed tensor."""
+    q = t[..., int_indices]
+    fp = t[..., fp_indices]
+    q = int_fake_quant_dynamic(q, bit, sym, granularity)
+    out = torch.zeros_like(t)
+    out[..., int_indices] = q
+    out[..., fp_indices] = fp
+    return out
+
+
+def quik_col_absmax(running, tensor):
+    """QUIK get_tensor_scale (quik.py:35-42): running per-channel max |x| in fp32 on the host."""
+    hidden = tensor.shape[-1]
+    m = torch.max(tensor.view(-1, hidden).abs().detach(), dim=0)[0].float().cpu()
+    return m if running is None else torch.max(running, m)
+
+
+def quik_select(layer_scales, outlier_num):
+    """QUIK.block_opt (quik.py:119-120): the outlier_num channels with the largest statistic stay fp."""
+    order = torch.sort(layer_scales)[1]
+    return order[:-outlier_num], order[-outlier_num:]
+
+
 def w48_level(cfg, bit):
     """Weight48IntegerQuantizer.__init__ (quant.py:1232-1287) for one of its two levels: code range
     and the clamps of scale and zero point.  (The reference derives the zero-point clamp from

@@ -165,6 +165,37 @@ def make_w48(rq, out_dir):
     print('rtn_w48.pt', len(cases), 'cases')
 
 
+def make_quik(rq, out_dir):
+    """The mixed-precision fake quant QUIK's w_qdq / a_qdq run (IntegerQuantizer with int_indices /
+    fp_indices), with the column split quik.py:119-120 derives from the activation statistic."""
+    gen = torch.Generator().manual_seed(2005)
+    cases = {}
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for sym in (True, False):
+            hidden, n_fp = 256, 24
+            acts = [torch.randn(2, 20, hidden, generator=gen) for _ in range(3)]
+            for a in acts:
+                a[:, :, ::11] *= 12
+            acts = [a.to(dtype) for a in acts]
+            stat = None
+            for a in acts:
+                m = torch.max(a.view(-1, hidden).abs().detach(), dim=0)[0].float().cpu()      # quik.py:35-42
+                stat = m if stat is None else torch.max(stat, m)
+            order = torch.sort(stat)[1]
+            int_ids, fp_ids = order[:-n_fp].clone(), order[-n_fp:].clone()
+            args = {'int_indices': int_ids, 'fp_indices': fp_ids, 'current_bit': torch.tensor(8)}
+            w = (torch.randn(40, hidden, generator=gen) * 0.05).to(dtype)
+            wq = rq.IntegerQuantizer(4, sym, 'per_channel')
+            aq = rq.IntegerQuantizer(8, sym, 'per_token')
+            fw = wq.fake_quant_weight_dynamic(w.clone(), dict(args))
+            fa = aq.fake_quant_act_dynamic(acts[0].clone(), dict(args))
+            name = f"{str(dtype).split('.')[-1]}_{'sym' if sym else 'asym'}"
+            cases[name] = dict(acts=acts, stat=stat, int_ids=int_ids, fp_ids=fp_ids, w=w, sym=sym, wbit=4, abit=8,
+                               fake_w=fw, fake_a=fa)
+    torch.save(cases, os.path.join(out_dir, 'quik_mixed.pt'))
+    print('quik_mixed.pt', len(cases), 'cases')
+
+
 def make_fp8(rq, out_dir):
     rq.float_quantize = lambda x, e, m, rounding: x.to(torch.float8_e4m3fn).float()
     gen = torch.Generator().manual_seed(5001)
@@ -442,7 +473,7 @@ if __name__ == '__main__':
     only = set(sys.argv[2:])            # optional: names of the fixtures to (re)make; default all
     steps = {'rtn': lambda: make_rtn(rq, out_dir), 'rtn_mse': lambda: make_rtn_mse(rq, out_dir),
              'gptq': lambda: make_gptq(rq, rg, out_dir), 'gptq_owq': lambda: make_gptq_owq(rq, rg, out_dir),
-             'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
+             'quik': lambda: make_quik(rq, out_dir), 'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
              'export': lambda: make_export_configs(ref_root, out_dir)}
     for name, step in steps.items():
         if not only or name in only:

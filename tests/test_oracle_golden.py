@@ -121,6 +121,23 @@ def test_w48_oracle_matches_reference(golden):
         _eq(quant_ref.w48_fake_quant(c['w'], c['bit4'], c['bit8']), c['fake'])
 
 
+def test_quik_mixed_precision_oracle_matches_reference(golden):
+    """QUIK: activation statistic, column split and the int / fp mixed fake quant of weight and activation."""
+    cases = golden('quik_mixed.pt')
+    assert len(cases) == 6
+    for key, c in cases.items():
+        stat = None
+        for a in c['acts']:
+            stat = quant_ref.quik_col_absmax(stat, a)
+        _eq(stat, c['stat'])
+        int_ids, fp_ids = quant_ref.quik_select(stat, c['fp_ids'].numel())
+        _eq(int_ids, c['int_ids'])
+        _eq(fp_ids, c['fp_ids'])
+        _eq(quant_ref.int_fake_quant_mixed(c['w'], c['wbit'], c['sym'], 'per_channel', int_ids, fp_ids), c['fake_w'])
+        _eq(quant_ref.int_fake_quant_mixed(c['acts'][0], c['abit'], c['sym'], 'per_token', int_ids, fp_ids),
+            c['fake_a'])
+
+
 def test_group_not_divisible_raises():
     import pytest
     with pytest.raises(ValueError):
