@@ -82,16 +82,38 @@ __global__ void __launch_bounds__(256) row_masked_kernel(MaskedArgs a) {
       else mk[k] = *reinterpret_cast<const uint32_t*>(a.mask + i * 4);
     }
   }
+  // short rows: the next row's vectors are requested before this row is processed, so that a CTA
+  // does not sit idle for a DRAM round trip per row
+  constexpr bool kPrefetch = V <= 4;
+  uint4 v[V], nx[kPrefetch ? V : 1];
+  if (kPrefetch && (int64_t)blockIdx.x < a.rows) {
+    const uint4* in0 = reinterpret_cast<const uint4*>(a.in) + (int64_t)blockIdx.x * nvec;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const int64_t i = threadIdx.x + (int64_t)k * 256;
+      if (i < nvec) v[k] = __ldcs(in0 + i);
+    }
+  }
   for (int64_t row = blockIdx.x; row < a.rows; row += gridDim.x) {
     const uint4* in = reinterpret_cast<const uint4*>(a.in) + row * nvec;
     uint4* out = reinterpret_cast<uint4*>(a.out) + row * nvec;
-    uint4 v[V];
+    if constexpr (kPrefetch) {
+      const int64_t next = row + gridDim.x;
+      if (next < a.rows) {
+        const uint4* inn = reinterpret_cast<const uint4*>(a.in) + next * nvec;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const int64_t i = threadIdx.x + (int64_t)k * 256;
+          if (i < nvec) nx[k] = __ldcs(inn + i);
+        }
+      }
+    }
     float mx = -INFINITY, mn = INFINITY;
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;
       if (i < nvec) {
-        v[k] = __ldcs(in + i);
+        if constexpr (!kPrefetch) v[k] = __ldcs(in + i);
         float f[N];
         const T* p = reinterpret_cast<const T*>(&v[k]);
 #pragma unroll
@@ -143,6 +165,10 @@ __global__ void __launch_bounds__(256) row_masked_kernel(MaskedArgs a) {
         }
         __stcs(out + i, o);
       }
+    }
+    if constexpr (kPrefetch) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) v[k] = nx[k];
     }
   }
 }
