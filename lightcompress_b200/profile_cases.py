@@ -1,7 +1,7 @@
 """Small, self-terminating workloads of each kernel family, sized for profiler captures
 (inputs larger than the 126 MB L2, a few hundred MB on the device, a handful of launches).
 
-    python -m lightcompress_b200.profile_cases hessian|hessian_wide|rtn|fp8|gptq|factor|block_ops|fp8_linear|mse|awq_clip [--launches N]
+    python -m lightcompress_b200.profile_cases hessian|hessian_wide|rtn|fp8|gptq|factor|block_ops|fp8_linear|mse|awq_clip|act_static|quik|w48 [--launches N]
 """
 import argparse
 
@@ -146,11 +146,51 @@ def gptq(n):
     torch.cuda.synchronize()
 
 
+def act_static(n):
+    """Per-tensor ranges of 8 calibration tensors of 64 MB (bf16) in one launch."""
+    qz = IntegerQuantizer(8, True, 'per_tensor', calib_algo='static_minmax')
+    g = torch.Generator(device='cuda').manual_seed(8)
+    acts = [torch.randn(4, 2048, 4096, generator=g, device='cuda').to(torch.bfloat16) for _ in range(8)]
+    for _ in range(n):
+        qz._tensor_ranges(acts)
+    torch.cuda.synchronize()
+
+
+def quik(n):
+    """QUIK: per-channel max |x| of 65536 x 4096 bf16 and the masked per-token fake quant of 32768 x 4096."""
+    from .quik import QUIK
+    g = torch.Generator(device='cuda').manual_seed(9)
+    x = torch.randn(65536, 4096, generator=g, device='cuda').to(torch.bfloat16)
+    aq = IntegerQuantizer(8, True, 'per_token')
+    q = QUIK(IntegerQuantizer(4, True, 'per_channel'), aq, {'fp_relative': False, 'fp_features': 256, 'fp_threshold': 0.0})
+    order = torch.randperm(4096, generator=g, device='cuda')
+    args = {'int_indices': order[:-256], 'fp_indices': order[-256:]}
+    for _ in range(n):
+        q.get_tensor_scale('l', x)
+        aq.fake_quant_act_dynamic(x[:32768], args)
+    torch.cuda.synchronize()
+
+
+def w48(n):
+    """Weight48IntegerQuantizer on a 16384 x 8192 bf16 weight (the levels of rtn_w_a_wint4aint8.yml)."""
+    from . import Weight48IntegerQuantizer
+    bit4 = {'symmetric': False, 'granularity': 'per_group', 'group_size': 128, 'scales_bit': 8,
+            'scales_symmetric': True, 'zeros_bit': 8, 'zeros_symmetric': True}
+    bit8 = {'symmetric': True, 'granularity': 'per_channel', 'int_range': [-120, 120]}
+    qz = Weight48IntegerQuantizer(48, bit4, bit8)
+    g = torch.Generator(device='cuda').manual_seed(10)
+    w = torch.randn(16384, 8192, generator=g, device='cuda').to(torch.bfloat16)
+    for _ in range(n):
+        qz.fake_quant_weight_dynamic(w)
+    torch.cuda.synchronize()
+
+
 if __name__ == '__main__':
     ap = argparse.ArgumentParser()
-    ap.add_argument('case', choices=['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'factor', 'block_ops', 'fp8_linear', 'mse', 'awq_clip'])
+    ap.add_argument('case', choices=['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'factor', 'block_ops', 'fp8_linear', 'mse', 'awq_clip', 'act_static', 'quik', 'w48'])
     ap.add_argument('--launches', type=int, default=3)
     a = ap.parse_args()
     {'hessian': hessian, 'hessian_wide': hessian_wide, 'rtn': rtn, 'fp8': fp8, 'gptq': gptq, 'factor': factor,
-     'block_ops': block_ops, 'fp8_linear': fp8_linear, 'mse': mse, 'awq_clip': awq_clip}[a.case](a.launches)
+     'block_ops': block_ops, 'fp8_linear': fp8_linear, 'mse': mse, 'awq_clip': awq_clip, 'act_static': act_static,
+     'quik': quik, 'w48': w48}[a.case](a.launches)
     print('done', a.case)
