@@ -12,6 +12,9 @@
 //    depend on the order of its columns, so a per-column byte mask (1 = keep floating point) gives
 //    the same result in one read and one write; columns in neither index list come out zero, as in
 //    the reference.  Arithmetic as in the one-level kernels (bit-identical to the op chain).
+#include <type_traits>
+
+#include "bf16x2.cuh"
 #include "lc_common.cuh"
 
 namespace lc {
@@ -82,6 +85,20 @@ __global__ void __launch_bounds__(256) row_masked_kernel(MaskedArgs a) {
       else mk[k] = *reinterpret_cast<const uint32_t*>(a.mask + i * 4);
     }
   }
+  // bf16: 16-bit select masks per pair of elements (quantise / keep), for the packed-arithmetic path
+  constexpr bool kPacked = std::is_same<T, __nv_bfloat16>::value && V <= 4;
+  uint32_t sel[kPacked ? V : 1][4], keep[kPacked ? V : 1][4];
+  if constexpr (kPacked) {
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned b0 = (unsigned)((mk[k] >> (16 * j)) & 0xff), b1 = (unsigned)((mk[k] >> (16 * j + 8)) & 0xff);
+        sel[k][j] = (b0 == 0 ? 0xffffu : 0u) | (b1 == 0 ? 0xffff0000u : 0u);
+        keep[k][j] = (b0 == 1 ? 0xffffu : 0u) | (b1 == 1 ? 0xffff0000u : 0u);
+      }
+    }
+  }
   // short rows: the next row's vectors are requested before this row is processed, so that a CTA
   // does not sit idle for a DRAM round trip per row
   constexpr bool kPrefetch = V <= 4;
@@ -114,14 +131,27 @@ __global__ void __launch_bounds__(256) row_masked_kernel(MaskedArgs a) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;
       if (i < nvec) {
         if constexpr (!kPrefetch) v[k] = __ldcs(in + i);
-        float f[N];
-        const T* p = reinterpret_cast<const T*>(&v[k]);
+        if constexpr (kPacked) {
+          // elements that are not quantised are replaced by -inf / +inf before the packed max / min
+          const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+          __nv_bfloat162 mx2 = bf2_of(0xff80ff80u), mn2 = bf2_of(0x7f807f80u);
 #pragma unroll
-        for (int e = 0; e < N; ++e) {
-          f[e] = E::to_f(p[e]);
-          if (((mk[k] >> (8 * e)) & 0xff) == 0) {
-            mx = nan_max(mx, f[e]);
-            mn = nan_min(mn, f[e]);
+          for (int j = 0; j < 4; ++j) {
+            mx2 = __hmax2_nan(mx2, bf2_of((w[j] & sel[k][j]) | (0xff80ff80u & ~sel[k][j])));
+            mn2 = __hmin2_nan(mn2, bf2_of((w[j] & sel[k][j]) | (0x7f807f80u & ~sel[k][j])));
+          }
+          mx = nan_max(mx, nan_max(bf_lo(u32_of(mx2)), bf_hi(u32_of(mx2))));
+          mn = nan_min(mn, nan_min(bf_lo(u32_of(mn2)), bf_hi(u32_of(mn2))));
+        } else {
+          float f[N];
+          const T* p = reinterpret_cast<const T*>(&v[k]);
+#pragma unroll
+          for (int e = 0; e < N; ++e) {
+            f[e] = E::to_f(p[e]);
+            if (((mk[k] >> (8 * e)) & 0xff) == 0) {
+              mx = nan_max(mx, f[e]);
+              mn = nan_min(mn, f[e]);
+            }
           }
         }
       }
@@ -147,6 +177,30 @@ __global__ void __launch_bounds__(256) row_masked_kernel(MaskedArgs a) {
     float s, z;
     int_qparams<T>(mn, mx, a.qr, a.sym, s, z);
     const QuantCtx c = make_quant_ctx(s, z, nan_max(fabsf(mx), fabsf(mn)));
+    if constexpr (kPacked) {
+      if (!c.exact) {
+        const QuantCtx2 c2 = make_ctx2(c, a.qr);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const int64_t i = threadIdx.x + (int64_t)k * 256;
+          if (i < nvec) {
+            const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t d = u32_of(dequant2(quant2(bf_lo(w[j]), bf_hi(w[j]), c, c2), c2));
+              o[j] = (d & sel[k][j]) | (w[j] & keep[k][j]);      // neither bit set: zero
+            }
+            __stcs(out + i, make_uint4(o[0], o[1], o[2], o[3]));
+          }
+        }
+        if constexpr (kPrefetch) {
+#pragma unroll
+          for (int k = 0; k < V; ++k) v[k] = nx[k];
+        }
+        continue;
+      }
+    }
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;

@@ -9,6 +9,9 @@
 // dtype after every op), so the result is bit-identical.  The divisions w / s use the reciprocal-and-
 // correct scheme of the one-level kernels (exact, see div_rint): at both levels the dividend and the
 // scale are values of the dtype (the level-2 dividends are integers of at most 8 bits).
+#include <type_traits>
+
+#include "bf16x2.cuh"
 #include "lc_common.cuh"
 
 namespace lc {
@@ -46,8 +49,8 @@ __device__ __forceinline__ void w48_qparams(float mn, float mx, const LevelCfg& 
     t = rintf(t);
     z = E::rnd(__fsub_rn(c.qmin, t));
   }
-  s = clampf(s, c.s_lo, c.s_hi);
-  z = clampf(z, c.z_lo, c.z_hi);
+  s = E::rnd(clampf(s, c.s_lo, c.s_hi));     // the clamp bounds need not be values of T
+  z = E::rnd(clampf(z, c.z_lo, c.z_hi));
 }
 
 template <typename T, int N>
@@ -120,20 +123,48 @@ __global__ void __launch_bounds__(256) w48_kernel(W48Args a) {
     const QRange qr8{a.l8.qmin, a.l8.qmax};
     const QRange qr4{a.l4.qmin, a.l4.qmax};
 
+    // bf16 rows without NaN / inf / degenerate scale: packed bf16x2 arithmetic (see bf16x2.cuh)
+    bool packed = false;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) packed = !c8.exact;
+    QuantCtx2 c8p;
+    __nv_bfloat162 z8p, s8p;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      c8p = make_ctx2(c8, qr8);
+      z8p = c8p.z;
+      s8p = c8p.s;
+    }
+
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;
       const bool live = i < nvec;
       float q8[N];
+      uint32_t q8w[4] = {0u, 0u, 0u, 0u};
       float gmx = -INFINITY, gmn = INFINITY;
       if (live) {
-        float f[N];
-        unpack_vec<T, N>(v[k], f);
+        if (packed) {
+          if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+            const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+            __nv_bfloat162 mx2 = bf2_of(0xff80ff80u), mn2 = bf2_of(0x7f807f80u);
 #pragma unroll
-        for (int e = 0; e < N; ++e) {
-          q8[e] = int_quant_fast<T>(f[e], c8, qr8);       // step 1: the 8-bit codes, as values of T
-          gmx = nan_max(gmx, q8[e]);
-          gmn = nan_min(gmn, q8[e]);
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 q = quant2(bf_lo(w[j]), bf_hi(w[j]), c8, c8p);   // step 1
+              q8w[j] = u32_of(q);
+              mx2 = __hmax2_nan(mx2, q);
+              mn2 = __hmin2_nan(mn2, q);
+            }
+            gmx = nan_max(bf_lo(u32_of(mx2)), bf_hi(u32_of(mx2)));
+            gmn = nan_min(bf_lo(u32_of(mn2)), bf_hi(u32_of(mn2)));
+          }
+        } else {
+          float f[N];
+          unpack_vec<T, N>(v[k], f);
+#pragma unroll
+          for (int e = 0; e < N; ++e) {
+            q8[e] = int_quant_fast<T>(f[e], c8, qr8);       // step 1: the 8-bit codes, as values of T
+            gmx = nan_max(gmx, q8[e]);
+            gmn = nan_min(gmn, q8[e]);
+          }
         }
       }
       // the lg lanes that hold one group are adjacent and aligned (nvec is a multiple of lg)
@@ -145,6 +176,28 @@ __global__ void __launch_bounds__(256) w48_kernel(W48Args a) {
         float s4, z4;
         w48_qparams<T>(gmn, gmx, a.l4, s4, z4);
         const QuantCtx c4 = make_quant_ctx(s4, z4, abs8);
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+          if (packed && !c4.exact) {
+            const QuantCtx2 c4p = make_ctx2(c4, qr4);
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 q4 = quant2(bf_lo(q8w[j]), bf_hi(q8w[j]), c4, c4p);      // step 2
+              const __nv_bfloat162 d8 = dequant2(q4, c4p);                                  // step 3
+              const __nv_bfloat162 t8 = z8 == 0.f ? d8 : __hsub2(d8, z8p);                  // step 4
+              o[j] = u32_of(__hmul2(t8, s8p));
+            }
+            __stcs(out + i, make_uint4(o[0], o[1], o[2], o[3]));
+            continue;
+          }
+          if (packed) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              q8[2 * j] = bf_lo(q8w[j]);
+              q8[2 * j + 1] = bf_hi(q8w[j]);
+            }
+          }
+        }
         float d[N];
 #pragma unroll
         for (int e = 0; e < N; ++e) {
