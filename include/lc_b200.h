@@ -377,6 +377,24 @@ int lc_gptq_weight_transform_tc_owq(float* W, const float* U, const float* U_lo,
                                     float* panel_lo, float* scales, float* zeros, uint8_t* codes_u8,
                                     float* loss_rows, int32_t* status, lc_stream_t stream);
 
+/* GPTQ.weight_transform with static groups (special.static_groups, gptq.py:224-227, with
+ * search_group_qparams :377-393): the qparams are not searched block by block but taken from the
+ * layer's round-to-nearest buffers, and with act-order column i of the permuted weight uses the group
+ * of its ORIGINAL column.
+ *   scales, zeros  INPUT, rows x ceil(cols / 128) fp32 in the layer's buf_scales layout (row-major:
+ *                  row r, group g at r * n_groups + g); zeros may be NULL when sym
+ *   col_group      cols int32: group of permuted column j, i.e. perm[j] / 128 (j / 128 without act-order)
+ * Everything else as lc_gptq_weight_transform / lc_gptq_weight_transform_tc; nothing is written to
+ * scales / zeros. */
+int lc_gptq_weight_transform_static(float* W, const float* U, int64_t rows, int64_t cols, int bits, int sym,
+                                    float* scratch_err, const float* scales, const float* zeros,
+                                    const int32_t* col_group, uint8_t* codes_u8, float* loss_rows,
+                                    lc_stream_t stream);
+int lc_gptq_weight_transform_tc_static(float* W, const float* U, const float* U_lo, int64_t rows, int64_t cols,
+                                       int bits, int sym, float* scratch_err, float* panel_hi, float* panel_lo,
+                                       const float* scales, const float* zeros, const int32_t* col_group,
+                                       uint8_t* codes_u8, float* loss_rows, int32_t* status, lc_stream_t stream);
+
 /* lc_gptq_weight_transform for callers that cannot allocate.  (No counterpart in the reference:
  * its solver allocates freely through torch.)
  *

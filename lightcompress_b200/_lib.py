@@ -41,6 +41,8 @@ SIGNATURES = {
     'lc_gptq_weight_transform': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p],
     'lc_gptq_weight_transform_owq': [_p, _p, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p],
     'lc_gptq_weight_transform_tc_owq': [_p, _p, _p, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p],
+    'lc_gptq_weight_transform_static': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p, _p],
+    'lc_gptq_weight_transform_tc_static': [_p, _p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p],
     'lc_gptq_weight_transform_noalloc': [_p, _p, _i64, _i64, _i, _i, _p, _p, _p, _p, _p],
     'lc_gptq_split_tf32': [_p, _i64, _p, _p],
     'lc_gptq_panel_update': [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _p],

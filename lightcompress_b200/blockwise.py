@@ -175,10 +175,16 @@ class GPTQBlockwise:
         # as one stacked matrix (q/k/v: 12288 rows, gate/up: 22016), which cuts the number of latency-bound
         # 128-column steps by the number of linears; in a process group every rank takes a row range.
         stacked = layers[0].weight.data if len(layers) == 1 else torch.cat([l.weight.data for l in layers], 0)
+        static = None
+        if self.solver.static_groups:
+            # static groups: the layers' own round-to-nearest buffers, stacked like the rows
+            parts = [self.solver.static_qparams(l) for l in layers]
+            static = (torch.cat([p[0] for p in parts], 0),
+                      None if parts[0][1] is None else torch.cat([p[1] for p in parts], 0))
         if world == 1:
-            res = self.solver.solve(stacked, H, hscale, factor=fac)
+            res = self.solver.solve(stacked, H, hscale, factor=fac, static=static)
         else:
-            res = self._sharded_solve(stacked, fac, rank, world)
+            res = self._sharded_solve(stacked, fac, rank, world, static)
         n_groups = (H.shape[0] + 127) // 128
         r0 = 0
         for layer in layers:
@@ -186,13 +192,13 @@ class GPTQBlockwise:
             part = {'weight': res['weight'][r0:r1], 'buf_scales': res['buf_scales'][r0 * n_groups:r1 * n_groups],
                     'buf_zeros': None if res['buf_zeros'] is None else res['buf_zeros'][r0 * n_groups:r1 * n_groups],
                     'buf_perm': res['buf_perm'], 'buf_invperm': res['buf_invperm'],
-                    'buf_n_nonout': res.get('buf_n_nonout')}
+                    'buf_n_nonout': res.get('buf_n_nonout'), 'static': res.get('static')}
             if res.get('codes_perm') is not None:
                 part['codes_perm'] = res['codes_perm'][r0:r1]
             self.solver._install(layer, part)
             r0 = r1
 
-    def _sharded_solve(self, stacked, fac, rank, world):
+    def _sharded_solve(self, stacked, fac, rank, world, static=None):
         """Row range `rank` of the stacked weight solved here, all ranges broadcast: every rank returns
         the same full result."""
         H = fac['H']
@@ -211,12 +217,13 @@ class GPTQBlockwise:
         blocks = (R + 127) // 128
         bounds = [min(R, 128 * ((blocks * r) // world)) for r in range(world)] + [R]
         a, b = bounds[rank], bounds[rank + 1]
-        mine = self.solver.solve(stacked, H, rows=(a, b), factor=fac) if b > a else None
+        mine = self.solver.solve(stacked, H, rows=(a, b), factor=fac, static=static) if b > a else None
         for owner in range(world):
             a, b = bounds[owner], bounds[owner + 1]
             if b <= a:
                 continue
-            for key in ('weight', 'buf_scales', 'buf_zeros'):
+            # static groups: the qparams are inputs that every rank already holds
+            for key in (('weight',) if static is not None else ('weight', 'buf_scales', 'buf_zeros')):
                 dst = full[key]
                 if dst is None:
                     continue
@@ -224,6 +231,8 @@ class GPTQBlockwise:
                 if owner == rank:
                     view.copy_(mine[key])
                 dist.broadcast(view, src=owner)
+        if static is not None:
+            full['buf_scales'], full['buf_zeros'], full['static'] = static[0], static[1], True
         return full
 
     # ---- the block -----------------------------------------------------------------------------

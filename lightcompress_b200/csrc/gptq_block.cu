@@ -41,6 +41,9 @@ struct BlockArgs {
   int64_t rows, cols, col0, n_groups;
   int count, sym;
   QRange qr;
+  // static groups (gptq.py:224-227): scales / zeros are INPUT tables (rows x n_groups) and column
+  // col0 + i uses group col_group[col0 + i] of its row; NULL = qparams from the block's columns
+  const int32_t* col_group;
 };
 
 __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
@@ -87,10 +90,25 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
     mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
   }
-  float s, z;
-  int_qparams<float>(mn, mx, a.qr, a.sym, s, z);
+  const bool is_static = a.col_group != nullptr;
+  float s = 1.f, z = 0.f;
+  if (!is_static) int_qparams<float>(mn, mx, a.qr, a.sym, s, z);
   // error feedback can move a weight a little outside the block's initial range: leave headroom
-  const QuantCtx qc = make_quant_ctx(s, z, 16.f * nan_max(fabsf(mx), fabsf(mn)));
+  const float bound = 16.f * nan_max(fabsf(mx), fabsf(mn));
+  const QuantCtx qc = make_quant_ctx(s, z, bound);
+  // static groups: every lane prepares the contexts of its own four columns; the column loop fetches
+  // them with shuffles that do not depend on the weights (off the sequential chain)
+  float ls[4], lz[4], lr[4];
+  int lex[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    ls[c] = 1.f, lz[c] = 0.f, lr[c] = 1.f, lex[c] = 0;
+    if (is_static && valid[c]) {
+      const int64_t g = r * a.n_groups + a.col_group[a.col0 + lane + 32 * c];
+      const QuantCtx t = make_quant_ctx(a.scales[g], a.sym ? 0.f : a.zeros[g], bound);
+      ls[c] = t.s, lz[c] = t.z, lr[c] = t.r, lex[c] = t.exact ? 1 : 0;
+    }
+  }
 
   float loss = 0.f;
 #pragma unroll
@@ -100,8 +118,15 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
       const int i = 32 * c + il;
       const float wi = __shfl_sync(0xffffffffu, w[c], il);
       const float d = u1[i * kBlk + i], rd = dinv[i];
-      const float q = int_quant_fast<float>(wi, qc, a.qr);   // the same code the IEEE division gives
-      const float dq = int_dequant_fast<float>(q, qc);
+      QuantCtx qi = qc;
+      if (is_static) {
+        qi.s = __shfl_sync(0xffffffffu, ls[c], il);
+        qi.z = __shfl_sync(0xffffffffu, lz[c], il);
+        qi.r = __shfl_sync(0xffffffffu, lr[c], il);
+        qi.exact = __shfl_sync(0xffffffffu, lex[c], il) != 0;
+      }
+      const float q = int_quant_fast<float>(wi, qi, a.qr);   // the same code the IEEE division gives
+      const float dq = int_dequant_fast<float>(q, qi);
       const float diff = __fsub_rn(wi, dq);
       // (w - q) / d through the precomputed reciprocal and one residual correction: within an ulp
       // of the IEEE quotient (the value only feeds the error propagation)
@@ -137,9 +162,11 @@ __global__ void __launch_bounds__(kThreads) gptq_block_kernel(BlockArgs a) {
     }
   }
   if (lane == 0) {
-    const int64_t g = r * a.n_groups + a.col0 / kBlk;
-    a.scales[g] = s;
-    a.zeros[g] = z;
+    if (!is_static) {
+      const int64_t g = r * a.n_groups + a.col0 / kBlk;
+      a.scales[g] = s;
+      a.zeros[g] = z;
+    }
     if (a.loss_rows) a.loss_rows[r] += loss;
   }
 }
@@ -312,7 +339,7 @@ __global__ void __launch_bounds__(kQuadThreads) gptq_block_quad_kernel(BlockArgs
 int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0, int count,
                       int bits, int sym, float* err_t, float* scales, float* zeros, int64_t n_groups,
                       uint8_t* codes, float* loss_rows, cudaStream_t st, float* panel_hi, float* panel_lo,
-                      int panel_k0) {
+                      int panel_k0, const int32_t* col_group) {
   constexpr int kSmem = (kBlk * kBlk + kBlk) * (int)sizeof(float);
   // per-device attribute; setting it on every call keeps multi-device processes correct
   if (cudaFuncSetAttribute(gptq_block_quad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
@@ -339,7 +366,8 @@ int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int6
   a.count = count;
   a.sym = sym ? 1 : 0;
   a.qr = int_qrange(bits, a.sym);
-  const bool quad = count == kBlk && cols % 4 == 0 && aligned16(W) && aligned16(U) &&
+  a.col_group = col_group;
+  const bool quad = !col_group && count == kBlk && cols % 4 == 0 && aligned16(W) && aligned16(U) &&
                     (!codes || (reinterpret_cast<uintptr_t>(codes) & 3u) == 0);
   if (quad) {
     const unsigned grid = (unsigned)((rows + kQuadRowsPerCta - 1) / kQuadRowsPerCta);
@@ -364,5 +392,6 @@ extern "C" LC_API int lc_gptq_block_quant(float* W, const float* U, int64_t rows
   if (bits < 2 || bits > 8) return LC_ERR_ARG;
   if (n_groups < (cols + 127) / 128) return LC_ERR_SHAPE;
   return lc::gptq_block_launch(W, U, rows, cols, col0, count, bits, sym, err_out, scales, zeros, n_groups,
-                               codes_u8, loss_rows, reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, 0);
+                               codes_u8, loss_rows, reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, 0,
+                               nullptr);
 }

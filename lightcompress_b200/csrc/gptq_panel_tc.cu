@@ -45,7 +45,7 @@ int gptq_trail_launch(float* W, const float* err_t, const float* U, int64_t rows
 int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0, int count,
                       int bits, int sym, float* err_t, float* scales, float* zeros, int64_t n_groups,
                       uint8_t* codes, float* loss_rows, cudaStream_t st, float* panel_hi, float* panel_lo,
-                      int panel_k0);
+                      int panel_k0, const int32_t* col_group);
 
 }  // namespace lc
 
@@ -69,14 +69,16 @@ extern "C" LC_API int lc_gptq_panel_update(float* W, const float* e_hi, const fl
                              reinterpret_cast<cudaStream_t>(stream));
 }
 
-extern "C" LC_API int lc_gptq_weight_transform_tc_owq(float* W, const float* U, const float* U_lo, int64_t rows,
-                                                      int64_t cols, int64_t n_quant, int bits, int sym,
-                                                      float* scratch_err, float* panel_hi, float* panel_lo,
-                                                      float* scales, float* zeros, uint8_t* codes_u8,
-                                                      float* loss_rows, int32_t* status, lc_stream_t stream) {
+// The block loop with the three-level trailing update.  n_quant < cols: owq; col_group != NULL: static
+// groups (scales / zeros are input tables).
+static int transform_tc(float* W, const float* U, const float* U_lo, int64_t rows, int64_t cols, int64_t n_quant,
+                        int bits, int sym, float* scratch_err, float* panel_hi, float* panel_lo, float* scales,
+                        float* zeros, const int32_t* col_group, uint8_t* codes_u8, float* loss_rows,
+                        int32_t* status, lc_stream_t stream) {
   using namespace lc;
   constexpr int kPanel = 1024, kSub = 256;
-  if (!W || !U || !U_lo || !scratch_err || !panel_hi || !panel_lo || !scales || !zeros) return LC_ERR_ARG;
+  if (!W || !U || !U_lo || !scratch_err || !panel_hi || !panel_lo || !scales || (!zeros && !(col_group && sym)))
+    return LC_ERR_ARG;
   if (rows <= 0 || cols <= 0 || n_quant <= 0 || n_quant > cols || bits < 2 || bits > 8) return LC_ERR_ARG;
   if (cols % 128 != 0 || rows % 4 != 0) return LC_ERR_SHAPE;      // TMA pitch / whole blocks; use the FFMA entry point otherwise
   if (!aligned16(W) || !aligned16(U) || !aligned16(U_lo) || !aligned16(panel_hi) || !aligned16(panel_lo)) return LC_ERR_ALIGN;
@@ -107,7 +109,7 @@ extern "C" LC_API int lc_gptq_weight_transform_tc_owq(float* W, const float* U, 
       for (int64_t i1 = s1; i1 < sq; i1 += 128) {
         const int count = (int)((n_quant - i1 < 128) ? (n_quant - i1) : 128);
         int rc = gptq_block_launch(W, U, rows, cols, i1, count, bits, sym, scratch_err, scales, zeros, n_groups,
-                                   codes_u8, loss_rows, st, panel_hi, panel_lo, (int)(i1 - p1));
+                                   codes_u8, loss_rows, st, panel_hi, panel_lo, (int)(i1 - p1), col_group);
         if (rc != LC_OK) return rc;
         // level 1, eager: the rest of the 256-column sub-panel (K <= 128, at most 255 columns: FFMA kernel)
         rc = gptq_trail_launch(W, scratch_err, U, rows, cols, i1, count, i1 + count, st, s2);
@@ -128,6 +130,27 @@ extern "C" LC_API int lc_gptq_weight_transform_tc_owq(float* W, const float* U, 
     }
   }
   return LC_OK;
+}
+
+extern "C" LC_API int lc_gptq_weight_transform_tc_owq(float* W, const float* U, const float* U_lo, int64_t rows,
+                                                      int64_t cols, int64_t n_quant, int bits, int sym,
+                                                      float* scratch_err, float* panel_hi, float* panel_lo,
+                                                      float* scales, float* zeros, uint8_t* codes_u8,
+                                                      float* loss_rows, int32_t* status, lc_stream_t stream) {
+  return transform_tc(W, U, U_lo, rows, cols, n_quant, bits, sym, scratch_err, panel_hi, panel_lo, scales, zeros,
+                      nullptr, codes_u8, loss_rows, status, stream);
+}
+
+extern "C" LC_API int lc_gptq_weight_transform_tc_static(float* W, const float* U, const float* U_lo, int64_t rows,
+                                                         int64_t cols, int bits, int sym, float* scratch_err,
+                                                         float* panel_hi, float* panel_lo, const float* scales,
+                                                         const float* zeros, const int32_t* col_group,
+                                                         uint8_t* codes_u8, float* loss_rows, int32_t* status,
+                                                         lc_stream_t stream) {
+  if (!col_group) return LC_ERR_ARG;
+  return transform_tc(W, U, U_lo, rows, cols, cols, bits, sym, scratch_err, panel_hi, panel_lo,
+                      const_cast<float*>(scales), const_cast<float*>(zeros), col_group, codes_u8, loss_rows, status,
+                      stream);
 }
 
 extern "C" LC_API int lc_gptq_weight_transform_tc(float* W, const float* U, const float* U_lo, int64_t rows,

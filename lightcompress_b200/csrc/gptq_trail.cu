@@ -150,7 +150,7 @@ int gptq_trail_launch(float* W, const float* err_t, const float* U, int64_t rows
 int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int64_t col0, int count,
                       int bits, int sym, float* err_t, float* scales, float* zeros, int64_t n_groups,
                       uint8_t* codes, float* loss_rows, cudaStream_t st, float* panel_hi, float* panel_lo,
-                      int panel_k0);
+                      int panel_k0, const int32_t* col_group);
 
 }  // namespace lc
 
@@ -204,10 +204,12 @@ extern "C" LC_API int lc_gptq_weight_transform_noalloc(float* W, const float* U,
   return lc_gptq_weight_transform(W, U, rows, cols, bits, sym, scratch, scales, zeros, codes_u8, loss_rows, stream);
 }
 
-extern "C" LC_API int lc_gptq_weight_transform_owq(float* W, const float* U, int64_t rows, int64_t cols, int64_t n_quant,
-                                                   int bits, int sym, float* scratch_err, float* scales, float* zeros,
-                                                   uint8_t* codes_u8, float* loss_rows, lc_stream_t stream) {
-  if (!W || !U || !scratch_err || !scales || !zeros) return LC_ERR_ARG;
+// The block loop of GPTQ.weight_transform with the FFMA trailing update.  n_quant < cols: owq;
+// col_group != NULL: static groups (scales / zeros are input tables).
+static int transform_ffma(float* W, const float* U, int64_t rows, int64_t cols, int64_t n_quant, int bits, int sym,
+                          float* scratch_err, float* scales, float* zeros, const int32_t* col_group,
+                          uint8_t* codes_u8, float* loss_rows, lc_stream_t stream) {
+  if (!W || !U || !scratch_err || !scales || (!zeros && !(col_group && sym))) return LC_ERR_ARG;
   if (rows <= 0 || cols <= 0 || n_quant <= 0 || n_quant > cols || bits < 2 || bits > 8) return LC_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int64_t n_groups = (cols + 127) / 128;
@@ -215,12 +217,28 @@ extern "C" LC_API int lc_gptq_weight_transform_owq(float* W, const float* U, int
   for (int64_t i1 = 0; i1 < n_quant; i1 += 128) {
     const int count = (int)((n_quant - i1 < 128) ? (n_quant - i1) : 128);
     int rc = lc::gptq_block_launch(W, U, rows, cols, i1, count, bits, sym, scratch_err, scales, zeros, n_groups,
-                                   codes_u8, loss_rows, st, nullptr, nullptr, 0);
+                                   codes_u8, loss_rows, st, nullptr, nullptr, 0, col_group);
     if (rc != LC_OK) return rc;
     rc = lc::gptq_trail_launch(W, scratch_err, U, rows, cols, i1, count, i1 + count, st, -1);
     if (rc != LC_OK) return rc;
   }
   return LC_OK;
+}
+
+extern "C" LC_API int lc_gptq_weight_transform_owq(float* W, const float* U, int64_t rows, int64_t cols, int64_t n_quant,
+                                                   int bits, int sym, float* scratch_err, float* scales, float* zeros,
+                                                   uint8_t* codes_u8, float* loss_rows, lc_stream_t stream) {
+  return transform_ffma(W, U, rows, cols, n_quant, bits, sym, scratch_err, scales, zeros, nullptr, codes_u8, loss_rows,
+                        stream);
+}
+
+extern "C" LC_API int lc_gptq_weight_transform_static(float* W, const float* U, int64_t rows, int64_t cols, int bits,
+                                                      int sym, float* scratch_err, const float* scales,
+                                                      const float* zeros, const int32_t* col_group, uint8_t* codes_u8,
+                                                      float* loss_rows, lc_stream_t stream) {
+  if (!col_group) return LC_ERR_ARG;
+  return transform_ffma(W, U, rows, cols, cols, bits, sym, scratch_err, const_cast<float*>(scales),
+                        const_cast<float*>(zeros), col_group, codes_u8, loss_rows, stream);
 }
 
 extern "C" LC_API int lc_gptq_weight_transform(float* W, const float* U, int64_t rows, int64_t cols, int bits, int sym,

@@ -88,8 +88,6 @@ class GPTQ:
 
     def _check_config(self):
         wq = self.wquantizer
-        if self.static_groups:
-            raise NotImplementedError('static_groups is outside the B200 hot path')
         if wq.granularity != 'per_group' or wq.group_size != 128 or self.blocksize != 128:
             # gptq.py:216-223 reads group statistics that are only well defined when a group
             # starts at a block boundary; the kernels implement group_size == blocksize == 128.
@@ -158,12 +156,26 @@ class GPTQ:
         H, hscale = self._finish_hessian(name)
         n_out = self.n_out_of(name)
         fac = self.factorize(H, hscale, n_out=n_out) if n_out else None
-        res = self.solve(layer.weight.data, H, hscale, rows=rows, factor=fac)
+        static = self.static_qparams(layer) if self.static_groups else None
+        res = self.solve(layer.weight.data, H, hscale, rows=rows, factor=fac, static=static)
         if rows is None:
             self._install(layer, res)
         return res
 
     @torch.no_grad()
+    @torch.no_grad()
+    def static_qparams(self, layer):
+        """static_groups: the layer's round-to-nearest buffers (collect_block_qparams,
+        base_blockwise_quantization.py:349-376, leaves them before GPTQ runs; computed and registered here
+        when the layer does not have them yet).  Returns (buf_scales, buf_zeros or None)."""
+        wq = self.wquantizer
+        if 'buf_scales' not in layer._buffers:
+            _, s, z, qmax, qmin = wq.get_tensor_qparams(layer.weight.data)
+            layer.register_buffer('buf_scales', s)
+            if not wq.sym:
+                layer.register_buffer('buf_zeros', z)
+        return layer.buf_scales, (None if wq.sym else layer.buf_zeros)
+
     def n_out_of(self, name):
         """owq: the number of outlier columns of the linear `name` (gptq.py:122); 0 without owq."""
         if not self.owq:
@@ -329,7 +341,8 @@ class GPTQ:
         return ws
 
     @torch.no_grad()
-    def solve(self, W, H, hscale=1.0, rows=None, factor=None):
+    def solve(self, W, H, hscale=1.0, rows=None, factor=None, static=None):
+        """static: (buf_scales, buf_zeros or None) of all rows of W, for static_groups."""
         wq = self.wquantizer
         fac = factor or self.factorize(H, hscale)
         H, perm, invperm, U = fac['H'], fac['perm'], fac['invperm'], fac['U']
@@ -351,6 +364,8 @@ class GPTQ:
         loss_rows = torch.empty(R, dtype=torch.float32, device=dev)
         # owq: the last n_out (permuted) columns are not quantised; they take the error feedback and stay fp32
         n_quant = C - int(fac.get('n_out', 0))
+        if static is not None:
+            return self._solve_static(Wp, fac, static, rows, err, codes, loss_rows, stream)
         if fac.get('U_lo') is not None and R % 4 == 0:
             panel = torch.empty((2, 1024, R), dtype=torch.float32, device=dev)
             status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -370,6 +385,40 @@ class GPTQ:
             if codes is not None:
                 codes[:, n_quant:] = 0          # the outlier columns have no codes
         return res
+
+    def _solve_static(self, Wp, fac, static, rows, err, codes, loss_rows, stream):
+        """weight_transform with static groups (gptq.py:224-227): the layer's own qparams, looked up by the
+        group of each column's original position; the buffers are returned unchanged."""
+        wq = self.wquantizer
+        R, C = Wp.shape
+        dev = Wp.device
+        perm, invperm, U = fac['perm'], fac['invperm'], fac['U']
+        n_groups = C // 128
+        if C % 128:
+            raise NotImplementedError('static_groups needs columns % 128 == 0')
+        s_all, z_all = static
+        r0, r1 = rows if rows is not None else (0, R)
+        # the solver computes in fp32 on the promoted qparams (their values are those of the weight dtype)
+        s32 = s_all.reshape(-1, n_groups)[r0:r1].float().contiguous()
+        z32 = None if wq.sym else z_all.reshape(-1, n_groups)[r0:r1].float().contiguous()
+        cols = torch.arange(C, device=dev) if perm is None else perm
+        col_group = (cols // 128).to(torch.int32).contiguous()
+        if fac.get('U_lo') is not None and R % 4 == 0:
+            panel = torch.empty((2, 1024, R), dtype=torch.float32, device=dev)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            L.call('lc_gptq_weight_transform_tc_static', L.ptr(Wp), L.ptr(U), L.ptr(fac['U_lo']), R, C, int(wq.bit),
+                   int(wq.sym), L.ptr(err), L.ptr(panel[0]), L.ptr(panel[1]), L.ptr(s32), L.ptr(z32),
+                   L.ptr(col_group), L.ptr(codes), L.ptr(loss_rows), L.ptr(status), stream)
+            self._pending_status.append(status)
+        else:
+            L.call('lc_gptq_weight_transform_static', L.ptr(Wp), L.ptr(U), R, C, int(wq.bit), int(wq.sym),
+                   L.ptr(err), L.ptr(s32), L.ptr(z32), L.ptr(col_group), L.ptr(codes), L.ptr(loss_rows), stream)
+        out = torch.empty((R, C), dtype=torch.float32, device=dev)
+        L.call('lc_gptq_unpermute', L.ptr(Wp), L.ptr(perm), R, C, L.ptr(out), L.LC_F32, stream)
+        sl = slice(r0 * n_groups, r1 * n_groups)
+        return {'weight': out, 'buf_scales': s_all[sl], 'buf_zeros': None if wq.sym else z_all[sl],
+                'buf_perm': perm, 'buf_invperm': invperm, 'codes_perm': codes, 'loss_rows': loss_rows,
+                'static': True}
 
     def act_order(self, H):
         """perm = argsort(diag(H), descending) and its inverse (gptq.py:58-64, :158), or (None, None)."""
@@ -441,7 +490,7 @@ class GPTQ:
         # tensor so that a weight replaced later falls back to re-quantising
         # (not with owq: the outlier columns have no codes, deploy re-quantises like the reference)
         codes = res.get('codes_perm')
-        layer._lc_codes = None if codes is None or res.get('buf_n_nonout') is not None else (
+        layer._lc_codes = None if codes is None or res.get('buf_n_nonout') is not None or res.get('static') else (
             codes, layer.weight.data.data_ptr())
 
     @torch.no_grad()

@@ -4,7 +4,7 @@ Follows llmc/compression/quantization/gptq.py: add_batch :254-295, hessian_sorti
 :58-64, process_hessian_and_weights :128-176, weight_transform :199-244,
 search_column_qparams :359-366, merge/update qparams :344-356, :398-409 and the
 deploy-time w_qdq :425-452.  Only the configuration the hot path covers is restated:
-nn.Linear, per_group with group_size == blocksize, static_groups off; owq (:44-50, :66-83, :186-188,
+nn.Linear, per_group with group_size == blocksize, static_groups off or on (:224-227, :377-393); owq (:44-50, :66-83, :186-188,
 :440-447) with fewer outlier columns than a group.
 """
 import math
@@ -66,7 +66,16 @@ def prepare(W, H, percdamp=0.01, actorder=True, n_out=0):
     return W, U, perm, invperm
 
 
-def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128, n_out=0):
+def static_group_qparams(W, bit=4, sym=False, group_size=128):
+    """The round-to-nearest qparams collect_block_qparams leaves on a layer
+    (base_blockwise_quantization.py:349-376), in the weight's dtype: buf_scales / buf_zeros,
+    (R * n_groups, 1), which search_group_qparams (gptq.py:377-393) splits per group."""
+    g = Q.group_view(W, 'per_group', group_size)
+    s, z, qmax, qmin = Q.int_qparams(g, bit, sym)
+    return s, z
+
+
+def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128, n_out=0, static=None, perm=None):
     """gptq.py:199-244.  W is modified in place like the reference; returns
     (kept weights `tmp`, Losses, per-group scales list, per-group zeros list).  With owq the last
     n_out columns are not quantised (they only receive the error feedback) and `tmp` is zero there."""
@@ -76,6 +85,12 @@ def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128, n_ou
     tmp = torch.zeros_like(W)
     Losses = torch.zeros_like(W)
     g_scales, g_zeros = [], []
+    if static is not None:
+        # static groups (gptq.py:224-227): column i of the permuted weight uses the group of its original column
+        n_g = C // group_size
+        st_s = static[0].reshape(R, n_g)
+        st_z = None if sym else static[1].reshape(R, n_g)
+        qmin, qmax = Q.int_range(bit, sym)
     for i1 in range(0, n_nonout, blocksize):
         i2 = min(i1 + blocksize, n_nonout)
         W1 = W[:, i1:i2].clone()
@@ -84,7 +99,12 @@ def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128, n_ou
         for i in range(i2 - i1):
             w = W1[:, i].clone()
             d = U1[i, i]
-            if (i1 + i) % group_size == 0:
+            if static is not None:
+                idx = i1 + i if perm is None else int(perm[i1 + i])
+                gi = idx // group_size
+                s = st_s[:, gi:gi + 1]
+                z = torch.tensor(0.0) if sym else st_z[:, gi:gi + 1]
+            elif (i1 + i) % group_size == 0:
                 cols = W[:, i1 + i: min(i1 + i + group_size, n_nonout)]
                 s, z, qmax, qmin = Q.int_qparams(cols, bit, sym)
                 g_scales.append(s)
@@ -105,7 +125,7 @@ def merge_group_qparams(per_group):
 
 
 def quantize_layer(W, H, bit=4, sym=False, group_size=128, blocksize=128,
-                   percdamp=0.01, actorder=True, n_out=0):
+                   percdamp=0.01, actorder=True, n_out=0, static_groups=False):
     """layer_transform (gptq.py:114-117, :178-196): returns a dict with the reference's
     per-layer results: weight (compensated, fp32, original column order), buf_scales,
     buf_zeros (permuted-group order), buf_perm, buf_invperm, loss.  n_out > 0 is the owq mode
@@ -113,9 +133,18 @@ def quantize_layer(W, H, bit=4, sym=False, group_size=128, blocksize=128,
     the reference's w_qdq only works then): the outlier columns keep their error-compensated fp32 values
     (gptq.py:186-188)."""
     Wp, U, perm, invperm = prepare(W, H, percdamp, actorder and not n_out, n_out)
-    tmp, Losses, gs, gz = weight_transform(Wp, U, bit, sym, group_size, blocksize, n_out)
+    static = static_group_qparams(W, bit, sym, group_size) if static_groups else None
+    tmp, Losses, gs, gz = weight_transform(Wp, U, bit, sym, group_size, blocksize, n_out, static,
+                                           perm if (static_groups and actorder) else None)
     if n_out:
         tmp[:, W.shape[1] - n_out:] = Wp[:, W.shape[1] - n_out:]
+    if static_groups:
+        # the layer keeps its round-to-nearest buffers (gptq.py:195-196) and deploys without a permutation
+        out = {'weight': tmp[:, invperm].contiguous(), 'buf_scales': static[0],
+               'buf_zeros': None if sym else static[1], 'buf_perm': torch.arange(W.shape[1]),
+               'buf_invperm': torch.arange(W.shape[1]), 'solver_perm': perm, 'loss': float(Losses.sum()), 'U': U,
+               'n_nonout': W.shape[1]}
+        return out
     out = {
         'weight': tmp[:, invperm].contiguous(),
         'buf_scales': merge_group_qparams(gs),

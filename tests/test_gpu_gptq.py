@@ -397,3 +397,90 @@ def test_owq_rejects_what_the_reference_cannot_deploy():
     H = torch.eye(256, device='cuda')
     with pytest.raises(NotImplementedError):
         solver.factorize(H, 1.0, n_out=128)
+
+
+# ---- static groups (gptq.py:224-227, :377-393) ---------------------------------------------------------
+
+def _static_layer(W, X, sym, actorder):
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    wq = IntegerQuantizer(4, sym, 'per_group', group_size=128)
+    solver = GPTQ(wq, {'actorder': actorder, 'static_groups': True, 'percdamp': 0.01, 'blocksize': 128},
+                  model_dtype=W.dtype)
+    assert not solver.need_perm
+    R, C = W.shape
+    layer = torch.nn.Linear(C, R, bias=False, dtype=W.dtype).cuda()
+    layer.weight.data = W.cuda()
+    solver.layer_init(layer, 'l')
+    Xc = X.cuda()
+    for i in range(X.shape[0]):
+        solver.add_batch(layer, 'l', Xc[i:i + 1])
+    res = solver.layer_transform(layer, 'l')
+    fq = solver.w_qdq(layer, wq)
+    solver.check_status()
+    assert layer._lc_codes is None
+    return solver, layer, res, fq
+
+
+def test_static_groups_match_reference_golden(golden):
+    """The reference's own static_groups runs: the buffers stay the round-to-nearest ones bit for bit,
+    the deploy-time codes (original column order, no permutation) and the reconstruction error agree."""
+    from lightcompress_b200 import IntegerQuantizer
+    for key, c in golden('gptq_static.pt').items():
+        solver, layer, res, fq = _static_layer(c['W'], c['X'], c['sym'], c['actorder'])
+        assert torch.equal(layer.buf_scales.cpu(), c['buf_scales']), key
+        if not c['sym']:
+            assert torch.equal(layer.buf_zeros.cpu(), c['buf_zeros']), key
+        wq = IntegerQuantizer(4, c['sym'], 'per_group', group_size=128)
+        codes = wq.quant(layer.weight.data.reshape(-1, 128), layer.buf_scales.float(),
+                         None if c['sym'] else layer.buf_zeros.float(), None, None).reshape(c['W'].shape)
+        mism = float((codes.cpu().to(torch.int16) != c['codes_perm']).float().mean())
+        X = c['X'].reshape(-1, c['X'].shape[-1]).float()
+        e_ref = gptq_ref.recon_error(c['W'].float(), c['w_qdq'].float(), X)
+        e_gpu = gptq_ref.recon_error(c['W'].float(), fq.cpu().float(), X)
+        print(f'{key}: code mismatch {mism:.5%}, recon ref {e_ref:.6f} gpu {e_gpu:.6f}')
+        assert mism < CODE_MISMATCH_MAX, key
+        assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref, key
+        # the codes the solver emitted (permuted order) are the deploy-time codes
+        perm = res['buf_perm'].cpu() if c['actorder'] else torch.arange(c['W'].shape[1])
+        back = torch.empty_like(res['codes_perm'].cpu())
+        back[:, perm] = res['codes_perm'].cpu()
+        off = 8 if c['sym'] else 0
+        assert torch.equal(back.to(torch.int16) - off, codes.cpu().to(torch.int16)), key
+
+
+@pytest.mark.parametrize('R,C,sym', [(256, 2304, True), (128, 1024, False)])
+def test_static_groups_vs_oracle(R, C, sym):
+    """Wider layers (C = 2304: tensor-core trailing path) against the CPU oracle given the same Hessian
+    and column order."""
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    g = torch.Generator().manual_seed(2800 + C)
+    ns, T = 10, 512
+    W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16)
+    X = _x(g, ns, T, C)
+    st = gptq_ref.hessian_init(C)
+    for i in range(ns):
+        gptq_ref.add_batch(st, X[i:i + 1])
+    ref = gptq_ref.quantize_layer(W, st['H'], sym=sym, static_groups=True)
+    wq = IntegerQuantizer(4, sym, 'per_group', group_size=128)
+    solver = GPTQ(wq, {'actorder': True, 'static_groups': True, 'percdamp': 0.01}, model_dtype=W.dtype)
+    layer = torch.nn.Linear(C, R, bias=False, dtype=W.dtype).cuda()
+    layer.weight.data = W.cuda()
+    fac = solver.factorize(st['H'].cuda(), 1.0, perm=ref['solver_perm'])
+    assert (fac['U_lo'] is not None) == (C > 1024)
+    res = solver.solve(layer.weight.data, st['H'].cuda(), 1.0, factor=fac, static=solver.static_qparams(layer))
+    solver._install(layer, res)
+    fq = solver.w_qdq(layer, wq)
+    solver.check_status()
+    assert torch.equal(layer.buf_scales.cpu(), ref['buf_scales'])
+    rel = float((layer.weight.data.cpu() - ref['weight']).abs().max() / ref['weight'].abs().max())
+    ref_codes = gptq_ref.codes_permuted(ref, 4, sym)
+    res_t = {'weight': layer.weight.data.cpu(), 'buf_scales': ref['buf_scales'], 'buf_zeros': ref['buf_zeros'],
+             'buf_perm': ref['buf_perm']}
+    mism = float((gptq_ref.codes_permuted(res_t, 4, sym) != ref_codes).float().mean())
+    Xf = X.reshape(-1, C).float()
+    e_ref = gptq_ref.recon_error(W.float(), gptq_ref.w_qdq(ref, torch.bfloat16, 4, sym).float(), Xf)
+    e_gpu = gptq_ref.recon_error(W.float(), fq.cpu().float(), Xf)
+    print(f'static R={R} C={C} sym={sym}: code mismatch {mism:.5%}, weight rel diff {rel:.2e}, '
+          f'recon ref {e_ref:.6f} gpu {e_gpu:.6f}')
+    assert mism < CODE_MISMATCH_MAX
+    assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref
