@@ -133,3 +133,40 @@ def test_staged_plan_is_bit_identical_to_reforwarding():
         for name in state:
             for a, b in zip(state[name], results[0][0][name]):
                 assert torch.equal(a, b), name
+
+
+@pytest.mark.parametrize('mode', ['static_groups', 'owq'])
+def test_block_schedule_with_static_groups_and_owq(mode):
+    """The two other modes of the solver through the block schedule: staged plan and generic
+    re-forwarding agree bit for bit; static groups keep every linear's round-to-nearest buffers, owq
+    leaves the outlier columns unquantised in the deployed weight."""
+    from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer, llama_subsets
+    block, xs, kwargs = _make_block(seed=5)
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    extra = {'static_groups': True} if mode == 'static_groups' else {'owq': True, 'n_outs': [6, 6, 6, 6, 2, 2, 6]}
+    results = []
+    for plan in (True, False):
+        gblock = copy.deepcopy(block).cuda()
+        runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'hessian_batch': 8, 'hessian_ksplit': 1,
+                                         'stage_plan': plan}, **extra))
+        outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
+        runner.solver.check_status()
+        torch.cuda.synchronize()
+        results.append((gblock, torch.cat(outs)))
+    assert torch.equal(results[0][1], results[1][1])
+    gblock = results[0][0]
+    orig = dict(block.named_modules())
+    for subset in llama_subsets(gblock):
+        for name, (parent, attr) in subset.items():
+            m = getattr(parent, attr)
+            other = dict(results[1][0].named_modules())[name]
+            assert torch.equal(m.weight, other.weight) and torch.equal(m.tmp_weight, other.tmp_weight), name
+            if mode == 'static_groups':
+                _, s, z, _, _ = wq.get_tensor_qparams(orig[name].weight.data.cuda())
+                assert torch.equal(m.buf_scales, s) and torch.equal(m.buf_zeros, z), name
+                assert m.buf_scales.dtype == torch.bfloat16
+            else:
+                n_nonout = int(m.buf_n_nonout)
+                assert n_nonout == m.weight.shape[1] - (2 if 'gate' in name or 'up' in name else 6), name
+                outl = m.buf_perm[n_nonout:]
+                assert torch.equal(m.tmp_weight[:, outl], m.weight[:, outl].to(m.tmp_weight.dtype)), name

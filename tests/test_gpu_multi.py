@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, extra=None):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE='0')
@@ -22,7 +22,8 @@ def _worker(rank, world, port, out_dir):
     block, xs, kwargs = _make_block()
     b, e = parallel.sequence_shard(len(xs))
     wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
-    runner = GPTQBlockwise(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4})
+    runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4},
+                                    **(extra or {})))
     gblock = copy.deepcopy(block).cuda()
     outs = runner.block_opt(gblock, [x.cuda() for x in xs[b:e]], _to_cuda(kwargs))
     torch.cuda.synchronize()
@@ -70,6 +71,39 @@ def test_two_rank_block_matches_single_gpu(tmp_path):
             b[:, two['buf_perm']] = gptq_ref.codes_permuted(two)
             mism = float((a != b).float().mean())
             print(f'{name}: 1-GPU vs 2-GPU code mismatch {mism:.4%}')
+            assert mism < 1e-3, (name, mism)
+    full = torch.cat([o.cpu() for o in outs]).float()
+    both = torch.cat(r0['outs'] + r1['outs']).float()
+    assert float((full - both).norm() / full.norm()) < 1e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_two_rank_static_groups_block_matches_single_gpu(tmp_path):
+    """static_groups through the row-sharded solve: the ranks agree exactly, the buffers are every
+    linear's round-to-nearest ones, and the quantised block's outputs match the single-GPU run."""
+    import copy
+    import torch.multiprocessing as mp
+    from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer
+    from tests.test_gpu_blockwise import _make_block, _to_cuda
+    port = 29900 + (os.getpid() % 100)
+    extra = {'static_groups': True}
+    mp.spawn(_worker, args=(2, port, str(tmp_path), extra), nprocs=2, join=True)
+    r0 = torch.load(os.path.join(str(tmp_path), 'r0.pt'))
+    r1 = torch.load(os.path.join(str(tmp_path), 'r1.pt'))
+    for name in r0['state']:
+        for k in r0['state'][name]:
+            assert torch.equal(r0['state'][name][k], r1['state'][name][k]), (name, k)
+        assert r0['state'][name]['buf_scales'].dtype == torch.bfloat16
+    block, xs, kwargs = _make_block()
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4}, **extra))
+    gblock = copy.deepcopy(block).cuda()
+    outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
+    for name, m in gblock.named_modules():
+        if name in r0['state']:
+            assert torch.equal(m.buf_scales.cpu(), r0['state'][name]['buf_scales']), name
+            mism = float((m.tmp_weight.cpu() != r0['state'][name]['tmp_weight']).float().mean())
+            print(f'{name}: 1-GPU vs 2-GPU deployed weights differing {mism:.4%}')
             assert mism < 1e-3, (name, mism)
     full = torch.cat([o.cpu() for o in outs]).float()
     both = torch.cat(r0['outs'] + r1['outs']).float()
