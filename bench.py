@@ -382,9 +382,13 @@ def main():
     ap.add_argument('--workload', default='block', choices=['block', 'layer', 'awq', 'moe'])
     ap.add_argument('--calib-bs', type=int, default=1,
                     help='sequences per block-forward call (calib.bs of the reference config; block workload)')
+    ap.add_argument('--static-groups', action='store_true',
+                    help='special.static_groups of the reference (its export configs); a side measurement')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
     args = ap.parse_args()
+    if args.static_groups:
+        SPECIAL['static_groups'] = True
     rank = int(os.environ.get('RANK', 0))
     local_rank = int(os.environ.get('LOCAL_RANK', 0))
     world = int(os.environ.get('WORLD_SIZE', 1))
@@ -694,7 +698,8 @@ def main():
             'config': {'workload': WORKLOADS[args.workload], 'name': args.workload,
                        'l2': 'inputs (2.1 GB of activations per step) exceed the 126 MB L2',
                        'sharding': f'{n_seq} sequences per rank; solve units (linear, row range) dealt to the ranks',
-                       'hessian_batch': HESSIAN_BATCH, 'calib_bs': args.calib_bs if args.workload == 'block' else 1},
+                       'hessian_batch': HESSIAN_BATCH, 'calib_bs': args.calib_bs if args.workload == 'block' else 1,
+                       'static_groups': bool(SPECIAL['static_groups'])},
             'roofline': roofline, 'gpu_launches': launches * args.steps, 'clocks': clocks}
     if e2e:
         line['e2e'] = e2e

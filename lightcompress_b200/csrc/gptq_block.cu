@@ -203,10 +203,13 @@ struct QuadRow {
 // The 16 column steps of slot `t` with NG live slots (the current one and NG-1 to its right), then
 // the slot is stored and the register file shifts down by one slot.  All U values of a step are
 // fetched before the step's dependent chain starts, so the chain never waits on shared memory.
-template <int NG>
+// ST (static groups): the context of column i comes from the row's table of per-group contexts in
+// shared memory (tab: s, z, 1/s per group; 1/s = NaN marks a scale the reciprocal scheme cannot take),
+// indexed by the column's group cg[i]; like the U values it is fetched before the dependent chain.
+template <int NG, bool ST>
 __device__ __forceinline__ void quad_slot(QuadRow& row, const BlockArgs& a, const float* u1, const float* dinv,
                                           const QuantCtx& qc, int t, int sub, int quad_base, bool live, int64_t r,
-                                          float* wrow) {
+                                          float* wrow, const float* tab, const int* cg) {
   float er[4] = {0.f, 0.f, 0.f, 0.f};
   int cd[4] = {0, 0, 0, 0};
   float (&w)[32] = row.w;
@@ -220,9 +223,15 @@ __device__ __forceinline__ void quad_slot(QuadRow& row, const BlockArgs& a, cons
 #pragma unroll
     for (int g = 0; g < NG; ++g) u[g] = *reinterpret_cast<const float4*>(urow + 16 * (t + g) + 4 * sub);
 
+    QuantCtx qi = qc;
+    if constexpr (ST) {
+      const float* e = tab + 3 * cg[i];
+      qi.s = e[0], qi.z = e[1], qi.r = e[2];
+      qi.exact = !(qi.r == qi.r);
+    }
     const float wi = __shfl_sync(0xffffffffu, w[k], quad_base | owner);
-    const float q = quad_quant(wi, qc, a.qr);
-    const float dq = int_dequant_fast<float>(q, qc);
+    const float q = quad_quant(wi, qi, a.qr);
+    const float dq = int_dequant_fast<float>(q, qi);
     const float diff = __fsub_rn(wi, dq);
     const float e0 = __fmul_rn(diff, rd);
     const float err = __fmaf_rn(__fmaf_rn(-e0, d, diff), rd, e0);
@@ -268,9 +277,29 @@ __device__ __forceinline__ void quad_slot(QuadRow& row, const BlockArgs& a, cons
   for (int k = 0; k < 28; ++k) w[k] = w[k + 4];
 }
 
+// odd row pitch of the per-row context tables: the eight rows of a warp fall into eight different banks
+__host__ __device__ inline int quad_tab_pitch(int64_t n_groups) { return (int)(3 * n_groups) | 1; }
+
+template <bool ST>
 __global__ void __launch_bounds__(kQuadThreads) gptq_block_quad_kernel(BlockArgs a) {
   extern __shared__ float u1[];  // [128][128]; row i is only filled from column (i & ~3) on
   float* dinv = u1 + kBlk * kBlk;
+  int* cg = reinterpret_cast<int*>(dinv + kBlk);       // ST: [128] group of each column of the block
+  float* tabs = reinterpret_cast<float*>(cg + kBlk);    // ST: [32 rows][pitch]
+  const int pitch = quad_tab_pitch(a.n_groups);
+  if constexpr (ST) {
+    if (threadIdx.x < kBlk) cg[threadIdx.x] = a.col_group[a.col0 + threadIdx.x];
+    const int64_t row0 = (int64_t)blockIdx.x * kQuadRowsPerCta;
+    for (int idx = threadIdx.x; idx < kQuadRowsPerCta * (int)a.n_groups; idx += kQuadThreads) {
+      const int rl = idx / (int)a.n_groups, g = idx - rl * (int)a.n_groups;
+      const int64_t rr = (row0 + rl < a.rows) ? row0 + rl : a.rows - 1;
+      const float sv = a.scales[rr * a.n_groups + g];
+      float* e = tabs + rl * pitch + 3 * g;
+      e[0] = sv;
+      e[1] = a.sym ? 0.f : a.zeros[rr * a.n_groups + g];
+      e[2] = (sv > 1e-30f && sv < 1e30f) ? __frcp_rn(sv) : __int_as_float(0x7fc00000);
+    }
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 3;
 
@@ -310,26 +339,29 @@ __global__ void __launch_bounds__(kQuadThreads) gptq_block_quad_kernel(BlockArgs
     mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
   }
-  float s, z;
-  int_qparams<float>(mn, mx, a.qr, a.sym, s, z);
+  float s = 1.f, z = 0.f;
+  if constexpr (!ST) int_qparams<float>(mn, mx, a.qr, a.sym, s, z);
   const QuantCtx qc = make_quant_ctx(s, z, 16.f * nan_max(fabsf(mx), fabsf(mn)));
   row.loss = 0.f;
   const int quad_base = lane & ~3;
+  const float* tab = tabs + (warp * 8 + (lane >> 2)) * pitch;
 
   // live slots shrink as slots retire; four code copies (8, 6, 4, 2 live slots), two slots each
 #pragma unroll 1
-  for (int t = 0; t < 2; ++t) quad_slot<8>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+  for (int t = 0; t < 2; ++t) quad_slot<8, ST>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow, tab, cg);
 #pragma unroll 1
-  for (int t = 2; t < 4; ++t) quad_slot<6>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+  for (int t = 2; t < 4; ++t) quad_slot<6, ST>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow, tab, cg);
 #pragma unroll 1
-  for (int t = 4; t < 6; ++t) quad_slot<4>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+  for (int t = 4; t < 6; ++t) quad_slot<4, ST>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow, tab, cg);
 #pragma unroll 1
-  for (int t = 6; t < 8; ++t) quad_slot<2>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow);
+  for (int t = 6; t < 8; ++t) quad_slot<2, ST>(row, a, u1, dinv, qc, t, sub, quad_base, live, r, wrow, tab, cg);
 
   if (live && sub == 0) {
-    const int64_t g = r * a.n_groups + a.col0 / kBlk;
-    a.scales[g] = s;
-    a.zeros[g] = z;
+    if constexpr (!ST) {
+      const int64_t g = r * a.n_groups + a.col0 / kBlk;
+      a.scales[g] = s;
+      a.zeros[g] = z;
+    }
     if (a.loss_rows) a.loss_rows[r] += row.loss;
   }
 }
@@ -342,8 +374,16 @@ int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int6
                       int panel_k0, const int32_t* col_group) {
   constexpr int kSmem = (kBlk * kBlk + kBlk) * (int)sizeof(float);
   // per-device attribute; setting it on every call keeps multi-device processes correct
-  if (cudaFuncSetAttribute(gptq_block_quad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+  if (cudaFuncSetAttribute(gptq_block_quad_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
       cudaSuccess)
+    return LC_ERR_CUDA;
+  // static groups: plus the block's column groups and 32 per-row context tables
+  const int64_t smem_static = kSmem + kBlk * (int)sizeof(int) +
+                              (int64_t)kQuadRowsPerCta * quad_tab_pitch(n_groups) * (int)sizeof(float);
+  const bool static_fits = smem_static <= 200 * 1024;
+  if (col_group && static_fits &&
+      cudaFuncSetAttribute(gptq_block_quad_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem_static) != cudaSuccess)
     return LC_ERR_CUDA;
   if (cudaFuncSetAttribute(gptq_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (kBlk * kBlk + kBlk) * (int)sizeof(float)) != cudaSuccess)
@@ -367,11 +407,12 @@ int gptq_block_launch(float* W, const float* U, int64_t rows, int64_t cols, int6
   a.sym = sym ? 1 : 0;
   a.qr = int_qrange(bits, a.sym);
   a.col_group = col_group;
-  const bool quad = !col_group && count == kBlk && cols % 4 == 0 && aligned16(W) && aligned16(U) &&
+  const bool quad = (!col_group || static_fits) && count == kBlk && cols % 4 == 0 && aligned16(W) && aligned16(U) &&
                     (!codes || (reinterpret_cast<uintptr_t>(codes) & 3u) == 0);
   if (quad) {
     const unsigned grid = (unsigned)((rows + kQuadRowsPerCta - 1) / kQuadRowsPerCta);
-    gptq_block_quad_kernel<<<grid, kQuadThreads, kSmem, st>>>(a);
+    if (col_group) gptq_block_quad_kernel<true><<<grid, kQuadThreads, (size_t)smem_static, st>>>(a);
+    else gptq_block_quad_kernel<false><<<grid, kQuadThreads, kSmem, st>>>(a);
   } else {
     const unsigned grid = (unsigned)((rows + kRowsPerCta - 1) / kRowsPerCta);
     gptq_block_kernel<<<grid, kThreads, kSmem, st>>>(a);
