@@ -176,7 +176,7 @@ class GPTQBlockwise:
         # 128-column steps by the number of linears; in a process group every rank takes a row range.
         stacked = layers[0].weight.data if len(layers) == 1 else torch.cat([l.weight.data for l in layers], 0)
         static = None
-        if self.solver.static_groups:
+        if self.solver.uses_static():
             # static groups: the layers' own round-to-nearest buffers, stacked like the rows
             parts = [self.solver.static_qparams(l) for l in layers]
             static = (torch.cat([p[0] for p in parts], 0),
@@ -185,7 +185,7 @@ class GPTQBlockwise:
             res = self.solver.solve(stacked, H, hscale, factor=fac, static=static)
         else:
             res = self._sharded_solve(stacked, fac, rank, world, static)
-        n_groups = (H.shape[0] + 127) // 128
+        n_groups = res['buf_scales'].shape[0] // stacked.shape[0]      # qparams per row (1 for per_channel)
         r0 = 0
         for layer in layers:
             r1 = r0 + layer.weight.shape[0]

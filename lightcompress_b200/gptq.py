@@ -88,10 +88,15 @@ class GPTQ:
 
     def _check_config(self):
         wq = self.wquantizer
-        if wq.granularity != 'per_group' or wq.group_size != 128 or self.blocksize != 128:
+        # per_channel (the reference's w8a8 configs): search_layer_qparams (gptq.py:368-375) fixes one scale per
+        # row for every column, i.e. static groups with a single group spanning the row
+        self.per_channel = wq.granularity == 'per_channel'
+        if self.per_channel and self.owq:
+            raise NotImplementedError('owq with per_channel weights is outside the B200 hot path')
+        if self.blocksize != 128 or not (self.per_channel or (wq.granularity == 'per_group' and wq.group_size == 128)):
             # gptq.py:216-223 reads group statistics that are only well defined when a group
             # starts at a block boundary; the kernels implement group_size == blocksize == 128.
-            raise NotImplementedError('GPTQ kernels need per_group with group_size == blocksize == 128')
+            raise NotImplementedError('GPTQ kernels need per_channel, or per_group with group_size == blocksize == 128')
         wq._check_supported()
 
     # ---- Hessian ---------------------------------------------------------------------------
@@ -156,13 +161,17 @@ class GPTQ:
         H, hscale = self._finish_hessian(name)
         n_out = self.n_out_of(name)
         fac = self.factorize(H, hscale, n_out=n_out) if n_out else None
-        static = self.static_qparams(layer) if self.static_groups else None
+        static = self.static_qparams(layer) if self.uses_static() else None
         res = self.solve(layer.weight.data, H, hscale, rows=rows, factor=fac, static=static)
         if rows is None:
             self._install(layer, res)
         return res
 
     @torch.no_grad()
+    def uses_static(self):
+        """The solver quantises with the layer's own buffers (static_groups, or per_channel weights)."""
+        return bool(self.static_groups or self.per_channel)
+
     @torch.no_grad()
     def static_qparams(self, layer):
         """static_groups: the layer's round-to-nearest buffers (collect_block_qparams,
@@ -393,14 +402,20 @@ class GPTQ:
         R, C = Wp.shape
         dev = Wp.device
         perm, invperm, U = fac['perm'], fac['invperm'], fac['U']
-        n_groups = C // 128
-        if C % 128:
+        n_groups = (C + 127) // 128
+        if C % 128 and not self.per_channel:
             raise NotImplementedError('static_groups needs columns % 128 == 0')
         s_all, z_all = static
         r0, r1 = rows if rows is not None else (0, R)
-        # the solver computes in fp32 on the promoted qparams (their values are those of the weight dtype)
-        s32 = s_all.reshape(-1, n_groups)[r0:r1].float().contiguous()
-        z32 = None if wq.sym else z_all.reshape(-1, n_groups)[r0:r1].float().contiguous()
+        # the solver computes in fp32 on the promoted qparams (their values are those of the weight dtype);
+        # per_channel: the row's one scale stands in every column group of the kernels' table
+        per = 1 if self.per_channel else n_groups
+
+        def table(t):
+            t = t.reshape(-1, per)[r0:r1].float()
+            return (t.expand(-1, n_groups) if self.per_channel else t).contiguous()
+        s32 = table(s_all)
+        z32 = None if wq.sym else table(z_all)
         cols = torch.arange(C, device=dev) if perm is None else perm
         col_group = (cols // 128).to(torch.int32).contiguous()
         if fac.get('U_lo') is not None and R % 4 == 0:
@@ -415,7 +430,7 @@ class GPTQ:
                    L.ptr(err), L.ptr(s32), L.ptr(z32), L.ptr(col_group), L.ptr(codes), L.ptr(loss_rows), stream)
         out = torch.empty((R, C), dtype=torch.float32, device=dev)
         L.call('lc_gptq_unpermute', L.ptr(Wp), L.ptr(perm), R, C, L.ptr(out), L.LC_F32, stream)
-        sl = slice(r0 * n_groups, r1 * n_groups)
+        sl = slice(r0 * per, r1 * per)
         return {'weight': out, 'buf_scales': s_all[sl], 'buf_zeros': None if wq.sym else z_all[sl],
                 'buf_perm': perm, 'buf_invperm': invperm, 'codes_perm': codes, 'loss_rows': loss_rows,
                 'static': True}

@@ -4,7 +4,8 @@ Follows llmc/compression/quantization/gptq.py: add_batch :254-295, hessian_sorti
 :58-64, process_hessian_and_weights :128-176, weight_transform :199-244,
 search_column_qparams :359-366, merge/update qparams :344-356, :398-409 and the
 deploy-time w_qdq :425-452.  Only the configuration the hot path covers is restated:
-nn.Linear, per_group with group_size == blocksize, static_groups off or on (:224-227, :377-393); owq (:44-50, :66-83, :186-188,
+nn.Linear, per_group with group_size == blocksize, static_groups off or on (:224-227, :377-393),
+per_channel (:368-375); owq (:44-50, :66-83, :186-188,
 :440-447) with fewer outlier columns than a group.
 """
 import math
@@ -70,7 +71,7 @@ def static_group_qparams(W, bit=4, sym=False, group_size=128):
     """The round-to-nearest qparams collect_block_qparams leaves on a layer
     (base_blockwise_quantization.py:349-376), in the weight's dtype: buf_scales / buf_zeros,
     (R * n_groups, 1), which search_group_qparams (gptq.py:377-393) splits per group."""
-    g = Q.group_view(W, 'per_group', group_size)
+    g = W if group_size is None else Q.group_view(W, 'per_group', group_size)     # None: per_channel
     s, z, qmax, qmin = Q.int_qparams(g, bit, sym)
     return s, z
 
@@ -79,7 +80,7 @@ def weight_transform(W, U, bit=4, sym=False, group_size=128, blocksize=128, n_ou
     """gptq.py:199-244.  W is modified in place like the reference; returns
     (kept weights `tmp`, Losses, per-group scales list, per-group zeros list).  With owq the last
     n_out columns are not quantised (they only receive the error feedback) and `tmp` is zero there."""
-    assert group_size == blocksize
+    assert group_size == blocksize or static is not None
     R, C = W.shape
     n_nonout = C - n_out
     tmp = torch.zeros_like(W)
@@ -125,7 +126,7 @@ def merge_group_qparams(per_group):
 
 
 def quantize_layer(W, H, bit=4, sym=False, group_size=128, blocksize=128,
-                   percdamp=0.01, actorder=True, n_out=0, static_groups=False):
+                   percdamp=0.01, actorder=True, n_out=0, static_groups=False, granularity='per_group'):
     """layer_transform (gptq.py:114-117, :178-196): returns a dict with the reference's
     per-layer results: weight (compensated, fp32, original column order), buf_scales,
     buf_zeros (permuted-group order), buf_perm, buf_invperm, loss.  n_out > 0 is the owq mode
@@ -133,7 +134,13 @@ def quantize_layer(W, H, bit=4, sym=False, group_size=128, blocksize=128,
     the reference's w_qdq only works then): the outlier columns keep their error-compensated fp32 values
     (gptq.py:186-188)."""
     Wp, U, perm, invperm = prepare(W, H, percdamp, actorder and not n_out, n_out)
-    static = static_group_qparams(W, bit, sym, group_size) if static_groups else None
+    if granularity == 'per_channel':
+        # search_layer_qparams (gptq.py:368-375): the layer's per-channel round-to-nearest qparams for every
+        # column -- static groups with one group spanning the row
+        static_groups, group_size = True, W.shape[1]
+        static = static_group_qparams(W, bit, sym, None)
+    else:
+        static = static_group_qparams(W, bit, sym, group_size) if static_groups else None
     tmp, Losses, gs, gz = weight_transform(Wp, U, bit, sym, group_size, blocksize, n_out, static,
                                            perm if (static_groups and actorder) else None)
     if n_out:

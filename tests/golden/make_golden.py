@@ -231,14 +231,16 @@ def make_fp8(rq, out_dir):
     print('fp8_block.pt', len(blk), 'cases')
 
 
-def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01, n_out=0, static_groups=False):
+def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01, n_out=0, static_groups=False,
+                    per_channel=False):
     """Drives the reference GPTQ class on one nn.Linear, bypassing its model plumbing.  n_out > 0: owq."""
     g = object.__new__(rg.GPTQ)
     g.dev = torch.device('cpu')
-    g.wquantizer = rq.IntegerQuantizer(bit, sym, 'per_group', group_size=128)
+    g.wquantizer = (rq.IntegerQuantizer(bit, sym, 'per_channel') if per_channel
+                    else rq.IntegerQuantizer(bit, sym, 'per_group', group_size=128))
     g.true_sequential, g.static_groups, g.actorder = True, static_groups, actorder
     g.percdamp, g.blocksize, g.owq, g.chunk_num = percdamp, 128, n_out > 0, 1
-    g.need_perm = (actorder and not static_groups) or n_out > 0
+    g.need_perm = (actorder and not static_groups and not per_channel) or n_out > 0
     if n_out:
         g.n_out_dict = {'l': n_out}
     g.layers_cache = {'l': {}}
@@ -257,8 +259,9 @@ def _ref_gptq_layer(rq, rg, W, X, bit, sym, actorder, percdamp=0.01, n_out=0, st
     H = g.layers_cache['l']['H'].clone()
     g.layer_transform(layer, 'l')
     fq = g.w_qdq(layer, g.wquantizer)
-    perm = layer.buf_perm if ((actorder and not static_groups) or n_out) else torch.arange(W.shape[1])
-    codes = g.wquantizer.quant(layer.weight.data[:, perm].reshape(-1, 128), layer.buf_scales,
+    perm = layer.buf_perm if g.need_perm else torch.arange(W.shape[1])
+    codes = g.wquantizer.quant(layer.weight.data[:, perm].reshape(-1, W.shape[1] if per_channel else 128),
+                               layer.buf_scales,
                                layer.buf_zeros if not sym else torch.tensor(0.0),
                                layer.buf_qmax, layer.buf_qmin).reshape(W.shape)
     return dict(W=W, X=X, H=H, bit=bit, sym=sym, actorder=actorder, percdamp=percdamp,
@@ -298,6 +301,21 @@ def make_gptq_static(rq, rg, out_dir):
         cases[name] = _ref_gptq_layer(rq, rg, W, X, 4, sym, act, static_groups=True)
     torch.save(cases, os.path.join(out_dir, 'gptq_static.pt'))
     print('gptq_static.pt', len(cases), 'cases')
+
+
+def make_gptq_per_channel(rq, rg, out_dir):
+    """GPTQ on per_channel 8-bit weights (the reference's w8a8 configs, step_2_gptq.yml)."""
+    gen = torch.Generator().manual_seed(2007)
+    cases = {}
+    for name, R, C, ns, T, bit, sym in (('w8_sym', 48, 384, 6, 160, 8, True), ('w4_asym', 32, 256, 4, 128, 4, False)):
+        W = (torch.randn(R, C, generator=gen) * 0.02).to(torch.bfloat16)
+        X = torch.randn(ns, T, C, generator=gen)
+        out_ch = torch.randperm(C, generator=gen)[:max(1, C // 100)]
+        X[:, :, out_ch] *= 20
+        X = X.to(torch.bfloat16)
+        cases[name] = _ref_gptq_layer(rq, rg, W, X, bit, sym, True, static_groups=True, per_channel=True)
+    torch.save(cases, os.path.join(out_dir, 'gptq_per_channel.pt'))
+    print('gptq_per_channel.pt', len(cases), 'cases')
 
 
 def make_gptq_owq(rq, rg, out_dir):
@@ -490,6 +508,7 @@ if __name__ == '__main__':
     only = set(sys.argv[2:])            # optional: names of the fixtures to (re)make; default all
     steps = {'rtn': lambda: make_rtn(rq, out_dir), 'rtn_mse': lambda: make_rtn_mse(rq, out_dir),
              'gptq': lambda: make_gptq(rq, rg, out_dir), 'gptq_owq': lambda: make_gptq_owq(rq, rg, out_dir),
+             'gptq_per_channel': lambda: make_gptq_per_channel(rq, rg, out_dir),
              'gptq_static': lambda: make_gptq_static(rq, rg, out_dir),
              'quik': lambda: make_quik(rq, out_dir), 'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
              'export': lambda: make_export_configs(ref_root, out_dir)}

@@ -484,3 +484,80 @@ def test_static_groups_vs_oracle(R, C, sym):
           f'recon ref {e_ref:.6f} gpu {e_gpu:.6f}')
     assert mism < CODE_MISMATCH_MAX
     assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref
+
+
+# ---- per_channel weights (gptq.py:368-375; the reference's w8a8 GPTQ configs) ---------------------------
+
+@pytest.mark.parametrize('factorization', ['native', 'reference'])
+def test_per_channel_matches_reference_golden(golden, factorization):
+    """The solver on the reference's own Hessian (one flipped code early in a row changes the error
+    feedback of the rest of that row, so the Hessian kernel's last-bit differences are kept out of this
+    comparison; test_hessian_equals_reference_add_batch covers them)."""
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    for key, c in golden('gptq_per_channel.pt').items():
+        wq = IntegerQuantizer(c['bit'], c['sym'], 'per_channel')
+        solver = GPTQ(wq, {'actorder': True, 'static_groups': True, 'percdamp': 0.01, 'blocksize': 128,
+                           'factorization': factorization}, model_dtype=c['W'].dtype)
+        assert solver.per_channel and not solver.need_perm
+        R, C = c['W'].shape
+        layer = torch.nn.Linear(C, R, bias=False, dtype=c['W'].dtype).cuda()
+        layer.weight.data = c['W'].cuda()
+        res = solver.solve(layer.weight.data, c['H'].cuda().float(), 1.0, static=solver.static_qparams(layer))
+        solver._install(layer, res)
+        fq = solver.w_qdq(layer, wq)
+        solver.check_status()
+        assert layer.buf_scales.shape == (R, 1) and torch.equal(layer.buf_scales.cpu(), c['buf_scales']), key
+        codes = wq.quant(layer.weight.data, layer.buf_scales.float(),
+                         None if c['sym'] else layer.buf_zeros.float(), None, None)
+        diff = codes.cpu().to(torch.int16) != c['codes_perm']
+        mism = float(diff.float().mean())
+        X = c['X'].reshape(-1, C).float()
+        e_ref = gptq_ref.recon_error(c['W'].float(), c['w_qdq'].float(), X)
+        e_gpu = gptq_ref.recon_error(c['W'].float(), fq.cpu().float(), X)
+        print(f'per_channel {key} ({factorization}): code mismatch {mism:.5%} in {int(diff.any(1).sum())} rows, '
+              f'recon ref {e_ref:.6f} gpu {e_gpu:.6f}')
+        assert mism < CODE_MISMATCH_MAX, key
+        assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref, key
+
+
+def test_per_channel_wide_vs_oracle():
+    """W8 per_channel on a 2304-wide layer (tensor-core trailing path) and a ragged width (2200: the
+    last block has 24 columns), against the CPU oracle with the same Hessian and column order."""
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    for R, C in ((128, 2304), (64, 2200)):
+        g = torch.Generator().manual_seed(2900 + C)
+        ns, T = 8, 512
+        W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16)
+        X = _x(g, ns, T, C)
+        st = gptq_ref.hessian_init(C)
+        for i in range(ns):
+            gptq_ref.add_batch(st, X[i:i + 1])
+        ref = gptq_ref.quantize_layer(W, st['H'], bit=8, sym=True, granularity='per_channel')
+        wq = IntegerQuantizer(8, True, 'per_channel')
+        solver = GPTQ(wq, {'actorder': True, 'static_groups': True, 'percdamp': 0.01}, model_dtype=W.dtype)
+        layer = torch.nn.Linear(C, R, bias=False, dtype=W.dtype).cuda()
+        layer.weight.data = W.cuda()
+        fac = solver.factorize(st['H'].cuda(), 1.0, perm=ref['solver_perm'])
+        res = solver.solve(layer.weight.data, st['H'].cuda(), 1.0, factor=fac, static=solver.static_qparams(layer))
+        solver._install(layer, res)
+        fq = solver.w_qdq(layer, wq)
+        solver.check_status()
+        assert torch.equal(layer.buf_scales.cpu(), ref['buf_scales'])
+        ref_codes = gptq_ref.codes_permuted(ref, 8, True, group_size=C)
+        mine = {'weight': layer.weight.data.cpu(), 'buf_scales': ref['buf_scales'], 'buf_zeros': None,
+                'buf_perm': ref['buf_perm']}
+        my_codes = gptq_ref.codes_permuted(mine, 8, True, group_size=C)
+        mism = float((my_codes != ref_codes).float().mean())
+        step = float((my_codes - ref_codes).abs().max())
+        Xf = X.reshape(-1, C).float()
+        e_ref = gptq_ref.recon_error(W.float(), gptq_ref.w_qdq(ref, torch.bfloat16, 8, True, group_size=C).float(), Xf)
+        e_gpu = gptq_ref.recon_error(W.float(), fq.cpu().float(), Xf)
+        print(f'per_channel R={R} C={C}: code mismatch {mism:.5%} (largest code difference {step:.0f}), '
+              f'recon ref {e_ref:.6f} gpu {e_gpu:.6f}')
+        # An 8-bit grid is 16 times finer than the 4-bit one the 0.1 % bar is stated for: the same fp32-level
+        # differences in U (factorisation route, summation order of the trailing update) move 16 times as
+        # many weights across a rounding boundary.  The differing codes are neighbours and the
+        # reconstruction error is unchanged; with the reference's own Hessian and 384 columns the golden
+        # test above has none.
+        assert mism < 5 * CODE_MISMATCH_MAX and step <= 1
+        assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref

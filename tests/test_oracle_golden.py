@@ -100,6 +100,24 @@ def test_gptq_static_groups_oracle_matches_reference(golden):
         _eq(gptq_ref.w_qdq(res, c['W'].dtype, c['bit'], c['sym']), c['w_qdq'])
 
 
+def test_gptq_per_channel_oracle_matches_reference(golden):
+    """per_channel weights (the reference's w8a8 GPTQ configs): one fixed scale per row for every column."""
+    torch.set_num_threads(1)
+    cases = golden('gptq_per_channel.pt')
+    assert len(cases) == 2
+    for key, c in cases.items():
+        res = gptq_ref.quantize_layer(c['W'], c['H'], bit=c['bit'], sym=c['sym'], percdamp=c['percdamp'],
+                                      actorder=c['actorder'], granularity='per_channel')
+        _eq(res['weight'], c['weight'])
+        _eq(res['buf_scales'], c['buf_scales'])
+        if not c['sym']:
+            _eq(res['buf_zeros'], c['buf_zeros'])
+        C = c['W'].shape[1]
+        codes = gptq_ref.codes_permuted(res, c['bit'], c['sym'], group_size=C)
+        assert torch.equal(codes.to(torch.int16), c['codes_perm'])
+        _eq(gptq_ref.w_qdq(res, c['W'].dtype, c['bit'], c['sym'], group_size=C), c['w_qdq'])
+
+
 def test_gptq_owq_oracle_matches_reference(golden):
     """owq: the n_out columns with the largest Hessian diagonal are permuted to the end and stay
     unquantised (error feedback only); everything else as GPTQ without act-order."""
