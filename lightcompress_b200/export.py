@@ -17,6 +17,20 @@ def pack_compressed_tensors_int4(weight, wquantizer):
     return packed.view(torch.int32), s
 
 
+def pack_compressed_tensors_int4_static(weight, scales, wquantizer):
+    """The same with given scales (real_quant_weight_static, quant.py:870-913, then the packer): the
+    export step of a GPTQ layer solved with static_groups, whose weight is the fp32 compensated weight
+    and whose scales are the layer's buf_scales.  Returns (packed int32 (rows, cols/8), scales
+    (rows, n_groups))."""
+    if not wquantizer.sym or wquantizer.bit != 4:
+        raise NotImplementedError('compressed-tensors int4 packing is for symmetric 4-bit weights')
+    if weight.dim() != 2 or weight.shape[1] % 8:
+        raise ValueError('in_features must be a multiple of 8')
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    _, packed, _, _ = wquantizer._launch(w, wquantizer._group_len(w.shape[-1]), scales, None, codes=L.LC_CODES_PACK4)
+    return packed.view(torch.int32), scales.reshape(w.shape[0], -1)
+
+
 def pack_autoawq_gemm(codes_u8, zeros_u8):
     """AutoAWQ GEMM layout: codes (out, in) uint8 -> qweight (in, out/8) int32; zeros (out, n_groups)
     uint8 -> qzeros (n_groups, out/8) int32."""

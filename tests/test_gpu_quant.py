@@ -259,6 +259,14 @@ def test_export_packing_layouts():
     q, s_ref, _ = quant_ref.int_real_quant_dynamic(w, 4, True, 'per_group', 128)
     assert torch.equal(packed.cpu(), quant_ref.pack_compressed_tensors(q))
     _same(s, s_ref, 'scales')
+    # static scales on an fp32 weight: the export of a GPTQ layer solved with static_groups
+    from lightcompress_b200.export import pack_compressed_tensors_int4_static
+    w32 = (w.float() + 0.003 * torch.randn(256, 512, generator=g))
+    packed2, s_back = pack_compressed_tensors_int4_static(w32.cuda(), s, qs)
+    q2 = quant_ref.int_quant(w32.reshape(-1, 128), s_ref.reshape(-1, 1), torch.tensor(0.0), *reversed(
+        quant_ref.int_range(4, True))).reshape(256, 512)
+    assert torch.equal(packed2.cpu(), quant_ref.pack_compressed_tensors(q2))
+    assert s_back.shape == (256, 4)
     qa = IntegerQuantizer(4, False, 'per_group', group_size=128)
     codes, s2, z2 = qa.real_quant_weight_dynamic(w.cuda())
     qweight, qzeros = pack_autoawq_gemm(codes.to(torch.uint8), z2.to(torch.uint8))
