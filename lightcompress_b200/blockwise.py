@@ -52,6 +52,9 @@ class FakeQuantLinear(nn.Module):
                 self.register_buffer(name, buf.data)
         self.w_qdq = w_qdq
         self.in_features, self.out_features = module.in_features, module.out_features
+        # the solver's codes of this very weight tensor (GPTQ._install): the deploy-time weight is then
+        # one dequantise + un-permute kernel instead of the gather / fake quant / gather chain
+        self._lc_codes = getattr(module, '_lc_codes', None)
 
     def forward(self, x):
         if not hasattr(self, 'tmp_weight'):
@@ -84,12 +87,25 @@ class _StopForward(Exception):
     """Raised by a Hessian hook once the tensor it needs has been seen (see early_exit)."""
 
 
+_stage_checked = {}
+
+
 class GPTQBlockwise:
-    def __init__(self, wquantizer, special=None, model_dtype=torch.bfloat16, quant_out=True):
+    def __init__(self, wquantizer, special=None, model_dtype=torch.bfloat16, quant_out=True, solver=None,
+                 fake_linear=None):
+        """solver: an existing lightcompress_b200.GPTQ to drive (default: a new one from `special`).
+        fake_linear: callable(module) -> replacement module for a quantised linear (default:
+        FakeQuantLinear of this file); the plugin passes the reference's own FakeQuantLinear.new so that
+        the block is left exactly as the reference leaves it."""
         special = dict(special or {})
-        self.solver = GPTQ(wquantizer, special, model_dtype)
+        self.solver = solver if solver is not None else GPTQ(wquantizer, special, model_dtype)
         self.wquantizer = wquantizer
         self.quant_out = quant_out
+        self.fake_linear = fake_linear or (lambda mod: FakeQuantLinear(
+            mod, lambda m: self.solver.w_qdq(m, self.wquantizer)))
+        # block classes whose staged forward did not reproduce the block's own forward (they run the
+        # generic re-forwarding schedule): visible to callers, nothing is skipped silently
+        self.stage_plan_rejected = []
         self.true_sequential = self.solver.true_sequential
         # A re-forward whose only purpose is to feed the hooks of one subset stops as soon as that
         # subset's input has been seen: the rest of the block computes values nobody reads.
@@ -199,40 +215,55 @@ class GPTQBlockwise:
             r0 = r1
 
     def _sharded_solve(self, stacked, fac, rank, world, static=None):
-        """Row range `rank` of the stacked weight solved here, all ranges broadcast: every rank returns
-        the same full result."""
+        """Row range `rank` of the stacked weight solved here, then ONE all-gather per subset: every
+        rank packs its rows as [compensated weight | scales | zeros | codes] into one fp32 buffer (row
+        ranges are padded to the longest), and unpacks the gathered buffer.  Every rank returns the
+        same full result."""
         H = fac['H']
         R, C = stacked.shape
         n_groups = (C + 127) // 128
         dev = H.device
-        full = {'weight': torch.empty((R, C), dtype=torch.float32, device=dev),
-                'buf_scales': torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
-                'buf_zeros': None if self.wquantizer.sym else
-                torch.empty((R * n_groups, 1), dtype=torch.float32, device=dev),
-                # every rank computes the same permutation from the same (reduced) Hessian
-                'buf_perm': fac['perm'], 'buf_invperm': fac['invperm']}
-        if fac.get('n_out'):
-            full['buf_n_nonout'] = torch.tensor(C - fac['n_out'])
+        sym = self.wquantizer.sym
         # row ranges in multiples of 128 rows (whole CTAs of the in-block kernel), as even as possible
         blocks = (R + 127) // 128
         bounds = [min(R, 128 * ((blocks * r) // world)) for r in range(world)] + [R]
         a, b = bounds[rank], bounds[rank + 1]
         mine = self.solver.solve(stacked, H, rows=(a, b), factor=fac, static=static) if b > a else None
-        for owner in range(world):
-            a, b = bounds[owner], bounds[owner + 1]
-            if b <= a:
-                continue
-            # static groups: the qparams are inputs that every rank already holds
-            for key in (('weight',) if static is not None else ('weight', 'buf_scales', 'buf_zeros')):
-                dst = full[key]
-                if dst is None:
-                    continue
-                view = dst[a:b] if key == 'weight' else dst[a * n_groups:b * n_groups]
-                if owner == rank:
-                    view.copy_(mine[key])
-                dist.broadcast(view, src=owner)
-        if static is not None:
+        # packed row: C weight floats, then (unless static: the qparams are inputs every rank holds)
+        # n_groups scales and n_groups zeros, then the uint8 codes viewed as C / 4 floats
+        with_codes = C % 4 == 0 and bool(self.solver.emit_codes)      # the same on every rank
+        n_q = 0 if static is not None else n_groups
+        off_s, off_z = C, C + n_q
+        off_c = off_z + (0 if sym else n_q)
+        row_len = off_c + (C // 4 if with_codes else 0)
+        max_rows = max(bounds[r + 1] - bounds[r] for r in range(world))
+        packed = torch.empty((world, max_rows, row_len), dtype=torch.float32, device=dev)
+        slot = packed[rank]
+        if mine is not None:
+            n = b - a
+            slot[:n, :C].copy_(mine['weight'])
+            if n_q:
+                slot[:n, off_s:off_s + n_q].copy_(mine['buf_scales'].view(n, n_q))
+                if not sym:
+                    slot[:n, off_z:off_z + n_q].copy_(mine['buf_zeros'].view(n, n_q))
+            if with_codes:
+                slot[:n, off_c:].view(torch.uint8).copy_(mine['codes_perm'])
+        parallel.all_gather_packed(packed)
+        pieces = [packed[r, :bounds[r + 1] - bounds[r]] for r in range(world) if bounds[r + 1] > bounds[r]]
+        rows = pieces[0] if len(pieces) == 1 else torch.cat(pieces, 0)           # (R, row_len)
+        full = {'weight': rows[:, :C].contiguous(),
+                # every rank computes the same permutation from the same (reduced) Hessian
+                'buf_perm': fac['perm'], 'buf_invperm': fac['invperm'], 'buf_zeros': None}
+        if n_q:
+            full['buf_scales'] = rows[:, off_s:off_s + n_q].reshape(R * n_q, 1)
+            if not sym:
+                full['buf_zeros'] = rows[:, off_z:off_z + n_q].reshape(R * n_q, 1)
+        else:
             full['buf_scales'], full['buf_zeros'], full['static'] = static[0], static[1], True
+        if with_codes:
+            full['codes_perm'] = rows[:, off_c:].contiguous().view(torch.uint8)
+        if fac.get('n_out'):
+            full['buf_n_nonout'] = torch.tensor(C - fac['n_out'])
         return full
 
     # ---- the block -----------------------------------------------------------------------------
@@ -245,7 +276,7 @@ class GPTQBlockwise:
             # n_outs are bound to the block's linears by position (gptq.py:89-93)
             self.solver.set_block_linears([n for sub in (subsets or llama_subsets(block)) for n in sub])
         if (subsets is None and self.stage_plan and self.true_sequential and self.quant_out
-                and is_llama_layout(block)):
+                and is_llama_layout(block) and self._staged_forward_matches(block, inputs, kwargs)):
             return self._block_opt_llama_staged(block, inputs, kwargs)
         subsets = subsets or llama_subsets(block)
         outs = None
@@ -259,7 +290,10 @@ class GPTQBlockwise:
             del first_out
             for i, subset in enumerate(subsets):
                 self.subset_transform(subset)
-                self._replace(subset)
+                # rehook_next_subset swaps a subset for fake-quant linears only when a re-forward follows
+                # (base_blockwise_quantization.py:522-525); the last one is swapped by quant_out below
+                if i + 1 < len(subsets) or self.quant_out:
+                    self._replace(subset)
                 if i + 1 < len(subsets):
                     handle = self._hook_subset(subsets[i + 1], stop=self.early_exit)
                     self.block_forward(block, inputs, kwargs, need_output=False)
@@ -273,11 +307,51 @@ class GPTQBlockwise:
                 outs = first_out
             for subset in subsets:
                 self.subset_transform(subset)
-                self._replace(subset)
+                if self.quant_out:
+                    self._replace(subset)
         if self.quant_out:
             outs = self.block_forward(block, inputs, kwargs)
         self.solver.check_status()
         return outs
+
+    @torch.no_grad()
+    def _staged_forward_matches(self, block, inputs, kwargs):
+        """The staged plan hard-codes the data flow of a pre-norm Llama block (x + attn(norm(x)), then
+        h + mlp(norm(h))).  Other decoder layers carry the same attribute names and compute something
+        else (extra norms around the attention output, residual multipliers, ...), so before a block
+        class is first staged one sequence goes through the untouched block and through the staged
+        order of operations; only bit-equal outputs admit the plan.  Once per class, device, dtype."""
+        if not inputs:
+            return False
+        x = inputs[0]
+        key = (type(block), type(block.self_attn), type(block.mlp), str(x.device), x.dtype, bool(self.fused_block_ops))
+        if key not in _stage_checked:
+            if self.on_input is not None:
+                self.on_input(0)
+            kw = kwargs[0] if isinstance(kwargs, (list, tuple)) else kwargs
+            a, m = block.self_attn, block.mlp
+            norm = block_ops.rms_norm if self.fused_block_ops else (lambda mod, t: mod(t))
+            ok = False
+            try:
+                ref = block(x, **kw)
+                ref = ref[0] if isinstance(ref, tuple) else ref
+                rotary = (block_ops.fused_rotary(a, x.device, x.dtype) if self.fused_block_ops
+                          else contextlib.nullcontext())
+                with rotary:
+                    att = a(hidden_states=norm(block.input_layernorm, x), **kw)
+                att = att[0] if isinstance(att, tuple) else att
+                h = x + att
+                y = norm(block.post_attention_layernorm, h)
+                prod = (block_ops.gated_act(m.act_fn, m.gate_proj(y), m.up_proj(y)) if self.fused_block_ops
+                        else m.act_fn(m.gate_proj(y)) * m.up_proj(y))
+                out = h + m.down_proj(prod)
+                ok = ref.shape == out.shape and torch.equal(ref, out)
+            except (TypeError, RuntimeError, ValueError, AttributeError):
+                ok = False
+            _stage_checked[key] = ok
+        if not _stage_checked[key] and type(block).__name__ not in self.stage_plan_rejected:
+            self.stage_plan_rejected.append(type(block).__name__)
+        return _stage_checked[key]
 
     @torch.no_grad()
     def _block_opt_llama_staged(self, block, inputs, kwargs):
@@ -359,5 +433,8 @@ class GPTQBlockwise:
     def _replace(self, subset):
         for n, (parent, attr) in subset.items():
             mod = getattr(parent, attr)
-            if not isinstance(mod, FakeQuantLinear):
-                setattr(parent, attr, FakeQuantLinear(mod, lambda m: self.solver.w_qdq(m, self.wquantizer)))
+            if isinstance(mod, nn.Linear):
+                new = self.fake_linear(mod)
+                if getattr(new, '_lc_codes', None) is None:
+                    new._lc_codes = getattr(mod, '_lc_codes', None)
+                setattr(parent, attr, new)

@@ -4,9 +4,9 @@ Method names, arguments and the buffers left on each layer follow
 llmc/compression/quantization/gptq.py: layer_init :298-308, add_batch :254-295,
 layer_transform :114-117 (hessian_sorting :58-64, process_hessian_and_weights :128-176,
 update_layer_with_transformed_weights :178-196, weight_transform :199-244,
-update_model_qparams :398-409), w_qdq :425-452, free :466-471.  `plugin.install` binds them
-onto the reference's registered `GPTQ` class; used stand-alone the class drives one or more
-`nn.Linear` layers directly.
+update_model_qparams :398-409), w_qdq :425-452, free :466-471.  `lightcompress_b200.plugin.install()`
+re-registers a subclass of the reference's `GPTQ` whose methods of these names forward here; used
+stand-alone the class drives one or more `nn.Linear` layers directly.
 
 Differences in schedule, not in result: the Hessian is kept as the raw sum of X^T X and scaled
 by 2/nsamples once, and with several ranks it is all-reduced once per layer (in
@@ -122,7 +122,11 @@ class GPTQ:
             raise NotImplementedError('the Hessian kernel takes bf16 activations')
         x = x if x.is_contiguous() else x.contiguous()
         L.require_cuda(x)
+        # held by reference until the batch is full: remember the tensor's version so that an in-place
+        # change made by the caller in between (the reference consumes the tensor inside the hook) is
+        # caught instead of silently entering the Hessian
         st['pending'].append(x)
+        st.setdefault('versions', []).append(x._version)
         st['nsamples'] += b
         if len(st['pending']) >= self.hessian_batch:
             self._flush(st)
@@ -132,6 +136,11 @@ class GPTQ:
         if not xs:
             return
         n = len(xs)
+        for x, v in zip(xs, st.get('versions', [])):
+            if x._version != v:
+                raise RuntimeError('an activation handed to add_batch was modified in place before its Hessian '
+                                   'batch was accumulated; pass a copy or set hessian_batch: 1')
+        st['versions'] = []
         ptrs = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
         toks = (ctypes.c_int64 * n)(*[x.shape[0] for x in xs])
         L.call('lc_hessian_accum_multi', ptrs, toks, n, xs[0].shape[1], L.ptr(st['H']), 1.0, 1.0, self.hessian_ksplit,
@@ -142,9 +151,10 @@ class GPTQ:
         """All-reduce once per layer (gptq.py:292-295 does it per call); returns (H_raw, 2/n)."""
         st = self.layers_cache[name]
         self._flush(st)
-        _, n = parallel.reduce_hessian(st['H'], st['nsamples'])
+        # the kernel's status word travels with the sample count: every rank learns of a failure on any
+        # rank and raises here, before the next collective, instead of waiting in it for a peer that left
+        _, n, code = parallel.reduce_hessian(st['H'], st['nsamples'], st['status'])
         self.check_status()
-        code = int(st['status'].item())
         if code != 0:
             raise L.LcError('lc_hessian_accum', code, L.status_string(code))
         if n == 0:
@@ -538,7 +548,14 @@ class GPTQ:
         return weight
 
     def check_status(self):
-        """Reads (one sync) the device status words of the tensor-core launches issued so far."""
+        """Reads (one sync) the device status words of the tensor-core launches issued so far.  In a
+        process group the words are first combined over the ranks (every rank issues the same launches),
+        so all ranks raise together."""
+        if parallel.world()[1] > 1 and (self._pending_info or self._pending_status):
+            if self._pending_info:
+                self._pending_info = [parallel.combine_status(torch.cat(self._pending_info).abs(), 'max')]
+            if self._pending_status:
+                self._pending_status = [parallel.combine_status(torch.cat(self._pending_status), 'min')]
         if self._pending_info:
             infos = torch.cat(self._pending_info).tolist()
             self._pending_info = []

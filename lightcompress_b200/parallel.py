@@ -42,16 +42,45 @@ def row_shard(rows, rank=None, world_size=None, multiple=16):
     return min(b, rows), min(e, rows)
 
 
-def reduce_hessian(H_raw, n_sequences):
-    """Sums the raw Hessians and the sequence counts over the ranks; returns (H_raw, total_n).
-    The caller scales by 2 / total_n."""
+def reduce_hessian(H_raw, n_sequences, status=None):
+    """Sums the raw Hessians and the sequence counts over the ranks; returns (H_raw, total_n, code).
+    The caller scales by 2 / total_n, which is the Hessian of all sequences whatever the split; the
+    reference's per-call all-reduce and division by the world size (gptq.py:292-295) equals it when
+    every rank holds the same number of sequences (sequence_shard deals them that way when the count
+    divides).  status: this rank's int32 device status word of the Hessian kernel (0 = ok, negative =
+    error); `code` is the worst one over all ranks, so that every rank can raise together."""
     _, w = world()
+    own = 0 if status is None else int(status.item())
     if w == 1:
-        return H_raw, n_sequences
+        return H_raw, n_sequences, own
     dist.all_reduce(H_raw, op=dist.ReduceOp.SUM)
-    nt = torch.tensor([n_sequences], dtype=torch.int64, device=H_raw.device)
+    # one small collective carries both: the count in slot 0, the number of failing ranks in slot 1
+    nt = torch.tensor([n_sequences, 1 if own != 0 else 0], dtype=torch.int64, device=H_raw.device)
     dist.all_reduce(nt, op=dist.ReduceOp.SUM)
-    return H_raw, int(nt.item())
+    total, failed = (int(v) for v in nt.tolist())
+    return H_raw, total, (own if own != 0 else (LC_ERR_PEER if failed else 0))
+
+
+LC_ERR_PEER = -8        # LC_ERR_CUDA: "a peer rank reported a device error"
+
+
+def combine_status(words, how):
+    """Element-wise min / max of an integer status vector over the ranks (all ranks pass the same length)."""
+    _, w = world()
+    if w > 1:
+        dist.all_reduce(words, op=dist.ReduceOp.MIN if how == 'min' else dist.ReduceOp.MAX)
+    return words
+
+
+def all_gather_packed(packed):
+    """packed: (world, ...) contiguous, slot [rank] filled by this rank; on return every slot holds its
+    rank's data.  One collective, in place."""
+    rank, w = world()
+    if w == 1:
+        return packed
+    assert packed.shape[0] == w and packed.is_contiguous()
+    dist.all_gather_into_tensor(packed.view(-1), packed[rank].reshape(-1).clone())
+    return packed
 
 
 def gather_rows(piece, rows):

@@ -217,7 +217,9 @@ class IntegerQuantizer(BaseQuantizer):
         return fake.reshape(t.shape)
 
     def _reject_args(self, args, allowed=()):
-        bad = [k for k in args if k not in allowed]
+        # keys the base class always passes with value None (lowbound_factor / upbound_factor,
+        # base_blockwise_quantization.py:50-56) carry no request
+        bad = [k for k in args if k not in allowed and args[k] is not None]
         if bad:
             raise NotImplementedError(f'args {bad} are outside the B200 hot path')
 
@@ -489,7 +491,7 @@ class FloatQuantizer(BaseQuantizer):
         return t, s.reshape(*t.shape[:-1], 1), torch.tensor(0.0), self.qmax, self.qmin
 
     def fake_quant_weight_dynamic(self, weight, args={}):
-        if args:
+        if any(v is not None for v in args.values()):
             raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
         if self.granularity == 'per_block':
             return self._launch_block(weight, fake=True)[0]
@@ -499,7 +501,7 @@ class FloatQuantizer(BaseQuantizer):
     fake_quant_act_dynamic = fake_quant_weight_dynamic
 
     def real_quant_weight_dynamic(self, weight, args={}):
-        if args:
+        if any(v is not None for v in args.values()):
             raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
         if self.granularity == 'per_block':
             _, codes, s = self._launch_block(weight, codes=True)
@@ -561,7 +563,7 @@ class Weight48IntegerQuantizer(BaseQuantizer):
                          float(st['zeros_qmin']), float(st['zeros_qmax']))
 
     def fake_quant_weight_dynamic(self, weight, args={}):
-        if args:
+        if any(v is not None for v in args.values()):
             raise NotImplementedError(f'args {list(args)} are outside the B200 hot path')
         if self.calib_algo != 'minmax':
             raise NotImplementedError(f"calib_algo '{self.calib_algo}' is outside the B200 hot path")

@@ -334,6 +334,37 @@ def make_gptq_owq(rq, rg, out_dir):
     print('gptq_owq.pt', len(cases), 'cases')
 
 
+def make_gptq_block(ref_root, out_dir):
+    """The reference's own GPTQ through its own driver -- model adapter, first-block catcher,
+    ALGO_REGISTRY['GPTQ'](...), run_block_loop() (blockwise_optimization.py:31-42 ->
+    base_blockwise_quantization.py:403-549) -- on a random-init two-layer Llama, settings of
+    gptq_w_only.yml.  Stored: the blocks' initial state, the first block's inputs, what every linear is
+    left with, and the tensors handed to the block after the last one."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(out_dir)))
+    from oracle import ref_driver as rd
+    ref = rd.import_reference(ref_root, on_cpu=True)
+    shape = dict(hidden=128, inter=256, heads=2, layers=2, vocab=64, max_pos=256)
+    n, T = 6, 48
+    cfg = rd.tiny_llama_config(**shape)
+    model = rd.synth_llama_adapter(ref, cfg, seed=21)
+    state0 = [{k: v.clone() for k, v in b.state_dict().items()} for b in model.get_blocks()]
+    calib = rd.calib_ids(n, T, cfg.vocab_size, seed=22)
+    model.collect_first_block_input(calib, None)
+    first = model.get_first_block_input()
+    x0 = [t.clone() for t in first['data']]
+    kw0 = {k: ((tuple(t.clone() for t in v) if isinstance(v, tuple) else v.clone() if torch.is_tensor(v) else v))
+           for k, v in first['kwargs'][0].items() if k != 'use_cache'}
+    algo = ref.ALGO_REGISTRY['GPTQ'](model, rd.gptq_quant_config(), first, None,
+                                     rd.AttrDict(model=dict(type='Llama'), calib=dict(bs=1, seq_len=T, n_samples=n),
+                                                 quant=rd.gptq_quant_config()))
+    algo.run_block_loop()
+    out = dict(shape=shape, T=T, state0=state0, x0=x0, kwargs=kw0, linears=rd.linear_state(model),
+               next_inputs=[t.clone() for t in algo.input['data']],
+               module_classes=sorted({type(m).__name__ for b in model.get_blocks() for m in b.modules()}))
+    torch.save(out, os.path.join(out_dir, 'gptq_block_loop.pt'))
+    print('gptq_block_loop.pt', len(out['linears']), 'blocks')
+
+
 class _TorchProxy:
     """Stands in for the `torch` name inside the reference's awq module: drops device='cuda'."""
 
@@ -511,7 +542,8 @@ if __name__ == '__main__':
              'gptq_per_channel': lambda: make_gptq_per_channel(rq, rg, out_dir),
              'gptq_static': lambda: make_gptq_static(rq, rg, out_dir),
              'quik': lambda: make_quik(rq, out_dir), 'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
-             'export': lambda: make_export_configs(ref_root, out_dir)}
+             'export': lambda: make_export_configs(ref_root, out_dir),
+             'gptq_block': lambda: make_gptq_block(ref_root, out_dir)}
     for name, step in steps.items():
         if not only or name in only:
             step()

@@ -1,0 +1,138 @@
+"""The drop-in itself, on the GPU: the reference's own driver objects (model adapter, first-block
+catcher, `ALGO_REGISTRY[method](...)`, `run_block_loop()`, `deploy('fake_quant')`,
+llmc/__main__.py:29-72) run twice on the same random-init Llama and the same token ids -- once with
+the reference's stock classes (torch ops on this GPU: the arbitration oracle for the tolerance-based
+bars) and once after `lightcompress_b200.plugin.install()`.
+
+Bars: every linear ends with the same buffers (names, shapes, dtypes), fewer than 0.1 % differing int
+codes in original column order, the deployed model's logits within 1 % of the reference's deployed
+model (relative to the quantisation error itself), identical module classes after deploy.  RTN:
+bit-identical deployed weights.
+
+Needs the reference's `llmc` package in baseline/_ref/ (placed by `python __graft_entry__.py` where
+the checkout is present); skipped otherwise."""
+import copy
+
+import pytest
+import torch
+
+from oracle import gptq_ref
+from oracle import ref_driver as rd
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(rd.find_reference() is None, reason='no reference checkout / baseline/_ref')]
+
+
+@pytest.fixture(scope='module')
+def ref():
+    return rd.import_reference()
+
+
+def _run(ref, quant_cfg, cfg, calib, seq_len, seed, with_plugin, probe):
+    from lightcompress_b200 import plugin
+    model = rd.synth_llama_adapter(ref, cfg, seed=seed)
+    fp = copy.deepcopy(model.model).cuda()
+    with torch.no_grad():
+        logits_fp = fp(probe.cuda()).logits.float().cpu()
+    del fp
+    if with_plugin:
+        plugin.install()
+    try:
+        algo = rd.run_algorithm(ref, model, copy.deepcopy(quant_cfg), calib, seq_len, deploy=None)
+        state = rd.linear_state(model)
+        algo.deploy('fake_quant')
+        classes = sorted({type(m).__name__ for b in model.get_blocks() for m in b.modules()})
+        model.model.cuda()
+        with torch.no_grad():
+            logits = model.model(probe.cuda()).logits.float().cpu()
+        model.model.cpu()
+    finally:
+        if with_plugin:
+            plugin.uninstall()
+    torch.cuda.synchronize()
+    return dict(state=state, logits=logits, logits_fp=logits_fp, classes=classes, algo_class=type(algo))
+
+
+def _codes_original_order(e, sym=False):
+    R, C = e['weight'].shape
+    res = {'weight': e['weight'], 'buf_scales': e['buf_scales'], 'buf_zeros': e.get('buf_zeros'),
+           'buf_perm': e['buf_perm']}
+    out = torch.empty(R, C)
+    out[:, e['buf_perm']] = gptq_ref.codes_permuted(res, 4, sym).float()
+    return out
+
+
+@pytest.mark.parametrize('shape,schedule', [('tiny', 'b200'), ('tiny', 'reference'), ('medium', 'b200')])
+def test_gptq_run_block_loop_and_deploy_through_the_reference_driver(ref, shape, schedule):
+    if shape == 'tiny':
+        cfg, n, T = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2), 8, 96
+    else:
+        # wide enough for the tensor-core trailing update (columns > 1024) and a ragged panel
+        cfg, n, T = rd.tiny_llama_config(hidden=1280, inter=2560, heads=10, layers=2, vocab=512), 12, 320
+    calib = rd.calib_ids(n, T, cfg.vocab_size, seed=5)
+    probe = rd.calib_ids(1, T, cfg.vocab_size, seed=6)[0]['input_ids']
+    qc = rd.gptq_quant_config({'b200_schedule': schedule} if schedule != 'b200' else None)
+    a = _run(ref, rd.gptq_quant_config(), cfg, calib, T, 3, False, probe)
+    b = _run(ref, qc, cfg, calib, T, 3, True, probe)
+    assert a['algo_class'].__name__ == b['algo_class'].__name__ == 'GPTQ' and a['algo_class'] is not b['algo_class']
+    assert a['classes'] == b['classes'] and 'EffcientFakeQuantLinear' in a['classes']
+    tot = dif = 0
+    for bi, (sa, sb) in enumerate(zip(a['state'], b['state'])):
+        assert list(sa) == list(sb)
+        for name in sa:
+            ea, eb = sa[name], sb[name]
+            assert sorted(ea) == sorted(eb), (name, sorted(ea), sorted(eb))
+            for k in ea:
+                assert ea[k].shape == eb[k].shape and ea[k].dtype == eb[k].dtype, (name, k, ea[k].dtype, eb[k].dtype)
+            ca, cb = _codes_original_order(ea), _codes_original_order(eb)
+            d = float((ca != cb).float().mean())
+            tot += ca.numel()
+            dif += int((ca != cb).sum())
+            print(f'{shape}/{schedule} block {bi} {name}: code mismatch {d:.4%}, '
+                  f'perm entries differing {int((ea["buf_perm"] != eb["buf_perm"]).sum())}')
+            assert d < 1e-3, (bi, name, d)
+    print(f'{shape}/{schedule}: overall code mismatch {dif / tot:.5%}')
+    # reconstruction: the deployed models' logits against the unquantised model's
+    err_a = float((a['logits'] - a['logits_fp']).norm() / a['logits_fp'].norm())
+    err_b = float((b['logits'] - b['logits_fp']).norm() / b['logits_fp'].norm())
+    print(f'{shape}/{schedule}: logit error of the deployed model: reference {err_a:.5f}, plugin {err_b:.5f}')
+    assert abs(err_a - err_b) <= 0.01 * err_a + 1e-5
+
+
+def test_rtn_deploy_is_bit_identical(ref):
+    cfg = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2)
+    probe = rd.calib_ids(1, 64, cfg.vocab_size, seed=6)[0]['input_ids']
+    out = []
+    for with_plugin in (False, True):
+        from lightcompress_b200 import plugin
+        model = rd.synth_llama_adapter(ref, cfg, seed=4)
+        if with_plugin:
+            plugin.install()
+        try:
+            rd.run_algorithm(ref, model, rd.rtn_quant_config(), None, 64, deploy='fake_quant')
+        finally:
+            if with_plugin:
+                plugin.uninstall()
+        out.append({n: m.weight.data.cpu() for n, m in model.model.named_modules()
+                    if type(m).__name__ == 'EffcientFakeQuantLinear'})
+    assert len(out[0]) == 14 and list(out[0]) == list(out[1])
+    for n in out[0]:
+        assert out[0][n].dtype == out[1][n].dtype and torch.equal(out[0][n], out[1][n]), n
+
+
+def test_standalone_rtn_mirror_matches_the_quantizer():
+    """lightcompress_b200.RTN (w_qdq / w_q / a_qdq of base_blockwise_quantization.py:50-86) against the oracle."""
+    import lightcompress_b200 as lcb
+    from oracle import quant_ref
+    g = torch.Generator().manual_seed(9)
+    lin = torch.nn.Linear(512, 96, bias=False, dtype=torch.bfloat16)
+    lin.weight.data = (torch.randn(96, 512, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(2, 7, 512, generator=g).to(torch.bfloat16)
+    rtn = lcb.RTN(lcb.IntegerQuantizer(4, False, 'per_group', group_size=128),
+                  lcb.IntegerQuantizer(8, True, 'per_token'))
+    glin = copy.deepcopy(lin).cuda()
+    assert torch.equal(rtn.w_qdq(glin).cpu(), quant_ref.int_fake_quant_dynamic(lin.weight.data, 4, False, 'per_group', 128))
+    q, s, z = rtn.w_q(glin)
+    rq, rs, rz = quant_ref.int_real_quant_dynamic(lin.weight.data, 4, False, 'per_group', 128)
+    assert torch.equal(q.cpu(), rq) and torch.equal(s.cpu(), rs) and torch.equal(z.cpu(), rz)
+    assert torch.equal(rtn.a_qdq(x.cuda()).cpu(), quant_ref.int_fake_quant_dynamic(x, 8, True, 'per_token', None))

@@ -206,3 +206,29 @@ def test_awq_oracle_matches_reference_block(golden):
         for k, v in c['state1'].items():
             assert torch.equal(got[k], v), (key, k, int((got[k] != v).sum()))
         assert any(not torch.equal(c['state0'][k], c['state1'][k]) for k in c['state1'])
+
+
+def test_gptq_block_schedule_oracle_matches_the_references_run_block_loop(golden):
+    """oracle/gptq_block_ref.py against the reference's own GPTQ run_block_loop() on a two-layer Llama
+    (tests/golden/make_golden.py: make_gptq_block): the compensated weight, scales, zeros and
+    permutation of all fourteen linears, and the tensors handed on after each block, bit for bit."""
+    from oracle import gptq_block_ref
+    torch.set_num_threads(1)
+    c = golden('gptq_block_loop.pt')
+    sh = c['shape']
+    inputs = [x.clone() for x in c['x0']]
+    assert c['module_classes'].count('FakeQuantLinear') == 1            # quant_out leaves fake-quant linears
+    for bi, state in enumerate(c['state0']):
+        from transformers.models.llama.modeling_llama import LlamaDecoderLayer
+        from oracle import ref_driver as rd
+        block = LlamaDecoderLayer(rd.tiny_llama_config(**sh), bi).to(torch.bfloat16)
+        block.load_state_dict(state)
+        kwargs = c['kwargs']          # as the reference's catcher recorded them (base_model.py:172-191)
+        results, inputs = gptq_block_ref.gptq_block(block, inputs, kwargs)
+        assert list(results) == list(c['linears'][bi])
+        for name, want in c['linears'][bi].items():
+            got = results[name]
+            for k in ('weight', 'buf_scales', 'buf_zeros', 'buf_perm', 'buf_invperm'):
+                assert got[k].dtype == want[k].dtype and torch.equal(got[k], want[k]), (bi, name, k)
+    for a, b in zip(inputs, c['next_inputs']):
+        assert torch.equal(a, b)

@@ -25,7 +25,8 @@ def _worker(rank, world_size, port, out_dir):
     for i in range(b, e):
         x = X[i].float()
         H += x.t() @ x
-    H, n = parallel.reduce_hessian(H, e - b)
+    H, n, code = parallel.reduce_hessian(H, e - b)
+    assert code == 0
     assert n == ns
     H = H * (2.0 / n)
     r0, r1 = parallel.row_shard(R)
@@ -66,3 +67,36 @@ def test_shard_arithmetic():
     assert all(a[1] == b[0] for a, b in zip(cover, cover[1:]))
     assert all((e - b) % 16 == 0 for b, e in cover)
     assert parallel.row_shard(40, 3, 4) == (40, 40)       # more ranks than row units: empty tail shard
+
+
+def _status_worker(rank, world_size, port, out_dir):
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world_size))
+    dist.init_process_group('gloo', rank=rank, world_size=world_size)
+    from lightcompress_b200 import parallel
+    # rank 1's Hessian kernel "timed out" (status word set on the host): both ranks must learn of it in
+    # the same reduction, so that neither goes on into the next collective alone
+    H = torch.ones(4, 4) * (rank + 1)
+    status = torch.tensor([-7 if rank == 1 else 0], dtype=torch.int32)
+    H, n, code = parallel.reduce_hessian(H, 3, status)
+    words = parallel.combine_status(torch.tensor([0, -6 if rank == 0 else 0], dtype=torch.int32), 'min')
+    # the packed all-gather of the row-sharded solve: slot r filled by rank r
+    packed = torch.zeros(world_size, 3, 5)
+    packed[rank] = rank + 1
+    parallel.all_gather_packed(packed)
+    torch.save({'H': H, 'n': n, 'code': code, 'words': words, 'packed': packed}, os.path.join(out_dir, f's{rank}.pt'))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_a_failed_rank_is_seen_by_every_rank(tmp_path):
+    from lightcompress_b200 import parallel
+    port = 29100 + (os.getpid() % 400)
+    mp.spawn(_status_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = torch.load(os.path.join(str(tmp_path), 's0.pt'))
+    r1 = torch.load(os.path.join(str(tmp_path), 's1.pt'))
+    assert r0['n'] == r1['n'] == 6 and torch.equal(r0['H'], torch.full((4, 4), 3.0))
+    assert r1['code'] == -7                       # the failing rank reports its own code
+    assert r0['code'] == parallel.LC_ERR_PEER     # its peer is told that some rank failed
+    assert r0['words'].tolist() == r1['words'].tolist() == [0, -6]
+    want = torch.stack([torch.full((3, 5), 1.0), torch.full((3, 5), 2.0)])
+    assert torch.equal(r0['packed'], want) and torch.equal(r1['packed'], want)
