@@ -1,6 +1,7 @@
 """Benchmark of the GPTQ calibration hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload block|layer]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload block|layer|model|awq|moe|kernel] [--case NAME --launches N]
 
 Default workload `block` (the end-to-end GPTQ configuration's unit of work): ONE Llama-2-7B-shape
 decoder layer (hidden 4096, 32 heads, MLP 11008, bf16, weights N(0, 0.02^2)) quantised with GPTQ
@@ -11,6 +12,15 @@ solves); value = decoder layers per second.
 
 Workload `layer` (the single-linear GPTQ configuration): one 4096 -> 4096 linear, 128 x 2048 x 4096
 calibration activations; a step = Hessian accumulation over all sequences + the layer solve.
+
+Workload `model` (the end-to-end configuration): a random-init 32-layer Llama-2-7B-shape model in host
+memory, 128 x 2048 token ids -> embedding -> the block loop over all 32 layers with every block
+streamed through the GPU (lightcompress_b200.HostStagedGPTQ.run_block_loop); a step = one pass over the
+model, value = 32 / its duration.
+
+Workload `kernel` (--case NAME): a small, self-terminating run of one kernel family sized for a
+profiler capture (inputs larger than the 126 MB L2, a few hundred MB on the device, a handful of
+launches); prints no benchmark line.
 
 N > 1 (launched by torch.distributed.run): calibration sequences are sharded over the ranks, each
 Hessian is all-reduced once (NCCL), the (linear, row-range) solve units are dealt to the ranks.
@@ -109,7 +119,10 @@ def kwargs_to(kwargs, dev):
     return out
 
 
-LINEAR_KEYS = ['q', 'k', 'v', 'o', 'gate', 'up', 'down']
+LINEAR_NAMES = ['self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj', 'self_attn.o_proj', 'mlp.gate_proj',
+                'mlp.up_proj', 'mlp.down_proj']
+# DRAM bytes per 16384-token Hessian launch by width, from the ncu captures under profiles/
+HESSIAN_NCU_TRAFFIC = {4096: 213.7e6, 11008: 2833.0e6}
 LINEAR_SHAPES = [(HID, HID)] * 4 + [(INTER, HID)] * 2 + [(HID, INTER)]   # (rows, cols) of q,k,v,o,gate,up,down
 
 
@@ -179,16 +192,21 @@ def cpu_port_layer(n_hess_samples=8):
     return 1.0 / (t_h + t_s), desc, cores, {'hessian_s': t_h, 'solver_s': t_s}
 
 
-def cpu_port_block():
-    """One sequence through the reference schedule's five forwards with its Hessian hooks (scaled
-    x128), plus the solver: prepare and weight_transform timed on a 4096x4096 linear and scaled to
-    the seven linears by C^3 and rows*cols respectively."""
+_SOLVER_CACHE = {}
+
+
+def cpu_port_block(seq_index=0):
+    """One sequence (number `seq_index` of the 128) through the reference schedule's five forwards with
+    its Hessian hooks, scaled x128, plus the solver: prepare and weight_transform timed once per process
+    on a 4096x4096 linear and scaled to the seven linears by C^3 and rows*cols respectively.
+    Returns (layers/s extrapolated, description, cores, parts, seconds actually spent)."""
     import torch
     from oracle import gptq_block_ref, gptq_ref
     cores = os.cpu_count()
     torch.set_num_threads(cores)
+    t_begin = time.perf_counter()
     block, kwargs = make_block()
-    x = make_activations(1, 2001)
+    x = make_activations(seq_index + 1, 2001)[seq_index:seq_index + 1]
     subsets = gptq_block_ref.llama_subsets(block)
     t0 = time.perf_counter()
     with torch.no_grad():
@@ -207,37 +225,54 @@ def cpu_port_block():
             for h in hs:
                 h.remove()
     t_fwd = (time.perf_counter() - t0) * NS
-    W = make_linear_weight()
-    g = torch.Generator().manual_seed(1)
-    Xs = torch.randn(8192, HID, generator=g)
-    H = (Xs.t() @ Xs) * (2.0 / 4)
-    t0 = time.perf_counter()
-    Wp, U, perm, invperm = gptq_ref.prepare(W, H)
-    t_prep = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    gptq_ref.weight_transform(Wp, U)
-    t_wt = time.perf_counter() - t0
-    t_solver = sum(t_prep * (c / HID) ** 3 + t_wt * (r * c) / (HID * HID) for r, c in LINEAR_SHAPES)
-    desc = (f'forwards + Hessian hooks: 1 of {NS} sequences through the 5 passes, scaled x{NS}; solver: prepare and '
-            f'weight_transform timed on one 4096x4096 linear, scaled to the 7 linears by C^3 and rows*cols')
-    return 1.0 / (t_fwd + t_solver), desc, cores, {'forward_hessian_s': t_fwd, 'solver_s': t_solver}
+    if 'solver' not in _SOLVER_CACHE:
+        W = make_linear_weight()
+        g = torch.Generator().manual_seed(1)
+        Xs = torch.randn(8192, HID, generator=g)
+        H = (Xs.t() @ Xs) * (2.0 / 4)
+        t0 = time.perf_counter()
+        Wp, U, perm, invperm = gptq_ref.prepare(W, H)
+        t_prep = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        gptq_ref.weight_transform(Wp, U)
+        t_wt = time.perf_counter() - t0
+        _SOLVER_CACHE['solver'] = sum(t_prep * (c / HID) ** 3 + t_wt * (r * c) / (HID * HID) for r, c in LINEAR_SHAPES)
+    t_solver = _SOLVER_CACHE['solver']
+    desc = (f'forwards + Hessian hooks: 1 of {NS} sequences (a different one each step) through the 5 passes, scaled '
+            f'x{NS}; solver: prepare and weight_transform timed once on one 4096x4096 linear, scaled to the 7 linears '
+            f'by C^3 and rows*cols')
+    return (1.0 / (t_fwd + t_solver), desc, cores, {'forward_hessian_s': t_fwd, 'solver_s': t_solver},
+            time.perf_counter() - t_begin)
 
 
 def run_reference(args, rank):
+    """The reference arm: the CPU port of the reference on the host cores.  A full step of the workload
+    takes over an hour on the host, so each step times a bounded sample and the value is an
+    extrapolation, marked as such; `ms_per_step` is the time a step really took here."""
     if rank != 0:
         return
-    fn = cpu_port_block if args.workload == 'block' else (lambda: cpu_port_layer(4))
-    vals, desc, cores = [], None, None
+    vals, spent, desc, cores = [], [], None, None
     for i in range(args.warmup + args.steps):
-        v, desc, cores, _ = fn()
+        if args.workload == 'layer':
+            t0 = time.perf_counter()
+            v, desc, cores, _ = cpu_port_layer(4)
+            dt = time.perf_counter() - t0
+        else:
+            v, desc, cores, _, dt = cpu_port_block(seq_index=i % NS)
         if i >= args.warmup:
             vals.append(v)
+            spent.append(dt)
     v = sum(vals) / len(vals)
+    name = 'layer' if args.workload == 'layer' else 'block'
     print(json.dumps({
         'impl': 'reference', 'metric': METRIC, 'value': v, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': args.steps,
-        'warmup': args.warmup, 'ms_per_step': 1e3 / v, 'higher_is_better': True, 'scaling': 'strong',
-        'vs_baseline': None, 'dtype': 'bf16 in / fp32 accumulate', 'data': 'synthetic',
-        'config': {'workload': WORKLOADS[args.workload], 'name': args.workload},
+        'warmup': args.warmup, 'ms_per_step': 1e3 * sum(spent) / len(spent), 'higher_is_better': True,
+        'scaling': 'strong', 'vs_baseline': None, 'dtype': 'bf16 in / fp32 accumulate', 'data': 'synthetic',
+        'extrapolated': True, 'extrapolated_ms_per_step': 1e3 / v,
+        'sample_fraction': {'sequences': 1.0 / NS if name == 'block' else 4.0 / NS,
+                            'solver': 'one 4096x4096 linear of the seven' if name == 'block' else 'full'},
+        'spread': {'min': min(vals), 'max': max(vals)},
+        'config': {'workload': WORKLOADS[name], 'name': name},
         'cpu_baseline': {'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc},
         'e2e': {'value': v, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}, 'gpu_launches': 0}))
 
@@ -274,13 +309,32 @@ class HessianTimer:
         return by_c
 
 
-def rtn_aux(hbm_peak, dev):
-    """quant_dequant GB/s of the RTN kernel on the configuration of the reference's CPU-runnable case
-    (fp32 4096x4096, W4 asymmetric, groups of 128) and on a tensor far larger than L2; raw C-ABI calls,
-    8 rotating buffers so that no launch finds its input in L2, CUDA events around 40 launches."""
+def _time_launches(run, n=40, warm=8):
     import torch
+    for i in range(warm):
+        run(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        run(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n * 1e3
+
+
+def rtn_aux(hbm_peak, dev):
+    """quant_dequant GB/s of the RTN kernel.  The reference's CPU-runnable configuration as stated -- fp32
+    4096x4096, W4 asymmetric, groups of 128, outputs: dequantised weight + packed int4 codes + scales +
+    zeros (143.7 MB algorithmic) -- through the raw C ABI and through the IntegerQuantizer methods a
+    caller uses; the dequantised weight alone (fake quant, 134.2 MB + parameters); and tensors far larger
+    than L2.  8 rotating buffers at 4096x4096 so that no launch finds its input in L2, CUDA events around
+    40 launches."""
+    import torch
+    import lightcompress_b200 as lc
     from lightcompress_b200 import _lib as L
     out = {}
+    qz = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
     for name, rows, cols, dt in (('rtn_w4_g128_fp32_4096x4096', 4096, 4096, torch.float32),
                                  ('rtn_w4_g128_fp32_16384x8192', 16384, 8192, torch.float32),
                                  ('rtn_w4_g128_bf16_16384x8192', 16384, 8192, torch.bfloat16)):
@@ -289,23 +343,39 @@ def rtn_aux(hbm_peak, dev):
         ws = [(torch.randn(rows, cols, generator=g) * 0.02).to(dt).to(dev) for _ in range(n_buf)]
         outs = [torch.empty_like(w) for w in ws]
         st = L.stream_of(ws[0])
+        esz = ws[0].element_size()
+        n_grp = rows * cols // 128
 
-        def run(i):
+        def fake_only(i):
             L.call('lc_rtn_int_quant', L.ptr(ws[i % n_buf]), L.lc_dtype(ws[0]), rows, cols, 128, 4, 0, None, None,
                    L.ptr(outs[i % n_buf]), None, L.LC_CODES_NONE, None, None, st)
-        for i in range(8):
-            run(i)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(40):
-            run(i)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) / 40 * 1e3
-        nbytes = 2 * rows * cols * ws[0].element_size()
-        gbs = nbytes / us / 1e3
-        out[name] = {'us': us, 'algorithmic_bytes': nbytes, 'gb_s': gbs, 'frac_of_measured_hbm': gbs / hbm_peak}
+        us = _time_launches(fake_only)
+        nbytes = 2 * rows * cols * esz
+        out[name] = {'us': us, 'algorithmic_bytes': nbytes, 'gb_s': nbytes / us / 1e3,
+                     'frac_of_measured_hbm': nbytes / us / 1e3 / hbm_peak, 'outputs': 'dequantised weight', 'via': 'C ABI'}
+        if rows == 4096:
+            codes = [torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev) for _ in range(n_buf)]
+            sc = [torch.empty((n_grp, 1), dtype=dt, device=dev) for _ in range(n_buf)]
+            zr = [torch.empty((n_grp, 1), dtype=dt, device=dev) for _ in range(n_buf)]
+
+            def all_outputs(i):
+                k = i % n_buf
+                L.call('lc_rtn_int_quant', L.ptr(ws[k]), L.lc_dtype(ws[0]), rows, cols, 128, 4, 0, None, None,
+                       L.ptr(outs[k]), L.ptr(codes[k]), L.LC_CODES_PACK4, L.ptr(sc[k]), L.ptr(zr[k]), st)
+            full_bytes = 2 * rows * cols * esz + rows * cols // 2 + 2 * n_grp * esz
+            for key, fn, via in (
+                    (name + '_all_outputs', all_outputs, 'C ABI'),
+                    (name + '_all_outputs_api', lambda i: qz.quant_all_dynamic(ws[i % n_buf], packed=True),
+                     'IntegerQuantizer.quant_all_dynamic'),
+                    (name + '_fake_api', lambda i: qz.fake_quant_weight_dynamic(ws[i % n_buf]),
+                     'IntegerQuantizer.fake_quant_weight_dynamic')):
+                us = _time_launches(fn)
+                nb = nbytes if key.endswith('_fake_api') else full_bytes
+                out[key] = {'us': us, 'algorithmic_bytes': nb, 'gb_s': nb / us / 1e3,
+                            'frac_of_measured_hbm': nb / us / 1e3 / hbm_peak, 'via': via,
+                            'outputs': ('dequantised weight' if key.endswith('_fake_api') else
+                                        'dequantised weight + packed int4 codes + scales + zeros')}
+            del codes, sc, zr
         del ws, outs
     return out
 
@@ -313,21 +383,35 @@ def rtn_aux(hbm_peak, dev):
 def run_secondary(args):
     """`--workload awq`: AWQ scale + clip search of one Llama-2-7B-shape block on 128 x 512 calibration
     tokens in one batch (W4 asym g128, trans_version v2, clip_version v1).  `--workload moe`: FP8 e4m3
-    fake quant of a 64-expert MoE layer (per-channel weights once, per-token activations per forward).
-    Device-resident inputs, CUDA events, one JSON line with the configuration's own metric."""
+    fake quant of a 64-expert MoE layer (per-channel weights once, per-token activations per forward);
+    under torch.distributed.run the experts are sharded over the ranks.  Device-resident inputs and an
+    end-to-end variant from pinned host memory, CUDA events, one JSON line with the configuration's own
+    metric."""
     import torch
+    import torch.distributed as dist
     import lightcompress_b200 as lc
-    dev = torch.device('cuda', 0)
+    rank = int(os.environ.get('RANK', 0))
+    local_rank = int(os.environ.get('LOCAL_RANK', 0))
+    world = int(os.environ.get('WORLD_SIZE', 1))
+    dev = torch.device('cuda', local_rank)
     torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
     hbm_peak = peaks()[0]
+    extra = {}
     if args.workload == 'awq':
+        if world > 1:
+            raise SystemExit('--workload awq runs on one GPU')
         from lightcompress_b200.awq import Awq
         block_host, kwargs_host = make_block(seq_len=512)
         kwargs = kwargs_to(kwargs_host, dev)
         g = torch.Generator().manual_seed(3001)
-        X = torch.randn(NS, 512, HID, generator=g)
-        X[:, :, torch.randperm(HID, generator=g)[:41]] *= 20
-        X = X.to(torch.bfloat16).to(dev)
+        X_host = torch.randn(NS, 512, HID, generator=g)
+        X_host[:, :, torch.randperm(HID, generator=g)[:41]] *= 20
+        X_host = X_host.to(torch.bfloat16).pin_memory()
+        X = X_host.to(dev)
+        for p in block_host.parameters():
+            p.data = p.data.pin_memory()
         master = copy.deepcopy(block_host).to(dev)
         wq = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
         awq = Awq(wq, {'trans': True, 'trans_version': 'v2', 'weight_clip': True, 'clip_version': 'v1'},
@@ -335,42 +419,285 @@ def run_secondary(args):
 
         def step():
             return awq.block_transform(copy.deepcopy(master), X, kwargs)
+
+        host_out = {n: torch.empty(p.shape, dtype=p.dtype).pin_memory() for n, p in block_host.named_parameters()}
+
+        def e2e_step():
+            blk = copy.deepcopy(block_host).to(dev, non_blocking=True)
+            rep = awq.block_transform(blk, X_host.to(dev, non_blocking=True), kwargs)
+            for n, p in blk.named_parameters():
+                host_out[n].copy_(p.data, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return rep
+        h2d = int(X_host.numel() * 2 + sum(p.numel() * 2 for p in block_host.parameters()))
+        d2h = int(sum(p.numel() * 2 for p in block_host.parameters()))
         metric, unit = 'AWQ W4 g128 scale+clip search blocks/sec', 'blocks/s'
         workload = ('one Llama-2-7B-shape decoder block, AWQ W4 asym g128, 20-point scale grid on 4 subsets + clip '
                     'search on 5 linears, 128x512 calibration tokens in one batch')
     else:
         from lightcompress_b200.moe_fp8 import Fp8FakeQuantMoE
         g = torch.Generator().manual_seed(5001)
-        x = torch.randn(16384, 2048, generator=g).to(torch.bfloat16).to(dev)
+        x_host = torch.randn(16384, 2048, generator=g).to(torch.bfloat16).pin_memory()
+        x = x_host.to(dev)
         moe = Fp8FakeQuantMoE(device=dev)
-        pristine = [t.clone() for t in (moe.w_gate, moe.w_up, moe.w_down, moe.s_gate, moe.s_up, moe.s_down)]
+        names = ('w_gate', 'w_up', 'w_down') + (('s_gate', 's_up', 's_down') if moe.has_shared else ())
+        pristine = {n: getattr(moe, n).clone() for n in names}
+        host_w = {n: t.cpu().pin_memory() for n, t in pristine.items()}
+        out_host = torch.empty((16384, 2048), dtype=torch.bfloat16).pin_memory()
 
         def step():
-            moe.w_gate, moe.w_up, moe.w_down, moe.s_gate, moe.s_up, moe.s_down = pristine
+            for n, t in pristine.items():
+                setattr(moe, n, t)
             moe.quantize_weights()
             return moe.forward(x)
+
+        def e2e_step():
+            for n, t in host_w.items():
+                setattr(moe, n, t.to(dev, non_blocking=True))
+            moe.quantize_weights()
+            y = moe.forward(x_host.to(dev, non_blocking=True))
+            if rank == 0:
+                out_host.copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        h2d = int(x_host.numel() * 2 * world + sum(t.numel() * 2 for t in host_w.values()) * world)
+        d2h = int(out_host.numel() * 2)
         metric, unit = 'FP8 e4m3 fake-quant MoE layer passes/sec (weights quantised + one forward)', 'passes/s'
         workload = ('64 routed experts (1408 x 2048) + shared MLP, top-6, 16384 tokens, e4m3 per-channel weights, '
-                    'per-token dynamic activations')
-    for _ in range(max(1, args.warmup)):
+                    'per-token dynamic activations; experts sharded over the ranks, one all-reduce of the output')
+        # algorithmic bytes of the fake-quant passes (weights once, activations per projection input)
+        wbytes = 4 * (64 * 3 * 1408 * 2048 + 3 * 2 * 1408 * 2048)
+        abytes = 4 * (16384 * 6 * (2048 + 1408) + 16384 * (2048 + 2816))
+        extra['algorithmic_bytes'] = {'weights': wbytes, 'activations': abytes}
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / steps
+    for _ in range(max(3, args.warmup)):
         step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({'metric': metric, 'value': 1e3 / ms, 'unit': unit, 'n_gpus': 1, 'steps': args.steps,
-                      'warmup': args.warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
-                      'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
-                      'config': {'workload': workload, 'name': args.workload}, 'hbm_peak_gbs': hbm_peak}))
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = timed(step, args.steps)
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        line = {'metric': metric, 'value': 1e3 / ms, 'unit': unit, 'n_gpus': world, 'steps': args.steps,
+                'warmup': max(3, args.warmup), 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
+                'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+                'config': {'workload': workload, 'name': args.workload}, 'hbm_peak_gbs': hbm_peak,
+                'e2e': {'value': 1e3 / e2e_ms, 'unit': unit, 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': h2d,
+                        'd2h_bytes_per_step': d2h}, 'clocks': clocks}
+        line.update(extra)
+        if args.workload == 'moe':
+            tot = extra['algorithmic_bytes']['weights'] + extra['algorithmic_bytes']['activations']
+            line['roofline'] = {'bound': 'hbm', 'achieved': tot / world / (ms * 1e-3) / 1e9, 'peak': hbm_peak,
+                                'unit': 'GB/s', 'frac': tot / world / (ms * 1e-3) / 1e9 / hbm_peak, 'traffic': None,
+                                'note': 'fake-quant bytes of one rank over the whole step; the step also runs the '
+                                        "experts' GEMMs (cuBLAS), so this is a lower bound of the kernels' rate"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def n_super(c):
     s = -(-c // 256)
     return s * (s + 1) // 2
+
+
+# ---- small kernel cases for profiler captures (--workload kernel --case NAME) -----------------------------
+def kernel_case(name, n):
+    import torch
+    import lightcompress_b200 as lc
+    from lightcompress_b200 import _lib as L
+    wq4 = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
+
+    def hessian(C, seed):
+        T = 16384
+        g = torch.Generator().manual_seed(seed)
+        X = torch.randn(T, C, generator=g).to(torch.bfloat16).cuda()
+        H = torch.zeros(C, C, device='cuda')
+        status = torch.zeros(1, dtype=torch.int32, device='cuda')
+        for _ in range(n):
+            L.call('lc_hessian_accum', L.ptr(X), T, C, L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        return X, H, status
+    if name == 'hessian':
+        X, H, status = hessian(4096, 1)
+        for _ in range(n):
+            L.call('lc_hessian_accum', L.ptr(X), 2048, 4096, L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
+    elif name == 'hessian_wide':                      # the down_proj width, 16384 tokens per launch
+        hessian(11008, 5)
+    elif name in ('factor', 'factor_wide'):           # damp + Cholesky + triangular inverse of one Hessian
+        C = 4096 if name == 'factor' else 11008
+        g = torch.Generator().manual_seed(6)
+        X = torch.randn(2 * C, C, generator=g).cuda()
+        H = X.t() @ X
+        del X
+        solver = lc.GPTQ(wq4, {'actorder': True})
+        for _ in range(n):
+            solver.factorize(H, 0.5)
+        solver.check_status()
+    elif name == 'block_ops':                         # RMS norm, rotary embedding, SiLU-gate at Llama-2-7B width
+        from lightcompress_b200 import block_ops as B
+        g = torch.Generator().manual_seed(7)
+        x = torch.randn(8, 2048, 4096, generator=g).to(torch.bfloat16).cuda()
+        w = torch.ones(4096, dtype=torch.bfloat16, device='cuda')
+        q = x.view(8, 2048, 32, 128).transpose(1, 2)
+        cs = torch.randn(8, 2048, 128, generator=g).to(torch.bfloat16).cuda()
+        gate = torch.randn(8 * 2048, 11008, generator=g).to(torch.bfloat16).cuda()
+        for _ in range(n):
+            B._rms_raw(x, w, 1e-5)
+            B.rope_apply_one(q, cs, cs)
+            B.silu_mul(gate, gate)
+    elif name == 'fp8_linear':                        # act_quant + block-scaled FP8 GEMM, M 8192, N 11008, K 4096
+        from lightcompress_b200.fp8_linear import act_quant, fp8_gemm
+        from lightcompress_b200.quant import weight_cast_to_fp8
+        g = torch.Generator().manual_seed(8)
+        x = torch.randn(8192, 4096, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(11008, 4096, generator=g) * 0.05).to(torch.bfloat16).cuda()
+        wq, ws = weight_cast_to_fp8(w)
+        for _ in range(n):
+            a, a_s = act_quant(x)
+            fp8_gemm(a, a_s, wq, ws)
+    elif name == 'mse':                               # MSE range search, W4 asym g128, 8192 x 4096 fp32
+        g = torch.Generator().manual_seed(9)
+        w = (torch.randn(8192, 4096, generator=g) * 0.02).cuda()
+        qz = lc.IntegerQuantizer(4, False, 'per_group', group_size=128, calib_algo='mse')
+        grouped = qz.reshape_tensor(w)
+        for _ in range(n):
+            qz.get_tensor_range(grouped)
+    elif name == 'awq_clip':                          # clip search of a 4096 x 4096 bf16 linear, 512 tokens
+        g = torch.Generator().manual_seed(10)
+        w = (torch.randn(4096, 4096, generator=g) * 0.02).to(torch.bfloat16).cuda()
+        x = torch.randn(16, 512, 4096, generator=g).to(torch.bfloat16).cuda()
+        awq = lc.Awq(wq4, {}, calib_seq_len=512)
+        for _ in range(n):
+            awq.auto_clip_layer(w, x, apply=False)
+    elif name == 'rtn':
+        g = torch.Generator().manual_seed(2)
+        w = (torch.randn(8192, 4096, generator=g) * 0.02).cuda()
+        for _ in range(n):
+            wq4.fake_quant_weight_dynamic(w)
+        for _ in range(n):
+            wq4.quant_all_dynamic(w, packed=True)
+        wb = w.to(torch.bfloat16)
+        for _ in range(n):
+            wq4.fake_quant_weight_dynamic(wb)
+        qa = lc.IntegerQuantizer(8, True, 'per_token')
+        x = torch.randn(16384, 4096, generator=g).to(torch.bfloat16).cuda()
+        for _ in range(n):
+            qa.fake_quant_act_dynamic(x)
+    elif name == 'fp8':
+        g = torch.Generator().manual_seed(3)
+        x = torch.randn(65536, 2048, generator=g).to(torch.bfloat16).cuda()
+        q = lc.FloatQuantizer('e4m3', True, 'per_token', use_qtorch=True)
+        for _ in range(n):
+            q.fake_quant_act_dynamic(x)
+    elif name in ('gptq', 'gptq_wide'):               # the layer solve (block kernel + trailing updates)
+        R, C = (4096, 4096) if name == 'gptq' else (4096, 11008)
+        g = torch.Generator().manual_seed(4)
+        W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16).cuda()
+        X = torch.randn(max(8192, 2 * C), C, generator=g).to(torch.bfloat16).cuda()
+        H = torch.zeros(C, C, device='cuda')
+        L.call('lc_hessian_accum', L.ptr(X), X.shape[0], C, L.ptr(H), 1.0, 1.0, 0, None, L.stream_of(X))
+        solver = lc.GPTQ(wq4, {'actorder': True})
+        fac = solver.factorize(H, 2.0 / 4)
+        for _ in range(n):
+            solver.solve(W, H, 2.0 / 4, factor=fac)
+        solver.check_status()
+    elif name == 'act_static':                        # per-tensor ranges of 8 tensors of 64 MB in one launch
+        qz = lc.IntegerQuantizer(8, True, 'per_tensor', calib_algo='static_minmax')
+        g = torch.Generator(device='cuda').manual_seed(8)
+        acts = [torch.randn(4, 2048, 4096, generator=g, device='cuda').to(torch.bfloat16) for _ in range(8)]
+        for _ in range(n):
+            qz._tensor_ranges(acts)
+    elif name == 'quik':
+        from lightcompress_b200.quik import QUIK
+        g = torch.Generator(device='cuda').manual_seed(9)
+        x = torch.randn(65536, 4096, generator=g, device='cuda').to(torch.bfloat16)
+        aq = lc.IntegerQuantizer(8, True, 'per_token')
+        q = QUIK(lc.IntegerQuantizer(4, True, 'per_channel'), aq,
+                 {'fp_relative': False, 'fp_features': 256, 'fp_threshold': 0.0})
+        order = torch.randperm(4096, generator=g, device='cuda')
+        a = {'int_indices': order[:-256], 'fp_indices': order[-256:]}
+        for _ in range(n):
+            q.get_tensor_scale('l', x)
+            aq.fake_quant_act_dynamic(x[:32768], a)
+    elif name == 'w48':
+        bit4 = {'symmetric': False, 'granularity': 'per_group', 'group_size': 128, 'scales_bit': 8,
+                'scales_symmetric': True, 'zeros_bit': 8, 'zeros_symmetric': True}
+        bit8 = {'symmetric': True, 'granularity': 'per_channel', 'int_range': [-120, 120]}
+        qz = lc.Weight48IntegerQuantizer(48, bit4, bit8)
+        g = torch.Generator(device='cuda').manual_seed(10)
+        w = torch.randn(16384, 8192, generator=g, device='cuda').to(torch.bfloat16)
+        for _ in range(n):
+            qz.fake_quant_weight_dynamic(w)
+    else:
+        raise SystemExit(f'unknown --case {name}')
+    torch.cuda.synchronize()
+    print('done', name)
+
+
+KERNEL_CASES = ['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'gptq_wide', 'factor', 'factor_wide', 'block_ops',
+                'fp8_linear', 'mse', 'awq_clip', 'act_static', 'quik', 'w48']
+
+
+# ---- parity of the timed configuration (outside the timed region) --------------------------------------
+def parity_of_linear(W, X_list, res_codes_perm, res_perm, deployed, world, dev):
+    """Code mismatch and reconstruction error of one quantised linear against the oracle evaluated with
+    torch on the same GPU.  W: the linear's original weight; X_list: this rank's input tensors of the
+    linear; res_*: the solver's codes (permuted order) and permutation; deployed: its fake-quant weight."""
+    import torch
+    import torch.distributed as dist
+    from oracle import gptq_ref
+    C = W.shape[1]
+    if world == 1:
+        st = gptq_ref.hessian_init(C, dev)
+        for x in X_list:
+            gptq_ref.add_batch(st, x)               # the reference's own running-mean arithmetic
+        H = st['H']
+    else:
+        # sequences are sharded: sum of the ranks' raw X^T X (fp32, cuBLAS), scaled like 2/n
+        H = torch.zeros(C, C, device=dev)
+        n = torch.zeros(1, device=dev)
+        for x in X_list:
+            x2 = x.reshape(-1, C).float()
+            H += x2.t() @ x2
+            n += x.shape[0]
+        dist.all_reduce(H)
+        dist.all_reduce(n)
+        H *= 2.0 / float(n.item())
+    ref = gptq_ref.quantize_layer(W, H)
+    a = torch.empty(W.shape, dtype=torch.int16, device=dev)
+    b = torch.empty(W.shape, dtype=torch.int16, device=dev)
+    a[:, res_perm] = res_codes_perm.to(torch.int16)
+    b[:, ref['buf_perm']] = gptq_ref.codes_permuted(ref).to(torch.int16)
+    Xs = X_list[0].reshape(-1, C)[:4096].double()
+    full = Xs @ W.double().t()
+    e_got = float((Xs @ (W.double() - deployed.double()).t()).norm() / full.norm())
+    e_ref = float((Xs @ (W.double() - gptq_ref.w_qdq(ref, torch.bfloat16).double()).t()).norm() / full.norm())
+    return {'code_mismatch': float((a != b).float().mean()),
+            'perm_entries_differing': int((res_perm != ref['buf_perm']).sum()),
+            'recon_error': e_got, 'recon_error_oracle': e_ref,
+            'recon_rel_diff': abs(e_got - e_ref) / e_ref,
+            'oracle': 'oracle/gptq_ref.py (pinned to the reference) with torch on the same GPU',
+            'bars': {'code_mismatch': 1e-3, 'recon_rel_diff': 1e-2}}
 
 
 def main():
@@ -379,32 +706,37 @@ def main():
     ap.add_argument('--steps', type=int, default=3)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
-    ap.add_argument('--workload', default='block', choices=['block', 'layer', 'awq', 'moe'])
+    ap.add_argument('--workload', default='block', choices=['block', 'layer', 'model', 'awq', 'moe', 'kernel'])
+    ap.add_argument('--case', default='hessian', choices=KERNEL_CASES, help='--workload kernel: which kernel family')
+    ap.add_argument('--launches', type=int, default=3, help='--workload kernel: launches of each kernel')
+    ap.add_argument('--layers', type=int, default=32, help='--workload model: decoder layers of the model')
     ap.add_argument('--calib-bs', type=int, default=1,
                     help='sequences per block-forward call (calib.bs of the reference config; block workload)')
     ap.add_argument('--static-groups', action='store_true',
                     help='special.static_groups of the reference (its export configs); a side measurement')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-parity', action='store_true')
     args = ap.parse_args()
     if args.static_groups:
         SPECIAL['static_groups'] = True
     rank = int(os.environ.get('RANK', 0))
     local_rank = int(os.environ.get('LOCAL_RANK', 0))
     world = int(os.environ.get('WORLD_SIZE', 1))
-    if args.workload in ('awq', 'moe'):
-        # secondary configurations (AWQ block search, FP8 MoE fake quant): one GPU, their own metric
-        if rank == 0:
-            run_secondary(args)
-        return
     if args.impl == 'reference':
         run_reference(args, rank)
+        return
+    if args.workload == 'kernel':
+        kernel_case(args.case, args.launches)
+        return
+    if args.workload in ('awq', 'moe'):
+        run_secondary(args)
         return
 
     import torch
     import torch.distributed as dist
     import lightcompress_b200 as lc
-    from lightcompress_b200 import parallel
+    from lightcompress_b200 import block_ops, parallel
 
     torch.cuda.set_device(local_rank)
     dev = torch.device('cuda', local_rank)
@@ -415,129 +747,14 @@ def main():
     n_seq = s1 - s0
     hbm_peak, tf_burst, tf_sust, peak_kind = peaks()
     wq = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
+    phases = None
+    parity_fn = None
+    checksum_fn = None
+    extra_cfg = {}
 
-    X_host = make_activations(n_seq, 2001 + rank, pin=not args.no_e2e)
-    X = X_host.to(dev)
-
-    if args.workload == 'block':
-        block_host, kwargs_host = make_block()
-        kwargs = kwargs_to(kwargs_host, dev)
-        master = copy.deepcopy(block_host).to(dev)
-        runner = lc.GPTQBlockwise(wq, SPECIAL, quant_out=True)
-        solver = runner.solver
-        timer = HessianTimer(solver)
-        bs = max(1, min(args.calib_bs, n_seq))
-        inputs = [X[i:i + bs] for i in range(0, n_seq, bs)]
-
-        def step():
-            block = copy.deepcopy(master)          # device copy of the bf16 block (the reference does block.cuda())
-            outs = runner.block_opt(block, inputs, kwargs)
-            return block, outs
-
-        if not args.no_e2e:
-            for p in block_host.parameters():
-                p.data = p.data.pin_memory()
-            x_stages = [torch.empty_like(X), torch.empty_like(X)]
-            w_host = {n: torch.empty(rc, dtype=torch.float32).pin_memory()
-                      for n, rc in zip(LINEAR_KEYS, LINEAR_SHAPES) if LINEAR_KEYS.index(n) % world == rank}
-
-            host_params = [p.data for p in block_host.parameters()]
-            copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-            chunk = 8
-            name_to_key = {'self_attn.q_proj': 'q', 'self_attn.k_proj': 'k', 'self_attn.v_proj': 'v',
-                           'self_attn.o_proj': 'o', 'mlp.gate_proj': 'gate', 'mlp.up_proj': 'up',
-                           'mlp.down_proj': 'down'}
-            # steps_left: steps still to run in the current (warm-up or timed) sequence; pending: the
-            # copy events of activations already on their way for the next step, and their buffer
-            e2e_state = {'steps_left': 0, 'pending': None, 'buf': 0, 'prev_block': None}
-
-            def start_input_copy(buf):
-                evs = []
-                with torch.cuda.stream(copy_in):
-                    for i in range(0, n_seq, chunk):
-                        x_stages[buf][i:i + chunk].copy_(X_host[i:i + chunk], non_blocking=True)
-                        ev = torch.cuda.Event()
-                        ev.record(copy_in)
-                        evs.append(ev)
-                return evs
-
-            p_stages = [[torch.empty_like(p, device=dev) for p in host_params] for _ in range(2)] if rank == 0 else None
-
-            def start_copies(buf):
-                """Parameters (rank 0) and activations of one step, host -> staging buffers `buf`."""
-                p_ev = None
-                if rank == 0:
-                    with torch.cuda.stream(copy_in):
-                        for d, hp in zip(p_stages[buf], host_params):
-                            d.copy_(hp, non_blocking=True)
-                        p_ev = torch.cuda.Event()
-                        p_ev.record(copy_in)
-                return p_ev, start_input_copy(buf)
-
-            def e2e_step():
-                # Host -> device copies run on their own stream into one of two sets of staging buffers:
-                # the block's parameters, then the activations chunk by chunk; the first stage of the block
-                # waits for the chunk it is about to read.  While a step computes, the parameters and
-                # activations of the NEXT step of the same sequence of steps are already copied into the
-                # other set (a caller that streams a model's blocks through the GPU prefetches the same
-                # way); the first step of a sequence copies its own inputs, the last one prefetches nothing
-                # and waits for its results to reach the host, so every copy lies inside the timed region.
-                # Each subset's quantised weights go back to the host on a third stream while the next
-                # stage (or the next step) computes (the reference's block.cuda() / block.cpu()).
-                main_s = torch.cuda.current_stream()
-                copy_in.wait_stream(main_s)
-                block = copy.deepcopy(master)
-                if e2e_state['pending'] is None:
-                    e2e_state['pending'] = start_copies(e2e_state['buf'])
-                (p_ev, evs), buf = e2e_state['pending'], e2e_state['buf']
-                # the block's parameters cross PCIe once (rank 0) and reach the other ranks over NVLink
-                if rank == 0:
-                    main_s.wait_event(p_ev)
-                for i, p in enumerate(block.parameters()):
-                    if rank == 0:
-                        p.data.copy_(p_stages[buf][i], non_blocking=True)
-                    if world > 1:
-                        dist.broadcast(p.data, src=0)
-                x_stage = x_stages[buf]
-                e2e_state['steps_left'] -= 1
-                if e2e_state['steps_left'] > 0:
-                    e2e_state['buf'] = 1 - buf
-                    e2e_state['pending'] = start_copies(1 - buf)
-                else:
-                    e2e_state['pending'] = None
-                mods = dict(block.named_modules())
-
-                def on_input(i):
-                    if (i * bs) % chunk == 0:
-                        main_s.wait_event(evs[min(len(evs) - 1, (i * bs) // chunk)])
-                    if bs > chunk:
-                        main_s.wait_event(evs[min(len(evs) - 1, ((i + 1) * bs - 1) // chunk)])
-
-                def on_subset_done(names):
-                    done = torch.cuda.Event()
-                    done.record(main_s)
-                    copy_out.wait_event(done)
-                    with torch.cuda.stream(copy_out):
-                        # every rank holds the same quantised weights; each linear goes back to the host
-                        # from one rank only
-                        for nme in names:
-                            key = name_to_key[nme]
-                            if LINEAR_KEYS.index(key) % world == rank:
-                                w_host[key].copy_(mods[nme].weight, non_blocking=True)
-                runner.on_input, runner.on_subset_done = on_input, on_subset_done
-                outs = runner.block_opt(block, [x_stage[i:i + bs] for i in range(0, n_seq, bs)], kwargs)
-                runner.on_input = runner.on_subset_done = None
-                # the device-to-host copies of the last subset may still run while the next step starts; the
-                # block they read from stays referenced until then.  The last step of a sequence waits.
-                e2e_state['prev_block'] = block
-                if e2e_state['steps_left'] <= 0:
-                    main_s.wait_stream(copy_out)
-                    e2e_state['prev_block'] = None
-                return outs
-            h2d = int(X_host.numel() * 2 * world + sum(p.numel() * 2 for p in block_host.parameters()))   # whole job
-            d2h = int(sum(r * c * 4 for r, c in LINEAR_SHAPES))
-        # kernels of this library per step (torch's own kernels -- cuBLAS GEMMs of the forward, cuSOLVER
-        # potrf, SDPA, argsort, gathers -- are not counted):
+    def blocks_per_step_launches(n_calls):
+        # kernels of this library per decoder block (torch's own kernels -- cuBLAS GEMMs of the forward,
+        # cuSOLVER potrf, SDPA, argsort, gathers -- are not counted):
         #   Hessian launches, 4 diag; per distinct Hessian (3 x C=4096, 1 x C=11008): damp + permute,
         #   low-part split, leaf inverse, flip, and 5 launches (2 GEMMs, 2 splits, 1 transpose) per internal
         #   node of the recursive triangular inverse (C/128 - 1 nodes);
@@ -545,24 +762,152 @@ def main():
         #   per 128-column block the block kernel plus the eager / sub-panel / panel updates counted below;
         #   per linear the deploy-time fake quant;
         #   per sequence: 2 RMS norms, 2 rotary embeddings, 1 SiLU-gate.
-        n_calls = -(-n_seq // bs)
-
         def solver_launches(c):
-            # block kernels, eager FFMA updates (one per block that is not the last of its 256-column
-            # sub-panel), K = 256 GEMMs (one per sub-panel that is not the last of its panel), K = 1024 GEMMs
             blocks, subs, panels = -(-c // 128), -(-c // 256), -(-c // 1024)
             return blocks + (blocks - subs) + (subs - panels) + (panels - 1)
-        launches = (4 * -(-n_calls // HESSIAN_BATCH) + 4
-                    + sum(2 + 1 + 1 + 1 + 5 * (c // 128 - 1) for c in (HID, HID, HID, INTER))
-                    + sum(2 + solver_launches(c) for c in (HID, HID, HID, INTER)) + len(LINEAR_SHAPES)
-                    + 5 * n_calls)
+        return (4 * -(-n_calls // HESSIAN_BATCH) + 4
+                + sum(2 + 1 + 1 + 1 + 5 * (c // 128 - 1) for c in (HID, HID, HID, INTER))
+                + sum(2 + solver_launches(c) for c in (HID, HID, HID, INTER)) + len(LINEAR_SHAPES)
+                + 5 * n_calls)
+
+    def fresh_host_block(block_host):
+        """New module objects over the same (pinned) parameter storage: a step must not see the quantised
+        weights an earlier step left on the host copy."""
+        return copy.deepcopy(block_host, memo={id(p): torch.nn.Parameter(p.data, requires_grad=False)
+                                               for p in block_host.parameters()})
+
+    if args.workload == 'block':
+        X_host = make_activations(n_seq, 2001 + rank, pin=not args.no_e2e)
+        X = X_host.to(dev)
+        block_host, kwargs_host = make_block()
+        kwargs = kwargs_to(kwargs_host, dev)
+        master = copy.deepcopy(block_host).to(dev)
+        runner = lc.GPTQBlockwise(wq, SPECIAL, quant_out=True)
+        solver = runner.solver
+        phases = runner.phases
+        timer = HessianTimer(solver)
+        bs = max(1, min(args.calib_bs, n_seq))
+        inputs = [X[i:i + bs] for i in range(0, n_seq, bs)]
+        last = {}
+
+        def step():
+            block = copy.deepcopy(master)          # device copy of the bf16 block (the reference does block.cuda())
+            outs = runner.block_opt(block, inputs, kwargs)
+            last['block'] = block
+            return block, outs
+
+        if not args.no_e2e:
+            for p in block_host.parameters():
+                p.data = p.data.pin_memory()
+            stager = lc.HostStagedGPTQ(runner, dev, chunk=8)
+            host_inputs = [X_host[i:i + bs] for i in range(0, n_seq, bs)]
+            out_host = {n: torch.empty(rc, dtype=torch.float32).pin_memory()
+                        for n, rc in zip(LINEAR_NAMES, LINEAR_SHAPES) if LINEAR_NAMES.index(n) % world == rank}
+            e2e_state = {'steps_left': 0, 'next': None}
+
+            def e2e_step():
+                # One block from host memory through lightcompress_b200.HostStagedGPTQ: parameters and
+                # activations cross PCIe on a copy stream (the first stage waits chunk by chunk), the
+                # quantised weights return on another stream while the next stage computes.  Within a
+                # sequence of steps the parameters and activations of step s+1 are prefetched while step s
+                # computes (a caller that streams a model's blocks through the GPU does the same); the first
+                # step copies its own inputs, the last one prefetches nothing and waits for its results on
+                # the host, so every copy lies inside the timed region.
+                blk = e2e_state['next'] or fresh_host_block(block_host)
+                e2e_state['steps_left'] -= 1
+                nxt = None
+                if e2e_state['steps_left'] > 0:
+                    nxt = fresh_host_block(block_host)
+                e2e_state['next'] = nxt
+                xs = e2e_state.get('xs') or list(host_inputs)
+                nxt_xs = list(host_inputs) if nxt is not None else None
+                e2e_state['xs'] = nxt_xs
+                return stager.block_opt(blk, xs, kwargs, next_block_host=nxt, wait_results=nxt is None,
+                                        out_host=out_host, next_inputs=nxt_xs)
+            h2d = int(X_host.numel() * 2 * world + sum(p.numel() * 2 for p in block_host.parameters()))   # whole job
+            d2h = int(sum(r * c * 4 for r, c in LINEAR_SHAPES))
+        launches = blocks_per_step_launches(-(-n_seq // bs))
+
+        def parity_fn():
+            blk = last['block']
+            q = blk.self_attn.q_proj
+            xs = [block_ops.rms_norm(master.input_layernorm, x) for x in inputs]
+            return dict(parity_of_linear(master.self_attn.q_proj.weight.data, xs, q._lc_codes[0], q.buf_perm,
+                                         q.tmp_weight, world, dev), linear='self_attn.q_proj (4096x4096)')
+
+        def checksum_fn():
+            blk = last['block']
+            return torch.stack([getattr(p, a).tmp_weight.float().sum() for s in lc.llama_subsets(blk)
+                                for p, a in s.values()])
+    elif args.workload == 'model':
+        from transformers import LlamaConfig
+        from transformers.models.llama.modeling_llama import LlamaDecoderLayer
+        n_layers = args.layers
+        cfg = LlamaConfig(hidden_size=HID, intermediate_size=INTER, num_attention_heads=HEADS,
+                          num_key_value_heads=HEADS, num_hidden_layers=n_layers, vocab_size=32000,
+                          max_position_embeddings=4096, rms_norm_eps=1e-5)
+        cfg._attn_implementation = 'sdpa'
+        _, kwargs_host = make_block()
+        kwargs = kwargs_to(kwargs_host, dev)
+        # random-init weights N(0, 0.02^2) drawn on the GPU (seed per layer, the same on every rank) and
+        # kept in pinned host memory like the reference's CPU-resident model; token ids uniform in the vocab
+        template = LlamaDecoderLayer(cfg, 0).to(torch.bfloat16)
+        blocks_host = []
+        for li in range(n_layers):
+            gg = torch.Generator(device=dev).manual_seed(7000 + li)
+            blk = copy.deepcopy(template)
+            for p in blk.parameters():
+                d = (torch.randn(p.shape, generator=gg, device=dev) * 0.02).to(torch.bfloat16) if p.dim() == 2 \
+                    else torch.ones(p.shape, dtype=torch.bfloat16, device=dev)
+                h = torch.empty(p.shape, dtype=torch.bfloat16).pin_memory()
+                h.copy_(d)
+                p.data = h
+            blocks_host.append(blk)
+        gg = torch.Generator(device=dev).manual_seed(6999)
+        embed_host = (torch.randn(32000, HID, generator=gg, device=dev) * 0.02).to(torch.bfloat16).cpu().pin_memory()
+        gi = torch.Generator().manual_seed(4001)
+        ids_host = torch.randint(0, 32000, (NS, T), generator=gi)[s0:s1].pin_memory()
+        out_pool = [{n: torch.empty(rc, dtype=torch.float32).pin_memory()
+                     for n, rc in zip(LINEAR_NAMES, LINEAR_SHAPES) if LINEAR_NAMES.index(n) % world == rank}
+                    for _ in range(n_layers)]
+        runner = lc.GPTQBlockwise(wq, SPECIAL, quant_out=True)
+        solver = runner.solver
+        phases = runner.phases
+        timer = HessianTimer(solver)
+        stager = lc.HostStagedGPTQ(runner, dev, chunk=8)
+        per_block = []
+
+        def model_step():
+            """Token ids and the embedding table from pinned host memory -> hidden states -> run_block_loop over
+            all layers, every block streamed from and back to the host copy (llmc/__main__.py:55-70)."""
+            fresh = [fresh_host_block(b) for b in blocks_host]
+            emb = embed_host.to(dev, non_blocking=True)
+            ids = ids_host.to(dev, non_blocking=True)
+            xs = [torch.nn.functional.embedding(ids[i:i + 1], emb) for i in range(n_seq)]
+            del emb
+            outs, secs = stager.run_block_loop(fresh, xs, kwargs, out_host=out_pool)
+            per_block[:] = secs
+            return outs
+        step = e2e_step = model_step
+        h2d = int(ids_host.numel() * 8 * world + embed_host.numel() * 2 * world
+                  + n_layers * sum(p.numel() * 2 for p in template.parameters()))
+        d2h = int(n_layers * sum(r * c * 4 for r, c in LINEAR_SHAPES))
+        launches = n_layers * blocks_per_step_launches(n_seq)
+        extra_cfg = {'layers': n_layers, 'inputs': 'token ids + embedding table in pinned host memory'}
+        WORKLOADS['model'] = (f'random-init {n_layers}-layer Llama-2-7B-shape model (hidden 4096, 32 heads, MLP 11008, '
+                              'vocab 32000, bf16 N(0,0.02^2)) in host memory, GPTQ W4A16 asym g128, act_order, '
+                              'true_sequential, quant_out; 128x2048 token ids uniform in the vocab; every block '
+                              'streamed through the GPU')
     else:
+        X_host = make_activations(n_seq, 2001 + rank, pin=not args.no_e2e)
+        X = X_host.to(dev)
         W_host = make_linear_weight().pin_memory() if not args.no_e2e else make_linear_weight()
         W = W_host.to(dev)
         solver = lc.GPTQ(wq, SPECIAL)
         timer = HessianTimer(solver)
         layer = torch.nn.Linear(HID, HID, bias=False, dtype=torch.bfloat16, device=dev)
         r0, r1 = parallel.row_shard(HID)
+        last = {}
 
         def run_layer(x_dev, w):
             layer.weight.data = w
@@ -572,6 +917,7 @@ def main():
             res = solver.layer_transform(layer, 'l', rows=None if world == 1 else (r0, r1))
             out = res['weight'] if world == 1 else parallel.gather_rows(res['weight'], HID)
             solver.free('l')
+            last['res'] = res
             return out, res
 
         def step():
@@ -606,9 +952,23 @@ def main():
                 sc_host.copy_(res['buf_scales'], non_blocking=True)
                 zr_host.copy_(res['buf_zeros'], non_blocking=True)
                 solver.free('l')
-            h2d = int(X_host.numel() * 2 + W_host.numel() * 2)
-            d2h = int(out_host.numel() * 4 + sc_host.numel() * 8)
+                torch.cuda.current_stream().synchronize()      # the step's result is on the host
+            h2d = int(X_host.numel() * 2 * world + W_host.numel() * 2 * world)
+            d2h = int(HID * HID * 4 + HID * (HID // 128) * 8)
         launches = -(-n_seq // HESSIAN_BATCH) + 1 + 3 + 1 + 2 * (HID // 128) - 1 + 1
+
+        def parity_fn():
+            if world > 1:
+                return None                      # rows are sharded here; the block workload covers N > 1
+            res = last['res']
+            lin = torch.nn.Linear(HID, HID, bias=False, dtype=torch.bfloat16, device=dev)
+            lin.weight.data = res['weight']
+            for k in ('buf_scales', 'buf_zeros', 'buf_perm', 'buf_invperm'):
+                lin.register_buffer(k, res[k])
+            lin.register_buffer('buf_qmax', wq.qmax.to(dev))
+            lin.register_buffer('buf_qmin', wq.qmin.to(dev))
+            return dict(parity_of_linear(W, [X[i:i + 1] for i in range(n_seq)], res['codes_perm'], res['buf_perm'],
+                                         solver.w_qdq(lin, wq), world, dev), linear='the 4096x4096 layer')
 
     def sync_all():
         torch.cuda.synchronize()
@@ -629,19 +989,32 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    # ---- device-resident throughput ------------------------------------------------------------
+    # ---- device-resident throughput (model workload: the same host-staged loop, it has no other form) ----
     for _ in range(args.warmup):
         step()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     timer.on = True
+    if phases is not None:
+        phases.spans = []
+        phases.on = True
     ms_step = timed(step, args.steps) / args.steps
     timer.on = False
-    value = 1e3 / ms_step
+    phase_ms = None
+    if phases is not None:
+        phases.on = False
+        phase_ms = {k: v / args.steps for k, v in phases.summary().items()}
+        phase_ms['other (host waits, copies of the block, residual)'] = ms_step - sum(phase_ms.values())
+    value = (args.layers if args.workload == 'model' else 1) * 1e3 / ms_step
     hess = timer.summary()
 
     # ---- end to end: host buffers in, host result out ------------------------------------------
     e2e = None
-    if not args.no_e2e:
+    if args.workload == 'model':
+        e2e = {'value': value, 'unit': UNIT, 'ms_per_step': ms_step, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+               'overlap': 'the model loop is host-staged by construction: value and e2e are the same measurement',
+               'per_block_s': {'first': per_block[0], 'median': sorted(per_block)[len(per_block) // 2],
+                               'last': per_block[-1]}}
+    elif not args.no_e2e:
         if args.workload == 'block':
             e2e_state['steps_left'] = 2
         for _ in range(2):
@@ -651,11 +1024,26 @@ def main():
         e2e_ms = timed(e2e_step, args.steps) / args.steps
         e2e = {'value': 1e3 / e2e_ms, 'unit': UNIT, 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': h2d,
                'd2h_bytes_per_step': d2h,
+               'api': 'lightcompress_b200.HostStagedGPTQ.block_opt' if args.workload == 'block' else 'lightcompress_b200.GPTQ',
                'overlap': ('copies on side streams; the parameters and activations of step s+1 are prefetched into '
                            'a second set of staging buffers while step s computes (not for the first step, none '
                            'after the last, which also waits for its results on the host: all copies lie inside '
                            'the timed region)') if args.workload == 'block' else 'none'}
     clocks = sampler.stop() if sampler else None
+
+    # ---- parity of what was just timed, and agreement of the ranks ---------------------------------
+    parity = None
+    if not args.no_parity and args.workload in ('block', 'layer'):
+        if args.workload == 'block':
+            step()
+        parity = parity_fn()
+        if world > 1 and checksum_fn is not None:
+            cs = checksum_fn()
+            lo, hi = cs.clone(), cs.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            parity['ranks_agree'] = bool(torch.equal(lo, hi))
+            parity['ranks_checksum'] = 'sum of every deployed linear weight, min == max over the ranks'
 
     # ---- the other two headline kernels, timed alone (HBM-bound family 1) ----------------------
     aux = None
@@ -668,49 +1056,66 @@ def main():
         return
 
     # ---- roofline of the dominant kernel of ours: the Hessian GEMM -------------------------------
-    # algorithmic FLOPs = 2 * tokens * C^2 per launch (the full square the reference computes);
-    # executed = the 256x256 tiles on/above the diagonal that are actually issued
+    # executed FLOPs = the 256x256 tiles on/above the diagonal that are actually issued (the kernel mirrors
+    # them); algorithmic = 2 * tokens * C^2 per launch, the full square the reference computes
     n_l = sum(d[0] for d in hess.values())
     ms_l = sum(d[1] for d in hess.values())
     alg = sum(2.0 * d[2] * c * c for c, d in hess.items())
     exe = sum(2.0 * d[2] * 256 * 256 * n_super(c) for c, d in hess.items())
-    achieved = alg / (ms_l * 1e-3) / 1e12
+    achieved = exe / (ms_l * 1e-3) / 1e12
     roofline = {'bound': 'tensor', 'kernel': 'hessian_umma_kernel', 'achieved': achieved, 'peak': tf_sust,
                 'unit': 'TFLOP/s', 'frac': achieved / tf_sust,
+                'basis': 'executed FLOPs (tiles on and above the diagonal; the rest is mirrored)',
                 'peak_kind': f'{peak_kind} sustained cuBLAS bf16 (of measured)',
-                'achieved_executed': exe / (ms_l * 1e-3) / 1e12, 'frac_executed': exe / (ms_l * 1e-3) / 1e12 / tf_sust,
+                'achieved_algorithmic': alg / (ms_l * 1e-3) / 1e12,
                 'launch_ms': ms_l / n_l, 'launches_per_step': n_l / args.steps,
                 'share_of_step': ms_l / args.steps / ms_step,
                 'per_cols': {str(c): {'launches_per_step': d[0] / args.steps, 'launch_ms': d[1] / d[0],
                                       'tokens_per_launch': d[2] / d[0]} for c, d in hess.items()},
                 'traffic': None}
-    # DRAM bytes per 16384-token launch from the ncu captures summarised under profiles/ (Hessian kernel)
-    # (dram__bytes_read.sum + dram__bytes_write.sum); the bench launches the same shapes
-    ncu_traffic = {4096: 213.7e6, 11008: 2833.0e6}
+    # DRAM bytes per 16384-token launch: static figures from the ncu captures summarised under profiles/
+    # (dram__bytes_read.sum + dram__bytes_write.sum of the same launch shapes), not measured in this run
+    ncu_traffic = HESSIAN_NCU_TRAFFIC
     if all(c in ncu_traffic and abs(d[2] / d[0] - 16384) < 1 for c, d in hess.items()):
         roofline['traffic'] = sum(d[0] * ncu_traffic[c] for c, d in hess.items()) / n_l
-        roofline['traffic_source'] = 'ncu, per launch, weighted over the launch mix of the step'
+        roofline['traffic_source'] = ('static: profiles/hessian_umma_C4096.md (ncu, per launch), weighted over the '
+                                      'launch mix of the step')
         roofline['algorithmic_bytes'] = sum(d[0] * (2.0 * 16384 * c + 8.0 * c * c) for c, d in hess.items()) / n_l
 
     line = {'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'bf16 in / fp32 accumulate', 'data': 'synthetic',
-            'config': {'workload': WORKLOADS[args.workload], 'name': args.workload,
-                       'l2': 'inputs (2.1 GB of activations per step) exceed the 126 MB L2',
-                       'sharding': f'{n_seq} sequences per rank; solve units (linear, row range) dealt to the ranks',
-                       'hessian_batch': HESSIAN_BATCH, 'calib_bs': args.calib_bs if args.workload == 'block' else 1,
-                       'static_groups': bool(SPECIAL['static_groups'])},
+            'config': dict({'workload': WORKLOADS[args.workload], 'name': args.workload,
+                            'l2': 'inputs (2.1 GB of activations per step) exceed the 126 MB L2',
+                            'sharding': f'{n_seq} sequences per rank; solve units (row ranges of a subset) dealt to the ranks',
+                            'hessian_batch': HESSIAN_BATCH, 'calib_bs': args.calib_bs if args.workload == 'block' else 1,
+                            'static_groups': bool(SPECIAL['static_groups'])}, **extra_cfg),
             'roofline': roofline, 'gpu_launches': launches * args.steps, 'clocks': clocks}
+    if phase_ms:
+        line['phases_ms'] = phase_ms
     if e2e:
         line['e2e'] = e2e
+    if parity:
+        line['parity'] = parity
+    if args.workload in ('block', 'model'):
+        line['fused_op_rejections'] = block_ops.rejected() + [('stage_plan', c) for c in runner.stage_plan_rejected]
     if aux:
         line['aux_kernels'] = aux
     if not args.no_cpu_baseline and world == 1:
-        v, desc, cores, parts = (cpu_port_block() if args.workload == 'block' else cpu_port_layer(8))
-        line['cpu_baseline'] = dict({'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc}, **parts)
+        if args.workload == 'layer':
+            v, desc, cores, parts = cpu_port_layer(8)
+        else:
+            v, desc, cores, parts, _ = cpu_port_block()
+        line['cpu_baseline'] = dict({'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': desc,
+                                     'extrapolated': True}, **parts)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if line.get('fused_op_rejections'):
+        raise SystemExit('a fused block op or the staged plan was rejected by its self-check: ' +
+                         str(line['fused_op_rejections']))
+    if parity and (parity['code_mismatch'] >= 1e-3 or parity['recon_rel_diff'] >= 1e-2 or parity.get('ranks_agree') is False):
+        raise SystemExit('parity of the timed configuration is outside its bars: ' + json.dumps(parity))
 
 
 if __name__ == '__main__':

@@ -412,6 +412,9 @@ int lc_gptq_weight_transform_tc_static(float* W, const float* U, const float* U_
  *     Nothing in it needs to start at zero (each 128-column block overwrites it completely
  *     before reading it), but two calls whose kernels overlap on the GPU -- different streams,
  *     or different host threads -- race on it: serialise them.
+ *   - The cached address belongs to the CUDA context that was current at that first call.  After
+ *     a cudaDeviceReset, or from a second context on the same device ordinal, it is stale: such
+ *     processes must not use this entry point.
  * Results are identical to lc_gptq_weight_transform. */
 int lc_gptq_weight_transform_noalloc(float* W, const float* U, int64_t rows, int64_t cols, int bits,
                                      int sym, float* scales, float* zeros, uint8_t* codes_u8,

@@ -9,5 +9,6 @@ from .gptq import GPTQ  # noqa: F401
 from .rtn import RTN  # noqa: F401
 from .awq import Awq  # noqa: F401
 from .blockwise import GPTQBlockwise, FakeQuantLinear, llama_subsets  # noqa: F401
+from .streaming import HostStagedGPTQ  # noqa: F401
 
-__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'Weight48IntegerQuantizer', 'GPTQ', 'RTN', 'Awq', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets']
+__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'Weight48IntegerQuantizer', 'GPTQ', 'RTN', 'Awq', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets', 'HostStagedGPTQ']

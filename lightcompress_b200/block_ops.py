@@ -21,6 +21,14 @@ _DTYPES = (torch.bfloat16, torch.float16, torch.float32)
 _checked = {}
 
 
+def rejected():
+    """The self-checks that failed so far, i.e. the module kinds for which the stock tensor ops were kept
+    because the fused kernel did not reproduce them bit for bit: [(kind, detail), ...].  Empty on the
+    Llama block this library is built for; a benchmark or a caller that expects the fused path reads this
+    instead of guessing."""
+    return [(k[0], str(k[1])) for k, ok in _checked.items() if not ok]
+
+
 def rope_apply_one(x, cos, sin):
     """x: (B, H, T, D) view of a (B, T, H, D) contiguous tensor; cos, sin: (B, T, D) or (1, T, D)
     contiguous.  Returns the embedded tensor with x's shape and memory layout."""

@@ -83,6 +83,37 @@ def is_llama_layout(block):
             and all(hasattr(m, k) for k in ('gate_proj', 'up_proj', 'down_proj', 'act_fn')))
 
 
+class PhaseTimer:
+    """Optional split of a block step into its phases, by CUDA events on the launching stream.  A phase's
+    time is the span between its first and last kernel on the device timeline, so time the device spends
+    waiting for the host between phases shows up as the remainder of the step, not inside a phase."""
+
+    def __init__(self):
+        self.on = False
+        self.spans = []
+
+    @contextlib.contextmanager
+    def __call__(self, name):
+        if not self.on:
+            yield
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        try:
+            yield
+        finally:
+            e1.record()
+            self.spans.append((name, e0, e1))
+
+    def summary(self):
+        """{phase: total ms}; call after a device synchronisation.  Clears the record."""
+        out = {}
+        for name, e0, e1 in self.spans:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        self.spans = []
+        return out
+
+
 class _StopForward(Exception):
     """Raised by a Hessian hook once the tensor it needs has been seen (see early_exit)."""
 
@@ -106,6 +137,7 @@ class GPTQBlockwise:
         # block classes whose staged forward did not reproduce the block's own forward (they run the
         # generic re-forwarding schedule): visible to callers, nothing is skipped silently
         self.stage_plan_rejected = []
+        self.phases = PhaseTimer()
         self.true_sequential = self.solver.true_sequential
         # A re-forward whose only purpose is to feed the hooks of one subset stops as soon as that
         # subset's input has been seen: the rest of the block computes values nobody reads.
@@ -172,7 +204,8 @@ class GPTQBlockwise:
         rank, world = parallel.world()
         names = list(subset)
         layers = [getattr(*subset[n]) for n in names]
-        H, hscale = self.solver._finish_hessian(names[0])
+        with self.phases('hessian_reduce'):
+            H, hscale = self.solver._finish_hessian(names[0])
         # owq: linears with different outlier counts order the columns differently; each count gets its
         # own factor (the reference's n_outs are equal within every Llama subset: one factor as usual)
         by_n_out = OrderedDict()
@@ -186,7 +219,8 @@ class GPTQBlockwise:
             self.on_subset_done(names)
 
     def _solve_group(self, layers, H, hscale, n_out, rank, world):
-        fac = self.solver.factorize(H, hscale, n_out=n_out)       # shared by the linears of the group
+        with self.phases('factorize'):
+            fac = self.solver.factorize(H, hscale, n_out=n_out)   # shared by the linears of the group
         # The rows of all linears of a subset are independent given the shared factor: they are solved
         # as one stacked matrix (q/k/v: 12288 rows, gate/up: 22016), which cuts the number of latency-bound
         # 128-column steps by the number of linears; in a process group every rank takes a row range.
@@ -198,7 +232,8 @@ class GPTQBlockwise:
             static = (torch.cat([p[0] for p in parts], 0),
                       None if parts[0][1] is None else torch.cat([p[1] for p in parts], 0))
         if world == 1:
-            res = self.solver.solve(stacked, H, hscale, factor=fac, static=static)
+            with self.phases('solve'):
+                res = self.solver.solve(stacked, H, hscale, factor=fac, static=static)
         else:
             res = self._sharded_solve(stacked, fac, rank, world, static)
         n_groups = res['buf_scales'].shape[0] // stacked.shape[0]      # qparams per row (1 for per_channel)
@@ -228,7 +263,8 @@ class GPTQBlockwise:
         blocks = (R + 127) // 128
         bounds = [min(R, 128 * ((blocks * r) // world)) for r in range(world)] + [R]
         a, b = bounds[rank], bounds[rank + 1]
-        mine = self.solver.solve(stacked, H, rows=(a, b), factor=fac, static=static) if b > a else None
+        with self.phases('solve'):
+            mine = self.solver.solve(stacked, H, rows=(a, b), factor=fac, static=static) if b > a else None
         # packed row: C weight floats, then (unless static: the qparams are inputs every rank holds)
         # n_groups scales and n_groups zeros, then the uint8 codes viewed as C / 4 floats
         with_codes = C % 4 == 0 and bool(self.solver.emit_codes)      # the same on every rank
@@ -237,6 +273,13 @@ class GPTQBlockwise:
         off_c = off_z + (0 if sym else n_q)
         row_len = off_c + (C // 4 if with_codes else 0)
         max_rows = max(bounds[r + 1] - bounds[r] for r in range(world))
+        with self.phases('gather'):
+            return self._gather_solved(mine, bounds, rank, world, R, C, n_q, sym, off_s, off_z, off_c, row_len,
+                                       max_rows, with_codes, static, fac, dev)
+
+    def _gather_solved(self, mine, bounds, rank, world, R, C, n_q, sym, off_s, off_z, off_c, row_len, max_rows,
+                       with_codes, static, fac, dev):
+        a, b = bounds[rank], bounds[rank + 1]
         packed = torch.empty((world, max_rows, row_len), dtype=torch.float32, device=dev)
         slot = packed[rank]
         if mine is not None:
@@ -367,11 +410,12 @@ class GPTQBlockwise:
 
         name, layer = self._init_subset(subsets[0])
         normed = []
-        for i, x in enumerate(inputs):
-            if self.on_input is not None:
-                self.on_input(i)
-            normed.append(norm(block.input_layernorm, x))
-            self.solver.add_batch(layer, name, normed[-1], None)
+        with self.phases('forward_hessian'):
+            for i, x in enumerate(inputs):
+                if self.on_input is not None:
+                    self.on_input(i)
+                normed.append(norm(block.input_layernorm, x))
+                self.solver.add_batch(layer, name, normed[-1], None)
         self.subset_transform(subsets[0])
         self._replace(subsets[0])
 
@@ -385,7 +429,7 @@ class GPTQBlockwise:
         ctx = []
         rotary = (block_ops.fused_rotary(a, normed[0].device, normed[0].dtype) if self.fused_block_ops
                   else contextlib.nullcontext())
-        with rotary:
+        with rotary, self.phases('forward_hessian'):
             for i in range(n):
                 try:
                     a(hidden_states=normed[i], **kw(i))
@@ -400,33 +444,36 @@ class GPTQBlockwise:
 
         name, layer = self._init_subset(subsets[2])
         resid, normed = [], []
-        for i, x in enumerate(inputs):
-            h = x + a.o_proj(ctx[i])
-            ctx[i] = None
-            resid.append(h)
-            normed.append(norm(block.post_attention_layernorm, h))
-            self.solver.add_batch(layer, name, normed[-1], None)
+        with self.phases('forward_hessian'):
+            for i, x in enumerate(inputs):
+                h = x + a.o_proj(ctx[i])
+                ctx[i] = None
+                resid.append(h)
+                normed.append(norm(block.post_attention_layernorm, h))
+                self.solver.add_batch(layer, name, normed[-1], None)
         self.subset_transform(subsets[2])
         self._replace(subsets[2])
 
         name, layer = self._init_subset(subsets[3])
         prod = []
-        for i in range(n):
-            y = normed[i]
-            normed[i] = None
-            if self.fused_block_ops:
-                prod.append(block_ops.gated_act(m.act_fn, m.gate_proj(y), m.up_proj(y)))
-            else:
-                prod.append(m.act_fn(m.gate_proj(y)) * m.up_proj(y))
-            self.solver.add_batch(layer, name, prod[-1], None)
+        with self.phases('forward_hessian'):
+            for i in range(n):
+                y = normed[i]
+                normed[i] = None
+                if self.fused_block_ops:
+                    prod.append(block_ops.gated_act(m.act_fn, m.gate_proj(y), m.up_proj(y)))
+                else:
+                    prod.append(m.act_fn(m.gate_proj(y)) * m.up_proj(y))
+                self.solver.add_batch(layer, name, prod[-1], None)
         self.subset_transform(subsets[3])
         self._replace(subsets[3])
 
         outs = []
-        for i in range(n):
-            outs.append(resid[i] + m.down_proj(prod[i]))
-            prod[i] = None
-            resid[i] = None
+        with self.phases('forward_hessian'):
+            for i in range(n):
+                outs.append(resid[i] + m.down_proj(prod[i]))
+                prod[i] = None
+                resid[i] = None
         self.solver.check_status()
         return outs
 

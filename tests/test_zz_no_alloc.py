@@ -36,7 +36,10 @@ def test_noalloc_matches_scratch_variant_on_consecutive_calls():
     from lightcompress_b200 import _lib as L
     # two different problems back to back: the second call finds the first one's leftovers in the
     # shared scratch array (and, being smaller, does not even overwrite all of them)
-    for seed, R, C, sym in ((11, 320, 512, 0), (12, 96, 384, 1)):
+    # the third one is ragged both ways (rows % 4 != 0 takes the scalar trailing kernel, cols % 128 != 0 the
+    # warp-per-row block kernel) and runs against the leftovers of the two larger ones
+    free_before = None
+    for seed, R, C, sym in ((11, 320, 512, 0), (12, 96, 384, 1), (13, 51, 328, 0)):
         W0, U = _problem(seed, R, C)
         Wa, Wb = W0.clone(), W0.clone()
         oa, ob = _outputs(R, C), _outputs(R, C)
@@ -50,6 +53,13 @@ def test_noalloc_matches_scratch_variant_on_consecutive_calls():
                L.ptr(ob['zeros']), L.ptr(ob['codes']), L.ptr(ob['loss']), stream)
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
+        # the torch counter above only sees torch's allocator; the driver's free-memory figure would also
+        # show a cudaMalloc made inside the library (compared from the second problem on: the first call
+        # on a device may load the module that holds the scratch array)
+        free_now = torch.cuda.mem_get_info()[0]
+        if free_before is not None:
+            assert free_now == free_before
+        free_before = free_now
         # same kernels, same order of operations: the tolerance the solver tests use for codes
         # (< 0.1 % mismatches) is met with room to spare -- the results are in fact identical
         assert float((oa['codes'] != ob['codes']).float().mean()) < 1e-3
@@ -67,3 +77,23 @@ def test_noalloc_rejects_layers_beyond_its_scratch():
                                                 L.ptr(dummy), None, None, None)
     assert rc == L.LC_ERR_WORKSPACE
     assert 'workspace' in L.status_string(rc)
+
+
+def test_noalloc_accepts_a_layer_at_its_limit():
+    """16384 rows is the largest layer the built-in scratch holds: accepted, and equal to the scratch-taking
+    entry point."""
+    from lightcompress_b200 import _lib as L
+    R, C = 16384, 128
+    g = torch.Generator().manual_seed(14)
+    W0 = (torch.randn(R, C, generator=g) * 0.02).cuda()
+    _, U = _problem(14, 8, C)
+    Wa, Wb = W0.clone(), W0.clone()
+    oa, ob = _outputs(R, C), _outputs(R, C)
+    err = torch.empty(128, R, device='cuda')
+    stream = L.stream_of(W0)
+    L.call('lc_gptq_weight_transform', L.ptr(Wa), L.ptr(U), R, C, 4, 0, L.ptr(err), L.ptr(oa['scales']),
+           L.ptr(oa['zeros']), L.ptr(oa['codes']), L.ptr(oa['loss']), stream)
+    L.call('lc_gptq_weight_transform_noalloc', L.ptr(Wb), L.ptr(U), R, C, 4, 0, L.ptr(ob['scales']),
+           L.ptr(ob['zeros']), L.ptr(ob['codes']), L.ptr(ob['loss']), stream)
+    torch.cuda.synchronize()
+    assert torch.equal(oa['codes'], ob['codes']) and torch.equal(Wa, Wb)
