@@ -138,6 +138,10 @@ class GPTQBlockwise:
         # generic re-forwarding schedule): visible to callers, nothing is skipped silently
         self.stage_plan_rejected = []
         self.phases = PhaseTimer()
+        # {first linear of a subset: column order}: fixes the act-order permutation of that subset instead
+        # of argsort(diag H), whose order among near-equal entries is implementation-defined (gptq.py:63
+        # uses an unstable sort).  For reproducing an earlier run or comparing two implementations.
+        self.pinned_perms = dict(special.get('pinned_perms') or {})
         self.true_sequential = self.solver.true_sequential
         # A re-forward whose only purpose is to feed the hooks of one subset stops as soon as that
         # subset's input has been seen: the rest of the block computes values nobody reads.
@@ -212,15 +216,15 @@ class GPTQBlockwise:
         for layer, n in zip(layers, names):
             by_n_out.setdefault(self.solver.n_out_of(n), []).append(layer)
         for n_out, group in by_n_out.items():
-            self._solve_group(group, H, hscale, n_out, rank, world)
+            self._solve_group(group, H, hscale, n_out, rank, world, self.pinned_perms.get(names[0]))
         for n in names:
             self.solver.layers_cache.pop(n, None)
         if self.on_subset_done is not None:
             self.on_subset_done(names)
 
-    def _solve_group(self, layers, H, hscale, n_out, rank, world):
+    def _solve_group(self, layers, H, hscale, n_out, rank, world, perm=None):
         with self.phases('factorize'):
-            fac = self.solver.factorize(H, hscale, n_out=n_out)   # shared by the linears of the group
+            fac = self.solver.factorize(H, hscale, perm=perm, n_out=n_out)   # shared by the linears of the group
         # The rows of all linears of a subset are independent given the shared factor: they are solved
         # as one stacked matrix (q/k/v: 12288 rows, gate/up: 22016), which cuts the number of latency-bound
         # 128-column steps by the number of linears; in a process group every rank takes a row range.

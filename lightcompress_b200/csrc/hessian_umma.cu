@@ -26,6 +26,7 @@ namespace {
 
 constexpr int ST = 256;        // super-tile edge
 constexpr int BK = 32;         // tokens per pipeline stage
+constexpr int kMaxAccumTokens = 8192;   // most tokens one work item accumulates in the tensor core (see hessian_launch)
 constexpr int UMMA_K = 16;     // bf16
 constexpr int STAGES = 6;
 constexpr int ATOM = 64;       // channels per 128-byte swizzle row
@@ -417,24 +418,22 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
   a.tail_begin = a.n_super;
   a.tail_split = 1;
   if (ksplit == 0) {
-    // Enough super-tiles to occupy the SMs: no token split (one epilogue per super-tile).
-    // Otherwise split the token range so that about one item lands on every SM.
-    ksplit = 1;
-    if (a.n_super * 2 <= sms) {
-      ksplit = sms / a.n_super;
+    // The tensor core adds every MMA's products into the fp32 accumulator with truncation, so a sum loses
+    // about 2^-24 of its value per 16-token MMA step: a relative deficit that grows with the number of
+    // tokens one work item accumulates (measured: -5.6e-5 over 16384 tokens, -2.7e-5 over 8192), uniform
+    // over the matrix as long as every item accumulates the same number of tokens.  The uniform part does
+    // not change the GPTQ solve (act-order, dampening and the ratios of U all scale together); the spread
+    // around it does (it reorders near-equal diagonal entries), and it shrinks with the item length too.
+    // So the token range of a launch is cut into equal parts of at most kMaxAccumTokens, every super-tile
+    // the same way (no uneven split of a tail wave), and the parts are combined by fp32 atomic adds.
+    ksplit = (a.k_total * BK + kMaxAccumTokens - 1) / kMaxAccumTokens;
+    if (ksplit < 1) ksplit = 1;
+    // Few super-tiles: split further so that about one item lands on every SM.
+    if (a.n_super * ksplit * 2 <= sms) {
+      int fill = sms / a.n_super;
       const int max_split = a.k_total / 8 > 0 ? a.k_total / 8 : 1;
-      if (ksplit > max_split) ksplit = max_split;
-    } else if (a.n_super > sms && a.n_super % sms != 0) {
-      // Several waves of whole super-tiles and a partial last one (C = 11008: 946 tiles = 6.4 waves of
-      // 148): the tail's tiles are cut in token ranges so that the last wave is a fraction of a tile long.
-      const int tail = a.n_super % sms;
-      int split = sms / tail;
-      if (split > 8) split = 8;
-      if (split > a.k_total / 8) split = a.k_total / 8;
-      if (split > 1) {
-        a.tail_begin = a.n_super - tail;
-        a.tail_split = split;
-      }
+      if (fill > max_split) fill = max_split;
+      if (fill > ksplit) ksplit = fill;
     }
   }
   if (ksplit > a.k_total) ksplit = a.k_total;

@@ -46,6 +46,7 @@ class HostStagedGPTQ:
         self._pending = None               # (slot, key, param event) of a prefetched block
         self._keep = None                  # device block whose device-to-host copies may still run
         self._pending_x = {}               # id of a prefetched input list -> (staged tensors, events)
+        self._xbuf, self._xsig, self._xslot = [None, None], [None, None], 0    # input staging sets
 
     # ---- parameters ----------------------------------------------------------------------------
     def _layout(self, block_host):
@@ -110,24 +111,34 @@ class HostStagedGPTQ:
 
     # ---- inputs ----------------------------------------------------------------------------------
     def _stage_inputs(self, inputs):
-        """inputs: list of tensors.  Host tensors are copied on the copy stream in groups of `chunk`;
+        """inputs: list of tensors.  Host tensors are copied on the copy stream, in groups of `chunk`, into
+        one of two persistent sets of staging tensors (allocated on first use, kept until release());
         returns (device tensors, events per tensor index or None)."""
         if all(t.is_cuda for t in inputs):
             return list(inputs), None
         main = torch.cuda.current_stream(self.dev)
-        out, evs = [], []
+        k = self._xslot = 1 - self._xslot
+        sig = [(tuple(t.shape), t.dtype) for t in inputs]
+        if self._xbuf[k] is None or self._xsig[k] != sig:
+            self._xbuf[k] = [torch.empty(sh, dtype=dt, device=self.dev) for sh, dt in sig]
+            self._xsig[k] = sig
+        # the set's previous readers (the block before last) were enqueued on the compute stream earlier
+        self.copy_in.wait_stream(main)
+        out, evs = self._xbuf[k], []
         with torch.cuda.stream(self.copy_in):
             for i, t in enumerate(inputs):
-                d = torch.empty(t.shape, dtype=t.dtype, device=self.dev)
-                d.copy_(t, non_blocking=_is_pinned(t))
-                out.append(d)
+                out[i].copy_(t, non_blocking=_is_pinned(t))
                 if (i + 1) % self.chunk == 0 or i + 1 == len(inputs):
                     ev = torch.cuda.Event()
                     ev.record(self.copy_in)
                     evs.extend([ev] * (i + 1 - len(evs)))
-        for d in out:
-            d.record_stream(main)
-        return out, evs
+        return list(out), evs
+
+    def release(self):
+        """Frees the staging buffers (inputs and parameters)."""
+        self.finish()
+        self._xbuf, self._xsig, self._flat = [None, None], [None, None], [None, None]
+        self._pending, self._pending_x = None, {}
 
     def prefetch_inputs(self, inputs):
         """Starts copying host inputs that a later `block_opt` call will be given (the same list object)."""

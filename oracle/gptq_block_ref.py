@@ -43,9 +43,11 @@ def _forward(block, inputs, kwargs):
 
 @torch.no_grad()
 def gptq_block(block, inputs, kwargs, bit=4, sym=False, percdamp=0.01, actorder=True,
-               true_sequential=True, quant_out=True, model_dtype=torch.bfloat16):
+               true_sequential=True, quant_out=True, model_dtype=torch.bfloat16, capture=None):
     """Runs one decoder block through the schedule.  Returns (per-linear results, next inputs).
-    Each result is gptq_ref.quantize_layer's dict plus 'w_qdq' (the deployed weight)."""
+    Each result is gptq_ref.quantize_layer's dict plus 'w_qdq' (the deployed weight).
+    capture: a dict that receives, per linear, the list of input tensors its final Hessian was
+    accumulated from (for teacher-forced comparisons of a single linear)."""
     subsets = llama_subsets(block)
     states, handles = {}, []
 
@@ -54,8 +56,12 @@ def gptq_block(block, inputs, kwargs, bit=4, sym=False, percdamp=0.01, actorder=
         for name, parent, attr in items:
             layer = getattr(parent, attr)
             states[name] = gptq_ref.hessian_init(layer.weight.shape[1], layer.weight.device)
+            if capture is not None:
+                capture[name] = []                  # re-initialised with the Hessian (subset_init)
             def hook(m, inp, out, name=name):       # must return None: a value would replace the output
                 gptq_ref.add_batch(states[name], inp[0].data)
+                if capture is not None:
+                    capture[name].append(inp[0].data)
             hs.append(layer.register_forward_hook(hook))
         return hs
 

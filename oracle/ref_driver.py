@@ -234,7 +234,7 @@ def calib_ids(n_samples, seq_len, vocab, seed=1):
 def run_algorithm(ref, model, quant_cfg, calib, seq_len, deploy='fake_quant'):
     """llmc/__main__.py:55-74 for one modality: catch the first block's inputs, construct the registered
     algorithm, run its block loop, deploy.  Returns the algorithm object."""
-    config = AttrDict(model=dict(type='Llama'), calib=dict(bs=1, seq_len=seq_len, n_samples=len(calib)),
+    config = AttrDict(model=dict(type='Llama'), calib=dict(bs=1, seq_len=seq_len, n_samples=len(calib) if calib else 0),
                       quant=quant_cfg, base=dict(seed=0))
     if quant_cfg.method == 'RTN':
         algo = ref.ALGO_REGISTRY['RTN'](model, quant_cfg, None, None, config)
