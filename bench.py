@@ -46,6 +46,7 @@ NS, T, HID, INTER, HEADS = 128, 2048, 4096, 11008, 32
 METRIC = 'GPTQ W4 g128 decoder layers/sec'
 UNIT = 'layers/s'
 HESSIAN_BATCH = 8   # sequences handed to one Hessian launch (GPTQ special key `hessian_batch`)
+FACTORIZATION = 'native_full'   # `--workload kernel --case factor*`: this library's own blocked Cholesky + inverse
 SPECIAL = {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'true_sequential': True,
            'static_groups': False, 'hessian_batch': HESSIAN_BATCH, 'emit_codes': True}
 WORKLOADS = {
@@ -543,13 +544,13 @@ def kernel_case(name, n):
             L.call('lc_hessian_accum', L.ptr(X), 2048, 4096, L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
     elif name == 'hessian_wide':                      # the down_proj width, 16384 tokens per launch
         hessian(11008, 5)
-    elif name in ('factor', 'factor_wide'):           # damp + Cholesky + triangular inverse of one Hessian
-        C = 4096 if name == 'factor' else 11008
+    elif name in ('factor', 'factor_wide', 'factor_cusolver'):   # damp + Cholesky + triangular inverse of one Hessian
+        C = 11008 if name == 'factor_wide' else 4096
         g = torch.Generator().manual_seed(6)
         X = torch.randn(2 * C, C, generator=g).cuda()
         H = X.t() @ X
         del X
-        solver = lc.GPTQ(wq4, {'actorder': True})
+        solver = lc.GPTQ(wq4, {'actorder': True, 'factorization': 'native' if name == 'factor_cusolver' else FACTORIZATION})
         for _ in range(n):
             solver.factorize(H, 0.5)
         solver.check_status()
@@ -654,7 +655,7 @@ def kernel_case(name, n):
     print('done', name)
 
 
-KERNEL_CASES = ['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'gptq_wide', 'factor', 'factor_wide', 'block_ops',
+KERNEL_CASES = ['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'gptq_wide', 'factor', 'factor_wide', 'factor_cusolver', 'block_ops',
                 'fp8_linear', 'mse', 'awq_clip', 'act_static', 'quik', 'w48']
 
 

@@ -228,6 +228,21 @@ int lc_hessian_accum_multi(const void* const* xs_host, const int64_t* tokens_hos
                            int64_t cols, float* H, float alpha, float beta, int ksplit,
                            int32_t* status, lc_stream_t stream);
 
+/* lc_hessian_accum_multi maintaining only the upper triangle of H (entries H[m][n] with n >= m; what
+ * lies below the diagonal is left as it is and means nothing).  The mirrored atomic adds are half of the
+ * epilogue's work, and the GPTQ solver reads the Hessian through lc_gptq_diag and lc_gptq_permute_damp
+ * only, which can fetch entry (i, j) from the upper triangle (flag LC_H_UPPER there).  This is the form
+ * GPTQ.add_batch's replacement uses (gptq.py:283-290 computes the full product).
+ *
+ * Accuracy (all three entry points): the tensor core adds every 16-token MMA into its fp32 accumulator
+ * with truncation, so a sum over t tokens carries a relative deficit of about t / 16 * 2^-24, nearly but
+ * not exactly uniform over the matrix.  With ksplit = 0 a launch's tokens are cut into equal parts of at
+ * most 4096 per accumulation (parts are combined by fp32 atomic adds), which keeps the deficit below
+ * 1.5e-5 and what remains after a uniform factor is taken out near 1e-6. */
+int lc_hessian_accum_upper(const void* const* xs_host, const int64_t* tokens_host, int nseg,
+                           int64_t cols, float* H, float alpha, float beta, int ksplit,
+                           int32_t* status, lc_stream_t stream);
+
 /* Exercises the bounded-wait path of the tensor-core kernels without touching them: a one-thread
  * kernel waits (about a millisecond) on a barrier nothing arrives on and must write LC_ERR_TIMEOUT
  * to *status and return normally.  (No counterpart in the reference.) */
@@ -246,12 +261,16 @@ int lc_gptq_diag(const float* H, int64_t cols, float* diag_out, lc_stream_t stre
  * where dead(c) means H[c][c] == 0 and damp = percdamp * mean(diag(Hp)).  `hscale` lets the
  * caller keep H as the raw sum of X^T X and apply 2/nsamples here.
  *   W rows x cols in `w_dtype`; perm int64 (cols) or NULL for identity
- *   reverse_h != 0: Hp is written with both index orders reversed, Hp[i][j] <- entry
+ *   reverse_h: bit 0 (LC_H_REVERSE): Hp is written with both index orders reversed, Hp[i][j] <- entry
  *           (cols-1-i, cols-1-j), which is the input of the single-factorisation route to the
- *           upper factor of the inverse (see lc_gptq_flip); Wp is not affected
+ *           upper factor of the inverse (see lc_gptq_flip); Wp is not affected.
+ *           bit 1 (LC_H_UPPER): only the upper triangle of H is valid (lc_hessian_accum_upper); entry
+ *           (i, j) is read from H[min(i,j)][max(i,j)].  Hp is a full symmetric matrix either way
  *   scratch: at least 1 float (receives damp)
  * W/Wp may both be NULL (only the Hessian part runs: one factorisation serves every linear that
  * shares the input) and Hp may be NULL (only the weight gather runs). */
+#define LC_H_REVERSE 1
+#define LC_H_UPPER 2
 int lc_gptq_permute_damp(const void* W, int w_dtype, const float* H, const int64_t* perm,
                          int64_t rows, int64_t cols, float hscale, float percdamp, int reverse_h,
                          float* Wp, float* Hp, float* scratch, lc_stream_t stream);

@@ -18,6 +18,7 @@ LC_ERR_WORKSPACE, LC_ERR_NOT_PD, LC_ERR_TIMEOUT, LC_ERR_CUDA = -5, -6, -7, -8
 LC_F32, LC_BF16, LC_F16 = 0, 1, 2
 LC_CODES_NONE, LC_CODES_I32, LC_CODES_I8, LC_CODES_PACK4 = 0, 1, 2, 3
 LC_GEMM_UPPER_ONLY, LC_GEMM_B_LOWER, LC_GEMM_A_UPPER = 1, 2, 4
+LC_H_REVERSE, LC_H_UPPER = 1, 2
 
 _DTYPES = {torch.float32: LC_F32, torch.bfloat16: LC_BF16, torch.float16: LC_F16}
 
@@ -32,6 +33,7 @@ SIGNATURES = {
     'lc_fp8_e4m3_quant': [_p, _i, _i64, _i64, _p, _p, _p, _p],
     'lc_hessian_accum': [_p, _i64, _i64, _p, _f, _f, _i, _p, _p],
     'lc_hessian_accum_multi': [_p, _p, _i, _i64, _p, _f, _f, _i, _p, _p],
+    'lc_hessian_accum_upper': [_p, _p, _i, _i64, _p, _f, _f, _i, _p, _p],
     'lc_selftest_wait_expiry': [_p, _p],
     'lc_gptq_diag': [_p, _i64, _p, _p],
     'lc_gptq_permute_damp': [_p, _i, _p, _p, _i64, _i64, _f, _f, _i, _p, _p, _p, _p],

@@ -21,7 +21,7 @@ import contextlib
 import torch
 
 from . import _lib as L
-from . import block_ops
+from . import block_ops, parallel
 
 
 def _is_norm(m):
@@ -60,6 +60,11 @@ class Awq:
         scratch = torch.empty(splits * C, dtype=torch.float32, device=x.device)
         L.call('lc_awq_act_mean', L.ptr(x2), L.lc_dtype(x2), T, C, L.ptr(out), L.ptr(scratch), scratch.numel(),
                L.stream_of(x2))
+        if parallel.world()[1] > 1:
+            # token shards: the kernel's fp32 partial sums of |x| are added over the ranks and divided by the
+            # total token count, rounded to the activation dtype once -- the mean over all the data
+            total, n = parallel.sum_and_count(scratch.view(splits, C).sum(0), T)
+            out = (total / float(n)).to(x.dtype)
         return out
 
     def get_scales(self, x_mean, ratio):
@@ -120,6 +125,12 @@ class Awq:
             del out
         for l, w in zip(layers, org):
             l.weight.data = w
+        if parallel.world()[1] > 1:
+            # every rank evaluated the grid on its own tokens: squared-error sums and element counts are added
+            # over the ranks, so all ranks pick the grid point of the whole calibration set
+            n_el = org_out.numel()
+            sums, total = parallel.sum_and_count(losses * float(n_el), n_el)
+            losses = sums / float(total)
         best = torch.argmin(losses)            # first minimum == the reference's strict `<` update
         return cand.index_select(0, best.view(1)).view(-1), losses
 
@@ -166,9 +177,18 @@ class Awq:
         n_g = C // wq.group_size
         best_max = torch.empty((R, n_g, 1), dtype=w.dtype, device=w.device)
         best_min = torch.empty((R, n_g, 1), dtype=w.dtype, device=w.device)
+        multi = parallel.world()[1] > 1
         L.call('lc_awq_clip_search', L.ptr(w), L.ptr(x2), L.lc_dtype(w), R, C, n_tok_all, step, wq.group_size,
                int(wq.bit), int(wq.sym), int(self.clip_sym), self.clip_n_grid, float(self.clip_max_shrink),
-               L.ptr(best_max), L.ptr(best_min), L.ptr(w) if apply else None, L.stream_of(w))
+               L.ptr(best_max), L.ptr(best_min), L.ptr(w) if apply and not multi else None, L.stream_of(w))
+        if multi:
+            # AutoClipper.run averages the ranks' thresholds before clamping (auto_clip.py:72-76, :194-212)
+            parallel.average_over_ranks(best_max)
+            parallel.average_over_ranks(best_min)
+            if apply:
+                wg = w.view(R, n_g, wq.group_size)
+                lo = -best_max if self.clip_sym else best_min
+                w.copy_(torch.clamp(wg, lo, best_max).view(R, C))
         if apply and w.data_ptr() != weight.data_ptr():
             weight.copy_(w)
         return best_max, best_min

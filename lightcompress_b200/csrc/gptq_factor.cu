@@ -32,7 +32,7 @@ namespace {
 constexpr int kB = 128;            // diagonal block
 constexpr int kOuter = 512;        // rows per lazy trailing update
 constexpr int kLeafThreads = 256;
-constexpr int kLd = kB + 1;        // padded shared-memory pitch
+constexpr int kLd = kB + 4;        // shared-memory pitch: a multiple of 4 floats for 16-byte accesses
 
 __device__ __forceinline__ float tf32_lo(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
@@ -41,16 +41,29 @@ __device__ __forceinline__ float tf32_lo(float x) { return x - __uint_as_float(_
 // G_kk^-1 (upper, dense 128x128 block in `v` / `v_lo`), and Vt_kk = V_kk^T with its low part into the
 // lower-triangular result.
 //
-// The block lives in registers: 256 threads as a 16 x 16 grid, thread (ty, tx) holding the 8 x 8
-// elements (ty + 16a, tx + 16b).  Each of the 128 steps of the right-looking Cholesky broadcasts one
-// scaled row through shared memory (double-buffered, one barrier per step) and applies the rank-1
-// update to the register tiles; the pivots are tracked redundantly by the 16 threads that own a row,
-// so that no second barrier is needed.  The inverse is a Gauss-Jordan elimination of [G | I] from the
-// bottom row up with the same communication pattern (column j of G and row j of the right-hand side
-// per step).  The loops over the 16-row bands are unrolled, which keeps every register index static.
+// The block lives in shared memory and both phases are blocked on 16 x 16 sub-blocks, so that the
+// CTA-wide barriers number a few dozen instead of one per column:
+//   Cholesky, right-looking over the 8 sub-blocks: (a) one warp factorises the 16 x 16 diagonal
+//   sub-block in registers (lane = column, the pivot row travels by shuffles; this chain of 128
+//   dependent sqrt / divide / update steps is what bounds the kernel), (b) a thread per column solves
+//   the 16-row strip right of it by forward substitution, (c) all threads apply the rank-16 update to
+//   the rest in 4 x 4 register tiles.
+//   Inverse V = G^-1, block row by block row from the bottom: the eight 16 x 16 diagonal inverses first
+//   (one warp each), then per block row i the products sum_k G_ik V_kj in 4 x 4 register tiles and a
+//   thread per column applies -D_i^-1.
+// Quotients are formed as x * (1/d) with one residual correction (the IEEE quotient up to rare last-bit
+// cases), like the column kernel this replaces; every accumulation is an fp32 FMA chain.
 //
 // kCholesky = false: A already holds the factor G_kk (upper); only the inverse is computed and only Vt /
 // Vt_lo are written.  One CTA per diagonal block (blockIdx.x), all blocks of a matrix in one launch.
+constexpr int kSB = 16;            // sub-block edge
+constexpr int kLeafSmemFloats = 2 * kB * kLd;
+
+__device__ __forceinline__ float quot(float x, float d, float dinv) {
+  const float q0 = x * dinv;
+  return fmaf(fmaf(-q0, d, x), dinv, q0);
+}
+
 template <bool kCholesky>
 __global__ void __launch_bounds__(kLeafThreads, 1) chol_leaf_kernel(const float* __restrict__ A, int64_t lda,
                                                                      float* __restrict__ G, float* __restrict__ G_lo,
@@ -58,138 +71,333 @@ __global__ void __launch_bounds__(kLeafThreads, 1) chol_leaf_kernel(const float*
                                                                      float* __restrict__ v_lo, float* __restrict__ Vt,
                                                                      float* __restrict__ Vt_lo, int64_t ldv,
                                                                      int32_t* status) {
-  extern __shared__ float stage[];          // [128][129]: staging for the transposed store
-  __shared__ float rowbuf[2][kB], colbuf[2][kB];
+  extern __shared__ __align__(16) float leaf_sm[];
+  float (*S)[kLd] = reinterpret_cast<float (*)[kLd]>(leaf_sm);              // A, then G (upper)
+  float (*V)[kLd] = reinterpret_cast<float (*)[kLd]>(leaf_sm + kB * kLd);   // G^-1 (upper)
+  __shared__ float Dinv[kB / kSB][kSB][kSB + 1];   // inverses of the diagonal sub-blocks of G
+  __shared__ float rdiag[kB];                      // 1 / G_jj
   __shared__ int s_bad;
-  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) s_bad = 0;
   if (!kCholesky) {
-    // block b of the diagonal
     A += (int64_t)blockIdx.x * kB * (lda + 1);
     Vt += (int64_t)blockIdx.x * kB * (ldv + 1);
     Vt_lo += (int64_t)blockIdx.x * kB * (ldv + 1);
   }
-
-  float t[8][8], pd[8], dg[8];
-#pragma unroll
-  for (int a = 0; a < 8; ++a) {
-    const int r = ty + 16 * a;
-#pragma unroll
-    for (int b = 0; b < 8; ++b) t[a][b] = A[(int64_t)r * lda + tx + 16 * b];
-    pd[a] = A[(int64_t)r * lda + r];
-    dg[a] = kCholesky ? 1.f : pd[a];
+#pragma unroll 4
+  for (int idx = tid; idx < kB * kB / 4; idx += kLeafThreads) {
+    const int r = idx >> 5, c = (idx & 31) << 2;
+    float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c + 3 >= r) a4 = *reinterpret_cast<const float4*>(A + (int64_t)r * lda + c);
+    a4.x = (c >= r) ? a4.x : 0.f, a4.y = (c + 1 >= r) ? a4.y : 0.f;
+    a4.z = (c + 2 >= r) ? a4.z : 0.f, a4.w = (c + 3 >= r) ? a4.w : 0.f;
+    *reinterpret_cast<float4*>(&S[r][c]) = a4;
+    *reinterpret_cast<float4*>(&V[r][c]) = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   __syncthreads();
 
   // ---- Cholesky: A = G^T G ----
-#pragma unroll
-  for (int jb = 0; jb < (kCholesky ? 8 : 0); ++jb) {
+  if (kCholesky) {
 #pragma unroll 1
-    for (int jj = 0; jj < 16; ++jj) {
-      const int j = 16 * jb + jj, buf = j & 1;
-      if (ty == jj) {
-        const float p = pd[jb];
-        const float d = sqrtf(p), dinv = __frcp_rn(d);
-        if (tx == 0 && (!(p > 0.f) || !(p < INFINITY))) s_bad = 1;
-        dg[jb] = d;
+    for (int jb = 0; jb < kB / kSB; ++jb) {
+      const int j0 = jb * kSB;
+      // (a) the diagonal sub-block, in the registers of warp 0: lane c (and its twin c + 16) holds column c
+      if (warp == 0) {
+        const int c = lane & 15;
+        float col[kSB];
 #pragma unroll
-        for (int b = 0; b < 8; ++b) {
-          const int c = tx + 16 * b;
-          float x = t[jb][b];
-          if (c == j) {
-            x = d;
-          } else if (c > j) {
-            // IEEE quotient through the reciprocal and one residual correction
-            const float q0 = x * dinv;
-            x = fmaf(fmaf(-q0, d, x), dinv, q0);
+        for (int r = 0; r < kSB; ++r) col[r] = S[j0 + r][j0 + c];
+        bool bad = false;
+        float rd = 0.f;
+#pragma unroll
+        for (int j = 0; j < kSB; ++j) {
+          const float p = __shfl_sync(0xffffffffu, col[j], j);
+          bad = bad || !(p > 0.f) || !(p < INFINITY);
+          // 1 / sqrt(p) by the hardware approximation and one Newton step, then sqrt(p) = p * that with one
+          // residual correction: both within an ulp, in a third of the latency of sqrtf followed by a divide
+          // (this chain of 128 dependent pivots is what bounds the kernel)
+          float dinv = rsqrtf(p);
+          dinv = dinv * fmaf(-0.5f * p * dinv, dinv, 1.5f);
+          float d = p * dinv;
+          d = fmaf(fmaf(-d, d, p), 0.5f * dinv, d);
+          const float g = (c == j) ? d : ((c > j) ? quot(col[j], d, dinv) : 0.f);
+          col[j] = g;
+          if (c == j) rd = dinv;
+#pragma unroll
+          for (int r = j + 1; r < kSB; ++r) {
+            const float gr = __shfl_sync(0xffffffffu, g, r);
+            col[r] = fmaf(-gr, g, col[r]);          // rows below the diagonal of this column: unused values
           }
-          t[jb][b] = x;
-          rowbuf[buf][c] = x;
+        }
+        if (lane < kSB) {
+#pragma unroll
+          for (int r = 0; r < kSB; ++r) S[j0 + r][j0 + c] = (c >= r) ? col[r] : 0.f;
+          rdiag[j0 + c] = rd;
+        }
+        if (bad && lane == 0) s_bad = 1;
+      }
+      __syncthreads();
+      const int ncol = kB - j0 - kSB;          // columns right of the sub-block (multiple of 16)
+      if (ncol == 0) break;
+      // (b) the strip right of it: X = D^-T S[j0 : j0 + 16, right], a thread per column
+      if (tid < ncol) {
+        const int c = j0 + kSB + tid;
+        // right-looking substitution: as soon as x[k] is known it is taken out of every later row, so the
+        // dependent chain per step is one FMA and one quotient instead of a k-term sum
+        float x[kSB];
+#pragma unroll
+        for (int i = 0; i < kSB; ++i) x[i] = S[j0 + i][c];
+#pragma unroll
+        for (int k = 0; k < kSB; ++k) {
+          x[k] = quot(x[k], S[j0 + k][j0 + k], rdiag[j0 + k]);
+#pragma unroll
+          for (int i = k + 1; i < kSB; ++i) x[i] = fmaf(-S[j0 + k][j0 + i], x[k], x[i]);
+          S[j0 + k][c] = x[k];
         }
       }
       __syncthreads();
-      float gr[8], gc[8];
+      // (c) S[r][c] -= sum_k X[k][r] X[k][c] for r, c right of the sub-block, tiles on or above the diagonal
+      const int nt = ncol / 4, ntri = nt * (nt + 1) / 2;
+      for (int t = tid; t < ntri; t += kLeafThreads) {
+        // row-major index of the upper triangle -> (tr, tc)
+        int tr = (int)((2.f * nt + 1.f - sqrtf((2.f * nt + 1.f) * (2.f * nt + 1.f) - 8.f * (float)t)) * 0.5f);
+        while (tr > 0 && tr * nt - tr * (tr - 1) / 2 > t) --tr;
+        while ((tr + 1) * nt - (tr + 1) * tr / 2 <= t) ++tr;
+        const int tc = tr + (t - (tr * nt - tr * (tr - 1) / 2));
+        const int r0 = j0 + kSB + 4 * tr, c0 = j0 + kSB + 4 * tc;
+        float acc[4][4];
 #pragma unroll
-      for (int a = jb; a < 8; ++a) gr[a] = rowbuf[buf][ty + 16 * a];
+        for (int a = 0; a < 4; ++a)
 #pragma unroll
-      for (int b = jb; b < 8; ++b) gc[b] = rowbuf[buf][tx + 16 * b];
+          for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
 #pragma unroll
-      for (int a = jb; a < 8; ++a) {
-        if (a > jb || ty > jj) {
+        for (int k = 0; k < kSB; ++k) {
+          const float4 xr = *reinterpret_cast<const float4*>(&S[j0 + k][r0]);
+          const float4 xc = *reinterpret_cast<const float4*>(&S[j0 + k][c0]);
+          const float ar[4] = {xr.x, xr.y, xr.z, xr.w}, ac[4] = {xc.x, xc.y, xc.z, xc.w};
 #pragma unroll
-          for (int b = jb; b < 8; ++b) t[a][b] = fmaf(-gr[a], gc[b], t[a][b]);
-          pd[a] = fmaf(-gr[a], gr[a], pd[a]);
+          for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(ar[a], ac[b], acc[a][b]);
         }
-      }
-    }
-  }
-
-  // ---- inverse: Gauss-Jordan on [G | I], bottom row first ----
-  __syncthreads();   // the last row buffer of the Cholesky loop is about to be reused
-  float w[8][8];
 #pragma unroll
-  for (int a = 0; a < 8; ++a)
+        for (int a = 0; a < 4; ++a)
 #pragma unroll
-    for (int b = 0; b < 8; ++b) w[a][b] = (ty + 16 * a == tx + 16 * b) ? 1.f : 0.f;
-#pragma unroll
-  for (int jb = 7; jb >= 0; --jb) {
-#pragma unroll 1
-    for (int jj = 15; jj >= 0; --jj) {
-      const int j = 16 * jb + jj, buf = j & 1;
-      if (ty == jj) {
-        const float d = dg[jb];
-#pragma unroll
-        for (int b = jb; b < 8; ++b) {
-          w[jb][b] = __fdiv_rn(w[jb][b], d);
-          rowbuf[buf][tx + 16 * b] = w[jb][b];
-        }
-      }
-      if (tx == jj) {
-#pragma unroll
-        for (int a = 0; a <= jb; ++a) colbuf[buf][ty + 16 * a] = t[a][jb];
+          for (int b = 0; b < 4; ++b) S[r0 + a][c0 + b] -= acc[a][b];
       }
       __syncthreads();
-      float cr[8], rw[8];
-#pragma unroll
-      for (int a = 0; a <= jb; ++a) cr[a] = colbuf[buf][ty + 16 * a];
-#pragma unroll
-      for (int b = jb; b < 8; ++b) rw[b] = rowbuf[buf][tx + 16 * b];
-#pragma unroll
-      for (int a = 0; a <= jb; ++a) {
-        if (a < jb || ty < jj) {
-#pragma unroll
-          for (int b = jb; b < 8; ++b) w[a][b] = fmaf(-cr[a], rw[b], w[a][b]);
-        }
-      }
     }
+  } else {
+    if (tid < kB) rdiag[tid] = __frcp_rn(S[tid][tid]);
+    __syncthreads();
   }
 
-  // ---- stores ----
+  // ---- inverse V = G^-1 ----
+  // diagonal sub-blocks: warp w inverts D_w (upper) by back substitution, lane c < 16 the column c
+  {
+    const int j0 = warp * kSB, c = lane & 15;
+    float x[kSB];
 #pragma unroll
-  for (int a = 0; a < 8; ++a) {
-    const int r = ty + 16 * a;
+    for (int i = 0; i < kSB; ++i) x[i] = (i == c) ? 1.f : 0.f;
 #pragma unroll
-    for (int b = 0; b < 8; ++b) {
-      const int c = tx + 16 * b;
-      const float gv = (c >= r) ? t[a][b] : 0.f;
-      const float wv = (c >= r) ? w[a][b] : 0.f;
-      if (kCholesky) {
-        G[(int64_t)r * ldg + c] = gv;
-        G_lo[(int64_t)r * ldg + c] = tf32_lo(gv);
-        v[r * kB + c] = wv;
-        v_lo[r * kB + c] = tf32_lo(wv);
+    for (int k = kSB - 1; k >= 0; --k) {
+      x[k] = (k <= c) ? quot(x[k], S[j0 + k][j0 + k], rdiag[j0 + k]) : 0.f;
+#pragma unroll
+      for (int i = 0; i < k; ++i) x[i] = fmaf(-S[j0 + i][j0 + k], x[k], x[i]);
+    }
+    if (lane < kSB) {
+#pragma unroll
+      for (int i = 0; i < kSB; ++i) {
+        Dinv[warp][i][c] = x[i];
+        V[j0 + i][j0 + c] = x[i];
       }
-      stage[c * kLd + r] = wv;           // transposed
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < kB * kB; idx += kLeafThreads) {
-    const int i = idx >> 7, jcol = idx & 127;
-    const float wt = stage[i * kLd + jcol];
-    Vt[(int64_t)i * ldv + jcol] = wt;
-    Vt_lo[(int64_t)i * ldv + jcol] = tf32_lo(wt);
+#pragma unroll 1
+  for (int bi = kB / kSB - 2; bi >= 0; --bi) {
+    const int i0 = bi * kSB, k0 = i0 + kSB, ncol = kB - k0;
+    // T[r][c] = sum_{k = k0 .. c} G[i0 + r][k] V[k][c], stored where V[i0 + r][c] will go; 2 x 4 register
+    // tiles (8 row pairs x ncol / 4 column quads: up to 224 threads), k in steps of 4 with 16-byte reads
+    const int ntc = ncol / 4;
+    for (int t = tid; t < 8 * ntc; t += kLeafThreads) {
+      const int tr = t / ntc, tc = t % ntc;
+      const int r0 = i0 + 2 * tr, c0 = k0 + 4 * tc;
+      float acc[2][4];
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+      const int kend = c0 + 4;                      // V[k][c] == 0 for k > c; k0 and kend are multiples of 4
+#pragma unroll 2
+      for (int k = k0; k < kend; k += 4) {
+        const float4 g0 = *reinterpret_cast<const float4*>(&S[r0][k]);
+        const float4 g1 = *reinterpret_cast<const float4*>(&S[r0 + 1][k]);
+        const float ga[2][4] = {{g0.x, g0.y, g0.z, g0.w}, {g1.x, g1.y, g1.z, g1.w}};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 vc = *reinterpret_cast<const float4*>(&V[k + q][c0]);
+          const float ac[4] = {vc.x, vc.y, vc.z, vc.w};
+#pragma unroll
+          for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(ga[a][q], ac[b], acc[a][b]);
+        }
+      }
+      // rows i0 .. i0 + 15 of V are not read by this loop (k >= k0 = i0 + 16): safe to park T there
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+        *reinterpret_cast<float4*>(&V[r0 + a][c0]) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    }
+    __syncthreads();
+    // V[i0 + r][c] = -sum_{k >= r} Dinv[r][k] T[k][c], a thread per column
+    if (tid < ncol) {
+      const int c = k0 + tid;
+      float tcol[kSB];
+#pragma unroll
+      for (int k = 0; k < kSB; ++k) tcol[k] = V[i0 + k][c];
+#pragma unroll
+      for (int r = 0; r < kSB; ++r) {
+        float sacc = 0.f;
+#pragma unroll
+        for (int k = r; k < kSB; ++k) sacc = fmaf(Dinv[bi][r][k], tcol[k], sacc);
+        V[i0 + r][c] = -sacc;
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- stores ----
+  for (int idx = tid; idx < kB * kB / 4; idx += kLeafThreads) {
+    const int r = idx >> 5, c = (idx & 31) << 2;
+    if (kCholesky) {
+      float gv[4], wv[4], gl[4], wl[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        gv[e] = (c + e >= r) ? S[r][c + e] : 0.f;
+        wv[e] = (c + e >= r) ? V[r][c + e] : 0.f;
+        gl[e] = tf32_lo(gv[e]), wl[e] = tf32_lo(wv[e]);
+      }
+      *reinterpret_cast<float4*>(G + (int64_t)r * ldg + c) = make_float4(gv[0], gv[1], gv[2], gv[3]);
+      *reinterpret_cast<float4*>(G_lo + (int64_t)r * ldg + c) = make_float4(gl[0], gl[1], gl[2], gl[3]);
+      *reinterpret_cast<float4*>(v + r * kB + c) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+      *reinterpret_cast<float4*>(v_lo + r * kB + c) = make_float4(wl[0], wl[1], wl[2], wl[3]);
+    }
+    // Vt[r][c + e] = V[c + e][r] (lower)
+    float wt[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) wt[e] = (r >= c + e) ? V[c + e][r] : 0.f;
+    *reinterpret_cast<float4*>(Vt + (int64_t)r * ldv + c) = make_float4(wt[0], wt[1], wt[2], wt[3]);
+    *reinterpret_cast<float4*>(Vt_lo + (int64_t)r * ldv + c) =
+        make_float4(tf32_lo(wt[0]), tf32_lo(wt[1]), tf32_lo(wt[2]), tf32_lo(wt[3]));
   }
   if (tid == 0 && s_bad && status) atomicCAS(status, 0, (int)LC_ERR_NOT_PD);
+}
+
+// G[k : k + 128, c] = V_kk^T A[k : k + 128, c] for the columns c right of a diagonal block (the panel
+// solve of the blocked Cholesky), with the low part of the result: exact fp32 FMA chains, one launch
+// instead of split + GEMM + split.  A CTA takes 64 columns; V_kk (upper, so the sum runs over r <= i)
+// and the A tile sit in shared memory; a thread computes 8 rows x 4 columns.
+constexpr int kPanelCols = 64;
+__global__ void __launch_bounds__(256) chol_panel_kernel(const float* __restrict__ Vkk, const float* __restrict__ Ap,
+                                                          int64_t lda, float* __restrict__ Gp, float* __restrict__ Gp_lo,
+                                                          int64_t ldg, int64_t ncols) {
+  extern __shared__ __align__(16) float panel_sm[];
+  float (*Vs)[kB + 4] = reinterpret_cast<float (*)[kB + 4]>(panel_sm);                       // [r][i]
+  float (*As)[kPanelCols + 4] = reinterpret_cast<float (*)[kPanelCols + 4]>(panel_sm + kB * (kB + 4));   // [r][c]
+  const int tid = threadIdx.x;
+  const int64_t c_base = (int64_t)blockIdx.x * kPanelCols;
+#pragma unroll
+  for (int idx = tid; idx < kB * kB / 4; idx += 256) {
+    const int r = idx >> 5, i4 = (idx & 31) << 2;
+    *reinterpret_cast<float4*>(&Vs[r][i4]) = *reinterpret_cast<const float4*>(Vkk + r * kB + i4);
+  }
+#pragma unroll
+  for (int idx = tid; idx < kB * kPanelCols / 4; idx += 256) {
+    const int r = idx >> 4, c4 = (idx & 15) << 2;
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c_base + c4 < ncols) val = *reinterpret_cast<const float4*>(Ap + (int64_t)r * lda + c_base + c4);
+    *reinterpret_cast<float4*>(&As[r][c4]) = val;
+  }
+  __syncthreads();
+  const int ti = tid >> 4, tc = tid & 15;          // rows 8 ti .. 8 ti + 7, columns 4 tc .. 4 tc + 3
+  const int i0 = ti * 8, c0 = tc * 4;
+  float acc[8][4];
+#pragma unroll
+  for (int a = 0; a < 8; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+  // V upper: V[r][i] != 0 only for r <= i, so rows r beyond i0 + 7 contribute nothing
+  for (int r = 0; r < i0 + 8; ++r) {
+    const float4 av = *reinterpret_cast<const float4*>(&As[r][c0]);
+    const float4 v0 = *reinterpret_cast<const float4*>(&Vs[r][i0]);
+    const float4 v1 = *reinterpret_cast<const float4*>(&Vs[r][i0 + 4]);
+    const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w}, aa[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(vv[a], aa[b], acc[a][b]);
+  }
+  if (c_base + c0 < ncols) {
+#pragma unroll
+    for (int a = 0; a < 8; ++a) {
+      const int64_t o = (int64_t)(i0 + a) * ldg + c_base + c0;
+      *reinterpret_cast<float4*>(Gp + o) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+      *reinterpret_cast<float4*>(Gp_lo + o) =
+          make_float4(tf32_lo(acc[a][0]), tf32_lo(acc[a][1]), tf32_lo(acc[a][2]), tf32_lo(acc[a][3]));
+    }
+  }
+}
+
+// A[r][c] -= sum_{i < 128} P[i][r] P[i][c] for r in [r_begin, r_end), c in [r, n): the eager part of the
+// blocked Cholesky's trailing update (the rows of the current outer block), P = the panel row block just
+// solved (pitch ldp, column index = matrix column).  64 x 64 tiles, tiles entirely below the diagonal
+// skipped; exact fp32.
+constexpr int kStripTile = 64;
+__global__ void __launch_bounds__(256) chol_strip_kernel(const float* __restrict__ P, int64_t ldp, float* __restrict__ Am,
+                                                          int64_t lda, int64_t r_begin, int64_t r_end, int64_t n) {
+  extern __shared__ __align__(16) float strip_sm[];
+  float (*Pr)[kStripTile + 4] = reinterpret_cast<float (*)[kStripTile + 4]>(strip_sm);
+  float (*Pc)[kStripTile + 4] = reinterpret_cast<float (*)[kStripTile + 4]>(strip_sm + kB * (kStripTile + 4));
+  const int64_t r0 = r_begin + (int64_t)blockIdx.y * kStripTile;
+  const int64_t c0 = r_begin + (int64_t)blockIdx.x * kStripTile;
+  if (c0 + kStripTile <= r0 || r0 >= r_end || c0 >= n) return;      // below the diagonal or outside
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int idx = tid; idx < kB * kStripTile / 4; idx += 256) {
+    const int i = idx >> 4, x4 = (idx & 15) << 2;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (r0 + x4 < n) a = *reinterpret_cast<const float4*>(P + (int64_t)i * ldp + r0 + x4);
+    if (c0 + x4 < n) b = *reinterpret_cast<const float4*>(P + (int64_t)i * ldp + c0 + x4);
+    *reinterpret_cast<float4*>(&Pr[i][x4]) = a;
+    *reinterpret_cast<float4*>(&Pc[i][x4]) = b;
+  }
+  __syncthreads();
+  const int tr = (tid >> 4) * 4, tc = (tid & 15) * 4;
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < kB; ++i) {
+    const float4 xr = *reinterpret_cast<const float4*>(&Pr[i][tr]);
+    const float4 xc = *reinterpret_cast<const float4*>(&Pc[i][tc]);
+    const float ar[4] = {xr.x, xr.y, xr.z, xr.w}, ac[4] = {xc.x, xc.y, xc.z, xc.w};
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(ar[a], ac[b], acc[a][b]);
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int64_t r = r0 + tr + a;
+    if (r >= r_end || c0 + tc >= n) continue;
+    float4* p = reinterpret_cast<float4*>(Am + r * lda + c0 + tc);
+    float4 cur = *p;
+    cur.x -= acc[a][0], cur.y -= acc[a][1], cur.z -= acc[a][2], cur.w -= acc[a][3];
+    *p = cur;
+  }
 }
 
 constexpr int kMaxRegions = 64;
@@ -408,32 +616,40 @@ int invert_range(const Factor& f, int64_t lo, int64_t hi, bool skip_root = false
   return LC_OK;
 }
 
+constexpr size_t kLeafSmemBytes = kLeafSmemFloats * sizeof(float);
+constexpr size_t kPanelSmemBytes = (kB * (kB + 4) + kB * (kPanelCols + 4)) * sizeof(float);
+constexpr size_t kStripSmemBytes = 2 * kB * (kStripTile + 4) * sizeof(float);
+
 int factorize(const Factor& f) {
   const int64_t n = f.n;
   int rc;
   LC_CHECK_CUDA(cudaFuncSetAttribute(chol_leaf_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kB * kLd * (int)sizeof(float)));
+                                     (int)kLeafSmemBytes));
+  LC_CHECK_CUDA(cudaFuncSetAttribute(chol_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kPanelSmemBytes));
+  LC_CHECK_CUDA(cudaFuncSetAttribute(chol_strip_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kStripSmemBytes));
   LC_CHECK_CUDA(cudaMemsetAsync(f.Vt, 0, n * n * sizeof(float), f.st));
   LC_CHECK_CUDA(cudaMemsetAsync(f.Vt_lo, 0, n * n * sizeof(float), f.st));
   for (int64_t o = 0; o < n; o += kOuter) {
     const int64_t o2 = o + kOuter < n ? o + kOuter : n;
     for (int64_t k = o; k < o2; k += kB) {
       const int64_t kk = k * n + k, blk = (k / kB) * kB * kB;
-      chol_leaf_kernel<true><<<1, kLeafThreads, kB * kLd * sizeof(float), f.st>>>(
+      chol_leaf_kernel<true><<<1, kLeafThreads, kLeafSmemBytes, f.st>>>(
           f.A + kk, n, f.G + kk, f.G_lo + kk, n, f.Vd + blk, f.Vd_lo + blk, f.Vt + kk, f.Vt_lo + kk, n, f.status);
       LC_LAUNCH_CHECK();
       const int64_t k2 = k + kB, right = n - k2;
       if (right == 0) break;
-      // G[k:k2, k2:] = V_kk^T A[k:k2, k2:]; the low part of the A panel borrows the place of the result's
-      if ((rc = split_region(f, f.A + k * n + k2, f.G_lo + k * n + k2, kB, right, n)) != LC_OK) return rc;
-      if ((rc = tf32x3_gemm_launch(f.G + k * n + k2, n, f.mVd, k, 0, f.mA, k, k2, kB, right, kB, 0, 1.f, kGemmAUpper,
-                                   f.status, f.st)) != LC_OK)
-        return rc;
-      if ((rc = split_region(f, f.G + k * n + k2, f.G_lo + k * n + k2, kB, right, n)) != LC_OK) return rc;
+      // G[k:k2, k2:] = V_kk^T A[k:k2, k2:], with its low part
+      chol_panel_kernel<<<(unsigned)((right + kPanelCols - 1) / kPanelCols), 256, kPanelSmemBytes, f.st>>>(
+          f.Vd + blk, f.A + k * n + k2, n, f.G + k * n + k2, f.G_lo + k * n + k2, n, right);
+      LC_LAUNCH_CHECK();
       // eager update of the rest of the outer block's rows
-      if (k2 < o2 && (rc = tf32x3_gemm_launch(f.A + k2 * n + k2, n, f.mG, k, k2, f.mG, k, k2, o2 - k2, right, kB, 1,
-                                              -1.f, kGemmUpperOnly, f.status, f.st)) != LC_OK)
-        return rc;
+      if (k2 < o2) {
+        const dim3 grid((unsigned)((right + kStripTile - 1) / kStripTile), (unsigned)((o2 - k2) / kStripTile));
+        chol_strip_kernel<<<grid, 256, kStripSmemBytes, f.st>>>(f.G + k * n, n, f.A, n, k2, o2, n);
+        LC_LAUNCH_CHECK();
+      }
     }
     if (o2 < n && (rc = tf32x3_gemm_launch(f.A + o2 * n + o2, n, f.mG, o, o2, f.mG, o, o2, n - o2, n - o2, o2 - o, 1,
                                            -1.f, kGemmUpperOnly, f.status, f.st)) != LC_OK)
@@ -459,11 +675,11 @@ int invert_prologue(const Factor& f) {
   const int64_t n = f.n;
   int rc;
   LC_CHECK_CUDA(cudaFuncSetAttribute(chol_leaf_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kB * kLd * (int)sizeof(float)));
+                                     (int)kLeafSmemBytes));
   LC_CHECK_CUDA(cudaMemsetAsync(f.Vt, 0, n * n * sizeof(float), f.st));
   LC_CHECK_CUDA(cudaMemsetAsync(f.Vt_lo, 0, n * n * sizeof(float), f.st));
   if ((rc = split_region(f, f.G, f.G_lo, n, n, n)) != LC_OK) return rc;
-  chol_leaf_kernel<false><<<(unsigned)(n / kB), kLeafThreads, kB * kLd * sizeof(float), f.st>>>(
+  chol_leaf_kernel<false><<<(unsigned)(n / kB), kLeafThreads, kLeafSmemBytes, f.st>>>(
       f.G, n, nullptr, nullptr, 0, nullptr, nullptr, f.Vt, f.Vt_lo, n, nullptr);
   LC_LAUNCH_CHECK();
   return LC_OK;

@@ -32,7 +32,8 @@ __global__ void __launch_bounds__(1024) damp_kernel(const float* H, int64_t cols
 }
 
 __global__ void __launch_bounds__(256) permute_h_kernel(const float* H, const int64_t* perm, int64_t cols,
-                                                        float hscale, const float* damp, float* Hp, int reverse) {
+                                                        float hscale, const float* damp, float* Hp, int flags) {
+  const int reverse = flags & 1, upper = flags & 2;
   const int64_t i = blockIdx.y;
   const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= cols) return;
@@ -41,7 +42,8 @@ __global__ void __launch_bounds__(256) permute_h_kernel(const float* H, const in
   const int64_t sj = reverse ? cols - 1 - j : j;
   const int64_t pi = perm ? perm[si] : si;
   const int64_t pj = perm ? perm[sj] : sj;
-  float v = hscale * H[pi * cols + pj];
+  // upper: H holds its upper triangle only (lc_hessian_accum_upper)
+  float v = hscale * (upper && pi > pj ? H[pj * cols + pi] : H[pi * cols + pj]);
   if (i == j) {
     if (v == 0.f) v = 1.f;
     v += damp[0];

@@ -26,7 +26,7 @@ namespace {
 
 constexpr int ST = 256;        // super-tile edge
 constexpr int BK = 32;         // tokens per pipeline stage
-constexpr int kMaxAccumTokens = 8192;   // most tokens one work item accumulates in the tensor core (see hessian_launch)
+constexpr int kMaxAccumTokens = 4096;   // most tokens one work item accumulates in the tensor core (see hessian_launch)
 constexpr int UMMA_K = 16;     // bf16
 constexpr int STAGES = 6;
 constexpr int ATOM = 64;       // channels per 128-byte swizzle row
@@ -65,6 +65,7 @@ struct HessArgs {
   int seg_k[MAX_SEG];
   float alpha;
   int use3d;       // tensor maps are 3-D views: two 64-channel atoms per copy
+  int upper_only;  // only H[m][n] with n >= m is maintained: no mirrored adds (half the epilogue's atomics)
 };
 
 struct Item {
@@ -277,6 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
               for (int j = 0; j < 32; j += 4)
                 if (n0 + j < C) red_add_v4(row + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
+            if (a.upper_only) continue;
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 32; ++j) stg[j * STG_STRIDE + lane] = v[j];
@@ -297,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
               const int64_t nn = n0 + j;
               if (m < C && nn < C) {
                 if (j >= lane) red_add(a.H + m * C + nn, v[j]);
-                if (j > lane) red_add(a.H + nn * C + m, v[j]);
+                if (j > lane && !a.upper_only) red_add(a.H + nn * C + m, v[j]);
               }
             }
           }
@@ -348,7 +350,7 @@ __global__ void wait_expiry_selftest_kernel(int32_t* status, uint32_t limit) {
 }
 
 int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64_t cols, float* H, float alpha,
-                   float beta, int ksplit, int32_t* status, cudaStream_t st) {
+                   float beta, int ksplit, int32_t* status, cudaStream_t st, int upper_only = 0) {
   if (!H || cols <= 0 || ksplit < 0 || nseg < 0 || nseg > MAX_SEG) return LC_ERR_ARG;
   if (cols % 8 != 0) return LC_ERR_ALIGN;
   if (!aligned16(H)) return LC_ERR_ALIGN;
@@ -415,12 +417,13 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
   a.n_st = (int)((cols + ST - 1) / ST);
   a.n_super = a.n_st * (a.n_st + 1) / 2;
   a.alpha = alpha;
+  a.upper_only = upper_only;
   a.tail_begin = a.n_super;
   a.tail_split = 1;
   if (ksplit == 0) {
     // The tensor core adds every MMA's products into the fp32 accumulator with truncation, so a sum loses
     // about 2^-24 of its value per 16-token MMA step: a relative deficit that grows with the number of
-    // tokens one work item accumulates (measured: -5.6e-5 over 16384 tokens, -2.7e-5 over 8192), uniform
+    // tokens one work item accumulates (measured: -5.6e-5 over 16384 tokens, -2.7e-5 over 8192, -1.0e-5 over 4096), nearly uniform
     // over the matrix as long as every item accumulates the same number of tokens.  The uniform part does
     // not change the GPTQ solve (act-order, dampening and the ratios of U all scale together); the spread
     // around it does (it reorders near-equal diagonal entries), and it shrinks with the item length too.
@@ -471,4 +474,12 @@ extern "C" LC_API int lc_hessian_accum_multi(const void* const* xs_host, const i
   if (nseg < 0 || nseg > lc::MAX_SEG || (nseg > 0 && (!xs_host || !tokens_host))) return LC_ERR_ARG;
   return lc::hessian_launch(xs_host, tokens_host, nseg, cols, H, alpha, beta, ksplit, status,
                             reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" LC_API int lc_hessian_accum_upper(const void* const* xs_host, const int64_t* tokens_host, int nseg,
+                                             int64_t cols, float* H, float alpha, float beta, int ksplit,
+                                             int32_t* status, lc_stream_t stream) {
+  if (nseg < 0 || nseg > lc::MAX_SEG || (nseg > 0 && (!xs_host || !tokens_host))) return LC_ERR_ARG;
+  return lc::hessian_launch(xs_host, tokens_host, nseg, cols, H, alpha, beta, ksplit, status,
+                            reinterpret_cast<cudaStream_t>(stream), 1);
 }

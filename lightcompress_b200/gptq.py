@@ -59,9 +59,14 @@ class GPTQ:
         # 'direct': one Cholesky of the index-reversed matrix + one triangular inverse (cuSOLVER / cuBLAS);
         # 'native': the Cholesky by cuSOLVER, the triangular inverse blocked on 128x128 diagonal blocks with
         #           its products on the tensor cores (lc_gptq_invert_factor; C % 128 == 0, else 'direct');
-        # 'native_full': the Cholesky blocked the same way too (lc_gptq_factorize);
+        # 'native_full': the Cholesky blocked the same way too (lc_gptq_factorize): this library's own kernels
+        #           from the dampened Hessian to U;
+        # 'auto' (default): 'native_full' from `own_cholesky_min` columns on (measured on B200: 13.7 ms against
+        #           17.1 ms at C = 11008), 'native' below it (at C = 4096 the own Cholesky's chain of 32
+        #           dependent leaf / panel / strip launches takes 3.1 ms against 2.2 ms);
         # 'reference': the reference's three factorisations (gptq.py:172-174).  Same U up to fp32 rounding.
-        self.factorization = special.get('factorization', 'native')
+        self.factorization = special.get('factorization', 'auto')
+        self.own_cholesky_min = int(special.get('own_cholesky_min', 8192))
         # 'tensor': trailing update batched per 1024-column panel on tcgen05 (3-term tf32 split);
         # 'ffma': the reference's per-block update with the fp32 FFMA kernel
         self.trailing = special.get('trailing', 'tensor')
@@ -79,6 +84,9 @@ class GPTQ:
         # atomics in varying order when the matrix is small), 1 = one work item per tile (deterministic)
         self.hessian_ksplit = int(special.get('hessian_ksplit', 0))
         self.model_dtype = model_dtype
+        # the Hessians accumulated by add_batch hold their upper triangle only (see _flush); a caller that
+        # hands factorize() / solve() a full symmetric matrix of its own is served by the same read
+        self.h_upper = True
         self.layers_cache = {}
         self._pending_status = []       # device status words of tensor-core launches, read lazily
         self._pending_info = []         # cuSOLVER potrf info words (non-zero: not positive definite)
@@ -143,7 +151,8 @@ class GPTQ:
         st['versions'] = []
         ptrs = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
         toks = (ctypes.c_int64 * n)(*[x.shape[0] for x in xs])
-        L.call('lc_hessian_accum_multi', ptrs, toks, n, xs[0].shape[1], L.ptr(st['H']), 1.0, 1.0, self.hessian_ksplit,
+        # only the upper triangle of H is kept (half the epilogue's atomic adds); its readers fetch (i, j) from it
+        L.call('lc_hessian_accum_upper', ptrs, toks, n, xs[0].shape[1], L.ptr(st['H']), 1.0, 1.0, self.hessian_ksplit,
                L.ptr(st['status']), L.stream_of(xs[0]))
         st['pending'] = []
 
@@ -162,6 +171,11 @@ class GPTQ:
         return st['H'], 2.0 / n
 
     # ---- solver ----------------------------------------------------------------------------
+    @staticmethod
+    def hessian_full(H_upper):
+        """The full symmetric matrix of a Hessian kept as its upper triangle."""
+        return torch.triu(H_upper) + torch.triu(H_upper, 1).t()
+
     @torch.no_grad()
     def layer_transform(self, layer, name, rows=None):
         """Quantises `layer` in place like the reference: weight.data becomes the fp32
@@ -243,10 +257,14 @@ class GPTQ:
             invperm = torch.argsort(perm)
         Hp = torch.empty((C, C), dtype=torch.float32, device=H.device)
         scratch = torch.empty(4, dtype=torch.float32, device=H.device)
-        native = self.factorization in ('native', 'native_full') and C % 128 == 0
-        direct = native or self.factorization in ('direct', 'native', 'native_full')
+        mode = self.factorization
+        if mode == 'auto':
+            mode = 'native_full' if C >= self.own_cholesky_min else 'native'
+        native = mode in ('native', 'native_full') and C % 128 == 0
+        direct = native or mode in ('direct', 'native', 'native_full')
         L.call('lc_gptq_permute_damp', None, L.LC_F32, L.ptr(H), L.ptr(perm), 0, C, float(hscale),
-               float(self.percdamp), int(direct), None, L.ptr(Hp), L.ptr(scratch), L.stream_of(H))
+               float(self.percdamp), (L.LC_H_REVERSE if direct else 0) | (L.LC_H_UPPER if self.h_upper else 0), None,
+               L.ptr(Hp), L.ptr(scratch), L.stream_of(H))
         want_lo = self.trailing == 'tensor' and C % 128 == 0 and C > 1024
         fac = {'H': H, 'perm': perm, 'invperm': invperm, 'U': None, 'U_lo': None, 'n_out': int(n_out)}
         if native:
@@ -257,7 +275,7 @@ class GPTQ:
             ws_floats = int(L.lib.lc_gptq_factor_workspace_floats(C))
             ws = self._workspace(ws_floats, H.device)
             status = torch.zeros(1, dtype=torch.int32, device=H.device)
-            if self.factorization == 'native_full':
+            if mode == 'native_full':
                 L.call('lc_gptq_factorize', L.ptr(Hp), C, L.ptr(U), L.ptr(U_lo), L.ptr(ws), ws_floats,
                        L.ptr(status), L.stream_of(H))
             else:

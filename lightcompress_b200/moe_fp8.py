@@ -65,35 +65,52 @@ class Fp8FakeQuantMoE:
         return w.to(x.dtype), idx
 
     @torch.no_grad()
-    def forward(self, x, a_qdq=True):
-        """x: (tokens, hidden).  Returns the layer output (summed over ranks)."""
-        T = x.shape[0]
+    def forward(self, x, a_qdq=True, grouped=True):
+        """x: (tokens, hidden).  Returns the layer output (summed over ranks).
+
+        The routed tokens are sorted by expert once; the expert boundaries stay on the device as a
+        cumulative offset table, and with grouped=True the three projections of all local experts are one
+        grouped GEMM each (torch.nn.functional.grouped_mm over the offset table), so a single-rank forward
+        never synchronises with the host.  With several ranks the one host read left is the pair of row
+        bounds of this rank's expert slice (it fixes tensor shapes).  grouped=False evaluates expert by
+        expert with F.linear (one host read of the 64 counts)."""
         w, idx = self.route(x)
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         tok = (order // self.top_k)
         e_sorted = flat_e[order]
-        counts = torch.bincount(e_sorted, minlength=self.n_experts).tolist()
-        starts = [0]
-        for c in counts:
-            starts.append(starts[-1] + c)
-        lo, hi = starts[self.e0], starts[self.e1]
+        ends = torch.cumsum(torch.bincount(e_sorted, minlength=self.n_experts), 0)      # device: row ends per expert
+        n_rows = flat_e.numel()
+        if parallel.world()[1] == 1:
+            lo, hi = 0, n_rows
+        else:
+            b = torch.stack([ends[self.e0 - 1] if self.e0 > 0 else ends.new_zeros(()), ends[self.e1 - 1]]).tolist()
+            lo, hi = int(b[0]), int(b[1])
         out = torch.zeros_like(x, dtype=torch.float32)
         if hi > lo:
             xin = x[tok[lo:hi]]
             xq = self.aq.fake_quant_act_dynamic(xin) if a_qdq else xin          # gate_proj / up_proj input
-            hmid = torch.empty((hi - lo, self.inter), dtype=x.dtype, device=x.device)
-            for e in range(self.e0, self.e1):
-                a, b = starts[e] - lo, starts[e + 1] - lo
-                if b > a:
-                    le = e - self.e0
-                    hmid[a:b] = F.silu(F.linear(xq[a:b], self.w_gate[le])) * F.linear(xq[a:b], self.w_up[le])
-            hq = self.aq.fake_quant_act_dynamic(hmid) if a_qdq else hmid         # down_proj input
-            y = torch.empty((hi - lo, self.hidden), dtype=x.dtype, device=x.device)
-            for e in range(self.e0, self.e1):
-                a, b = starts[e] - lo, starts[e + 1] - lo
-                if b > a:
-                    y[a:b] = F.linear(hq[a:b], self.w_down[e - self.e0])
+            if grouped:
+                offs = (ends[self.e0:self.e1] - lo).to(torch.int32)
+                g = F.grouped_mm(xq, self.w_gate.transpose(1, 2), offs=offs)
+                u = F.grouped_mm(xq, self.w_up.transpose(1, 2), offs=offs)
+                hmid = F.silu(g) * u
+                hq = self.aq.fake_quant_act_dynamic(hmid) if a_qdq else hmid     # down_proj input
+                y = F.grouped_mm(hq, self.w_down.transpose(1, 2), offs=offs)
+            else:
+                starts = [0] + ends.tolist()
+                hmid = torch.empty((hi - lo, self.inter), dtype=x.dtype, device=x.device)
+                for e in range(self.e0, self.e1):
+                    a, b = starts[e] - lo, starts[e + 1] - lo
+                    if b > a:
+                        le = e - self.e0
+                        hmid[a:b] = F.silu(F.linear(xq[a:b], self.w_gate[le])) * F.linear(xq[a:b], self.w_up[le])
+                hq = self.aq.fake_quant_act_dynamic(hmid) if a_qdq else hmid
+                y = torch.empty((hi - lo, self.hidden), dtype=x.dtype, device=x.device)
+                for e in range(self.e0, self.e1):
+                    a, b = starts[e] - lo, starts[e + 1] - lo
+                    if b > a:
+                        y[a:b] = F.linear(hq[a:b], self.w_down[e - self.e0])
             wsel = w.reshape(-1)[order][lo:hi].unsqueeze(1)
             out.index_add_(0, tok[lo:hi], (y * wsel).float())
         if self.has_shared:

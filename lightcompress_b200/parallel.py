@@ -72,6 +72,29 @@ def combine_status(words, how):
     return words
 
 
+def sum_and_count(vec, count):
+    """Sums a per-rank partial-sum vector and its element count over the ranks: (vec, total_count).
+    AWQ statistics over token shards: sum |x| per channel with the token count, squared-error sums per
+    grid point with the element count (the reference instead lets the rank with the lowest local loss win,
+    awq.py:256-273; summing is what its single-rank run over all the data computes)."""
+    _, w = world()
+    if w == 1:
+        return vec, count
+    t = torch.cat([vec.reshape(-1).double(), torch.tensor([float(count)], dtype=torch.float64, device=vec.device)])
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return t[:-1].to(vec.dtype).reshape(vec.shape), int(round(float(t[-1].item())))
+
+
+def average_over_ranks(t):
+    """all_reduce(SUM) / world in the tensor's own dtype, in place: the clip thresholds of
+    AutoClipper.run (auto_clip.py:72-76)."""
+    _, w = world()
+    if w > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        t /= w
+    return t
+
+
 def all_gather_packed(packed):
     """packed: (world, ...) contiguous, slot [rank] filled by this rank; on return every slot holds its
     rank's data.  One collective, in place."""

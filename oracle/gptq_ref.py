@@ -42,13 +42,17 @@ def owq_perm(H, n_out):
     return torch.cat([torch.arange(C)[keep], descending_ids[:n_out]])
 
 
-def prepare(W, H, percdamp=0.01, actorder=True, n_out=0):
+def prepare(W, H, percdamp=0.01, actorder=True, n_out=0, perm=None):
     """hessian_sorting + process_hessian_and_weights (gptq.py:58-83, :128-176).
-    Returns permuted fp32 W, upper Cholesky factor U of the damped inverse Hessian, perm, invperm."""
+    Returns permuted fp32 W, upper Cholesky factor U of the damped inverse Hessian, perm, invperm.
+    perm: a column order to use instead of the one sorted from diag(H) (an extension for comparisons
+    that must not depend on how near-equal diagonal entries happen to sort)."""
     W = W.clone().float()
     H = H.clone()
     C = W.shape[1]
-    if n_out:
+    if perm is not None:
+        perm = perm.to(H.device)
+    elif n_out:
         perm = owq_perm(H, n_out)
     else:
         perm = torch.argsort(torch.diag(H), descending=True) if actorder else torch.arange(C, device=H.device)
@@ -126,14 +130,14 @@ def merge_group_qparams(per_group):
 
 
 def quantize_layer(W, H, bit=4, sym=False, group_size=128, blocksize=128,
-                   percdamp=0.01, actorder=True, n_out=0, static_groups=False, granularity='per_group'):
+                   percdamp=0.01, actorder=True, n_out=0, static_groups=False, granularity='per_group', perm=None):
     """layer_transform (gptq.py:114-117, :178-196): returns a dict with the reference's
     per-layer results: weight (compensated, fp32, original column order), buf_scales,
     buf_zeros (permuted-group order), buf_perm, buf_invperm, loss.  n_out > 0 is the owq mode
     (0 < n_out < group_size with C a multiple of group_size, so that the group count stays C / group_size:
     the reference's w_qdq only works then): the outlier columns keep their error-compensated fp32 values
     (gptq.py:186-188)."""
-    Wp, U, perm, invperm = prepare(W, H, percdamp, actorder and not n_out, n_out)
+    Wp, U, perm, invperm = prepare(W, H, percdamp, actorder and not n_out, n_out, perm)
     if granularity == 'per_channel':
         # search_layer_qparams (gptq.py:368-375): the layer's per-channel round-to-nearest qparams for every
         # column -- static groups with one group spanning the row

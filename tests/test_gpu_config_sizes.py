@@ -62,7 +62,7 @@ def _layer_case(R, C, ns, T, seed):
     X = _acts(g, ns, T, C)
     wq = lcb.IntegerQuantizer(4, False, 'per_group', group_size=128)
     solver = lcb.GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128})
-    assert solver.factorization == 'native' and solver.trailing == 'tensor'           # the defaults the bench runs
+    assert solver.factorization == 'auto' and solver.trailing == 'tensor'             # the defaults the bench runs
     layer = torch.nn.Linear(C, R, bias=False, dtype=torch.bfloat16, device='cuda')
     layer.weight.data = W.clone()
     solver.layer_init(layer, 'l')
@@ -74,7 +74,7 @@ def _layer_case(R, C, ns, T, seed):
     st = gptq_ref.hessian_init(C, 'cuda')
     for i in range(ns):
         gptq_ref.add_batch(st, X[i:i + 1])
-    H_kernel = solver.layers_cache['l']['H'] * (2.0 / ns)
+    H_kernel = lcb.GPTQ.hessian_full(solver.layers_cache['l']['H']) * (2.0 / ns)     # add_batch keeps the upper triangle
     H64 = torch.zeros(C, C, dtype=torch.float64, device='cuda')
     for i in range(ns):
         x = X[i].double()
@@ -115,7 +115,7 @@ def _layer_case(R, C, ns, T, seed):
           f'{c - 1:+.2e} (oracle\'s fp32 Hessian: {herr_oracle:.2e}); '
           f'code mismatch perm pinned {mism_pinned:.5%}; not pinned {mism:.5%} with {perm_diff} perm entries '
           f'differing (oracle noise floor: {floor:.5%} with {floor_perm}); recon error {e_got:.6f} vs oracle {e_ref:.6f}')
-    assert herr < 4e-5 and herr_shape < 5e-6
+    assert herr < 2e-5 and herr_shape < 5e-6
     assert mism_pinned < CODE_MISMATCH_MAX
     assert mism < max(CODE_MISMATCH_MAX, 3 * floor)
     assert abs(e_got - e_ref) <= RECON_REL_TOL * e_ref
@@ -162,7 +162,10 @@ def test_gptq_7b_shape_block_against_the_schedule_oracle():
 
     Teacher-forced: every subset's linears are solved from the very tensors the oracle accumulated its
     Hessian from, column order pinned to the oracle's -- the kernels on real block-internal activations
-    (normed hidden states, attention context, SiLU products) at full width; bar 0.1 % per linear.
+    (normed hidden states, attention context, SiLU products) at full width; bar 0.1 % per linear, or
+    the oracle's own noise floor on that input where that is higher (o_proj: a random-init attention
+    averages its values almost uniformly over the positions, which leaves the Hessian of the attention
+    context nearly rank deficient).
     Cascaded: the whole block through GPTQBlockwise (staged plan, fused block ops, defaults).  Code-level
     agreement downstream of the first subset is not a property of any implementation here: a random-init
     attention averages its values almost uniformly, so the o_proj Hessian is nearly rank deficient and a
@@ -193,20 +196,34 @@ def test_gptq_7b_shape_block_against_the_schedule_oracle():
     for subset in lcb.llama_subsets(block):
         names = list(subset)
         xs = capture[names[0]]
+        C = xs[0].shape[-1]
         lin = copy.deepcopy(orig[names[0]]).cuda()
         solver.layer_init(lin, 's')
         for x in xs:
             solver.add_batch(lin, 's', x)
         H, hscale = solver._finish_hessian('s')
-        fac = solver.factorize(H, hscale, perm=results[names[0]]['buf_perm'])
+        perm = results[names[0]]['buf_perm']
+        fac = solver.factorize(H, hscale, perm=perm)
+        # the oracle's own sensitivity on this input, column order pinned as well: its Hessian summed as
+        # sum(x^T x) * 2/n instead of the running mean
+        H_alt = torch.zeros(C, C, device='cuda')
+        for x in xs:
+            x2 = x.reshape(-1, C).float()
+            H_alt += x2.t() @ x2
+        H_alt *= 2.0 / len(xs)
         for name in names:
-            res = solver.solve(orig[name].weight.data.cuda(), H, hscale, factor=fac)
+            W = orig[name].weight.data.cuda()
+            res = solver.solve(W, H, hscale, factor=fac)
             solver.check_status()
             want = gptq_ref.codes_permuted(results[name]).to(torch.int16)
             d = float((res['codes_perm'].to(torch.int16) != want).float().mean())
-            print(f'teacher-forced {name}: code mismatch {d:.5%}')
-            assert d < CODE_MISMATCH_MAX, (name, d)
+            alt = gptq_ref.quantize_layer(W, H_alt, perm=perm)
+            floor = float((gptq_ref.codes_permuted(alt).to(torch.int16) != want).float().mean())
+            print(f'teacher-forced {name}: code mismatch {d:.5%} (oracle noise floor, same pinned order: {floor:.5%})')
+            assert d < max(CODE_MISMATCH_MAX, 3 * floor), (name, d, floor)
+            del alt
         solver.free('s')
+        del H_alt
         capture[names[0]] = None
     del capture
 

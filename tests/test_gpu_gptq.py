@@ -561,3 +561,34 @@ def test_per_channel_wide_vs_oracle():
         # test above has none.
         assert mism < 5 * CODE_MISMATCH_MAX and step <= 1
         assert abs(e_gpu - e_ref) <= RECON_REL_TOL * e_ref
+
+
+def test_hessian_upper_only_equals_the_upper_triangle_of_the_full_update():
+    """lc_hessian_accum_upper: the upper triangle it maintains equals that of lc_hessian_accum_multi (same
+    token split, so the same sums), what lies below the diagonal is not touched, and the solver's readers
+    (lc_gptq_diag, lc_gptq_permute_damp with LC_H_UPPER) see the same matrix."""
+    import ctypes
+    from lightcompress_b200 import _lib as L
+    g = torch.Generator().manual_seed(2300)
+    C = 640
+    xs = [_x(g, 1, T, C)[0].cuda() for T in (512, 300)]
+    ptrs = (ctypes.c_void_p * 2)(*[x.data_ptr() for x in xs])
+    toks = (ctypes.c_int64 * 2)(*[x.shape[0] for x in xs])
+    full = torch.zeros(C, C, device='cuda')
+    up = torch.tril(torch.full((C, C), -7.0, device='cuda'), -1)     # zeros on and above the diagonal, -7 below
+    status = torch.zeros(1, dtype=torch.int32, device='cuda')
+    L.call('lc_hessian_accum_multi', ptrs, toks, 2, C, L.ptr(full), 1.0, 1.0, 1, L.ptr(status), L.stream_of(full))
+    L.call('lc_hessian_accum_upper', ptrs, toks, 2, C, L.ptr(up), 1.0, 1.0, 1, L.ptr(status), L.stream_of(up))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(torch.triu(up), torch.triu(full))
+    assert bool((torch.tril(up, -1) == torch.tril(torch.full((C, C), -7.0, device='cuda'), -1)).all())
+    perm = torch.randperm(C, generator=g).cuda()
+    outs = []
+    for H, flags in ((full, L.LC_H_REVERSE), (up, L.LC_H_REVERSE | L.LC_H_UPPER)):
+        Hp = torch.empty(C, C, device='cuda')
+        scratch = torch.empty(4, device='cuda')
+        L.call('lc_gptq_permute_damp', None, L.LC_F32, L.ptr(H), L.ptr(perm), 0, C, 0.5, 0.01, flags, None, L.ptr(Hp),
+               L.ptr(scratch), L.stream_of(H))
+        outs.append(Hp)
+    assert torch.equal(outs[0], outs[1])

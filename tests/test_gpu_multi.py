@@ -153,3 +153,47 @@ def test_shared_triangular_inverse_equals_the_single_rank_one(tmp_path):
         assert torch.equal(r0[n][0], r0[n][1]), n
         assert torch.equal(r1[n][0], r0[n][0]), n
         assert torch.equal(r0[n][0], torch.triu(r0[n][0]))
+
+
+def _moe_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    from lightcompress_b200.moe_fp8 import Fp8FakeQuantMoE
+    layer = Fp8FakeQuantMoE(hidden=512, inter=256, n_experts=16, n_shared=2, top_k=4, seed=5200,
+                            device=torch.device('cuda', rank))
+    assert (layer.e0, layer.e1) == (8 * rank, 8 * rank + 8) and layer.has_shared == (rank == 0)
+    g = torch.Generator().manual_seed(5201)
+    x = torch.randn(1500, 512, generator=g).to(torch.bfloat16).cuda()
+    layer.quantize_weights()
+    y = layer.forward(x)
+    torch.cuda.synchronize()
+    torch.save(y.cpu(), os.path.join(out_dir, f'moe{rank}.pt'))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_two_rank_expert_sharded_moe_matches_the_oracle(tmp_path):
+    """The FP8 fake-quantised MoE layer with its experts split over two ranks (8 routed experts each, the
+    shared experts on rank 0, one all-reduce of the output): both ranks end with the same output, equal to
+    the oracle's on one GPU up to the order of the bf16-rounded expert sums."""
+    import torch.multiprocessing as mp
+    from lightcompress_b200.moe_fp8 import Fp8FakeQuantMoE
+    from oracle import moe_fp8_ref
+    port = 29400 + (os.getpid() % 200)
+    mp.spawn(_moe_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    y0 = torch.load(os.path.join(str(tmp_path), 'moe0.pt'))
+    y1 = torch.load(os.path.join(str(tmp_path), 'moe1.pt'))
+    assert torch.equal(y0, y1)
+    layer = Fp8FakeQuantMoE(hidden=512, inter=256, n_experts=16, n_shared=2, top_k=4, seed=5200)
+    raw = {k: getattr(layer, k).clone() for k in ('gate', 'w_gate', 'w_up', 'w_down', 's_gate', 's_up', 's_down')}
+    g = torch.Generator().manual_seed(5201)
+    x = torch.randn(1500, 512, generator=g).to(torch.bfloat16).cuda()
+    ref = moe_fp8_ref.moe_forward(x, raw['gate'], raw['w_gate'], raw['w_up'], raw['w_down'], raw['s_gate'],
+                                  raw['s_up'], raw['s_down'], 4)
+    rel = float((y0.float() - ref.cpu().float()).norm() / ref.cpu().float().norm())
+    print(f'two-rank MoE vs oracle: rel diff {rel:.2e}')
+    assert rel < 3e-3

@@ -83,7 +83,11 @@ def _status_worker(rank, world_size, port, out_dir):
     packed = torch.zeros(world_size, 3, 5)
     packed[rank] = rank + 1
     parallel.all_gather_packed(packed)
-    torch.save({'H': H, 'n': n, 'code': code, 'words': words, 'packed': packed}, os.path.join(out_dir, f's{rank}.pt'))
+    # AWQ over token shards: sums of |x| / of squared errors with their counts; averaged clip thresholds
+    sums, cnt = parallel.sum_and_count(torch.tensor([1.0, 2.0, 3.0]) * (rank + 1), 10 * (rank + 1))
+    avg = parallel.average_over_ranks(torch.tensor([2.0, 4.0]) * (rank + 1))
+    torch.save({'H': H, 'n': n, 'code': code, 'words': words, 'packed': packed, 'sums': sums, 'cnt': cnt, 'avg': avg},
+               os.path.join(out_dir, f's{rank}.pt'))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -100,3 +104,6 @@ def test_a_failed_rank_is_seen_by_every_rank(tmp_path):
     assert r0['words'].tolist() == r1['words'].tolist() == [0, -6]
     want = torch.stack([torch.full((3, 5), 1.0), torch.full((3, 5), 2.0)])
     assert torch.equal(r0['packed'], want) and torch.equal(r1['packed'], want)
+    for r in (r0, r1):
+        assert torch.equal(r['sums'], torch.tensor([3.0, 6.0, 9.0])) and r['cnt'] == 30
+        assert torch.equal(r['avg'], torch.tensor([3.0, 6.0]))
