@@ -146,6 +146,14 @@ int lc_gptq_dequant_unpermute(const uint8_t* codes, const float* scales, const f
 int lc_act_range_per_tensor(const void* const* tensors, const int64_t* numels, int count, int dtype,
                             float* min_out, float* max_out, lc_stream_t stream);
 
+/* 2048-bin (any `bins` <= 4096) histograms of a batch of calibration tensors, tensor i over its own range
+ * [mins[i], maxs[i]] (device fp32 arrays) -- the torch.histc(tensor.float(), bins, min, max) calls of
+ * BaseQuantizer.get_static_hist_range (quant.py:461-521), one launch for the whole batch.  Binning as
+ * torch.histc on CUDA: values outside the range (and NaN) are not counted, bin = (int)((x - min) * bins /
+ * (max - min)) in fp32, x == max falls into the last bin.  hist: count x bins fp32, overwritten. */
+int lc_act_hist_per_tensor(const void* const* tensors, const int64_t* numels, int count, int dtype,
+                           const float* mins, const float* maxs, int bins, float* hist, lc_stream_t stream);
+
 /* The moving average of get_static_moving_minmax_range (quant.py:534-538) over the `count` per-tensor
  * values above, in order: m = v[0]; m = m + alpha * (v[i] - m), every op rounded to `dtype` as the
  * reference's 0-dim tensor arithmetic does.  out2[0] = moving min, out2[1] = moving max (fp32 holding

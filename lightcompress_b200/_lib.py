@@ -70,6 +70,7 @@ SIGNATURES = {
     'lc_gptq_dequant_unpermute': [_p, _p, _p, _p, _i64, _i64, _i, _i, _p, _i, _p],
     'lc_act_range_per_tensor': [_p, _p, _i, _i, _p, _p, _p],
     'lc_act_range_moving': [_p, _p, _i, _i, _d, _p, _p],
+    'lc_act_hist_per_tensor': [_p, _p, _i, _i, _p, _p, _i, _p, _p],
     'lc_rtn_w48_fake_quant': [_p, _i, _i64, _i64, _i64, _p, _p, _p, _p],
     'lc_quik_col_absmax': [_p, _i, _i64, _i64, _p, _p],
     'lc_rtn_int_fake_quant_masked': [_p, _i, _i64, _i64, _i, _i, _p, _p, _p],

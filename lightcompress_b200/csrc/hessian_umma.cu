@@ -261,6 +261,48 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
         const int64_t m_blk0 = (int64_t)w.si * ST + h * 128 + q * 32;
         if ((int64_t)w.si * ST + h * 128 >= C) break;
         const int64_t m = m_blk0 + lane;
+        if (a.upper_only) {
+          // upper triangle only: the 32-column chunks strictly right of this warp's rows go out as plain
+          // 128-bit atomic adds, two chunks' tensor-memory loads in flight at a time
+          const uint32_t tbase = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 256);
+          int cc = 0;
+          while (cc < ST / 32 && (int64_t)w.sj * ST + cc * 32 <= m_blk0 && (int64_t)w.sj * ST + cc * 32 < C) {
+            const int64_t n0 = (int64_t)w.sj * ST + cc * 32;
+            if (n0 == m_blk0) {      // the diagonal chunk: element-wise, n >= m
+              float v[32];
+              tmem_ld32(tbase + (uint32_t)(cc * 32), v);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (m < C && n0 + j < C && j >= lane) red_add(a.H + m * C + n0 + j, v[j] * a.alpha);
+            }
+            ++cc;
+          }
+          for (; cc < ST / 32; cc += 2) {
+            const int64_t n0 = (int64_t)w.sj * ST + cc * 32;
+            if (n0 >= C) break;
+            const bool two = cc + 1 < ST / 32 && n0 + 32 < C;
+            uint32_t r0[32], r1[32];
+            tmem_ld32_nowait(tbase + (uint32_t)(cc * 32), r0);
+            if (two) tmem_ld32_nowait(tbase + (uint32_t)(cc * 32 + 32), r1);
+            tmem_wait_ld();
+            if (m < C) {
+              float* row = a.H + m * C + n0;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                if (n0 + j < C)
+                  red_add_v4(row + j, __uint_as_float(r0[j]) * a.alpha, __uint_as_float(r0[j + 1]) * a.alpha,
+                             __uint_as_float(r0[j + 2]) * a.alpha, __uint_as_float(r0[j + 3]) * a.alpha);
+              if (two) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  if (n0 + 32 + j < C)
+                    red_add_v4(row + 32 + j, __uint_as_float(r1[j]) * a.alpha, __uint_as_float(r1[j + 1]) * a.alpha,
+                               __uint_as_float(r1[j + 2]) * a.alpha, __uint_as_float(r1[j + 3]) * a.alpha);
+              }
+            }
+          }
+          continue;
+        }
 #pragma unroll 1
         for (int cc = 0; cc < ST / 32; ++cc) {
           const int64_t n0 = (int64_t)w.sj * ST + cc * 32;
@@ -278,7 +320,6 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
               for (int j = 0; j < 32; j += 4)
                 if (n0 + j < C) red_add_v4(row + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
-            if (a.upper_only) continue;
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 32; ++j) stg[j * STG_STRIDE + lane] = v[j];
@@ -299,7 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
               const int64_t nn = n0 + j;
               if (m < C && nn < C) {
                 if (j >= lane) red_add(a.H + m * C + nn, v[j]);
-                if (j > lane && !a.upper_only) red_add(a.H + nn * C + m, v[j]);
+                if (j > lane) red_add(a.H + nn * C + m, v[j]);
               }
             }
           }

@@ -16,7 +16,7 @@ import torch
 from . import _lib as L
 
 _INT_GRANS = ('per_group', 'per_channel', 'per_token')
-_STATIC_ALGOS = ('static_minmax', 'static_moving_minmax')
+_STATIC_ALGOS = ('static_minmax', 'static_moving_minmax', 'static_hist')
 
 
 class BaseQuantizer(object):
@@ -40,6 +40,8 @@ class BaseQuantizer(object):
         self.mse_grid = kwargs.get('mse_grid', 100)
         self.ste = kwargs.get('ste', False)
         self.ste_all = bool(kwargs.get('ste_all', False))
+        self.bins = kwargs.get('bins', 2048)          # static_hist (quant.py:83-87)
+        self.upsample_rate = 16
 
     def _check_supported(self, allow_mse=False, per_tensor=False):
         """per_tensor: the caller is one of the static per-tensor activation methods."""
@@ -363,14 +365,39 @@ class IntegerQuantizer(BaseQuantizer):
             maxs_out.append(out2[1].to(ts[0].dtype))
         return mins_out, maxs_out
 
+    def get_static_hist_range(self, act_tensors):
+        """quant.py:461-521.  Per input: the tensors' ranges (one launch), the running range after each
+        tensor (two tiny cumulative ops on the per-tensor values), every tensor's 2048-bin histogram over its
+        running range (one launch over the whole batch; the reference calls torch.histc per tensor on an
+        fp32 copy), then the reference's own host-side histogram merging and threshold search (hist.py)."""
+        from . import hist as HH
+        mins_out, maxs_out = [], []
+        for tensors in self.reshape_batch_tensors(act_tensors):
+            mins, maxs, ts = self._tensor_ranges(list(tensors))
+            run_min, run_max = torch.cummin(mins, 0).values, torch.cummax(maxs, 0).values
+            n = len(ts)
+            hists = torch.empty((n, self.bins), dtype=torch.float32, device=mins.device)
+            ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
+            numels = (ctypes.c_int64 * n)(*[t.numel() for t in ts])
+            L.call('lc_act_hist_per_tensor', ptrs, numels, n, L.lc_dtype(ts[0]), L.ptr(run_min), L.ptr(run_max),
+                   int(self.bins), L.ptr(hists), L.stream_of(ts[0]))
+            hists, run_min, run_max = hists.cpu(), run_min.cpu(), run_max.cpu()
+            new_min, new_max = HH.static_hist_range([hists[i] for i in range(n)], run_min, run_max, self.bins,
+                                                    self.upsample_rate, self.dst_nbins)
+            mins_out.append(new_min)
+            maxs_out.append(new_max)
+        return mins_out, maxs_out
+
     def get_batch_tensors_qparams(self, act_tensors, alpha=0.01, args={}):
-        """quant.py:560-585 ('static_hist' is not built)."""
-        if self.calib_algo == 'static_minmax':
+        """quant.py:560-585."""
+        if self.calib_algo == 'static_hist':
+            assert self.sym is True and self.granularity == 'per_tensor', \
+                'Only support per tensor static symmetric int quantize.'
+            min_vals, max_vals = self.get_static_hist_range(act_tensors)
+        elif self.calib_algo == 'static_minmax':
             min_vals, max_vals = self.get_static_minmax_range(act_tensors)
         elif self.calib_algo == 'static_moving_minmax':
             min_vals, max_vals = self.get_static_moving_minmax_range(act_tensors, alpha)
-        elif self.calib_algo == 'static_hist':
-            raise NotImplementedError("calib_algo 'static_hist' is outside the B200 hot path")
         else:
             raise ValueError(f'Unsupported calibration algorithm: {self.calib_algo}')
         scales_list, zeros_list, qmin_list, qmax_list = [], [], [], []

@@ -221,9 +221,121 @@ def static_moving_minmax_range(act_tensors, alpha=0.01):
     return mins, maxs
 
 
+def _hist_quantization_error(histogram, min_val, max_val, next_start_bin, next_end_bin, bins, dst_nbins):
+    """get_quantization_error with get_norm (quant.py:264-330)."""
+    bin_width = (max_val.item() - min_val.item()) / bins
+    dst_bin_width = bin_width * (next_end_bin - next_start_bin + 1) / dst_nbins
+    if dst_bin_width == 0.0:
+        return 0.0
+
+    def get_norm(delta_begin, delta_end, density):
+        norm = (delta_end * delta_end * delta_end - delta_begin * delta_begin * delta_begin) / 3
+        return density * norm
+    src_bin = torch.arange(bins, device=histogram.device)
+    src_bin_begin = (src_bin - next_start_bin) * bin_width
+    src_bin_end = src_bin_begin + bin_width
+    dst_bin_of_begin = torch.clamp(torch.div(src_bin_begin, dst_bin_width, rounding_mode='floor'), 0, dst_nbins - 1)
+    dst_bin_of_begin_center = (dst_bin_of_begin + 0.5) * dst_bin_width
+    dst_bin_of_end = torch.clamp(torch.div(src_bin_end, dst_bin_width, rounding_mode='floor'), 0, dst_nbins - 1)
+    density = histogram / bin_width
+    norm = torch.zeros(bins, device=histogram.device)
+    delta_begin = src_bin_begin - dst_bin_of_begin_center
+    delta_end = dst_bin_width / 2
+    norm += get_norm(delta_begin, torch.ones(bins, device=histogram.device) * delta_end, density)
+    norm += (dst_bin_of_end - dst_bin_of_begin - 1) * get_norm(
+        torch.tensor(-dst_bin_width / 2), torch.tensor(dst_bin_width / 2), density)
+    dst_bin_of_end_center = dst_bin_of_end * dst_bin_width + dst_bin_width / 2
+    delta_begin = -dst_bin_width / 2
+    delta_end = src_bin_end - dst_bin_of_end_center
+    norm += get_norm(torch.tensor(delta_begin), delta_end, density)
+    return norm.sum().item()
+
+
+def _hist_threshold(histogram, min_val, max_val, bins, dst_nbins):
+    """get_hist_threshold (quant.py:402-459)."""
+    bin_width = (max_val - min_val) / bins
+    total = torch.sum(histogram).item()
+    cSum = torch.cumsum(histogram, dim=0)
+    stepsize, alpha, beta = 1e-8, 0.0, 1.0
+    start_bin, end_bin, norm_min = 0, bins - 1, float('inf')
+    while alpha < beta:
+        next_alpha, next_beta = alpha + stepsize, beta - stepsize
+        left, right = start_bin, end_bin
+        while left < end_bin and cSum[left] < next_alpha * total:
+            left = left + 1
+        while right > start_bin and cSum[right] > next_beta * total:
+            right = right - 1
+        next_start_bin, next_end_bin = start_bin, end_bin
+        if (left - start_bin) > (end_bin - right):
+            next_start_bin = left
+            alpha = next_alpha
+        else:
+            next_end_bin = right
+            beta = next_beta
+        if next_start_bin == start_bin and next_end_bin == end_bin:
+            continue
+        norm = _hist_quantization_error(histogram, min_val, max_val, next_start_bin, next_end_bin, bins, dst_nbins)
+        if norm > norm_min:
+            break
+        norm_min, start_bin, end_bin = norm, next_start_bin, next_end_bin
+    return min_val + bin_width * start_bin, min_val + bin_width * (end_bin + 1)
+
+
+def _hist_combine(orig_hist, orig_min, orig_max, update_hist, update_min, update_max, bins, upsample_rate=16):
+    """_combine_histograms with _upscale_histogram (quant.py:332-400)."""
+    if update_min == orig_min and update_max == orig_max:
+        return orig_hist + update_hist
+    if orig_min == orig_max:
+        bin_value = torch.sum(update_hist)
+        return torch.histc(orig_min, bins=bins, min=update_min, max=update_max) * bin_value + update_hist
+    assert update_min <= orig_min and update_max >= orig_max
+    histogram = orig_hist.repeat_interleave(upsample_rate) / upsample_rate
+    bin_size = (orig_max - orig_min) / (bins * upsample_rate)
+    mid_points = (torch.linspace(orig_min, orig_max, bins * upsample_rate + 1, device=orig_min.device)[:-1]
+                  .to(histogram.device) + 0.5 * bin_size)
+    boundaries = torch.linspace(update_min, update_max, bins + 1, device=update_min.device).to(histogram.device)
+    bucket = torch.bucketize(mid_points, boundaries, right=True) - 1
+    bucket[bucket >= bins] = bins - 1
+    bucket[bucket < 0] = 0
+    return update_hist + torch.bincount(bucket, weights=histogram, minlength=bins)
+
+
+def static_hist_range(act_tensors, bit, bins=2048):
+    """get_static_hist_range (quant.py:461-521), per_tensor: per input, a running 2048-bin histogram over the
+    calibration tensors (torch.histc on each tensor's fp32 copy, on the tensor's device; the running
+    histogram itself lives on the CPU), then the threshold search."""
+    dst_nbins = 2 ** bit
+    mins_out, maxs_out = [], []
+    for tensors in reshape_batch_tensors(act_tensors):
+        t_min = [t.min().detach().cpu().to(torch.float32) for t in tensors]       # get_minmax_stats
+        t_max = [t.max().detach().cpu().to(torch.float32) for t in tensors]
+        min_val = max_val = None
+        histogram = torch.zeros(bins)
+        for idx, tensor in enumerate(tensors):
+            tensor = tensor.float()
+            x_min, x_max = t_min[idx], t_max[idx]
+            if min_val is None:
+                histogram = torch.histc(tensor, bins, min=x_min.item(), max=x_max.item()).cpu()
+                min_val, max_val = x_min, x_max
+            else:
+                new_min, new_max = torch.min(min_val, x_min), torch.max(max_val, x_max)
+                update = torch.histc(tensor, bins, min=new_min.item(), max=new_max.item()).cpu()
+                if new_min == min_val and new_max == max_val:
+                    histogram = histogram + update
+                else:
+                    histogram = _hist_combine(histogram, min_val, max_val, update, new_min, new_max, bins)
+                min_val, max_val = new_min, new_max
+        new_min, new_max = _hist_threshold(histogram, min_val, max_val, bins, dst_nbins)
+        mins_out.append(new_min)
+        maxs_out.append(new_max)
+    return mins_out, maxs_out
+
+
 def batch_tensors_qparams(act_tensors, bit, sym, calib_algo, alpha=0.01):
-    """get_batch_tensors_qparams (quant.py:560-585) for 'static_minmax' / 'static_moving_minmax'."""
-    if calib_algo == 'static_minmax':
+    """get_batch_tensors_qparams (quant.py:560-585)."""
+    if calib_algo == 'static_hist':
+        mins, maxs = static_hist_range(act_tensors, bit)
+    elif calib_algo == 'static_minmax':
         mins, maxs = static_minmax_range(act_tensors)
     elif calib_algo == 'static_moving_minmax':
         mins, maxs = static_moving_minmax_range(act_tensors, alpha)

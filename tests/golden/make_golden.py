@@ -140,6 +140,26 @@ def make_act_static(rq, out_dir):
     print('act_static.pt', len(cases), 'cases')
 
 
+def make_act_hist(rq, out_dir):
+    """calib_algo 'static_hist' (symmetric per_tensor int8): get_batch_tensors_qparams over a batch whose
+    running range widens twice (so that histograms are re-binned), then fake_quant_act_static."""
+    gen = torch.Generator().manual_seed(2008)
+    cases = {}
+    for dtype in (torch.bfloat16, torch.float32):
+        scales = (1.0, 0.6, 1.4, 1.0, 2.2, 0.9)
+        acts = [(torch.randn(2, 40, 128, generator=gen) * sc).to(dtype) for sc in scales]
+        acts[1][0, 0, 0] = 0.25            # a tensor whose range lies inside the running one
+        qz = rq.IntegerQuantizer(8, True, 'per_tensor', calib_algo='static_hist')
+        mins, maxs = qz.get_static_hist_range([a.clone() for a in acts])
+        sl, zl, qminl, qmaxl = qz.get_batch_tensors_qparams([a.clone() for a in acts])
+        x = (torch.randn(2, 9, 128, generator=gen) * 1.5).to(dtype)
+        fq = qz.fake_quant_act_static(x.clone(), {'scales': sl[0], 'zeros': zl[0], 'qmax': qmaxl[0], 'qmin': qminl[0]})
+        cases[str(dtype).split('.')[-1]] = dict(acts=acts, dtype=dtype, min=mins[0], max=maxs[0], scales=sl[0],
+                                                 x=x, fake=fq)
+    torch.save(cases, os.path.join(out_dir, 'act_hist.pt'))
+    print('act_hist.pt', len(cases), 'cases')
+
+
 W48_BIT4 = {'symmetric': False, 'granularity': 'per_group', 'group_size': 128, 'scales_bit': 8,
             'scales_symmetric': True, 'zeros_bit': 8, 'zeros_symmetric': True}
 W48_BIT8 = {'symmetric': True, 'granularity': 'per_channel', 'int_range': [-120, 120]}
@@ -541,7 +561,7 @@ if __name__ == '__main__':
              'gptq': lambda: make_gptq(rq, rg, out_dir), 'gptq_owq': lambda: make_gptq_owq(rq, rg, out_dir),
              'gptq_per_channel': lambda: make_gptq_per_channel(rq, rg, out_dir),
              'gptq_static': lambda: make_gptq_static(rq, rg, out_dir),
-             'quik': lambda: make_quik(rq, out_dir), 'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
+             'quik': lambda: make_quik(rq, out_dir), 'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'act_hist': lambda: make_act_hist(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
              'export': lambda: make_export_configs(ref_root, out_dir),
              'gptq_block': lambda: make_gptq_block(ref_root, out_dir)}
     for name, step in steps.items():

@@ -134,3 +134,53 @@ def test_range_kernel_bandwidth():
     print(f'lc_act_range_per_tensor: {ms:.3f} ms for {nbytes / 1e9:.2f} GB = {nbytes / ms / 1e6:.0f} GB/s; '
           f'torch.max + torch.min per tensor: {ms_t:.3f} ms')
     assert ms < ms_t
+
+
+def test_histogram_kernel_equals_torch_histc_on_this_gpu():
+    """lc_act_hist_per_tensor against torch.histc on the same GPU (what the reference calls there), bin
+    for bin: ranges wider than the data, equal to it (x == max lands in the last bin), and narrower."""
+    import ctypes
+    from lightcompress_b200 import _lib as L
+    g = torch.Generator().manual_seed(2400)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        ts = [(torch.randn(n, generator=g) * sc).to(dtype).cuda() for n, sc in ((300001, 1.0), (4096, 3.0), (77, 0.5),
+                                                                                (1 << 21, 1.7))]
+        mins = torch.tensor([float(ts[0].min()), -20.0, float(ts[2].min()), -2.0], device='cuda')
+        maxs = torch.tensor([float(ts[0].max()), 25.0, float(ts[2].max()), 2.5], device='cuda')
+        n = len(ts)
+        hist = torch.empty((n, 2048), device='cuda')
+        ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
+        numels = (ctypes.c_int64 * n)(*[t.numel() for t in ts])
+        L.call('lc_act_hist_per_tensor', ptrs, numels, n, L.lc_dtype(ts[0]), L.ptr(mins), L.ptr(maxs), 2048,
+               L.ptr(hist), L.stream_of(ts[0]))
+        for i, t in enumerate(ts):
+            want = torch.histc(t.float(), 2048, min=float(mins[i]), max=float(maxs[i]))
+            assert torch.equal(hist[i], want), (dtype, i, int((hist[i] != want).sum()))
+
+
+def test_static_hist_qparams_match_oracle_and_golden(golden):
+    """calib_algo 'static_hist' end to end: the searched range, the scale and the fake-quantised activations
+    against the oracle evaluated on the same GPU (torch.histc there), and against the reference's CPU
+    fixture where CPU and CUDA histc bin alike."""
+    from lightcompress_b200 import IntegerQuantizer
+    for key, c in golden('act_hist.pt').items():
+        acts = [a.cuda() for a in c['acts']]
+        qz = IntegerQuantizer(8, True, 'per_tensor', calib_algo='static_hist')
+        mins, maxs = qz.get_static_hist_range([a.clone() for a in acts])
+        rmin, rmax = quant_ref.static_hist_range([a.clone() for a in acts], 8)
+        assert torch.equal(mins[0], rmin[0]) and torch.equal(maxs[0], rmax[0]), (key, mins, rmin, maxs, rmax)
+        sl, zl, qminl, qmaxl = qz.get_batch_tensors_qparams([a.clone() for a in acts])
+        (s, z, qmax, qmin), = quant_ref.batch_tensors_qparams([a.clone() for a in acts], 8, True, 'static_hist')
+        assert torch.equal(sl[0].cpu(), s.cpu())
+        fq = qz.fake_quant_act_static(c['x'].cuda(), {'scales': sl[0], 'zeros': zl[0], 'qmax': qmaxl[0], 'qmin': qminl[0]})
+        same = bool(torch.equal(sl[0].cpu(), c['scales']))
+        print(f'static_hist {key}: range [{float(mins[0]):.5f}, {float(maxs[0]):.5f}], scale equal to the CPU fixture: {same}')
+        # the static fake quant against the stock tensor ops with the scale as a 0-dim CUDA buffer (how the
+        # reference holds it at deploy time; its CUDA kernels cast such a scale to the activation dtype, its
+        # CPU kernels do not, so the CPU fixture only applies to fp32 activations)
+        s_dev = sl[0].cuda()
+        xq = c['x'].cuda()
+        stock = torch.clamp(torch.round(xq / s_dev), qminl[0].cuda(), qmaxl[0].cuda()) * s_dev
+        assert torch.equal(fq, stock.to(fq.dtype))
+        if same and c['dtype'] == torch.float32:
+            assert torch.equal(fq.cpu(), c['fake'])

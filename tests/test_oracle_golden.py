@@ -232,3 +232,15 @@ def test_gptq_block_schedule_oracle_matches_the_references_run_block_loop(golden
                 assert got[k].dtype == want[k].dtype and torch.equal(got[k], want[k]), (bi, name, k)
     for a, b in zip(inputs, c['next_inputs']):
         assert torch.equal(a, b)
+
+
+def test_static_hist_oracle_matches_reference(golden):
+    """calib_algo 'static_hist': the searched range and the resulting scale of the reference's
+    get_static_hist_range / get_batch_tensors_qparams, bit for bit."""
+    for key, c in golden('act_hist.pt').items():
+        mins, maxs = quant_ref.static_hist_range([a.clone() for a in c['acts']], 8)
+        _eq(mins[0], c['min'])
+        _eq(maxs[0], c['max'])
+        (s, z, qmax, qmin), = quant_ref.batch_tensors_qparams([a.clone() for a in c['acts']], 8, True, 'static_hist')
+        _eq(s, c['scales'])
+        assert c['max'] < max(a.max() for a in c['acts']).float()       # the search did clip the range
