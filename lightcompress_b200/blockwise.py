@@ -142,6 +142,7 @@ class GPTQBlockwise:
         # of argsort(diag H), whose order among near-equal entries is implementation-defined (gptq.py:63
         # uses an unstable sort).  For reproducing an earlier run or comparing two implementations.
         self.pinned_perms = dict(special.get('pinned_perms') or {})
+        self.used_perms = {}     # {first linear of a subset: the column order its solve used} of the last block
         self.true_sequential = self.solver.true_sequential
         # A re-forward whose only purpose is to feed the hooks of one subset stops as soon as that
         # subset's input has been seen: the rest of the block computes values nobody reads.
@@ -216,7 +217,8 @@ class GPTQBlockwise:
         for layer, n in zip(layers, names):
             by_n_out.setdefault(self.solver.n_out_of(n), []).append(layer)
         for n_out, group in by_n_out.items():
-            self._solve_group(group, H, hscale, n_out, rank, world, self.pinned_perms.get(names[0]))
+            fac = self._solve_group(group, H, hscale, n_out, rank, world, self.pinned_perms.get(names[0]))
+            self.used_perms[names[0]] = fac['perm']
         for n in names:
             self.solver.layers_cache.pop(n, None)
         if self.on_subset_done is not None:
@@ -252,6 +254,7 @@ class GPTQBlockwise:
                 part['codes_perm'] = res['codes_perm'][r0:r1]
             self.solver._install(layer, part)
             r0 = r1
+        return fac
 
     def _sharded_solve(self, stacked, fac, rank, world, static=None):
         """Row range `rank` of the stacked weight solved here, then ONE all-gather per subset: every

@@ -19,11 +19,15 @@ def _worker(rank, world, port, out_dir, extra=None):
     import copy
     from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer, llama_subsets, parallel
     from tests.test_gpu_blockwise import _make_block, _to_cuda
-    block, xs, kwargs = _make_block()
+    extra = dict(extra or {})
+    block, xs, kwargs = _make_block(**extra.pop('_block', {}))
     b, e = parallel.sequence_shard(len(xs))
     wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
-    runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4},
-                                    **(extra or {})))
+    pins = os.path.join(out_dir, 'pins.pt')
+    if os.path.exists(pins):
+        # column orders of the single-GPU run: act-order near-ties must not decide the comparison
+        extra['pinned_perms'] = {k: v.cuda() for k, v in torch.load(pins).items()}
+    runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4}, **extra))
     gblock = copy.deepcopy(block).cuda()
     outs = runner.block_opt(gblock, [x.cuda() for x in xs[b:e]], _to_cuda(kwargs))
     torch.cuda.synchronize()
@@ -80,36 +84,36 @@ def test_two_rank_block_matches_single_gpu(tmp_path):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
 def test_two_rank_static_groups_block_matches_single_gpu(tmp_path):
     """static_groups through the row-sharded solve: the ranks agree exactly, the buffers are every
-    linear's round-to-nearest ones, and the quantised block's outputs match the single-GPU run."""
+    linear's round-to-nearest ones, and with every subset's column order pinned to the single-GPU run's
+    (near-equal Hessian diagonals of this small random block would otherwise sort differently after the
+    all-reduce changes the last bits) fewer than 0.1 % of the deployed weights differ, linear by linear."""
     import copy
     import torch.multiprocessing as mp
     from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer
     from tests.test_gpu_blockwise import _make_block, _to_cuda
     port = 29900 + (os.getpid() % 100)
+    # 32 sequences of 384 tokens: 24 tokens per column of the widest linear, a well-conditioned Hessian
+    shape = {'T': 384, 'n_seq': 32}
     extra = {'static_groups': True}
-    mp.spawn(_worker, args=(2, port, str(tmp_path), extra), nprocs=2, join=True)
+    block, xs, kwargs = _make_block(**shape)
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4}, **extra))
+    gblock = copy.deepcopy(block).cuda()
+    outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
+    torch.save({k: v.cpu() for k, v in runner.used_perms.items()}, os.path.join(str(tmp_path), 'pins.pt'))
+    mp.spawn(_worker, args=(2, port, str(tmp_path), dict(extra, _block=shape)), nprocs=2, join=True)
     r0 = torch.load(os.path.join(str(tmp_path), 'r0.pt'))
     r1 = torch.load(os.path.join(str(tmp_path), 'r1.pt'))
     for name in r0['state']:
         for k in r0['state'][name]:
             assert torch.equal(r0['state'][name][k], r1['state'][name][k]), (name, k)
         assert r0['state'][name]['buf_scales'].dtype == torch.bfloat16
-    block, xs, kwargs = _make_block()
-    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
-    runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4}, **extra))
-    gblock = copy.deepcopy(block).cuda()
-    outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
     for name, m in gblock.named_modules():
         if name in r0['state']:
             assert torch.equal(m.buf_scales.cpu(), r0['state'][name]['buf_scales']), name
             mism = float((m.tmp_weight.cpu() != r0['state'][name]['tmp_weight']).float().mean())
             print(f'{name}: 1-GPU vs 2-GPU deployed weights differing {mism:.4%}')
-            # q / k / v read the same input in both runs: the sharded solve itself must reproduce the
-            # single-GPU result.  Later linears see inputs that differ in the last bits (summation order of
-            # the all-reduced Hessians upstream), which on this tiny random block can reorder near-equal
-            # act-order columns; for them the bar is the block output below.
-            assert mism < (1e-3 if 'self_attn.q' in name or 'self_attn.k' in name or 'self_attn.v' in name else 0.1), (
-                name, mism)
+            assert mism < 1e-3, (name, mism)
     full = torch.cat([o.cpu() for o in outs]).float()
     both = torch.cat(r0['outs'] + r1['outs']).float()
     assert float((full - both).norm() / full.norm()) < 1e-2
