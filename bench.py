@@ -527,6 +527,12 @@ def kernel_case(name, n):
     from lightcompress_b200 import _lib as L
     wq4 = lc.IntegerQuantizer(4, False, 'per_group', group_size=128)
 
+    def hessian_call(X, T, H, status):
+        # the entry point GPTQ.add_batch's replacement uses: only the upper triangle of H is maintained
+        import ctypes
+        ptrs, toks = (ctypes.c_void_p * 1)(X.data_ptr()), (ctypes.c_int64 * 1)(T)
+        L.call('lc_hessian_accum_upper', ptrs, toks, 1, X.shape[1], L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
+
     def hessian(C, seed):
         T = 16384
         g = torch.Generator().manual_seed(seed)
@@ -534,14 +540,14 @@ def kernel_case(name, n):
         H = torch.zeros(C, C, device='cuda')
         status = torch.zeros(1, dtype=torch.int32, device='cuda')
         for _ in range(n):
-            L.call('lc_hessian_accum', L.ptr(X), T, C, L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
+            hessian_call(X, T, H, status)
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         return X, H, status
     if name == 'hessian':
         X, H, status = hessian(4096, 1)
         for _ in range(n):
-            L.call('lc_hessian_accum', L.ptr(X), 2048, 4096, L.ptr(H), 1.0, 1.0, 0, L.ptr(status), L.stream_of(X))
+            hessian_call(X, 2048, H, status)
     elif name == 'hessian_wide':                      # the down_proj width, 16384 tokens per launch
         hessian(11008, 5)
     elif name in ('factor', 'factor_wide', 'factor_cusolver'):   # damp + Cholesky + triangular inverse of one Hessian
@@ -784,22 +790,17 @@ def main():
     extra_cfg = {}
 
     def blocks_per_step_launches(n_calls):
-        # kernels of this library per decoder block (torch's own kernels -- cuBLAS GEMMs of the forward,
-        # cuSOLVER potrf, SDPA, argsort, gathers -- are not counted):
-        #   Hessian launches, 4 diag; per distinct Hessian (3 x C=4096, 1 x C=11008): damp + permute,
-        #   low-part split, leaf inverse, flip, and 5 launches (2 GEMMs, 2 splits, 1 transpose) per internal
-        #   node of the recursive triangular inverse (C/128 - 1 nodes);
-        #   per subset (the rows of its linears are solved as one stacked matrix): permute W, un-permute, and
-        #   per 128-column block the block kernel plus the eager / sub-panel / panel updates counted below;
-        #   per linear the deploy-time fake quant;
-        #   per sequence: 2 RMS norms, 2 rotary embeddings, 1 SiLU-gate.
-        def solver_launches(c):
-            blocks, subs, panels = -(-c // 128), -(-c // 256), -(-c // 1024)
-            return blocks + (blocks - subs) + (subs - panels) + (panels - 1)
-        return (4 * -(-n_calls // HESSIAN_BATCH) + 4
-                + sum(2 + 1 + 1 + 1 + 5 * (c // 128 - 1) for c in (HID, HID, HID, INTER))
-                + sum(2 + solver_launches(c) for c in (HID, HID, HID, INTER)) + len(LINEAR_SHAPES)
-                + 5 * n_calls)
+        # Kernels of this library per decoder block (torch's own kernels -- cuBLAS GEMMs of the forward, cuSOLVER
+        # potrf of the three 4096-wide Hessians, SDPA, argsort, residual adds -- are not counted).  Per sequence:
+        # 2 RMS norms, 2 rotary embeddings, 1 SiLU-gate.  Per Hessian batch and subset: one accumulation launch.
+        # The rest is fixed by the shapes (3 Hessians of width 4096, one of 11008; 182 column blocks) and was
+        # counted from the ncu launch list of this very workload (profiles/bench_block_workload_launch_list.md):
+        # 4 x (diag, damp, permute H, flip, permute W, un-permute), 7 deploy-time dequantisations, 182 in-block
+        # kernels, 91 eager FFMA updates, 152 tensor-core GEMMs (triangular inverses + sub-panel / panel updates)
+        # with 47 low-part splits and 22 transposes, 3 leaf-inverse launches, and the own Cholesky of the
+        # 11008-wide Hessian: 86 leaf + 85 panel + 64 strip launches.
+        fixed = 4 * 6 + 7 + 182 + 91 + 152 + 47 + 22 + 3 + 86 + 85 + 64
+        return 5 * n_calls + 4 * -(-n_calls // HESSIAN_BATCH) + fixed
 
     def fresh_host_block(block_host):
         """New module objects over the same (pinned) parameter storage: a step must not see the quantised
