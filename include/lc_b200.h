@@ -274,11 +274,15 @@ int lc_gptq_diag(const float* H, int64_t cols, float* diag_out, lc_stream_t stre
  *           upper factor of the inverse (see lc_gptq_flip); Wp is not affected.
  *           bit 1 (LC_H_UPPER): only the upper triangle of H is valid (lc_hessian_accum_upper); entry
  *           (i, j) is read from H[min(i,j)][max(i,j)].  Hp is a full symmetric matrix either way
+ *           bit 2 (LC_H_LATE_DEAD): SpQR's order of operations (llmc/compression/quantization/spqr.py:143-149):
+ *           damp = percdamp * mean|diag| with the dead columns counted as 0, and a dead column's diagonal
+ *           becomes exactly 1 instead of 1 + damp
  *   scratch: at least 1 float (receives damp)
  * W/Wp may both be NULL (only the Hessian part runs: one factorisation serves every linear that
  * shares the input) and Hp may be NULL (only the weight gather runs). */
 #define LC_H_REVERSE 1
 #define LC_H_UPPER 2
+#define LC_H_LATE_DEAD 4
 int lc_gptq_permute_damp(const void* W, int w_dtype, const float* H, const int64_t* perm,
                          int64_t rows, int64_t cols, float hscale, float percdamp, int reverse_h,
                          float* Wp, float* Hp, float* scratch, lc_stream_t stream);
@@ -403,6 +407,38 @@ int lc_gptq_weight_transform_tc_owq(float* W, const float* U, const float* U_lo,
                                     int64_t n_quant, int bits, int sym, float* scratch_err, float* panel_hi,
                                     float* panel_lo, float* scales, float* zeros, uint8_t* codes_u8,
                                     float* loss_rows, int32_t* status, lc_stream_t stream);
+
+/* SpQR.weight_transform (llmc/compression/quantization/spqr.py:184-285): the GPTQ block loop with groups
+ * of 16 columns (the reference's spqr_w_only.yml), asymmetric `bits`-bit codes with unrounded zero points
+ * (round_zp False, quant.py:544-558, :698-711), the second-level quantisation of every group's scale and
+ * zero point (spqr.py:325-346), leave-one-out outlier detection per group (spqr.py:185-203, unless
+ * `simplified`) and outliers kept unquantised (spqr.py:262-267).
+ *   W          rows x cols fp32 (permuted order), updated in place: on return the kept (error-compensated,
+ *              unquantised) values, the reference's `tmp`
+ *   U          cols x cols fp32 upper Cholesky factor of the damped inverse Hessian
+ *   U_lo       lc_gptq_split_tf32(U), or NULL: with it the trailing update is batched over 256- and
+ *              1024-column panels on the tensor cores (needs panel_hi / panel_lo, 1024 x rows each, and
+ *              rows % 4 == 0); without it every block is followed by the fp32 update of all later columns
+ *   threshold  device scalar, relative_threshold * mean(var(W, dim 0) / diag(U)^2) (spqr.py:205-207);
+ *              +inf switches the detection off
+ *   scratch_err 128 x rows fp32
+ *   scales, zeros  rows x (cols / 16) fp32: group g of row r at r * (cols / 16) + g, the layout of the
+ *              reference's buf_scales / buf_zeros (set_model_qparams, spqr.py:348-356)
+ *   mask_u8    rows x cols bytes, 1 = outlier (permuted order), or NULL
+ *   loss_rows  rows fp32, sum of squared errors per row, or NULL
+ * cols % 128 == 0.  Per block bit-identical to the reference's fp32 arithmetic except for the
+ * leave-one-out errors, which are only compared with the threshold. */
+int lc_spqr_weight_transform(float* W, const float* U, const float* U_lo, int64_t rows, int64_t cols, int bits,
+                             const float* threshold, int simplified, float* scratch_err, float* panel_hi,
+                             float* panel_lo, float* scales, float* zeros, uint8_t* mask_u8, float* loss_rows,
+                             int32_t* status, lc_stream_t stream);
+
+/* SpQR.w_qdq (spqr.py:367-390) in one pass: out[r][c] = W[r][c] where mask is set, else the static fake
+ * quantisation of W[r][c] with the statistics of group invperm[c] / 16 of row r (invperm NULL: c / 16);
+ * W fp32 in original column order, mask_u8 in original column order, out in `out_dtype`. */
+int lc_spqr_dequant(const float* W, const float* scales, const float* zeros, const uint8_t* mask_u8,
+                    const int64_t* invperm, int64_t rows, int64_t cols, int bits, void* out, int out_dtype,
+                    lc_stream_t stream);
 
 /* GPTQ.weight_transform with static groups (special.static_groups, gptq.py:224-227, with
  * search_group_qparams :377-393): the qparams are not searched block by block but taken from the

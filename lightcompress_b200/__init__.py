@@ -6,9 +6,10 @@ Host-side mirrors of the reference plugin interface (`IntegerQuantizer`, `FloatQ
 from . import _lib  # noqa: F401  (raises if the CUDA library is not built)
 from .quant import FloatQuantizer, IntegerQuantizer, Weight48IntegerQuantizer  # noqa: F401
 from .gptq import GPTQ  # noqa: F401
+from .spqr import SpQR  # noqa: F401
 from .rtn import RTN  # noqa: F401
 from .awq import Awq  # noqa: F401
 from .blockwise import GPTQBlockwise, FakeQuantLinear, llama_subsets  # noqa: F401
 from .streaming import HostStagedGPTQ  # noqa: F401
 
-__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'Weight48IntegerQuantizer', 'GPTQ', 'RTN', 'Awq', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets', 'HostStagedGPTQ']
+__all__ = ['IntegerQuantizer', 'FloatQuantizer', 'Weight48IntegerQuantizer', 'GPTQ', 'SpQR', 'RTN', 'Awq', 'GPTQBlockwise', 'FakeQuantLinear', 'llama_subsets', 'HostStagedGPTQ']

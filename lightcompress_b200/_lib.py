@@ -18,7 +18,7 @@ LC_ERR_WORKSPACE, LC_ERR_NOT_PD, LC_ERR_TIMEOUT, LC_ERR_CUDA = -5, -6, -7, -8
 LC_F32, LC_BF16, LC_F16 = 0, 1, 2
 LC_CODES_NONE, LC_CODES_I32, LC_CODES_I8, LC_CODES_PACK4 = 0, 1, 2, 3
 LC_GEMM_UPPER_ONLY, LC_GEMM_B_LOWER, LC_GEMM_A_UPPER = 1, 2, 4
-LC_H_REVERSE, LC_H_UPPER = 1, 2
+LC_H_REVERSE, LC_H_UPPER, LC_H_LATE_DEAD = 1, 2, 4
 
 _DTYPES = {torch.float32: LC_F32, torch.bfloat16: LC_BF16, torch.float16: LC_F16}
 
@@ -71,6 +71,8 @@ SIGNATURES = {
     'lc_act_range_per_tensor': [_p, _p, _i, _i, _p, _p, _p],
     'lc_act_range_moving': [_p, _p, _i, _i, _d, _p, _p],
     'lc_act_hist_per_tensor': [_p, _p, _i, _i, _p, _p, _i, _p, _p],
+    'lc_spqr_weight_transform': [_p, _p, _p, _i64, _i64, _i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p],
+    'lc_spqr_dequant': [_p, _p, _p, _p, _p, _i64, _i64, _i, _p, _i, _p],
     'lc_rtn_w48_fake_quant': [_p, _i, _i64, _i64, _i64, _p, _p, _p, _p],
     'lc_quik_col_absmax': [_p, _i, _i64, _i64, _p, _p],
     'lc_rtn_int_fake_quant_masked': [_p, _i, _i64, _i64, _i, _i, _p, _p, _p],

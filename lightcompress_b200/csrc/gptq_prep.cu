@@ -11,14 +11,16 @@ __global__ void diag_kernel(const float* H, int64_t cols, float* out) {
   if (i < cols) out[i] = H[i * cols + i];
 }
 
-// damp = percdamp * mean_i( dead_i ? 1 : hscale * H_ii ); one CTA, fixed summation order
+// damp = percdamp * mean_i( dead_i ? 1 : hscale * H_ii ); one CTA, fixed summation order.
+// late_dead (SpQR, spqr.py:143-149): the mean is taken over |hscale * H_ii| before the dead columns are set
 __global__ void __launch_bounds__(1024) damp_kernel(const float* H, int64_t cols, float hscale, float percdamp,
-                                                    float* damp_out) {
+                                                    float* damp_out, int late_dead) {
   __shared__ double red[32];
   double acc = 0.0;
   for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
     const float h = H[i * cols + i];
-    acc += (h == 0.f) ? 1.0 : (double)(hscale * h);
+    if (late_dead) acc += (double)fabsf(hscale * h);
+    else acc += (h == 0.f) ? 1.0 : (double)(hscale * h);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -45,8 +47,10 @@ __global__ void __launch_bounds__(256) permute_h_kernel(const float* H, const in
   // upper: H holds its upper triangle only (lc_hessian_accum_upper)
   float v = hscale * (upper && pi > pj ? H[pj * cols + pi] : H[pi * cols + pj]);
   if (i == j) {
-    if (v == 0.f) v = 1.f;
-    v += damp[0];
+    // a dead column's diagonal: 1 + damp (gptq.py:139-150 sets it before dampening), or exactly 1 with
+    // LC_H_LATE_DEAD (spqr.py:143-149 sets it after)
+    if (v == 0.f) v = (flags & 4) ? 1.f : 1.f + damp[0];
+    else v += damp[0];
   }
   Hp[i * cols + j] = v;
 }
@@ -131,7 +135,7 @@ extern "C" LC_API int lc_gptq_permute_damp(const void* W, int w_dtype, const flo
   if (w_dtype != LC_F32 && w_dtype != LC_BF16 && w_dtype != LC_F16) return LC_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (Hp) {
-    damp_kernel<<<1, 1024, 0, st>>>(H, cols, hscale, percdamp, scratch);
+    damp_kernel<<<1, 1024, 0, st>>>(H, cols, hscale, percdamp, scratch, (reverse_h & 4) ? 1 : 0);
     LC_LAUNCH_CHECK();
     dim3 gh((unsigned)((cols + 255) / 256), (unsigned)cols);
     permute_h_kernel<<<gh, 256, 0, st>>>(H, perm, cols, hscale, scratch, Hp, reverse_h);

@@ -263,7 +263,8 @@ class GPTQ:
         native = mode in ('native', 'native_full') and C % 128 == 0
         direct = native or mode in ('direct', 'native', 'native_full')
         L.call('lc_gptq_permute_damp', None, L.LC_F32, L.ptr(H), L.ptr(perm), 0, C, float(hscale),
-               float(self.percdamp), (L.LC_H_REVERSE if direct else 0) | (L.LC_H_UPPER if self.h_upper else 0), None,
+               float(self.percdamp), (L.LC_H_REVERSE if direct else 0) | (L.LC_H_UPPER if self.h_upper else 0)
+               | getattr(self, 'prep_flags', 0), None,
                L.ptr(Hp), L.ptr(scratch), L.stream_of(H))
         want_lo = self.trailing == 'tensor' and C % 128 == 0 and C > 1024
         fac = {'H': H, 'perm': perm, 'invperm': invperm, 'U': None, 'U_lo': None, 'n_out': int(n_out)}

@@ -11,7 +11,7 @@ What `install()` changes, all of it on the imported `llmc` modules of this proce
     `BaseBlockwiseQuantization.set_quant_config` instantiates from the YAML dicts
     (llmc/compression/quantization/base_blockwise_quantization.py:156-193) become the classes of
     `lightcompress_b200.quant` (same constructor keywords, attributes and method names);
-  * `ALGO_REGISTRY['GPTQ' | 'Awq' | 'RTN']` become subclasses of the registered classes.  Item
+  * `ALGO_REGISTRY['GPTQ' | 'Awq' | 'RTN' | 'SpQR']` become subclasses of the registered classes.  Item
     assignment goes through `Register.__setitem__` (llmc/utils/registry_factory.py:23-24), which does
     not run the duplicate-name check of the decorator.  Constructor signature, YAML keys, the `buf_*`
     buffers left on every linear and the replacement modules in the blocks stay the reference's.
@@ -25,6 +25,7 @@ and only swaps the methods above.
 Awq: `block_transform` runs the fused scale + clip search of `lightcompress_b200.Awq` for blocks with
 the Llama layout and one calibration batch (`calib.bs: -1`); other cases raise.
 RTN: nothing to override beyond the quantizer classes (llmc/compression/quantization/rtn.py:10-28).
+SpQR: the per-layer methods forward to `lightcompress_b200.SpQR`; its block loop stays the reference's.
 
 `uninstall()` restores every name.
 """
@@ -36,6 +37,7 @@ from . import quant as _quant
 from .awq import Awq as _B200Awq
 from .blockwise import GPTQBlockwise, is_llama_layout
 from .gptq import GPTQ as _B200GPTQ
+from .spqr import SpQR as _B200SpQR
 
 _saved = {}
 
@@ -171,6 +173,46 @@ def _make_awq(RefAwq):
     return Awq
 
 
+def _make_spqr(RefSpQR):
+    class SpQR(RefSpQR):
+        """The registered SpQR algorithm (llmc/compression/quantization/spqr.py:19) over the B200 kernels:
+        the per-layer methods forward to `lightcompress_b200.SpQR`; the block loop (hooks, true_sequential
+        re-forwards, module replacement, spqr.py:60-112) stays the reference's."""
+
+        def __init__(self, model, quant_config, input, padding_mask, config):
+            super().__init__(model, quant_config, input, padding_mask, config)
+            self.layers_cache = self._b200.layers_cache        # the constructor re-creates the dict (spqr.py:29)
+
+        @torch.no_grad()
+        def add_quant_config(self):
+            super().add_quant_config()
+            self._b200 = _B200SpQR(self.wquantizer, dict(self.quant_config['special']), self.model_dtype)
+
+        @torch.no_grad()
+        def layer_init(self, layer, name):
+            self._b200.layer_init(layer, name)
+
+        @torch.no_grad()
+        def add_batch(self, layer, name, inp, out):
+            self._b200.add_batch(layer, name, inp, out)
+
+        @torch.no_grad()
+        def layer_transform(self, layer, name):
+            self._b200.layer_transform(layer, name)
+            self._b200.check_status()
+
+        @torch.no_grad()
+        def w_qdq(self, module, wquantizer):
+            return self._b200.w_qdq(module, wquantizer)
+
+        @torch.no_grad()
+        def free(self, name):
+            self._b200.layers_cache.pop(name, None)
+
+    SpQR.__name__ = SpQR.__qualname__ = 'SpQR'
+    return SpQR
+
+
 def _make_rtn(RefRTN):
     class RTN(RefRTN):
         """llmc/compression/quantization/rtn.py:10-28: no transform; `deploy` calls w_qdq / w_q / a_qdq of the
@@ -189,15 +231,17 @@ def install():
     import llmc.compression.quantization.gptq as rgptq
     import llmc.compression.quantization.module_utils as rmu
     import llmc.compression.quantization.rtn as rrtn
+    import llmc.compression.quantization.spqr as rspqr
     from llmc.utils.registry_factory import ALGO_REGISTRY
     _saved['rmu'] = rmu
     _saved['quantizers'] = {n: getattr(rbase, n) for n in
                             ('IntegerQuantizer', 'FloatQuantizer', 'Weight48IntegerQuantizer')}
-    _saved['algos'] = {n: ALGO_REGISTRY[n] for n in ('GPTQ', 'Awq', 'RTN')}
+    _saved['algos'] = {n: ALGO_REGISTRY[n] for n in ('GPTQ', 'Awq', 'RTN', 'SpQR')}
     _saved['rbase'], _saved['registry'] = rbase, ALGO_REGISTRY
     for n in _saved['quantizers']:
         setattr(rbase, n, getattr(_quant, n))
-    classes = {'GPTQ': _make_gptq(rgptq.GPTQ, rmu), 'Awq': _make_awq(rawq.Awq), 'RTN': _make_rtn(rrtn.RTN)}
+    classes = {'GPTQ': _make_gptq(rgptq.GPTQ, rmu), 'Awq': _make_awq(rawq.Awq), 'RTN': _make_rtn(rrtn.RTN),
+               'SpQR': _make_spqr(rspqr.SpQR)}
     for n, c in classes.items():
         ALGO_REGISTRY[n] = c
     _saved['classes'] = classes

@@ -170,8 +170,10 @@ def import_reference(root=None, on_cpu=None):
         rmu._TRANSFORMERS_LN_TYPES_.append(LlamaRMSNorm)
     if on_cpu:
         import llmc.compression.quantization.awq as rawq
+        import llmc.compression.quantization.spqr as rspqr
         rgptq.torch = _CpuTorchProxy()
         rawq.torch = _CpuTorchProxy()
+        rspqr.torch = _CpuTorchProxy()
     _state['root'] = root
     return types.SimpleNamespace(root=root, quant=rq, gptq=rgptq, base=rbase, llama=rllama, pkg=rquant_pkg,
                                  ALGO_REGISTRY=ALGO_REGISTRY, on_cpu=on_cpu)
@@ -218,6 +220,19 @@ def gptq_quant_config(special=None, bit=4, symmetric=False, quant_out=True):
     sp.update(special or {})
     return AttrDict(method='GPTQ', modality='language', quant_out=quant_out,
                     weight=dict(bit=bit, symmetric=symmetric, granularity='per_group', group_size=128),
+                    special=sp)
+
+
+def spqr_quant_config(special=None, quant_out=True):
+    """`quant` section of configs/quantization/methods/SpQR/spqr_w_only.yml (values restated: W4 groups of
+    16, round_zp False, actorder, percdamp 1, blocksize 128, relative_threshold 0.2, 3-bit second-level
+    statistics in groups of 16)."""
+    stat = dict(bit=3, symmetric=False, granularity='per_group', group_size=16, round_zp=False)
+    sp = dict(actorder=True, percdamp=1, blocksize=128, true_sequential=True, relative_threshold=0.2,
+              simplified_outliers=False, scale=dict(stat), zero=dict(stat))
+    sp.update(special or {})
+    return AttrDict(method='SpQR', modality='language', quant_out=quant_out,
+                    weight=dict(bit=4, symmetric=False, granularity='per_group', group_size=16, round_zp=False),
                     special=sp)
 
 

@@ -354,6 +354,60 @@ def make_gptq_owq(rq, rg, out_dir):
     print('gptq_owq.pt', len(cases), 'cases')
 
 
+def _ref_spqr_layer(rq, rs, W, X, bit, group, percdamp, rel_threshold, simplified, actorder=True):
+    """Drives the reference SpQR class (spqr.py) on one nn.Linear, bypassing its model plumbing."""
+    g = object.__new__(rs.SpQR)
+    g.dev = torch.device('cpu')
+    g.wquantizer = rq.IntegerQuantizer(bit, False, 'per_group', group_size=group, round_zp=False)
+    sub = dict(bit=3, symmetric=False, granularity='per_group', group_size=16, round_zp=False)
+    g.scale_quantizer = rq.IntegerQuantizer(**sub)
+    g.zero_quantizer = rq.IntegerQuantizer(**sub)
+    g.Q = rq.IntegerQuantizer(bit, False, 'per_channel', round_zp=False)
+    g.true_sequential, g.actorder, g.percdamp, g.blocksize = True, actorder, percdamp, 128
+    g.relative_threshold, g.simplified_outliers = rel_threshold, simplified
+    if actorder:
+        g.need_perm = True
+    g.layers_cache = {'l': {}}
+    g.model_dtype = W.dtype
+    layer = torch.nn.Linear(W.shape[1], W.shape[0], bias=False, dtype=W.dtype)
+    layer.weight.data = W.clone()
+    g.layer_init(layer, 'l')
+    for i in range(X.shape[0]):
+        g.add_batch(layer, 'l', X[i:i + 1], X[i:i + 1])
+    H = g.layers_cache['l']['H'].clone()
+    g.layer_transform(layer, 'l')
+    fq = g.w_qdq(layer, g.wquantizer)
+    perm = layer.buf_perm if actorder else torch.arange(W.shape[1])
+    return dict(W=W, X=X, H=H, bit=bit, group=group, percdamp=percdamp, rel_threshold=rel_threshold,
+                simplified=simplified, actorder=actorder, weight=layer.weight.data.clone(),
+                buf_scales=layer.buf_scales.clone(), buf_zeros=layer.buf_zeros.clone(), buf_perm=perm.clone(),
+                mask=layer.buf_mask.to_dense().bool(), w_qdq=fq.clone())
+
+
+def make_spqr(rq, out_dir):
+    """SpQR (spqr.py:184-285) with the settings of the reference's spqr_w_only.yml (4 bit, groups of 16,
+    3-bit second-level statistics, relative_threshold 0.2, percdamp 1) and its two other outlier modes."""
+    import math
+    import llmc.compression.quantization.spqr as rs
+    gen = torch.Generator().manual_seed(2011)
+    cases = {}
+    for name, R, C, ns, T, thr, simp, act in (('loo_act', 48, 384, 6, 160, 0.2, False, True),
+                                              ('simplified_act', 32, 256, 4, 128, 0.2, True, True),
+                                              ('no_outliers_act', 32, 256, 4, 128, math.inf, False, True),
+                                              ('loo_noact', 32, 256, 4, 128, 0.1, False, False)):
+        W = (torch.randn(R, C, generator=gen) * 0.02)
+        W[torch.rand(R, C, generator=gen) < 0.01] *= 8           # weight outliers for the detector to find
+        W = W.to(torch.bfloat16)
+        X = torch.randn(ns, T, C, generator=gen)
+        out_ch = torch.randperm(C, generator=gen)[:max(1, C // 100)]
+        X[:, :, out_ch] *= 20
+        X = X.to(torch.bfloat16)
+        cases[name] = _ref_spqr_layer(rq, rs, W, X, 4, 16, 1.0, thr, simp, act)
+        print(name, 'outliers', int(cases[name]['mask'].sum()), 'of', R * C)
+    torch.save(cases, os.path.join(out_dir, 'spqr_layer.pt'))
+    print('spqr_layer.pt', len(cases), 'cases')
+
+
 def make_gptq_block(ref_root, out_dir):
     """The reference's own GPTQ through its own driver -- model adapter, first-block catcher,
     ALGO_REGISTRY['GPTQ'](...), run_block_loop() (blockwise_optimization.py:31-42 ->
@@ -563,7 +617,7 @@ if __name__ == '__main__':
              'gptq_static': lambda: make_gptq_static(rq, rg, out_dir),
              'quik': lambda: make_quik(rq, out_dir), 'w48': lambda: make_w48(rq, out_dir), 'act_static': lambda: make_act_static(rq, out_dir), 'act_hist': lambda: make_act_hist(rq, out_dir), 'fp8': lambda: make_fp8(rq, out_dir), 'awq': lambda: make_awq(rq, out_dir),
              'export': lambda: make_export_configs(ref_root, out_dir),
-             'gptq_block': lambda: make_gptq_block(ref_root, out_dir)}
+             'gptq_block': lambda: make_gptq_block(ref_root, out_dir), 'spqr': lambda: make_spqr(rq, out_dir)}
     for name, step in steps.items():
         if not only or name in only:
             step()

@@ -86,7 +86,8 @@ def test_two_rank_static_groups_block_matches_single_gpu(tmp_path):
     """static_groups through the row-sharded solve: the ranks agree exactly, the buffers are every
     linear's round-to-nearest ones, and with every subset's column order pinned to the single-GPU run's
     (near-equal Hessian diagonals of this small random block would otherwise sort differently after the
-    all-reduce changes the last bits) fewer than 0.1 % of the deployed weights differ, linear by linear."""
+    all-reduce changes the last bits) fewer than 0.1 % of the deployed weights differ, linear by linear, or
+    three times what another summation order of the Hessian changes on one GPU."""
     import copy
     import torch.multiprocessing as mp
     from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer
@@ -101,6 +102,15 @@ def test_two_rank_static_groups_block_matches_single_gpu(tmp_path):
     gblock = copy.deepcopy(block).cuda()
     outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
     torch.save({k: v.cpu() for k, v in runner.used_perms.items()}, os.path.join(str(tmp_path), 'pins.pt'))
+    # noise floor: the same single-GPU run with the Hessians summed in another order (8 sequences per launch
+    # instead of 4) and the same pinned column orders.  o_proj and down_proj see Hessians of nearly
+    # rank-deficient activations, where the last bits of H already move some roundings
+    runner8 = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 8}, **extra))
+    runner8.pinned_perms = {k: v.clone() for k, v in runner.used_perms.items()}
+    gblock8 = copy.deepcopy(block).cuda()
+    runner8.block_opt(gblock8, [x.cuda() for x in xs], _to_cuda(kwargs))
+    floor = {n: float((m.tmp_weight != dict(gblock.named_modules())[n].tmp_weight).float().mean())
+             for n, m in gblock8.named_modules() if hasattr(m, 'tmp_weight')}
     mp.spawn(_worker, args=(2, port, str(tmp_path), dict(extra, _block=shape)), nprocs=2, join=True)
     r0 = torch.load(os.path.join(str(tmp_path), 'r0.pt'))
     r1 = torch.load(os.path.join(str(tmp_path), 'r1.pt'))
@@ -112,8 +122,9 @@ def test_two_rank_static_groups_block_matches_single_gpu(tmp_path):
         if name in r0['state']:
             assert torch.equal(m.buf_scales.cpu(), r0['state'][name]['buf_scales']), name
             mism = float((m.tmp_weight.cpu() != r0['state'][name]['tmp_weight']).float().mean())
-            print(f'{name}: 1-GPU vs 2-GPU deployed weights differing {mism:.4%}')
-            assert mism < 1e-3, (name, mism)
+            print(f'{name}: 1-GPU vs 2-GPU deployed weights differing {mism:.4%} '
+                  f'(single GPU, other summation order: {floor[name]:.4%})')
+            assert mism < max(1e-3, 3 * floor[name]), (name, mism, floor[name])
     full = torch.cat([o.cpu() for o in outs]).float()
     both = torch.cat(r0['outs'] + r1['outs']).float()
     assert float((full - both).norm() / full.norm()) < 1e-2

@@ -112,6 +112,45 @@ def test_gptq_run_block_loop_and_deploy_through_the_reference_driver(ref, shape,
     assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
 
 
+def test_spqr_run_block_loop_and_deploy_through_the_reference_driver(ref):
+    """The registered SpQR (spqr.py) with and without the plugin: same buffers on every linear (buf_mask a
+    sparse float tensor), first-subset codes and outlier masks of the first block within the bars, deployed
+    logits within 5 %."""
+    cfg, n, T = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2, vocab=2048, max_pos=1024), 16, 512
+    calib = rd.calib_ids(n, T, cfg.vocab_size, seed=5)
+    probe = rd.calib_ids(1, T, cfg.vocab_size, seed=6)[0]['input_ids']
+    a = _run(ref, rd.spqr_quant_config(), cfg, calib, T, 3, False, probe)
+    b = _run(ref, rd.spqr_quant_config(), cfg, calib, T, 3, True, probe)
+    err_a = float((a['logits'] - a['logits_fp']).norm() / a['logits_fp'].norm())
+    err_b = float((b['logits'] - b['logits_fp']).norm() / b['logits_fp'].norm())
+    print(f'spqr: logit error of the deployed model: reference {err_a:.5f}, plugin {err_b:.5f}')
+    assert a['algo_class'].__name__ == b['algo_class'].__name__ == 'SpQR' and a['algo_class'] is not b['algo_class']
+    assert a['classes'] == b['classes']
+    worst = []
+    for bi, (sa, sb) in enumerate(zip(a['state'], b['state'])):
+        assert list(sa) == list(sb)
+        for name in sa:
+            ea, eb = sa[name], sb[name]
+            assert sorted(ea) == sorted(eb) and 'buf_mask' in ea, (name, sorted(ea), sorted(eb))
+            for k in ea:
+                assert ea[k].shape == eb[k].shape and ea[k].dtype == eb[k].dtype, (name, k, ea[k].dtype, eb[k].dtype)
+            assert ea['buf_mask'].is_sparse and eb['buf_mask'].is_sparse
+            ma, mb = ea['buf_mask'].to_dense() != 0, eb['buf_mask'].to_dense() != 0
+
+            def codes(e):
+                wp = e['weight'][:, e['buf_perm']].reshape(-1, 16)
+                q = torch.clamp(torch.round(wp / e['buf_scales'].clamp_min(1e-9) + e['buf_zeros']), 0, 15)
+                return q.reshape(e['weight'].shape)[:, e['buf_invperm']]
+            d = float((codes(ea) != codes(eb)).float().mean())
+            dm = float((ma != mb).float().mean())
+            print(f'spqr block {bi} {name}: code mismatch {d:.4%}, outliers {int(ma.sum())} / {int(mb.sum())}, '
+                  f'mask mismatch {dm:.4%}')
+            if bi == 0 and name in ('self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj'):
+                worst.append((d, dm, name))
+    assert len(worst) == 3 and max(w[0] for w in worst) < 1e-3 and max(w[1] for w in worst) < 5e-4, worst
+    assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
+
+
 def test_rtn_deploy_is_bit_identical(ref):
     cfg = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2)
     probe = rd.calib_ids(1, 64, cfg.vocab_size, seed=6)[0]['input_ids']

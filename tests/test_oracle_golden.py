@@ -135,6 +135,25 @@ def test_gptq_owq_oracle_matches_reference(golden):
         _eq(gptq_ref.w_qdq(res, c['W'].dtype, c['bit'], c['sym']), c['w_qdq'])
 
 
+def test_spqr_oracle_matches_reference(golden):
+    """SpQR: leave-one-out outlier detection, simplified outliers, no outliers, with and without
+    act-order — compensated weight, outlier mask, statistics and deploy-time weight, bit for bit."""
+    from oracle import spqr_ref
+    torch.set_num_threads(1)
+    cases = golden('spqr_layer.pt')
+    assert len(cases) == 4
+    for key, c in cases.items():
+        res = spqr_ref.quantize_layer(c['W'], c['H'], bit=c['bit'], group_size=c['group'], percdamp=c['percdamp'],
+                                      relative_threshold=c['rel_threshold'], simplified=c['simplified'],
+                                      actorder=c['actorder'])
+        _eq(res['buf_perm'], c['buf_perm'])
+        _eq(res['mask'], c['mask'])
+        _eq(res['weight'], c['weight'])
+        _eq(res['buf_scales'], c['buf_scales'])
+        _eq(res['buf_zeros'], c['buf_zeros'])
+        _eq(spqr_ref.w_qdq(res, c['W'].dtype, c['bit'], c['group']), c['w_qdq'])
+
+
 def test_static_activation_ranges_oracle_matches_reference(golden):
     """calib_algo 'static_minmax' / 'static_moving_minmax' (per_tensor): qparams from a batch of
     calibration activations and the static fake quant that uses them."""
