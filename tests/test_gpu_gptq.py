@@ -592,3 +592,32 @@ def test_hessian_upper_only_equals_the_upper_triangle_of_the_full_update():
                L.ptr(scratch), L.stream_of(H))
         outs.append(Hp)
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize('static', [False, True])
+@pytest.mark.parametrize('C', [512, 2304])
+def test_row_ranges_solve_to_the_same_bits_as_the_whole(static, C):
+    """Rows only share U: a row range solved on its own (what a rank of a process group does with its
+    share of a subset's stacked rows) gives the bits of the whole solve, with searched and static groups,
+    on the FFMA and on the tensor-core trailing path."""
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    g = torch.Generator().manual_seed(4100 + C)
+    R, ns, T = 384, 8, 512
+    W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16)
+    X = _x(g, ns, T, C).cuda()
+    H = (X.reshape(-1, C).float().t() @ X.reshape(-1, C).float()) * (2.0 / ns)
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    solver = GPTQ(wq, {'actorder': True, 'static_groups': static, 'percdamp': 0.01}, model_dtype=W.dtype)
+    solver.h_upper = False
+    layer = torch.nn.Linear(C, R, bias=False, dtype=W.dtype).cuda()
+    layer.weight.data = W.cuda()
+    fac = solver.factorize(H, 1.0)
+    st = solver.static_qparams(layer) if static else None
+    whole = solver.solve(layer.weight.data, H, 1.0, factor=fac, static=st)
+    for a, b in ((0, 128), (128, 384)):
+        part = solver.solve(layer.weight.data, H, 1.0, rows=(a, b), factor=fac, static=st)
+        assert torch.equal(part['weight'], whole['weight'][a:b]), (a, b)
+        assert torch.equal(part['codes_perm'], whole['codes_perm'][a:b]), (a, b)
+        n_g = C // 128
+        assert torch.equal(part['buf_scales'].reshape(-1, n_g), whole['buf_scales'].reshape(-1, n_g)[a:b]), (a, b)
+    solver.check_status()

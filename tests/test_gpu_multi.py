@@ -102,10 +102,12 @@ def test_two_rank_static_groups_block_matches_single_gpu(tmp_path):
     gblock = copy.deepcopy(block).cuda()
     outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
     torch.save({k: v.cpu() for k, v in runner.used_perms.items()}, os.path.join(str(tmp_path), 'pins.pt'))
-    # noise floor: the same single-GPU run with the Hessians summed in another order (8 sequences per launch
-    # instead of 4) and the same pinned column orders.  o_proj and down_proj see Hessians of nearly
-    # rank-deficient activations, where the last bits of H already move some roundings
-    runner8 = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 8}, **extra))
+    # noise floor: the same single-GPU run with the Hessians summed in another order (every launch's tokens
+    # accumulated in two parts that meet in fp32 atomics, as two ranks' partial sums meet in the all-reduce)
+    # and the same pinned column orders.  o_proj and down_proj see Hessians of nearly rank-deficient
+    # activations, where the last bits of H already move some roundings
+    runner8 = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4,
+                                      'hessian_ksplit': 2}, **extra))
     runner8.pinned_perms = {k: v.clone() for k, v in runner.used_perms.items()}
     gblock8 = copy.deepcopy(block).cuda()
     runner8.block_opt(gblock8, [x.cuda() for x in xs], _to_cuda(kwargs))
