@@ -433,6 +433,13 @@ def run_secondary(args):
         h2d = int(X_host.numel() * 2 + sum(p.numel() * 2 for p in block_host.parameters()))
         d2h = int(sum(p.numel() * 2 for p in block_host.parameters()))
         metric, unit = 'AWQ W4 g128 scale+clip search blocks/sec', 'blocks/s'
+        extra['_phases'] = awq.phases
+        # FLOPs of the 80 inspect-module forwards (20 candidates x 4 subsets; the block's own bf16 GEMMs, run
+        # by cuBLAS): attention module = q, k, v, o projections + attention; MLP = gate, up, down
+        tok = NS * 512
+        attn = 4 * 2 * tok * HID * HID + 2 * 2 * NS * 512 * 512 * HID
+        mlp = 3 * 2 * tok * HID * INTER
+        extra["_flops"] = 20 * (attn + 2 * tok * HID * HID + mlp + 2 * tok * HID * INTER)
         workload = ('one Llama-2-7B-shape decoder block, AWQ W4 asym g128, 20-point scale grid on 4 subsets + clip '
                     'search on 5 linears, 128x512 calibration tokens in one batch')
     else:
@@ -491,7 +498,15 @@ def run_secondary(args):
     for _ in range(max(3, args.warmup)):
         step()
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    phases = extra.pop('_phases', None)
+    flops = extra.pop('_flops', None)
+    if phases is not None:
+        phases.spans, phases.on = [], True
     ms = timed(step, args.steps)
+    if phases is not None:
+        phases.on = False
+        extra['phases_ms'] = {k: v / args.steps for k, v in phases.summary().items()}
+        extra['phases_ms']['other (capture forward, block copy)'] = ms - sum(extra['phases_ms'].values())
     for _ in range(2):
         e2e_step()
     e2e_ms = timed(e2e_step, args.steps)
@@ -504,6 +519,14 @@ def run_secondary(args):
                 'e2e': {'value': 1e3 / e2e_ms, 'unit': unit, 'ms_per_step': e2e_ms, 'h2d_bytes_per_step': h2d,
                         'd2h_bytes_per_step': d2h}, 'clocks': clocks}
         line.update(extra)
+        if flops:
+            tf_peak = peaks()[2]
+            line['roofline'] = {'bound': 'tensor', 'kernel': 'bf16 GEMMs of the inspect-module forwards (cuBLAS, library)',
+                                'achieved': flops / (ms * 1e-3) / 1e12, 'peak': tf_peak, 'unit': 'TFLOP/s',
+                                'frac': flops / (ms * 1e-3) / 1e12 / tf_peak, 'traffic': None,
+                                'peak_kind': 'measured sustained cuBLAS bf16 (of measured)',
+                                'note': 'FLOPs of the 80 candidate forwards over the whole step, which also holds the '
+                                        'clip search (CUDA cores) and the scale kernels'}
         if args.workload == 'moe':
             tot = extra['algorithmic_bytes']['weights'] + extra['algorithmic_bytes']['activations']
             line['roofline'] = {'bound': 'hbm', 'achieved': tot / world / (ms * 1e-3) / 1e9, 'peak': hbm_peak,

@@ -22,6 +22,7 @@ import torch
 
 from . import _lib as L
 from . import block_ops, parallel
+from .blockwise import PhaseTimer
 
 
 def _is_norm(m):
@@ -42,6 +43,7 @@ class Awq:
         self.clip_n_grid, self.clip_max_shrink = 20, 0.5
         self.n_sample_token = calib_seq_len
         self.fused_block_ops = special.get('fused_block_ops', True)
+        self.phases = PhaseTimer()      # off unless a caller switches it on (bench.py)
         if self.trans_version != 'v2' or self.clip_version != 'v1':
             raise NotImplementedError('only trans_version v2 / clip_version v1 are on the B200 hot path')
         if wquantizer.granularity != 'per_group':
@@ -228,12 +230,14 @@ class Awq:
                     ('gate_up', [m.gate_proj, m.up_proj], 'gate', m, {}, block.post_attention_layernorm),
                     ('down', [m.down_proj], 'down', m.down_proj, {}, m.up_proj))
             for key, layers, f, inspect, kw, prev in plan:
-                s, ls = self.search_scale_subset(layers, feats[f], inspect, kw)
-                self.apply_scale(s, prev, layers)
-                feats[f] = self.scaling_input(feats[f], s)
+                with self.phases('scale_search'):
+                    s, ls = self.search_scale_subset(layers, feats[f], inspect, kw)
+                    self.apply_scale(s, prev, layers)
+                    feats[f] = self.scaling_input(feats[f], s)
                 report['scales'][key], report['losses'][key] = s, ls
         if self.weight_clip:
             for name, mod, f in (('v', a.v_proj, 'q'), ('o', a.o_proj, 'o'), ('gate', m.gate_proj, 'gate'),
                                  ('up', m.up_proj, 'gate'), ('down', m.down_proj, 'down')):
-                report['clip'][name] = self.auto_clip_layer(mod.weight.data, feats[f])
+                with self.phases('clip_search'):
+                    report['clip'][name] = self.auto_clip_layer(mod.weight.data, feats[f])
         return report
