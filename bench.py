@@ -651,6 +651,22 @@ def kernel_case(name, n):
         for _ in range(n):
             solver.solve(W, H, 2.0 / 4, factor=fac)
         solver.check_status()
+    elif name == 'spqr':                              # SpQR solve of a 4096 x 4096 layer (groups of 16, outlier detection)
+        R, C = 4096, 4096
+        g = torch.Generator().manual_seed(11)
+        W = torch.randn(R, C, generator=g) * 0.02
+        W[torch.rand(R, C, generator=g) < 0.01] *= 8
+        W = W.to(torch.bfloat16).cuda()
+        X = torch.randn(8192, C, generator=g).to(torch.bfloat16).cuda()
+        H = torch.zeros(C, C, device='cuda')
+        L.call('lc_hessian_accum', L.ptr(X), X.shape[0], C, L.ptr(H), 1.0, 1.0, 0, None, L.stream_of(X))
+        solver = lc.SpQR(lc.IntegerQuantizer(4, False, 'per_group', group_size=16, round_zp=False),
+                         {'actorder': True, 'percdamp': 1, 'relative_threshold': 0.2})
+        solver.h_upper = False
+        fac = solver.factorize(H, 2.0 / 4)
+        for _ in range(n):
+            solver.solve(W, H, 2.0 / 4, factor=fac)
+        solver.check_status()
     elif name == 'act_static':                        # per-tensor ranges of 8 tensors of 64 MB in one launch
         qz = lc.IntegerQuantizer(8, True, 'per_tensor', calib_algo='static_minmax')
         g = torch.Generator(device='cuda').manual_seed(8)
@@ -685,7 +701,7 @@ def kernel_case(name, n):
 
 
 KERNEL_CASES = ['hessian', 'hessian_wide', 'rtn', 'fp8', 'gptq', 'gptq_wide', 'factor', 'factor_wide', 'factor_cusolver', 'block_ops',
-                'fp8_linear', 'mse', 'awq_clip', 'act_static', 'quik', 'w48']
+                'fp8_linear', 'mse', 'awq_clip', 'act_static', 'quik', 'w48', 'spqr']
 
 
 # ---- parity of the timed configuration (outside the timed region) --------------------------------------
