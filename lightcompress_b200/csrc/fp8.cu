@@ -112,13 +112,28 @@ __global__ void __launch_bounds__(256) fp8_row_vec_kernel(Fp8Args a) {
       const int64_t i = threadIdx.x + (int64_t)k * 256;
       if (i < nvec) v[k] = __ldcs(in + i);
     }
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      // packed: |x| and the NaN-propagating maximum on two bf16 values per instruction
+      __nv_bfloat162 am2 = __float2bfloat162_rn(0.f);
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      const int64_t i = threadIdx.x + (int64_t)k * 256;
-      if (i < nvec) {
-        const T* p = reinterpret_cast<const T*>(&v[k]);
+      for (int k = 0; k < V; ++k) {
+        const int64_t i = threadIdx.x + (int64_t)k * 256;
+        if (i < nvec) {
+          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
 #pragma unroll
-        for (int e = 0; e < N; ++e) am = nan_max(am, fabsf(E::to_f(p[e])));
+          for (int e = 0; e < 4; ++e) am2 = __hmax2_nan(am2, __habs2(p2[e]));
+        }
+      }
+      am = nan_max(__low2float(am2), __high2float(am2));
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const int64_t i = threadIdx.x + (int64_t)k * 256;
+        if (i < nvec) {
+          const T* p = reinterpret_cast<const T*>(&v[k]);
+#pragma unroll
+          for (int e = 0; e < N; ++e) am = nan_max(am, fabsf(E::to_f(p[e])));
+        }
       }
     }
     am = block_absmax(am, smem);

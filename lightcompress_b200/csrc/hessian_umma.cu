@@ -56,10 +56,8 @@ struct HessArgs {
   int64_t cols;
   int n_st;        // super-tiles per dimension
   int n_super;     // super-tiles on or above the diagonal
-  int n_items;     // n_super * ksplit, or tail_begin + (n_super - tail_begin) * tail_split
+  int n_items;     // n_super * ksplit: every super-tile's tokens in ksplit equal parts, walked part-major
   int ksplit;
-  int tail_begin;  // super-tiles from this index on (the partial last wave) are split tail_split ways in k
-  int tail_split;  // 1 = no tail split
   int k_total;     // pipeline iterations over all segments
   int nseg;
   int seg_k[MAX_SEG];
@@ -74,20 +72,9 @@ struct Item {
 
 __device__ __forceinline__ Item decode_item(const HessArgs& a, int item) {
   Item it;
-  int split = item / a.n_super;
+  const int split = item / a.n_super;
   int t = item % a.n_super;
-  int parts = a.ksplit;
-  if (a.tail_split > 1) {
-    // whole super-tiles first, then the tail wave's super-tiles in tail_split token ranges each
-    if (item < a.tail_begin) {
-      t = item, split = 0, parts = 1;
-    } else {
-      const int idx = item - a.tail_begin;
-      t = a.tail_begin + idx / a.tail_split;
-      split = idx % a.tail_split;
-      parts = a.tail_split;
-    }
-  }
+  const int parts = a.ksplit;
   int si = 0;
   for (; si < a.n_st; ++si) {
     const int cnt = a.n_st - si;
@@ -459,8 +446,6 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
   a.n_super = a.n_st * (a.n_st + 1) / 2;
   a.alpha = alpha;
   a.upper_only = upper_only;
-  a.tail_begin = a.n_super;
-  a.tail_split = 1;
   if (ksplit == 0) {
     // The tensor core adds every MMA's products into the fp32 accumulator with truncation, so a sum loses
     // about 2^-24 of its value per 16-token MMA step: a relative deficit that grows with the number of
@@ -482,7 +467,7 @@ int hessian_launch(const void* const* xs, const int64_t* tokens, int nseg, int64
   }
   if (ksplit > a.k_total) ksplit = a.k_total;
   a.ksplit = ksplit;
-  a.n_items = a.tail_split > 1 ? a.tail_begin + (a.n_super - a.tail_begin) * a.tail_split : a.n_super * ksplit;
+  a.n_items = a.n_super * ksplit;
   const int grid = a.n_items < sms ? a.n_items : sms;
   LC_CHECK_CUDA(cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
   hessian_umma_kernel<<<grid, kThreads, SMEM_BYTES, st>>>(maps, a);

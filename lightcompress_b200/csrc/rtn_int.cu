@@ -317,16 +317,35 @@ __global__ void __launch_bounds__(256) row_vec_kernel(QuantArgs a) {
     float mx_all = 0.f, mn_all = 0.f;
     if (!is_static) {
       float mx = -INFINITY, mn = INFINITY;
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        // packed NaN-propagating max / min on two bf16 values per instruction
+        __nv_bfloat162 mx2 = __float2bfloat162_rn(-INFINITY), mn2 = __float2bfloat162_rn(INFINITY);
 #pragma unroll
-      for (int k = 0; k < V; ++k) {
-        const int64_t i = threadIdx.x + (int64_t)k * 256;
-        if (i < nvec) {
-          float f[N];
-          unpack<T, N>(v[k], f);
+        for (int k = 0; k < V; ++k) {
+          const int64_t i = threadIdx.x + (int64_t)k * 256;
+          if (i < nvec) {
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
 #pragma unroll
-          for (int e = 0; e < N; ++e) {
-            mx = nan_max(mx, f[e]);
-            mn = nan_min(mn, f[e]);
+            for (int e = 0; e < 4; ++e) {
+              mx2 = __hmax2_nan(mx2, p2[e]);
+              mn2 = __hmin2_nan(mn2, p2[e]);
+            }
+          }
+        }
+        mx = nan_max(__low2float(mx2), __high2float(mx2));
+        mn = nan_min(__low2float(mn2), __high2float(mn2));
+      } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const int64_t i = threadIdx.x + (int64_t)k * 256;
+          if (i < nvec) {
+            float f[N];
+            unpack<T, N>(v[k], f);
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+              mx = nan_max(mx, f[e]);
+              mn = nan_min(mn, f[e]);
+            }
           }
         }
       }

@@ -236,6 +236,14 @@ def spqr_quant_config(special=None, quant_out=True):
                     special=sp)
 
 
+def awq_quant_config(symmetric=True, quant_out=True):
+    """`quant` section of configs/quantization/methods/Awq/awq_w_only.yml (values restated: W4 g128
+    symmetric, trans v2, weight_clip, clip_sym)."""
+    return AttrDict(method='Awq', modality='language', quant_out=quant_out,
+                    weight=dict(bit=4, symmetric=symmetric, granularity='per_group', group_size=128),
+                    special=dict(trans=True, trans_version='v2', weight_clip=True, clip_sym=symmetric))
+
+
 def rtn_quant_config(bit=4, symmetric=False):
     return AttrDict(method='RTN', modality='language',
                     weight=dict(bit=bit, symmetric=symmetric, granularity='per_group', group_size=128))

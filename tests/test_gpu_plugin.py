@@ -151,6 +151,61 @@ def test_spqr_run_block_loop_and_deploy_through_the_reference_driver(ref):
     assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
 
 
+def test_awq_run_block_loop_and_deploy_through_the_reference_driver(ref):
+    """The registered Awq (awq.py, auto_clip.py) with and without the plugin, one calibration batch
+    (calib.bs: -1 of the reference's awq_w_only.yml): the transformed weights of the first block (scaled,
+    clipped) differ in fewer than 0.1 % of their elements, the layer norms that absorbed the scales agree to
+    bf16 rounding, deployed logits within 5 %."""
+    cfg, n, T = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2, vocab=2048, max_pos=1024), 16, 256
+    g = torch.Generator().manual_seed(5)
+    calib = [{'input_ids': torch.randint(0, cfg.vocab_size, (n, T), generator=g)}]      # one batch
+    probe = rd.calib_ids(1, T, cfg.vocab_size, seed=6)[0]['input_ids']
+    out = []
+    for with_plugin in (False, True):
+        from lightcompress_b200 import plugin
+        model = rd.synth_llama_adapter(ref, cfg, seed=3)
+        fp = copy.deepcopy(model.model).cuda()
+        with torch.no_grad():
+            logits_fp = fp(probe.cuda()).logits.float().cpu()
+        del fp
+        if with_plugin:
+            plugin.install()
+        try:
+            algo = rd.run_algorithm(ref, model, rd.awq_quant_config(), calib, T, deploy=None)
+            state = {f'layers.{bi}.{n_}.weight': e['weight'].float() for bi, blk in enumerate(rd.linear_state(model))
+                     for n_, e in blk.items()}
+            state.update({n_: p.detach().float().cpu().clone() for n_, p in model.model.named_parameters()
+                          if 'layernorm' in n_})
+            algo.deploy('fake_quant')
+            model.model.cuda()
+            with torch.no_grad():
+                logits = model.model(probe.cuda()).logits.float().cpu()
+            model.model.cpu()
+        finally:
+            if with_plugin:
+                plugin.uninstall()
+        out.append(dict(state=state, logits=logits, err=float((logits - logits_fp).norm() / logits_fp.norm()),
+                        cls=type(algo)))
+    a, b = out
+    assert a['cls'].__name__ == b['cls'].__name__ == 'Awq' and a['cls'] is not b['cls']
+    print(f'awq: logit error of the deployed model: reference {a["err"]:.5f}, plugin {b["err"]:.5f}')
+    worst = 0.0
+    assert sum(n_.startswith('layers.0.') and n_.endswith('_proj.weight') for n_ in a['state']) == 7
+    for name in a['state']:
+        wa, wb = a['state'][name], b['state'][name]
+        assert wa.shape == wb.shape, name
+        d = float((wa != wb).float().mean())
+        rel = float((wa - wb).norm() / wa.norm().clamp_min(1e-12))
+        if 'layers.0.' in name:
+            print(f'awq {name}: elements differing {d:.4%}, relative difference {rel:.2e}')
+            if name.endswith('_proj.weight'):
+                worst = max(worst, d)
+            else:
+                assert rel < 1e-2, (name, rel)
+    assert worst < 1e-3, worst
+    assert abs(a['err'] - b['err']) <= 0.05 * a['err'] + 1e-5
+
+
 def test_rtn_deploy_is_bit_identical(ref):
     cfg = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2)
     probe = rd.calib_ids(1, 64, cfg.vocab_size, seed=6)[0]['input_ids']
