@@ -170,3 +170,66 @@ def test_block_schedule_with_static_groups_and_owq(mode):
                 assert n_nonout == m.weight.shape[1] - (2 if 'gate' in name or 'up' in name else 6), name
                 outl = m.buf_perm[n_nonout:]
                 assert torch.equal(m.tmp_weight[:, outl], m.weight[:, outl].to(m.tmp_weight.dtype)), name
+
+
+def _other_family_block(kind, hidden=256, inter=512, heads=4, T=96, n_seq=16, seed=5):
+    """A decoder layer of another model family that has Llama's attribute names: Qwen2 (biases on q / k / v,
+    the same data flow) or Granite (residual and attention multipliers: another data flow)."""
+    if kind == 'qwen2':
+        from transformers.models.qwen2.modeling_qwen2 import Qwen2Config as Cfg, Qwen2DecoderLayer as Layer
+        from transformers.models.qwen2.modeling_qwen2 import Qwen2RotaryEmbedding as Rot
+        extra = {}
+    else:
+        from transformers.models.granite.modeling_granite import GraniteConfig as Cfg, GraniteDecoderLayer as Layer
+        from transformers.models.granite.modeling_granite import GraniteRotaryEmbedding as Rot
+        extra = dict(residual_multiplier=0.5, attention_multiplier=0.1)
+    cfg = Cfg(hidden_size=hidden, intermediate_size=inter, num_attention_heads=heads, num_key_value_heads=heads,
+              num_hidden_layers=1, vocab_size=128, max_position_embeddings=4 * T, **extra)
+    cfg._attn_implementation = 'sdpa'
+    torch.manual_seed(seed)
+    block = Layer(cfg, 0).to(torch.bfloat16)
+    g = torch.Generator().manual_seed(seed + 1)
+    for p in block.parameters():
+        p.data = (torch.randn(p.shape, generator=g) * (0.02 if p.dim() == 2 else 0.1)).to(torch.bfloat16) + (
+            0 if p.dim() == 2 or p.shape[0] != hidden else 1)
+    rot = Rot(cfg)
+    pos = torch.arange(T)[None]
+    cos, sin = rot(torch.zeros(1, T, hidden, dtype=torch.bfloat16), pos)
+    kwargs = dict(position_embeddings=(cos, sin), attention_mask=None, position_ids=pos)
+    xs = [torch.randn(1, T, hidden, generator=g).to(torch.bfloat16) for _ in range(n_seq)]
+    return block, xs, kwargs
+
+
+@pytest.mark.parametrize('kind', ['qwen2', 'granite'])
+def test_stage_plan_is_only_taken_where_it_reproduces_the_block(kind):
+    """The staged plan is chosen by attribute names and then checked against the block's own forward.
+    Qwen2's layer (biases) computes what the plan computes: it is taken, one forward.  Granite's layer
+    scales the residual branches: the check refuses the plan for that class and the generic re-forwarding
+    schedule runs.  Either way the result equals the generic schedule's bit for bit."""
+    from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer, llama_subsets
+    block, xs, kwargs = _other_family_block(kind)
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    results = []
+    for special in ({'stage_plan': True}, {'stage_plan': False}):
+        gblock = copy.deepcopy(block).cuda()
+        runner = GPTQBlockwise(wq, dict({'actorder': True, 'percdamp': 0.01, 'hessian_ksplit': 1}, **special))
+        outs = runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
+        torch.cuda.synchronize()
+        state = {name: (getattr(parent, attr).weight.clone(), getattr(parent, attr).buf_scales.clone(),
+                        getattr(parent, attr).buf_perm.clone())
+                 for subset in llama_subsets(gblock) for name, (parent, attr) in subset.items()}
+        results.append((state, torch.cat(outs), runner.forward_passes, list(runner.stage_plan_rejected)))
+    staged, generic = results
+    if kind == 'qwen2':
+        assert staged[2] == 1 and not staged[3]
+    else:
+        assert staged[2] == 5 and staged[3] == ['GraniteDecoderLayer']
+    assert torch.equal(staged[1], generic[1])
+    for name in staged[0]:
+        for a, b in zip(staged[0][name], generic[0][name]):
+            assert torch.equal(a, b), name
+    # and the output is the quantised block's own forward
+    with torch.no_grad():
+        ys = [gblock(x.cuda(), **_to_cuda(kwargs)) for x in xs]
+    want = torch.cat([y[0] if isinstance(y, tuple) else y for y in ys])
+    assert torch.equal(want, generic[1])
