@@ -214,3 +214,71 @@ def test_two_rank_expert_sharded_moe_matches_the_oracle(tmp_path):
     rel = float((y0.float() - ref.cpu().float()).norm() / ref.cpu().float().norm())
     print(f'two-rank MoE vs oracle: rel diff {rel:.2e}')
     assert rel < 3e-3
+
+
+def _awq_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    import copy
+    from lightcompress_b200 import Awq, IntegerQuantizer
+    from tests.test_gpu_blockwise import _make_block, _to_cuda
+    block, xs, kwargs = _make_block(hidden=512, inter=1024, heads=4, T=128, n_seq=8, seed=11)
+    x = torch.cat(xs)                                  # one calibration batch; every rank takes half of it
+    half = x.shape[0] // world
+    awq = Awq(IntegerQuantizer(4, False, 'per_group', group_size=128),
+              {'trans': True, 'trans_version': 'v2', 'weight_clip': True, 'clip_version': 'v1'}, calib_seq_len=128)
+    gblock = copy.deepcopy(block).cuda()
+    rep = awq.block_transform(gblock, x[rank * half:(rank + 1) * half].cuda(), _to_cuda(kwargs))
+    torch.cuda.synchronize()
+    torch.save({'params': {n: p.data.cpu() for n, p in gblock.named_parameters()},
+                'scales': {k: v.cpu() for k, v in rep['scales'].items()},
+                'losses': {k: torch.as_tensor(v).float().cpu() for k, v in rep['losses'].items()}},
+               os.path.join(out_dir, f'awq{rank}.pt'))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_two_rank_awq_matches_single_gpu(tmp_path):
+    """AWQ with the calibration batch split over two ranks (summed |x| statistics, summed candidate
+    losses, averaged clip thresholds; awq.py:256-273, auto_clip.py:72-76): both ranks end with the same
+    block, the chosen scales equal the single-GPU run's on the whole batch up to the rounding of the
+    reduced statistics, and the transformed weights differ in fewer than 1 % of their elements (the clip
+    thresholds of two half batches are averaged, which is not the threshold of the whole batch)."""
+    import copy
+    import torch.multiprocessing as mp
+    from lightcompress_b200 import Awq, IntegerQuantizer
+    from tests.test_gpu_blockwise import _make_block, _to_cuda
+    port = 29500 + (os.getpid() % 100)
+    mp.spawn(_awq_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = torch.load(os.path.join(str(tmp_path), 'awq0.pt'))
+    r1 = torch.load(os.path.join(str(tmp_path), 'awq1.pt'))
+    for n in r0['params']:
+        assert torch.equal(r0['params'][n], r1['params'][n]), n
+    block, xs, kwargs = _make_block(hidden=512, inter=1024, heads=4, T=128, n_seq=8, seed=11)
+    awq = Awq(IntegerQuantizer(4, False, 'per_group', group_size=128),
+              {'trans': True, 'trans_version': 'v2', 'weight_clip': True, 'clip_version': 'v1'}, calib_seq_len=128)
+    gblock = copy.deepcopy(block).cuda()
+    rep = awq.block_transform(gblock, torch.cat(xs).cuda(), _to_cuda(kwargs))
+    same_choice = True
+    for k, s in rep['scales'].items():
+        l1, l2 = torch.as_tensor(rep['losses'][k]).float().cpu(), r0['losses'][k]
+        lrel = float((l1 - l2).abs().max() / l1.abs().max())
+        i1, i2 = int(l1.argmin()), int(l2.argmin())
+        print(f'awq {k}: candidate losses differ by {lrel:.2e} (relative), chosen grid point {i1} / {i2}')
+        # the mean of two half-batch means is the whole batch's mean up to rounding
+        assert lrel < 2e-2, (k, lrel)
+        if i1 == i2:
+            rel = float((s.cpu().float() - r0['scales'][k].float()).abs().max() / s.float().abs().max())
+            assert rel < 2e-2, (k, rel)
+        else:
+            same_choice = False
+            assert abs(float(l1[i1] - l1[i2])) <= 2e-2 * float(l1[i1]), (k, i1, i2)      # a near tie
+    if same_choice:
+        for n, p in gblock.named_parameters():
+            rel = float((p.data.cpu().float() - r0['params'][n].float()).norm() / p.data.float().norm())
+            print(f'awq {n}: relative difference 1 GPU vs 2 GPUs {rel:.2e}')
+            assert rel < 3e-2, (n, rel)
