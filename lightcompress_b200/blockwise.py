@@ -299,8 +299,11 @@ class GPTQBlockwise:
             if with_codes:
                 slot[:n, off_c:].view(torch.uint8).copy_(mine['codes_perm'])
         parallel.all_gather_packed(packed)
-        pieces = [packed[r, :bounds[r + 1] - bounds[r]] for r in range(world) if bounds[r + 1] > bounds[r]]
-        rows = pieces[0] if len(pieces) == 1 else torch.cat(pieces, 0)           # (R, row_len)
+        if world * max_rows == R:
+            rows = packed.view(R, row_len)                 # even row ranges: the gathered buffer is the result
+        else:
+            pieces = [packed[r, :bounds[r + 1] - bounds[r]] for r in range(world) if bounds[r + 1] > bounds[r]]
+            rows = pieces[0] if len(pieces) == 1 else torch.cat(pieces, 0)       # (R, row_len)
         full = {'weight': rows[:, :C].contiguous(),
                 # every rank computes the same permutation from the same (reduced) Hessian
                 'buf_perm': fac['perm'], 'buf_invperm': fac['invperm'], 'buf_zeros': None}
