@@ -43,12 +43,15 @@ def _forward(block, inputs, kwargs):
 
 @torch.no_grad()
 def gptq_block(block, inputs, kwargs, bit=4, sym=False, percdamp=0.01, actorder=True,
-               true_sequential=True, quant_out=True, model_dtype=torch.bfloat16, capture=None):
+               true_sequential=True, quant_out=True, model_dtype=torch.bfloat16, capture=None, subsets=None):
     """Runs one decoder block through the schedule.  Returns (per-linear results, next inputs).
     Each result is gptq_ref.quantize_layer's dict plus 'w_qdq' (the deployed weight).
     capture: a dict that receives, per linear, the list of input tensors its final Hessian was
-    accumulated from (for teacher-forced comparisons of a single linear)."""
-    subsets = llama_subsets(block)
+    accumulated from (for teacher-forced comparisons of a single linear).
+    subsets: another adapter's subsets, e.g. llmc/models/opt.py:53-90."""
+    # subsets: lists of (name, parent module, attribute) in schedule order, as the model adapters'
+    # get_subsets_in_block give them (default: the Llama adapter's, llmc/models/llama.py:52-91)
+    subsets = subsets if subsets is not None else llama_subsets(block)
     states, handles = {}, []
 
     def hook_layers(items):

@@ -233,3 +233,70 @@ def test_stage_plan_is_only_taken_where_it_reproduces_the_block(kind):
         ys = [gblock(x.cuda(), **_to_cuda(kwargs)) for x in xs]
     want = torch.cat([y[0] if isinstance(y, tuple) else y for y in ys])
     assert torch.equal(want, generic[1])
+
+
+def test_generic_schedule_on_a_block_of_another_layout():
+    """A decoder layer without Llama's attribute names (OPT: q / k / v, out_proj, fc1, fc2 with biases and
+    LayerNorms; subsets of llmc/models/opt.py:53-90) goes through the generic hook-and-re-forward schedule
+    with the adapter's subsets, against the oracle schedule on the same GPU."""
+    from collections import OrderedDict
+    from transformers.models.opt.modeling_opt import OPTConfig, OPTDecoderLayer
+    from lightcompress_b200 import FakeQuantLinear, GPTQBlockwise, IntegerQuantizer
+    from oracle import gptq_block_ref, gptq_ref
+    hidden, ffn, T, n_seq = 256, 512, 96, 16
+    cfg = OPTConfig(hidden_size=hidden, ffn_dim=ffn, num_attention_heads=4, num_hidden_layers=1, vocab_size=128,
+                    max_position_embeddings=4 * T, word_embed_proj_dim=hidden, dropout=0.0, attention_dropout=0.0)
+    cfg._attn_implementation = 'sdpa'
+    torch.manual_seed(21)
+    block = OPTDecoderLayer(cfg, layer_idx=0).to(torch.bfloat16).eval()
+    g = torch.Generator().manual_seed(22)
+    for p in block.parameters():
+        if p.dim() == 2:
+            p.data = (torch.randn(p.shape, generator=g) * 0.02).to(torch.bfloat16)
+    xs = [torch.randn(1, T, hidden, generator=g).to(torch.bfloat16) for _ in range(n_seq)]
+    kwargs = {}
+
+    def names(b):
+        a = b.self_attn
+        return [[('self_attn.q_proj', a, 'q_proj'), ('self_attn.k_proj', a, 'k_proj'), ('self_attn.v_proj', a, 'v_proj')],
+                [('self_attn.out_proj', a, 'out_proj')], [('fc1', b, 'fc1')], [('fc2', b, 'fc2')]]
+
+    ref_block = copy.deepcopy(block).cuda()
+    ref_res, ref_out = gptq_block_ref.gptq_block(ref_block, [x.cuda() for x in xs], kwargs, subsets=names(ref_block))
+    gblock = copy.deepcopy(block).cuda()
+    assert not hasattr(gblock, 'mlp')
+    pairs = [OrderedDict((n, (parent, attr)) for n, parent, attr in sub) for sub in names(gblock)]
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    # every subset's column order pinned to the oracle's: the LayerNorm outputs feeding fc1 have near-equal
+    # Hessian diagonals, whose argsort order is decided by the last bits of the sums
+    pins = {sub[0][0]: ref_res[sub[0][0]]['buf_perm'] for sub in names(gblock)}
+    runner = GPTQBlockwise(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4,
+                                'pinned_perms': pins})
+    outs = runner.block_opt(gblock, [x.cuda() for x in xs], kwargs, subsets=pairs)
+    torch.cuda.synchronize()
+    assert runner.forward_passes == 5
+    with torch.no_grad():
+        fp_block = copy.deepcopy(block).cuda()
+        ys = [fp_block(x.cuda()) for x in xs]
+        o_fp = torch.cat([y[0] if isinstance(y, tuple) else y for y in ys]).float().cpu()
+    for si, sub in enumerate(names(gblock)):
+        for name, parent, attr in sub:
+            mod = getattr(parent, attr)
+            assert isinstance(mod, FakeQuantLinear) and mod.bias is not None
+            r = ref_res[name]
+            R, C = r['weight'].shape
+            got = {'weight': mod.weight.cpu(), 'buf_scales': mod.buf_scales.cpu(), 'buf_zeros': mod.buf_zeros.cpu(),
+                   'buf_perm': mod.buf_perm.cpu(), 'buf_invperm': mod.buf_invperm.cpu()}
+            a, b = torch.empty(R, C), torch.empty(R, C)
+            a[:, got['buf_perm']] = gptq_ref.codes_permuted(got)
+            b[:, r['buf_perm'].cpu()] = gptq_ref.codes_permuted({k: (v.cpu() if torch.is_tensor(v) else v)
+                                                                  for k, v in r.items()})
+            mism = float((a != b).float().mean())
+            print(f'opt {name}: code mismatch {mism:.4%}')
+            assert mism < 1e-3, (name, mism)
+    o_ref = torch.cat([o.cpu() for o in ref_out]).float()
+    o_gpu = torch.cat([o.cpu() for o in outs]).float()
+    e_ref = float((o_ref - o_fp).norm() / o_fp.norm())
+    e_gpu = float((o_gpu - o_fp).norm() / o_fp.norm())
+    print(f'opt block output error vs the unquantised block: oracle {e_ref:.5f}, ours {e_gpu:.5f}')
+    assert abs(e_gpu - e_ref) <= 0.01 * e_ref
