@@ -213,6 +213,38 @@ def synth_llama_adapter(ref, hf_config, seed=0, dtype=torch.bfloat16):
     return SynthLlama(config)
 
 
+def synth_adapter(ref, family, hf_config, seed=0, dtype=torch.bfloat16):
+    """Another of the reference's model adapters over a random-init HF model: family 'opt' (llmc/models/opt.py,
+    subsets q/k/v | out_proj | fc1 | fc2) or 'qwen2' (llmc/models/qwen2.py, Llama's layout with biases)."""
+    import importlib
+    import transformers
+    mod = importlib.import_module(f'llmc.models.{family}')
+    ref_cls = {'opt': 'Opt', 'qwen2': 'Qwen2', 'llama': 'Llama'}[family]
+    hf_cls = {'opt': 'OPTForCausalLM', 'qwen2': 'Qwen2ForCausalLM', 'llama': 'LlamaForCausalLM'}[family]
+
+    class Synth(getattr(mod, ref_cls)):
+        def build_tokenizer(self):
+            self.tokenizer = None
+
+        def build_model(self):
+            self.model_config = hf_config
+            model = getattr(transformers, hf_cls)(hf_config).to(dtype).eval()
+            g = torch.Generator().manual_seed(seed)
+            for n, p in model.named_parameters():
+                if p.dim() == 2:
+                    p.data = (torch.randn(p.shape, generator=g) * 0.02).to(dtype)
+                elif 'norm' in n and n.endswith('weight'):
+                    p.data = (1 + 0.1 * torch.randn(p.shape, generator=g)).to(dtype)
+                else:
+                    p.data = (0.02 * torch.randn(p.shape, generator=g)).to(dtype)
+            self.model = model
+
+    Synth.__name__ = ref_cls
+    config = AttrDict(model=dict(type=ref_cls, path=None, torch_dtype=str(dtype), tokenizer_mode='fast',
+                                 use_cpu_to_save_cuda_mem_for_catcher=bool(ref.on_cpu)))
+    return Synth(config)
+
+
 def gptq_quant_config(special=None, bit=4, symmetric=False, quant_out=True):
     """`quant` section of configs/quantization/methods/GPTQ/gptq_w_only.yml (values restated: W4 g128,
     actorder, static_groups False, percdamp 0.01, blocksize 128, true_sequential, quant_out)."""
