@@ -243,6 +243,39 @@ def test_gptq_on_another_model_family_through_the_reference_driver(ref):
     assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
 
 
+def test_gptq_on_qwen2_through_the_reference_driver(ref):
+    """Qwen2 (llmc/models/qwen2.py): Llama's layout with biases on q / k / v, so the staged plan applies after
+    its check against the block's own forward.  Same bars as for Llama."""
+    from transformers import Qwen2Config
+    T, n = 512, 16
+    cfg = Qwen2Config(hidden_size=256, intermediate_size=512, num_attention_heads=4, num_key_value_heads=4,
+                      num_hidden_layers=2, vocab_size=2048, max_position_embeddings=1024, rms_norm_eps=1e-5,
+                      use_cache=False, attention_dropout=0.0)
+    cfg._attn_implementation = 'sdpa'
+    calib = rd.calib_ids(n, T, cfg.vocab_size, seed=5)
+    probe = rd.calib_ids(1, T, cfg.vocab_size, seed=6)[0]['input_ids']
+    a = _run(ref, rd.gptq_quant_config(), cfg, calib, T, 3, False, probe, family='qwen2')
+    b = _run(ref, rd.gptq_quant_config(), cfg, calib, T, 3, True, probe, family='qwen2')
+    err_a = float((a['logits'] - a['logits_fp']).norm() / a['logits_fp'].norm())
+    err_b = float((b['logits'] - b['logits_fp']).norm() / b['logits_fp'].norm())
+    print(f'qwen2: logit error of the deployed model: reference {err_a:.5f}, plugin {err_b:.5f}')
+    assert a['classes'] == b['classes']
+    worst = []
+    for bi, (sa, sb) in enumerate(zip(a['state'], b['state'])):
+        assert list(sa) == list(sb) and len(sa) == 7
+        for name in sa:
+            ea, eb = sa[name], sb[name]
+            assert sorted(ea) == sorted(eb), (name, sorted(ea), sorted(eb))
+            for k in ea:
+                assert ea[k].shape == eb[k].shape and ea[k].dtype == eb[k].dtype, (name, k)
+            d = float((_codes_original_order(ea) != _codes_original_order(eb)).float().mean())
+            print(f'qwen2 block {bi} {name}: code mismatch {d:.4%}')
+            if bi == 0 and name in ('self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj'):
+                worst.append(d)
+    assert len(worst) == 3 and max(worst) < 1e-3, worst
+    assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
+
+
 def test_rtn_deploy_is_bit_identical(ref):
     cfg = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2)
     probe = rd.calib_ids(1, 64, cfg.vocab_size, seed=6)[0]['input_ids']
