@@ -255,6 +255,17 @@ def gptq_quant_config(special=None, bit=4, symmetric=False, quant_out=True):
                     special=sp)
 
 
+def gptq_w8a8_quant_config():
+    """`quant` section of configs/quantization/backend/vllm/w8a8_combin/step_2_gptq.yml (values restated:
+    W8 symmetric per_channel, A8 symmetric per_token, static_groups, actorder)."""
+    return AttrDict(method='GPTQ', modality='language', quant_out=True,
+                    weight=dict(bit=8, symmetric=True, granularity='per_channel', group_size=-1, qmax_to_tensor=True,
+                                calib_algo='minmax'),
+                    act=dict(bit=8, symmetric=True, granularity='per_token', qmax_to_tensor=True, calib_algo='minmax'),
+                    special=dict(actorder=True, static_groups=True, percdamp=0.01, blocksize=128, true_sequential=True,
+                                 online_rotate=False, fp32_had=True))
+
+
 def spqr_quant_config(special=None, quant_out=True):
     """`quant` section of configs/quantization/methods/SpQR/spqr_w_only.yml (values restated: W4 groups of
     16, round_zp False, actorder, percdamp 1, blocksize 128, relative_threshold 0.2, 3-bit second-level

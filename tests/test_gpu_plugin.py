@@ -276,6 +276,39 @@ def test_gptq_on_qwen2_through_the_reference_driver(ref):
     assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
 
 
+def test_gptq_w8a8_through_the_reference_driver(ref):
+    """The reference's W8A8 GPTQ recipe (w8a8_combin/step_2_gptq.yml): per_channel 8-bit weights with static
+    groups and per-token 8-bit activation fake quantisation inside every replaced linear's forward
+    (module_utils.py:712-737 -> a_qdq -> IntegerQuantizer.fake_quant_act_dynamic).  First-subset codes of the
+    first block below 0.1 %, deployed logits within 5 %."""
+    cfg, n, T = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2, vocab=2048, max_pos=1024), 16, 512
+    calib = rd.calib_ids(n, T, cfg.vocab_size, seed=5)
+    probe = rd.calib_ids(1, T, cfg.vocab_size, seed=6)[0]['input_ids']
+    a = _run(ref, rd.gptq_w8a8_quant_config(), cfg, calib, T, 3, False, probe)
+    b = _run(ref, rd.gptq_w8a8_quant_config(), cfg, calib, T, 3, True, probe)
+    err_a = float((a['logits'] - a['logits_fp']).norm() / a['logits_fp'].norm())
+    err_b = float((b['logits'] - b['logits_fp']).norm() / b['logits_fp'].norm())
+    print(f'w8a8: logit error of the deployed model: reference {err_a:.5f}, plugin {err_b:.5f}')
+    assert a['classes'] == b['classes']
+    worst = []
+    for bi, (sa, sb) in enumerate(zip(a['state'], b['state'])):
+        assert list(sa) == list(sb)
+        for name in sa:
+            ea, eb = sa[name], sb[name]
+            assert sorted(ea) == sorted(eb), (name, sorted(ea), sorted(eb))
+            for k in ea:
+                assert ea[k].shape == eb[k].shape and ea[k].dtype == eb[k].dtype, (name, k, ea[k].dtype, eb[k].dtype)
+            assert torch.equal(ea['buf_scales'], eb['buf_scales']), name       # static: the round-to-nearest scales
+            ca = torch.clamp(torch.round(ea['weight'].float() / ea['buf_scales'].float()), -128, 127)
+            cb = torch.clamp(torch.round(eb['weight'].float() / eb['buf_scales'].float()), -128, 127)
+            d = float((ca != cb).float().mean())
+            print(f'w8a8 block {bi} {name}: code mismatch {d:.4%}')
+            if bi == 0 and name in ('self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj'):
+                worst.append(d)
+    assert len(worst) == 3 and max(worst) < 1e-3, worst
+    assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
+
+
 def test_rtn_deploy_is_bit_identical(ref):
     cfg = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2)
     probe = rd.calib_ids(1, 64, cfg.vocab_size, seed=6)[0]['input_ids']
