@@ -309,6 +309,38 @@ def test_gptq_w8a8_through_the_reference_driver(ref):
     assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
 
 
+def test_gptq_static_groups_through_the_reference_driver(ref):
+    """static_groups (the setting of the reference's backend export recipes, e.g. vllm/gptq_w4a16.yml): the
+    linears keep their round-to-nearest buffers, the codes are taken in original column order."""
+    cfg, n, T = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2, vocab=2048, max_pos=1024), 16, 512
+    calib = rd.calib_ids(n, T, cfg.vocab_size, seed=5)
+    probe = rd.calib_ids(1, T, cfg.vocab_size, seed=6)[0]['input_ids']
+    qc = rd.gptq_quant_config({'static_groups': True}, symmetric=True)
+    a = _run(ref, copy.deepcopy(qc), cfg, calib, T, 3, False, probe)
+    b = _run(ref, copy.deepcopy(qc), cfg, calib, T, 3, True, probe)
+    err_a = float((a['logits'] - a['logits_fp']).norm() / a['logits_fp'].norm())
+    err_b = float((b['logits'] - b['logits_fp']).norm() / b['logits_fp'].norm())
+    print(f'static groups: logit error of the deployed model: reference {err_a:.5f}, plugin {err_b:.5f}')
+    worst = []
+    for bi, (sa, sb) in enumerate(zip(a['state'], b['state'])):
+        for name in sa:
+            ea, eb = sa[name], sb[name]
+            assert sorted(ea) == sorted(eb), (name, sorted(ea), sorted(eb))
+            for k in ea:
+                assert ea[k].shape == eb[k].shape and ea[k].dtype == eb[k].dtype, (name, k, ea[k].dtype, eb[k].dtype)
+            assert torch.equal(ea['buf_scales'], eb['buf_scales']), name
+
+            def codes(e):
+                g = e['weight'].float().reshape(-1, 128)
+                return torch.clamp(torch.round(g / e['buf_scales'].float()), -8, 7)
+            d = float((codes(ea) != codes(eb)).float().mean())
+            print(f'static groups block {bi} {name}: code mismatch {d:.4%}')
+            if bi == 0 and name in ('self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj'):
+                worst.append(d)
+    assert len(worst) == 3 and max(worst) < 1e-3, worst
+    assert abs(err_a - err_b) <= 0.05 * err_a + 1e-5
+
+
 def test_rtn_deploy_is_bit_identical(ref):
     cfg = rd.tiny_llama_config(hidden=256, inter=512, heads=4, layers=2)
     probe = rd.calib_ids(1, 64, cfg.vocab_size, seed=6)[0]['input_ids']
