@@ -526,6 +526,14 @@ int lc_awq_clip_search(const void* W, const void* X, int dtype, int64_t rows, in
                        int64_t x_token_step, int64_t group, int bits, int sym, int clip_sym, int n_grid,
                        double max_shrink, void* best_max, void* best_min, void* W_out, lc_stream_t stream);
 
+/* The same search with the sums formed on the CUDA cores (an unpack and an fp32 add per product) instead of
+ * by MMAs against a matrix of ones.  Both round every product to the tensor dtype first and differ only in
+ * the order of the fp32 additions; kept for comparison and for token counts that are not a multiple of 16,
+ * which lc_awq_clip_search routes here by itself. */
+int lc_awq_clip_search_cuda_cores(const void* W, const void* X, int dtype, int64_t rows, int64_t cols, int64_t x_tokens,
+                       int64_t x_token_step, int64_t group, int bits, int sym, int clip_sym, int n_grid,
+                       double max_shrink, void* best_max, void* best_min, void* W_out, lc_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Export layouts for 4-bit codes (what follows the hot path when a real-quant model is saved).
  * ------------------------------------------------------------------------------------------ */

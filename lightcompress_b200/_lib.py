@@ -81,6 +81,7 @@ SIGNATURES = {
     'lc_silu_mul': [_p, _p, _i, _i64, _p, _p],
     'lc_rmsnorm': [_p, _p, _i, _i64, _i64, _f, _f, _p, _p],
     'lc_awq_clip_search': [_p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _d, _p, _p, _p, _p],
+    'lc_awq_clip_search_cuda_cores': [_p, _p, _i, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _d, _p, _p, _p, _p],
 }
 
 

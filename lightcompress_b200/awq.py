@@ -43,6 +43,9 @@ class Awq:
         self.clip_n_grid, self.clip_max_shrink = 20, 0.5
         self.n_sample_token = calib_seq_len
         self.fused_block_ops = special.get('fused_block_ops', True)
+        # clip search: the sums of the rounded products on the tensor cores ('tensor': MMAs against a matrix of
+        # ones) or on the CUDA cores ('cuda_cores'); same products, another order of the fp32 additions
+        self.clip_sums = special.get('clip_sums', 'tensor')
         self.phases = PhaseTimer()      # off unless a caller switches it on (bench.py)
         if self.trans_version != 'v2' or self.clip_version != 'v1':
             raise NotImplementedError('only trans_version v2 / clip_version v1 are on the B200 hot path')
@@ -180,7 +183,8 @@ class Awq:
         best_max = torch.empty((R, n_g, 1), dtype=w.dtype, device=w.device)
         best_min = torch.empty((R, n_g, 1), dtype=w.dtype, device=w.device)
         multi = parallel.world()[1] > 1
-        L.call('lc_awq_clip_search', L.ptr(w), L.ptr(x2), L.lc_dtype(w), R, C, n_tok_all, step, wq.group_size,
+        L.call('lc_awq_clip_search' if self.clip_sums == 'tensor' else 'lc_awq_clip_search_cuda_cores',
+               L.ptr(w), L.ptr(x2), L.lc_dtype(w), R, C, n_tok_all, step, wq.group_size,
                int(wq.bit), int(wq.sym), int(self.clip_sym), self.clip_n_grid, float(self.clip_max_shrink),
                L.ptr(best_max), L.ptr(best_min), L.ptr(w) if apply and not multi else None, L.stream_of(w))
         if multi:

@@ -191,6 +191,7 @@ struct ClipArgs {
   void* best_min;
   int64_t rows, cols, x_row_stride;  // x_row_stride: elements between sampled token rows
   int n_tok, n_groups, n_iter, n_grid, bits, sym, clip_sym, rows_per_cta;
+  int ffma_sums;       // 1: sums on the CUDA cores (the kernel without MMAs), for comparison
   QRange qr;
 };
 
@@ -336,19 +337,270 @@ __global__ void __launch_bounds__(kClipWarps * 32, 1) clip_search_kernel(ClipArg
   }
 }
 
+
+// ---- clip search, summation on the tensor cores -------------------------------------------------------
+// The reference's errors are sums of products that were each rounded to the tensor dtype
+// ((input_feat * q_w).sum(-1), auto_clip.py:150-171), so the products cannot come from a GEMM.  The
+// SUMS can: a lane forms the rounded products with packed multiplies directly in the register layout
+// of an MMA A operand (16 tokens x 16 columns; the lane's x values come from ldmatrix, its four column
+// weights from shared memory) and the MMA multiplies them by a matrix of ones, which adds them up in
+// fp32 -- one instruction per 256 products instead of an unpack and an add per product.  The original
+// weights and all clip candidates of a row are prepared first (kMmaCands vectors of 128 values, stored
+// in the operand's column order), so an x fragment is loaded once per row and used by every candidate.
+constexpr int kMmaCands = 11;      // the unclipped row + up to 10 grid points (max_shrink 0.5 of a 20-point grid)
+
+template <typename T> struct MmaOps;
+template <> struct MmaOps<__nv_bfloat16> {
+  static constexpr uint32_t kOnes = 0x3F803F80u;
+  __device__ static __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 p = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&p);
+  }
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  __device__ static __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 v = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  __device__ static __forceinline__ float sum2(uint32_t a) {
+    return __uint_as_float(a << 16) + __uint_as_float(a & 0xffff0000u);
+  }
+  __device__ static __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(kOnes), "r"(kOnes));
+  }
+};
+template <> struct MmaOps<__half> {
+  static constexpr uint32_t kOnes = 0x3C003C00u;
+  __device__ static __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+    const __half2 p = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&p);
+  }
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  __device__ static __forceinline__ uint32_t sub2(uint32_t a, uint32_t b) {
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  __device__ static __forceinline__ float sum2(uint32_t a) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&a));
+    return f.x + f.y;
+  }
+  __device__ static __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(kOnes), "r"(kOnes));
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kClipWarps * 32, 1) clip_search_mma_kernel(ClipArgs a) {
+  using E = Elem<T>;
+  using M = MmaOps<T>;
+  extern __shared__ __align__(16) unsigned char smem[];
+  T* xs = reinterpret_cast<T*>(smem);                                              // [n_tok][kXStride]
+  uint32_t* wq_all = reinterpret_cast<uint32_t*>(xs + (size_t)kClipMaxTok * kXStride);   // [warps][cands][64]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = blockIdx.x;
+  const T* X = reinterpret_cast<const T*>(a.X);
+  const T* W = reinterpret_cast<const T*>(a.W);
+
+  for (int idx = threadIdx.x; idx < a.n_tok * (kClipGroup / 8); idx += blockDim.x) {
+    const int t = idx / (kClipGroup / 8), j = idx % (kClipGroup / 8);
+    const uint4 v = *reinterpret_cast<const uint4*>(X + (int64_t)t * a.x_row_stride + (int64_t)g * kClipGroup + j * 8);
+    *reinterpret_cast<uint4*>(xs + (size_t)t * kXStride + j * 8) = v;
+  }
+  __syncthreads();
+
+  uint32_t* wq = wq_all + warp * (kMmaCands * 64);
+  // The lane owns columns 4 * lane .. + 3 of the group: k tile lane / 4, and inside it the column pairs
+  // (2c, 2c + 1) of c = 2 * (lane & 1) and 2 * (lane & 1) + 1, first half of the tile for (lane & 3) < 2,
+  // second half otherwise.  Operand order of a k tile: [c][half] pairs, 8 words.
+  const int st_kt = lane >> 2, st_half = (lane & 3) >> 1, st_c = 2 * (lane & 1);
+  const int st0 = st_kt * 8 + st_c * 2 + st_half, st1 = st0 + 2;
+  const int c = lane & 3;
+  const float n_tok_f = (float)a.n_tok;
+  const int n_cand = a.n_iter + 1;
+  const uint32_t xs_base = (uint32_t)__cvta_generic_to_shared(xs);
+  // ldmatrix row address of this lane: matrix lane / 8 = (token half, column half), row lane % 8
+  const uint32_t ld_off = (uint32_t)((((lane >> 3) & 1) * 8 + (lane & 7)) * kXStride + (lane >> 4) * 8) * (uint32_t)sizeof(T);
+
+  const int64_t r_begin = (int64_t)blockIdx.y * a.rows_per_cta;
+  const int64_t r_end = min(a.rows, r_begin + a.rows_per_cta);
+  for (int64_t r = r_begin + warp; r < r_end; r += kClipWarps) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(W + r * a.cols + (int64_t)g * kClipGroup + 4 * lane);
+    const T* wp = reinterpret_cast<const T*>(&raw);
+    float w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = E::to_f(wp[i]);
+    float mx = a.clip_sym ? fabsf(w[0]) : w[0], mn = w[0];
+#pragma unroll
+    for (int i = 1; i < 4; ++i) {
+      mx = nan_max(mx, a.clip_sym ? fabsf(w[i]) : w[i]);
+      mn = nan_min(mn, w[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = nan_max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      mn = nan_min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    }
+    const float org_max = mx, org_min = mn;
+
+    // ---- the row and its clip candidates, in operand order ----
+    __syncwarp();
+    wq[st0] = raw.x;
+    wq[st1] = raw.y;
+    for (int it = 0; it < a.n_iter; ++it) {
+      const float ratio = (float)(1.0 - (double)it / (double)a.n_grid);
+      const float max_val = E::rnd(__fmul_rn(org_max, ratio));
+      const float min_val = a.clip_sym ? -max_val : E::rnd(__fmul_rn(org_min, ratio));
+      float cw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cw[i] = clampf(w[i], min_val, max_val);
+      float cmx = cw[0], cmn = cw[0];
+#pragma unroll
+      for (int i = 1; i < 4; ++i) {
+        cmx = nan_max(cmx, cw[i]);
+        cmn = nan_min(cmn, cw[i]);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        cmx = nan_max(cmx, __shfl_xor_sync(0xffffffffu, cmx, o));
+        cmn = nan_min(cmn, __shfl_xor_sync(0xffffffffu, cmn, o));
+      }
+      float s, z;
+      int_qparams<T>(cmn, cmx, a.qr, a.sym, s, z);
+      T qw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qw[i] = E::from_f(int_dequant<T>(int_quant<T>(cw[i], s, z, a.qr), s, z));
+      const uint2 packed = *reinterpret_cast<const uint2*>(qw);
+      wq[(it + 1) * 64 + st0] = packed.x;
+      wq[(it + 1) * 64 + st1] = packed.y;
+    }
+    __syncwarp();
+
+    // ---- sums of rounded products: tokens in tiles of 16, columns in tiles of 16 ----
+    float errsum[kMmaCands];
+#pragma unroll
+    for (int q = 0; q < kMmaCands; ++q) errsum[q] = 0.f;
+#pragma unroll 1
+    for (int tt = 0; tt < a.n_tok; tt += 16) {
+      float acc[kMmaCands][4];
+#pragma unroll
+      for (int q = 0; q < kMmaCands; ++q) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
+      // x fragment of the next column tile in flight while the eleven candidates of this one are multiplied;
+      // a candidate's four weights are loaded for all candidates before the first product, so that the loads,
+      // the packed multiplies and the eleven independent accumulator chains overlap
+      uint32_t xf[2][4];
+      {
+        const uint32_t addr = xs_base + (uint32_t)(tt * kXStride) * (uint32_t)sizeof(T) + ld_off;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(xf[0][0]), "=r"(xf[0][1]), "=r"(xf[0][2]), "=r"(xf[0][3])
+                     : "r"(addr));
+      }
+#pragma unroll
+      for (int kt = 0; kt < kClipGroup / 16; ++kt) {
+        const int cur = kt & 1;
+        if (kt + 1 < kClipGroup / 16) {
+          const uint32_t addr = xs_base + (uint32_t)(tt * kXStride + (kt + 1) * 16) * (uint32_t)sizeof(T) + ld_off;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                       : "=r"(xf[cur ^ 1][0]), "=r"(xf[cur ^ 1][1]), "=r"(xf[cur ^ 1][2]), "=r"(xf[cur ^ 1][3])
+                       : "r"(addr));
+        }
+        uint2 qv[kMmaCands];
+#pragma unroll
+        for (int q = 0; q < kMmaCands; ++q) qv[q] = *reinterpret_cast<const uint2*>(&wq[q * 64 + kt * 8 + c * 2]);
+#pragma unroll
+        for (int q = 0; q < kMmaCands; ++q) {
+          if (q < n_cand)
+            M::mma(acc[q], M::mul2(xf[cur][0], qv[q].x), M::mul2(xf[cur][1], qv[q].x), M::mul2(xf[cur][2], qv[q].y),
+                   M::mul2(xf[cur][3], qv[q].y));
+        }
+      }
+      // rows grp and grp + 8 of the tile; the four lanes of a quad hold the same sums: lane c == 0 counts
+      // (packed: both tokens of the lane at once; the difference of two T values and the square of a T value
+      // round once to T either way)
+      if (c == 0) {
+        const uint32_t org2 = M::pack(acc[0][0], acc[0][2]);
+#pragma unroll
+        for (int q = 1; q < kMmaCands; ++q) {
+          if (q < n_cand) {
+            const uint32_t d2 = M::sub2(M::pack(acc[q][0], acc[q][2]), org2);
+            errsum[q] += M::sum2(M::mul2(d2, d2));
+          }
+        }
+      }
+    }
+    float best_max = org_max, best_min = org_min;
+    float min_err = E::rnd(1e9f);
+#pragma unroll
+    for (int q = 1; q < kMmaCands; ++q) {
+      if (q < n_cand) {
+        float accq = errsum[q];
+#pragma unroll
+        for (int o = 16; o >= 4; o >>= 1) accq += __shfl_xor_sync(0xffffffffu, accq, o);
+        accq = __shfl_sync(0xffffffffu, accq, 0);
+        const float err = E::rnd(__fdiv_rn(accq, n_tok_f));
+        if (err < min_err) {
+          const float ratio = (float)(1.0 - (double)(q - 1) / (double)a.n_grid);
+          min_err = err;
+          best_max = E::rnd(__fmul_rn(org_max, ratio));
+          best_min = a.clip_sym ? -best_max : E::rnd(__fmul_rn(org_min, ratio));
+        }
+      }
+    }
+    if (lane == 0) {
+      reinterpret_cast<T*>(a.best_max)[r * a.n_groups + g] = E::from_f(best_max);
+      reinterpret_cast<T*>(a.best_min)[r * a.n_groups + g] = E::from_f(best_min);
+    }
+    if (a.W_out) {
+      const float lo = a.clip_sym ? -best_max : best_min;
+      T cwv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cwv[i] = E::from_f(clampf(w[i], lo, best_max));
+      *reinterpret_cast<uint2*>(reinterpret_cast<T*>(a.W_out) + r * a.cols + (int64_t)g * kClipGroup + 4 * lane) =
+          *reinterpret_cast<const uint2*>(cwv);
+    }
+  }
+}
+
 template <typename T>
 int clip_launch(const ClipArgs& a0, cudaStream_t st) {
   ClipArgs a = a0;
   const size_t smem = ((size_t)kClipMaxTok * kXStride + (size_t)kClipWarps * kClipGroup) * sizeof(T);
+  const size_t smem_mma = (size_t)kClipMaxTok * kXStride * sizeof(T) + (size_t)kClipWarps * kMmaCands * 64 * sizeof(uint32_t);
+  const bool use_mma = a.n_tok % 16 == 0 && a.n_iter + 1 <= kMmaCands && !a.ffma_sums;
   LC_CHECK_CUDA(cudaFuncSetAttribute(clip_search_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  // one CTA per (group, row chunk): about two waves of CTAs, each staging its x slice once
-  int splits = (2 * kNumSMsB200 + a.n_groups - 1) / a.n_groups;
-  if (splits < 1) splits = 1;
-  int64_t rpc = (a.rows + splits - 1) / splits;
+  LC_CHECK_CUDA(cudaFuncSetAttribute(clip_search_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem_mma));
+  // one CTA per (group, row chunk), one CTA per SM at a time: the number of row chunks is the one between
+  // one and four waves of CTAs that fills its last wave best (each CTA stages its x slice once)
+  int best_splits = 1;
+  double best_eff = -1.0;
+  const int max_splits = (int)((a.rows + kClipWarps - 1) / kClipWarps);
+  for (int sp = 1; sp <= max_splits && (int64_t)sp * a.n_groups <= 4 * kNumSMsB200 + a.n_groups; ++sp) {
+    int64_t rp = (a.rows + sp - 1) / sp;
+    rp = (rp + kClipWarps - 1) / kClipWarps * kClipWarps;
+    const int64_t ctas = (int64_t)a.n_groups * ((a.rows + rp - 1) / rp);
+    if (ctas < kNumSMsB200 && sp < max_splits) continue;
+    const int64_t waves = (ctas + kNumSMsB200 - 1) / kNumSMsB200;
+    // time ~ waves x rows per CTA; efficiency = work / (SMs x time)
+    const double eff = (double)a.rows * a.n_groups / ((double)kNumSMsB200 * (double)waves * (double)rp);
+    if (eff > best_eff + 1e-9) best_eff = eff, best_splits = sp;
+  }
+  int64_t rpc = (a.rows + best_splits - 1) / best_splits;
   rpc = (rpc + kClipWarps - 1) / kClipWarps * kClipWarps;
   a.rows_per_cta = (int)rpc;
   dim3 grid((unsigned)a.n_groups, (unsigned)((a.rows + rpc - 1) / rpc));
-  clip_search_kernel<T><<<grid, kClipWarps * 32, smem, st>>>(a);
+  if (use_mma) clip_search_mma_kernel<T><<<grid, kClipWarps * 32, smem_mma, st>>>(a);
+  else clip_search_kernel<T><<<grid, kClipWarps * 32, smem, st>>>(a);
   LC_LAUNCH_CHECK();
   return LC_OK;
 }
@@ -441,10 +693,10 @@ extern "C" LC_API int lc_awq_loss(const void* a, const void* b, int dtype, int64
   return LC_OK;
 }
 
-extern "C" LC_API int lc_awq_clip_search(const void* W, const void* X, int dtype, int64_t rows, int64_t cols,
-                                         int64_t x_tokens, int64_t x_token_step, int64_t group, int bits, int sym,
-                                         int clip_sym, int n_grid, double max_shrink, void* best_max, void* best_min,
-                                         void* W_out, lc_stream_t stream) {
+static int clip_search_impl(const void* W, const void* X, int dtype, int64_t rows, int64_t cols, int64_t x_tokens,
+                            int64_t x_token_step, int64_t group, int bits, int sym, int clip_sym, int n_grid,
+                            double max_shrink, void* best_max, void* best_min, void* W_out, int ffma_sums,
+                            lc_stream_t stream) {
   using namespace lc;
   if (!W || !X || !best_max || !best_min || rows <= 0 || cols <= 0 || x_tokens <= 0 || x_token_step <= 0) return LC_ERR_ARG;
   if (bits < 2 || bits > 8 || n_grid <= 0 || max_shrink < 0.0 || max_shrink > 1.0) return LC_ERR_ARG;
@@ -470,7 +722,24 @@ extern "C" LC_API int lc_awq_clip_search(const void* W, const void* X, int dtype
   a.sym = sym ? 1 : 0;
   a.clip_sym = clip_sym ? 1 : 0;
   a.rows_per_cta = 0;
+  a.ffma_sums = ffma_sums;
   a.qr = int_qrange(bits, a.sym);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return dtype == LC_BF16 ? clip_launch<__nv_bfloat16>(a, st) : clip_launch<__half>(a, st);
+}
+
+extern "C" LC_API int lc_awq_clip_search(const void* W, const void* X, int dtype, int64_t rows, int64_t cols,
+                                         int64_t x_tokens, int64_t x_token_step, int64_t group, int bits, int sym,
+                                         int clip_sym, int n_grid, double max_shrink, void* best_max, void* best_min,
+                                         void* W_out, lc_stream_t stream) {
+  return clip_search_impl(W, X, dtype, rows, cols, x_tokens, x_token_step, group, bits, sym, clip_sym, n_grid, max_shrink,
+                          best_max, best_min, W_out, 0, stream);
+}
+
+extern "C" LC_API int lc_awq_clip_search_cuda_cores(const void* W, const void* X, int dtype, int64_t rows, int64_t cols,
+                                                    int64_t x_tokens, int64_t x_token_step, int64_t group, int bits,
+                                                    int sym, int clip_sym, int n_grid, double max_shrink,
+                                                    void* best_max, void* best_min, void* W_out, lc_stream_t stream) {
+  return clip_search_impl(W, X, dtype, rows, cols, x_tokens, x_token_step, group, bits, sym, clip_sym, n_grid, max_shrink,
+                          best_max, best_min, W_out, 1, stream);
 }

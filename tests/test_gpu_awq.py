@@ -83,6 +83,34 @@ def test_clip_search_matches_oracle(sym, clip_sym):
     assert torch.equal(w2, awq_ref.apply_clip(w, mn, mx, clip_sym))
 
 
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_clip_search_sums_on_tensor_cores_agree_with_cuda_cores(dtype):
+    """The two ways of adding up the rounded products (MMAs against ones / fp32 adds) against each other and
+    against torch on the same GPU, at a 4096-wide linear: the share of (row, group) ranges that differ between
+    any two of the three is the share of near-ties of the flat objective, the same for every pair."""
+    from lightcompress_b200 import Awq
+    g = torch.Generator().manual_seed(3400)
+    R, C, T = 1024, 4096, 2048
+    w = (torch.randn(R, C, generator=g) * 0.02).to(dtype).cuda()
+    x = torch.randn(4, T // 4, C, generator=g)
+    x[:, :, torch.randperm(C, generator=g)[:40]] *= 20
+    x = x.to(dtype).cuda()
+    res = {}
+    for how in ('tensor', 'cuda_cores'):
+        awq = Awq(_wq(False), {'clip_sym': False, 'clip_sums': how}, calib_seq_len=512)
+        w2 = w.clone()
+        mx, mn = awq.auto_clip_layer(w2, x)
+        res[how] = (mx, mn, w2)
+        assert torch.equal(w2, awq_ref.apply_clip(w, mn, mx, False))
+    mx_ref, mn_ref = awq_ref.auto_clip_layer(w, x, 4, False, 128, False, n_sample_token=512)
+    res['torch'] = (mx_ref, mn_ref, None)
+    pairs = {}
+    for a_, b_ in (('tensor', 'cuda_cores'), ('tensor', 'torch'), ('cuda_cores', 'torch')):
+        pairs[(a_, b_)] = float(((res[a_][0] != res[b_][0]) | (res[a_][1] != res[b_][1])).float().mean())
+        print(f'clip search {dtype}: {a_} vs {b_}: {pairs[(a_, b_)]:.3%} of (row, group) ranges differ')
+    assert pairs[('tensor', 'torch')] < max(0.05, 1.5 * pairs[('cuda_cores', 'torch')])
+
+
 def _tiny_block(state, hidden=256, inter=512, heads=4, T=64):
     from tests.test_oracle_golden import _tiny_block as tb
     return tb(state, hidden, inter, heads, T)
