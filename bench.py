@@ -526,7 +526,7 @@ def run_secondary(args):
                                 'frac': flops / (ms * 1e-3) / 1e12 / tf_peak, 'traffic': None,
                                 'peak_kind': 'measured sustained cuBLAS bf16 (of measured)',
                                 'note': 'FLOPs of the 80 candidate forwards over the whole step, which also holds the '
-                                        'clip search (CUDA cores) and the scale kernels'}
+                                        'clip search and the scale kernels'}
         if args.workload == 'moe':
             tot = extra['algorithmic_bytes']['weights'] + extra['algorithmic_bytes']['activations']
             line['roofline'] = {'bound': 'hbm', 'achieved': tot / world / (ms * 1e-3) / 1e9, 'peak': hbm_peak,
