@@ -160,12 +160,16 @@ class GPTQ:
         """All-reduce once per layer (gptq.py:292-295 does it per call); returns (H_raw, 2/n)."""
         st = self.layers_cache[name]
         self._flush(st)
-        # the kernel's status word travels with the sample count: every rank learns of a failure on any
-        # rank and raises here, before the next collective, instead of waiting in it for a peer that left
-        _, n, code = parallel.reduce_hessian(st['H'], st['nsamples'], st['status'])
-        self.check_status()
-        if code != 0:
-            raise L.LcError('lc_hessian_accum', code, L.status_string(code))
+        if parallel.world()[1] == 1:
+            # one rank: no host wait here; the status word is read with the others at check_status()
+            n = st['nsamples']
+            self._pending_status.append(st['status'])
+        else:
+            # every rank learns in this reduction whether any rank's kernel failed, and all raise together;
+            # the other pending status words are combined over the ranks at the block's check_status()
+            _, n, code = parallel.reduce_hessian(st['H'], st['nsamples'], st['status'])
+            if code != 0:
+                raise L.LcError('lc_hessian_accum', code, L.status_string(code))
         if n == 0:
             raise RuntimeError(f'no calibration samples were accumulated for layer {name}')
         return st['H'], 2.0 / n
@@ -590,7 +594,7 @@ class GPTQ:
                     if c == L.LC_ERR_NOT_PD:
                         raise torch.linalg.LinAlgError('lc_gptq_factorize: the dampened Hessian is not '
                                                        'positive definite')
-                    raise L.LcError('lc_gptq_weight_transform_tc / lc_gptq_factorize', c, L.status_string(c))
+                    raise L.LcError('lc_hessian_accum / lc_gptq_factorize / lc_gptq_weight_transform_tc', c, L.status_string(c))
 
     @torch.no_grad()
     def free(self, name):

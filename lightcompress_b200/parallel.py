@@ -50,15 +50,21 @@ def reduce_hessian(H_raw, n_sequences, status=None):
     divides).  status: this rank's int32 device status word of the Hessian kernel (0 = ok, negative =
     error); `code` is the worst one over all ranks, so that every rank can raise together."""
     _, w = world()
-    own = 0 if status is None else int(status.item())
     if w == 1:
-        return H_raw, n_sequences, own
+        return H_raw, n_sequences, (0 if status is None else int(status.item()))
     dist.all_reduce(H_raw, op=dist.ReduceOp.SUM)
-    # one small collective carries both: the count in slot 0, the number of failing ranks in slot 1
-    nt = torch.tensor([n_sequences, 1 if own != 0 else 0], dtype=torch.int64, device=H_raw.device)
+    # one small collective carries both: the count in slot 0, the number of failing ranks in slot 1 (formed on
+    # the device from the status word: the host waits once, for the reduced pair)
+    nt = torch.zeros(2, dtype=torch.int64, device=H_raw.device)
+    nt[0] = n_sequences
+    if status is not None:
+        nt[1] = (status.reshape(-1)[0] != 0).to(torch.int64)
     dist.all_reduce(nt, op=dist.ReduceOp.SUM)
     total, failed = (int(v) for v in nt.tolist())
-    return H_raw, total, (own if own != 0 else (LC_ERR_PEER if failed else 0))
+    if not failed:
+        return H_raw, total, 0
+    own = 0 if status is None else int(status.item())
+    return H_raw, total, (own if own != 0 else LC_ERR_PEER)
 
 
 LC_ERR_PEER = -8        # LC_ERR_CUDA: "a peer rank reported a device error"
