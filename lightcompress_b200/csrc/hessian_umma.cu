@@ -272,21 +272,27 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_umma_kernel(const __grid_
             tmem_ld32_nowait(tbase + (uint32_t)(cc * 32), r0);
             if (two) tmem_ld32_nowait(tbase + (uint32_t)(cc * 32 + 32), r1);
             tmem_wait_ld();
-            if (m < C) {
-              float* row = a.H + m * C + n0;
+            // A lane holds one row of the chunk.  Written straight from there, a 128-bit atomic of the warp would
+            // touch 32 rows with 16 bytes each (32 half-used sectors); through the warp's staging tile eight
+            // lanes cover 128 contiguous bytes of a row, so an instruction touches 4 rows x 4 full sectors.
+            auto flush_chunk = [&](const uint32_t (&rv)[32], int64_t nbase) {
+              __syncwarp();
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
-                if (n0 + j < C)
-                  red_add_v4(row + j, __uint_as_float(r0[j]) * a.alpha, __uint_as_float(r0[j + 1]) * a.alpha,
-                             __uint_as_float(r0[j + 2]) * a.alpha, __uint_as_float(r0[j + 3]) * a.alpha);
-              if (two) {
+                *reinterpret_cast<float4*>(&stg[lane * STG_STRIDE + j]) =
+                    make_float4(__uint_as_float(rv[j]) * a.alpha, __uint_as_float(rv[j + 1]) * a.alpha,
+                                __uint_as_float(rv[j + 2]) * a.alpha, __uint_as_float(rv[j + 3]) * a.alpha);
+              __syncwarp();
+              const int64_t nc = nbase + 4 * (lane & 7);
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                  if (n0 + 32 + j < C)
-                    red_add_v4(row + 32 + j, __uint_as_float(r1[j]) * a.alpha, __uint_as_float(r1[j + 1]) * a.alpha,
-                               __uint_as_float(r1[j + 2]) * a.alpha, __uint_as_float(r1[j + 3]) * a.alpha);
+              for (int i = 0; i < 8; ++i) {
+                const int rr = 4 * i + (lane >> 3);
+                const float4 t = *reinterpret_cast<const float4*>(&stg[rr * STG_STRIDE + 4 * (lane & 7)]);
+                if (m_blk0 + rr < C && nc < C) red_add_v4(a.H + (m_blk0 + rr) * C + nc, t.x, t.y, t.z, t.w);
               }
-            }
+            };
+            flush_chunk(r0, n0);
+            if (two) flush_chunk(r1, n0 + 32);
           }
           continue;
         }
