@@ -123,7 +123,7 @@ def kwargs_to(kwargs, dev):
 LINEAR_NAMES = ['self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj', 'self_attn.o_proj', 'mlp.gate_proj',
                 'mlp.up_proj', 'mlp.down_proj']
 # DRAM bytes per 16384-token Hessian launch by width, from the ncu captures under profiles/
-HESSIAN_NCU_TRAFFIC = {4096: 213.7e6, 11008: 2833.0e6}
+HESSIAN_NCU_TRAFFIC = {4096: 310.4e6, 11008: 3511.0e6}
 LINEAR_SHAPES = [(HID, HID)] * 4 + [(INTER, HID)] * 2 + [(HID, INTER)]   # (rows, cols) of q,k,v,o,gate,up,down
 
 
@@ -1151,7 +1151,9 @@ def main():
         roofline['traffic'] = sum(d[0] * ncu_traffic[c] for c, d in hess.items()) / n_l
         roofline['traffic_source'] = ('static: profiles/hessian_umma_C4096.md (ncu, per launch), weighted over the '
                                       'launch mix of the step')
-        roofline['algorithmic_bytes'] = sum(d[0] * (2.0 * 16384 * c + 8.0 * c * c) for c, d in hess.items()) / n_l
+        # X read once (bf16) + the 256 x 256 tiles on and above the diagonal of H read and written once (fp32)
+        roofline['algorithmic_bytes'] = sum(d[0] * (2.0 * 16384 * c + 8.0 * 65536 * n_super(c))
+                                            for c, d in hess.items()) / n_l
 
     line = {'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong',
