@@ -29,7 +29,9 @@ constexpr int P_ATOM_BYTES = ATOM_F * 4 * PBK;   // 2048: one 32-float x 16-row 
 constexpr int A_ATOMS = PM / ATOM_F;          // 4
 constexpr int B_ATOMS = PN / ATOM_F;          // 8
 constexpr int P_STAGE_BYTES = 2 * (A_ATOMS + B_ATOMS) * P_ATOM_BYTES;  // 49152: A_hi, A_lo, B_hi, B_lo
-constexpr int P_SMEM_BYTES = PSTAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_STG_STRIDE = 36;                                   // floats per staged row of the epilogue
+constexpr int P_STG_BYTES_PER_WARP = 32 * P_STG_STRIDE * 4;        // 4608
+constexpr int P_SMEM_BYTES = PSTAGES * P_STAGE_BYTES + 1024 + 256 + 4 * P_STG_BYTES_PER_WARP;
 constexpr int P_TMEM_COLS = 512;              // two accumulators of 256 columns
 constexpr int kThreads = 192;
 
@@ -92,6 +94,7 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
   uint64_t* bars = reinterpret_cast<uint64_t*>(gen_base + PSTAGES * P_STAGE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* staging = reinterpret_cast<float*>(gen_base + PSTAGES * P_STAGE_BYTES + 256);
   const uint32_t bar0 = base + PSTAGES * P_STAGE_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (PSTAGES + s); };
@@ -233,26 +236,39 @@ __global__ void __launch_bounds__(kThreads, 1) tf32x3_gemm_kernel(const __grid_c
       const uint32_t tmem_acc = tmem_base + buf * PN;
       const int pM = a.p[w.pi].M, pN = a.p[w.pi].N;
       float* const pC = a.p[w.pi].C;
-      const int m = w.m0 + q * 32 + lane;
 #pragma unroll 1
       for (int cc = 0; cc < PN / 32; ++cc) {
         const int n0 = w.n0 + cc * 32;
         if (n0 >= pN) break;
         float v[32];
         tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(cc * 32), v);
-        if (m < pM) {
-          float* row = pC + (int64_t)m * a.ldc + n0;
+        // A lane holds one row of the 32 x 32 chunk; through the warp's staging tile eight lanes cover 128
+        // contiguous bytes of a row of C, so the read-modify-write moves whole sectors
+        float* stg = staging + q * (P_STG_BYTES_PER_WARP / 4);
+        __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            if (n0 + j < pN) {
-              float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (a.beta) c = *reinterpret_cast<float4*>(row + j);
-              c.x = fmaf(a.sign, v[j], c.x);
-              c.y = fmaf(a.sign, v[j + 1], c.y);
-              c.z = fmaf(a.sign, v[j + 2], c.z);
-              c.w = fmaf(a.sign, v[j + 3], c.w);
-              *reinterpret_cast<float4*>(row + j) = c;
-            }
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(&stg[lane * P_STG_STRIDE + j]) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        __syncwarp();
+        const int nc = n0 + 4 * (lane & 7);
+        const int mr0 = w.m0 + q * 32 + (lane >> 3);
+        float4 cv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          cv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (a.beta && mr0 + 4 * i < pM && nc < pN)
+            cv[i] = *reinterpret_cast<const float4*>(pC + (int64_t)(mr0 + 4 * i) * a.ldc + nc);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (mr0 + 4 * i < pM && nc < pN) {
+            const float4 t = *reinterpret_cast<const float4*>(&stg[(4 * i + (lane >> 3)) * P_STG_STRIDE + 4 * (lane & 7)]);
+            float4 c = cv[i];
+            c.x = fmaf(a.sign, t.x, c.x);
+            c.y = fmaf(a.sign, t.y, c.y);
+            c.z = fmaf(a.sign, t.z, c.z);
+            c.w = fmaf(a.sign, t.w, c.w);
+            *reinterpret_cast<float4*>(pC + (int64_t)(mr0 + 4 * i) * a.ldc + nc) = c;
           }
         }
       }
