@@ -67,6 +67,62 @@ __global__ void __launch_bounds__(256) permute_w_kernel(const T* W, const float*
   }
 }
 
+// The same two gathers with a row at a time through shared memory, so that global memory is read and written
+// in whole rows (a thread per column gathers 2 or 4 bytes from a different sector for every element).
+// Shared memory: cols int32 (source column, -1 = dead) + one row.
+template <typename T>
+__global__ void __launch_bounds__(256) permute_w_rows_kernel(const T* __restrict__ W, const float* __restrict__ H,
+                                                             const int64_t* __restrict__ perm, int64_t rows,
+                                                             int64_t cols, float* __restrict__ Wp) {
+  extern __shared__ __align__(16) unsigned char prep_sm[];
+  int32_t* sperm = reinterpret_cast<int32_t*>(prep_sm);
+  T* srow = reinterpret_cast<T*>(sperm + cols);
+  for (int64_t j = threadIdx.x; j < cols; j += 256) {
+    const int64_t pj = perm ? perm[j] : j;
+    sperm[j] = (H[pj * cols + pj] == 0.f) ? -1 : (int32_t)pj;
+  }
+  __syncthreads();
+  constexpr int N = 16 / (int)sizeof(T);
+  const bool vec = cols % N == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* wr = W + r * cols;
+    if (vec) {
+      for (int64_t v = threadIdx.x; v < cols / N; v += 256)
+        reinterpret_cast<uint4*>(srow)[v] = reinterpret_cast<const uint4*>(wr)[v];
+    } else {
+      for (int64_t j = threadIdx.x; j < cols; j += 256) srow[j] = wr[j];
+    }
+    __syncthreads();
+    float* out = Wp + r * cols;
+    for (int64_t j = threadIdx.x; j < cols; j += 256) {
+      const int32_t p = sperm[j];
+      out[j] = p < 0 ? 0.f : Elem<T>::to_f(srow[p]);
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) unpermute_rows_kernel(const float* __restrict__ Wp,
+                                                             const int64_t* __restrict__ perm, int64_t rows,
+                                                             int64_t cols, T* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char prep_sm[];
+  int32_t* sperm = reinterpret_cast<int32_t*>(prep_sm);
+  float* srow = reinterpret_cast<float*>(sperm + cols);
+  for (int64_t j = threadIdx.x; j < cols; j += 256) sperm[j] = (int32_t)(perm ? perm[j] : j);
+  __syncthreads();
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float* wr = Wp + r * cols;
+    for (int64_t j = threadIdx.x; j < cols; j += 256) srow[sperm[j]] = wr[j];
+    __syncthreads();
+    T* o = out + r * cols;
+    for (int64_t c = threadIdx.x; c < cols; c += 256) o[c] = Elem<T>::from_f(srow[c]);
+    __syncthreads();
+  }
+}
+
+constexpr int64_t kPrepMaxSmem = 200 * 1024;
+
 template <typename T>
 __global__ void __launch_bounds__(256) unpermute_kernel(const float* Wp, const int64_t* perm, int64_t rows,
                                                         int64_t cols, T* out) {
@@ -142,6 +198,34 @@ extern "C" LC_API int lc_gptq_permute_damp(const void* W, int w_dtype, const flo
     LC_LAUNCH_CHECK();
   }
   if (!W) return LC_OK;
+  {
+    // a row at a time through shared memory when a row and the column table fit
+    const int64_t esz = w_dtype == LC_F32 ? 4 : 2;
+    const int64_t smem = cols * (4 + esz);
+    if (smem <= kPrepMaxSmem) {
+      const unsigned grid = (unsigned)(rows < 8 * kNumSMsB200 ? rows : 8 * kNumSMsB200);
+      switch (w_dtype) {
+        case LC_F32:
+          LC_CHECK_CUDA(cudaFuncSetAttribute(permute_w_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kPrepMaxSmem));
+          permute_w_rows_kernel<float><<<grid, 256, (size_t)smem, st>>>((const float*)W, H, perm, rows, cols, Wp);
+          break;
+        case LC_BF16:
+          LC_CHECK_CUDA(cudaFuncSetAttribute(permute_w_rows_kernel<__nv_bfloat16>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrepMaxSmem));
+          permute_w_rows_kernel<__nv_bfloat16><<<grid, 256, (size_t)smem, st>>>((const __nv_bfloat16*)W, H, perm, rows,
+                                                                                  cols, Wp);
+          break;
+        default:
+          LC_CHECK_CUDA(cudaFuncSetAttribute(permute_w_rows_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kPrepMaxSmem));
+          permute_w_rows_kernel<__half><<<grid, 256, (size_t)smem, st>>>((const __half*)W, H, perm, rows, cols, Wp);
+          break;
+      }
+      LC_LAUNCH_CHECK();
+      return LC_OK;
+    }
+  }
   dim3 gw((unsigned)((cols + 255) / 256), (unsigned)(rows < 1024 ? rows : 1024));
   switch (w_dtype) {
     case LC_F32: permute_w_kernel<float><<<gw, 256, 0, st>>>((const float*)W, H, perm, rows, cols, Wp); break;
@@ -160,6 +244,29 @@ extern "C" LC_API int lc_gptq_unpermute(const float* Wp, const int64_t* perm, in
   if (!Wp || !out || rows <= 0 || cols <= 0) return LC_ERR_ARG;
   if (out_dtype != LC_F32 && out_dtype != LC_BF16 && out_dtype != LC_F16) return LC_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (cols * 8 <= kPrepMaxSmem) {
+    const size_t smem = (size_t)cols * 8;
+    const unsigned grid = (unsigned)(rows < 8 * kNumSMsB200 ? rows : 8 * kNumSMsB200);
+    switch (out_dtype) {
+      case LC_F32:
+        LC_CHECK_CUDA(cudaFuncSetAttribute(unpermute_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)kPrepMaxSmem));
+        unpermute_rows_kernel<float><<<grid, 256, smem, st>>>(Wp, perm, rows, cols, (float*)out);
+        break;
+      case LC_BF16:
+        LC_CHECK_CUDA(cudaFuncSetAttribute(unpermute_rows_kernel<__nv_bfloat16>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrepMaxSmem));
+        unpermute_rows_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(Wp, perm, rows, cols, (__nv_bfloat16*)out);
+        break;
+      default:
+        LC_CHECK_CUDA(cudaFuncSetAttribute(unpermute_rows_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)kPrepMaxSmem));
+        unpermute_rows_kernel<__half><<<grid, 256, smem, st>>>(Wp, perm, rows, cols, (__half*)out);
+        break;
+    }
+    LC_LAUNCH_CHECK();
+    return LC_OK;
+  }
   dim3 g((unsigned)((cols + 255) / 256), (unsigned)(rows < 1024 ? rows : 1024));
   switch (out_dtype) {
     case LC_F32: unpermute_kernel<float><<<g, 256, 0, st>>>(Wp, perm, rows, cols, (float*)out); break;
