@@ -82,6 +82,46 @@ def test_two_rank_block_matches_single_gpu(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_two_rank_uneven_row_ranges(tmp_path):
+    """A block whose stacked subsets hold an odd number of 128-row units (hidden 384: q/k/v 9 units, o 3,
+    down 3), so the two ranks solve row ranges of different lengths and the packed gather pads the shorter
+    one: the ranks agree exactly, and q/k/v -- same inputs as on one GPU -- match the single-GPU codes."""
+    import copy
+    import torch.multiprocessing as mp
+    from lightcompress_b200 import GPTQBlockwise, IntegerQuantizer, llama_subsets
+    from oracle import gptq_ref
+    from tests.test_gpu_blockwise import _make_block, _to_cuda
+    port = 29300 + (os.getpid() % 100)
+    shape = {'hidden': 384, 'inter': 640, 'heads': 3, 'T': 256, 'n_seq': 16}
+    block, xs, kwargs = _make_block(**shape)
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    runner = GPTQBlockwise(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128, 'hessian_batch': 4})
+    gblock = copy.deepcopy(block).cuda()
+    runner.block_opt(gblock, [x.cuda() for x in xs], _to_cuda(kwargs))
+    torch.save({k: v.cpu() for k, v in runner.used_perms.items()}, os.path.join(str(tmp_path), 'pins.pt'))
+    mp.spawn(_worker, args=(2, port, str(tmp_path), {'_block': shape}), nprocs=2, join=True)
+    r0 = torch.load(os.path.join(str(tmp_path), 'r0.pt'))
+    r1 = torch.load(os.path.join(str(tmp_path), 'r1.pt'))
+    for name in r0['state']:
+        for k in r0['state'][name]:
+            assert torch.equal(r0['state'][name][k], r1['state'][name][k]), (name, k)
+    for subset in llama_subsets(gblock):
+        for name, (parent, attr) in subset.items():
+            m = getattr(parent, attr)
+            one = {'weight': m.weight.cpu(), 'buf_scales': m.buf_scales.cpu(), 'buf_zeros': m.buf_zeros.cpu(),
+                   'buf_perm': m.buf_perm.cpu()}
+            two = r0['state'][name]
+            R, C = one['weight'].shape
+            a, b = torch.empty(R, C), torch.empty(R, C)
+            a[:, one['buf_perm']] = gptq_ref.codes_permuted(one)
+            b[:, two['buf_perm']] = gptq_ref.codes_permuted(two)
+            mism = float((a != b).float().mean())
+            print(f'uneven {name} ({R} rows): 1-GPU vs 2-GPU code mismatch {mism:.4%}')
+            if name in ('self_attn.q_proj', 'self_attn.k_proj', 'self_attn.v_proj'):
+                assert mism < 1e-3, (name, mism)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
 def test_two_rank_static_groups_block_matches_single_gpu(tmp_path):
     """static_groups through the row-sharded solve: the ranks agree exactly, the buffers are every
     linear's round-to-nearest ones, and with every subset's column order pinned to the single-GPU run's
