@@ -191,14 +191,22 @@ int lc_fp8_e4m3_quant(const void* in, int dtype, int64_t rows, int64_t cols, voi
  * scales_out (fp32, ceil(rows/128) x ceil(cols/128)) may each be NULL.  block must be 128. */
 int lc_fp8_e4m3_block_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t block, void* fake_out,
                             void* codes_out, float* scales_out, lc_stream_t stream);
+
+/* The same cast with the arithmetic of the reference's Triton kernel weight_cast_to_fp8 (kernel.py:56-83), which
+ * the reference binds instead of its torch helper on GPUs with FP8 support (base_blockwise_quantization.py:22-27):
+ * scale = max|x| * fl(1/448) in fp32 (what its `/ 448.` compiles to) and no floor on the scale.  Bit-identical to
+ * that kernel's codes and scales on a B200. */
+int lc_fp8_e4m3_block_quant_triton(const void* in, int dtype, int64_t rows, int64_t cols, int64_t block, void* fake_out,
+                            void* codes_out, float* scales_out, lc_stream_t stream);
 /* out[r][c] = e4m3 value of codes[r][c] * scales[r/128][c/128], rounded once to out_dtype. */
 int lc_fp8_e4m3_block_dequant(const void* codes, const float* scales, int64_t rows, int64_t cols, int64_t block,
                               void* out, int out_dtype, lc_stream_t stream);
 
 /* The block-wise FP8 linear's forward (block_wise_fp8_forward_func, module_utils.py:41-46), the
  * reference's Triton kernels act_quant (kernel.py:7-53) and fp8_gemm (kernel.py:153-242):
- *   act_quant: per group of 128 values along the last dimension, scales[g] = max|x| / 448 (fp32, no
- *              floor), y = e4m3(x / scales[g]); n = number of elements, a multiple of 128.
+ *   act_quant: per group of 128 values along the last dimension, scales[g] = max|x| * fl(1/448) (fp32, no
+ *              floor: what the Triton kernel's `/ 448.0` computes; bit-identical to its scales and codes on a
+ *              B200), y = e4m3(x / scales[g]); n = number of elements, a multiple of 128.
  *   gemm:      c[M][N] = sum over 128-wide k blocks kb of (a[:, kb] b[:, kb]^T) * (a_s[m][kb] *
  *              b_s[n / 128][kb]); a: M x K e4m3 (row-major), a_s: M x K/128 fp32; b: N x K e4m3, b_s:
  *              ceil(N/128) x K/128 fp32; c: bf16 or fp32.  K % 128 == 0.  tcgen05 kind::f8f6f4, each k

@@ -64,6 +64,7 @@ SIGNATURES = {
     'lc_gptq_invert_factor_part': [_p, _i64, _p, _i64, _i64, _i64, _p, _p],
     'lc_gptq_invert_factor_finish': [_i64, _p, _i64, _p, _p, _p],
     'lc_fp8_e4m3_block_quant': [_p, _i, _i64, _i64, _i64, _p, _p, _p, _p],
+    'lc_fp8_e4m3_block_quant_triton': [_p, _i, _i64, _i64, _i64, _p, _p, _p, _p],
     'lc_fp8_e4m3_block_dequant': [_p, _p, _i64, _i64, _i64, _p, _i, _p],
     'lc_fp8_e4m3_act_quant': [_p, _i, _i64, _i64, _p, _p, _p],
     'lc_fp8_block_gemm': [_p, _p, _p, _p, _i64, _i64, _i64, _p, _i, _p, _p],

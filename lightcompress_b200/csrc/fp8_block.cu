@@ -19,6 +19,16 @@ namespace {
 
 constexpr int kBlk = 128;
 
+constexpr float kRcp448 = 0.002232142956927419f;      // 1 / 448 rounded to fp32
+
+// fp32 `/` as the reference's Triton kernels compile it: the full-range approximate division (within 2 ulp of
+// the quotient).  It matters where x / s falls within an ulp of the midpoint of two e4m3 values.
+__device__ __forceinline__ float div_full(float a, float b) {
+  float r;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
 struct BlockQuantArgs {
   const void* in;
   void* fake_out;
@@ -26,6 +36,7 @@ struct BlockQuantArgs {
   float* scales_out;   // (ceil(rows/128), ceil(cols/128))
   int64_t rows, cols;
   int n_col_blocks;
+  int triton_scale;    // 1: s = max|x| * fl(1/448) without a floor, as the reference's Triton kernel computes it
 };
 
 __device__ __forceinline__ float e4m3_value(uint8_t c) {
@@ -79,7 +90,7 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(BlockQuantArgs a) 
     for (int w = 1; w < 8; ++w) am = nan_max(am, red[w]);
   }
   // scales = clamp(absmax, 1e-5) / 448 in fp32 (never zero after the clamp)
-  const float s = __fdiv_rn(nan_max(am, 1e-5f), 448.f);
+  const float s = a.triton_scale ? __fmul_rn(am, kRcp448) : __fdiv_rn(nan_max(am, 1e-5f), 448.f);
   if (threadIdx.x == 0 && a.scales_out) a.scales_out[(int64_t)bi * a.n_col_blocks + bj] = s;
 
 #pragma unroll
@@ -90,7 +101,7 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(BlockQuantArgs a) 
     uint8_t cd[N];
 #pragma unroll
     for (int e = 0; e < N; ++e) {
-      const float u = __fadd_rn(__fdiv_rn(x[p][e], s), 0.f);
+      const float u = a.triton_scale ? div_full(x[p][e], s) : __fadd_rn(__fdiv_rn(x[p][e], s), 0.f);
       const __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(u, __NV_SATFINITE, __NV_E4M3);
       cd[e] = (uint8_t)c;
       fk[e] = E::from_f(__fmul_rn(__fsub_rn(e4m3_value((uint8_t)c), 0.f), s));
@@ -138,6 +149,9 @@ __global__ void __launch_bounds__(256) fp8_block_dequant_kernel(const uint8_t* _
 
 // act_quant of the block-wise FP8 linear (kernel.py:7-53): per group of 128 values, s = max|x| / 448 in
 // fp32 (no floor: an all-zero group gives s = 0 and NaN codes, like the reference), y = e4m3(x / s).
+// The Triton kernel's `/ 448.0` is a multiplication by the fp32 reciprocal (its scales on a B200 equal
+// max|x| * fl(1/448) in every case tried and the exactly rounded quotient in 41 % of them), and its
+// x / s is the full-range approximate division (div_full above).
 // One warp per group, four elements per lane.
 template <typename T>
 __global__ void __launch_bounds__(256) fp8_act_quant_kernel(const T* __restrict__ x, int64_t n_groups,
@@ -171,11 +185,11 @@ __global__ void __launch_bounds__(256) fp8_act_quant_kernel(const T* __restrict_
       float am = nan_max(nan_max(fabsf(v[u][0]), fabsf(v[u][1])), nan_max(fabsf(v[u][2]), fabsf(v[u][3])));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) am = nan_max(am, __shfl_xor_sync(0xffffffffu, am, o));
-      const float s = __fdiv_rn(am, 448.f);
+      const float s = __fmul_rn(am, kRcp448);
       uint8_t c[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        c[i] = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(v[u][i], s), __NV_SATFINITE, __NV_E4M3);
+        c[i] = (uint8_t)__nv_cvt_float_to_fp8(div_full(v[u][i], s), __NV_SATFINITE, __NV_E4M3);
       *reinterpret_cast<uint32_t*>(y + g * kBlk + lane * 4) = *reinterpret_cast<const uint32_t*>(c);
       if (lane == 0) s_out[g] = s;
     }
@@ -209,8 +223,8 @@ extern "C" LC_API int lc_fp8_e4m3_act_quant(const void* x, int dtype, int64_t n,
   return LC_OK;
 }
 
-extern "C" LC_API int lc_fp8_e4m3_block_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t block,
-                                              void* fake_out, void* codes_out, float* scales_out, lc_stream_t stream) {
+static int block_quant_impl(const void* in, int dtype, int64_t rows, int64_t cols, int64_t block, void* fake_out,
+                            void* codes_out, float* scales_out, int triton_scale, lc_stream_t stream) {
   using namespace lc;
   if (rows < 0 || cols < 0 || block != kBlk) return LC_ERR_ARG;
   if (dtype != LC_F32 && dtype != LC_BF16 && dtype != LC_F16) return LC_ERR_ARG;
@@ -227,6 +241,7 @@ extern "C" LC_API int lc_fp8_e4m3_block_quant(const void* in, int dtype, int64_t
   a.rows = rows;
   a.cols = cols;
   a.n_col_blocks = (int)((cols + kBlk - 1) / kBlk);
+  a.triton_scale = triton_scale;
   const int64_t n_blocks = ((rows + kBlk - 1) / kBlk) * a.n_col_blocks;
   if (n_blocks > 0x7fffffff) return LC_ERR_SHAPE;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -237,6 +252,17 @@ extern "C" LC_API int lc_fp8_e4m3_block_quant(const void* in, int dtype, int64_t
   }
   LC_LAUNCH_CHECK();
   return LC_OK;
+}
+
+extern "C" LC_API int lc_fp8_e4m3_block_quant(const void* in, int dtype, int64_t rows, int64_t cols, int64_t block,
+                                              void* fake_out, void* codes_out, float* scales_out, lc_stream_t stream) {
+  return block_quant_impl(in, dtype, rows, cols, block, fake_out, codes_out, scales_out, 0, stream);
+}
+
+extern "C" LC_API int lc_fp8_e4m3_block_quant_triton(const void* in, int dtype, int64_t rows, int64_t cols,
+                                                     int64_t block, void* fake_out, void* codes_out, float* scales_out,
+                                                     lc_stream_t stream) {
+  return block_quant_impl(in, dtype, rows, cols, block, fake_out, codes_out, scales_out, 1, stream);
 }
 
 extern "C" LC_API int lc_fp8_e4m3_block_dequant(const void* codes, const float* scales, int64_t rows, int64_t cols,

@@ -24,6 +24,30 @@ def act_quant(x, block_size=128):
     return y, s
 
 
+def weight_cast_to_fp8(x, block_size=128):
+    """kernel.py:73-83 (the Triton version the reference binds on GPUs with FP8 support,
+    base_blockwise_quantization.py:22-27): (e4m3 weight, fp32 scale per 128 x 128 block) with that kernel's
+    arithmetic -- scale = max|x| * fl(1/448), no floor.  `lightcompress_b200.quant.weight_cast_to_fp8` is the
+    torch helper's arithmetic (quant.py:36-45: exactly rounded quotient, floor 1e-5)."""
+    if block_size != 128:
+        raise NotImplementedError('the block-wise FP8 kernels use 128 x 128 blocks')
+    L.require_cuda(x)
+    assert x.is_contiguous() and x.dim() == 2
+    m, n = x.shape
+    y = torch.empty((m, n), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((-(-m // 128), -(-n // 128)), dtype=torch.float32, device=x.device)
+    L.call('lc_fp8_e4m3_block_quant_triton', L.ptr(x), L.lc_dtype(x), m, n, 128, None, L.ptr(y), L.ptr(s),
+           L.stream_of(x))
+    return y, s
+
+
+def weight_cast_to_bf16(x, s, block_size=128):
+    """kernel.py:115-131: e4m3 weight times its block scale (the Triton kernel writes the default dtype; its
+    callers cast to bf16, which is what this returns)."""
+    from .quant import weight_cast_to_bf16 as cast
+    return cast(x, s, block_size)
+
+
 def fp8_gemm(a, a_s, b, b_s, out_dtype=torch.bfloat16):
     """a: (..., K) e4m3 with scales a_s (..., K / 128); b: (N, K) e4m3 with scales b_s (ceil(N / 128), K / 128).
     Returns (..., N) in out_dtype (the reference allocates torch.get_default_dtype() and its caller casts

@@ -1,7 +1,7 @@
 """Block-wise FP8 linear forward (act_quant + block-scaled FP8 GEMM on tcgen05) against a restatement of
 the reference's Triton kernels' arithmetic (llmc/compression/quantization/kernel.py:7-53, :153-242) in
-torch ops.  The Triton kernels themselves cannot run where the fixtures are made, so this parity is
-not pinned to reference output."""
+torch ops, and against those Triton kernels themselves, run on the same GPU from the copy of the
+reference's package that travels with the tests (the last test: that is the pin)."""
 import pytest
 import torch
 
@@ -24,7 +24,11 @@ def test_act_quant_matches_the_restated_kernel(dtype):
     a, b = y.cpu().view(torch.uint8), ry.view(torch.uint8)
     nan = (a & 0x7f) == 0x7f
     assert torch.equal(nan, (b & 0x7f) == 0x7f) and bool(nan[0, 0, :128].all())
-    assert torch.equal(a[~nan], b[~nan])
+    # the kernel divides like the reference's Triton kernel (approximate full-range division), the restatement
+    # exactly: a quotient within an ulp of the midpoint of two e4m3 values may get the neighbouring code
+    diff = a[~nan] != b[~nan]
+    assert float(diff.float().mean()) < 1e-4
+    assert int((a[~nan][diff].int() - b[~nan][diff].int()).abs().max().item() if diff.any() else 0) <= 1
 
 
 @pytest.mark.parametrize('M,N,K', [(128, 128, 128), (300, 256, 512), (1000, 1408, 2048), (64, 200, 384),
@@ -67,3 +71,68 @@ def test_block_wise_fp8_forward_func():
     assert y.shape == (4, 96, 768) and y.dtype == torch.bfloat16
     ref = torch.nn.functional.linear(x.float(), weight_cast_to_bf16(wq, ws, 128).float(), bias.float())
     assert float((y.float() - ref).norm() / ref.norm()) < 0.05
+
+
+def _reference_triton_kernels():
+    """The reference's own Triton kernels (llmc/compression/quantization/kernel.py), loaded by file path from
+    the copy of its package that travels with the tests; None where that copy or Triton is missing."""
+    import importlib.util
+    import os
+    from oracle import ref_driver as rd
+    root = rd.find_reference()
+    if root is None:
+        return None
+    path = os.path.join(root, 'llmc', 'compression', 'quantization', 'kernel.py')
+    try:
+        import triton  # noqa: F401
+        spec = importlib.util.spec_from_file_location('llmc_ref_triton_kernels', path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+    except Exception:
+        return None
+
+
+def test_block_fp8_kernels_against_the_reference_triton_kernels_on_this_gpu():
+    """Pins the block-wise FP8 path to the reference itself: its Triton kernels act_quant, weight_cast_to_fp8,
+    weight_cast_to_bf16 and fp8_gemm (kernel.py:7-242) run on this GPU on the same inputs.  Codes and scales
+    bit for bit; the GEMM to 1e-5 of max |C| (the two accumulate the 128-wide k blocks in different orders)."""
+    ref = _reference_triton_kernels()
+    if ref is None:
+        pytest.skip('no reference copy or no Triton')
+    from lightcompress_b200.fp8_linear import act_quant, fp8_gemm
+    from lightcompress_b200.quant import weight_cast_to_bf16, weight_cast_to_fp8
+    g = torch.Generator().manual_seed(77)
+    M, N, K = 256, 384, 512
+    x = (torch.randn(M, K, generator=g) * 2).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    w[:, ::61] *= 20
+    w = w.cuda()
+    try:
+        ry, rs = ref.act_quant(x)
+        rw, rws = ref.weight_cast_to_fp8(w)
+        rback = ref.weight_cast_to_bf16(rw, rws)
+        rc = ref.fp8_gemm(ry, rs, rw, rws)
+        torch.cuda.synchronize()
+    except Exception as e:                                  # Triton without a backend for this GPU
+        pytest.skip(f'the reference Triton kernels do not compile here: {type(e).__name__}')
+    from lightcompress_b200 import fp8_linear
+    y, s = act_quant(x)
+    assert torch.equal(s, rs)
+    assert torch.equal(y.view(torch.uint8), ry.view(torch.uint8))
+    wq, ws = fp8_linear.weight_cast_to_fp8(w)
+    assert torch.equal(ws.reshape(rws.shape), rws)
+    assert torch.equal(wq.view(torch.uint8), rw.view(torch.uint8))
+    back = fp8_linear.weight_cast_to_bf16(wq, ws)
+    assert torch.equal(back, rback.to(torch.bfloat16).reshape(back.shape))      # the Triton kernel writes fp32
+    c = fp8_gemm(y, s, wq, ws, out_dtype=torch.float32)
+    err = float((c.float() - rc.float()).abs().max() / rc.float().abs().max())
+    print(f'fp8_gemm vs the reference Triton kernel: max |diff| / max |C| = {err:.2e}')
+    assert err < 1e-5
+    # the torch helper's arithmetic (quant.py:36-45), which the fixtures pin, differs from the Triton kernel's
+    # in the last bit of some scales (exact quotient against a multiplication by fl(1/448))
+    wq2, ws2 = weight_cast_to_fp8(w)
+    ulp = (ws2.reshape(rws.shape).view(torch.int32).long() - rws.view(torch.int32).long()).abs().max().item()
+    print(f'torch-helper scales vs Triton scales: max distance {ulp} ulp, '
+          f'{float((wq2.view(torch.uint8) != rw.view(torch.uint8)).float().mean()):.4%} of the codes differ')
+    assert ulp <= 1
