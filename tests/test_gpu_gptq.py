@@ -621,3 +621,36 @@ def test_row_ranges_solve_to_the_same_bits_as_the_whole(static, C):
         n_g = C // 128
         assert torch.equal(part['buf_scales'].reshape(-1, n_g), whole['buf_scales'].reshape(-1, n_g)[a:b]), (a, b)
     solver.check_status()
+
+
+def test_dead_input_channels():
+    """Input channels that are zero in every calibration token (gptq.py:139-150: their Hessian diagonal is
+    set to 1 and their weights to 0): same codes as the oracle, zero weights in the dead columns."""
+    from lightcompress_b200 import GPTQ, IntegerQuantizer
+    g = torch.Generator().manual_seed(2099)
+    R, C, ns, T = 256, 512, 8, 256
+    W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16)
+    X = _x(g, ns, T, C)
+    dead = torch.tensor([3, 130, 511])
+    X[:, :, dead] = 0
+    st = gptq_ref.hessian_init(C)
+    for i in range(ns):
+        gptq_ref.add_batch(st, X[i:i + 1])
+    ref = gptq_ref.quantize_layer(W, st['H'])
+    ref_codes = gptq_ref.codes_permuted(ref)
+    wq = IntegerQuantizer(4, False, 'per_group', group_size=128)
+    solver = GPTQ(wq, {'actorder': True, 'percdamp': 0.01, 'blocksize': 128})
+    layer = torch.nn.Linear(C, R, bias=False, dtype=torch.bfloat16).cuda()
+    layer.weight.data = W.cuda()
+    solver.layer_init(layer, 'l')
+    Xc = X.cuda()
+    for i in range(ns):
+        solver.add_batch(layer, 'l', Xc[i:i + 1])
+    res = solver.layer_transform(layer, 'l')
+    solver.check_status()
+    assert bool((layer.weight.data[:, dead.cuda()] == 0).all())
+    assert bool((ref['weight'][:, dead] == 0).all())
+    mism = _mismatch(res['codes_perm'].cpu().to(ref_codes.dtype), res['buf_perm'].cpu(), ref_codes, ref['buf_perm'])
+    print(f'dead channels: code mismatch {mism:.5%}, perm entries differing '
+          f'{int((res["buf_perm"].cpu() != ref["buf_perm"]).sum())}')
+    assert mism < CODE_MISMATCH_MAX

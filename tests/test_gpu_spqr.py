@@ -94,3 +94,32 @@ def test_layer_matches_oracle_on_the_same_gpu(R, C, T, thr):
     want = spqr_ref.w_qdq({k: out[k] if k != 'mask' else out['mask'].bool() for k in
                            ('weight', 'mask', 'buf_scales', 'buf_zeros', 'buf_perm', 'buf_invperm')}, torch.bfloat16)
     assert torch.equal(fq, want)
+
+
+def test_dead_input_channels_follow_the_reference_order_of_operations():
+    """spqr.py:143-149: the damp is a fraction of mean |diag| taken with the dead columns at 0, and a dead
+    column's diagonal becomes exactly 1 afterwards (GPTQ sets it before dampening)."""
+    g = torch.Generator().manual_seed(71)
+    R, C, T = 128, 512, 2048
+    W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    X = torch.randn(T, C, generator=g).to(torch.bfloat16)
+    dead = torch.tensor([7, 300, 510])
+    X[:, dead] = 0
+    X = X.cuda()
+    H = (X.float().t() @ X.float()) * (2.0 / 4)
+    res = spqr_ref.quantize_layer(W, H, percdamp=1.0, relative_threshold=0.2)
+    c = dict(bit=4, group=16, actorder=True, percdamp=1.0, rel_threshold=0.2, simplified=False, W=W)
+    solver, wq = _solver(c)
+    solver.h_upper = False
+    fac = solver.factorize(H, 1.0, perm=res['buf_perm'])
+    rel = float((fac['U'] - res['U']).abs().max() / res['U'].abs().max())
+    assert rel < 1e-4, rel
+    thr_dev = torch.full((1,), float(res['threshold']), dtype=torch.float32, device='cuda')
+    out = solver.solve(W, H, 1.0, factor=fac, threshold=thr_dev)
+    solver.check_status()
+    assert bool((out['weight'][:, dead.cuda()] == 0).all())
+    ours = _codes(out['weight'], out['buf_scales'], out['buf_zeros'], res['buf_perm'], 4, 16)
+    ref = _codes(res['weight'], res['buf_scales'], res['buf_zeros'], res['buf_perm'], 4, 16)
+    code_diff = float((ours != ref).float().mean())
+    print(f'spqr dead channels: codes {code_diff:.4%}, U relative difference {rel:.2e}')
+    assert code_diff < 1e-3
