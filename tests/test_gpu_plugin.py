@@ -69,7 +69,8 @@ def _codes_original_order(e, sym=False):
     return out
 
 
-@pytest.mark.parametrize('shape,schedule', [('tiny', 'b200'), ('tiny', 'reference'), ('medium', 'b200')])
+@pytest.mark.parametrize('shape,schedule', [('tiny', 'b200'), ('tiny', 'reference'), ('medium', 'b200'),
+                                            ('tiny', 'not_sequential')])
 def test_gptq_run_block_loop_and_deploy_through_the_reference_driver(ref, shape, schedule):
     # token counts of at least 16x the widest linear's columns and a vocabulary several times the hidden size
     # (the first block's inputs are embedding rows: a small vocabulary makes its Hessian rank deficient): with
@@ -82,8 +83,14 @@ def test_gptq_run_block_loop_and_deploy_through_the_reference_driver(ref, shape,
         cfg, n, T = rd.tiny_llama_config(hidden=1280, inter=2560, heads=10, layers=2, vocab=8192, max_pos=2048), 24, 2048
     calib = rd.calib_ids(n, T, cfg.vocab_size, seed=5)
     probe = rd.calib_ids(1, T, cfg.vocab_size, seed=6)[0]['input_ids']
-    qc = rd.gptq_quant_config({'b200_schedule': schedule} if schedule != 'b200' else None)
-    a = _run(ref, rd.gptq_quant_config(), cfg, calib, T, 3, False, probe)
+    if schedule == 'not_sequential':
+        # true_sequential False: every linear of a block is solved on the unquantised block's activations
+        # (base_blockwise_quantization.py:487-527 without the re-forwards)
+        qc = rd.gptq_quant_config({'true_sequential': False})
+        a = _run(ref, rd.gptq_quant_config({'true_sequential': False}), cfg, calib, T, 3, False, probe)
+    else:
+        qc = rd.gptq_quant_config({'b200_schedule': schedule} if schedule != 'b200' else None)
+        a = _run(ref, rd.gptq_quant_config(), cfg, calib, T, 3, False, probe)
     b = _run(ref, qc, cfg, calib, T, 3, True, probe)
     err_a = float((a['logits'] - a['logits_fp']).norm() / a['logits_fp'].norm())
     err_b = float((b['logits'] - b['logits_fp']).norm() / b['logits_fp'].norm())
